@@ -1,0 +1,233 @@
+// Internal definitions shared by the host-side C layer and the CUDA kernels.
+//
+// Device storage convention: every activation tensor is NHWC with the channel count padded
+// up to a multiple of 4 (`cp`), so that each pixel row is a whole number of 16-byte cells and is
+// a legal TMA / vector-load operand.  Pad channels always hold 0.  Weights use the same
+// convention with (n=filters, h=w=size, c=input channels): [filter][tap][cp].
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+#include <vector>
+
+#include "../../include/aet_b200.h"
+
+#define AET_STATUS_TIMEOUT 1
+
+void aet_set_error(const char *fmt, ...);
+
+#define AET_CUDA(call)                                                                              \
+    do {                                                                                            \
+        cudaError_t e__ = (call);                                                                   \
+        if (e__ != cudaSuccess) {                                                                   \
+            aet_set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), __FILE__, __LINE__); \
+            return AET_E_CUDA;                                                                      \
+        }                                                                                           \
+    } while (0)
+
+#define AET_TRY(call)                  \
+    do {                               \
+        int r__ = (call);              \
+        if (r__ != AET_OK) return r__; \
+    } while (0)
+
+static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+static inline size_t round_up_sz(size_t v, size_t m) { return (v + m - 1) / m * m; }
+
+struct ProfileRecord {
+    const char *name;
+    double bytes, flops;
+    cudaEvent_t e0, e1;
+};
+
+struct aet_context {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    aet_parity_mode parity = AET_PARITY_MTCS;
+    aet_math_mode math = AET_MATH_TF32;
+    int conv_path = 0;  // 0 auto (TMA where the shape allows), 1 force gather producer
+    // staging buffer for NCHW <-> NHWC host taps
+    float *staging = nullptr;
+    size_t staging_bytes = 0;
+    float *pinned = nullptr;  // pinned host mirror used by async uploads
+    size_t pinned_bytes = 0;
+    // scratch arena (split-K partials, reduction partials)
+    float *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    int *status_dev = nullptr;  // device status word written by bounded waits
+    // profiling
+    bool profiling = false;
+    std::vector<ProfileRecord> records;
+    std::vector<cudaEvent_t> event_pool;
+    size_t event_next = 0;
+    long launches = 0;
+    bool capturing = false;
+};
+
+struct aet_tensor {
+    aet_context *ctx = nullptr;
+    int n = 0, c = 0, h = 0, w = 0, cp = 0;
+    float *d = nullptr;
+    bool owns = true;
+    // Logically all-zero without having been cleared: the next writer overwrites instead of
+    // accumulating, and host reads return zeros.  Lets the network skip one memset per layer.
+    bool lazy_zero = false;
+    size_t count() const { return (size_t)n * c * h * w; }
+    size_t elems() const { return (size_t)n * h * w * cp; }  // device floats
+    size_t pixels() const { return (size_t)n * h * w; }
+};
+
+// One contiguous run of parameters inside the arena, a multiple of 1024 floats long.
+struct ParamSegment {
+    size_t offset = 0, count = 0, padded = 0;
+};
+
+struct ParamArena {
+    float *W = nullptr, *U = nullptr, *G = nullptr;  // values, momentum, per-step gradient
+    size_t capacity = 0, used = 0;
+    bool owns = false;
+};
+
+struct aet_layer {
+    aet_context *ctx = nullptr;
+    aet_network *net = nullptr;
+    aet_layer_type type = AET_CONVOLUTIONAL;
+    int index = 0;
+    int batch = 0, c = 0, h = 0, w = 0, cp = 0;         // input
+    int oc = 0, oh = 0, ow = 0, ocp = 0;                // output
+    int size = 1, stride_x = 1, stride_y = 1, pad = 0;  // conv / pool (pool: pad = padding)
+    int bn = 0, train = 1;
+    aet_activation act = AET_LINEAR;
+    float lr_scale = 1.0f;
+    aet_tensor *output = nullptr, *delta = nullptr, *x = nullptr;  // x: conv result before BN
+    // parameters (slices of an arena)
+    ParamArena *arena = nullptr;
+    ParamArena own_arena;
+    ParamSegment seg_w, seg_b, seg_s;
+    float *mean = nullptr, *variance = nullptr, *rolling_mean = nullptr, *rolling_variance = nullptr;
+    float *inv_std = nullptr;            // per-channel 1/std in the parity mode's form
+    float *bwd_coef = nullptr;           // [3][ocp] coefficients of the BN backward apply pass
+    float *shift = nullptr;              // BN statistics shift (first pixel of each channel)
+    // pooling
+    int *indexes = nullptr;
+    // softmax
+    int groups = 1;
+    float temperature = 1.0f;
+    float *loss = nullptr, *sample_loss = nullptr, *cost_dev = nullptr;
+    float cost_host = 0.0f;
+    bool cost_valid = false;
+    // dropout
+    float probability = 0.0f;
+    float *rnd = nullptr;
+    bool rnd_fixed = false;  // uniforms were supplied by the caller; forward does not regenerate
+    aet_layer *prev = nullptr;
+    uint64_t seed = 0;
+    unsigned long long *step_dev = nullptr;
+    // TMA descriptors are built lazily per (layer, pass, operand address)
+    void *tma_cache = nullptr;
+};
+
+struct aet_network {
+    aet_context *ctx = nullptr;
+    std::vector<aet_layer *> layers;
+    int batch = 1, subdivisions = 1, c = 0, h = 0, w = 0, train = 1;
+    float learning_rate = 0.001f, momentum = 0.9f, decay = 0.0001f;
+    int policy = 0;  // 0 constant 1 step 2 steps 3 exp 4 poly 5 sig
+    int burn_in = 0, max_batches = 0, step = 1, num_steps = 0;
+    float power = 4.0f, gamma = 1.0f, scale = 1.0f;
+    std::vector<int> steps;
+    std::vector<float> scales;
+    int64_t seen = 0, cur_iteration = 0;
+    float loss_scale = 1.0f;
+    int try_fix_nan = 0;
+    aet_tensor *input = nullptr, *truth = nullptr;
+    ParamArena arena;
+    // SGD launch tables
+    int *block_seg = nullptr;    // per 1024-float block: segment id
+    float *seg_table = nullptr;  // per segment: lr multiplier, decay flag
+    int n_blocks = 0, n_segments = 0;
+    float *hyper_dev = nullptr;  // {lr/B, momentum, -decay*B*loss_scale, unused}
+    float hyper_host[4] = {0, 0, 0, 0};
+    float *loss_pinned = nullptr;
+    // CUDA graph of one train step
+    bool use_graph = false;
+    cudaGraphExec_t graph_exec = nullptr;
+    int update_batch_world = 0;  // batch * world for data parallel
+    // data parallel
+    void *comm = nullptr;
+    int rank = 0, world = 1;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t ev_grad_ready[8] = {nullptr}, ev_comm_done = nullptr;
+    long launches_per_step = 0;
+};
+
+// ---- launch bookkeeping -----------------------------------------------------------------
+void prof_begin(aet_context *ctx, const char *name, double bytes, double flops);
+void prof_end(aet_context *ctx);
+struct LaunchScope {
+    aet_context *ctx;
+    LaunchScope(aet_context *c, const char *name, double bytes, double flops) : ctx(c) {
+        ctx->launches++;
+        if (ctx->profiling) prof_begin(ctx, name, bytes, flops);
+    }
+    ~LaunchScope() {
+        if (ctx->profiling) prof_end(ctx);
+    }
+};
+int aet_check_launch(const char *what);
+int ctx_scratch(aet_context *ctx, size_t bytes, float **out);
+int ctx_staging(aet_context *ctx, size_t bytes);
+
+// ---- layout taps (tensor.cu) ------------------------------------------------------------------
+int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int n, int c, int h, int w, int cp,
+                       bool async_pinned);
+int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp);
+int tensor_download_nchw(aet_context *ctx, const float *dev_nhwc, float *host, int n, int c, int h, int w, int cp);
+int tensor_download_nchw_int(aet_context *ctx, const int *dev_nhwc, int *host, int n, int c, int h, int w, int cp);
+int vector_upload(aet_context *ctx, float *dev, const float *host, size_t count);
+int vector_download(aet_context *ctx, const float *dev, float *host, size_t count);
+
+// ---- kernels (launchers return AET_OK or an error) ----------------------------------------------
+struct ConvGeom {
+    int N, C, H, W, cp;      // input activation
+    int K, OH, OW, kp;       // output activation
+    int R, S, sy, sx, pad;
+};
+int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue);
+int conv_dgrad(aet_layer *l, const float *dy, float *dx);
+int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate);
+void conv_release(aet_layer *l);
+
+int k_bn_stats(aet_layer *l, int update_rolling);
+int k_bn_apply(aet_layer *l, int use_rolling);
+int k_bn_backward(aet_layer *l);
+int k_bias_act_backward(aet_layer *l);
+int k_maxpool_forward(aet_layer *l, const float *x);
+int k_maxpool_backward(aet_layer *l, float *prev_delta, int accumulate);
+int k_avgpool_forward(aet_layer *l, const float *x);
+int k_avgpool_backward(aet_layer *l, float *prev_delta, int accumulate);
+int k_softmax_forward(aet_layer *l, const float *x, const float *truth);
+int k_axpy(aet_context *ctx, float *y, const float *x, float a, size_t n, int accumulate, const char *name);
+int k_dropout_forward(aet_layer *l, float *x, int generate);
+int k_dropout_backward(aet_layer *l, float *delta);
+int k_fill(aet_context *ctx, float *p, float v, size_t n);
+int k_step_counter(aet_context *ctx, unsigned long long *ctr);
+int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, float lr_over_b, float momentum,
+                  float decay_term);
+int k_sgd_arena(aet_network *net);
+int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev);
+
+// parameter pointers
+static inline float *layer_W(aet_layer *l) { return l->arena->W + l->seg_w.offset; }
+static inline float *layer_U(aet_layer *l) { return l->arena->U + l->seg_w.offset; }
+static inline float *layer_G(aet_layer *l) { return l->arena->G + l->seg_w.offset; }
+static inline float *layer_b(aet_layer *l) { return l->arena->W + l->seg_b.offset; }
+static inline float *layer_bU(aet_layer *l) { return l->arena->U + l->seg_b.offset; }
+static inline float *layer_bG(aet_layer *l) { return l->arena->G + l->seg_b.offset; }
+static inline float *layer_s(aet_layer *l) { return l->arena->W + l->seg_s.offset; }
+static inline float *layer_sU(aet_layer *l) { return l->arena->U + l->seg_s.offset; }
+static inline float *layer_sG(aet_layer *l) { return l->arena->G + l->seg_s.offset; }

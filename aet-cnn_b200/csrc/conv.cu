@@ -1,0 +1,544 @@
+// Convolution forward / backward-data / backward-weight as implicit GEMMs on the sm_100a
+// tensor cores (tcgen05.mma kind::tf32, FP32 accumulators in TMEM).  No im2col buffer exists:
+// operand tiles are assembled in shared memory straight from the NHWC activations.
+//
+// Replaces the per-image im2col + SGEMM (+ col2im) loops of the reference:
+//   forward   mtcs/MtcsConvLayer.c:78-149   (dnn/ConvolutionalLayer.c:717-806)
+//   backward  mtcs/MtcsConvLayer.c:332-409  (dnn/ConvolutionalLayer.c:909-947)
+//
+// GEMM views (M x N x K), all with a 128-row M tile:
+//   fprop  M = output pixels (n,oh,ow)   N = filters           K = (tap, input channel)
+//   dgrad  M = input pixels  (n,h,w)     N = input channels    K = (tap, filter)
+//   wgrad  M = filters                   N = (tap, in channel) K = output pixels, split over CTAs
+//
+// Two producers feed the same MMA/epilogue skeleton:
+//   * gather producer: 128 threads build the tiles with 16-byte loads into the un-swizzled
+//     core-matrix layout (any size / stride / padding / ragged edge);
+//   * TMA producer (conv_tma.cuh): one thread issues tiled bulk-tensor copies with out-of-bounds
+//     zero fill into 128-byte-swizzled tiles (stride-1 convolutions whose 128-pixel tile is a
+//     whole number of image rows, channel count a multiple of 32).
+//
+// CTA = 5 warps: warps 0-3 produce and later run the epilogue (TMEM lane quarter = warp id),
+// warp 4 allocates TMEM and its lane 0 issues every MMA.
+#include "common.h"
+#include "umma.cuh"
+
+using namespace umma;
+
+namespace {
+
+enum { KIND_FPROP = 0, KIND_DGRAD = 1, KIND_WGRAD = 2 };
+constexpr int BM = 128;        // MMA M
+constexpr int BK = 32;         // K elements per pipeline stage (4 MMAs of K=8)
+constexpr int MAX_STAGES = 6;
+constexpr int NTHREADS = 160;
+
+struct ConvArgs {
+    ConvGeom g;
+    const float *src_a;   // fprop: x      dgrad: dy      wgrad: dy
+    const float *src_b;   // fprop: w      dgrad: w       wgrad: x
+    float *out;           // fprop: y      dgrad: dx      wgrad: split-K partials
+    const float *bias;    // fprop epilogue, may be null
+    int act;              // fprop epilogue activation
+    int bn;               // N tile (multiple of 16, <= 256)
+    int n_rows, n_cols;   // valid GEMM M and N extents
+    int k_total;          // GEMM K extent
+    int k_per_split;      // K handled by one blockIdx.z (multiple of BK)
+    int out_ld;
+    long long split_stride;
+    int stages, x3, tmem_cols;
+    int *status;
+};
+
+struct SharedCtl {
+    unsigned long long full[MAX_STAGES];
+    unsigned long long empty[MAX_STAGES];
+    unsigned long long accum;
+    uint32_t tmem_base;
+    int abort_flag;
+    int4 jtab[64];  // wgrad: per 4-column chunk of the N tile -> {r, s, c, valid}
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == AET_LEAKY) return v > 0.f ? v : 0.1f * v;
+    if (act == AET_RELU) return v > 0.f ? v : 0.f;
+    return v;
+}
+
+__device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+
+__device__ __forceinline__ void st_cell(unsigned char *stage, uint32_t off, uint32_t lo_off, float4 v, int x3) {
+    if (x3) {
+        float4 hi, lo;
+        hi.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+        hi.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+        hi.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+        hi.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+        lo.x = v.x - hi.x; lo.y = v.y - hi.y; lo.z = v.z - hi.z; lo.w = v.w - hi.w;
+        *reinterpret_cast<float4 *>(stage + off) = hi;
+        *reinterpret_cast<float4 *>(stage + lo_off + off) = lo;
+    } else {
+        *reinterpret_cast<float4 *>(stage + off) = v;
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ SharedCtl ctl;
+
+    const ConvGeom &g = a.g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM;
+    const int n0 = blockIdx.y * a.bn;
+    const int bn = a.bn;
+    const int k_begin = (KIND == KIND_WGRAD) ? blockIdx.z * a.k_per_split : 0;
+    int k_end = (KIND == KIND_WGRAD) ? k_begin + a.k_per_split : a.k_total;
+    if (k_end > a.k_total) k_end = a.k_total;
+    const int nslabs = (k_end > k_begin) ? (k_end - k_begin + BK - 1) / BK : 0;
+
+    const uint32_t a_bytes = BM * BK * 4;
+    const uint32_t b_bytes = bn * BK * 4;
+    const uint32_t half_bytes = a_bytes + b_bytes;            // one precision half of a stage
+    const uint32_t stage_bytes = half_bytes * (a.x3 ? 2 : 1);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 128);
+            mbar_init(smem_u32(&ctl.empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl.accum), 1);
+        ctl.abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (KIND == KIND_WGRAD && threadIdx.x < 64) {
+        int4 e = make_int4(0, 0, 0, 0);
+        int j = n0 + threadIdx.x * 4;
+        if ((int)threadIdx.x * 4 < bn && j < a.n_cols) {
+            int tap = j / g.cp;
+            e.z = j - tap * g.cp;
+            e.x = tap / g.S;
+            e.y = tap - e.x * g.S;
+            e.w = 1;
+        }
+        ctl.jtab[threadIdx.x] = e;
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = ctl.tmem_base;
+    volatile int *abort_flag = &ctl.abort_flag;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ producer
+        // K-major operands: a thread owns 4 rows x 2 sixteen-byte cells; a warp instruction
+        // touches 8 rows x 4 cells (128 contiguous bytes of shared memory per quarter warp).
+        int rinfo_base[4], rinfo_y[4], rinfo_x[4];
+        if (KIND != KIND_WGRAD) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int m = m0 + (warp + 4 * i) * 8 + (lane & 7);
+                if (m < a.n_rows) {
+                    if (KIND == KIND_FPROP) {
+                        int n = m / (g.OH * g.OW);
+                        int rem = m - n * g.OH * g.OW;
+                        int oh = rem / g.OW, ow = rem - oh * g.OW;
+                        rinfo_base[i] = n * g.H * g.W;
+                        rinfo_y[i] = oh * g.sy - g.pad;
+                        rinfo_x[i] = ow * g.sx - g.pad;
+                    } else {
+                        int n = m / (g.H * g.W);
+                        int rem = m - n * g.H * g.W;
+                        int h = rem / g.W, w = rem - h * g.W;
+                        rinfo_base[i] = n * g.OH * g.OW;
+                        rinfo_y[i] = h + g.pad;
+                        rinfo_x[i] = w + g.pad;
+                    }
+                } else {
+                    rinfo_base[i] = 0;
+                    rinfo_y[i] = -(1 << 28);
+                    rinfo_x[i] = -(1 << 28);
+                }
+            }
+        }
+        const int kc_lo = lane >> 3;  // first of the thread's two K cells (second is +4)
+        const int nb_groups = bn / 16;  // B groups handled per warp
+
+        for (int it = 0; it < nslabs; ++it) {
+            const int s = it % a.stages;
+            const uint32_t phase = (it / a.stages) & 1;
+            const int k0 = k_begin + it * BK;
+            unsigned char *stage = smem + (size_t)s * stage_bytes;
+            float4 va[8];
+            uint32_t oa[8];
+
+            if (KIND != KIND_WGRAD) {
+                // ---- A: K-major gather
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int kc = kc_lo + 4 * h;
+                    const int kk = k0 + kc * 4;
+                    int tap = 0, ch = 0, r = 0, sx_ = 0;
+                    const bool kvalid = kk < k_end;
+                    const int inner = (KIND == KIND_FPROP) ? g.cp : g.kp;
+                    if (kvalid) {
+                        tap = kk / inner;
+                        ch = kk - tap * inner;
+                        r = tap / g.S;
+                        sx_ = tap - r * g.S;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (kvalid) {
+                            if (KIND == KIND_FPROP) {
+                                int ih = rinfo_y[i] + r, iw = rinfo_x[i] + sx_;
+                                if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+                                    v = ldg4(a.src_a + ((size_t)(rinfo_base[i] + ih * g.W + iw) * g.cp + ch));
+                            } else {
+                                int th = rinfo_y[i] - r, tw = rinfo_x[i] - sx_;
+                                if (th >= 0 && tw >= 0) {
+                                    int oh = th / g.sy, ow = tw / g.sx;
+                                    if (oh * g.sy == th && ow * g.sx == tw && oh < g.OH && ow < g.OW)
+                                        v = ldg4(a.src_a + ((size_t)(rinfo_base[i] + oh * g.OW + ow) * g.kp + ch));
+                                }
+                            }
+                        }
+                        const int row = (warp + 4 * i) * 8 + (lane & 7);
+                        va[h * 4 + i] = v;
+                        oa[h * 4 + i] = (uint32_t)kc * (BM * 16) + (uint32_t)row * 16;
+                    }
+                }
+            } else {
+                // ---- A: MN-major gather from dy: one pixel per thread, 8 channel cells
+                const int kq = warp * 8 + (lane & 7);
+                const int p = k0 + kq;
+                const bool pvalid = p < k_end;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int mc = i * 4 + (lane >> 3);
+                    const int ko = m0 + mc * 4;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (pvalid && ko < g.kp) v = ldg4(a.src_a + ((size_t)p * g.kp + ko));
+                    va[i] = v;
+                    oa[i] = (uint32_t)warp * (BM * 32) + (uint32_t)mc * 128 + (uint32_t)(lane & 7) * 16;
+                }
+            }
+
+            if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st_cell(stage, oa[i], half_bytes, va[i], a.x3);
+
+            // ---- B
+            unsigned char *stage_b = stage + a_bytes;
+            if (KIND == KIND_FPROP) {
+                // K-major, rows = filters
+                for (int i = 0; i < nb_groups; ++i) {
+                    const int gi = warp + 4 * i;
+                    const int rb = gi % (bn / 8), half = gi / (bn / 8);
+                    const int row = rb * 8 + (lane & 7);
+                    const int kc = half * 4 + (lane >> 3);
+                    const int kk = k0 + kc * 4;
+                    const int j = n0 + row;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (j < g.K && kk < k_end) v = ldg4(a.src_b + ((size_t)j * a.k_total + kk));
+                    st_cell(stage_b, (uint32_t)kc * (bn * 16) + (uint32_t)row * 16, half_bytes, v, a.x3);
+                }
+            } else if (KIND == KIND_DGRAD) {
+                // MN-major, rows = input channels (contiguous in the weight tensor), K = (tap, filter)
+                const int kq = warp * 8 + (lane & 7);
+                const int kk = k0 + kq;
+                int tap = 0, ko = 0;
+                const bool kvalid = kk < k_end;
+                if (kvalid) { tap = kk / g.kp; ko = kk - tap * g.kp; }
+                const bool fvalid = kvalid && ko < g.K;
+                const float *wrow = a.src_b + ((size_t)ko * (g.R * g.S) + tap) * g.cp;
+                for (int i = 0; i < nb_groups; ++i) {
+                    const int mc = i * 4 + (lane >> 3);
+                    const int c = n0 + mc * 4;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (fvalid && c < g.cp) v = ldg4(wrow + c);
+                    st_cell(stage_b, (uint32_t)warp * (bn * 32) + (uint32_t)mc * 128 + (uint32_t)(lane & 7) * 16,
+                            half_bytes, v, a.x3);
+                }
+            } else {
+                // MN-major gather from x, rows = (tap, channel), K = output pixel
+                const int kq = warp * 8 + (lane & 7);
+                const int p = k0 + kq;
+                const bool pvalid = p < k_end;
+                int nb = 0, ih0 = 0, iw0 = 0;
+                if (pvalid) {
+                    int n = p / (g.OH * g.OW);
+                    int rem = p - n * g.OH * g.OW;
+                    int oh = rem / g.OW, ow = rem - oh * g.OW;
+                    nb = n * g.H * g.W;
+                    ih0 = oh * g.sy - g.pad;
+                    iw0 = ow * g.sx - g.pad;
+                }
+                for (int i = 0; i < nb_groups; ++i) {
+                    const int mc = i * 4 + (lane >> 3);
+                    const int4 e = ctl.jtab[mc];
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (pvalid && e.w) {
+                        int ih = ih0 + e.x, iw = iw0 + e.y;
+                        if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+                            v = ldg4(a.src_b + ((size_t)(nb + ih * g.W + iw) * g.cp + e.z));
+                    }
+                    st_cell(stage_b, (uint32_t)warp * (bn * 32) + (uint32_t)mc * 128 + (uint32_t)(lane & 7) * 16,
+                            half_bytes, v, a.x3);
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&ctl.full[s]));
+        }
+
+        // ------------------------------------------------------------------ epilogue
+        bool ready = nslabs == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
+        tc_fence_after_sync();
+        const int row = m0 + warp * 32 + lane;
+        const bool row_ok = row < a.n_rows;
+        float *orow = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)row * a.out_ld;
+        if (ready) {
+            for (int cc = 0; cc < bn; cc += 16) {
+                float v[16];
+                if (nslabs > 0) {
+                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) v[q] = 0.f;
+                }
+                if (!row_ok) continue;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int col = n0 + cc + q * 4;
+                    if (col >= a.n_cols) continue;
+                    float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                    if (KIND == KIND_FPROP) {
+                        if (a.bias) {
+                            float4 b = ldg4(a.bias + col);
+                            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                        }
+                        o.x = apply_act(o.x, a.act); o.y = apply_act(o.y, a.act);
+                        o.z = apply_act(o.z, a.act); o.w = apply_act(o.w, a.act);
+                    }
+                    *reinterpret_cast<float4 *>(orow + col) = o;
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        const int a_mn = (KIND == KIND_WGRAD) ? 1 : 0;
+        const int b_mn = (KIND == KIND_FPROP) ? 0 : 1;
+        const uint32_t idesc = make_idesc_tf32(BM, bn, a_mn, b_mn);
+        uint32_t accumulate = 0;
+        for (int it = 0; it < nslabs; ++it) {
+            const int s = it % a.stages;
+            const uint32_t phase = (it / a.stages) & 1;
+            if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
+            const uint32_t sb = sa + a_bytes;
+            const int k0 = k_begin + it * BK;
+            int ksteps = (k_end - k0 + 7) / 8;
+            if (ksteps > 4) ksteps = 4;
+            for (int j = 0; j < ksteps; ++j) {
+                uint32_t a_addr, b_addr, a_lbo, b_lbo;
+                if (a_mn) { a_addr = sa + j * (BM * 32); a_lbo = BM * 32; }
+                else      { a_addr = sa + j * 2 * (BM * 16); a_lbo = BM * 16; }
+                if (b_mn) { b_addr = sb + j * (bn * 32); b_lbo = bn * 32; }
+                else      { b_addr = sb + j * 2 * (bn * 16); b_lbo = bn * 16; }
+                const uint64_t da = make_desc(a_addr, a_lbo, 128, LAYOUT_NONE);
+                const uint64_t db = make_desc(b_addr, b_lbo, 128, LAYOUT_NONE);
+                if (a.x3) {
+                    const uint64_t da_lo = make_desc(a_addr + half_bytes, a_lbo, 128, LAYOUT_NONE);
+                    const uint64_t db_lo = make_desc(b_addr + half_bytes, b_lbo, 128, LAYOUT_NONE);
+                    mma_tf32(tmem, da_lo, db, idesc, accumulate);
+                    mma_tf32(tmem, da, db_lo, idesc, 1);
+                    mma_tf32(tmem, da, db, idesc, 1);
+                } else {
+                    mma_tf32(tmem, da, db, idesc, accumulate);
+                }
+                accumulate = 1;
+            }
+            mma_commit(smem_u32(&ctl.empty[s]));
+        }
+        mma_commit(smem_u32(&ctl.accum));
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        tmem_dealloc(tmem, a.tmem_cols);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+    }
+}
+
+// Fixed-order second stage of the split-K weight gradient: dw (+)= sum over splits.
+__global__ void wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dw, size_t count4,
+                                    int splits, size_t split_stride, int accumulate) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count4) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        float4 v = __ldg(reinterpret_cast<const float4 *>(partial + (size_t)s * split_stride) + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float4 *o = reinterpret_cast<float4 *>(dw) + i;
+    if (accumulate) {
+        float4 p = *o;
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    *o = acc;
+}
+
+int pow2_cols(int n) {
+    int c = 32;
+    while (c < n) c <<= 1;
+    return c;
+}
+
+ConvGeom layer_geom(const aet_layer *l) {
+    ConvGeom g;
+    g.N = l->batch; g.C = l->c; g.H = l->h; g.W = l->w; g.cp = l->cp;
+    g.K = l->oc; g.OH = l->oh; g.OW = l->ow; g.kp = l->ocp;
+    g.R = l->size; g.S = l->size; g.sy = l->stride_y; g.sx = l->stride_x; g.pad = l->pad;
+    return g;
+}
+
+int pick_bn(int n_cols, int m_tiles, int sm_count) {
+    int full = round_up(n_cols, 16);
+    if (full <= 64) return full;
+    const int cands[3] = {256, 128, 64};
+    for (int i = 0; i < 3; ++i) {
+        int bn = cands[i] < full ? cands[i] : full;
+        int n_tiles = (n_cols + bn - 1) / bn;
+        if (m_tiles * n_tiles >= sm_count) return bn;
+    }
+    return full < 64 ? full : 64;
+}
+
+template <int KIND>
+int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, double flops) {
+    a.x3 = ctx->math == AET_MATH_3XTF32 ? 1 : 0;
+    a.tmem_cols = pow2_cols(a.bn);
+    a.status = ctx->status_dev;
+    const size_t half = (size_t)BM * BK * 4 + (size_t)a.bn * BK * 4;
+    const size_t stage = half * (a.x3 ? 2 : 1);
+    int stages = (int)((96 * 1024) / stage);
+    if (stages < 3) stages = (int)((200 * 1024) / stage);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) stages = 2;
+    a.stages = stages;
+    const size_t smem_bytes = stage * stages;
+    static bool attr_set[3] = {false, false, false};
+    if (!attr_set[KIND]) {
+        AET_CUDA(cudaFuncSetAttribute(conv_gather_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set[KIND] = true;
+    }
+    LaunchScope scope(ctx, name, 0, flops);
+    conv_gather_kernel<KIND><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(a);
+    return aet_check_launch(name);
+}
+
+}  // namespace
+
+#include "conv_tma.cuh"
+
+int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue) {
+    aet_context *ctx = l->ctx;
+    ConvArgs a = {};
+    a.g = layer_geom(l);
+    const ConvGeom &g = a.g;
+    a.src_a = x; a.src_b = layer_W(l); a.out = y; a.bias = bias;
+    a.act = act_in_epilogue ? (int)l->act : (int)AET_LINEAR;
+    a.n_rows = g.N * g.OH * g.OW;
+    a.n_cols = g.kp;
+    a.k_total = g.R * g.S * g.cp;
+    a.k_per_split = a.k_total;
+    a.out_ld = g.kp;
+    const int m_tiles = (a.n_rows + BM - 1) / BM;
+    a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    int r = tma_fprop(l, a, flops);
+    if (r != 1) return r;   // 1 = shape not eligible for the TMA producer
+    dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
+    return launch_gather<KIND_FPROP>(ctx, a, grid, "conv_fprop_gather", flops);
+}
+
+int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
+    aet_context *ctx = l->ctx;
+    ConvArgs a = {};
+    a.g = layer_geom(l);
+    const ConvGeom &g = a.g;
+    a.src_a = dy; a.src_b = layer_W(l); a.out = dx;
+    a.n_rows = g.N * g.H * g.W;
+    a.n_cols = g.cp;
+    a.k_total = g.R * g.S * g.kp;
+    a.k_per_split = a.k_total;
+    a.out_ld = g.cp;
+    const int m_tiles = (a.n_rows + BM - 1) / BM;
+    a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    int r = tma_dgrad(l, a, flops);
+    if (r != 1) return r;
+    dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
+    return launch_gather<KIND_DGRAD>(ctx, a, grid, "conv_dgrad_gather", flops);
+}
+
+int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate) {
+    aet_context *ctx = l->ctx;
+    ConvArgs a = {};
+    a.g = layer_geom(l);
+    const ConvGeom &g = a.g;
+    a.src_a = dy; a.src_b = x;
+    a.n_rows = g.K;
+    a.n_cols = g.R * g.S * g.cp;
+    a.k_total = g.N * g.OH * g.OW;
+    a.out_ld = a.n_cols;
+    const int m_tiles = (g.K + BM - 1) / BM;
+    // N tile: the multiple of 16 (<= 256) that wastes the fewest padded columns, larger on ties
+    int best_bn = 16, best_pad = 1 << 30;
+    const int full = round_up(a.n_cols, 16);
+    if (full <= 256) best_bn = full;
+    else
+        for (int bn = 256; bn >= 64; bn -= 16) {
+            int padded = (a.n_cols + bn - 1) / bn * bn;
+            if (padded < best_pad) { best_pad = padded; best_bn = bn; }
+        }
+    a.bn = best_bn;
+    const int n_tiles = (a.n_cols + a.bn - 1) / a.bn;
+    const int total_slabs = (a.k_total + BK - 1) / BK;
+    int want = (2 * ctx->sm_count) / (m_tiles * n_tiles);
+    if (want < 1) want = 1;
+    int max_splits = total_slabs / 4;
+    if (max_splits < 1) max_splits = 1;
+    if (want > max_splits) want = max_splits;
+    const int slabs_per_split = (total_slabs + want - 1) / want;
+    const int splits = (total_slabs + slabs_per_split - 1) / slabs_per_split;
+    a.k_per_split = slabs_per_split * BK;
+    const size_t out_floats = (size_t)g.K * a.n_cols;
+    a.split_stride = (long long)out_floats;
+    float *partial = nullptr;
+    AET_TRY(ctx_scratch(ctx, out_floats * splits * sizeof(float), &partial));
+    a.out = partial;
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    int r = tma_wgrad(l, a, splits, flops);
+    if (r == 1) {
+        dim3 grid(m_tiles, n_tiles, splits);
+        r = launch_gather<KIND_WGRAD>(ctx, a, grid, "conv_wgrad_gather", flops);
+    }
+    if (r != AET_OK) return r;
+    {
+        const size_t count4 = out_floats / 4;
+        LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (splits + 1 + (accumulate ? 1 : 0)), 0);
+        wgrad_reduce_kernel<<<(unsigned)((count4 + 255) / 256), 256, 0, ctx->stream>>>(partial, dw, count4, splits,
+                                                                                        out_floats, accumulate);
+        return aet_check_launch("wgrad_reduce");
+    }
+}
+
+void conv_release(aet_layer *l) { tma_release(l); }

@@ -1,0 +1,409 @@
+// TMA producer variant of the implicit-GEMM convolution kernels (included by conv.cu).
+//
+// Eligible shapes: stride 1, padded channel counts that are multiples of 32, and a 128-pixel M
+// tile (fprop, dgrad) or 32-pixel K slab (wgrad) that is a whole number of image rows or whole
+// images.  One thread issues tiled bulk-tensor copies whose coordinates are shifted by the filter
+// tap; pixels outside the image are zero-filled by the copy engine, so there is no halo logic and
+// no im2col buffer.  Tiles land in shared memory in the 128-byte swizzled layout that the
+// tcgen05 descriptors name directly.  Only plain per-CTA tensor copies are used.
+//
+// Return convention of tma_fprop / tma_dgrad / tma_wgrad: AET_OK launched, 1 not eligible (caller
+// falls back to the gather producer), negative error.
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+struct TmaKey {
+    const void *ptr;
+    int tag;
+    int box[5];
+};
+struct TmaEntry {
+    TmaKey key;
+    CUtensorMap map;
+};
+struct TmaCache {
+    std::vector<TmaEntry> entries;
+};
+
+// dims/strides innermost first; strides[i] is the byte stride of dim i+1.
+int get_map(aet_layer *l, int tag, const void *ptr, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
+            const cuuint32_t *box, const CUtensorMap **out) {
+    if (!l->tma_cache) l->tma_cache = new TmaCache();
+    TmaCache *c = static_cast<TmaCache *>(l->tma_cache);
+    TmaKey key = {ptr, tag, {0, 0, 0, 0, 0}};
+    for (int i = 0; i < rank; ++i) key.box[i] = (int)box[i];
+    for (auto &e : c->entries)
+        if (e.key.ptr == key.ptr && e.key.tag == key.tag && memcmp(e.key.box, key.box, sizeof(key.box)) == 0) {
+            *out = &e.map;
+            return AET_OK;
+        }
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        aet_set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+        return AET_E_CUDA;
+    }
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    TmaEntry e;
+    e.key = key;
+    CUresult r = fn(&e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(ptr), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        aet_set_error("cuTensorMapEncodeTiled failed with code %d (tag %d)", (int)r, tag);
+        return AET_E_CUDA;
+    }
+    c->entries.reserve(64);
+    c->entries.push_back(e);
+    *out = &c->entries.back().map;
+    return AET_OK;
+}
+
+struct TmaArgs {
+    float *out;
+    const float *bias;
+    int act, bn, n_rows, n_cols, out_ld;
+    long long split_stride;
+    int slabs_per_tap;   // fprop/dgrad: inner channel count / 32
+    int S, pad;
+    int pix_per_img, tile_w, img_w;  // M-tile (fprop/dgrad) or K-slab (wgrad) decomposition
+    int total_slabs, slabs_per_split;
+    int col_blocks;      // wgrad: N tiles per tap
+    int stages, tmem_cols;
+    uint32_t tx_bytes, a_bytes;
+    int *status;
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(NTHREADS, 1)
+conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TmaArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ SharedCtl ctl;
+    // 128-byte swizzled tiles must start on a 1024-byte boundary
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM;
+    const int bn = a.bn;
+    int n0 = blockIdx.y * bn;   // GEMM column of this tile
+    int tap_w = 0, cblk_w = 0;  // wgrad: tap and channel block of this N tile
+    if (KIND == KIND_WGRAD) {
+        tap_w = blockIdx.y / a.col_blocks;
+        cblk_w = blockIdx.y - tap_w * a.col_blocks;
+        n0 = tap_w * (a.col_blocks * bn) + cblk_w * bn;
+    }
+    int slab_begin = 0, nslabs = a.total_slabs;
+    if (KIND == KIND_WGRAD) {
+        slab_begin = blockIdx.z * a.slabs_per_split;
+        nslabs = a.total_slabs - slab_begin;
+        if (nslabs > a.slabs_per_split) nslabs = a.slabs_per_split;
+        if (nslabs < 0) nslabs = 0;
+    }
+    const uint32_t b_bytes = (uint32_t)bn * BK * 4;
+    const uint32_t stage_bytes = a.a_bytes + b_bytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 1);
+            mbar_init(smem_u32(&ctl.empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl.accum), 1);
+        ctl.abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = ctl.tmem_base;
+    volatile int *abort_flag = &ctl.abort_flag;
+
+    if (warp < 4) {
+        if (threadIdx.x == 0) {
+            // ------------------------------------------------------------------ TMA producer
+            const int img0 = m0 / a.pix_per_img;                       // fprop/dgrad tile origin
+            const int row0 = (m0 - img0 * a.pix_per_img) / a.tile_w;
+            for (int it = 0; it < nslabs; ++it) {
+                const int s = it % a.stages;
+                const uint32_t phase = (it / a.stages) & 1;
+                if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
+                const uint32_t bar = smem_u32(&ctl.full[s]);
+                const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
+                const uint32_t sb = sa + a.a_bytes;
+                mbar_arrive_expect_tx(bar, a.tx_bytes);
+                if (KIND == KIND_FPROP) {
+                    const int tap = it / a.slabs_per_tap, cb = it - tap * a.slabs_per_tap;
+                    const int r = tap / a.S, sx = tap - r * a.S;
+                    tma_load_4d(sa, &map_a, bar, cb * 32, sx - a.pad, row0 + r - a.pad, img0);
+                    tma_load_2d(sb, &map_b, bar, it * 32, n0);
+                } else if (KIND == KIND_DGRAD) {
+                    const int tap = it / a.slabs_per_tap, kb = it - tap * a.slabs_per_tap;
+                    const int r = tap / a.S, sx = tap - r * a.S;
+                    tma_load_4d(sa, &map_a, bar, kb * 32, a.pad - sx, row0 + a.pad - r, img0);
+                    tma_load_4d(sb, &map_b, bar, 0, kb * 32, n0 / 32, tap);
+                } else {
+                    const int p0 = (slab_begin + it) * BK;
+                    const int img = p0 / a.pix_per_img;
+                    const int rem = p0 - img * a.pix_per_img;
+                    const int oh0 = rem / a.img_w, ow0 = rem - oh0 * a.img_w;
+                    const int r = tap_w / a.S, sx = tap_w - r * a.S;
+                    tma_load_5d(sa, &map_a, bar, 0, ow0, oh0, img, m0 / 32);
+                    tma_load_5d(sb, &map_b, bar, 0, ow0 + sx - a.pad, oh0 + r - a.pad, img, cblk_w * (bn / 32));
+                }
+            }
+        }
+        __syncwarp();
+        // ------------------------------------------------------------------ epilogue
+        bool ready = nslabs == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
+        tc_fence_after_sync();
+        const int row = m0 + warp * 32 + lane;
+        const bool row_ok = row < a.n_rows;
+        float *orow = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)row * a.out_ld;
+        if (ready) {
+            for (int cc = 0; cc < bn; cc += 16) {
+                float v[16];
+                if (nslabs > 0) {
+                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) v[q] = 0.f;
+                }
+                if (!row_ok) continue;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int col = n0 + cc + q * 4;
+                    if (col >= a.n_cols) continue;
+                    float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                    if (KIND == KIND_FPROP) {
+                        if (a.bias) {
+                            float4 b = ldg4(a.bias + col);
+                            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                        }
+                        o.x = apply_act(o.x, a.act); o.y = apply_act(o.y, a.act);
+                        o.z = apply_act(o.z, a.act); o.w = apply_act(o.w, a.act);
+                    }
+                    *reinterpret_cast<float4 *>(orow + col) = o;
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        const int a_mn = (KIND == KIND_WGRAD) ? 1 : 0;
+        const int b_mn = (KIND == KIND_FPROP) ? 0 : 1;
+        const uint32_t idesc = make_idesc_tf32(BM, bn, a_mn, b_mn);
+        uint32_t accumulate = 0;
+        for (int it = 0; it < nslabs; ++it) {
+            const int s = it % a.stages;
+            const uint32_t phase = (it / a.stages) & 1;
+            if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
+            tc_fence_after_sync();
+            const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
+            const uint32_t sb = sa + a.a_bytes;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint64_t da = a_mn ? make_desc(sa + j * 1024, 4096, 1024, LAYOUT_SW128)
+                                         : make_desc(sa + j * 32, 0, 1024, LAYOUT_SW128);
+                const uint64_t db = b_mn ? make_desc(sb + j * 1024, 4096, 1024, LAYOUT_SW128)
+                                         : make_desc(sb + j * 32, 0, 1024, LAYOUT_SW128);
+                mma_tf32(tmem, da, db, idesc, accumulate);
+                accumulate = 1;
+            }
+            mma_commit(smem_u32(&ctl.empty[s]));
+        }
+        mma_commit(smem_u32(&ctl.accum));
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        tmem_dealloc(tmem, a.tmem_cols);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+    }
+}
+
+// A 128-pixel (or `tile`-pixel) run of consecutive (n,h,w) pixels is a box iff it is whole rows
+// of one image or whole images.  Fills box = {w, rows, images}.
+bool pixel_box(int tile, int h, int w, cuuint32_t *bw, cuuint32_t *bh, cuuint32_t *bi) {
+    if (w <= 0 || h <= 0) return false;
+    if (w >= tile) {
+        if (w % tile) return false;
+        *bw = tile; *bh = 1; *bi = 1;
+        return true;
+    }
+    if (tile % w) return false;
+    int rows = tile / w;
+    if (h >= rows) {
+        if (h % rows) return false;
+        *bw = w; *bh = rows; *bi = 1;
+        return true;
+    }
+    if (rows % h) return false;
+    *bw = w; *bh = h; *bi = rows / h;
+    return bw[0] <= 256 && bh[0] <= 256 && bi[0] <= 256;
+}
+
+template <int KIND>
+int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, TmaArgs &t, dim3 grid, const char *name,
+               double flops) {
+    t.tmem_cols = pow2_cols(t.bn);
+    t.status = ctx->status_dev;
+    const size_t stage = (size_t)t.a_bytes + (size_t)t.bn * BK * 4;
+    int stages = (int)((99 * 1024) / stage);
+    if (stages < 3) stages = (int)((200 * 1024) / stage);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) stages = 2;
+    t.stages = stages;
+    const size_t smem_bytes = stage * stages + 1024;
+    static bool attr_set[3] = {false, false, false};
+    if (!attr_set[KIND]) {
+        AET_CUDA(cudaFuncSetAttribute(conv_tma_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set[KIND] = true;
+    }
+    LaunchScope scope(ctx, name, 0, flops);
+    conv_tma_kernel<KIND><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(*ma, *mb, t);
+    return aet_check_launch(name);
+}
+
+bool tma_common_ok(const aet_layer *l) {
+    return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && l->stride_x == 1 && l->stride_y == 1 &&
+           l->cp % 32 == 0 && l->ocp % 32 == 0;
+}
+
+int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
+    const ConvGeom &g = a.g;
+    if (!tma_common_ok(l)) return 1;
+    cuuint32_t bw, bh, bi;
+    if (!pixel_box(BM, g.OH, g.OW, &bw, &bh, &bi) || (int)bw != g.OW) return 1;
+    if (g.OW > g.W || g.OH > g.H) return 1;
+    const int bn = a.bn % 32 == 0 ? a.bn : 0;
+    if (!bn) return 1;
+    const CUtensorMap *ma, *mb;
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)g.cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
+        cuuint64_t str[3] = {(cuuint64_t)g.cp * 4, (cuuint64_t)g.W * g.cp * 4, (cuuint64_t)g.H * g.W * g.cp * 4};
+        cuuint32_t box[4] = {32, bw, bh, bi};
+        AET_TRY(get_map(l, 0, a.src_a, 4, dims, str, box, &ma));
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.k_total, (cuuint64_t)g.K};
+        cuuint64_t str[1] = {(cuuint64_t)a.k_total * 4};
+        cuuint32_t box[2] = {32, (cuuint32_t)bn};
+        AET_TRY(get_map(l, 1, a.src_b, 2, dims, str, box, &mb));
+    }
+    TmaArgs t = {};
+    t.out = a.out; t.bias = a.bias; t.act = a.act; t.bn = bn;
+    t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    t.slabs_per_tap = g.cp / 32; t.S = g.S; t.pad = g.pad;
+    t.pix_per_img = g.OH * g.OW; t.tile_w = g.OW; t.img_w = g.OW;
+    t.total_slabs = a.k_total / 32; t.slabs_per_split = t.total_slabs;
+    t.a_bytes = BM * BK * 4;
+    t.tx_bytes = t.a_bytes + bn * BK * 4;
+    dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    return launch_tma<KIND_FPROP>(l->ctx, ma, mb, t, grid, "conv_fprop_tma", flops);
+}
+
+int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
+    const ConvGeom &g = a.g;
+    if (!tma_common_ok(l)) return 1;
+    if (g.OH != g.H || g.OW != g.W) return 1;   // same-size convolutions only
+    cuuint32_t bw, bh, bi;
+    if (!pixel_box(BM, g.H, g.W, &bw, &bh, &bi) || (int)bw != g.W) return 1;
+    const int bn = a.bn % 32 == 0 ? a.bn : 0;
+    if (!bn || g.cp % bn) return 1;
+    const CUtensorMap *ma, *mb;
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)g.kp, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N};
+        cuuint64_t str[3] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4};
+        cuuint32_t box[4] = {32, bw, bh, bi};
+        AET_TRY(get_map(l, 2, a.src_a, 4, dims, str, box, &ma));
+    }
+    {
+        // weights [filter][tap][cp] viewed as (c%32, filter, c/32, tap)
+        const int taps = g.R * g.S;
+        cuuint64_t dims[4] = {32, (cuuint64_t)g.K, (cuuint64_t)g.cp / 32, (cuuint64_t)taps};
+        cuuint64_t str[3] = {(cuuint64_t)taps * g.cp * 4, 128, (cuuint64_t)g.cp * 4};
+        cuuint32_t box[4] = {32, 32, (cuuint32_t)bn / 32, 1};
+        AET_TRY(get_map(l, 3, a.src_b, 4, dims, str, box, &mb));
+    }
+    TmaArgs t = {};
+    t.out = a.out; t.bias = nullptr; t.act = AET_LINEAR; t.bn = bn;
+    t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    t.slabs_per_tap = g.kp / 32; t.S = g.S; t.pad = g.pad;
+    t.pix_per_img = g.H * g.W; t.tile_w = g.W; t.img_w = g.W;
+    t.total_slabs = a.k_total / 32; t.slabs_per_split = t.total_slabs;
+    t.a_bytes = BM * BK * 4;
+    t.tx_bytes = t.a_bytes + bn * BK * 4;
+    dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    return launch_tma<KIND_DGRAD>(l->ctx, ma, mb, t, grid, "conv_dgrad_tma", flops);
+}
+
+// `a.out` already points at the split-K partial buffer sized for `splits_hint` splits of the
+// gather decomposition; the TMA variant keeps the same split count and partial layout.
+int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
+    const ConvGeom &g = a.g;
+    if (!tma_common_ok(l)) return 1;
+    if (g.OW > g.W || g.OH > g.H) return 1;
+    cuuint32_t bw, bh, bi;
+    if (!pixel_box(BK, g.OH, g.OW, &bw, &bh, &bi)) return 1;
+    const int bn = g.cp <= 256 ? g.cp : (g.cp % 256 == 0 ? 256 : (g.cp % 128 == 0 ? 128 : 0));
+    if (!bn) return 1;
+    const int m_blocks = g.kp / 32 < 4 ? g.kp / 32 : 4;
+    const CUtensorMap *ma, *mb;
+    {
+        cuuint64_t dims[5] = {32, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N, (cuuint64_t)g.kp / 32};
+        cuuint64_t str[4] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4, 128};
+        cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)m_blocks};
+        AET_TRY(get_map(l, 4, a.src_a, 5, dims, str, box, &ma));
+    }
+    {
+        cuuint64_t dims[5] = {32, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N, (cuuint64_t)g.cp / 32};
+        cuuint64_t str[4] = {(cuuint64_t)g.cp * 4, (cuuint64_t)g.W * g.cp * 4, (cuuint64_t)g.H * g.W * g.cp * 4, 128};
+        cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)bn / 32};
+        AET_TRY(get_map(l, 5, a.src_b, 5, dims, str, box, &mb));
+    }
+    TmaArgs t = {};
+    t.out = a.out; t.bias = nullptr; t.act = AET_LINEAR; t.bn = bn;
+    t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    t.split_stride = a.split_stride;
+    t.S = g.S; t.pad = g.pad;
+    t.pix_per_img = g.OH * g.OW; t.tile_w = g.OW; t.img_w = g.OW;
+    t.total_slabs = (a.k_total + BK - 1) / BK;
+    t.slabs_per_split = a.k_per_split / BK;
+    t.col_blocks = g.cp / bn;
+    t.a_bytes = BM * BK * 4;                                   // stage slot; the copy fills m_blocks * 4 KB of it
+    t.tx_bytes = (uint32_t)m_blocks * 4096 + (uint32_t)bn * BK * 4;
+    const int m_tiles = (g.K + BM - 1) / BM;
+    dim3 grid(m_tiles, g.R * g.S * t.col_blocks, splits_hint);
+    return launch_tma<KIND_WGRAD>(l->ctx, ma, mb, t, grid, "conv_wgrad_tma", flops);
+}
+
+void tma_release(aet_layer *l) {
+    if (l->tma_cache) {
+        delete static_cast<TmaCache *>(l->tma_cache);
+        l->tma_cache = nullptr;
+    }
+}
+
+}  // namespace

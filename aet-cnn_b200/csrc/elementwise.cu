@@ -1,0 +1,820 @@
+// Bandwidth-bound kernels around the convolution: batch-norm statistics / apply / backward fused
+// with the activation and its gradient, bias gradient, max-pool and global average-pool in both
+// directions, softmax + cross-entropy with an on-device loss reduction, dropout, and the fused
+// SGD-momentum update.  All tensors are NHWC with `cp` (multiple of 4) floats per pixel, so every
+// access is a 16-byte vector and consecutive threads touch consecutive addresses.  Reductions
+// are two-stage with a fixed summation order (no floating-point atomics): results are bitwise
+// reproducible from run to run and identical on every rank of a data-parallel job.
+//
+// Reference kernels replaced (one scalar thread per element / one block per channel each):
+//   BN forward   mtcs/MtcsNormData.c:54-133,193-232,336-347   (CPU: dnn/NormData.c:141-282)
+//   BN backward  mtcs/MtcsBiasData.c:27-45, mtcs/MtcsScaleData.c:53-71, mtcs/MtcsDeltaData.c:40-52,
+//                89-114,158-185,229-236                        (CPU: dnn/DeltaData.c:23-80)
+//   activation   mtcs/MtcsActivation.c:112-138,471-513
+//   max-pool     mtcs/MtcsMaxPoolLayer.c:60-100,295-332        (CPU: dnn/MaxPoolLayer.c:237-272,318-331)
+//   avg-pool     dnn/AvgPoolLayer.c:49-66,92-106
+//   softmax-CE   dnn/SoftMaxLayer.c:122-139,172-199, mtcs/MtcsData.c:20-29
+//   dropout      dnn/DropoutLayer.c:55-86
+//   SGD          mtcs/MtcsConvLayer.c:618-631 -> mtcs/MtcsTool.c:33-52
+#include <float.h>
+#include <math.h>
+
+#include "common.h"
+
+namespace {
+
+constexpr int TB = 256;
+
+// Thread -> (channel vector, pixel lane) map shared by the per-channel kernels: a block covers
+// `lanes_c` channel vectors (4 channels each) times `pl_count` pixel lanes.
+struct CMap {
+    int cvec, lanes_c, pl_count, cslabs;
+};
+CMap make_cmap(int cp) {
+    CMap m;
+    m.cvec = cp / 4;
+    m.lanes_c = m.cvec < TB ? m.cvec : TB;
+    m.pl_count = TB / m.lanes_c;
+    m.cslabs = (m.cvec + TB - 1) / TB;
+    return m;
+}
+__device__ __forceinline__ bool cmap_thread(const CMap &m, int &cv, int &pl) {
+    int t = threadIdx.x;
+    int cl = t % m.lanes_c;
+    pl = t / m.lanes_c;
+    cv = blockIdx.y * TB + cl;
+    return pl < m.pl_count && cv < m.cvec;
+}
+
+__device__ __forceinline__ float act_fwd(float v, int act) {
+    if (act == AET_LEAKY) return v > 0.f ? v : 0.1f * v;
+    if (act == AET_RELU) return v > 0.f ? v : 0.f;
+    return v;
+}
+// Gradient of the activation evaluated on its OUTPUT, as the reference does (dnn/Activation.h:99,104).
+__device__ __forceinline__ float act_grad(float y, int act) {
+    if (act == AET_LEAKY) return y > 0.f ? 1.f : 0.1f;
+    if (act == AET_RELU) return y > 0.f ? 1.f : 0.f;
+    return 1.f;
+}
+__device__ __forceinline__ float bn_val(float x, float mean, float inv, float g, float b) {
+    return __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(x, mean), inv), g), b);
+}
+
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+
+// ---------------------------------------------------------------------------- generic two-sum reduction
+// MODE 0: BN statistics        s1 = sum(x - shift), s2 = sum((x - shift)^2)
+// MODE 1: BN backward          d' = delta * act'(bn(x)); s1 = sum d', s2 = sum d' * (x - mean)
+// MODE 2: bias/act backward    d' = delta * act'(y) written back in place; s1 = sum d'
+struct ReduceArgs {
+    const float *x;       // MODE 0/1: conv result before BN;  MODE 2: layer output y
+    float *delta;         // MODE 1/2
+    const float *mean, *inv, *gamma, *beta, *shift;
+    float *partial;       // [blocks][2][cp]
+    int act;
+    long long pixels;
+    int cp;
+    long long pix_per_block;
+    CMap m;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
+    __shared__ float4 sh1[TB];
+    __shared__ float4 sh2[TB];
+    int cv, pl;
+    const bool active = cmap_thread(a.m, cv, pl);
+    float4 s1 = make_float4(0.f, 0.f, 0.f, 0.f), s2 = s1;
+    if (active) {
+        const int c = cv * 4;
+        float4 mean = make_float4(0.f, 0.f, 0.f, 0.f), inv = mean, gam = mean, bet = mean, sft = mean;
+        if (MODE == 0) sft = ld4(a.shift + c);
+        if (MODE == 1) { mean = ld4(a.mean + c); inv = ld4(a.inv + c); gam = ld4(a.gamma + c); bet = ld4(a.beta + c); }
+        long long p0 = (long long)blockIdx.x * a.pix_per_block;
+        long long p1 = p0 + a.pix_per_block;
+        if (p1 > a.pixels) p1 = a.pixels;
+        for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
+            const size_t off = (size_t)p * a.cp + c;
+            if (MODE == 0) {
+                float4 v = ld4(a.x + off);
+                v.x -= sft.x; v.y -= sft.y; v.z -= sft.z; v.w -= sft.w;
+                s1.x += v.x; s1.y += v.y; s1.z += v.z; s1.w += v.w;
+                s2.x += v.x * v.x; s2.y += v.y * v.y; s2.z += v.z * v.z; s2.w += v.w * v.w;
+            } else if (MODE == 1) {
+                float4 v = ld4(a.x + off), d = ld4(a.delta + off);
+                d.x *= act_grad(act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
+                d.y *= act_grad(act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
+                d.z *= act_grad(act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
+                d.w *= act_grad(act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+                s1.x += d.x; s1.y += d.y; s1.z += d.z; s1.w += d.w;
+                s2.x += d.x * (v.x - mean.x); s2.y += d.y * (v.y - mean.y);
+                s2.z += d.z * (v.z - mean.z); s2.w += d.w * (v.w - mean.w);
+            } else {
+                float4 y = ld4(a.x + off), d = ld4(a.delta + off);
+                d.x *= act_grad(y.x, a.act); d.y *= act_grad(y.y, a.act);
+                d.z *= act_grad(y.z, a.act); d.w *= act_grad(y.w, a.act);
+                if (a.act != AET_LINEAR) st4(a.delta + off, d);
+                s1.x += d.x; s1.y += d.y; s1.z += d.z; s1.w += d.w;
+            }
+        }
+    }
+    sh1[threadIdx.x] = s1;
+    sh2[threadIdx.x] = s2;
+    __syncthreads();
+    if (active && pl == 0) {
+        const int cl = threadIdx.x;  // pl == 0 => threadIdx.x is the channel lane
+        for (int q = 1; q < a.m.pl_count; ++q) {
+            float4 t1 = sh1[q * a.m.lanes_c + cl], t2 = sh2[q * a.m.lanes_c + cl];
+            s1.x += t1.x; s1.y += t1.y; s1.z += t1.z; s1.w += t1.w;
+            s2.x += t2.x; s2.y += t2.y; s2.z += t2.z; s2.w += t2.w;
+        }
+        float *dst = a.partial + (size_t)blockIdx.x * 2 * a.cp + cv * 4;
+        st4(dst, s1);
+        st4(dst + a.cp, s2);
+    }
+}
+
+struct FinalizeArgs {
+    const float *partial;
+    int blocks, cp, c;
+    long long m;          // elements per channel
+    int parity, update_rolling;
+    const float *shift;
+    float *mean, *variance, *inv, *rolling_mean, *rolling_variance;
+    // backward
+    const float *gamma;
+    float *g_gamma, *g_beta, *coef;   // coef: [3][cp]
+};
+
+// MODE 0: statistics -> mean, variance, 1/std, rolling update.  MODE 1: BN backward coefficients
+// and the scale / shift gradients.  MODE 2: bias gradient.
+template <int MODE>
+__global__ void finalize_kernel(const FinalizeArgs a) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= a.cp) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int b = 0; b < a.blocks; ++b) {
+        s1 += (double)a.partial[(size_t)b * 2 * a.cp + c];
+        if (MODE != 2) s2 += (double)a.partial[(size_t)b * 2 * a.cp + a.cp + c];
+    }
+    const double m = (double)a.m;
+    if (MODE == 0) {
+        if (c >= a.c) { a.mean[c] = 0.f; a.variance[c] = 0.f; a.inv[c] = 0.f; return; }
+        const double mean_sh = s1 / m;
+        double ss = s2 - s1 * mean_sh;   // sum (x - mean)^2
+        if (ss < 0.0) ss = 0.0;
+        const float mean = (float)(mean_sh + (double)a.shift[c]);
+        float var, inv;
+        if (a.parity == AET_PARITY_CPU) {
+            var = (float)(ss / (m - 1.0));
+            inv = (float)(1.0 / (sqrt((double)var) + (double).000001f));
+        } else {
+            var = (float)(ss / m);
+            inv = 1.0f / sqrtf(var + .00001f);
+        }
+        a.mean[c] = mean; a.variance[c] = var; a.inv[c] = inv;
+        if (a.update_rolling) {
+            const float keep = a.parity == AET_PARITY_CPU ? .9f : .99f, add = a.parity == AET_PARITY_CPU ? .1f : .01f;
+            float rm = a.rolling_mean[c] * keep; rm += add * mean;
+            float rv = a.rolling_variance[c] * keep; rv += add * var;
+            a.rolling_mean[c] = rm; a.rolling_variance[c] = rv;
+        }
+    } else if (MODE == 1) {
+        if (c >= a.c) { a.coef[c] = 0.f; a.coef[a.cp + c] = 0.f; a.coef[2 * a.cp + c] = 0.f; return; }
+        const float var = a.variance[c], gam = a.gamma[c];
+        const float S1 = (float)s1, S2 = (float)s2;
+        a.g_gamma[c] += S2 * a.inv[c];
+        float md, vd, k1;
+        if (a.parity == AET_PARITY_CPU) {
+            md = (float)((double)(gam * S1) * (-1. / sqrt((double)(var + .00001f))));
+            vd = (float)((double)(gam * S2) * (-.5 * pow((double)(var + .00001f), (double)(float)(-3. / 2.))));
+            k1 = (float)(1. / sqrt((double)(var + .00001f)));
+        } else {
+            a.g_beta[c] += S1;
+            md = (gam * S1) * (-1.f / sqrtf(var + .000001f));
+            vd = (float)((double)(gam * S2) * (-.5 * (double)powf(var + .000001f, (float)(-3. / 2.))));
+            k1 = 1.f / (sqrtf(var) + .000001f);
+        }
+        a.coef[c] = gam * k1;
+        a.coef[a.cp + c] = (float)((double)vd * 2. / m);
+        a.coef[2 * a.cp + c] = (float)((double)md / m);
+    } else {
+        if (c < a.c) a.g_beta[c] += (float)s1;
+    }
+}
+
+// y = act(bn(x)) ; optionally with the rolling statistics (eval).
+struct ApplyArgs {
+    const float *x;
+    float *y;
+    const float *mean, *inv, *gamma, *beta;
+    int act, cp;
+    long long pixels, pix_per_block;
+    CMap m;
+};
+__global__ void __launch_bounds__(TB) bn_apply_kernel(const ApplyArgs a) {
+    int cv, pl;
+    if (!cmap_thread(a.m, cv, pl)) return;
+    const int c = cv * 4;
+    const float4 mean = ld4(a.mean + c), inv = ld4(a.inv + c), gam = ld4(a.gamma + c), bet = ld4(a.beta + c);
+    long long p0 = (long long)blockIdx.x * a.pix_per_block, p1 = p0 + a.pix_per_block;
+    if (p1 > a.pixels) p1 = a.pixels;
+    for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
+        const size_t off = (size_t)p * a.cp + c;
+        float4 v = ld4(a.x + off);
+        v.x = act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act);
+        v.y = act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act);
+        v.z = act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act);
+        v.w = act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), a.act);
+        st4(a.y + off, v);
+    }
+}
+
+// delta <- d' * a[c] + (x - mean) * b[c] + c0[c], with d' = delta * act'(y) recomputed from x.
+struct BwdApplyArgs {
+    const float *x;
+    float *delta;
+    const float *mean, *inv, *gamma, *beta, *coef;
+    int act, cp;
+    long long pixels, pix_per_block;
+    CMap m;
+};
+__global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) {
+    int cv, pl;
+    if (!cmap_thread(a.m, cv, pl)) return;
+    const int c = cv * 4;
+    const float4 mean = ld4(a.mean + c), inv = ld4(a.inv + c), gam = ld4(a.gamma + c), bet = ld4(a.beta + c);
+    const float4 ka = ld4(a.coef + c), kb = ld4(a.coef + a.cp + c), kc = ld4(a.coef + 2 * a.cp + c);
+    long long p0 = (long long)blockIdx.x * a.pix_per_block, p1 = p0 + a.pix_per_block;
+    if (p1 > a.pixels) p1 = a.pixels;
+    for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
+        const size_t off = (size_t)p * a.cp + c;
+        float4 v = ld4(a.x + off), d = ld4(a.delta + off);
+        d.x *= act_grad(act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
+        d.y *= act_grad(act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
+        d.z *= act_grad(act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
+        d.w *= act_grad(act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+        d.x = d.x * ka.x + (v.x - mean.x) * kb.x + kc.x;
+        d.y = d.y * ka.y + (v.y - mean.y) * kb.y + kc.y;
+        d.z = d.z * ka.z + (v.z - mean.z) * kb.z + kc.z;
+        d.w = d.w * ka.w + (v.w - mean.w) * kb.w + kc.w;
+        st4(a.delta + off, d);
+    }
+}
+
+__global__ void eval_inv_kernel(const float *rolling_variance, float *inv, int c, int cp, int parity) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= cp) return;
+    float v = 0.f;
+    if (i < c)
+        v = parity == AET_PARITY_CPU ? (float)(1.0 / (sqrt((double)rolling_variance[i]) + (double).000001f))
+                                     : 1.0f / sqrtf(rolling_variance[i] + .00001f);
+    inv[i] = v;
+}
+
+__global__ void copy_first_pixel_kernel(const float *x, float *shift, int cp) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < cp) shift[i] = x[i];
+}
+
+// ---------------------------------------------------------------------------- max pool
+struct PoolArgs {
+    const float *x;
+    float *y;
+    int *idx;
+    int N, C, H, W, cp, OH, OW, size, sx, sy, off, parity;
+    long long total;   // N*OH*OW*cvec
+};
+__global__ void __launch_bounds__(TB) maxpool_fwd_kernel(const PoolArgs a) {
+    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= a.total) return;
+    const int cvec = a.cp / 4;
+    const int cv = (int)(e % cvec);
+    long long p = e / cvec;
+    const int ow = (int)(p % a.OW); p /= a.OW;
+    const int oh = (int)(p % a.OH);
+    const int n = (int)(p / a.OH);
+    const float lowest = a.parity == AET_PARITY_CPU ? -FLT_MAX : -INFINITY;
+    float4 mx = make_float4(lowest, lowest, lowest, lowest);
+    int4 mi = make_int4(-1, -1, -1, -1);
+    const int c = cv * 4;
+    for (int l = 0; l < a.size; ++l)
+        for (int m = 0; m < a.size; ++m) {
+            const int ch = a.off + oh * a.sy + l, cw = a.off + ow * a.sx + m;
+            const bool valid = ch >= 0 && ch < a.H && cw >= 0 && cw < a.W;
+            float4 v = make_float4(lowest, lowest, lowest, lowest);
+            if (valid) v = ld4(a.x + ((size_t)(n * a.H + ch) * a.W + cw) * a.cp + c);
+            // index in the reference's NCHW numbering: cw + W*(ch + H*(k + n*C))
+            const int base = cw + a.W * (ch + a.H * (c + n * a.C));
+            const int hw = a.H * a.W;
+            if (v.x > mx.x) { mx.x = v.x; mi.x = base; }
+            if (v.y > mx.y) { mx.y = v.y; mi.y = base + hw; }
+            if (v.z > mx.z) { mx.z = v.z; mi.z = base + 2 * hw; }
+            if (v.w > mx.w) { mx.w = v.w; mi.w = base + 3 * hw; }
+        }
+    if (c + 1 >= a.C) { mx.y = 0.f; mi.y = -1; }   // pad channels stay zero
+    if (c + 2 >= a.C) { mx.z = 0.f; mi.z = -1; }
+    if (c + 3 >= a.C) { mx.w = 0.f; mi.w = -1; }
+    const size_t o = ((size_t)(n * a.OH + oh) * a.OW + ow) * a.cp + c;
+    st4(a.y + o, mx);
+    if (a.idx) *reinterpret_cast<int4 *>(a.idx + o) = mi;
+}
+
+struct PoolBwdArgs {
+    const float *delta;
+    const int *idx;
+    float *prev;
+    int N, C, H, W, cp, OH, OW, size, sx, sy, off, accumulate;
+    long long total;   // N*H*W*cvec
+};
+// Gather form (mtcs/MtcsMaxPoolLayer.c:295-332): every input element adds the deltas of the
+// windows whose argmax it is.
+__global__ void __launch_bounds__(TB) maxpool_bwd_kernel(const PoolBwdArgs a) {
+    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= a.total) return;
+    const int cvec = a.cp / 4;
+    const int cv = (int)(e % cvec);
+    long long p = e / cvec;
+    const int j = (int)(p % a.W); p /= a.W;
+    const int i = (int)(p % a.H);
+    const int n = (int)(p / a.H);
+    const int c = cv * 4;
+    const int area_x = (a.size - 1) / a.sx, area_y = (a.size - 1) / a.sy;
+    const int hw = a.H * a.W;
+    const int my = j + a.W * (i + a.H * (c + n * a.C));
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int l = -area_y; l < area_y + 1; ++l)
+        for (int m = -area_x; m < area_x + 1; ++m) {
+            const int ow = (j - a.off) / a.sx + m, oh = (i - a.off) / a.sy + l;
+            if (ow < 0 || ow >= a.OW || oh < 0 || oh >= a.OH) continue;
+            const size_t o = ((size_t)(n * a.OH + oh) * a.OW + ow) * a.cp + c;
+            const int4 id = *reinterpret_cast<const int4 *>(a.idx + o);
+            const float4 dv = ld4(a.delta + o);
+            if (id.x == my) d.x += dv.x;
+            if (id.y == my + hw) d.y += dv.y;
+            if (id.z == my + 2 * hw) d.z += dv.z;
+            if (id.w == my + 3 * hw) d.w += dv.w;
+        }
+    const size_t io = ((size_t)(n * a.H + i) * a.W + j) * a.cp + c;
+    if (a.accumulate) {
+        float4 q = ld4(a.prev + io);
+        d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+    }
+    st4(a.prev + io, d);
+}
+
+// ---------------------------------------------------------------------------- global average pool
+__global__ void avgpool_fwd_kernel(const float *x, float *y, int N, int spatial, int cp) {
+    int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int cvec = cp / 4;
+    if (e >= N * cvec) return;
+    const int cv = e % cvec, n = e / cvec;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *src = x + (size_t)n * spatial * cp + cv * 4;
+    for (int i = 0; i < spatial; ++i) {
+        float4 v = ld4(src + (size_t)i * cp);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    s.x /= spatial; s.y /= spatial; s.z /= spatial; s.w /= spatial;
+    st4(y + (size_t)n * cp + cv * 4, s);
+}
+__global__ void avgpool_bwd_kernel(const float *delta, float *prev, long long total4, int spatial, int cp, int accumulate) {
+    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total4) return;
+    const int cvec = cp / 4;
+    const int cv = (int)(e % cvec);
+    const long long pix = e / cvec;
+    const long long n = pix / spatial;
+    float4 d = ld4(delta + (size_t)n * cp + cv * 4);
+    d.x /= spatial; d.y /= spatial; d.z /= spatial; d.w /= spatial;
+    float *dst = prev + (size_t)pix * cp + cv * 4;
+    if (accumulate) {
+        float4 q = ld4(dst);
+        d.x += q.x; d.y += q.y; d.z += q.z; d.w += q.w;
+    }
+    st4(dst, d);
+}
+
+// ---------------------------------------------------------------------------- softmax + cross entropy
+// One warp per (sample, group).  Writes probabilities, delta = truth - p, the per-element error and
+// one partial loss per warp; softmax_cost_kernel then adds the partials in a fixed tree order.
+struct SoftmaxArgs {
+    const float *x, *truth;
+    float *p, *delta, *loss, *unit_loss;
+    int units, groups, n, cp, parity;
+    float temp;
+};
+__global__ void __launch_bounds__(TB) softmax_kernel(const SoftmaxArgs a) {
+    const int unit = blockIdx.x * (TB / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (unit >= a.units) return;
+    const int b = unit / a.groups, g = unit - b * a.groups;
+    const size_t base = (size_t)b * a.cp + (size_t)g * a.n;
+    float largest = a.parity == AET_PARITY_CPU ? -FLT_MAX : -INFINITY;
+    for (int i = lane; i < a.n; i += 32) {
+        float v = a.x[base + i];
+        if (a.parity != AET_PARITY_CPU) v = (float)(int)v;   // the MTCS kernel compares through an int
+        largest = fmaxf(largest, v);
+    }
+    for (int o = 16; o; o >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+    float sum = 0.f;
+    for (int i = lane; i < a.n; i += 32) {
+        float e = expf(a.x[base + i] / a.temp - largest / a.temp);
+        a.p[base + i] = e;
+        sum += e;
+    }
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    float l = 0.f;
+    for (int i = lane; i < a.n; i += 32) {
+        float q = a.p[base + i] / sum;
+        a.p[base + i] = q;
+        if (a.truth) {
+            float t = a.truth[base + i];
+            float err = t ? -logf(q) : 0.f;
+            a.loss[base + i] = err;
+            a.delta[base + i] = t - q;
+            l += err;
+        }
+    }
+    for (int o = 16; o; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) a.unit_loss[unit] = l;
+}
+__global__ void __launch_bounds__(1024) softmax_cost_kernel(const float *unit_loss, int units, float *cost, float inv_batch,
+                                                            float *mean_loss) {
+    __shared__ float sh[1024];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < units; i += 1024) s += unit_loss[i];
+    sh[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 512; o; o >>= 1) {
+        if ((int)threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        cost[0] = sh[0];
+        if (mean_loss) mean_loss[0] = sh[0] * inv_batch;
+    }
+}
+
+// ---------------------------------------------------------------------------- small utilities
+__global__ void axpy_kernel(float *y, const float *x, float a, size_t n4, int accumulate) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 v = ld4(x + i * 4);
+    v.x *= a; v.y *= a; v.z *= a; v.w *= a;
+    if (accumulate) {
+        float4 q = ld4(y + i * 4);
+        v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    st4(y + i * 4, v);
+}
+__global__ void fill_kernel(float *p, float v, size_t n4) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n4) st4(p + i * 4, make_float4(v, v, v, v));
+}
+__global__ void step_counter_kernel(unsigned long long *ctr) { ctr[0] += 1ull; }
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+// Counter-based uniforms: u = top 24 bits of mix64(seed + step*A + (index+1)*B).
+__global__ void dropout_fwd_kernel(float *x, float *rnd, size_t n, int c, int cp, float prob, float scale,
+                                   unsigned long long seed, const unsigned long long *step, int generate) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float r;
+    if (generate) {
+        unsigned long long s = seed + step[0] * 0xD1342543DE82EF95ull + (i + 1) * 0x9E3779B97F4A7C15ull;
+        r = (float)(mix64(s) >> 40) * (1.0f / 16777216.0f);
+        rnd[i] = r;
+    } else {
+        r = rnd[i];
+    }
+    if ((int)(i % cp) >= c) return;
+    x[i] = r < prob ? 0.f : x[i] * scale;
+}
+__global__ void dropout_bwd_kernel(float *d, const float *rnd, size_t n, float prob, float scale) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    d[i] = rnd[i] < prob ? 0.f : d[i] * scale;
+}
+
+// ---------------------------------------------------------------------------- SGD with momentum
+// u = U + G (+ decay_term * w for weights); w += rate * u; U = momentum * u; G = 0.
+// Same operation order as the three reference passes (U += -decay*B*W; W += lr/B*U; U *= momentum).
+__global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float *G, const int *block_seg,
+                                                       const float *seg_table, const float *hyper) {
+    const int seg = block_seg[blockIdx.x];
+    const float rate = hyper[0] * seg_table[2 * seg];
+    const float momentum = hyper[1];
+    const float decay_term = seg_table[2 * seg + 1] != 0.f ? hyper[2] : 0.f;
+    const size_t i = ((size_t)blockIdx.x * TB + threadIdx.x) * 4;
+    float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i);
+    u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    u.x += decay_term * w.x; u.y += decay_term * w.y; u.z += decay_term * w.z; u.w += decay_term * w.w;
+    w.x += rate * u.x; w.y += rate * u.y; w.z += rate * u.z; w.w += rate * u.w;
+    u.x *= momentum; u.y *= momentum; u.z *= momentum; u.w *= momentum;
+    st4(W + i, w);
+    st4(U + i, u);
+    st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+__global__ void sgd_segment_kernel(float *W, float *U, float *G, size_t n4, float rate, float momentum, float decay_term) {
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
+    if (i >= n4) return;
+    i *= 4;
+    float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i);
+    u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    u.x += decay_term * w.x; u.y += decay_term * w.y; u.z += decay_term * w.z; u.w += decay_term * w.w;
+    w.x += rate * u.x; w.y += rate * u.y; w.z += rate * u.z; w.w += rate * u.w;
+    u.x *= momentum; u.y *= momentum; u.z *= momentum; u.w *= momentum;
+    st4(W + i, w);
+    st4(U + i, u);
+    st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+
+__global__ void param_hash_kernel(const float *p, size_t n, unsigned long long *hash) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    unsigned long long h = 0;
+    if (i < n) h = mix64((unsigned long long)__float_as_uint(p[i]) ^ ((i + 1) * 0x9E3779B97F4A7C15ull));
+    for (int o = 16; o; o >>= 1) h += __shfl_xor_sync(0xffffffffu, h, o);
+    if ((threadIdx.x & 31) == 0) atomicAdd(hash, h);   // integer addition: order-independent
+}
+
+struct ReducePlan {
+    CMap m;
+    int blocks;
+    long long pix_per_block;
+};
+ReducePlan plan_reduce(aet_context *ctx, long long pixels, int cp) {
+    ReducePlan p;
+    p.m = make_cmap(cp);
+    long long want = 2LL * ctx->sm_count / p.m.cslabs;
+    if (want < 1) want = 1;
+    long long min_pix = (long long)p.m.pl_count * 4;   // at least 4 pixels per thread
+    long long maxb = (pixels + min_pix - 1) / min_pix;
+    if (want > maxb) want = maxb;
+    if (want < 1) want = 1;
+    p.pix_per_block = (pixels + want - 1) / want;
+    p.blocks = (int)((pixels + p.pix_per_block - 1) / p.pix_per_block);
+    return p;
+}
+ReducePlan plan_apply(aet_context *ctx, long long pixels, int cp) {
+    ReducePlan p;
+    p.m = make_cmap(cp);
+    long long want = 8LL * ctx->sm_count / p.m.cslabs;
+    long long min_pix = (long long)p.m.pl_count * 2;
+    long long maxb = (pixels + min_pix - 1) / min_pix;
+    if (want > maxb) want = maxb;
+    if (want < 1) want = 1;
+    p.pix_per_block = (pixels + want - 1) / want;
+    p.blocks = (int)((pixels + p.pix_per_block - 1) / p.pix_per_block);
+    return p;
+}
+
+}  // namespace
+
+int aet_check_launch(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        aet_set_error("launch of %s failed: %s", what, cudaGetErrorString(e));
+        return AET_E_CUDA;
+    }
+    return AET_OK;
+}
+
+// Batch statistics of l->x (the convolution result) into mean / variance / inv_std.
+int k_bn_stats(aet_layer *l, int update_rolling) {
+    aet_context *ctx = l->ctx;
+    const long long pixels = (long long)l->batch * l->oh * l->ow;
+    ReducePlan p = plan_reduce(ctx, pixels, l->ocp);
+    float *partial = nullptr;
+    AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
+    {
+        LaunchScope s(ctx, "bn_shift", 0, 0);
+        copy_first_pixel_kernel<<<(l->ocp + 255) / 256, 256, 0, ctx->stream>>>(l->x->d, l->shift, l->ocp);
+        AET_TRY(aet_check_launch("bn_shift"));
+    }
+    ReduceArgs a = {};
+    a.x = l->x->d; a.shift = l->shift; a.partial = partial; a.pixels = pixels; a.cp = l->ocp;
+    a.pix_per_block = p.pix_per_block; a.m = p.m;
+    {
+        LaunchScope s(ctx, "bn_stats", (double)pixels * l->ocp * 4.0, 0);
+        reduce2_kernel<0><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        AET_TRY(aet_check_launch("bn_stats"));
+    }
+    FinalizeArgs f = {};
+    f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels;
+    f.parity = ctx->parity; f.update_rolling = update_rolling; f.shift = l->shift;
+    f.mean = l->mean; f.variance = l->variance; f.inv = l->inv_std;
+    f.rolling_mean = l->rolling_mean; f.rolling_variance = l->rolling_variance;
+    LaunchScope s(ctx, "bn_stats_finalize", 0, 0);
+    finalize_kernel<0><<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(f);
+    return aet_check_launch("bn_stats_finalize");
+}
+
+// output = act(bn(x)) with the batch statistics (or the rolling ones for inference).
+int k_bn_apply(aet_layer *l, int use_rolling) {
+    aet_context *ctx = l->ctx;
+    const long long pixels = (long long)l->batch * l->oh * l->ow;
+    if (use_rolling) {
+        LaunchScope s(ctx, "bn_eval_inv", 0, 0);
+        eval_inv_kernel<<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(l->rolling_variance, l->inv_std, l->oc, l->ocp,
+                                                                        ctx->parity);
+        AET_TRY(aet_check_launch("bn_eval_inv"));
+    }
+    ReducePlan p = plan_apply(ctx, pixels, l->ocp);
+    ApplyArgs a = {};
+    a.x = l->x->d; a.y = l->output->d;
+    a.mean = use_rolling ? l->rolling_mean : l->mean; a.inv = l->inv_std;
+    a.gamma = layer_s(l); a.beta = layer_b(l);
+    a.act = l->act; a.cp = l->ocp; a.pixels = pixels; a.pix_per_block = p.pix_per_block; a.m = p.m;
+    LaunchScope s(ctx, "bn_apply_act", (double)pixels * l->ocp * 8.0, 0);
+    bn_apply_kernel<<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+    return aet_check_launch("bn_apply_act");
+}
+
+// delta <- BN backward of (delta * act'(output)); accumulates the scale (and, MTCS parity, shift) gradients.
+int k_bn_backward(aet_layer *l) {
+    aet_context *ctx = l->ctx;
+    const long long pixels = (long long)l->batch * l->oh * l->ow;
+    ReducePlan p = plan_reduce(ctx, pixels, l->ocp);
+    float *partial = nullptr;
+    AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
+    ReduceArgs a = {};
+    a.x = l->x->d; a.delta = l->delta->d; a.mean = l->mean; a.inv = l->inv_std;
+    a.gamma = layer_s(l); a.beta = layer_b(l); a.partial = partial; a.act = l->act;
+    a.pixels = pixels; a.cp = l->ocp; a.pix_per_block = p.pix_per_block; a.m = p.m;
+    {
+        LaunchScope s(ctx, "bn_bwd_reduce", (double)pixels * l->ocp * 8.0, 0);
+        reduce2_kernel<1><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        AET_TRY(aet_check_launch("bn_bwd_reduce"));
+    }
+    FinalizeArgs f = {};
+    f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels; f.parity = ctx->parity;
+    f.variance = l->variance; f.inv = l->inv_std; f.gamma = layer_s(l);
+    f.g_gamma = layer_sG(l); f.g_beta = layer_bG(l); f.coef = l->bwd_coef;
+    {
+        LaunchScope s(ctx, "bn_bwd_finalize", 0, 0);
+        finalize_kernel<1><<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(f);
+        AET_TRY(aet_check_launch("bn_bwd_finalize"));
+    }
+    ReducePlan q = plan_apply(ctx, pixels, l->ocp);
+    BwdApplyArgs b = {};
+    b.x = l->x->d; b.delta = l->delta->d; b.mean = l->mean; b.inv = l->inv_std;
+    b.gamma = layer_s(l); b.beta = layer_b(l); b.coef = l->bwd_coef; b.act = l->act; b.cp = l->ocp;
+    b.pixels = pixels; b.pix_per_block = q.pix_per_block; b.m = q.m;
+    LaunchScope s(ctx, "bn_bwd_apply", (double)pixels * l->ocp * 12.0, 0);
+    bn_bwd_apply_kernel<<<dim3(q.blocks, q.m.cslabs), TB, 0, ctx->stream>>>(b);
+    return aet_check_launch("bn_bwd_apply");
+}
+
+// Convolution without BN: delta *= act'(output) in place and the bias gradient accumulates.
+int k_bias_act_backward(aet_layer *l) {
+    aet_context *ctx = l->ctx;
+    const long long pixels = (long long)l->batch * l->oh * l->ow;
+    ReducePlan p = plan_reduce(ctx, pixels, l->ocp);
+    float *partial = nullptr;
+    AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
+    ReduceArgs a = {};
+    a.x = l->output->d; a.delta = l->delta->d; a.partial = partial; a.act = l->act;
+    a.pixels = pixels; a.cp = l->ocp; a.pix_per_block = p.pix_per_block; a.m = p.m;
+    {
+        LaunchScope s(ctx, "bias_act_bwd", (double)pixels * l->ocp * (l->act == AET_LINEAR ? 4.0 : 12.0), 0);
+        reduce2_kernel<2><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        AET_TRY(aet_check_launch("bias_act_bwd"));
+    }
+    FinalizeArgs f = {};
+    f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels; f.g_beta = layer_bG(l);
+    LaunchScope s(ctx, "bias_bwd_finalize", 0, 0);
+    finalize_kernel<2><<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(f);
+    return aet_check_launch("bias_bwd_finalize");
+}
+
+int k_maxpool_forward(aet_layer *l, const float *x) {
+    aet_context *ctx = l->ctx;
+    PoolArgs a = {};
+    a.x = x; a.y = l->output->d; a.idx = l->indexes;
+    a.N = l->batch; a.C = l->c; a.H = l->h; a.W = l->w; a.cp = l->cp; a.OH = l->oh; a.OW = l->ow;
+    a.size = l->size; a.sx = l->stride_x; a.sy = l->stride_y; a.off = -l->pad / 2; a.parity = ctx->parity;
+    a.total = (long long)l->batch * l->oh * l->ow * (l->cp / 4);
+    const double bytes = 4.0 * l->batch * l->h * l->w * l->cp + 8.0 * l->batch * l->oh * l->ow * l->cp;
+    LaunchScope s(ctx, "maxpool_fwd", bytes, 0);
+    maxpool_fwd_kernel<<<(unsigned)((a.total + TB - 1) / TB), TB, 0, ctx->stream>>>(a);
+    return aet_check_launch("maxpool_fwd");
+}
+
+int k_maxpool_backward(aet_layer *l, float *prev_delta, int accumulate) {
+    aet_context *ctx = l->ctx;
+    PoolBwdArgs a = {};
+    a.delta = l->delta->d; a.idx = l->indexes; a.prev = prev_delta;
+    a.N = l->batch; a.C = l->c; a.H = l->h; a.W = l->w; a.cp = l->cp; a.OH = l->oh; a.OW = l->ow;
+    a.size = l->size; a.sx = l->stride_x; a.sy = l->stride_y; a.off = -l->pad / 2; a.accumulate = accumulate;
+    a.total = (long long)l->batch * l->h * l->w * (l->cp / 4);
+    const double bytes = 8.0 * l->batch * l->oh * l->ow * l->cp + (accumulate ? 8.0 : 4.0) * l->batch * l->h * l->w * l->cp;
+    LaunchScope s(ctx, "maxpool_bwd", bytes, 0);
+    maxpool_bwd_kernel<<<(unsigned)((a.total + TB - 1) / TB), TB, 0, ctx->stream>>>(a);
+    return aet_check_launch("maxpool_bwd");
+}
+
+int k_avgpool_forward(aet_layer *l, const float *x) {
+    aet_context *ctx = l->ctx;
+    const int total = l->batch * (l->cp / 4);
+    LaunchScope s(ctx, "avgpool_fwd", 4.0 * l->batch * l->h * l->w * l->cp + 4.0 * l->batch * l->cp, 0);
+    avgpool_fwd_kernel<<<(total + 127) / 128, 128, 0, ctx->stream>>>(x, l->output->d, l->batch, l->h * l->w, l->cp);
+    return aet_check_launch("avgpool_fwd");
+}
+
+int k_avgpool_backward(aet_layer *l, float *prev_delta, int accumulate) {
+    aet_context *ctx = l->ctx;
+    const long long total4 = (long long)l->batch * l->h * l->w * (l->cp / 4);
+    LaunchScope s(ctx, "avgpool_bwd", (accumulate ? 8.0 : 4.0) * l->batch * l->h * l->w * l->cp + 4.0 * l->batch * l->cp, 0);
+    avgpool_bwd_kernel<<<(unsigned)((total4 + TB - 1) / TB), TB, 0, ctx->stream>>>(l->delta->d, prev_delta, total4,
+                                                                                   l->h * l->w, l->cp, accumulate);
+    return aet_check_launch("avgpool_bwd");
+}
+
+int k_softmax_forward(aet_layer *l, const float *x, const float *truth) {
+    aet_context *ctx = l->ctx;
+    SoftmaxArgs a = {};
+    a.x = x; a.truth = truth; a.p = l->output->d; a.delta = l->delta->d; a.loss = l->loss; a.unit_loss = l->sample_loss;
+    a.groups = l->groups; a.units = l->batch * l->groups; a.n = l->c / l->groups; a.cp = l->cp;
+    a.parity = ctx->parity; a.temp = l->temperature;
+    {
+        LaunchScope s(ctx, "softmax_xent", 20.0 * l->batch * l->c, 0);
+        softmax_kernel<<<(a.units + TB / 32 - 1) / (TB / 32), TB, 0, ctx->stream>>>(a);
+        AET_TRY(aet_check_launch("softmax_xent"));
+    }
+    if (truth) {
+        float *mean_loss = l->net ? l->cost_dev + 1 : nullptr;
+        LaunchScope s(ctx, "softmax_cost", 0, 0);
+        softmax_cost_kernel<<<1, 1024, 0, ctx->stream>>>(l->sample_loss, a.units, l->cost_dev, 1.0f / l->batch, mean_loss);
+        AET_TRY(aet_check_launch("softmax_cost"));
+    }
+    return AET_OK;
+}
+
+int k_axpy(aet_context *ctx, float *y, const float *x, float a, size_t n, int accumulate, const char *name) {
+    const size_t n4 = n / 4;
+    LaunchScope s(ctx, name, (accumulate ? 12.0 : 8.0) * n, 0);
+    axpy_kernel<<<(unsigned)((n4 + TB - 1) / TB), TB, 0, ctx->stream>>>(y, x, a, n4, accumulate);
+    return aet_check_launch(name);
+}
+
+int k_fill(aet_context *ctx, float *p, float v, size_t n) {
+    const size_t n4 = n / 4;
+    LaunchScope s(ctx, "fill", 4.0 * n, 0);
+    fill_kernel<<<(unsigned)((n4 + TB - 1) / TB), TB, 0, ctx->stream>>>(p, v, n4);
+    return aet_check_launch("fill");
+}
+
+int k_step_counter(aet_context *ctx, unsigned long long *ctr) {
+    LaunchScope s(ctx, "step_counter", 0, 0);
+    step_counter_kernel<<<1, 1, 0, ctx->stream>>>(ctr);
+    return aet_check_launch("step_counter");
+}
+
+int k_dropout_forward(aet_layer *l, float *x, int generate) {
+    aet_context *ctx = l->ctx;
+    const size_t n = (size_t)l->batch * l->h * l->w * l->cp;
+    LaunchScope s(ctx, "dropout_fwd", 12.0 * n, 0);
+    dropout_fwd_kernel<<<(unsigned)((n + TB - 1) / TB), TB, 0, ctx->stream>>>(x, l->rnd, n, l->c, l->cp, l->probability,
+                                                                             1.f / (1.f - l->probability), l->seed,
+                                                                             l->step_dev, generate);
+    return aet_check_launch("dropout_fwd");
+}
+
+int k_dropout_backward(aet_layer *l, float *delta) {
+    aet_context *ctx = l->ctx;
+    const size_t n = (size_t)l->batch * l->h * l->w * l->cp;
+    LaunchScope s(ctx, "dropout_bwd", 12.0 * n, 0);
+    dropout_bwd_kernel<<<(unsigned)((n + TB - 1) / TB), TB, 0, ctx->stream>>>(delta, l->rnd, n, l->probability,
+                                                                             1.f / (1.f - l->probability));
+    return aet_check_launch("dropout_bwd");
+}
+
+int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, float lr_over_b, float momentum,
+                  float decay_term) {
+    const size_t n4 = count / 4;
+    LaunchScope s(ctx, "sgd_segment", 24.0 * count, 0);
+    sgd_segment_kernel<<<(unsigned)((n4 + TB - 1) / TB), TB, 0, ctx->stream>>>(W, U, G, n4, lr_over_b, momentum, decay_term);
+    return aet_check_launch("sgd_segment");
+}
+
+int k_sgd_arena(aet_network *net) {
+    aet_context *ctx = net->ctx;
+    LaunchScope s(ctx, "sgd_momentum", 24.0 * net->arena.used, 0);
+    sgd_arena_kernel<<<net->n_blocks, TB, 0, ctx->stream>>>(net->arena.W, net->arena.U, net->arena.G, net->block_seg,
+                                                           net->seg_table, net->hyper_dev);
+    return aet_check_launch("sgd_momentum");
+}
+
+int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev) {
+    LaunchScope s(ctx, "param_hash", 4.0 * count, 0);
+    param_hash_kernel<<<(unsigned)((count + TB - 1) / TB), TB, 0, ctx->stream>>>(p, count,
+                                                                                reinterpret_cast<unsigned long long *>(hash_dev));
+    return aet_check_launch("param_hash");
+}

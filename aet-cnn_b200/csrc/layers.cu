@@ -1,0 +1,559 @@
+// Host-side layer objects: the C restatement of the reference's NLayer subclasses.  Each layer
+// owns its output / delta tensors and its parameters exactly as the reference's constructors do
+// (dnn/ConvolutionalLayer.c:60-230, dnn/MaxPoolLayer.c:12-56, dnn/AvgPoolLayer.c:17-27,
+// dnn/SoftMaxLayer.c:20-45, dnn/DropoutLayer.c:20-50); forward / backward / update keep the
+// reference's call order and write semantics:
+//   conv forward overwrites its output; conv backward overwrites the previous delta;
+//   pool / avg-pool / softmax ADD into the previous delta; gradients ACCUMULATE until update().
+#include <math.h>
+#include <string.h>
+
+#include "common.h"
+
+namespace {
+
+int fail_invalid(const char *msg) {
+    aet_set_error("%s", msg);
+    return AET_E_INVALID;
+}
+
+int arena_create(ParamArena *a, size_t floats) {
+    a->capacity = floats;
+    a->used = 0;
+    a->owns = true;
+    if (floats == 0) return AET_OK;
+    AET_CUDA(cudaMalloc(&a->W, floats * sizeof(float)));
+    AET_CUDA(cudaMalloc(&a->U, floats * sizeof(float)));
+    AET_CUDA(cudaMalloc(&a->G, floats * sizeof(float)));
+    AET_CUDA(cudaMemset(a->W, 0, floats * sizeof(float)));
+    AET_CUDA(cudaMemset(a->U, 0, floats * sizeof(float)));
+    AET_CUDA(cudaMemset(a->G, 0, floats * sizeof(float)));
+    return AET_OK;
+}
+
+ParamSegment arena_take(ParamArena *a, size_t count) {
+    ParamSegment s;
+    s.offset = a->used;
+    s.count = count;
+    s.padded = round_up_sz(count, 1024);
+    a->used += s.padded;
+    return s;
+}
+
+uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    return z ^ (z >> 31);
+}
+
+int read_tensor_or_zero(aet_tensor *t, float *host) {
+    if (t->lazy_zero) {
+        memset(host, 0, t->count() * sizeof(float));
+        return AET_OK;
+    }
+    return aet_tensor_read(t, host);
+}
+
+}  // namespace
+
+size_t conv_param_floats(int c, int n, int size, int batch_normalize) {
+    const int cp = round_up(c, 4);
+    size_t total = round_up_sz((size_t)n * size * size * cp, 1024) + round_up_sz((size_t)round_up(n, 4), 1024);
+    if (batch_normalize) total += round_up_sz((size_t)round_up(n, 4), 1024);
+    return total;
+}
+
+void arena_destroy(ParamArena *a) {
+    if (a->owns) {
+        if (a->W) cudaFree(a->W);
+        if (a->U) cudaFree(a->U);
+        if (a->G) cudaFree(a->G);
+    }
+    a->W = a->U = a->G = nullptr;
+}
+
+int arena_create_public(ParamArena *a, size_t floats) { return arena_create(a, floats); }
+
+// ---------------------------------------------------------------------------- constructors
+aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, int h, int w, int c, int n, int groups,
+                                int size, int stride_x, int stride_y, int dilation, int padding, aet_activation activation,
+                                int batch_normalize, int train, int index) {
+    if (!ctx) { aet_set_error("null context"); return nullptr; }
+    if (groups != 1 || dilation != 1) { aet_set_error("convolutional: only groups=1, dilation=1 are supported"); return nullptr; }
+    if (batch_normalize != 0 && batch_normalize != 1) { aet_set_error("convolutional: batch_normalize must be 0 or 1"); return nullptr; }
+    if (activation != AET_LINEAR && activation != AET_RELU && activation != AET_LEAKY) { aet_set_error("convolutional: unsupported activation"); return nullptr; }
+    if (batch <= 0 || h <= 0 || w <= 0 || c <= 0 || n <= 0 || size <= 0 || stride_x <= 0 || stride_y <= 0 || padding < 0) {
+        aet_set_error("convolutional: bad geometry");
+        return nullptr;
+    }
+    const int oh = (h + 2 * padding - size) / stride_y + 1, ow = (w + 2 * padding - size) / stride_x + 1;
+    if (oh <= 0 || ow <= 0) { aet_set_error("convolutional: empty output"); return nullptr; }
+    aet_layer *l = new aet_layer();
+    l->ctx = ctx; l->type = AET_CONVOLUTIONAL; l->index = index;
+    l->batch = batch; l->c = c; l->h = h; l->w = w; l->cp = round_up(c, 4);
+    l->oc = n; l->oh = oh; l->ow = ow; l->ocp = round_up(n, 4);
+    l->size = size; l->stride_x = stride_x; l->stride_y = stride_y; l->pad = padding;
+    l->bn = batch_normalize; l->act = activation; l->train = train;
+    if (!arena) {
+        if (arena_create(&l->own_arena, conv_param_floats(c, n, size, batch_normalize)) != AET_OK) { delete l; return nullptr; }
+        arena = &l->own_arena;
+    }
+    l->arena = arena;
+    l->seg_w = arena_take(arena, (size_t)n * size * size * l->cp);
+    l->seg_b = arena_take(arena, (size_t)l->ocp);
+    if (batch_normalize) l->seg_s = arena_take(arena, (size_t)l->ocp);
+    if (arena->used > arena->capacity) { aet_set_error("parameter arena overflow"); delete l; return nullptr; }
+    l->output = aet_tensor_create(ctx, batch, n, oh, ow);
+    l->delta = train ? aet_tensor_create(ctx, batch, n, oh, ow) : nullptr;
+    if (!l->output || (train && !l->delta)) { aet_layer_destroy(l); return nullptr; }
+    if (batch_normalize) {
+        l->x = aet_tensor_create(ctx, batch, n, oh, ow);
+        float *blk = nullptr;
+        if (!l->x || cudaMalloc(&blk, (size_t)9 * l->ocp * sizeof(float)) != cudaSuccess) {
+            aet_set_error("convolutional: BN buffer allocation failed");
+            aet_layer_destroy(l);
+            return nullptr;
+        }
+        cudaMemset(blk, 0, (size_t)9 * l->ocp * sizeof(float));
+        l->mean = blk; l->variance = blk + l->ocp; l->rolling_mean = blk + 2 * l->ocp;
+        l->rolling_variance = blk + 3 * l->ocp; l->inv_std = blk + 4 * l->ocp; l->shift = blk + 5 * l->ocp;
+        l->bwd_coef = blk + 6 * l->ocp;
+        std::vector<float> ones(l->ocp, 0.f);
+        for (int i = 0; i < n; ++i) ones[i] = 1.f;
+        cudaMemcpy(layer_s(l), ones.data(), l->ocp * sizeof(float), cudaMemcpyHostToDevice);
+    }
+    // Initial weights: scale * U(-1,1), scale = sqrt(2/(size*size*c)) as dnn/WeightData.c:153-167,
+    // from a counter-based generator instead of rand().
+    {
+        std::vector<float> wts((size_t)n * c * size * size);
+        const float scale = sqrtf(2.f / (size * size * c));
+        for (size_t i = 0; i < wts.size(); ++i) {
+            uint64_t z = mix64(0xA17C0DEULL + (uint64_t)index * 0x632BE59BD9B4E019ULL + (i + 1) * 0x9E3779B97F4A7C15ULL);
+            float u = (float)(z >> 40) * (1.0f / 16777216.0f);
+            wts[i] = scale * (2.f * u - 1.f);
+        }
+        if (tensor_upload_nchw(ctx, layer_W(l), wts.data(), n, c, size, size, l->cp, false) != AET_OK) {
+            aet_layer_destroy(l);
+            return nullptr;
+        }
+    }
+    return l;
+}
+
+extern "C" aet_layer *aet_convolutional_layer_create(aet_context *ctx, int batch, int h, int w, int c, int n, int groups,
+                                                     int size, int stride_x, int stride_y, int dilation, int padding,
+                                                     aet_activation activation, int batch_normalize, int train) {
+    return conv_layer_create_in(ctx, nullptr, batch, h, w, c, n, groups, size, stride_x, stride_y, dilation, padding,
+                                activation, batch_normalize, train, 0);
+}
+
+extern "C" aet_layer *aet_maxpool_layer_create(aet_context *ctx, int batch, int h, int w, int c, int size, int stride_x,
+                                               int stride_y, int padding, int train) {
+    if (!ctx || batch <= 0 || h <= 0 || w <= 0 || c <= 0 || size <= 0 || stride_x <= 0 || stride_y <= 0 || padding < 0) {
+        aet_set_error("maxpool: bad geometry");
+        return nullptr;
+    }
+    const int oh = (h + padding - size) / stride_y + 1, ow = (w + padding - size) / stride_x + 1;  // dnn/MaxPoolLayer.c:40-41
+    if (oh <= 0 || ow <= 0) { aet_set_error("maxpool: empty output"); return nullptr; }
+    aet_layer *l = new aet_layer();
+    l->ctx = ctx; l->type = AET_MAXPOOL;
+    l->batch = batch; l->c = c; l->h = h; l->w = w; l->cp = round_up(c, 4);
+    l->oc = c; l->oh = oh; l->ow = ow; l->ocp = l->cp;
+    l->size = size; l->stride_x = stride_x; l->stride_y = stride_y; l->pad = padding; l->train = train;
+    l->output = aet_tensor_create(ctx, batch, c, oh, ow);
+    l->delta = train ? aet_tensor_create(ctx, batch, c, oh, ow) : nullptr;
+    bool ok = l->output && (!train || l->delta);
+    if (ok && train) {
+        ok = cudaMalloc(&l->indexes, l->output->elems() * sizeof(int)) == cudaSuccess &&
+             cudaMemset(l->indexes, 0xFF, l->output->elems() * sizeof(int)) == cudaSuccess;
+        if (!ok) aet_set_error("maxpool: index allocation failed");
+    }
+    if (!ok) { aet_layer_destroy(l); return nullptr; }
+    return l;
+}
+
+extern "C" aet_layer *aet_avgpool_layer_create(aet_context *ctx, int batch, int w, int h, int c) {
+    if (!ctx || batch <= 0 || h <= 0 || w <= 0 || c <= 0) { aet_set_error("avgpool: bad geometry"); return nullptr; }
+    aet_layer *l = new aet_layer();
+    l->ctx = ctx; l->type = AET_AVGPOOL;
+    l->batch = batch; l->c = c; l->h = h; l->w = w; l->cp = round_up(c, 4);
+    l->oc = c; l->oh = 1; l->ow = 1; l->ocp = l->cp;
+    l->output = aet_tensor_create(ctx, batch, c, 1, 1);
+    l->delta = aet_tensor_create(ctx, batch, c, 1, 1);
+    if (!l->output || !l->delta) { aet_layer_destroy(l); return nullptr; }
+    return l;
+}
+
+extern "C" aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int inputs, int groups, float temperature) {
+    if (!ctx || batch <= 0 || inputs <= 0 || groups <= 0 || inputs % groups || !(temperature > 0.f)) {
+        aet_set_error("softmax: bad arguments");
+        return nullptr;
+    }
+    aet_layer *l = new aet_layer();
+    l->ctx = ctx; l->type = AET_SOFTMAX;
+    l->batch = batch; l->c = inputs; l->h = 1; l->w = 1; l->cp = round_up(inputs, 4);
+    l->oc = inputs; l->oh = 1; l->ow = 1; l->ocp = l->cp;
+    l->groups = groups; l->temperature = temperature;
+    l->output = aet_tensor_create(ctx, batch, inputs, 1, 1);
+    l->delta = aet_tensor_create(ctx, batch, inputs, 1, 1);
+    bool ok = l->output && l->delta;
+    const size_t n = (size_t)batch * l->cp;
+    ok = ok && cudaMalloc(&l->loss, n * sizeof(float)) == cudaSuccess && cudaMemset(l->loss, 0, n * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&l->sample_loss, (size_t)batch * groups * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&l->cost_dev, 4 * sizeof(float)) == cudaSuccess && cudaMemset(l->cost_dev, 0, 4 * sizeof(float)) == cudaSuccess;
+    if (!ok) { aet_set_error("softmax: allocation failed"); aet_layer_destroy(l); return nullptr; }
+    return l;
+}
+
+extern "C" aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int inputs, float probability, aet_layer *prev) {
+    if (!ctx || !prev || !prev->output || batch != prev->batch || inputs != prev->oc * prev->oh * prev->ow ||
+        !(probability >= 0.f && probability < 1.f)) {
+        aet_set_error("dropout: bad arguments (needs the previous layer and a matching input count)");
+        return nullptr;
+    }
+    aet_layer *l = new aet_layer();
+    l->ctx = ctx; l->type = AET_DROPOUT; l->prev = prev;
+    l->batch = batch; l->c = prev->oc; l->h = prev->oh; l->w = prev->ow; l->cp = prev->ocp;
+    l->oc = l->c; l->oh = l->h; l->ow = l->w; l->ocp = l->cp;
+    l->probability = probability;
+    l->output = prev->output;   // aliases, not owned
+    l->delta = prev->delta;
+    const size_t n = prev->output->elems();
+    bool ok = cudaMalloc(&l->rnd, n * sizeof(float)) == cudaSuccess && cudaMemset(l->rnd, 0, n * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&l->step_dev, sizeof(unsigned long long)) == cudaSuccess &&
+         cudaMemset(l->step_dev, 0, sizeof(unsigned long long)) == cudaSuccess;
+    if (!ok) { aet_set_error("dropout: allocation failed"); aet_layer_destroy(l); return nullptr; }
+    l->seed = 0xD509ULL;
+    return l;
+}
+
+extern "C" void aet_layer_destroy(aet_layer *l) {
+    if (!l) return;
+    if (l->ctx) cudaStreamSynchronize(l->ctx->stream);
+    conv_release(l);
+    if (l->type != AET_DROPOUT) {
+        aet_tensor_destroy(l->output);
+        aet_tensor_destroy(l->delta);
+    }
+    aet_tensor_destroy(l->x);
+    if (l->mean) cudaFree(l->mean);
+    if (l->indexes) cudaFree(l->indexes);
+    if (l->loss) cudaFree(l->loss);
+    if (l->sample_loss) cudaFree(l->sample_loss);
+    if (l->cost_dev) cudaFree(l->cost_dev);
+    if (l->rnd) cudaFree(l->rnd);
+    if (l->step_dev) cudaFree(l->step_dev);
+    arena_destroy(&l->own_arena);
+    delete l;
+}
+
+// ---------------------------------------------------------------------------- forward
+static int check_input(const aet_layer *l, const aet_tensor *in) {
+    if (!in) return fail_invalid("layer forward/backward: state.input is NULL");
+    if (in->n != l->batch || in->c != l->c || in->h != l->h || in->w != l->w) {
+        aet_set_error("layer %d: input is %dx%dx%dx%d, expected %dx%dx%dx%d", l->index, in->n, in->c, in->h, in->w, l->batch,
+                      l->c, l->h, l->w);
+        return AET_E_INVALID;
+    }
+    return AET_OK;
+}
+
+extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
+    if (!l) return fail_invalid("null layer");
+    AET_TRY(check_input(l, state.input));
+    switch (l->type) {
+    case AET_CONVOLUTIONAL:
+        if (l->bn) {
+            AET_TRY(conv_fprop(l, state.input->d, l->x->d, nullptr, 0));
+            if (state.train) {
+                AET_TRY(k_bn_stats(l, 1));
+                AET_TRY(k_bn_apply(l, 0));
+            } else {
+                AET_TRY(k_bn_apply(l, 1));
+            }
+        } else {
+            AET_TRY(conv_fprop(l, state.input->d, l->output->d, layer_b(l), 1));
+        }
+        l->output->lazy_zero = false;
+        return AET_OK;
+    case AET_MAXPOOL:
+        l->output->lazy_zero = false;
+        return k_maxpool_forward(l, state.input->d);
+    case AET_AVGPOOL:
+        l->output->lazy_zero = false;
+        return k_avgpool_forward(l, state.input->d);
+    case AET_SOFTMAX: {
+        const float *truth = nullptr;
+        if (state.truth) {
+            if (state.truth->n != l->batch || state.truth->c * state.truth->h * state.truth->w != l->c)
+                return fail_invalid("softmax: truth tensor shape does not match");
+            truth = state.truth->d;
+        }
+        l->cost_valid = false;
+        AET_TRY(k_softmax_forward(l, state.input->d, truth));
+        if (truth) l->delta->lazy_zero = false;
+        return AET_OK;
+    }
+    case AET_DROPOUT:
+        if (!state.train) return AET_OK;
+        if (state.input != l->prev->output) return fail_invalid("dropout: state.input must be the previous layer's output");
+        if (!l->rnd_fixed) AET_TRY(k_step_counter(l->ctx, l->step_dev));
+        return k_dropout_forward(l, l->prev->output->d, l->rnd_fixed ? 0 : 1);
+    }
+    return fail_invalid("unknown layer type");
+}
+
+// ---------------------------------------------------------------------------- backward
+extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
+    if (!l) return fail_invalid("null layer");
+    if (!l->delta) return fail_invalid("layer was created with train=0");
+    aet_tensor *pd = state.delta;
+    if (pd && (pd->n != l->batch || pd->c != l->c || pd->h != l->h || pd->w != l->w))
+        return fail_invalid("layer backward: state.delta shape does not match the layer input");
+    switch (l->type) {
+    case AET_CONVOLUTIONAL: {
+        AET_TRY(check_input(l, state.input));
+        if (l->delta->lazy_zero) {   // nothing upstream wrote a gradient: materialise the zeros
+            AET_TRY(aet_tensor_zero(l->delta));
+            l->delta->lazy_zero = false;
+        }
+        if (l->bn) AET_TRY(k_bn_backward(l));
+        else AET_TRY(k_bias_act_backward(l));
+        AET_TRY(conv_wgrad(l, state.input->d, l->delta->d, layer_G(l), 1));
+        if (pd) {
+            AET_TRY(conv_dgrad(l, l->delta->d, pd->d));
+            pd->lazy_zero = false;
+        }
+        return AET_OK;
+    }
+    case AET_MAXPOOL:
+        if (!pd) return AET_OK;
+        if (l->delta->lazy_zero) { AET_TRY(aet_tensor_zero(l->delta)); l->delta->lazy_zero = false; }
+        AET_TRY(k_maxpool_backward(l, pd->d, pd->lazy_zero ? 0 : 1));
+        pd->lazy_zero = false;
+        return AET_OK;
+    case AET_AVGPOOL:
+        if (!pd) return AET_OK;
+        if (l->delta->lazy_zero) { AET_TRY(aet_tensor_zero(l->delta)); l->delta->lazy_zero = false; }
+        AET_TRY(k_avgpool_backward(l, pd->d, pd->lazy_zero ? 0 : 1));
+        pd->lazy_zero = false;
+        return AET_OK;
+    case AET_SOFTMAX: {
+        if (!pd) return AET_OK;
+        if (pd->cp != l->cp) return fail_invalid("softmax backward: previous delta layout mismatch");
+        // CPU path scales by 1, MTCS path by loss_scale (dnn/SoftMaxLayer.c:293-314)
+        const float ls = (l->ctx->parity == AET_PARITY_MTCS && l->net) ? l->net->loss_scale : 1.0f;
+        AET_TRY(k_axpy(l->ctx, pd->d, l->delta->d, ls, (size_t)l->batch * l->cp, pd->lazy_zero ? 0 : 1, "softmax_bwd"));
+        pd->lazy_zero = false;
+        return AET_OK;
+    }
+    case AET_DROPOUT:
+        if (!pd) return AET_OK;
+        if (pd != l->prev->delta) return fail_invalid("dropout: state.delta must be the previous layer's delta");
+        if (pd->lazy_zero) return AET_OK;
+        return k_dropout_backward(l, pd->d);
+    }
+    return fail_invalid("unknown layer type");
+}
+
+// ---------------------------------------------------------------------------- update
+extern "C" int aet_layer_update(aet_layer *l, int batch, float learning_rate, float momentum, float decay, float loss_scale) {
+    if (!l) return fail_invalid("null layer");
+    if (l->type != AET_CONVOLUTIONAL) return AET_OK;
+    if (batch <= 0 || !(loss_scale > 0.f)) return fail_invalid("update: batch and loss_scale must be positive");
+    // mtcs/MtcsConvLayer.c:582,618-631
+    const float lr = learning_rate * l->lr_scale / loss_scale;
+    const float rate = lr / batch;
+    AET_TRY(k_sgd_segment(l->ctx, layer_W(l), layer_U(l), layer_G(l), l->seg_w.padded, rate, momentum, -decay * batch * loss_scale));
+    AET_TRY(k_sgd_segment(l->ctx, layer_b(l), layer_bU(l), layer_bG(l), l->seg_b.padded, rate, momentum, 0.f));
+    if (l->bn) AET_TRY(k_sgd_segment(l->ctx, layer_s(l), layer_sU(l), layer_sG(l), l->seg_s.padded, rate, momentum, 0.f));
+    return AET_OK;
+}
+
+extern "C" int aet_layer_init_delta(aet_layer *l) {
+    if (!l) return fail_invalid("null layer");
+    if (!l->delta || l->type == AET_DROPOUT) return AET_OK;
+    AET_TRY(aet_tensor_zero(l->delta));
+    l->delta->lazy_zero = false;
+    return AET_OK;
+}
+
+extern "C" aet_tensor *aet_layer_output(aet_layer *l) { return l ? l->output : nullptr; }
+extern "C" aet_tensor *aet_layer_delta(aet_layer *l) { return l ? l->delta : nullptr; }
+extern "C" aet_layer_type aet_layer_kind(const aet_layer *l) { return l ? l->type : AET_CONVOLUTIONAL; }
+extern "C" int aet_layer_out_shape(const aet_layer *l, int *c, int *h, int *w) {
+    if (!l) return fail_invalid("null layer");
+    if (c) *c = l->oc;
+    if (h) *h = l->oh;
+    if (w) *w = l->ow;
+    return AET_OK;
+}
+
+extern "C" float aet_layer_cost(aet_layer *l) {
+    if (!l || l->type != AET_SOFTMAX) return 0.f;
+    if (!l->cost_valid) {
+        float v = 0.f;
+        if (vector_download(l->ctx, l->cost_dev, &v, 1) != AET_OK) return NAN;
+        l->cost_host = v;
+        l->cost_valid = true;
+    }
+    return l->cost_host;
+}
+
+// ---------------------------------------------------------------------------- parameter taps
+extern "C" size_t aet_layer_param_count(const aet_layer *l, aet_param which) {
+    if (!l) return 0;
+    const size_t act = (size_t)l->batch * l->oc * l->oh * l->ow;
+    switch (which) {
+    case AET_P_WEIGHTS: case AET_P_WEIGHT_UPDATES:
+        return l->type == AET_CONVOLUTIONAL ? (size_t)l->oc * l->c * l->size * l->size : 0;
+    case AET_P_BIASES: case AET_P_BIAS_UPDATES:
+        return l->type == AET_CONVOLUTIONAL ? (size_t)l->oc : 0;
+    case AET_P_SCALES: case AET_P_SCALE_UPDATES: case AET_P_ROLLING_MEAN: case AET_P_ROLLING_VARIANCE:
+    case AET_P_MEAN: case AET_P_VARIANCE:
+        return (l->type == AET_CONVOLUTIONAL && l->bn) ? (size_t)l->oc : 0;
+    case AET_P_OUTPUT: return act;
+    case AET_P_DELTA: return l->delta ? act : 0;
+    case AET_P_X: case AET_P_X_NORM: return l->x ? act : 0;
+    case AET_P_INDEXES: return l->indexes ? act : 0;
+    case AET_P_LOSS: return l->loss ? act : 0;
+    case AET_P_RAND: return l->rnd ? act : 0;
+    }
+    return 0;
+}
+
+static int read_vec_sum(aet_layer *l, const float *a, const float *b, float *host, size_t n) {
+    AET_TRY(vector_download(l->ctx, a, host, n));
+    if (b) {
+        std::vector<float> t(n);
+        AET_TRY(vector_download(l->ctx, b, t.data(), n));
+        for (size_t i = 0; i < n; ++i) host[i] += t[i];
+    }
+    return AET_OK;
+}
+
+extern "C" int aet_layer_read(aet_layer *l, aet_param which, void *host_v) {
+    if (!l || !host_v) return fail_invalid("aet_layer_read: null argument");
+    if (aet_layer_param_count(l, which) == 0) return fail_invalid("aet_layer_read: this layer has no such buffer");
+    float *host = static_cast<float *>(host_v);
+    aet_context *ctx = l->ctx;
+    const size_t nw = (size_t)l->oc * l->c * l->size * l->size;
+    switch (which) {
+    case AET_P_WEIGHTS:
+        return tensor_download_nchw(ctx, layer_W(l), host, l->oc, l->c, l->size, l->size, l->cp);
+    case AET_P_WEIGHT_UPDATES: {
+        // what the reference's weight_updates holds: carried momentum plus the pending gradient
+        AET_TRY(tensor_download_nchw(ctx, layer_U(l), host, l->oc, l->c, l->size, l->size, l->cp));
+        std::vector<float> g(nw);
+        AET_TRY(tensor_download_nchw(ctx, layer_G(l), g.data(), l->oc, l->c, l->size, l->size, l->cp));
+        for (size_t i = 0; i < nw; ++i) host[i] += g[i];
+        return AET_OK;
+    }
+    case AET_P_BIASES: return vector_download(ctx, layer_b(l), host, l->oc);
+    case AET_P_BIAS_UPDATES: return read_vec_sum(l, layer_bU(l), layer_bG(l), host, l->oc);
+    case AET_P_SCALES: return vector_download(ctx, layer_s(l), host, l->oc);
+    case AET_P_SCALE_UPDATES: return read_vec_sum(l, layer_sU(l), layer_sG(l), host, l->oc);
+    case AET_P_ROLLING_MEAN: return vector_download(ctx, l->rolling_mean, host, l->oc);
+    case AET_P_ROLLING_VARIANCE: return vector_download(ctx, l->rolling_variance, host, l->oc);
+    case AET_P_MEAN: return vector_download(ctx, l->mean, host, l->oc);
+    case AET_P_VARIANCE: return vector_download(ctx, l->variance, host, l->oc);
+    case AET_P_OUTPUT: return read_tensor_or_zero(l->output, host);
+    case AET_P_DELTA: return read_tensor_or_zero(l->delta, host);
+    case AET_P_X: return aet_tensor_read(l->x, host);
+    case AET_P_X_NORM: {
+        AET_TRY(aet_tensor_read(l->x, host));
+        std::vector<float> mean(l->oc), inv(l->oc);
+        AET_TRY(vector_download(ctx, l->mean, mean.data(), l->oc));
+        AET_TRY(vector_download(ctx, l->inv_std, inv.data(), l->oc));
+        const size_t sp = (size_t)l->oh * l->ow;
+        for (int b = 0; b < l->batch; ++b)
+            for (int c = 0; c < l->oc; ++c) {
+                float *p = host + ((size_t)b * l->oc + c) * sp;
+                for (size_t i = 0; i < sp; ++i) p[i] = (p[i] - mean[c]) * inv[c];
+            }
+        return AET_OK;
+    }
+    case AET_P_INDEXES:
+        return tensor_download_nchw_int(ctx, l->indexes, static_cast<int *>(host_v), l->batch, l->oc, l->oh, l->ow, l->ocp);
+    case AET_P_LOSS:
+        return tensor_download_nchw(ctx, l->loss, host, l->batch, l->oc, 1, 1, l->ocp);
+    case AET_P_RAND:
+        return tensor_download_nchw(ctx, l->rnd, host, l->batch, l->oc, l->oh, l->ow, l->ocp);
+    }
+    return fail_invalid("aet_layer_read: unknown selector");
+}
+
+static int write_vec(aet_layer *l, float *dev, const float *host, size_t n, float *zero_also) {
+    AET_TRY(vector_upload(l->ctx, dev, host, n));
+    if (zero_also) AET_CUDA(cudaMemsetAsync(zero_also, 0, n * sizeof(float), l->ctx->stream));
+    return AET_OK;
+}
+
+extern "C" int aet_layer_write(aet_layer *l, aet_param which, const void *host_v) {
+    if (!l || !host_v) return fail_invalid("aet_layer_write: null argument");
+    if (aet_layer_param_count(l, which) == 0) return fail_invalid("aet_layer_write: this layer has no such buffer");
+    const float *host = static_cast<const float *>(host_v);
+    aet_context *ctx = l->ctx;
+    switch (which) {
+    case AET_P_WEIGHTS:
+        return tensor_upload_nchw(ctx, layer_W(l), host, l->oc, l->c, l->size, l->size, l->cp, false);
+    case AET_P_WEIGHT_UPDATES:
+        AET_TRY(tensor_upload_nchw(ctx, layer_U(l), host, l->oc, l->c, l->size, l->size, l->cp, false));
+        AET_CUDA(cudaMemsetAsync(layer_G(l), 0, l->seg_w.padded * sizeof(float), ctx->stream));
+        return AET_OK;
+    case AET_P_BIASES: return write_vec(l, layer_b(l), host, l->oc, nullptr);
+    case AET_P_BIAS_UPDATES: return write_vec(l, layer_bU(l), host, l->oc, layer_bG(l));
+    case AET_P_SCALES: return write_vec(l, layer_s(l), host, l->oc, nullptr);
+    case AET_P_SCALE_UPDATES: return write_vec(l, layer_sU(l), host, l->oc, layer_sG(l));
+    case AET_P_ROLLING_MEAN: return write_vec(l, l->rolling_mean, host, l->oc, nullptr);
+    case AET_P_ROLLING_VARIANCE: return write_vec(l, l->rolling_variance, host, l->oc, nullptr);
+    case AET_P_MEAN: return write_vec(l, l->mean, host, l->oc, nullptr);
+    case AET_P_VARIANCE: return write_vec(l, l->variance, host, l->oc, nullptr);
+    case AET_P_OUTPUT:
+        l->output->lazy_zero = false;
+        return aet_tensor_write(l->output, host);
+    case AET_P_DELTA:
+        l->delta->lazy_zero = false;
+        return aet_tensor_write(l->delta, host);
+    case AET_P_X: return aet_tensor_write(l->x, host);
+    case AET_P_RAND:
+        l->rnd_fixed = true;
+        return tensor_upload_nchw(ctx, l->rnd, host, l->batch, l->oc, l->oh, l->ow, l->ocp, false);
+    default: break;
+    }
+    return fail_invalid("aet_layer_write: this buffer is read-only");
+}
+
+// ---------------------------------------------------------------------------- weights file records
+// dnn/ConvolutionalLayer.c:422-430 (save) and :456-486 (load): biases, then for BN layers scales,
+// rolling mean, rolling variance, then the weights [n][c][size][size].
+extern "C" int aet_layer_save_weights(aet_layer *l, void *fpv) {
+    FILE *fp = static_cast<FILE *>(fpv);
+    if (!l || !fp) return fail_invalid("aet_layer_save_weights: null argument");
+    if (l->type != AET_CONVOLUTIONAL) return AET_OK;
+    std::vector<float> v(l->oc);
+    const aet_param order[4] = {AET_P_BIASES, AET_P_SCALES, AET_P_ROLLING_MEAN, AET_P_ROLLING_VARIANCE};
+    for (int i = 0; i < (l->bn ? 4 : 1); ++i) {
+        AET_TRY(aet_layer_read(l, order[i], v.data()));
+        if (fwrite(v.data(), sizeof(float), v.size(), fp) != v.size()) { aet_set_error("weights file: short write"); return AET_E_IO; }
+    }
+    std::vector<float> wts(aet_layer_param_count(l, AET_P_WEIGHTS));
+    AET_TRY(aet_layer_read(l, AET_P_WEIGHTS, wts.data()));
+    if (fwrite(wts.data(), sizeof(float), wts.size(), fp) != wts.size()) { aet_set_error("weights file: short write"); return AET_E_IO; }
+    return AET_OK;
+}
+
+extern "C" int aet_layer_load_weights(aet_layer *l, void *fpv) {
+    FILE *fp = static_cast<FILE *>(fpv);
+    if (!l || !fp) return fail_invalid("aet_layer_load_weights: null argument");
+    if (l->type != AET_CONVOLUTIONAL) return AET_OK;
+    std::vector<float> v(l->oc);
+    const aet_param order[4] = {AET_P_BIASES, AET_P_SCALES, AET_P_ROLLING_MEAN, AET_P_ROLLING_VARIANCE};
+    for (int i = 0; i < (l->bn ? 4 : 1); ++i) {
+        if (fread(v.data(), sizeof(float), v.size(), fp) != v.size()) { aet_set_error("weights file: unexpected end (layer %d)", l->index); return AET_E_IO; }
+        AET_TRY(aet_layer_write(l, order[i], v.data()));
+    }
+    std::vector<float> wts(aet_layer_param_count(l, AET_P_WEIGHTS));
+    if (fread(wts.data(), sizeof(float), wts.size(), fp) != wts.size()) { aet_set_error("weights file: unexpected end (layer %d weights)", l->index); return AET_E_IO; }
+    return aet_layer_write(l, AET_P_WEIGHTS, wts.data());
+}

@@ -1,0 +1,743 @@
+// Network runtime: cfg reader + factory (dnn/NetworkFactory.c:77-173,328-354,543-601,671-824,
+// 830-1013 and dnn/ConfigFile.c), the forward / backward / update loops of dnn/NNetwork.c:382-396,
+// 627-654,667-716,740-813, the learning-rate schedule (:215-246), the Darknet .weights container
+// (:64-147), plus what the reference does not have: a CUDA graph of the whole training step, a flat
+// parameter arena updated by one fused kernel, and the NCCL gradient all-reduce for batch
+// data-parallel training (issued per bucket on a side stream while backward continues).
+#include <dlfcn.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+
+#include "common.h"
+
+aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, int h, int w, int c, int n, int groups,
+                                int size, int stride_x, int stride_y, int dilation, int padding, aet_activation activation,
+                                int batch_normalize, int train, int index);
+size_t conv_param_floats(int c, int n, int size, int batch_normalize);
+void arena_destroy(ParamArena *a);
+int arena_create_public(ParamArena *a, size_t floats);
+
+namespace {
+
+// ---------------------------------------------------------------------------- cfg text
+struct Section {
+    std::string name;
+    std::map<std::string, std::string> kv;
+    int line = 0;
+};
+
+std::string trim(const std::string &s) {
+    size_t a = s.find_first_not_of(" \t\r\n"), b = s.find_last_not_of(" \t\r\n");
+    return a == std::string::npos ? std::string() : s.substr(a, b - a + 1);
+}
+
+int parse_cfg(const char *text, std::vector<Section> &out) {
+    std::string all(text), line;
+    size_t pos = 0;
+    int lineno = 0;
+    while (pos <= all.size()) {
+        size_t nl = all.find('\n', pos);
+        if (nl == std::string::npos) nl = all.size();
+        line = trim(all.substr(pos, nl - pos));
+        pos = nl + 1;
+        ++lineno;
+        if (line.empty() || line[0] == '#' || line[0] == ';') continue;
+        if (line[0] == '[') {
+            size_t close = line.find(']');
+            if (close == std::string::npos) { aet_set_error("cfg line %d: missing ']'", lineno); return AET_E_IO; }
+            Section s;
+            s.name = trim(line.substr(1, close - 1));
+            s.line = lineno;
+            out.push_back(s);
+            continue;
+        }
+        size_t eq = line.find('=');
+        if (eq == std::string::npos || out.empty()) { aet_set_error("cfg line %d: expected key=value inside a section", lineno); return AET_E_IO; }
+        out.back().kv[trim(line.substr(0, eq))] = trim(line.substr(eq + 1));
+    }
+    return AET_OK;
+}
+
+int opt_int(const Section &s, const char *key, int def) {
+    auto it = s.kv.find(key);
+    return it == s.kv.end() ? def : atoi(it->second.c_str());
+}
+float opt_float(const Section &s, const char *key, float def) {
+    auto it = s.kv.find(key);
+    return it == s.kv.end() ? def : (float)atof(it->second.c_str());
+}
+std::string opt_str(const Section &s, const char *key, const char *def) {
+    auto it = s.kv.find(key);
+    return it == s.kv.end() ? std::string(def) : it->second;
+}
+
+int parse_activation(const std::string &a, aet_activation *out) {
+    if (a == "linear") *out = AET_LINEAR;
+    else if (a == "relu") *out = AET_RELU;
+    else if (a == "leaky") *out = AET_LEAKY;
+    else {
+        aet_set_error("activation '%s' is outside the supported set (linear, relu, leaky); note the reference's "
+                      "default for a missing key is 'logistic'", a.c_str());
+        return AET_E_INVALID;
+    }
+    return AET_OK;
+}
+
+const char *kUnsupportedConvKeys[] = {"binary", "xnor", "bin_output", "sway", "rotate", "stretch", "stretch_sway",
+                                      "antialiasing", "assisted_excitation", "cbn", "coordconv", "grad_centr", "reverse",
+                                      "share_index", "flipped"};
+
+// ---------------------------------------------------------------------------- NCCL through dlopen
+struct NcclUniqueId { char internal[128]; };
+typedef int (*nccl_get_unique_id_t)(NcclUniqueId *);
+typedef int (*nccl_comm_init_rank_t)(void **, int, NcclUniqueId, int);
+typedef int (*nccl_all_reduce_t)(const void *, void *, size_t, int, int, void *, cudaStream_t);
+typedef int (*nccl_comm_destroy_t)(void *);
+typedef const char *(*nccl_get_error_string_t)(int);
+struct NcclApi {
+    void *handle = nullptr;
+    nccl_get_unique_id_t get_unique_id = nullptr;
+    nccl_comm_init_rank_t comm_init_rank = nullptr;
+    nccl_all_reduce_t all_reduce = nullptr;
+    nccl_comm_destroy_t comm_destroy = nullptr;
+    nccl_get_error_string_t error_string = nullptr;
+};
+NcclApi *nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        const char *names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char *n : names) {
+            api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (api.handle) {
+            api.get_unique_id = (nccl_get_unique_id_t)dlsym(api.handle, "ncclGetUniqueId");
+            api.comm_init_rank = (nccl_comm_init_rank_t)dlsym(api.handle, "ncclCommInitRank");
+            api.all_reduce = (nccl_all_reduce_t)dlsym(api.handle, "ncclAllReduce");
+            api.comm_destroy = (nccl_comm_destroy_t)dlsym(api.handle, "ncclCommDestroy");
+            api.error_string = (nccl_get_error_string_t)dlsym(api.handle, "ncclGetErrorString");
+        }
+    }
+    if (!api.handle || !api.get_unique_id || !api.comm_init_rank || !api.all_reduce || !api.comm_destroy) {
+        aet_set_error("NCCL (libnccl.so.2) could not be loaded: %s", dlerror() ? dlerror() : "missing symbols");
+        return nullptr;
+    }
+    return &api;
+}
+int nccl_fail(NcclApi *api, int code, const char *what) {
+    aet_set_error("%s failed: %s", what, api->error_string ? api->error_string(code) : "NCCL error");
+    return AET_E_NCCL;
+}
+
+// ---------------------------------------------------------------------------- helpers
+float current_rate(const aet_network *net) {
+    // dnn/NNetwork.c:215-246
+    const size_t batch_num = (size_t)(net->seen / ((int64_t)net->batch * net->subdivisions));
+    if ((int)batch_num < net->burn_in) return net->learning_rate * powf((float)batch_num / net->burn_in, net->power);
+    switch (net->policy) {
+    case 0: return net->learning_rate;
+    case 1: return net->learning_rate * powf(net->scale, (float)(batch_num / (size_t)net->step));
+    case 2: {
+        float rate = net->learning_rate;
+        for (int i = 0; i < net->num_steps; ++i) {
+            if ((size_t)net->steps[i] > batch_num) return rate;
+            rate *= net->scales[i];
+        }
+        return rate;
+    }
+    case 3: return net->learning_rate * powf(net->gamma, (float)(int)batch_num);
+    case 4: return net->learning_rate * powf(1 - (float)batch_num / net->max_batches, net->power);
+    case 5: return net->learning_rate * (float)(1. / (1. + exp((double)net->gamma * ((double)batch_num - net->step))));
+    default: return net->learning_rate;
+    }
+}
+
+int build_sgd_tables(aet_network *net) {
+    std::vector<int> block_seg;
+    std::vector<float> seg_table;
+    int seg_id = 0;
+    for (aet_layer *l : net->layers) {
+        if (l->type != AET_CONVOLUTIONAL) continue;
+        const ParamSegment *segs[3] = {&l->seg_w, &l->seg_b, l->bn ? &l->seg_s : nullptr};
+        for (int k = 0; k < 3; ++k) {
+            if (!segs[k]) continue;
+            if (segs[k]->offset != block_seg.size() * 1024) { aet_set_error("internal: arena segments are not contiguous"); return AET_E_INVALID; }
+            for (size_t b = 0; b < segs[k]->padded / 1024; ++b) block_seg.push_back(seg_id);
+            seg_table.push_back(l->lr_scale);
+            seg_table.push_back(k == 0 ? 1.f : 0.f);
+            ++seg_id;
+        }
+    }
+    net->n_blocks = (int)block_seg.size();
+    net->n_segments = seg_id;
+    if (net->n_blocks == 0) return AET_OK;
+    AET_CUDA(cudaMalloc(&net->block_seg, block_seg.size() * sizeof(int)));
+    AET_CUDA(cudaMalloc(&net->seg_table, seg_table.size() * sizeof(float)));
+    AET_CUDA(cudaMemcpy(net->block_seg, block_seg.data(), block_seg.size() * sizeof(int), cudaMemcpyHostToDevice));
+    AET_CUDA(cudaMemcpy(net->seg_table, seg_table.data(), seg_table.size() * sizeof(float), cudaMemcpyHostToDevice));
+    return AET_OK;
+}
+
+aet_layer *softmax_layer(aet_network *net) {
+    for (size_t i = net->layers.size(); i-- > 0;)
+        if (net->layers[i]->type == AET_SOFTMAX) return net->layers[i];
+    return nullptr;
+}
+
+int upload_hyper(aet_network *net) {
+    const int world = net->world > 0 ? net->world : 1;
+    const int update_batch = net->batch * net->subdivisions * world;
+    const float rate = current_rate(net);
+    float h[4] = {rate / net->loss_scale / update_batch, net->momentum, -net->decay * update_batch * net->loss_scale, 0.f};
+    if (memcmp(h, net->hyper_host, sizeof(h)) == 0) return AET_OK;
+    memcpy(net->hyper_host, h, sizeof(h));
+    memcpy(net->loss_pinned + 4, h, sizeof(h));
+    AET_CUDA(cudaMemcpyAsync(net->hyper_dev, net->loss_pinned + 4, sizeof(h), cudaMemcpyHostToDevice, net->ctx->stream));
+    return AET_OK;
+}
+
+int net_forward(aet_network *net, aet_state state) {
+    // dnn/NNetwork.c:382-396
+    for (size_t i = 0; i < net->layers.size(); ++i) {
+        aet_layer *l = net->layers[i];
+        state.index = (int)i;
+        if (l->delta && state.train && l->type != AET_DROPOUT) l->delta->lazy_zero = true;   // initDelta, without the memset
+        AET_TRY(aet_layer_forward(l, state));
+        state.input = l->output;
+    }
+    return AET_OK;
+}
+
+int issue_allreduce(aet_network *net, size_t lo, size_t hi, int slot) {
+    NcclApi *api = nccl_api();
+    if (!api) return AET_E_NCCL;
+    aet_context *ctx = net->ctx;
+    AET_CUDA(cudaEventRecord(net->ev_grad_ready[slot], ctx->stream));
+    AET_CUDA(cudaStreamWaitEvent(net->comm_stream, net->ev_grad_ready[slot], 0));
+    float *g = net->arena.G + lo;
+    int r = api->all_reduce(g, g, hi - lo, 7 /* ncclFloat32 */, 0 /* ncclSum */, net->comm, net->comm_stream);
+    if (r != 0) return nccl_fail(api, r, "ncclAllReduce");
+    return AET_OK;
+}
+
+int net_backward(aet_network *net, aet_state state) {
+    // dnn/NNetwork.c:627-654
+    aet_tensor *original_input = state.input, *original_delta = state.delta;
+    const bool dp = net->comm != nullptr && net->world > 1;
+    const size_t bucket_floats = 64 * 1024;
+    size_t pend_lo = 0, pend_hi = 0;
+    int slot = 0;
+    for (int i = (int)net->layers.size() - 1; i >= 0; --i) {
+        aet_layer *l = net->layers[i];
+        state.index = i;
+        if (i == 0) { state.input = original_input; state.delta = original_delta; }
+        else { state.input = net->layers[i - 1]->output; state.delta = net->layers[i - 1]->delta; }
+        AET_TRY(aet_layer_backward(l, state));
+        if (dp && l->type == AET_CONVOLUTIONAL) {
+            const ParamSegment &last = l->bn ? l->seg_s : l->seg_b;
+            const size_t lo = l->seg_w.offset, hi = last.offset + last.padded;
+            if (pend_hi == pend_lo) { pend_lo = lo; pend_hi = hi; }
+            else pend_lo = lo;   // layers are laid out in order, so walking backwards extends the range downwards
+            if (pend_hi - pend_lo >= bucket_floats && slot < 7) {
+                AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
+                pend_lo = pend_hi = 0;
+            }
+        }
+    }
+    if (dp) {
+        if (pend_hi > pend_lo) AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
+        AET_CUDA(cudaEventRecord(net->ev_comm_done, net->comm_stream));
+        AET_CUDA(cudaStreamWaitEvent(net->ctx->stream, net->ev_comm_done, 0));
+    }
+    return AET_OK;
+}
+
+int run_step(aet_network *net) {
+    aet_state st = {};
+    st.truth = net->truth; st.input = net->input; st.delta = nullptr; st.train = 1;
+    AET_TRY(net_forward(net, st));
+    st.input = net->input;
+    AET_TRY(net_backward(net, st));
+    if (net->n_blocks) AET_TRY(k_sgd_arena(net));
+    return AET_OK;
+}
+
+void graph_drop(aet_network *net) {
+    if (net->graph_exec) {
+        cudaGraphExecDestroy(net->graph_exec);
+        net->graph_exec = nullptr;
+    }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------- creation
+extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_text, int train, int batch_override) {
+    if (!ctx || !cfg_text) { aet_set_error("aet_network_create: null argument"); return nullptr; }
+    std::vector<Section> secs;
+    if (parse_cfg(cfg_text, secs) != AET_OK) return nullptr;
+    if (secs.empty() || (secs[0].name != "net" && secs[0].name != "network")) {
+        aet_set_error("cfg: the first section must be [net] or [network]");
+        return nullptr;
+    }
+    aet_network *net = new aet_network();
+    net->ctx = ctx; net->train = train;
+    const Section &ns = secs[0];
+    // dnn/NetworkFactory.c:671-824
+    net->max_batches = opt_int(ns, "max_batches", 0);
+    net->batch = opt_int(ns, "batch", 1);
+    net->learning_rate = opt_float(ns, "learning_rate", .001f);
+    net->momentum = opt_float(ns, "momentum", .9f);
+    net->decay = opt_float(ns, "decay", .0001f);
+    const int subdivs = opt_int(ns, "subdivisions", 1);
+    net->batch /= subdivs > 0 ? subdivs : 1;
+    net->subdivisions = subdivs > 0 ? subdivs : 1;
+    if (batch_override > 0) { net->batch = batch_override; net->subdivisions = 1; }
+    net->loss_scale = opt_float(ns, "loss_scale", 1.f);
+    net->try_fix_nan = opt_int(ns, "try_fix_nan", 0);
+    net->h = opt_int(ns, "height", 0); net->w = opt_int(ns, "width", 0); net->c = opt_int(ns, "channels", 0);
+    net->power = opt_float(ns, "power", 4.f);
+    net->burn_in = opt_int(ns, "burn_in", 0);
+    const std::string policy = opt_str(ns, "policy", "constant");
+    if (policy == "constant") net->policy = 0;
+    else if (policy == "step") { net->policy = 1; net->step = opt_int(ns, "step", 1); net->scale = opt_float(ns, "scale", 1.f); }
+    else if (policy == "steps") {
+        net->policy = 2;
+        std::string l = opt_str(ns, "steps", ""), p = opt_str(ns, "scales", "");
+        if (l.empty() || p.empty()) { aet_set_error("cfg: STEPS policy must have steps and scales"); delete net; return nullptr; }
+        char *sv = nullptr;
+        for (char *tok = strtok_r(&l[0], ",", &sv); tok; tok = strtok_r(nullptr, ",", &sv)) net->steps.push_back(atoi(tok));
+        for (char *tok = strtok_r(&p[0], ",", &sv); tok; tok = strtok_r(nullptr, ",", &sv)) net->scales.push_back((float)atof(tok));
+        net->num_steps = (int)(net->steps.size() < net->scales.size() ? net->steps.size() : net->scales.size());
+    }
+    else if (policy == "exp") { net->policy = 3; net->gamma = opt_float(ns, "gamma", 1.f); }
+    else if (policy == "poly") net->policy = 4;
+    else if (policy == "sig") { net->policy = 5; net->gamma = opt_float(ns, "gamma", 1.f); net->step = opt_int(ns, "step", 1); }
+    else { aet_set_error("cfg: unsupported learning-rate policy '%s'", policy.c_str()); delete net; return nullptr; }
+    const std::string parity = opt_str(ns, "parity", "");
+    if (parity == "cpu") ctx->parity = AET_PARITY_CPU;
+    else if (parity == "mtcs") ctx->parity = AET_PARITY_MTCS;
+    if (net->batch <= 0 || net->h <= 0 || net->w <= 0 || net->c <= 0) {
+        aet_set_error("cfg: [net] needs positive batch, height, width and channels");
+        delete net;
+        return nullptr;
+    }
+
+    // first pass: parameter arena size
+    size_t arena_floats = 0;
+    {
+        int c = net->c, h = net->h, w = net->w;
+        for (size_t i = 1; i < secs.size(); ++i) {
+            const Section &s = secs[i];
+            if (s.name == "convolutional" || s.name == "conv") {
+                const int n = opt_int(s, "filters", 1), size = opt_int(s, "size", 1);
+                int stride = opt_int(s, "stride", 1), sx = opt_int(s, "stride_x", -1), sy = opt_int(s, "stride_y", -1);
+                if (sx < 1) sx = stride;
+                if (sy < 1) sy = stride;
+                int padding = opt_int(s, "padding", 0);
+                if (opt_int(s, "pad", 0)) padding = size / 2;
+                arena_floats += conv_param_floats(c, n, size, opt_int(s, "batch_normalize", 0));
+                h = (h + 2 * padding - size) / (sy > 0 ? sy : 1) + 1;
+                w = (w + 2 * padding - size) / (sx > 0 ? sx : 1) + 1;
+                c = n;
+            } else if (s.name == "maxpool" || s.name == "max") {
+                const int stride = opt_int(s, "stride", 1), sx = opt_int(s, "stride_x", stride), sy = opt_int(s, "stride_y", stride);
+                const int size = opt_int(s, "size", stride), padding = opt_int(s, "padding", size - 1);
+                h = (h + padding - size) / (sy > 0 ? sy : 1) + 1;
+                w = (w + padding - size) / (sx > 0 ? sx : 1) + 1;
+            } else if (s.name == "avgpool" || s.name == "avg") {
+                h = w = 1;
+            }
+        }
+    }
+    if (arena_create_public(&net->arena, arena_floats) != AET_OK) { aet_network_destroy(net); return nullptr; }
+
+    // second pass: layers (dnn/NetworkFactory.c:615-666)
+    int c = net->c, h = net->h, w = net->w;
+    for (size_t i = 1; i < secs.size(); ++i) {
+        const Section &s = secs[i];
+        aet_layer *l = nullptr;
+        const int index = (int)net->layers.size();
+        if (s.name == "convolutional" || s.name == "conv") {
+            for (const char *k : kUnsupportedConvKeys)
+                if (opt_float(s, k, 0.f) != 0.f && !(strcmp(k, "share_index") == 0 && opt_int(s, k, -1000000000) == -1000000000)) {
+                    aet_set_error("cfg line %d: convolutional option '%s' is outside the supported hot path", s.line, k);
+                    aet_network_destroy(net);
+                    return nullptr;
+                }
+            const int n = opt_int(s, "filters", 1), groups = opt_int(s, "groups", 1), size = opt_int(s, "size", 1);
+            int stride = opt_int(s, "stride", 1), sx = opt_int(s, "stride_x", -1), sy = opt_int(s, "stride_y", -1);
+            if (sx < 1) sx = stride;
+            if (sy < 1) sy = stride;
+            int dilation = opt_int(s, "dilation", 1);
+            if (size == 1) dilation = 1;
+            int padding = opt_int(s, "padding", 0);
+            if (opt_int(s, "pad", 0)) padding = size / 2;
+            aet_activation act;
+            if (parse_activation(opt_str(s, "activation", "logistic"), &act) != AET_OK) { aet_network_destroy(net); return nullptr; }
+            l = conv_layer_create_in(ctx, &net->arena, net->batch, h, w, c, n, groups, size, sx, sy, dilation, padding, act,
+                                     opt_int(s, "batch_normalize", 0), train, index);
+            if (l) l->lr_scale = opt_float(s, "learning_rate", 1.f);
+        } else if (s.name == "maxpool" || s.name == "max") {
+            const int stride = opt_int(s, "stride", 1), sx = opt_int(s, "stride_x", stride), sy = opt_int(s, "stride_y", stride);
+            const int size = opt_int(s, "size", stride), padding = opt_int(s, "padding", size - 1);
+            if (opt_int(s, "maxpool_depth", 0) || opt_int(s, "antialiasing", 0) || opt_int(s, "maxpool_zero_nonmax", 0)) {
+                aet_set_error("cfg line %d: maxpool_depth / antialiasing / maxpool_zero_nonmax are outside the supported hot path", s.line);
+                aet_network_destroy(net);
+                return nullptr;
+            }
+            l = aet_maxpool_layer_create(ctx, net->batch, h, w, c, size, sx, sy, padding, train);
+        } else if (s.name == "avgpool" || s.name == "avg") {
+            l = aet_avgpool_layer_create(ctx, net->batch, w, h, c);
+        } else if (s.name == "softmax" || s.name == "soft") {
+            if (h != 1 || w != 1) { aet_set_error("cfg line %d: softmax input must be 1x1 spatial (got %dx%d)", s.line, h, w); aet_network_destroy(net); return nullptr; }
+            if (opt_int(s, "spatial", 0) || !opt_str(s, "tree", "").empty()) { aet_set_error("cfg line %d: spatial / tree softmax are outside the supported hot path", s.line); aet_network_destroy(net); return nullptr; }
+            l = aet_softmax_layer_create(ctx, net->batch, c, opt_int(s, "groups", 1), opt_float(s, "temperature", 1.f));
+        } else if (s.name == "dropout") {
+            if (net->layers.empty()) { aet_set_error("cfg line %d: dropout cannot be the first layer", s.line); aet_network_destroy(net); return nullptr; }
+            if (opt_int(s, "dropblock", 0)) { aet_set_error("cfg line %d: dropblock is outside the supported hot path", s.line); aet_network_destroy(net); return nullptr; }
+            l = aet_dropout_layer_create(ctx, net->batch, c * h * w, opt_float(s, "probability", .2f), net->layers.back());
+            if (l) l->seed = 0xD509ULL + 0x9E3779B97F4A7C15ULL * (uint64_t)(index + 1);
+        } else {
+            aet_set_error("cfg line %d: layer type [%s] is outside the supported hot path", s.line, s.name.c_str());
+            aet_network_destroy(net);
+            return nullptr;
+        }
+        if (!l) { aet_network_destroy(net); return nullptr; }
+        l->net = net;
+        l->index = index;
+        net->layers.push_back(l);
+        c = l->oc; h = l->oh; w = l->ow;
+    }
+    if (net->layers.empty()) { aet_set_error("cfg: no layers"); aet_network_destroy(net); return nullptr; }
+    net->input = aet_tensor_create(ctx, net->batch, net->c, net->h, net->w);
+    net->truth = aet_tensor_create(ctx, net->batch, c * h * w, 1, 1);
+    bool ok = net->input && net->truth && build_sgd_tables(net) == AET_OK;
+    ok = ok && cudaMalloc(&net->hyper_dev, 4 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMallocHost(&net->loss_pinned, 16 * sizeof(float)) == cudaSuccess;
+    if (!ok) {
+        if (!strlen(aet_last_error())) aet_set_error("network allocation failed");
+        aet_network_destroy(net);
+        return nullptr;
+    }
+    memset(net->loss_pinned, 0, 16 * sizeof(float));
+    net->hyper_host[1] = -1.f;   // force the first upload
+    cudaStreamSynchronize(ctx->stream);
+    return net;
+}
+
+extern "C" aet_network *aet_network_create_from_string(aet_context *ctx, const char *cfg_text, int train) {
+    return aet_network_create_ex(ctx, cfg_text, train, 0);
+}
+
+extern "C" aet_network *aet_network_create(aet_context *ctx, const char *cfg_path, int train) {
+    if (!cfg_path) { aet_set_error("aet_network_create: null path"); return nullptr; }
+    FILE *fp = fopen(cfg_path, "rb");
+    if (!fp) { aet_set_error("cannot open cfg file %s", cfg_path); return nullptr; }
+    std::string text;
+    char buf[4096];
+    size_t n;
+    while ((n = fread(buf, 1, sizeof(buf), fp)) > 0) text.append(buf, n);
+    fclose(fp);
+    return aet_network_create_ex(ctx, text.c_str(), train, 0);
+}
+
+extern "C" void aet_network_destroy(aet_network *net) {
+    if (!net) return;
+    if (net->ctx) cudaStreamSynchronize(net->ctx->stream);
+    aet_network_comm_destroy(net);
+    graph_drop(net);
+    for (size_t i = net->layers.size(); i-- > 0;) aet_layer_destroy(net->layers[i]);
+    aet_tensor_destroy(net->input);
+    aet_tensor_destroy(net->truth);
+    arena_destroy(&net->arena);
+    if (net->block_seg) cudaFree(net->block_seg);
+    if (net->seg_table) cudaFree(net->seg_table);
+    if (net->hyper_dev) cudaFree(net->hyper_dev);
+    if (net->loss_pinned) cudaFreeHost(net->loss_pinned);
+    delete net;
+}
+
+extern "C" int aet_network_layer_count(const aet_network *net) { return net ? (int)net->layers.size() : 0; }
+extern "C" aet_layer *aet_network_layer(aet_network *net, int index) {
+    if (!net || index < 0 || index >= (int)net->layers.size()) { aet_set_error("layer index out of range"); return nullptr; }
+    return net->layers[index];
+}
+extern "C" int aet_network_batch(const aet_network *net) { return net ? net->batch : 0; }
+extern "C" int aet_network_input_shape(const aet_network *net, int *c, int *h, int *w) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    if (c) *c = net->c;
+    if (h) *h = net->h;
+    if (w) *w = net->w;
+    return AET_OK;
+}
+extern "C" int aet_network_outputs(const aet_network *net) {
+    if (!net || net->layers.empty()) return 0;
+    const aet_layer *l = net->layers.back();
+    return l->oc * l->oh * l->ow;
+}
+extern "C" aet_tensor *aet_network_input(aet_network *net) { return net ? net->input : nullptr; }
+extern "C" aet_tensor *aet_network_truth(aet_network *net) { return net ? net->truth : nullptr; }
+extern "C" float aet_network_learning_rate(const aet_network *net) { return net ? current_rate(net) : 0.f; }
+extern "C" int aet_network_set_hyper(aet_network *net, float learning_rate, float momentum, float decay) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    net->learning_rate = learning_rate; net->momentum = momentum; net->decay = decay;
+    return AET_OK;
+}
+extern "C" int64_t aet_network_seen(const aet_network *net) { return net ? net->seen : 0; }
+
+// ---------------------------------------------------------------------------- forward / backward / update
+extern "C" int aet_network_forward(aet_network *net, aet_state state) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    return net_forward(net, state);
+}
+extern "C" int aet_network_backward(aet_network *net, aet_state state) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    return net_backward(net, state);
+}
+extern "C" int aet_network_update(aet_network *net) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    AET_TRY(upload_hyper(net));
+    if (net->n_blocks) AET_TRY(k_sgd_arena(net));
+    return AET_OK;
+}
+extern "C" float aet_network_cost(aet_network *net) {
+    // dnn/NNetwork.c:611-624
+    if (!net) return 0.f;
+    float sum = 0.f;
+    int count = 0;
+    for (aet_layer *l : net->layers)
+        if (l->type == AET_SOFTMAX) { sum += aet_layer_cost(l); ++count; }
+    return count ? sum / count : 0.f;
+}
+
+extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    if (!net->train) { aet_set_error("network was created with train=0"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    net->seen += net->batch;           // dnn/NNetwork.c:742
+    net->cur_iteration += 1;           // :773
+    AET_TRY(upload_hyper(net));
+    aet_layer *sm = softmax_layer(net);
+    if (sm) sm->cost_valid = false;
+    const long before = ctx->launches;
+    if (net->use_graph && net->graph_exec) {
+        AET_CUDA(cudaGraphLaunch(net->graph_exec, ctx->stream));
+        ctx->launches += net->launches_per_step;
+    } else if (net->use_graph && net->cur_iteration > 1 && !ctx->profiling) {
+        // the first eager step has sized every scratch buffer; capture the second one
+        cudaGraph_t graph = nullptr;
+        AET_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        ctx->capturing = true;
+        int r = run_step(net);
+        ctx->capturing = false;
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+        if (r != AET_OK) { if (graph) cudaGraphDestroy(graph); return r; }
+        if (e != cudaSuccess) { aet_set_error("graph capture failed: %s", cudaGetErrorString(e)); return AET_E_CUDA; }
+        net->launches_per_step = ctx->launches - before;
+        e = cudaGraphInstantiate(&net->graph_exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) { aet_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); net->graph_exec = nullptr; return AET_E_CUDA; }
+        AET_CUDA(cudaGraphLaunch(net->graph_exec, ctx->stream));
+    } else {
+        AET_TRY(run_step(net));
+        net->launches_per_step = ctx->launches - before;
+    }
+    if (loss) return aet_network_last_loss(net, loss);
+    return AET_OK;
+}
+
+extern "C" int aet_network_last_loss(aet_network *net, float *loss) {
+    if (!net || !loss) { aet_set_error("null argument"); return AET_E_INVALID; }
+    aet_layer *sm = softmax_layer(net);
+    if (!sm) { *loss = 0.f; return AET_OK; }
+    AET_CUDA(cudaMemcpyAsync(net->loss_pinned, sm->cost_dev, 2 * sizeof(float), cudaMemcpyDeviceToHost, net->ctx->stream));
+    AET_CUDA(cudaStreamSynchronize(net->ctx->stream));
+    sm->cost_host = net->loss_pinned[0];
+    sm->cost_valid = true;
+    *loss = net->loss_pinned[1];
+    return AET_OK;
+}
+
+extern "C" int aet_network_train_step(aet_network *net, const float *host_x, const float *host_truth, float *loss) {
+    if (!net || !host_x || !host_truth) { aet_set_error("aet_network_train_step: null argument"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    // both uploads share the pinned mirror: stage x and truth back to back in it
+    const size_t nx = net->input->count(), nt = net->truth->count();
+    AET_TRY(ctx_staging(ctx, (nx + nt) * sizeof(float)));
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    memcpy(ctx->pinned, host_x, nx * sizeof(float));
+    memcpy(ctx->pinned + nx, host_truth, nt * sizeof(float));
+    AET_CUDA(cudaMemcpyAsync(ctx->staging, ctx->pinned, (nx + nt) * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AET_TRY(tensor_upload_staged(ctx, net->input->d, ctx->staging, net->input->n, net->input->c, net->input->h, net->input->w, net->input->cp));
+    AET_TRY(tensor_upload_staged(ctx, net->truth->d, ctx->staging + nx, net->truth->n, net->truth->c, 1, 1, net->truth->cp));
+    return aet_network_train_step_device(net, loss);
+}
+
+extern "C" int aet_network_predict(aet_network *net, const float *host_x, float *host_out) {
+    if (!net || !host_x || !host_out) { aet_set_error("aet_network_predict: null argument"); return AET_E_INVALID; }
+    AET_TRY(aet_tensor_write(net->input, host_x));
+    aet_state st = {};
+    st.input = net->input; st.train = 0;
+    AET_TRY(net_forward(net, st));
+    return aet_tensor_read(net->layers.back()->output, host_out);
+}
+
+extern "C" int aet_network_use_graph(aet_network *net, int enable) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    net->use_graph = enable != 0;
+    if (!enable) graph_drop(net);
+    return AET_OK;
+}
+
+// ---------------------------------------------------------------------------- weights container
+extern "C" int aet_network_save_weights(aet_network *net, const char *path) {
+    if (!net || !path) { aet_set_error("null argument"); return AET_E_INVALID; }
+    FILE *fp = fopen(path, "wb");
+    if (!fp) { aet_set_error("cannot open %s for writing", path); return AET_E_IO; }
+    const int32_t header[3] = {0, 2, 5};
+    const uint64_t seen = (uint64_t)net->cur_iteration * net->batch * net->subdivisions;   // dnn/NNetwork.c:126
+    bool ok = fwrite(header, sizeof(int32_t), 3, fp) == 3 && fwrite(&seen, sizeof(uint64_t), 1, fp) == 1;
+    int r = ok ? AET_OK : AET_E_IO;
+    for (size_t i = 0; r == AET_OK && i < net->layers.size(); ++i) r = aet_layer_save_weights(net->layers[i], fp);
+    fclose(fp);
+    if (!ok) aet_set_error("weights file: short write");
+    return r;
+}
+
+extern "C" int aet_network_load_weights(aet_network *net, const char *path) {
+    if (!net || !path) { aet_set_error("null argument"); return AET_E_INVALID; }
+    FILE *fp = fopen(path, "rb");
+    if (!fp) { aet_set_error("cannot open weights file %s", path); return AET_E_IO; }
+    int32_t header[3];
+    if (fread(header, sizeof(int32_t), 3, fp) != 3) { fclose(fp); aet_set_error("weights file: short header"); return AET_E_IO; }
+    if (header[0] * 10 + header[1] >= 2) {
+        uint64_t seen = 0;
+        if (fread(&seen, sizeof(uint64_t), 1, fp) != 1) { fclose(fp); aet_set_error("weights file: short header"); return AET_E_IO; }
+        net->seen = (int64_t)seen;
+    } else {
+        int32_t seen = 0;
+        if (fread(&seen, sizeof(int32_t), 1, fp) != 1) { fclose(fp); aet_set_error("weights file: short header"); return AET_E_IO; }
+        net->seen = seen;
+    }
+    if (header[0] > 1000 || header[1] > 1000) { fclose(fp); aet_set_error("weights file: transposed ('flipped') files are not supported"); return AET_E_IO; }
+    net->cur_iteration = net->seen / ((int64_t)net->batch * net->subdivisions);
+    int r = AET_OK;
+    for (size_t i = 0; r == AET_OK && i < net->layers.size(); ++i) r = aet_layer_load_weights(net->layers[i], fp);
+    fclose(fp);
+    return r;
+}
+
+extern "C" int aet_network_param_hash(aet_network *net, uint64_t *hash) {
+    if (!net || !hash) { aet_set_error("null argument"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    uint64_t *dev = nullptr;
+    AET_CUDA(cudaMalloc(&dev, sizeof(uint64_t)));
+    AET_CUDA(cudaMemsetAsync(dev, 0, sizeof(uint64_t), ctx->stream));
+    int r = k_param_hash(ctx, net->arena.W, net->arena.used, dev);
+    if (r == AET_OK) r = k_param_hash(ctx, net->arena.U, net->arena.used, dev);
+    if (r == AET_OK) {
+        cudaError_t e = cudaMemcpyAsync(hash, dev, sizeof(uint64_t), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) { aet_set_error("param hash read-back failed: %s", cudaGetErrorString(e)); r = AET_E_CUDA; }
+    }
+    cudaFree(dev);
+    return r;
+}
+
+// ---------------------------------------------------------------------------- profiling
+extern "C" int aet_network_profile(aet_network *net, int enable) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->profiling = enable != 0;
+    ctx->records.clear();
+    ctx->event_next = 0;
+    return AET_OK;
+}
+
+extern "C" int aet_network_profile_read(aet_network *net, aet_kernel_time *table, int capacity, int *count) {
+    if (!net || !table || !count) { aet_set_error("null argument"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    int n = 0;
+    for (const ProfileRecord &r : ctx->records) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
+        int k = 0;
+        for (; k < n; ++k)
+            if (strcmp(table[k].name, r.name) == 0 && table[k].algo_bytes == r.bytes && table[k].algo_flops == r.flops) break;
+        if (k == n) {
+            if (n == capacity) continue;
+            memset(&table[n], 0, sizeof(table[n]));
+            strncpy(table[n].name, r.name, sizeof(table[n].name) - 1);
+            table[n].algo_bytes = r.bytes;
+            table[n].algo_flops = r.flops;
+            ++n;
+        }
+        table[k].launches += 1;
+        table[k].total_ms += ms;
+    }
+    *count = n;
+    return AET_OK;
+}
+
+extern "C" int aet_network_launches_per_step(const aet_network *net) { return net ? (int)net->launches_per_step : 0; }
+
+// ---------------------------------------------------------------------------- data parallel
+extern "C" int aet_comm_unique_id(void *unique_id_128) {
+    if (!unique_id_128) { aet_set_error("null argument"); return AET_E_INVALID; }
+    NcclApi *api = nccl_api();
+    if (!api) return AET_E_NCCL;
+    NcclUniqueId id;
+    int r = api->get_unique_id(&id);
+    if (r != 0) return nccl_fail(api, r, "ncclGetUniqueId");
+    memcpy(unique_id_128, &id, sizeof(id));
+    return AET_OK;
+}
+
+extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128, int rank, int world) {
+    if (!net || !unique_id_128 || world < 1 || rank < 0 || rank >= world) { aet_set_error("aet_network_comm_init: bad arguments"); return AET_E_INVALID; }
+    if (net->comm) { aet_set_error("communicator already initialised"); return AET_E_INVALID; }
+    NcclApi *api = nccl_api();
+    if (!api) return AET_E_NCCL;
+    AET_CUDA(cudaSetDevice(net->ctx->device));
+    NcclUniqueId id;
+    memcpy(&id, unique_id_128, sizeof(id));
+    void *comm = nullptr;
+    int r = api->comm_init_rank(&comm, world, id, rank);
+    if (r != 0) return nccl_fail(api, r, "ncclCommInitRank");
+    net->comm = comm; net->rank = rank; net->world = world;
+    AET_CUDA(cudaStreamCreateWithFlags(&net->comm_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 8; ++i) AET_CUDA(cudaEventCreateWithFlags(&net->ev_grad_ready[i], cudaEventDisableTiming));
+    AET_CUDA(cudaEventCreateWithFlags(&net->ev_comm_done, cudaEventDisableTiming));
+    graph_drop(net);
+    net->hyper_host[1] = -1.f;
+    return AET_OK;
+}
+
+extern "C" int aet_network_comm_destroy(aet_network *net) {
+    if (!net || !net->comm) return AET_OK;
+    cudaStreamSynchronize(net->ctx->stream);
+    cudaStreamSynchronize(net->comm_stream);
+    graph_drop(net);
+    NcclApi *api = nccl_api();
+    if (api) api->comm_destroy(net->comm);
+    net->comm = nullptr; net->world = 1; net->rank = 0;
+    for (int i = 0; i < 8; ++i) if (net->ev_grad_ready[i]) { cudaEventDestroy(net->ev_grad_ready[i]); net->ev_grad_ready[i] = nullptr; }
+    if (net->ev_comm_done) { cudaEventDestroy(net->ev_comm_done); net->ev_comm_done = nullptr; }
+    if (net->comm_stream) { cudaStreamDestroy(net->comm_stream); net->comm_stream = nullptr; }
+    return AET_OK;
+}
+
+extern "C" int aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count) {
+    if (!net || !device_ptr || !count) { aet_set_error("null argument"); return AET_E_INVALID; }
+    *device_ptr = net->arena.G;
+    *count = net->arena.used;
+    return AET_OK;
+}

@@ -1,0 +1,310 @@
+// Context (device, stream, scratch arena, status word, per-kernel profiling) and tensor
+// containers with their host taps.  The host side of every tap speaks the reference's layout
+// (FP32 NCHW, dnn/NData.h:14-68); device storage is NHWC padded to 4 channels, so a tap is one
+// copy plus one transposing kernel.  Replaces MtcsMem / MtcsStream call sites
+// (mtcs/MtcsTool.c:22-30, mtcs/MtcsIOData.c:15-52) and DataFactory.create*Data.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.h"
+
+static thread_local char g_error[512] = "";
+
+void aet_set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+extern "C" const char *aet_last_error(void) { return g_error; }
+extern "C" const char *aet_version(void) { return "aet-cnn-b200 0.1 (sm_100a)"; }
+
+namespace {
+
+// NCHW (dense, c channels) <-> NHWC (cp channels); pad channels are written as zero.
+__global__ void nchw_to_nhwc_kernel(const float *__restrict__ src, float *__restrict__ dst, int n, int c, int h, int w,
+                                    int cp) {
+    size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)n * h * w * cp;
+    if (e >= total) return;
+    const int ch = (int)(e % cp);
+    size_t p = e / cp;
+    const int x = (int)(p % w); p /= w;
+    const int y = (int)(p % h);
+    const int b = (int)(p / h);
+    dst[e] = ch < c ? src[(((size_t)b * c + ch) * h + y) * w + x] : 0.f;
+}
+__global__ void nhwc_to_nchw_kernel(const float *__restrict__ src, float *__restrict__ dst, int n, int c, int h, int w,
+                                    int cp) {
+    size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)n * c * h * w;
+    if (e >= total) return;
+    const int x = (int)(e % w);
+    size_t p = e / w;
+    const int y = (int)(p % h); p /= h;
+    const int ch = (int)(p % c);
+    const int b = (int)(p / c);
+    dst[e] = src[(((size_t)b * h + y) * w + x) * cp + ch];
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------- profiling
+void prof_begin(aet_context *ctx, const char *name, double bytes, double flops) {
+    if (ctx->event_next + 2 > ctx->event_pool.size()) {
+        for (int i = 0; i < 256; ++i) {
+            cudaEvent_t e;
+            if (cudaEventCreate(&e) != cudaSuccess) return;
+            ctx->event_pool.push_back(e);
+        }
+    }
+    ProfileRecord r;
+    r.name = name; r.bytes = bytes; r.flops = flops;
+    r.e0 = ctx->event_pool[ctx->event_next++];
+    r.e1 = ctx->event_pool[ctx->event_next++];
+    cudaEventRecord(r.e0, ctx->stream);
+    ctx->records.push_back(r);
+}
+void prof_end(aet_context *ctx) {
+    if (!ctx->records.empty()) cudaEventRecord(ctx->records.back().e1, ctx->stream);
+}
+
+int ctx_scratch(aet_context *ctx, size_t bytes, float **out) {
+    if (bytes > ctx->scratch_bytes) {
+        if (ctx->capturing) {
+            aet_set_error("scratch arena too small during graph capture (%zu > %zu)", bytes, ctx->scratch_bytes);
+            return AET_E_NOMEM;
+        }
+        AET_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch) cudaFree(ctx->scratch);
+        ctx->scratch = nullptr;
+        ctx->scratch_bytes = 0;
+        size_t want = round_up_sz(bytes + bytes / 4, 1 << 20);
+        AET_CUDA(cudaMalloc(&ctx->scratch, want));
+        ctx->scratch_bytes = want;
+    }
+    *out = ctx->scratch;
+    return AET_OK;
+}
+
+int ctx_staging(aet_context *ctx, size_t bytes) {
+    if (bytes > ctx->staging_bytes) {
+        if (ctx->capturing) {
+            aet_set_error("staging buffer too small during graph capture");
+            return AET_E_NOMEM;
+        }
+        AET_CUDA(cudaStreamSynchronize(ctx->stream));
+        if (ctx->staging) cudaFree(ctx->staging);
+        if (ctx->pinned) cudaFreeHost(ctx->pinned);
+        ctx->staging = nullptr; ctx->pinned = nullptr; ctx->staging_bytes = 0; ctx->pinned_bytes = 0;
+        size_t want = round_up_sz(bytes, 1 << 20);
+        AET_CUDA(cudaMalloc(&ctx->staging, want));
+        AET_CUDA(cudaMallocHost(&ctx->pinned, want));
+        ctx->staging_bytes = want;
+        ctx->pinned_bytes = want;
+    }
+    return AET_OK;
+}
+
+// ---------------------------------------------------------------------------- context
+extern "C" aet_context *aet_context_create(int device) {
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        aet_set_error("no CUDA device available (%s); this library has no CPU path", cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (device < 0 || device >= count) {
+        aet_set_error("device %d out of range (0..%d)", device, count - 1);
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) {
+        aet_set_error("cudaSetDevice(%d) failed", device);
+        return nullptr;
+    }
+    cudaDeviceProp prop;
+    cudaGetDeviceProperties(&prop, device);
+    if (prop.major != 10) {
+        aet_set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+        return nullptr;
+    }
+    aet_context *ctx = new aet_context();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        aet_set_error("cudaStreamCreate failed");
+        delete ctx;
+        return nullptr;
+    }
+    ctx->owns_stream = true;
+    if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess || cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
+        aet_set_error("status word allocation failed");
+        delete ctx;
+        return nullptr;
+    }
+    const char *path = getenv("AET_CONV_PATH");
+    if (path && strcmp(path, "gather") == 0) ctx->conv_path = 1;
+    return ctx;
+}
+
+extern "C" void aet_context_destroy(aet_context *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
+    if (ctx->staging) cudaFree(ctx->staging);
+    if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+extern "C" int aet_context_set_stream(aet_context *ctx, void *cuda_stream) {
+    if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (cuda_stream) {
+        ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+        ctx->owns_stream = false;
+    } else {
+        AET_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        ctx->owns_stream = true;
+    }
+    return AET_OK;
+}
+extern "C" void *aet_context_stream(aet_context *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+extern "C" int aet_context_set_parity(aet_context *ctx, aet_parity_mode mode) {
+    if (!ctx || (mode != AET_PARITY_CPU && mode != AET_PARITY_MTCS)) { aet_set_error("bad parity mode"); return AET_E_INVALID; }
+    ctx->parity = mode;
+    return AET_OK;
+}
+extern "C" int aet_context_set_math(aet_context *ctx, aet_math_mode mode) {
+    if (!ctx || (mode != AET_MATH_TF32 && mode != AET_MATH_3XTF32)) { aet_set_error("bad math mode"); return AET_E_INVALID; }
+    ctx->math = mode;
+    return AET_OK;
+}
+extern "C" int aet_context_synchronize(aet_context *ctx) {
+    if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AET_OK;
+}
+extern "C" int aet_context_check(aet_context *ctx) {
+    if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
+    int st = 0;
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    AET_CUDA(cudaMemcpy(&st, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        cudaMemset(ctx->status_dev, 0, sizeof(int));
+        aet_set_error("a bounded device-side wait expired (status %d)", st);
+        return AET_E_TIMEOUT;
+    }
+    return AET_OK;
+}
+
+// ---------------------------------------------------------------------------- layout taps
+int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int n, int c, int h, int w, int cp,
+                       bool async_pinned) {
+    const size_t dense = (size_t)n * c * h * w;
+    if (dense == 0) return AET_OK;
+    AET_TRY(ctx_staging(ctx, dense * sizeof(float)));
+    if (async_pinned) {
+        // the pinned mirror is reused every step: wait for the previous upload to have left it
+        AET_CUDA(cudaStreamSynchronize(ctx->stream));
+        memcpy(ctx->pinned, host, dense * sizeof(float));
+        AET_CUDA(cudaMemcpyAsync(ctx->staging, ctx->pinned, dense * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+        AET_CUDA(cudaMemcpyAsync(ctx->staging, host, dense * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    }
+    const size_t total = (size_t)n * h * w * cp;
+    ctx->launches++;
+    nchw_to_nhwc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(ctx->staging, dev_nhwc, n, c, h, w, cp);
+    AET_TRY(aet_check_launch("nchw_to_nhwc"));
+    if (!async_pinned) AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AET_OK;
+}
+
+// Transposes a dense NCHW image already resident in device memory into the NHWC tensor.
+int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp) {
+    const size_t total = (size_t)n * h * w * cp;
+    ctx->launches++;
+    nchw_to_nhwc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(dev_nchw, dev_nhwc, n, c, h, w, cp);
+    return aet_check_launch("nchw_to_nhwc");
+}
+
+int tensor_download_nchw(aet_context *ctx, const float *dev_nhwc, float *host, int n, int c, int h, int w, int cp) {
+    const size_t dense = (size_t)n * c * h * w;
+    if (dense == 0) return AET_OK;
+    AET_TRY(ctx_staging(ctx, dense * sizeof(float)));
+    ctx->launches++;
+    nhwc_to_nchw_kernel<<<(unsigned)((dense + 255) / 256), 256, 0, ctx->stream>>>(dev_nhwc, ctx->staging, n, c, h, w, cp);
+    AET_TRY(aet_check_launch("nhwc_to_nchw"));
+    AET_CUDA(cudaMemcpyAsync(host, ctx->staging, dense * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AET_OK;
+}
+
+int tensor_download_nchw_int(aet_context *ctx, const int *dev_nhwc, int *host, int n, int c, int h, int w, int cp) {
+    // the transposing kernel only moves 32-bit words
+    return tensor_download_nchw(ctx, reinterpret_cast<const float *>(dev_nhwc), reinterpret_cast<float *>(host), n, c, h, w, cp);
+}
+
+int vector_upload(aet_context *ctx, float *dev, const float *host, size_t count) {
+    AET_CUDA(cudaMemcpyAsync(dev, host, count * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AET_OK;
+}
+int vector_download(aet_context *ctx, const float *dev, float *host, size_t count) {
+    AET_CUDA(cudaMemcpyAsync(host, dev, count * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AET_OK;
+}
+
+// ---------------------------------------------------------------------------- tensors
+extern "C" aet_tensor *aet_tensor_create(aet_context *ctx, int batch, int c, int h, int w) {
+    if (!ctx || batch <= 0 || c <= 0 || h <= 0 || w <= 0) {
+        aet_set_error("aet_tensor_create: bad shape %d x %d x %d x %d", batch, c, h, w);
+        return nullptr;
+    }
+    aet_tensor *t = new aet_tensor();
+    t->ctx = ctx; t->n = batch; t->c = c; t->h = h; t->w = w; t->cp = round_up(c, 4);
+    if (cudaMalloc(&t->d, t->elems() * sizeof(float)) != cudaSuccess ||
+        cudaMemsetAsync(t->d, 0, t->elems() * sizeof(float), ctx->stream) != cudaSuccess) {
+        aet_set_error("aet_tensor_create: device allocation of %zu bytes failed", t->elems() * sizeof(float));
+        cudaGetLastError();
+        delete t;
+        return nullptr;
+    }
+    return t;
+}
+extern "C" void aet_tensor_destroy(aet_tensor *t) {
+    if (!t) return;
+    if (t->owns && t->d) {
+        cudaStreamSynchronize(t->ctx->stream);
+        cudaFree(t->d);
+    }
+    delete t;
+}
+extern "C" int aet_tensor_shape(const aet_tensor *t, int *batch, int *c, int *h, int *w) {
+    if (!t) { aet_set_error("null tensor"); return AET_E_INVALID; }
+    if (batch) *batch = t->n;
+    if (c) *c = t->c;
+    if (h) *h = t->h;
+    if (w) *w = t->w;
+    return AET_OK;
+}
+extern "C" size_t aet_tensor_count(const aet_tensor *t) { return t ? t->count() : 0; }
+extern "C" int aet_tensor_write(aet_tensor *t, const float *host_nchw) {
+    if (!t || !host_nchw) { aet_set_error("aet_tensor_write: null argument"); return AET_E_INVALID; }
+    return tensor_upload_nchw(t->ctx, t->d, host_nchw, t->n, t->c, t->h, t->w, t->cp, false);
+}
+extern "C" int aet_tensor_read(const aet_tensor *t, float *host_nchw) {
+    if (!t || !host_nchw) { aet_set_error("aet_tensor_read: null argument"); return AET_E_INVALID; }
+    return tensor_download_nchw(t->ctx, t->d, host_nchw, t->n, t->c, t->h, t->w, t->cp);
+}
+extern "C" int aet_tensor_zero(aet_tensor *t) {
+    if (!t) { aet_set_error("null tensor"); return AET_E_INVALID; }
+    AET_CUDA(cudaMemsetAsync(t->d, 0, t->elems() * sizeof(float), t->ctx->stream));
+    return AET_OK;
+}

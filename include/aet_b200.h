@@ -1,0 +1,210 @@
+/*
+ * aet_b200.h -- C ABI of the B200-native replacement for the AET-CNN training hot path.
+ *
+ * Every entry point replaces one seam of the reference (paths are inside the reference
+ * project; dnn/ = src/com/ai/dnn/, mtcs/ = src/com/ai/dnn/mtcs/).  The reference selects its
+ * back end by subclassing: mtcs/MtcsConvLayer.h:20, mtcs/MtcsIOData.h:12 override the CPU
+ * classes' virtual forward/backward/update (dnn/NLayer.h:159-166).  This header restates that
+ * seam as plain C: opaque handles, plain pointers and sizes, int status codes.
+ *
+ * Conventions
+ *   - Host-visible tensor layout is the reference's: FP32, NCHW, contiguous
+ *     (dnn/NData.h:14-68).  Device storage is private (NHWC, channel-padded to 4).
+ *   - Every function returning int returns AET_OK (0) or a negative AET_E_* code; the
+ *     message is available from aet_last_error().  Nothing aborts the process and no device
+ *     code traps: device-side waits are bounded and report through the status code.
+ *   - One host thread drives one context (as in the reference: mtcs/MtcsTool.c:22-30).
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     AET_E_CUDA.
+ */
+#ifndef AET_B200_H
+#define AET_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AET_OK            0
+#define AET_E_INVALID   (-1)   /* bad argument / unsupported configuration */
+#define AET_E_CUDA      (-2)   /* CUDA runtime or driver error */
+#define AET_E_NOMEM     (-3)
+#define AET_E_IO        (-4)   /* cfg or weights file */
+#define AET_E_TIMEOUT   (-5)   /* a bounded device-side wait expired */
+#define AET_E_NCCL      (-6)
+#define AET_E_NAN       (-7)   /* non-finite values detected (try_fix_nan diagnostics) */
+
+/* dnn/Activation.h:15-19 (only the types on the hot path) */
+typedef enum { AET_LINEAR = 0, AET_RELU = 1, AET_LEAKY = 2 } aet_activation;
+/* dnn/NLayer.c:30-60 layer kinds that NetworkFactory.createLayer instantiates on the hot path */
+typedef enum { AET_CONVOLUTIONAL = 0, AET_MAXPOOL = 1, AET_AVGPOOL = 2, AET_SOFTMAX = 3, AET_DROPOUT = 4 } aet_layer_type;
+/* Which of the reference's two numerically different back ends the formulas follow:
+ * the CPU classes (dnn/NormData.c, dnn/DeltaData.c, ...) or the MTCS kernels (mtcs/...). */
+typedef enum { AET_PARITY_CPU = 0, AET_PARITY_MTCS = 1 } aet_parity_mode;
+/* Tensor-core input precision of the implicit-GEMM kernels (accumulation is always FP32). */
+typedef enum { AET_MATH_TF32 = 0, AET_MATH_3XTF32 = 1 } aet_math_mode;
+
+/* Parameter / buffer selectors for aet_layer_read / aet_layer_write. */
+typedef enum {
+    AET_P_WEIGHTS = 0,       /* [n][c][size][size]   dnn/WeightData.h:24-82 */
+    AET_P_WEIGHT_UPDATES,    /* same shape; momentum buffer plus pending gradient */
+    AET_P_BIASES,            /* [n]                  dnn/BiasData.h */
+    AET_P_BIAS_UPDATES,
+    AET_P_SCALES,            /* [n] BN gamma         dnn/ScaleData.h */
+    AET_P_SCALE_UPDATES,
+    AET_P_ROLLING_MEAN,      /* dnn/NormData.h:20-40 */
+    AET_P_ROLLING_VARIANCE,
+    AET_P_MEAN,
+    AET_P_VARIANCE,
+    AET_P_OUTPUT,            /* layer output  [batch][c][h][w] */
+    AET_P_DELTA,             /* layer delta   [batch][c][h][w] */
+    AET_P_X,                 /* BN input saved by normalize (dnn/NormData.c:244-282) */
+    AET_P_X_NORM,            /* recomputed on read: (x-mean)*inv_std */
+    AET_P_INDEXES,           /* max-pool argmax, int32, reference numbering (dnn/MaxPoolLayer.c:250-270) */
+    AET_P_LOSS,              /* per-element cross entropy (dnn/SoftMaxLayer.c:47-55) */
+    AET_P_RAND               /* dropout uniforms (dnn/DropoutLayer.c:55-70) */
+} aet_param;
+
+typedef struct aet_context aet_context;
+typedef struct aet_tensor  aet_tensor;    /* NData / IOData / DeltaData / TruthData */
+typedef struct aet_layer   aet_layer;     /* NLayer and subclasses */
+typedef struct aet_network aet_network;   /* NNetwork */
+
+/* dnn/NLayer.h:21-29 NetworkState, passed by value exactly like the reference does. */
+typedef struct aet_state {
+    aet_tensor *truth;
+    aet_tensor *input;
+    aet_tensor *delta;      /* previous layer's delta; NULL for the first layer */
+    float      *workspace;  /* device scratch; NULL lets the layer use the context's */
+    int         train;
+    int         index;
+} aet_state;
+
+/* ------------------------------------------------------------------ context
+ * Replaces the MtcsTool / MtcsStream / MtcsMem singletons (call sites mtcs/MtcsTool.c:22-30,
+ * mtcs/MtcsIOData.c:21,47-51).  One context = one device + one stream + one scratch arena. */
+const char  *aet_last_error(void);
+const char  *aet_version(void);
+aet_context *aet_context_create(int device);
+void         aet_context_destroy(aet_context *ctx);
+/* Use an externally owned cudaStream_t (NULL = a stream the context creates itself). */
+int          aet_context_set_stream(aet_context *ctx, void *cuda_stream);
+void        *aet_context_stream(aet_context *ctx);
+int          aet_context_set_parity(aet_context *ctx, aet_parity_mode mode);
+int          aet_context_set_math(aet_context *ctx, aet_math_mode mode);
+int          aet_context_synchronize(aet_context *ctx);
+/* Reads and clears the device status word written by bounded waits; AET_OK or AET_E_TIMEOUT. */
+int          aet_context_check(aet_context *ctx);
+
+/* ------------------------------------------------------------------ tensors
+ * Replaces DataFactory.createOutputData/createDeltaData/createInputData/createTruthData
+ * (dnn/DataFactory.h:24-39) and the H2D/D2H taps of mtcs/MtcsIOData.c:47-52. */
+aet_tensor *aet_tensor_create(aet_context *ctx, int batch, int c, int h, int w);
+void        aet_tensor_destroy(aet_tensor *t);
+int         aet_tensor_shape(const aet_tensor *t, int *batch, int *c, int *h, int *w);
+int         aet_tensor_write(aet_tensor *t, const float *host_nchw);  /* InputData.setImageData */
+int         aet_tensor_read(const aet_tensor *t, float *host_nchw);
+int         aet_tensor_zero(aet_tensor *t);                             /* NData.setZero dnn/NData.c:232 */
+size_t      aet_tensor_count(const aet_tensor *t);                      /* batch*c*h*w */
+
+/* ------------------------------------------------------------------ layers
+ * Constructors keep the reference's argument order, restricted to the supported branch
+ * (groups=1, dilation=1, no binary/xnor/antialias/deform): dnn/ConvolutionalLayer.h:87-91,
+ * dnn/MaxPoolLayer.h:29-30, dnn/AvgPoolLayer.c:17, dnn/SoftMaxLayer.h:27-28,
+ * dnn/DropoutLayer.c:20-50.  `padding` is the resolved value (cfg `pad=1` => size/2). */
+aet_layer *aet_convolutional_layer_create(aet_context *ctx, int batch, int h, int w, int c, int n, int groups,
+                                          int size, int stride_x, int stride_y, int dilation, int padding,
+                                          aet_activation activation, int batch_normalize, int train);
+aet_layer *aet_maxpool_layer_create(aet_context *ctx, int batch, int h, int w, int c, int size, int stride_x,
+                                    int stride_y, int padding, int train);
+aet_layer *aet_avgpool_layer_create(aet_context *ctx, int batch, int w, int h, int c);
+aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int inputs, int groups, float temperature);
+/* Dropout works in place on `prev`'s output and delta (dnn/NetworkFactory.c:644-650). */
+aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int inputs, float probability, aet_layer *prev);
+void       aet_layer_destroy(aet_layer *l);
+
+/* NLayer.forward / backward / update / initDelta (dnn/NLayer.h:159-173). */
+int aet_layer_forward(aet_layer *l, aet_state state);
+int aet_layer_backward(aet_layer *l, aet_state state);
+int aet_layer_update(aet_layer *l, int batch, float learning_rate, float momentum, float decay, float loss_scale);
+int aet_layer_init_delta(aet_layer *l);
+aet_tensor *aet_layer_output(aet_layer *l);      /* NLayer.getOutputData */
+aet_tensor *aet_layer_delta(aet_layer *l);       /* NLayer.deltaData     */
+aet_layer_type aet_layer_kind(const aet_layer *l);
+int   aet_layer_out_shape(const aet_layer *l, int *c, int *h, int *w);
+float aet_layer_cost(aet_layer *l);              /* OutputLayer.getCost dnn/SoftMaxLayer.c:321 */
+size_t aet_layer_param_count(const aet_layer *l, aet_param which);
+int   aet_layer_read(aet_layer *l, aet_param which, void *host);        /* float, int32 for AET_P_INDEXES */
+int   aet_layer_write(aet_layer *l, aet_param which, const void *host);
+/* ConvolutionalLayer.loadWeights/saveWeights (dnn/ConvolutionalLayer.c:422-486): the `fp`
+ * is a C FILE* positioned at this layer's record. */
+int   aet_layer_load_weights(aet_layer *l, void *fp);
+int   aet_layer_save_weights(aet_layer *l, void *fp);
+
+/* ------------------------------------------------------------------ network
+ * NetworkFactory.createNetwork (dnn/NetworkFactory.c:830-1013) + NNetwork (dnn/NNetwork.h:141-195). */
+aet_network *aet_network_create(aet_context *ctx, const char *cfg_path, int train);
+aet_network *aet_network_create_from_string(aet_context *ctx, const char *cfg_text, int train);
+/* batch > 0 overrides the cfg's [net] batch (createNetwork(cfg,batch,time_steps), dnn/NetworkFactory.c:1023). */
+aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_text, int train, int batch);
+void         aet_network_destroy(aet_network *net);
+int          aet_network_layer_count(const aet_network *net);
+aet_layer   *aet_network_layer(aet_network *net, int index);
+int          aet_network_batch(const aet_network *net);
+int          aet_network_input_shape(const aet_network *net, int *c, int *h, int *w);
+int          aet_network_outputs(const aet_network *net);   /* NNetwork.getOuputSize */
+aet_tensor  *aet_network_input(aet_network *net);           /* NNetwork.inputData */
+aet_tensor  *aet_network_truth(aet_network *net);           /* NNetwork.truthData */
+float        aet_network_learning_rate(const aet_network *net);   /* NNetwork.getCurrentRate dnn/NNetwork.c:215-246 */
+int          aet_network_set_hyper(aet_network *net, float learning_rate, float momentum, float decay);
+int64_t      aet_network_seen(const aet_network *net);
+
+/* NNetwork.forward / backward / update (dnn/NNetwork.c:382-396,627-654,667-716). */
+int   aet_network_forward(aet_network *net, aet_state state);
+int   aet_network_backward(aet_network *net, aet_state state);
+int   aet_network_update(aet_network *net);
+float aet_network_cost(aet_network *net);                      /* getNetworkCost dnn/NNetwork.c:611-624 */
+/* NNetwork.train(InputData*,TruthData*) + update (dnn/NNetwork.c:740-774), subdivisions=1:
+ * host NCHW batch and one-hot truth in, mean loss out (cost / batch). Copies are asynchronous on
+ * the context stream; the loss read-back is the only host synchronisation. */
+int   aet_network_train_step(aet_network *net, const float *host_x, const float *host_truth, float *loss);
+/* Same step on data already resident in the network's input/truth tensors.  When `loss` is NULL
+ * nothing is read back (the loss stays in device memory until aet_network_last_loss). */
+int   aet_network_train_step_device(aet_network *net, float *loss);
+int   aet_network_last_loss(aet_network *net, float *loss);
+/* NNetwork.predict (dnn/NNetwork.c:411-428): forward with train=0, copy the last layer's output. */
+int   aet_network_predict(aet_network *net, const float *host_x, float *host_out);
+/* Capture forward+backward+update into a CUDA graph that later train steps replay (0 = off). */
+int   aet_network_use_graph(aet_network *net, int enable);
+/* NNetwork.loadWeights / saveWeights (dnn/NNetwork.c:64-147): Darknet .weights container. */
+int   aet_network_load_weights(aet_network *net, const char *path);
+int   aet_network_save_weights(aet_network *net, const char *path);
+/* 64-bit hash of all weights, biases, scales and momentum buffers (data-parallel consistency check). */
+int   aet_network_param_hash(aet_network *net, uint64_t *hash);
+/* Per-kernel device timing of the next train steps: enable, run steps, then read the table. */
+typedef struct aet_kernel_time {
+    char   name[48];
+    int    launches;
+    double total_ms;
+    double algo_bytes;   /* algorithmic bytes moved per launch (HBM-bound kernels), else 0 */
+    double algo_flops;   /* algorithmic FLOPs per launch (tensor-bound kernels), else 0 */
+} aet_kernel_time;
+int   aet_network_profile(aet_network *net, int enable);
+int   aet_network_profile_read(aet_network *net, aet_kernel_time *table, int capacity, int *count);
+int   aet_network_launches_per_step(const aet_network *net);
+
+/* ------------------------------------------------------------------ data parallel
+ * The reference is single GPU (dnn/Classifier.c:142, `ngpus = 1`); these entry points add the
+ * batch-data-parallel exchange: one NCCL all-reduce of the per-step gradient arena, issued per
+ * layer bucket during backward on a side stream.  `unique_id` is the 128-byte ncclUniqueId. */
+int   aet_comm_unique_id(void *unique_id_128);
+int   aet_network_comm_init(aet_network *net, const void *unique_id_128, int rank, int world);
+int   aet_network_comm_destroy(aet_network *net);
+/* Device pointer and float count of the gradient arena (for callers that run their own collective). */
+int   aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AET_B200_H */
