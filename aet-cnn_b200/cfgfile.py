@@ -1,0 +1,62 @@
+"""Python reader of the Darknet-style cfg subset the library accepts; same keys and defaults as the
+C reader (csrc/network.cu), which follows dnn/NetworkFactory.c:77-173,328-354,543-601,671-824.
+Used by the tests and the benchmark to describe the same network to the CPU oracle."""
+
+ACT = {"linear": 0, "relu": 1, "leaky": 2}
+CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
+
+
+def parse(text):
+    secs = []
+    for raw in text.splitlines():
+        line = raw.strip()
+        if not line or line[0] in "#;":
+            continue
+        if line.startswith("["):
+            secs.append((line[1:line.index("]")].strip(), {}))
+        else:
+            k, v = line.split("=", 1)
+            secs[-1][1][k.strip()] = v.strip()
+    return secs
+
+
+def network_spec(text, batch=0):
+    """Returns (net options dict, list of layer dicts shaped like the oracle's aeto_layer_spec)."""
+    secs = parse(text)
+    name, ns = secs[0]
+    assert name in ("net", "network")
+    sub = int(ns.get("subdivisions", 1))
+    net = dict(batch=int(ns.get("batch", 1)) // sub, subdivisions=sub, c=int(ns["channels"]), h=int(ns["height"]),
+               w=int(ns["width"]), learning_rate=float(ns.get("learning_rate", .001)),
+               momentum=float(ns.get("momentum", .9)), decay=float(ns.get("decay", .0001)))
+    if batch:
+        net["batch"], net["subdivisions"] = batch, 1
+    layers = []
+    for name, s in secs[1:]:
+        if name in ("convolutional", "conv"):
+            size = int(s.get("size", 1))
+            stride = int(s.get("stride", 1))
+            sx, sy = int(s.get("stride_x", -1)), int(s.get("stride_y", -1))
+            sx = stride if sx < 1 else sx
+            sy = stride if sy < 1 else sy
+            padding = int(s.get("padding", 0))
+            if int(s.get("pad", 0)):
+                padding = size // 2
+            layers.append(dict(type=CONV, filters=int(s.get("filters", 1)), size=size, stride_x=sx, stride_y=sy,
+                               pad=padding, batch_normalize=int(s.get("batch_normalize", 0)),
+                               activation=ACT[s.get("activation", "logistic")],
+                               learning_rate_scale=float(s.get("learning_rate", 1))))
+        elif name in ("maxpool", "max"):
+            stride = int(s.get("stride", 1))
+            size = int(s.get("size", stride))
+            layers.append(dict(type=MAXPOOL, size=size, stride_x=int(s.get("stride_x", stride)),
+                               stride_y=int(s.get("stride_y", stride)), pad=int(s.get("padding", size - 1))))
+        elif name in ("avgpool", "avg"):
+            layers.append(dict(type=AVGPOOL))
+        elif name in ("softmax", "soft"):
+            layers.append(dict(type=SOFTMAX, groups=int(s.get("groups", 1)), temperature=float(s.get("temperature", 1))))
+        elif name == "dropout":
+            layers.append(dict(type=DROPOUT, probability=float(s.get("probability", .2))))
+        else:
+            raise ValueError("unsupported layer type [%s]" % name)
+    return net, layers

@@ -526,7 +526,7 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
     aet_layer *sm = softmax_layer(net);
     if (sm) sm->cost_valid = false;
     const long before = ctx->launches;
-    if (net->use_graph && net->graph_exec) {
+    if (net->use_graph && net->graph_exec && !ctx->profiling) {
         AET_CUDA(cudaGraphLaunch(net->graph_exec, ctx->stream));
         ctx->launches += net->launches_per_step;
     } else if (net->use_graph && net->cur_iteration > 1 && !ctx->profiling) {
@@ -653,38 +653,11 @@ extern "C" int aet_network_param_hash(aet_network *net, uint64_t *hash) {
 // ---------------------------------------------------------------------------- profiling
 extern "C" int aet_network_profile(aet_network *net, int enable) {
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
-    aet_context *ctx = net->ctx;
-    AET_CUDA(cudaStreamSynchronize(ctx->stream));
-    ctx->profiling = enable != 0;
-    ctx->records.clear();
-    ctx->event_next = 0;
-    return AET_OK;
+    return aet_context_profile(net->ctx, enable);
 }
-
 extern "C" int aet_network_profile_read(aet_network *net, aet_kernel_time *table, int capacity, int *count) {
-    if (!net || !table || !count) { aet_set_error("null argument"); return AET_E_INVALID; }
-    aet_context *ctx = net->ctx;
-    AET_CUDA(cudaStreamSynchronize(ctx->stream));
-    int n = 0;
-    for (const ProfileRecord &r : ctx->records) {
-        float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
-        int k = 0;
-        for (; k < n; ++k)
-            if (strcmp(table[k].name, r.name) == 0 && table[k].algo_bytes == r.bytes && table[k].algo_flops == r.flops) break;
-        if (k == n) {
-            if (n == capacity) continue;
-            memset(&table[n], 0, sizeof(table[n]));
-            strncpy(table[n].name, r.name, sizeof(table[n].name) - 1);
-            table[n].algo_bytes = r.bytes;
-            table[n].algo_flops = r.flops;
-            ++n;
-        }
-        table[k].launches += 1;
-        table[k].total_ms += ms;
-    }
-    *count = n;
-    return AET_OK;
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    return aet_context_profile_read(net->ctx, table, capacity, count);
 }
 
 extern "C" int aet_network_launches_per_step(const aet_network *net) { return net ? (int)net->launches_per_step : 0; }

@@ -203,6 +203,42 @@ extern "C" int aet_context_check(aet_context *ctx) {
     return AET_OK;
 }
 
+extern "C" int aet_context_profile(aet_context *ctx, int enable) {
+    if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->profiling = enable != 0;
+    ctx->records.clear();
+    ctx->event_next = 0;
+    return AET_OK;
+}
+
+extern "C" int aet_context_profile_read(aet_context *ctx, aet_kernel_time *table, int capacity, int *count) {
+    if (!ctx || !table || !count) { aet_set_error("null argument"); return AET_E_INVALID; }
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    int n = 0;
+    for (const ProfileRecord &r : ctx->records) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
+        int k = 0;
+        for (; k < n; ++k)
+            if (strcmp(table[k].name, r.name) == 0 && table[k].algo_bytes == r.bytes && table[k].algo_flops == r.flops) break;
+        if (k == n) {
+            if (n == capacity) continue;
+            memset(&table[n], 0, sizeof(table[n]));
+            strncpy(table[n].name, r.name, sizeof(table[n].name) - 1);
+            table[n].algo_bytes = r.bytes;
+            table[n].algo_flops = r.flops;
+            ++n;
+        }
+        table[k].launches += 1;
+        table[k].total_ms += ms;
+    }
+    *count = n;
+    return AET_OK;
+}
+
+extern "C" long aet_context_launch_count(const aet_context *ctx) { return ctx ? ctx->launches : 0; }
+
 // ---------------------------------------------------------------------------- layout taps
 int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int n, int c, int h, int w, int cp,
                        bool async_pinned) {

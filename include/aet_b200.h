@@ -96,6 +96,19 @@ int          aet_context_set_math(aet_context *ctx, aet_math_mode mode);
 int          aet_context_synchronize(aet_context *ctx);
 /* Reads and clears the device status word written by bounded waits; AET_OK or AET_E_TIMEOUT. */
 int          aet_context_check(aet_context *ctx);
+/* Per-kernel device timing (CUDA events on the context stream around every launch the library
+ * makes): enable, run work, read the table grouped by kernel name.  Replaces the reference's
+ * wall-clock prints (dnn/Classifier.c:255,312-319). */
+typedef struct aet_kernel_time {
+    char   name[48];
+    int    launches;
+    double total_ms;
+    double algo_bytes;   /* algorithmic bytes moved per launch (HBM-bound kernels), else 0 */
+    double algo_flops;   /* algorithmic FLOPs per launch (tensor-bound kernels), else 0 */
+} aet_kernel_time;
+int          aet_context_profile(aet_context *ctx, int enable);
+int          aet_context_profile_read(aet_context *ctx, aet_kernel_time *table, int capacity, int *count);
+long         aet_context_launch_count(const aet_context *ctx);
 
 /* ------------------------------------------------------------------ tensors
  * Replaces DataFactory.createOutputData/createDeltaData/createInputData/createTruthData
@@ -182,14 +195,8 @@ int   aet_network_load_weights(aet_network *net, const char *path);
 int   aet_network_save_weights(aet_network *net, const char *path);
 /* 64-bit hash of all weights, biases, scales and momentum buffers (data-parallel consistency check). */
 int   aet_network_param_hash(aet_network *net, uint64_t *hash);
-/* Per-kernel device timing of the next train steps: enable, run steps, then read the table. */
-typedef struct aet_kernel_time {
-    char   name[48];
-    int    launches;
-    double total_ms;
-    double algo_bytes;   /* algorithmic bytes moved per launch (HBM-bound kernels), else 0 */
-    double algo_flops;   /* algorithmic FLOPs per launch (tensor-bound kernels), else 0 */
-} aet_kernel_time;
+/* Per-kernel device timing of the next train steps (aet_context_profile on the network's context;
+ * enabling it also suspends graph replay so that every launch is visible). */
 int   aet_network_profile(aet_network *net, int enable);
 int   aet_network_profile_read(aet_network *net, aet_kernel_time *table, int capacity, int *count);
 int   aet_network_launches_per_step(const aet_network *net);

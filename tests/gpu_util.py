@@ -1,0 +1,47 @@
+"""Helpers shared by the GPU parity tests: run one layer through the C ABI and through the oracle."""
+import numpy as np
+
+from oracle import binding as ob
+
+TOL_TF32 = 1e-2      # relative L2, TF32 inputs with FP32 accumulation
+TOL_3X = 1e-5        # relative L2, 3xTF32 split
+
+
+def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bias=True, want_dx=True):
+    """Forward + backward of one convolution (no BN) on the GPU and in the oracle; returns both result dicts."""
+    import aet_cnn_b200.synth as synth
+    oh, ow = (H + 2 * pad - size) // stride + 1, (W + 2 * pad - size) // stride + 1
+    x = synth.uniform((N, C, H, W), seed, 1)
+    w = synth.normal((K, C, size, size), seed, 2, 0.0, float(np.sqrt(2.0 / (size * size * C))))
+    b = synth.normal((K,), seed, 3, 0.0, 0.1) if bias else np.zeros(K, np.float32)
+    dy = synth.normal((N, K, oh, ow), seed, 4)
+
+    layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, size, stride, stride, pad, act, 0, 1)
+    layer.write(aet.P_WEIGHTS, w)
+    layer.write(aet.P_BIASES, b)
+    xin = aet.Tensor(ctx, N, C, H, W)
+    xin.write(x)
+    dxt = aet.Tensor(ctx, N, C, H, W) if want_dx else None
+    st = aet.make_state(input=xin, delta=dxt, train=1)
+    layer.forward(st)
+    got = dict(y=layer.read(aet.P_OUTPUT).reshape(N, K, oh, ow))
+    layer.write(aet.P_DELTA, dy)
+    layer.backward(st)
+    ctx.check()
+    got["dw"] = layer.read(aet.P_WEIGHT_UPDATES).reshape(w.shape)
+    got["db"] = layer.read(aet.P_BIAS_UPDATES)
+    got["dx"] = dxt.read() if want_dx else None
+    layer.close(); xin.close()
+    if dxt is not None:
+        dxt.close()
+
+    mode = ob.MODE_MTCS
+    y = oracle.activate(oracle.add_bias(oracle.conv_forward(x, w, stride, stride, pad), b), act, mode)
+    d = oracle.gradient(y, act, dy)
+    dw, dx = oracle.conv_backward(x, w, d, stride, stride, pad, need_dx=want_dx)
+    ref = dict(y=y, dw=dw, dx=dx, db=oracle.backward_bias(d))
+    return got, ref
+
+
+def kernels_used(ctx):
+    return {r["name"] for r in ctx.profile_read()}

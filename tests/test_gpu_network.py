@@ -1,0 +1,184 @@
+"""Whole-network parity on the GPU: the CIFAR-shaped small CNN trained for several SGD steps through
+the C ABI against the CPU oracle (loss curve and every parameter), CUDA-graph replay against eager
+execution (bitwise), the Darknet .weights container, and the reduced AlexNet-style step."""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from oracle import binding as ob
+
+pytestmark = pytest.mark.gpu
+
+PARAMS = ["P_WEIGHTS", "P_BIASES", "P_SCALES", "P_ROLLING_MEAN", "P_ROLLING_VARIANCE", "P_WEIGHT_UPDATES"]
+
+
+def build_pair(aet, ctx, oracle, cfg_name, batch, mode=ob.MODE_MTCS, seed=20241):
+    import aet_cnn_b200.cfgfile as cfgfile
+    import aet_cnn_b200.synth as synth
+    text = open(os.path.join(aet.CFG_DIR, cfg_name)).read()
+    ctx.set_parity(mode)
+    net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+    opts, specs = cfgfile.network_spec(text, batch)
+    onet = oracle.net(specs, batch, opts["c"], opts["h"], opts["w"], mode=mode)
+    cin = opts["c"]
+    for i, s in enumerate(specs):
+        if s["type"] != cfgfile.CONV:
+            continue
+        k, size = s["filters"], s["size"]
+        w = synth.normal((k, cin, size, size), seed, 1000 + i, 0.0, float(np.sqrt(2.0 / (size * size * cin))))
+        net.layer(i).write(aet.P_WEIGHTS, w)
+        onet.set_param(i, ob.P_WEIGHTS, w)
+        cin = k
+    return net, onet, opts, specs
+
+
+def batch_for(opts, classes, batch, seed, step):
+    import aet_cnn_b200.synth as synth
+    x = synth.uniform((batch, opts["c"], opts["h"], opts["w"]), seed, 2 * step)
+    _, truth = synth.labels(batch, classes, seed, 2 * step + 1)
+    return x, truth
+
+
+@pytest.mark.parametrize("mode", [ob.MODE_MTCS, ob.MODE_CPU])
+def test_small_cnn_training_matches_oracle(aet, ctx, oracle, mode):
+    batch, steps = 16, 6
+    ctx.set_math(aet.MATH_3XTF32)
+    try:
+        net, onet, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch, mode)
+        for step in range(steps):
+            x, truth = batch_for(opts, 10, batch, 20241, step)
+            loss = net.train(x, truth)
+            oloss = onet.train_step(x, truth, opts["learning_rate"], opts["momentum"], opts["decay"])
+            assert abs(loss - oloss) <= 2e-4 * abs(oloss), (step, loss, oloss)
+            if step in (0, steps - 1):
+                for i, s in enumerate(specs):
+                    for pname in PARAMS:
+                        ref = onet.param(i, getattr(ob, pname))
+                        if ref is None:
+                            continue
+                        got = net.layer(i).read(getattr(aet, pname))
+                        err = rel_l2(got, ref)
+                        assert err < 2e-3, (step, i, pname, err)
+        ctx.check()
+        net.close()
+    finally:
+        ctx.set_math(aet.MATH_TF32)
+        ctx.set_parity(ob.MODE_MTCS)
+
+
+def test_small_cnn_tf32_first_step_and_integer_outputs(aet, ctx, oracle):
+    """Default TF32 math: activations / gradients within 1e-2; max-pool indices compared where the
+    pooled inputs are identical (first pool layer sees TF32-perturbed values, so compare by value)."""
+    batch = 16
+    net, onet, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+    x, truth = batch_for(opts, 10, batch, 7, 0)
+    net.input.write(x); net.truth.write(truth)
+    st = aet.make_state(input=net.input, truth=net.truth, train=1)
+    net.forward(st)
+    net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    onet.forward(x, truth)
+    onet.backward(x)
+    for i in range(net.layer_count):
+        got = net.layer(i).read(aet.P_OUTPUT)
+        assert rel_l2(got, onet.param(i, ob.P_OUTPUT)) < 1e-2, i
+    for i, s in enumerate(specs):
+        if s["type"] == 0:
+            assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 2e-2, i
+    assert abs(net.cost() - onet.cost()) < 1e-2 * abs(onet.cost())
+    # the softmax delta's support (the labels) is integer data: exact
+    assert np.array_equal(net.layer(8).read(aet.P_LOSS) != 0, onet.param(8, ob.P_LOSS) != 0)
+    net.close()
+
+
+def test_graph_replay_is_bitwise_identical_to_eager(aet, ctx, oracle):
+    batch, steps = 8, 5
+    hashes = []
+    for use_graph in (False, True):
+        net, _, opts, _ = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+        net.use_graph(use_graph)
+        losses = []
+        for step in range(steps):
+            x, truth = batch_for(opts, 10, batch, 3, step)
+            losses.append(net.train(x, truth))
+        hashes.append((net.param_hash(), tuple(losses)))
+        assert net.launches_per_step() > 20
+        ctx.check()
+        net.close()
+    assert hashes[0] == hashes[1]
+
+
+def test_weights_file_roundtrip_and_layout(aet, ctx, oracle):
+    batch = 4
+    net, _, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+    x, truth = batch_for(opts, 10, batch, 3, 0)
+    net.train(x, truth)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "small.weights")
+        net.save_weights(path)
+        raw = np.fromfile(path, np.uint8)
+        header = raw[:12].view(np.int32)
+        assert tuple(header) == (0, 2, 5)                       # major, minor, revision
+        assert raw[12:20].view(np.uint64)[0] == batch           # seen = iterations * batch
+        body = raw[20:].view(np.float32)
+        # first record: biases[64], scales[64], rolling_mean[64], rolling_variance[64], weights[64*3*3*3]
+        l0 = net.layer(0)
+        assert np.array_equal(body[:64], l0.read(aet.P_BIASES))
+        assert np.array_equal(body[64:128], l0.read(aet.P_SCALES))
+        assert np.array_equal(body[128:192], l0.read(aet.P_ROLLING_MEAN))
+        assert np.array_equal(body[256:256 + 1728], l0.read(aet.P_WEIGHTS))
+        expect = sum((4 if s["batch_normalize"] else 1) * s["filters"] for s in specs if s["type"] == 0)
+        expect += 64 * 27 + 128 * 64 * 9 + 256 * 128 * 9 + 10 * 256
+        assert body.size == expect
+        net2 = aet.NNetwork(ctx, cfg_text=net.cfg_text, train=1, batch=batch)
+        net2.load_weights(path)
+        for i, s in enumerate(specs):
+            if s["type"] == 0:
+                assert np.array_equal(net2.layer(i).read(aet.P_WEIGHTS), net.layer(i).read(aet.P_WEIGHTS))
+        p1, p2 = net.predict(x), net2.predict(x)
+        assert np.array_equal(p1, p2) and np.allclose(p1.sum(1), 1.0, atol=1e-5)
+        with open(path, "r+b") as f:
+            f.truncate(200)
+        with pytest.raises(aet.AetError):
+            net2.load_weights(path)                              # a short file is an error, not a crash
+        net2.close()
+    net.close()
+
+
+def test_bad_cfg_is_rejected(aet, ctx):
+    for text in ["[convolutional]\nfilters=2\n",
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\n",          # logistic default
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[yolo]\n",
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nactivation=leaky\nxnor=1\n",
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[softmax]\n"]:
+        with pytest.raises(aet.AetError):
+            aet.NNetwork(ctx, cfg_text=text)
+
+
+def test_alexnet_style_reduced_step(aet, ctx, oracle):
+    """The AlexNet-style network (11x11/4, 5x5, FC as convolution, dropout) at batch 4, one step,
+    the dropout masks shared with the oracle."""
+    import aet_cnn_b200.cfgfile as cfgfile
+    batch = 4
+    net, onet, opts, specs = build_pair(aet, ctx, oracle, "alexnet_style.cfg", batch)
+    x, truth = batch_for(opts, 1000, batch, 11, 0)
+    net.input.write(x); net.truth.write(truth)
+    st = aet.make_state(input=net.input, truth=net.truth, train=1)
+    net.forward(st)
+    for i, s in enumerate(specs):
+        if s["type"] == cfgfile.DROPOUT:
+            onet.set_param(i, ob.P_RAND, net.layer(i).read(aet.P_RAND))
+    onet.forward(x, truth)
+    net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    onet.backward(x)
+    ctx.check()
+    assert [net.layer(i).out_shape for i in (0, 1, 3, 7, 8, 12)] == [(96, 55, 55), (96, 27, 27), (256, 13, 13), (256, 6, 6),
+                                                                   (4096, 1, 1), (1000, 1, 1)]
+    for i in range(net.layer_count):
+        assert rel_l2(net.layer(i).read(aet.P_OUTPUT), onet.param(i, ob.P_OUTPUT)) < 2e-2, i
+    assert abs(net.cost() - onet.cost()) < 1e-2 * abs(onet.cost())
+    for i in (0, 2, 8, 12):
+        assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 3e-2, i
+    net.close()
