@@ -298,6 +298,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
 
         // ------------------------------------------------------------------ epilogue
         bool ready = nslabs == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
+        ready = __all_sync(0xffffffffu, ready);   // the TMEM loads below are warp-collective
         tc_fence_after_sync();
         const int row = m0 + warp * 32 + lane;
         const bool row_ok = row < a.n_rows;

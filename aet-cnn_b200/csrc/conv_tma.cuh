@@ -177,6 +177,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
         // ------------------------------------------------------------------ epilogue
         bool ready = nslabs == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
+        ready = __all_sync(0xffffffffu, ready);   // the TMEM loads below are warp-collective
         tc_fence_after_sync();
         const int row = m0 + warp * 32 + lane;
         const bool row_ok = row < a.n_rows;

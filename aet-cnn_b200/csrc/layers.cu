@@ -28,6 +28,7 @@ int arena_create(ParamArena *a, size_t floats) {
     AET_CUDA(cudaMemset(a->W, 0, floats * sizeof(float)));
     AET_CUDA(cudaMemset(a->U, 0, floats * sizeof(float)));
     AET_CUDA(cudaMemset(a->G, 0, floats * sizeof(float)));
+    AET_CUDA(cudaDeviceSynchronize());   // the context stream does not order against the legacy stream
     return AET_OK;
 }
 
@@ -121,6 +122,7 @@ aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, 
         std::vector<float> ones(l->ocp, 0.f);
         for (int i = 0; i < n; ++i) ones[i] = 1.f;
         cudaMemcpy(layer_s(l), ones.data(), l->ocp * sizeof(float), cudaMemcpyHostToDevice);
+        cudaDeviceSynchronize();
     }
     // Initial weights: scale * U(-1,1), scale = sqrt(2/(size*size*c)) as dnn/WeightData.c:153-167,
     // from a counter-based generator instead of rand().
@@ -169,6 +171,7 @@ extern "C" aet_layer *aet_maxpool_layer_create(aet_context *ctx, int batch, int 
         if (!ok) aet_set_error("maxpool: index allocation failed");
     }
     if (!ok) { aet_layer_destroy(l); return nullptr; }
+    cudaDeviceSynchronize();
     return l;
 }
 
@@ -202,6 +205,7 @@ extern "C" aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int 
     ok = ok && cudaMalloc(&l->sample_loss, (size_t)batch * groups * sizeof(float)) == cudaSuccess;
     ok = ok && cudaMalloc(&l->cost_dev, 4 * sizeof(float)) == cudaSuccess && cudaMemset(l->cost_dev, 0, 4 * sizeof(float)) == cudaSuccess;
     if (!ok) { aet_set_error("softmax: allocation failed"); aet_layer_destroy(l); return nullptr; }
+    cudaDeviceSynchronize();
     return l;
 }
 
@@ -223,6 +227,7 @@ extern "C" aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int 
     ok = ok && cudaMalloc(&l->step_dev, sizeof(unsigned long long)) == cudaSuccess &&
          cudaMemset(l->step_dev, 0, sizeof(unsigned long long)) == cudaSuccess;
     if (!ok) { aet_set_error("dropout: allocation failed"); aet_layer_destroy(l); return nullptr; }
+    cudaDeviceSynchronize();
     l->seed = 0xD509ULL;
     return l;
 }
