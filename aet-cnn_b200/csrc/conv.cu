@@ -82,9 +82,18 @@ __device__ __forceinline__ void st_cell(unsigned char *stage, uint32_t off, uint
     }
 }
 
+// Byte offset of the 16-byte cell holding M/N elements 4*mc..4*mc+3 at K index k (0..31) inside an
+// MN-major tile stored as [32-element block][32 k-rows][128 B] in the 128B / 32-byte-atom swizzle.
+__device__ __forceinline__ uint32_t mn_cell_offset(int mc, int k) {
+    return (uint32_t)(mc >> 3) * 4096u + (uint32_t)(k >> 2) * 512u + (uint32_t)(k & 3) * 128u +
+           (uint32_t)((((mc & 7) >> 1) ^ (k & 3)) * 32) + (uint32_t)(mc & 1) * 16u;
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem[];
+    extern __shared__ unsigned char smem_raw[];
+    // swizzled MN-major tiles need their 512-byte atoms aligned; align every stage to 1024 bytes
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ SharedCtl ctl;
 
     const ConvGeom &g = a.g;
@@ -98,7 +107,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
     const int nslabs = (k_end > k_begin) ? (k_end - k_begin + BK - 1) / BK : 0;
 
     const uint32_t a_bytes = BM * BK * 4;
-    const uint32_t b_bytes = bn * BK * 4;
+    const uint32_t b_bytes = ((bn + 31) / 32) * 32 * BK * 4;
     const uint32_t half_bytes = a_bytes + b_bytes;            // one precision half of a stage
     const uint32_t stage_bytes = half_bytes * (a.x3 ? 2 : 1);
 
@@ -166,6 +175,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
             }
         }
         const int kc_lo = lane >> 3;  // first of the thread's two K cells (second is +4)
+        // MN-major operands: a warp instruction covers 8 k-rows x 4 cells; this lane split makes each
+        // quarter warp hit eight distinct 16-byte slots of the swizzled rows (no bank conflicts)
+        const int mn_k = (lane & 3) + 4 * ((lane >> 3) & 1);
+        const int mn_c = ((lane >> 2) & 1) + 2 * ((lane >> 4) & 1);
         const int nb_groups = bn / 16;  // B groups handled per warp
 
         for (int it = 0; it < nslabs; ++it) {
@@ -215,17 +228,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                 }
             } else {
                 // ---- A: MN-major gather from dy: one pixel per thread, 8 channel cells
-                const int kq = warp * 8 + (lane & 7);
+                const int kq = warp * 8 + mn_k;
                 const int p = k0 + kq;
                 const bool pvalid = p < k_end;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int mc = i * 4 + (lane >> 3);
+                    const int mc = i * 4 + mn_c;
                     const int ko = m0 + mc * 4;
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (pvalid && ko < g.kp) v = ldg4(a.src_a + ((size_t)p * g.kp + ko));
                     va[i] = v;
-                    oa[i] = (uint32_t)warp * (BM * 32) + (uint32_t)mc * 128 + (uint32_t)(lane & 7) * 16;
+                    oa[i] = mn_cell_offset(mc, kq);
                 }
             }
 
@@ -250,7 +263,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                 }
             } else if (KIND == KIND_DGRAD) {
                 // MN-major, rows = input channels (contiguous in the weight tensor), K = (tap, filter)
-                const int kq = warp * 8 + (lane & 7);
+                const int kq = warp * 8 + mn_k;
                 const int kk = k0 + kq;
                 int tap = 0, ko = 0;
                 const bool kvalid = kk < k_end;
@@ -258,16 +271,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                 const bool fvalid = kvalid && ko < g.K;
                 const float *wrow = a.src_b + ((size_t)ko * (g.R * g.S) + tap) * g.cp;
                 for (int i = 0; i < nb_groups; ++i) {
-                    const int mc = i * 4 + (lane >> 3);
+                    const int mc = i * 4 + mn_c;
                     const int c = n0 + mc * 4;
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (fvalid && c < g.cp) v = ldg4(wrow + c);
-                    st_cell(stage_b, (uint32_t)warp * (bn * 32) + (uint32_t)mc * 128 + (uint32_t)(lane & 7) * 16,
-                            half_bytes, v, a.x3);
+                    st_cell(stage_b, mn_cell_offset(mc, kq), half_bytes, v, a.x3);
                 }
             } else {
                 // MN-major gather from x, rows = (tap, channel), K = output pixel
-                const int kq = warp * 8 + (lane & 7);
+                const int kq = warp * 8 + mn_k;
                 const int p = k0 + kq;
                 const bool pvalid = p < k_end;
                 int nb = 0, ih0 = 0, iw0 = 0;
@@ -280,7 +292,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                     iw0 = ow * g.sx - g.pad;
                 }
                 for (int i = 0; i < nb_groups; ++i) {
-                    const int mc = i * 4 + (lane >> 3);
+                    const int mc = i * 4 + mn_c;
                     const int4 e = ctl.jtab[mc];
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (pvalid && e.w) {
@@ -288,8 +300,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                         if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
                             v = ldg4(a.src_b + ((size_t)(nb + ih * g.W + iw) * g.cp + e.z));
                     }
-                    st_cell(stage_b, (uint32_t)warp * (bn * 32) + (uint32_t)mc * 128 + (uint32_t)(lane & 7) * 16,
-                            half_bytes, v, a.x3);
+                    st_cell(stage_b, mn_cell_offset(mc, kq), half_bytes, v, a.x3);
                 }
             }
             fence_proxy_async_smem();
@@ -347,16 +358,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
             int ksteps = (k_end - k0 + 7) / 8;
             if (ksteps > 4) ksteps = 4;
             for (int j = 0; j < ksteps; ++j) {
-                uint32_t a_addr, b_addr, a_lbo, b_lbo;
-                if (a_mn) { a_addr = sa + j * (BM * 32); a_lbo = BM * 32; }
-                else      { a_addr = sa + j * 2 * (BM * 16); a_lbo = BM * 16; }
-                if (b_mn) { b_addr = sb + j * (bn * 32); b_lbo = bn * 32; }
-                else      { b_addr = sb + j * 2 * (bn * 16); b_lbo = bn * 16; }
-                const uint64_t da = make_desc(a_addr, a_lbo, 128, LAYOUT_NONE);
-                const uint64_t db = make_desc(b_addr, b_lbo, 128, LAYOUT_NONE);
+                // K-major: un-swizzled core matrices, two 16-byte K chunks per MMA at LBO, 8-row groups at SBO.
+                // MN-major: 128B / 32-byte-atom swizzle, 32-element blocks at LBO, 4-k atoms at SBO.
+                const uint32_t a_addr = a_mn ? sa + j * 1024 : sa + j * 2 * (BM * 16);
+                const uint32_t b_addr = b_mn ? sb + j * 1024 : sb + j * 2 * (bn * 16);
+                const uint32_t a_lbo = a_mn ? 4096u : BM * 16, a_sbo = a_mn ? 512u : 128u;
+                const uint32_t b_lbo = b_mn ? 4096u : bn * 16, b_sbo = b_mn ? 512u : 128u;
+                const uint64_t a_lay = a_mn ? LAYOUT_SW128_32B : LAYOUT_NONE, b_lay = b_mn ? LAYOUT_SW128_32B : LAYOUT_NONE;
+                const uint64_t da = make_desc(a_addr, a_lbo, a_sbo, a_lay);
+                const uint64_t db = make_desc(b_addr, b_lbo, b_sbo, b_lay);
                 if (a.x3) {
-                    const uint64_t da_lo = make_desc(a_addr + half_bytes, a_lbo, 128, LAYOUT_NONE);
-                    const uint64_t db_lo = make_desc(b_addr + half_bytes, b_lbo, 128, LAYOUT_NONE);
+                    const uint64_t da_lo = make_desc(a_addr + half_bytes, a_lbo, a_sbo, a_lay);
+                    const uint64_t db_lo = make_desc(b_addr + half_bytes, b_lbo, b_sbo, b_lay);
                     mma_tf32(tmem, da_lo, db, idesc, accumulate);
                     mma_tf32(tmem, da, db_lo, idesc, 1);
                     mma_tf32(tmem, da, db, idesc, 1);
@@ -378,14 +391,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
     }
 }
 
-// Fixed-order second stage of the split-K weight gradient: dw (+)= sum over splits.
-__global__ void wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dw, size_t count4,
-                                    int splits, size_t split_stride, int accumulate) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= count4) return;
+// Fixed-order second stage of the split-K weight gradient: dw (+)= sum over splits.  A block owns
+// 32 float4 outputs; its 16 split lanes each add every 16th partial, then lane 0 adds the 16
+// lane sums in order, so the result does not depend on scheduling.
+constexpr int RED_ELEMS = 32, RED_LANES = 16;
+__global__ void __launch_bounds__(RED_ELEMS * RED_LANES)
+wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dw, size_t count4, int splits,
+                    size_t split_stride, int accumulate) {
+    __shared__ float4 sh[RED_LANES][RED_ELEMS];
+    const int e = threadIdx.x % RED_ELEMS, sl = threadIdx.x / RED_ELEMS;
+    const size_t i = (size_t)blockIdx.x * RED_ELEMS + e;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < splits; ++s) {
-        float4 v = __ldg(reinterpret_cast<const float4 *>(partial + (size_t)s * split_stride) + i);
+    if (i < count4)
+        for (int s = sl; s < splits; s += RED_LANES) {
+            float4 v = __ldg(reinterpret_cast<const float4 *>(partial + (size_t)s * split_stride) + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    sh[sl][e] = acc;
+    __syncthreads();
+    if (sl != 0 || i >= count4) return;
+    for (int q = 1; q < RED_LANES; ++q) {
+        float4 v = sh[q][e];
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     float4 *o = reinterpret_cast<float4 *>(dw) + i;
@@ -427,14 +453,14 @@ int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, do
     a.x3 = ctx->math == AET_MATH_3XTF32 ? 1 : 0;
     a.tmem_cols = pow2_cols(a.bn);
     a.status = ctx->status_dev;
-    const size_t half = (size_t)BM * BK * 4 + (size_t)a.bn * BK * 4;
+    const size_t half = (size_t)BM * BK * 4 + (size_t)((a.bn + 31) / 32) * 32 * BK * 4;
     const size_t stage = half * (a.x3 ? 2 : 1);
     int stages = (int)((96 * 1024) / stage);
     if (stages < 3) stages = (int)((200 * 1024) / stage);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     a.stages = stages;
-    const size_t smem_bytes = stage * stages;
+    const size_t smem_bytes = stage * stages + 1024;
     static bool attr_set[3] = {false, false, false};
     if (!attr_set[KIND]) {
         AET_CUDA(cudaFuncSetAttribute(conv_gather_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
@@ -536,7 +562,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
     {
         const size_t count4 = out_floats / 4;
         LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (splits + 1 + (accumulate ? 1 : 0)), 0);
-        wgrad_reduce_kernel<<<(unsigned)((count4 + 255) / 256), 256, 0, ctx->stream>>>(partial, dw, count4, splits,
+        wgrad_reduce_kernel<<<(unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, ctx->stream>>>(partial, dw, count4, splits,
                                                                                         out_floats, accumulate);
         return aet_check_launch("wgrad_reduce");
     }

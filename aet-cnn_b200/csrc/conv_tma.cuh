@@ -5,7 +5,8 @@
 // images.  One thread issues tiled bulk-tensor copies whose coordinates are shifted by the filter
 // tap; pixels outside the image are zero-filled by the copy engine, so there is no halo logic and
 // no im2col buffer.  Tiles land in shared memory in the 128-byte swizzled layout that the
-// tcgen05 descriptors name directly.  Only plain per-CTA tensor copies are used.
+// tcgen05 descriptors name directly (16-byte-atom swizzle for K-major operands, 32-byte-atom
+// swizzle for the MN-major operands of dgrad and wgrad).  Only plain per-CTA tensor copies are used.
 //
 // Return convention of tma_fprop / tma_dgrad / tma_wgrad: AET_OK launched, 1 not eligible (caller
 // falls back to the gather producer), negative error.
@@ -45,7 +46,7 @@ struct TmaCache {
 
 // dims/strides innermost first; strides[i] is the byte stride of dim i+1.
 int get_map(aet_layer *l, int tag, const void *ptr, int rank, const cuuint64_t *dims, const cuuint64_t *strides,
-            const cuuint32_t *box, const CUtensorMap **out) {
+            const cuuint32_t *box, bool mn_major, const CUtensorMap **out) {
     if (!l->tma_cache) l->tma_cache = new TmaCache();
     TmaCache *c = static_cast<TmaCache *>(l->tma_cache);
     TmaKey key = {ptr, tag, {0, 0, 0, 0, 0}};
@@ -64,7 +65,8 @@ int get_map(aet_layer *l, int tag, const void *ptr, int rank, const cuuint64_t *
     TmaEntry e;
     e.key = key;
     CUresult r = fn(&e.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void *>(ptr), dims, strides,
-                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         aet_set_error("cuTensorMapEncodeTiled failed with code %d (tag %d)", (int)r, tag);
@@ -224,9 +226,11 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t sb = sa + a.a_bytes;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint64_t da = a_mn ? make_desc(sa + j * 1024, 4096, 1024, LAYOUT_SW128)
+                // K-major tiles: 128B swizzle, 16-byte atoms, K advances 32 bytes per MMA inside the row.
+                // MN-major tiles: [32-element block][32 k-rows][128 B] in the 32-byte-atom swizzle.
+                const uint64_t da = a_mn ? make_desc(sa + j * 1024, 4096, 512, LAYOUT_SW128_32B)
                                          : make_desc(sa + j * 32, 0, 1024, LAYOUT_SW128);
-                const uint64_t db = b_mn ? make_desc(sb + j * 1024, 4096, 1024, LAYOUT_SW128)
+                const uint64_t db = b_mn ? make_desc(sb + j * 1024, 4096, 512, LAYOUT_SW128_32B)
                                          : make_desc(sb + j * 32, 0, 1024, LAYOUT_SW128);
                 mma_tf32(tmem, da, db, idesc, accumulate);
                 accumulate = 1;
@@ -305,13 +309,13 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
         cuuint64_t dims[4] = {(cuuint64_t)g.cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
         cuuint64_t str[3] = {(cuuint64_t)g.cp * 4, (cuuint64_t)g.W * g.cp * 4, (cuuint64_t)g.H * g.W * g.cp * 4};
         cuuint32_t box[4] = {32, bw, bh, bi};
-        AET_TRY(get_map(l, 0, a.src_a, 4, dims, str, box, &ma));
+        AET_TRY(get_map(l, 0, a.src_a, 4, dims, str, box, false, &ma));
     }
     {
         cuuint64_t dims[2] = {(cuuint64_t)a.k_total, (cuuint64_t)g.K};
         cuuint64_t str[1] = {(cuuint64_t)a.k_total * 4};
         cuuint32_t box[2] = {32, (cuuint32_t)bn};
-        AET_TRY(get_map(l, 1, a.src_b, 2, dims, str, box, &mb));
+        AET_TRY(get_map(l, 1, a.src_b, 2, dims, str, box, false, &mb));
     }
     TmaArgs t = {};
     t.out = a.out; t.bias = a.bias; t.act = a.act; t.bn = bn;
@@ -338,7 +342,7 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
         cuuint64_t dims[4] = {(cuuint64_t)g.kp, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N};
         cuuint64_t str[3] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4};
         cuuint32_t box[4] = {32, bw, bh, bi};
-        AET_TRY(get_map(l, 2, a.src_a, 4, dims, str, box, &ma));
+        AET_TRY(get_map(l, 2, a.src_a, 4, dims, str, box, false, &ma));
     }
     {
         // weights [filter][tap][cp] viewed as (c%32, filter, c/32, tap)
@@ -346,7 +350,7 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
         cuuint64_t dims[4] = {32, (cuuint64_t)g.K, (cuuint64_t)g.cp / 32, (cuuint64_t)taps};
         cuuint64_t str[3] = {(cuuint64_t)taps * g.cp * 4, 128, (cuuint64_t)g.cp * 4};
         cuuint32_t box[4] = {32, 32, (cuuint32_t)bn / 32, 1};
-        AET_TRY(get_map(l, 3, a.src_b, 4, dims, str, box, &mb));
+        AET_TRY(get_map(l, 3, a.src_b, 4, dims, str, box, true, &mb));
     }
     TmaArgs t = {};
     t.out = a.out; t.bias = nullptr; t.act = AET_LINEAR; t.bn = bn;
@@ -376,13 +380,13 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
         cuuint64_t dims[5] = {32, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N, (cuuint64_t)g.kp / 32};
         cuuint64_t str[4] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4, 128};
         cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)m_blocks};
-        AET_TRY(get_map(l, 4, a.src_a, 5, dims, str, box, &ma));
+        AET_TRY(get_map(l, 4, a.src_a, 5, dims, str, box, true, &ma));
     }
     {
         cuuint64_t dims[5] = {32, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N, (cuuint64_t)g.cp / 32};
         cuuint64_t str[4] = {(cuuint64_t)g.cp * 4, (cuuint64_t)g.W * g.cp * 4, (cuuint64_t)g.H * g.W * g.cp * 4, 128};
         cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)bn / 32};
-        AET_TRY(get_map(l, 5, a.src_b, 5, dims, str, box, &mb));
+        AET_TRY(get_map(l, 5, a.src_b, 5, dims, str, box, true, &mb));
     }
     TmaArgs t = {};
     t.out = a.out; t.bias = nullptr; t.act = AET_LINEAR; t.bn = bn;

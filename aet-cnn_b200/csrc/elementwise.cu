@@ -151,14 +151,21 @@ struct FinalizeArgs {
 // MODE 0: statistics -> mean, variance, 1/std, rolling update.  MODE 1: BN backward coefficients
 // and the scale / shift gradients.  MODE 2: bias gradient.
 template <int MODE>
-__global__ void finalize_kernel(const FinalizeArgs a) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256) finalize_kernel(const FinalizeArgs a) {
+    // one warp per channel: lanes stride over the per-block partials, then a fixed xor tree
+    const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
     if (c >= a.cp) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int b = 0; b < a.blocks; ++b) {
+    for (int b = lane; b < a.blocks; b += 32) {
         s1 += (double)a.partial[(size_t)b * 2 * a.cp + c];
         if (MODE != 2) s2 += (double)a.partial[(size_t)b * 2 * a.cp + a.cp + c];
     }
+    for (int o = 16; o; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if (lane != 0) return;
     const double m = (double)a.m;
     if (MODE == 0) {
         if (c >= a.c) { a.mean[c] = 0.f; a.variance[c] = 0.f; a.inv[c] = 0.f; return; }
@@ -612,7 +619,7 @@ int k_bn_stats(aet_layer *l, int update_rolling) {
     f.mean = l->mean; f.variance = l->variance; f.inv = l->inv_std;
     f.rolling_mean = l->rolling_mean; f.rolling_variance = l->rolling_variance;
     LaunchScope s(ctx, "bn_stats_finalize", 0, 0);
-    finalize_kernel<0><<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(f);
+    finalize_kernel<0><<<(l->ocp + 7) / 8, 256, 0, ctx->stream>>>(f);
     return aet_check_launch("bn_stats_finalize");
 }
 
@@ -659,7 +666,7 @@ int k_bn_backward(aet_layer *l) {
     f.g_gamma = layer_sG(l); f.g_beta = layer_bG(l); f.coef = l->bwd_coef;
     {
         LaunchScope s(ctx, "bn_bwd_finalize", 0, 0);
-        finalize_kernel<1><<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(f);
+        finalize_kernel<1><<<(l->ocp + 7) / 8, 256, 0, ctx->stream>>>(f);
         AET_TRY(aet_check_launch("bn_bwd_finalize"));
     }
     ReducePlan q = plan_apply(ctx, pixels, l->ocp);
@@ -690,7 +697,7 @@ int k_bias_act_backward(aet_layer *l) {
     FinalizeArgs f = {};
     f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels; f.g_beta = layer_bG(l);
     LaunchScope s(ctx, "bias_bwd_finalize", 0, 0);
-    finalize_kernel<2><<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(f);
+    finalize_kernel<2><<<(l->ocp + 7) / 8, 256, 0, ctx->stream>>>(f);
     return aet_check_launch("bias_bwd_finalize");
 }
 

@@ -158,14 +158,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
 //   [0,14)  start address >> 4        [16,30) leading-dimension byte offset >> 4
 //   [32,46) stride-dimension byte offset >> 4     [46,48) descriptor version (1 on sm_100)
 //   [49,52) base offset (0: tiles are aligned to their swizzle span)
-//   [61,64) layout: 0 none (interleaved 8x16B core matrices), 2 = 128-byte swizzle
-// Canonical layouts in units of 16 bytes (T = 4 TF32 elements):
-//   K-major,  no swizzle : row r, 16B chunk j  ->  (r%8) + (r/8)*SBO + j*LBO
-//   K-major,  128B       : 8-row groups of 1024 B at SBO; LBO unused
-//   MN-major, no swizzle : chunk m (4 elements along M/N), k -> m*SBO + (k%8) + (k/8)*LBO
-//   MN-major, 128B       : 32 elements along M/N per 128-byte row, 8 k-rows per 1024-byte atom,
-//                          next 32 elements at LBO, next 8 k at SBO
-enum : uint64_t { LAYOUT_NONE = 0, LAYOUT_SW128 = 2 };
+//   [61,64) layout: 0 none (interleaved 8x16B core matrices), 1 = 128-byte swizzle with 32-byte
+//           atoms, 2 = 128-byte swizzle with 16-byte atoms
+// Layouts used here (measured on a B200 by reading back which element each (row, k) fetches):
+//   K-major, no swizzle (layout 0): row r, 16-byte chunk j of K -> (r%8)*16 + (r/8)*SBO + j*LBO
+//   K-major, 128B swizzle (layout 2): 128-byte rows, 8-row groups of 1024 B at SBO, 16-byte chunk
+//           index XOR (row % 8); LBO unused; K advances by adding bytes to the start address
+//   MN-major TF32 operands are only read correctly with layout 1 (layouts 0 and 2 yield zeros):
+//           element (mn, k) at (mn/32)*LBO + (k/4)*SBO + (k%4)*128 + (((mn%32)/8) ^ (k%4))*32
+//           + (mn%8)*4, i.e. 128-byte rows of 32 consecutive M/N elements, four k-rows per
+//           512-byte atom, 32-byte chunk index XOR (k % 4).  A TMA copy with the
+//           128B / 32-byte-atom swizzle mode writes exactly this pattern.
+enum : uint64_t { LAYOUT_NONE = 0, LAYOUT_SW128_32B = 1, LAYOUT_SW128 = 2 };
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                               uint64_t layout) {
     uint64_t d = 0;

