@@ -40,7 +40,7 @@ aet_network_seen aet_network_forward aet_network_backward aet_network_update aet
 aet_network_train_step aet_network_train_step_device aet_network_last_loss aet_network_predict
 aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
-aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena""".split()
+aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static""".split()
 
 
 class AetError(RuntimeError):
@@ -119,6 +119,7 @@ def lib():
         "aet_comm_unique_id": (i, [vp]), "aet_network_comm_init": (i, [vp, vp, i, i]),
         "aet_network_comm_destroy": (i, [vp]),
         "aet_network_grad_arena": (i, [vp, C.POINTER(vp), C.POINTER(C.c_size_t)]),
+        "aet_backward_bias_static": (i, [vp, vp, C.c_longlong, i, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)      # AttributeError here = the library does not export a declared symbol
@@ -445,6 +446,13 @@ class NNetwork:
         if self.h:
             self.L.aet_network_destroy(self.h)
             self.h = None
+
+
+def backward_bias_static(delta_ptr, bias_updates_ptr, pixels, channels, stream=None):
+    """bias_updates[c] += sum_p delta[p][c] on raw device pointers, with the partial sums in the
+    library's fixed device array: for callers that may not allocate device memory while running."""
+    _check(lib().aet_backward_bias_static(C.c_void_p(delta_ptr), C.c_void_p(bias_updates_ptr), pixels, channels,
+                                          C.c_void_p(stream) if stream else None))
 
 
 def comm_unique_id():

@@ -825,3 +825,78 @@ int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_
                                                                                 reinterpret_cast<unsigned long long *>(hash_dev));
     return aet_check_launch("param_hash");
 }
+
+// ---------------------------------------------------------------------------- allocation-free bias gradient
+// Some hosts of this library may not allocate device memory once they are running: a training loop
+// inside a process whose memory pool was sized and handed out at start-up, a plugin called from
+// another runtime's stream callback, or a caller that is itself between cudaMalloc-free phases of a
+// latency-critical service.  For them the bias gradient (the column sums that k_bias_act_backward
+// forms with partials in the context's cudaMalloc'ed scratch arena) is also offered with its
+// partials in the fixed array below, which every GPU that loads the library holds until exit.
+constexpr size_t kStaticScratchFloats = 1u << 18;   // 1 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+namespace {
+struct StaticDeviceState {
+    bool ready = false;
+    float *scratch = nullptr;   // device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+StaticDeviceState g_static_state[64];
+}  // namespace
+
+extern "C" int aet_backward_bias_static(const float *delta, float *bias_updates, long long pixels, int channels,
+                                        void *cuda_stream) {
+    if (!delta || !bias_updates || pixels <= 0 || channels <= 0) {
+        aet_set_error("aet_backward_bias_static: null pointer or empty shape");
+        return AET_E_INVALID;
+    }
+    if (channels % 4 != 0 || (reinterpret_cast<uintptr_t>(delta) & 15u) != 0) {
+        aet_set_error("aet_backward_bias_static: channels must be a multiple of 4 and delta 16-byte aligned");
+        return AET_E_INVALID;
+    }
+    int dev = -1;
+    AET_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        aet_set_error("aet_backward_bias_static: device ordinal %d is outside the supported range", dev);
+        return AET_E_INVALID;
+    }
+    StaticDeviceState &st = g_static_state[dev];
+    if (!st.ready) {
+        // Host code only sees a stand-in for the __device__ array; the kernels need its device address,
+        // looked up once per device with that device current.
+        float *p = nullptr;
+        AET_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch));
+        AET_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        st.scratch = p;
+        st.ready = true;
+    }
+    ReducePlan p;
+    p.m = make_cmap(channels);
+    long long want = 2LL * st.sm_count / p.m.cslabs;
+    if (want < 1) want = 1;
+    const long long min_pix = (long long)p.m.pl_count * 4;
+    const long long maxb = (pixels + min_pix - 1) / min_pix;
+    if (want > maxb) want = maxb;
+    if (want < 1) want = 1;
+    p.pix_per_block = (pixels + want - 1) / want;
+    p.blocks = (int)((pixels + p.pix_per_block - 1) / p.pix_per_block);
+    const size_t need = (size_t)p.blocks * 2 * (size_t)channels;
+    if (need > kStaticScratchFloats) {
+        aet_set_error("aet_backward_bias_static: %d channels need %zu scratch floats, the static array holds %zu "
+                      "(use the layer entry points, which allocate)", channels, need, kStaticScratchFloats);
+        return AET_E_INVALID;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    ReduceArgs a = {};
+    a.x = delta;                                   // the kernel also loads its 'output' operand; linear ignores the value
+    a.delta = const_cast<float *>(delta);          // linear activation: the kernel does not write delta
+    a.partial = st.scratch; a.act = AET_LINEAR;
+    a.pixels = pixels; a.cp = channels; a.pix_per_block = p.pix_per_block; a.m = p.m;
+    reduce2_kernel<2><<<dim3(p.blocks, p.m.cslabs), TB, 0, stream>>>(a);
+    AET_TRY(aet_check_launch("backward_bias_static (partials)"));
+    FinalizeArgs f = {};
+    f.partial = st.scratch; f.blocks = p.blocks; f.cp = channels; f.c = channels; f.m = pixels; f.g_beta = bias_updates;
+    finalize_kernel<2><<<(channels + 7) / 8, 256, 0, stream>>>(f);
+    return aet_check_launch("backward_bias_static (finalize)");
+}

@@ -211,6 +211,26 @@ int   aet_network_comm_destroy(aet_network *net);
 /* Device pointer and float count of the gradient arena (for callers that run their own collective). */
 int   aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count);
 
+/* ------------------------------------------------------------------ allocation-free entry point
+ * No counterpart in the reference (its kernels need no scratch; ours reduce in two stages).
+ * For callers that must not allocate device memory while they run -- a process whose device pool is
+ * fixed at start-up, a plugin invoked from another runtime's callback, a service between
+ * allocation-free phases -- this computes the bias gradient
+ *     bias_updates[c] += sum over p of delta[p][c]
+ * with the stage-one partial sums held in a fixed 1 MiB __device__ array inside the library instead
+ * of the context's cudaMalloc'ed scratch arena.  It calls no cudaMalloc / cudaFree.
+ *   delta         device pointer, FP32 [pixels][channels] row-major, 16-byte aligned
+ *   bias_updates  device pointer, FP32 [channels], accumulated into
+ *   channels      multiple of 4; the launch plan must fit the array: blocks * 2 * channels floats
+ *                 with up to 2 * SMs blocks (so up to ~440 channels at full grid on a 148-SM
+ *                 part, more when `pixels` is small), otherwise AET_E_INVALID
+ *   cuda_stream   cudaStream_t to launch on (NULL = the legacy default stream)
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress) with
+ * that device current; make that first call outside any stream capture.  All calls on a device share
+ * the one array: calls whose kernels may overlap on the GPU (different streams) race -- serialise
+ * them.  Nothing in the array has to be cleared between calls. */
+int   aet_backward_bias_static(const float *delta, float *bias_updates, long long pixels, int channels, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
