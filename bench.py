@@ -229,17 +229,14 @@ def main():
     ctx = aet.Context(local_rank, parity=aet.PARITY_MTCS, math=aet.MATH_TF32, stream=stream.cuda_stream)
     net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=args.batch)
     init_weights(aet, synth, cfgfile, net, specs, opts["c"])
+    import aet_cnn_b200.parallel as par
     if world > 1:
-        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            uid.copy_(torch.frombuffer(bytearray(aet.comm_unique_id()), dtype=torch.uint8))
-        dist.broadcast(uid, 0)
-        net.comm_init(bytes(uid.cpu().numpy().tobytes()), rank, world)
+        net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
 
     batch = args.batch
     host_batches = []
     for s in range(4):
-        tid = synth.shard_tensor_id(s, rank, world)
+        tid = par.shard_tensor_id(s, rank, world)
         host_batches.append((synth.uniform((batch, 3, 32, 32), SEED, 2 * tid), synth.labels(batch, CLASSES, SEED, 2 * tid + 1)[1]))
 
     def barrier():
@@ -248,12 +245,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    max_over_ranks = par.max_over_ranks
 
     # ---- device-resident throughput (graph replay)
     net.input.write(host_batches[0][0]); net.truth.write(host_batches[0][1])
@@ -273,6 +265,7 @@ def main():
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop()
     final_loss = net.last_loss()
+    weights_identical = par.hashes_identical(net.param_hash())
     launches = net.launches_per_step() * args.steps
     ctx.check()
     value = batch * world * args.steps / (ms_total / 1000.0)
@@ -336,7 +329,7 @@ def main():
                 "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms / args.steps},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
-                "final_loss": final_loss, "kernels": kernels}
+                "final_loss": final_loss, "weights_identical_across_ranks": weights_identical, "kernels": kernels}
         print(json.dumps(line), flush=True)
     net.close()
     ctx.close()
