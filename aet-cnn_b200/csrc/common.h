@@ -127,6 +127,14 @@ struct aet_layer {
     aet_layer *prev = nullptr;
     uint64_t seed = 0;
     unsigned long long *step_dev = nullptr;
+    // Network-level fusion: a BN convolution followed by a max-pool computes the pool's output in
+    // its own forward and gathers the pool's delta in its own backward; the pool layer then idles.
+    aet_layer *fused_pool = nullptr;   // set on the convolution
+    aet_layer *fused_into = nullptr;   // set on the max-pool
+    bool output_stale = false;         // conv output not materialised (recomputed on a host read)
+    bool last_forward_train = true;
+    bool fused_ready = false;          // pool: output already produced by the convolution this pass
+    bool gather_pending = false;       // conv: the pool deferred its backward to this layer
     // TMA descriptors are built lazily per (layer, pass, operand address)
     void *tma_cache = nullptr;
 };
@@ -204,7 +212,8 @@ void conv_release(aet_layer *l);
 
 int k_bn_stats(aet_layer *l, int update_rolling);
 int k_bn_apply(aet_layer *l, int use_rolling);
-int k_bn_backward(aet_layer *l);
+int k_bn_backward(aet_layer *l, aet_layer *pool);
+int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling);
 int k_bias_act_backward(aet_layer *l);
 int k_maxpool_forward(aet_layer *l, const float *x);
 int k_maxpool_backward(aet_layer *l, float *prev_delta, int accumulate);

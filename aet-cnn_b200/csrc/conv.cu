@@ -89,8 +89,9 @@ __device__ __forceinline__ uint32_t mn_cell_offset(int mc, int k) {
            (uint32_t)((((mc & 7) >> 1) ^ (k & 3)) * 32) + (uint32_t)(mc & 1) * 16u;
 }
 
-template <int KIND>
-__global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs a) {
+// NB = B-operand cells per producer thread and stage (N tile <= 16*NB).
+template <int KIND, int NB>
+__global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(const ConvArgs a) {
     extern __shared__ unsigned char smem_raw[];
     // swizzled MN-major tiles need their 512-byte atoms aligned; align every stage to 1024 bytes
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -242,15 +243,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                 }
             }
 
-            if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) st_cell(stage, oa[i], half_bytes, va[i], a.x3);
-
-            // ---- B
+            // ---- B: all loads of the stage are issued before anything is stored, so that their
+            // latencies overlap instead of adding up
             unsigned char *stage_b = stage + a_bytes;
+            float4 vb[NB];
+            uint32_t ob[NB];
             if (KIND == KIND_FPROP) {
                 // K-major, rows = filters
-                for (int i = 0; i < nb_groups; ++i) {
+#pragma unroll
+                for (int i = 0; i < NB; ++i) {
+                    if (i >= nb_groups) break;
                     const int gi = warp + 4 * i;
                     const int rb = gi % (bn / 8), half = gi / (bn / 8);
                     const int row = rb * 8 + (lane & 7);
@@ -259,7 +261,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                     const int j = n0 + row;
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (j < g.K && kk < k_end) v = ldg4(a.src_b + ((size_t)j * a.k_total + kk));
-                    st_cell(stage_b, (uint32_t)kc * (bn * 16) + (uint32_t)row * 16, half_bytes, v, a.x3);
+                    vb[i] = v;
+                    ob[i] = (uint32_t)kc * (bn * 16) + (uint32_t)row * 16;
                 }
             } else if (KIND == KIND_DGRAD) {
                 // MN-major, rows = input channels (contiguous in the weight tensor), K = (tap, filter)
@@ -270,12 +273,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                 if (kvalid) { tap = kk / g.kp; ko = kk - tap * g.kp; }
                 const bool fvalid = kvalid && ko < g.K;
                 const float *wrow = a.src_b + ((size_t)ko * (g.R * g.S) + tap) * g.cp;
-                for (int i = 0; i < nb_groups; ++i) {
+#pragma unroll
+                for (int i = 0; i < NB; ++i) {
+                    if (i >= nb_groups) break;
                     const int mc = i * 4 + mn_c;
                     const int c = n0 + mc * 4;
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (fvalid && c < g.cp) v = ldg4(wrow + c);
-                    st_cell(stage_b, mn_cell_offset(mc, kq), half_bytes, v, a.x3);
+                    vb[i] = v;
+                    ob[i] = mn_cell_offset(mc, kq);
                 }
             } else {
                 // MN-major gather from x, rows = (tap, channel), K = output pixel
@@ -291,7 +297,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                     ih0 = oh * g.sy - g.pad;
                     iw0 = ow * g.sx - g.pad;
                 }
-                for (int i = 0; i < nb_groups; ++i) {
+#pragma unroll
+                for (int i = 0; i < NB; ++i) {
+                    if (i >= nb_groups) break;
                     const int mc = i * 4 + mn_c;
                     const int4 e = ctl.jtab[mc];
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -300,8 +308,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) conv_gather_kernel(const ConvArgs
                         if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
                             v = ldg4(a.src_b + ((size_t)(nb + ih * g.W + iw) * g.cp + e.z));
                     }
-                    st_cell(stage_b, mn_cell_offset(mc, kq), half_bytes, v, a.x3);
+                    vb[i] = v;
+                    ob[i] = mn_cell_offset(mc, kq);
                 }
+            }
+            if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) st_cell(stage, oa[i], half_bytes, va[i], a.x3);
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                if (i >= nb_groups) break;
+                st_cell(stage_b, ob[i], half_bytes, vb[i], a.x3);
             }
             fence_proxy_async_smem();
             mbar_arrive(smem_u32(&ctl.full[s]));
@@ -448,6 +465,18 @@ int pick_bn(int n_cols, int m_tiles, int sm_count) {
     return full < 64 ? full : 64;
 }
 
+template <int KIND, int NB>
+int launch_gather_nb(aet_context *ctx, const ConvArgs &a, dim3 grid, size_t smem_bytes, const char *name, double flops) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        AET_CUDA(cudaFuncSetAttribute(conv_gather_kernel<KIND, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set = true;
+    }
+    LaunchScope scope(ctx, name, 0, flops);
+    conv_gather_kernel<KIND, NB><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(a);
+    return aet_check_launch(name);
+}
+
 template <int KIND>
 int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, double flops) {
     a.x3 = ctx->math == AET_MATH_3XTF32 ? 1 : 0;
@@ -456,19 +485,14 @@ int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, do
     const size_t half = (size_t)BM * BK * 4 + (size_t)((a.bn + 31) / 32) * 32 * BK * 4;
     const size_t stage = half * (a.x3 ? 2 : 1);
     int stages = (int)((96 * 1024) / stage);
+    if (a.bn <= 64 && stages > 3) stages = 3;   // small tiles: three CTAs share an SM
     if (stages < 3) stages = (int)((200 * 1024) / stage);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     a.stages = stages;
     const size_t smem_bytes = stage * stages + 1024;
-    static bool attr_set[3] = {false, false, false};
-    if (!attr_set[KIND]) {
-        AET_CUDA(cudaFuncSetAttribute(conv_gather_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set[KIND] = true;
-    }
-    LaunchScope scope(ctx, name, 0, flops);
-    conv_gather_kernel<KIND><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(a);
-    return aet_check_launch(name);
+    if (a.bn <= 64) return launch_gather_nb<KIND, 4>(ctx, a, grid, smem_bytes, name, flops);
+    return launch_gather_nb<KIND, 16>(ctx, a, grid, smem_bytes, name, flops);
 }
 
 }  // namespace

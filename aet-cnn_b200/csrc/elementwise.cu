@@ -64,6 +64,55 @@ __device__ __forceinline__ float bn_val(float x, float mean, float inv, float g,
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 __device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
 
+// ---------------------------------------------------------------------------- max-pool gather (fusion helper)
+// When a max-pool follows a BN convolution inside a network, the pool's backward pass is not run as
+// a kernel of its own: the BN backward kernels fetch "the delta the pool would have scattered here"
+// on the fly from the pool's (4x smaller) delta and argmax tensors.  Same gather rule as
+// maxpool_bwd_kernel (mtcs/MtcsMaxPoolLayer.c:295-332).
+struct PoolGather {
+    const float *delta;   // pool layer delta  [N][OH][OW][cp]
+    const int *idx;       // pool argmax       [N][OH][OW][cp], reference numbering
+    int C, H, W, OH, OW, size, sx, sy, off;
+    int simple2;          // size 2, stride 2, no offset: every input belongs to exactly one window
+};
+__device__ __forceinline__ float4 pool_gather(const PoolGather &g, long long p, int c, int cp) {
+    const unsigned pi = (unsigned)p;           // pixel counts stay far below 2^31
+    const int j = (int)(pi % (unsigned)g.W);
+    const unsigned q = pi / (unsigned)g.W;
+    const int i = (int)(q % (unsigned)g.H);
+    const int n = (int)(q / (unsigned)g.H);
+    const int hw = g.H * g.W;
+    const int my = j + g.W * (i + g.H * (c + n * g.C));
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (g.simple2) {
+        const int ow = j >> 1, oh = i >> 1;
+        if (ow < g.OW && oh < g.OH) {
+            const size_t o = ((size_t)(n * g.OH + oh) * g.OW + ow) * cp + c;
+            const int4 id = __ldg(reinterpret_cast<const int4 *>(g.idx + o));
+            const float4 dv = __ldg(reinterpret_cast<const float4 *>(g.delta + o));
+            if (id.x == my) d.x = dv.x;
+            if (id.y == my + hw) d.y = dv.y;
+            if (id.z == my + 2 * hw) d.z = dv.z;
+            if (id.w == my + 3 * hw) d.w = dv.w;
+        }
+        return d;
+    }
+    const int area_x = (g.size - 1) / g.sx, area_y = (g.size - 1) / g.sy;
+    for (int l = -area_y; l < area_y + 1; ++l)
+        for (int m = -area_x; m < area_x + 1; ++m) {
+            const int ow = (j - g.off) / g.sx + m, oh = (i - g.off) / g.sy + l;
+            if (ow < 0 || ow >= g.OW || oh < 0 || oh >= g.OH) continue;
+            const size_t o = ((size_t)(n * g.OH + oh) * g.OW + ow) * cp + c;
+            const int4 id = __ldg(reinterpret_cast<const int4 *>(g.idx + o));
+            const float4 dv = __ldg(reinterpret_cast<const float4 *>(g.delta + o));
+            if (id.x == my) d.x += dv.x;
+            if (id.y == my + hw) d.y += dv.y;
+            if (id.z == my + 2 * hw) d.z += dv.z;
+            if (id.w == my + 3 * hw) d.w += dv.w;
+        }
+    return d;
+}
+
 // ---------------------------------------------------------------------------- generic two-sum reduction
 // MODE 0: BN statistics        s1 = sum(x - shift), s2 = sum((x - shift)^2)
 // MODE 1: BN backward          d' = delta * act'(bn(x)); s1 = sum d', s2 = sum d' * (x - mean)
@@ -78,9 +127,10 @@ struct ReduceArgs {
     int cp;
     long long pix_per_block;
     CMap m;
+    PoolGather pool;      // MODE 1 with POOL: delta comes from the following max-pool layer
 };
 
-template <int MODE>
+template <int MODE, bool POOL = false>
 __global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
     __shared__ float4 sh1[TB];
     __shared__ float4 sh2[TB];
@@ -103,7 +153,7 @@ __global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
                 s1.x += v.x; s1.y += v.y; s1.z += v.z; s1.w += v.w;
                 s2.x += v.x * v.x; s2.y += v.y * v.y; s2.z += v.z * v.z; s2.w += v.w * v.w;
             } else if (MODE == 1) {
-                float4 v = ld4(a.x + off), d = ld4(a.delta + off);
+                float4 v = ld4(a.x + off), d = POOL ? pool_gather(a.pool, p, c, a.cp) : ld4(a.delta + off);
                 d.x *= act_grad(act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
                 d.y *= act_grad(act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
                 d.z *= act_grad(act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
@@ -151,21 +201,35 @@ struct FinalizeArgs {
 // MODE 0: statistics -> mean, variance, 1/std, rolling update.  MODE 1: BN backward coefficients
 // and the scale / shift gradients.  MODE 2: bias gradient.
 template <int MODE>
-__global__ void __launch_bounds__(256) finalize_kernel(const FinalizeArgs a) {
-    // one warp per channel: lanes stride over the per-block partials, then a fixed xor tree
-    const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (c >= a.cp) return;
+__global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
+    // A block owns 32 channels (one coalesced 128-byte row of each partial).  Its 32 warps each take
+    // every 32nd block's partial; the loads of a thread are independent and issued together, the sums
+    // are formed in double in a fixed order (within the thread, then over the 32 warps).
+    __shared__ double sh1[32][33], sh2[32][33];
+    const int cl = threadIdx.x & 31, part = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cl;
     double s1 = 0.0, s2 = 0.0;
-    for (int b = lane; b < a.blocks; b += 32) {
-        s1 += (double)a.partial[(size_t)b * 2 * a.cp + c];
-        if (MODE != 2) s2 += (double)a.partial[(size_t)b * 2 * a.cp + a.cp + c];
+    if (c < a.cp) {
+        for (int b0 = part; b0 < a.blocks; b0 += 32 * 8) {
+            float v1[8], v2[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int b = b0 + 32 * i;
+                v1[i] = 0.f; v2[i] = 0.f;
+                if (b < a.blocks) {
+                    v1[i] = __ldg(a.partial + (size_t)b * 2 * a.cp + c);
+                    if (MODE != 2) v2[i] = __ldg(a.partial + (size_t)b * 2 * a.cp + a.cp + c);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { s1 += (double)v1[i]; s2 += (double)v2[i]; }
+        }
     }
-    for (int o = 16; o; o >>= 1) {
-        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-    }
-    if (lane != 0) return;
+    sh1[part][cl] = s1;
+    sh2[part][cl] = s2;
+    __syncthreads();
+    if (part != 0 || c >= a.cp) return;
+    for (int q = 1; q < 32; ++q) { s1 += sh1[q][cl]; s2 += sh2[q][cl]; }
     const double m = (double)a.m;
     if (MODE == 0) {
         if (c >= a.c) { a.mean[c] = 0.f; a.variance[c] = 0.f; a.inv[c] = 0.f; return; }
@@ -247,7 +311,9 @@ struct BwdApplyArgs {
     int act, cp;
     long long pixels, pix_per_block;
     CMap m;
+    PoolGather pool;
 };
+template <bool POOL>
 __global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) {
     int cv, pl;
     if (!cmap_thread(a.m, cv, pl)) return;
@@ -258,7 +324,7 @@ __global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) 
     if (p1 > a.pixels) p1 = a.pixels;
     for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
         const size_t off = (size_t)p * a.cp + c;
-        float4 v = ld4(a.x + off), d = ld4(a.delta + off);
+        float4 v = ld4(a.x + off), d = POOL ? pool_gather(a.pool, p, c, a.cp) : ld4(a.delta + off);
         d.x *= act_grad(act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
         d.y *= act_grad(act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
         d.z *= act_grad(act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
@@ -295,14 +361,15 @@ struct PoolArgs {
     long long total;   // N*OH*OW*cvec
 };
 __global__ void __launch_bounds__(TB) maxpool_fwd_kernel(const PoolArgs a) {
-    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= a.total) return;
-    const int cvec = a.cp / 4;
+    const long long e64 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e64 >= a.total) return;
+    const unsigned e = (unsigned)e64;          // element counts stay below 2^32
+    const unsigned cvec = (unsigned)a.cp / 4;
     const int cv = (int)(e % cvec);
-    long long p = e / cvec;
-    const int ow = (int)(p % a.OW); p /= a.OW;
-    const int oh = (int)(p % a.OH);
-    const int n = (int)(p / a.OH);
+    unsigned p = e / cvec;
+    const int ow = (int)(p % (unsigned)a.OW); p /= (unsigned)a.OW;
+    const int oh = (int)(p % (unsigned)a.OH);
+    const int n = (int)(p / (unsigned)a.OH);
     const float lowest = a.parity == AET_PARITY_CPU ? -FLT_MAX : -INFINITY;
     float4 mx = make_float4(lowest, lowest, lowest, lowest);
     int4 mi = make_int4(-1, -1, -1, -1);
@@ -329,6 +396,58 @@ __global__ void __launch_bounds__(TB) maxpool_fwd_kernel(const PoolArgs a) {
     if (a.idx) *reinterpret_cast<int4 *>(a.idx + o) = mi;
 }
 
+// Fused BN-apply + activation + max-pool: y = act(bn(x)) is formed in registers for each window tap
+// and only the pooled values and argmax indices are written.  Comparison order and tie rule are those
+// of maxpool_fwd_kernel, on bit-identical y values.
+struct BnPoolArgs {
+    PoolArgs p;
+    const float *mean, *inv, *gamma, *beta;
+    int act;
+};
+__global__ void __launch_bounds__(TB) bn_pool_fwd_kernel(const BnPoolArgs b) {
+    const PoolArgs &a = b.p;
+    const long long e64 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e64 >= a.total) return;
+    const unsigned e = (unsigned)e64;          // element counts stay below 2^32
+    const unsigned cvec = (unsigned)a.cp / 4;
+    const int cv = (int)(e % cvec);
+    unsigned p = e / cvec;
+    const int ow = (int)(p % (unsigned)a.OW); p /= (unsigned)a.OW;
+    const int oh = (int)(p % (unsigned)a.OH);
+    const int n = (int)(p / (unsigned)a.OH);
+    const float lowest = a.parity == AET_PARITY_CPU ? -FLT_MAX : -INFINITY;
+    float4 mx = make_float4(lowest, lowest, lowest, lowest);
+    int4 mi = make_int4(-1, -1, -1, -1);
+    const int c = cv * 4;
+    const float4 mean = __ldg(reinterpret_cast<const float4 *>(b.mean + c)), inv = __ldg(reinterpret_cast<const float4 *>(b.inv + c));
+    const float4 gam = __ldg(reinterpret_cast<const float4 *>(b.gamma + c)), bet = __ldg(reinterpret_cast<const float4 *>(b.beta + c));
+    for (int l = 0; l < a.size; ++l)
+        for (int m = 0; m < a.size; ++m) {
+            const int ch = a.off + oh * a.sy + l, cw = a.off + ow * a.sx + m;
+            const bool valid = ch >= 0 && ch < a.H && cw >= 0 && cw < a.W;
+            float4 v = make_float4(lowest, lowest, lowest, lowest);
+            if (valid) {
+                v = ld4(a.x + ((size_t)(n * a.H + ch) * a.W + cw) * a.cp + c);
+                v.x = act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), b.act);
+                v.y = act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), b.act);
+                v.z = act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), b.act);
+                v.w = act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), b.act);
+            }
+            const int base = cw + a.W * (ch + a.H * (c + n * a.C));
+            const int hw = a.H * a.W;
+            if (v.x > mx.x) { mx.x = v.x; mi.x = base; }
+            if (v.y > mx.y) { mx.y = v.y; mi.y = base + hw; }
+            if (v.z > mx.z) { mx.z = v.z; mi.z = base + 2 * hw; }
+            if (v.w > mx.w) { mx.w = v.w; mi.w = base + 3 * hw; }
+        }
+    if (c + 1 >= a.C) { mx.y = 0.f; mi.y = -1; }
+    if (c + 2 >= a.C) { mx.z = 0.f; mi.z = -1; }
+    if (c + 3 >= a.C) { mx.w = 0.f; mi.w = -1; }
+    const size_t o = ((size_t)(n * a.OH + oh) * a.OW + ow) * a.cp + c;
+    st4(a.y + o, mx);
+    if (a.idx) *reinterpret_cast<int4 *>(a.idx + o) = mi;
+}
+
 struct PoolBwdArgs {
     const float *delta;
     const int *idx;
@@ -339,14 +458,15 @@ struct PoolBwdArgs {
 // Gather form (mtcs/MtcsMaxPoolLayer.c:295-332): every input element adds the deltas of the
 // windows whose argmax it is.
 __global__ void __launch_bounds__(TB) maxpool_bwd_kernel(const PoolBwdArgs a) {
-    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= a.total) return;
-    const int cvec = a.cp / 4;
+    const long long e64 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e64 >= a.total) return;
+    const unsigned e = (unsigned)e64;
+    const unsigned cvec = (unsigned)a.cp / 4;
     const int cv = (int)(e % cvec);
-    long long p = e / cvec;
-    const int j = (int)(p % a.W); p /= a.W;
-    const int i = (int)(p % a.H);
-    const int n = (int)(p / a.H);
+    unsigned p = e / cvec;
+    const int j = (int)(p % (unsigned)a.W); p /= (unsigned)a.W;
+    const int i = (int)(p % (unsigned)a.H);
+    const int n = (int)(p / (unsigned)a.H);
     const int c = cv * 4;
     const int area_x = (a.size - 1) / a.sx, area_y = (a.size - 1) / a.sy;
     const int hw = a.H * a.W;
@@ -600,13 +720,10 @@ int k_bn_stats(aet_layer *l, int update_rolling) {
     ReducePlan p = plan_reduce(ctx, pixels, l->ocp);
     float *partial = nullptr;
     AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
-    {
-        LaunchScope s(ctx, "bn_shift", 0, 0);
-        copy_first_pixel_kernel<<<(l->ocp + 255) / 256, 256, 0, ctx->stream>>>(l->x->d, l->shift, l->ocp);
-        AET_TRY(aet_check_launch("bn_shift"));
-    }
+    // The statistics are accumulated around a per-channel shift so that the one-pass variance does
+    // not cancel; any value near the data works, and the previous step's batch mean is already there.
     ReduceArgs a = {};
-    a.x = l->x->d; a.shift = l->shift; a.partial = partial; a.pixels = pixels; a.cp = l->ocp;
+    a.x = l->x->d; a.shift = l->mean; a.partial = partial; a.pixels = pixels; a.cp = l->ocp;
     a.pix_per_block = p.pix_per_block; a.m = p.m;
     {
         LaunchScope s(ctx, "bn_stats", (double)pixels * l->ocp * 4.0, 0);
@@ -615,11 +732,11 @@ int k_bn_stats(aet_layer *l, int update_rolling) {
     }
     FinalizeArgs f = {};
     f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels;
-    f.parity = ctx->parity; f.update_rolling = update_rolling; f.shift = l->shift;
+    f.parity = ctx->parity; f.update_rolling = update_rolling; f.shift = l->mean;
     f.mean = l->mean; f.variance = l->variance; f.inv = l->inv_std;
     f.rolling_mean = l->rolling_mean; f.rolling_variance = l->rolling_variance;
     LaunchScope s(ctx, "bn_stats_finalize", 0, 0);
-    finalize_kernel<0><<<(l->ocp + 7) / 8, 256, 0, ctx->stream>>>(f);
+    finalize_kernel<0><<<(l->ocp + 31) / 32, 1024, 0, ctx->stream>>>(f);
     return aet_check_launch("bn_stats_finalize");
 }
 
@@ -644,8 +761,41 @@ int k_bn_apply(aet_layer *l, int use_rolling) {
     return aet_check_launch("bn_apply_act");
 }
 
+static PoolGather make_pool_gather(const aet_layer *pool) {
+    PoolGather g;
+    g.delta = pool->delta->d; g.idx = pool->indexes;
+    g.C = pool->c; g.H = pool->h; g.W = pool->w; g.OH = pool->oh; g.OW = pool->ow;
+    g.size = pool->size; g.sx = pool->stride_x; g.sy = pool->stride_y; g.off = -pool->pad / 2;
+    g.simple2 = (g.size == 2 && g.sx == 2 && g.sy == 2 && g.off == 0) ? 1 : 0;
+    return g;
+}
+
+// output of the following max-pool layer straight from the convolution result: pool(act(bn(x))).
+int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling) {
+    aet_context *ctx = l->ctx;
+    if (use_rolling) {
+        LaunchScope s(ctx, "bn_eval_inv", 0, 0);
+        eval_inv_kernel<<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(l->rolling_variance, l->inv_std, l->oc, l->ocp,
+                                                                        ctx->parity);
+        AET_TRY(aet_check_launch("bn_eval_inv"));
+    }
+    BnPoolArgs b = {};
+    PoolArgs &a = b.p;
+    a.x = l->x->d; a.y = pool->output->d; a.idx = pool->indexes;
+    a.N = pool->batch; a.C = pool->c; a.H = pool->h; a.W = pool->w; a.cp = pool->cp; a.OH = pool->oh; a.OW = pool->ow;
+    a.size = pool->size; a.sx = pool->stride_x; a.sy = pool->stride_y; a.off = -pool->pad / 2; a.parity = ctx->parity;
+    a.total = (long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4);
+    b.mean = use_rolling ? l->rolling_mean : l->mean; b.inv = l->inv_std; b.gamma = layer_s(l); b.beta = layer_b(l);
+    b.act = l->act;
+    const double bytes = 4.0 * pool->batch * pool->h * pool->w * pool->cp + 8.0 * pool->batch * pool->oh * pool->ow * pool->cp;
+    LaunchScope s(ctx, "bn_act_maxpool_fwd", bytes, 0);
+    bn_pool_fwd_kernel<<<(unsigned)((a.total + TB - 1) / TB), TB, 0, ctx->stream>>>(b);
+    return aet_check_launch("bn_act_maxpool_fwd");
+}
+
 // delta <- BN backward of (delta * act'(output)); accumulates the scale (and, MTCS parity, shift) gradients.
-int k_bn_backward(aet_layer *l) {
+// With `pool` set, the incoming delta is gathered from that max-pool layer instead of being read.
+int k_bn_backward(aet_layer *l, aet_layer *pool) {
     aet_context *ctx = l->ctx;
     const long long pixels = (long long)l->batch * l->oh * l->ow;
     ReducePlan p = plan_reduce(ctx, pixels, l->ocp);
@@ -655,7 +805,13 @@ int k_bn_backward(aet_layer *l) {
     a.x = l->x->d; a.delta = l->delta->d; a.mean = l->mean; a.inv = l->inv_std;
     a.gamma = layer_s(l); a.beta = layer_b(l); a.partial = partial; a.act = l->act;
     a.pixels = pixels; a.cp = l->ocp; a.pix_per_block = p.pix_per_block; a.m = p.m;
-    {
+    const double pool_bytes = pool ? 8.0 * pool->batch * pool->oh * pool->ow * pool->cp : 0.0;
+    if (pool) {
+        a.pool = make_pool_gather(pool);
+        LaunchScope s(ctx, "bn_bwd_reduce_pool", (double)pixels * l->ocp * 4.0 + pool_bytes, 0);
+        reduce2_kernel<1, true><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        AET_TRY(aet_check_launch("bn_bwd_reduce_pool"));
+    } else {
         LaunchScope s(ctx, "bn_bwd_reduce", (double)pixels * l->ocp * 8.0, 0);
         reduce2_kernel<1><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
         AET_TRY(aet_check_launch("bn_bwd_reduce"));
@@ -666,7 +822,7 @@ int k_bn_backward(aet_layer *l) {
     f.g_gamma = layer_sG(l); f.g_beta = layer_bG(l); f.coef = l->bwd_coef;
     {
         LaunchScope s(ctx, "bn_bwd_finalize", 0, 0);
-        finalize_kernel<1><<<(l->ocp + 7) / 8, 256, 0, ctx->stream>>>(f);
+        finalize_kernel<1><<<(l->ocp + 31) / 32, 1024, 0, ctx->stream>>>(f);
         AET_TRY(aet_check_launch("bn_bwd_finalize"));
     }
     ReducePlan q = plan_apply(ctx, pixels, l->ocp);
@@ -674,8 +830,14 @@ int k_bn_backward(aet_layer *l) {
     b.x = l->x->d; b.delta = l->delta->d; b.mean = l->mean; b.inv = l->inv_std;
     b.gamma = layer_s(l); b.beta = layer_b(l); b.coef = l->bwd_coef; b.act = l->act; b.cp = l->ocp;
     b.pixels = pixels; b.pix_per_block = q.pix_per_block; b.m = q.m;
+    if (pool) {
+        b.pool = make_pool_gather(pool);
+        LaunchScope s(ctx, "bn_bwd_apply_pool", (double)pixels * l->ocp * 8.0 + pool_bytes, 0);
+        bn_bwd_apply_kernel<true><<<dim3(q.blocks, q.m.cslabs), TB, 0, ctx->stream>>>(b);
+        return aet_check_launch("bn_bwd_apply_pool");
+    }
     LaunchScope s(ctx, "bn_bwd_apply", (double)pixels * l->ocp * 12.0, 0);
-    bn_bwd_apply_kernel<<<dim3(q.blocks, q.m.cslabs), TB, 0, ctx->stream>>>(b);
+    bn_bwd_apply_kernel<false><<<dim3(q.blocks, q.m.cslabs), TB, 0, ctx->stream>>>(b);
     return aet_check_launch("bn_bwd_apply");
 }
 
@@ -697,7 +859,7 @@ int k_bias_act_backward(aet_layer *l) {
     FinalizeArgs f = {};
     f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels; f.g_beta = layer_bG(l);
     LaunchScope s(ctx, "bias_bwd_finalize", 0, 0);
-    finalize_kernel<2><<<(l->ocp + 7) / 8, 256, 0, ctx->stream>>>(f);
+    finalize_kernel<2><<<(l->ocp + 31) / 32, 1024, 0, ctx->stream>>>(f);
     return aet_check_launch("bias_bwd_finalize");
 }
 
@@ -897,6 +1059,6 @@ extern "C" int aet_backward_bias_static(const float *delta, float *bias_updates,
     AET_TRY(aet_check_launch("backward_bias_static (partials)"));
     FinalizeArgs f = {};
     f.partial = st.scratch; f.blocks = p.blocks; f.cp = channels; f.c = channels; f.m = pixels; f.g_beta = bias_updates;
-    finalize_kernel<2><<<(channels + 7) / 8, 256, 0, stream>>>(f);
+    finalize_kernel<2><<<(channels + 31) / 32, 1024, 0, stream>>>(f);
     return aet_check_launch("backward_bias_static (finalize)");
 }

@@ -270,11 +270,19 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
     case AET_CONVOLUTIONAL:
         if (l->bn) {
             AET_TRY(conv_fprop(l, state.input->d, l->x->d, nullptr, 0));
-            if (state.train) {
-                AET_TRY(k_bn_stats(l, 1));
-                AET_TRY(k_bn_apply(l, 0));
+            if (state.train) AET_TRY(k_bn_stats(l, 1));
+            l->last_forward_train = state.train != 0;
+            aet_layer *pool = l->fused_pool;
+            if (pool && (pool->indexes || !state.train)) {
+                // the following max-pool is produced here; the full-resolution activated output is
+                // only materialised if a host tap asks for it
+                AET_TRY(k_bn_pool_forward(l, pool, state.train ? 0 : 1));
+                l->output_stale = true;
+                pool->fused_ready = true;
+                pool->output->lazy_zero = false;
             } else {
-                AET_TRY(k_bn_apply(l, 1));
+                AET_TRY(k_bn_apply(l, state.train ? 0 : 1));
+                l->output_stale = false;
             }
         } else {
             AET_TRY(conv_fprop(l, state.input->d, l->output->d, layer_b(l), 1));
@@ -282,6 +290,11 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
         l->output->lazy_zero = false;
         return AET_OK;
     case AET_MAXPOOL:
+        if (l->fused_ready && l->fused_into && state.input == l->fused_into->output) {
+            l->fused_ready = false;   // already computed by the convolution's fused kernel
+            return AET_OK;
+        }
+        l->fused_ready = false;
         l->output->lazy_zero = false;
         return k_maxpool_forward(l, state.input->d);
     case AET_AVGPOOL:
@@ -318,12 +331,19 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     switch (l->type) {
     case AET_CONVOLUTIONAL: {
         AET_TRY(check_input(l, state.input));
-        if (l->delta->lazy_zero) {   // nothing upstream wrote a gradient: materialise the zeros
-            AET_TRY(aet_tensor_zero(l->delta));
+        if (l->gather_pending && l->bn && l->fused_pool) {
+            // the max-pool's backward was deferred: gather its delta inside the BN backward kernels
+            l->gather_pending = false;
+            AET_TRY(k_bn_backward(l, l->fused_pool));
             l->delta->lazy_zero = false;
+        } else {
+            if (l->delta->lazy_zero) {   // nothing upstream wrote a gradient: materialise the zeros
+                AET_TRY(aet_tensor_zero(l->delta));
+                l->delta->lazy_zero = false;
+            }
+            if (l->bn) AET_TRY(k_bn_backward(l, nullptr));
+            else AET_TRY(k_bias_act_backward(l));
         }
-        if (l->bn) AET_TRY(k_bn_backward(l));
-        else AET_TRY(k_bias_act_backward(l));
         AET_TRY(conv_wgrad(l, state.input->d, l->delta->d, layer_G(l), 1));
         if (pd) {
             AET_TRY(conv_dgrad(l, l->delta->d, pd->d));
@@ -334,6 +354,10 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     case AET_MAXPOOL:
         if (!pd) return AET_OK;
         if (l->delta->lazy_zero) { AET_TRY(aet_tensor_zero(l->delta)); l->delta->lazy_zero = false; }
+        if (l->fused_into && pd == l->fused_into->delta && pd->lazy_zero && l->indexes) {
+            l->fused_into->gather_pending = true;   // the convolution's BN backward gathers from this layer
+            return AET_OK;
+        }
         AET_TRY(k_maxpool_backward(l, pd->d, pd->lazy_zero ? 0 : 1));
         pd->lazy_zero = false;
         return AET_OK;
@@ -462,7 +486,12 @@ extern "C" int aet_layer_read(aet_layer *l, aet_param which, void *host_v) {
     case AET_P_ROLLING_VARIANCE: return vector_download(ctx, l->rolling_variance, host, l->oc);
     case AET_P_MEAN: return vector_download(ctx, l->mean, host, l->oc);
     case AET_P_VARIANCE: return vector_download(ctx, l->variance, host, l->oc);
-    case AET_P_OUTPUT: return read_tensor_or_zero(l->output, host);
+    case AET_P_OUTPUT:
+        if (l->output_stale) {   // fused forward skipped the full-resolution output: form it now
+            AET_TRY(k_bn_apply(l, l->last_forward_train ? 0 : 1));
+            l->output_stale = false;
+        }
+        return read_tensor_or_zero(l->output, host);
     case AET_P_DELTA: return read_tensor_or_zero(l->delta, host);
     case AET_P_X: return aet_tensor_read(l->x, host);
     case AET_P_X_NORM: {
@@ -516,6 +545,7 @@ extern "C" int aet_layer_write(aet_layer *l, aet_param which, const void *host_v
     case AET_P_VARIANCE: return write_vec(l, l->variance, host, l->oc, nullptr);
     case AET_P_OUTPUT:
         l->output->lazy_zero = false;
+        l->output_stale = false;
         return aet_tensor_write(l->output, host);
     case AET_P_DELTA:
         l->delta->lazy_zero = false;

@@ -411,6 +411,10 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
         if (!l) { aet_network_destroy(net); return nullptr; }
         l->net = net;
         l->index = index;
+        if (l->type == AET_MAXPOOL && !net->layers.empty() && !getenv("AET_NO_FUSE")) {
+            aet_layer *prev = net->layers.back();
+            if (prev->type == AET_CONVOLUTIONAL && prev->bn) { prev->fused_pool = l; l->fused_into = prev; }
+        }
         net->layers.push_back(l);
         c = l->oc; h = l->oh; w = l->ow;
     }

@@ -57,7 +57,9 @@ typedef enum {
     AET_P_ROLLING_VARIANCE,
     AET_P_MEAN,
     AET_P_VARIANCE,
-    AET_P_OUTPUT,            /* layer output  [batch][c][h][w] */
+    AET_P_OUTPUT,            /* layer output  [batch][c][h][w]; for a BN convolution followed by a max-pool inside a
+                              * network it is formed on demand from the saved convolution result with the layer's
+                              * current scale / shift: read it before the next update */
     AET_P_DELTA,             /* layer delta   [batch][c][h][w] */
     AET_P_X,                 /* BN input saved by normalize (dnn/NormData.c:244-282) */
     AET_P_X_NORM,            /* recomputed on read: (x-mean)*inv_std */

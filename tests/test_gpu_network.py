@@ -149,6 +149,39 @@ def test_graph_replay_is_bitwise_identical_to_eager(aet, ctx, oracle):
     assert hashes[0] == hashes[1]
 
 
+def test_fused_bn_pool_path_is_bitwise_identical_to_layer_by_layer(aet, ctx, oracle):
+    """Inside a network a BN convolution produces the following max-pool's output itself and gathers the
+    pool's delta in its BN backward; AET_NO_FUSE=1 runs every layer's own kernels instead."""
+    import os as _os
+    batch, steps = 8, 3
+    results = []
+    for no_fuse in (False, True):
+        if no_fuse:
+            _os.environ["AET_NO_FUSE"] = "1"
+        try:
+            net, _, opts, _ = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+        finally:
+            _os.environ.pop("AET_NO_FUSE", None)
+        losses = []
+        for step in range(steps):
+            x, truth = batch_for(opts, 10, batch, 3, step)
+            losses.append(net.train(x, truth))
+        # forward only, then the taps: the full-resolution conv outputs are formed lazily from the saved
+        # convolution result (with the layer's current scale / shift, so read them before an update)
+        x, truth = batch_for(opts, 10, batch, 3, steps)
+        net.input.write(x); net.truth.write(truth)
+        net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+        outs = [net.layer(i).read(aet.P_OUTPUT) for i in range(net.layer_count)]
+        idx = net.layer(1).read(aet.P_INDEXES)
+        results.append((net.param_hash(), tuple(losses), outs, idx, net.launches_per_step()))
+        net.close()
+    assert results[0][0] == results[1][0] and results[0][1] == results[1][1]
+    for a, b in zip(results[0][2], results[1][2]):
+        assert np.array_equal(a, b)
+    assert np.array_equal(results[0][3], results[1][3])
+    assert results[0][4] < results[1][4]          # fewer launches when fused
+
+
 def test_weights_file_roundtrip_and_layout(aet, ctx, oracle):
     batch = 4
     net, _, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
