@@ -145,28 +145,52 @@ __global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
         long long p0 = (long long)blockIdx.x * a.pix_per_block;
         long long p1 = p0 + a.pix_per_block;
         if (p1 > a.pixels) p1 = a.pixels;
-        for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
-            const size_t off = (size_t)p * a.cp + c;
-            if (MODE == 0) {
-                float4 v = ld4(a.x + off);
-                v.x -= sft.x; v.y -= sft.y; v.z -= sft.z; v.w -= sft.w;
-                s1.x += v.x; s1.y += v.y; s1.z += v.z; s1.w += v.w;
-                s2.x += v.x * v.x; s2.y += v.y * v.y; s2.z += v.z * v.z; s2.w += v.w * v.w;
-            } else if (MODE == 1) {
-                float4 v = ld4(a.x + off), d = POOL ? pool_gather(a.pool, p, c, a.cp) : ld4(a.delta + off);
-                d.x *= act_grad(act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
-                d.y *= act_grad(act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
-                d.z *= act_grad(act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
-                d.w *= act_grad(act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
-                s1.x += d.x; s1.y += d.y; s1.z += d.z; s1.w += d.w;
-                s2.x += d.x * (v.x - mean.x); s2.y += d.y * (v.y - mean.y);
-                s2.z += d.z * (v.z - mean.z); s2.w += d.w * (v.w - mean.w);
-            } else {
-                float4 y = ld4(a.x + off), d = ld4(a.delta + off);
-                d.x *= act_grad(y.x, a.act); d.y *= act_grad(y.y, a.act);
-                d.z *= act_grad(y.z, a.act); d.w *= act_grad(y.w, a.act);
-                if (a.act != AET_LINEAR) st4(a.delta + off, d);
-                s1.x += d.x; s1.y += d.y; s1.z += d.z; s1.w += d.w;
+        // four pixels per trip: all loads of a trip are issued before any arithmetic, which is what
+        // keeps enough bytes in flight per SM to approach HBM bandwidth
+        constexpr int U = 4;
+        const long long step = a.m.pl_count;
+        for (long long pb = p0 + pl; pb < p1; pb += U * step) {
+            float4 v[U], d[U];
+            bool ok[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const long long p = pb + u * step;
+                ok[u] = p < p1;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                d[u] = v[u];
+                if (ok[u]) {
+                    const size_t off = (size_t)p * a.cp + c;
+                    v[u] = ld4(a.x + off);
+                    if (MODE == 1) d[u] = POOL ? pool_gather(a.pool, p, c, a.cp) : ld4(a.delta + off);
+                    if (MODE == 2) d[u] = ld4(a.delta + off);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!ok[u]) continue;
+                if (MODE == 0) {
+                    float4 t = v[u];
+                    t.x -= sft.x; t.y -= sft.y; t.z -= sft.z; t.w -= sft.w;
+                    s1.x += t.x; s1.y += t.y; s1.z += t.z; s1.w += t.w;
+                    s2.x += t.x * t.x; s2.y += t.y * t.y; s2.z += t.z * t.z; s2.w += t.w * t.w;
+                } else if (MODE == 1) {
+                    const float4 t = v[u];
+                    float4 q = d[u];
+                    q.x *= act_grad(act_fwd(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
+                    q.y *= act_grad(act_fwd(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
+                    q.z *= act_grad(act_fwd(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
+                    q.w *= act_grad(act_fwd(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+                    s1.x += q.x; s1.y += q.y; s1.z += q.z; s1.w += q.w;
+                    s2.x += q.x * (t.x - mean.x); s2.y += q.y * (t.y - mean.y);
+                    s2.z += q.z * (t.z - mean.z); s2.w += q.w * (t.w - mean.w);
+                } else {
+                    const float4 y = v[u];
+                    float4 q = d[u];
+                    q.x *= act_grad(y.x, a.act); q.y *= act_grad(y.y, a.act);
+                    q.z *= act_grad(y.z, a.act); q.w *= act_grad(y.w, a.act);
+                    if (a.act != AET_LINEAR) st4(a.delta + (size_t)(pb + u * step) * a.cp + c, q);
+                    s1.x += q.x; s1.y += q.y; s1.z += q.z; s1.w += q.w;
+                }
             }
         }
     }
@@ -181,6 +205,86 @@ __global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
             s2.x += t2.x; s2.y += t2.y; s2.z += t2.z; s2.w += t2.w;
         }
         float *dst = a.partial + (size_t)blockIdx.x * 2 * a.cp + cv * 4;
+        st4(dst, s1);
+        st4(dst + a.cp, s2);
+    }
+}
+
+// Window-major BN backward for the common 2x2 / stride-2 pool over even-sized maps: one thread owns
+// one pool output (4 channels) and the four inputs of its window, so the pool's delta and argmax are
+// read once per window and no per-input index arithmetic is needed.  blockDim must be a multiple
+// of cp/4 so that a thread keeps its channel vector over the grid-stride loop.
+struct PoolWinArgs {
+    const float *x;          // conv result [N][H][W][cp]
+    float *dx;               // conv delta  [N][H][W][cp]   (apply pass)
+    const float *pdelta;     // pool delta  [N][OH][OW][cp]
+    const int *pidx;         // pool argmax
+    const float *mean, *inv, *gamma, *beta, *coef;
+    float *partial;          // [blocks][2][cp]              (reduce pass)
+    int act, cp, C, H, W, OH, OW;
+    unsigned total;          // N*OH*OW*cvec
+};
+__device__ __forceinline__ float sel(int id, int pos, float v) { return id == pos ? v : 0.f; }
+
+template <bool APPLY>
+__global__ void __launch_bounds__(TB) bn_bwd_poolwin_kernel(const PoolWinArgs a) {
+    __shared__ float4 sh1[TB];
+    __shared__ float4 sh2[TB];
+    const unsigned cvec = (unsigned)a.cp / 4;
+    const int cv = (int)(threadIdx.x % cvec);
+    const int c = cv * 4;
+    const float4 mean = ld4(a.mean + c), inv = ld4(a.inv + c), gam = ld4(a.gamma + c), bet = ld4(a.beta + c);
+    float4 ka, kb, kc;
+    if (APPLY) { ka = ld4(a.coef + c); kb = ld4(a.coef + a.cp + c); kc = ld4(a.coef + 2 * a.cp + c); }
+    float4 s1 = make_float4(0.f, 0.f, 0.f, 0.f), s2 = s1;
+    const int hw = a.H * a.W;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < a.total; e += gridDim.x * blockDim.x) {
+        unsigned p = e / cvec;                      // e % cvec == cv because blockDim and the stride are multiples of cvec
+        const int ow = (int)(p % (unsigned)a.OW); p /= (unsigned)a.OW;
+        const int oh = (int)(p % (unsigned)a.OH);
+        const int n = (int)(p / (unsigned)a.OH);
+        const size_t o = ((size_t)(n * a.OH + oh) * a.OW + ow) * a.cp + c;
+        const int4 id = __ldg(reinterpret_cast<const int4 *>(a.pidx + o));
+        const float4 dv = __ldg(reinterpret_cast<const float4 *>(a.pdelta + o));
+        const size_t i00 = ((size_t)(n * a.H + 2 * oh) * a.W + 2 * ow) * a.cp + c;
+        const size_t offs[4] = {i00, i00 + a.cp, i00 + (size_t)a.W * a.cp, i00 + (size_t)a.W * a.cp + a.cp};
+        float4 v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) v[t] = ld4(a.x + offs[t]);
+        // reference numbering of the window's top-left input, channel c
+        const int pos00 = 2 * ow + a.W * (2 * oh + a.H * (c + n * a.C));
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int pos = pos00 + (t & 1) + (t >> 1) * a.W;
+            float4 q;
+            q.x = sel(id.x, pos, dv.x) * act_grad(act_fwd(bn_val(v[t].x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
+            q.y = sel(id.y, pos + hw, dv.y) * act_grad(act_fwd(bn_val(v[t].y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
+            q.z = sel(id.z, pos + 2 * hw, dv.z) * act_grad(act_fwd(bn_val(v[t].z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
+            q.w = sel(id.w, pos + 3 * hw, dv.w) * act_grad(act_fwd(bn_val(v[t].w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+            if (APPLY) {
+                q.x = q.x * ka.x + (v[t].x - mean.x) * kb.x + kc.x;
+                q.y = q.y * ka.y + (v[t].y - mean.y) * kb.y + kc.y;
+                q.z = q.z * ka.z + (v[t].z - mean.z) * kb.z + kc.z;
+                q.w = q.w * ka.w + (v[t].w - mean.w) * kb.w + kc.w;
+                st4(a.dx + offs[t], q);
+            } else {
+                s1.x += q.x; s1.y += q.y; s1.z += q.z; s1.w += q.w;
+                s2.x += q.x * (v[t].x - mean.x); s2.y += q.y * (v[t].y - mean.y);
+                s2.z += q.z * (v[t].z - mean.z); s2.w += q.w * (v[t].w - mean.w);
+            }
+        }
+    }
+    if (APPLY) return;
+    sh1[threadIdx.x] = s1;
+    sh2[threadIdx.x] = s2;
+    __syncthreads();
+    if (threadIdx.x < cvec) {
+        for (unsigned q = threadIdx.x + cvec; q < blockDim.x; q += cvec) {
+            float4 t1 = sh1[q], t2 = sh2[q];
+            s1.x += t1.x; s1.y += t1.y; s1.z += t1.z; s1.w += t1.w;
+            s2.x += t2.x; s2.y += t2.y; s2.z += t2.z; s2.w += t2.w;
+        }
+        float *dst = a.partial + (size_t)blockIdx.x * 2 * a.cp + c;
         st4(dst, s1);
         st4(dst + a.cp, s2);
     }
@@ -292,14 +396,26 @@ __global__ void __launch_bounds__(TB) bn_apply_kernel(const ApplyArgs a) {
     const float4 mean = ld4(a.mean + c), inv = ld4(a.inv + c), gam = ld4(a.gamma + c), bet = ld4(a.beta + c);
     long long p0 = (long long)blockIdx.x * a.pix_per_block, p1 = p0 + a.pix_per_block;
     if (p1 > a.pixels) p1 = a.pixels;
-    for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
-        const size_t off = (size_t)p * a.cp + c;
-        float4 v = ld4(a.x + off);
-        v.x = act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act);
-        v.y = act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act);
-        v.z = act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act);
-        v.w = act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), a.act);
-        st4(a.y + off, v);
+    constexpr int U = 4;
+    const long long step = a.m.pl_count;
+    for (long long pb = p0 + pl; pb < p1; pb += U * step) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long p = pb + u * step;
+            if (p < p1) v[u] = ld4(a.x + (size_t)p * a.cp + c);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long p = pb + u * step;
+            if (p >= p1) continue;
+            float4 t = v[u];
+            t.x = act_fwd(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act);
+            t.y = act_fwd(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act);
+            t.z = act_fwd(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act);
+            t.w = act_fwd(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act);
+            st4(a.y + (size_t)p * a.cp + c, t);
+        }
     }
 }
 
@@ -322,18 +438,35 @@ __global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) 
     const float4 ka = ld4(a.coef + c), kb = ld4(a.coef + a.cp + c), kc = ld4(a.coef + 2 * a.cp + c);
     long long p0 = (long long)blockIdx.x * a.pix_per_block, p1 = p0 + a.pix_per_block;
     if (p1 > a.pixels) p1 = a.pixels;
-    for (long long p = p0 + pl; p < p1; p += a.m.pl_count) {
-        const size_t off = (size_t)p * a.cp + c;
-        float4 v = ld4(a.x + off), d = POOL ? pool_gather(a.pool, p, c, a.cp) : ld4(a.delta + off);
-        d.x *= act_grad(act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
-        d.y *= act_grad(act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
-        d.z *= act_grad(act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
-        d.w *= act_grad(act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
-        d.x = d.x * ka.x + (v.x - mean.x) * kb.x + kc.x;
-        d.y = d.y * ka.y + (v.y - mean.y) * kb.y + kc.y;
-        d.z = d.z * ka.z + (v.z - mean.z) * kb.z + kc.z;
-        d.w = d.w * ka.w + (v.w - mean.w) * kb.w + kc.w;
-        st4(a.delta + off, d);
+    constexpr int U = 4;
+    const long long step = a.m.pl_count;
+    for (long long pb = p0 + pl; pb < p1; pb += U * step) {
+        float4 v[U], d[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long p = pb + u * step;
+            if (p < p1) {
+                const size_t off = (size_t)p * a.cp + c;
+                v[u] = ld4(a.x + off);
+                d[u] = POOL ? pool_gather(a.pool, p, c, a.cp) : ld4(a.delta + off);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long p = pb + u * step;
+            if (p >= p1) continue;
+            const float4 t = v[u];
+            float4 q = d[u];
+            q.x *= act_grad(act_fwd(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
+            q.y *= act_grad(act_fwd(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
+            q.z *= act_grad(act_fwd(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
+            q.w *= act_grad(act_fwd(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+            q.x = q.x * ka.x + (t.x - mean.x) * kb.x + kc.x;
+            q.y = q.y * ka.y + (t.y - mean.y) * kb.y + kc.y;
+            q.z = q.z * ka.z + (t.z - mean.z) * kb.z + kc.z;
+            q.w = q.w * ka.w + (t.w - mean.w) * kb.w + kc.w;
+            st4(a.delta + (size_t)p * a.cp + c, q);
+        }
     }
 }
 
@@ -679,9 +812,9 @@ struct ReducePlan {
 ReducePlan plan_reduce(aet_context *ctx, long long pixels, int cp) {
     ReducePlan p;
     p.m = make_cmap(cp);
-    long long want = 2LL * ctx->sm_count / p.m.cslabs;
+    long long want = 4LL * ctx->sm_count / p.m.cslabs;
     if (want < 1) want = 1;
-    long long min_pix = (long long)p.m.pl_count * 4;   // at least 4 pixels per thread
+    long long min_pix = (long long)p.m.pl_count * 8;   // at least 8 pixels per thread
     long long maxb = (pixels + min_pix - 1) / min_pix;
     if (want > maxb) want = maxb;
     if (want < 1) want = 1;
@@ -806,7 +939,25 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     a.gamma = layer_s(l); a.beta = layer_b(l); a.partial = partial; a.act = l->act;
     a.pixels = pixels; a.cp = l->ocp; a.pix_per_block = p.pix_per_block; a.m = p.m;
     const double pool_bytes = pool ? 8.0 * pool->batch * pool->oh * pool->ow * pool->cp : 0.0;
-    if (pool) {
+    const bool window_major = pool && pool->size == 2 && pool->stride_x == 2 && pool->stride_y == 2 && pool->pad / 2 == 0 &&
+                              pool->h % 2 == 0 && pool->w % 2 == 0 && TB % (l->ocp / 4) == 0 &&
+                              (long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4) < (1LL << 31);
+    PoolWinArgs w = {};
+    if (window_major) {
+        w.x = l->x->d; w.dx = l->delta->d; w.pdelta = pool->delta->d; w.pidx = pool->indexes;
+        w.mean = l->mean; w.inv = l->inv_std; w.gamma = layer_s(l); w.beta = layer_b(l); w.coef = l->bwd_coef;
+        w.act = l->act; w.cp = l->ocp; w.C = pool->c; w.H = pool->h; w.W = pool->w; w.OH = pool->oh; w.OW = pool->ow;
+        w.total = (unsigned)((long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4));
+        int blocks = 4 * ctx->sm_count;
+        const int maxb = (int)((w.total + TB - 1) / TB);
+        if (blocks > maxb) blocks = maxb;
+        p.blocks = blocks;
+        AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
+        w.partial = partial;
+        LaunchScope s(ctx, "bn_bwd_reduce_poolwin", (double)pixels * l->ocp * 4.0 + pool_bytes, 0);
+        bn_bwd_poolwin_kernel<false><<<p.blocks, TB, 0, ctx->stream>>>(w);
+        AET_TRY(aet_check_launch("bn_bwd_reduce_poolwin"));
+    } else if (pool) {
         a.pool = make_pool_gather(pool);
         LaunchScope s(ctx, "bn_bwd_reduce_pool", (double)pixels * l->ocp * 4.0 + pool_bytes, 0);
         reduce2_kernel<1, true><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
@@ -830,6 +981,12 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     b.x = l->x->d; b.delta = l->delta->d; b.mean = l->mean; b.inv = l->inv_std;
     b.gamma = layer_s(l); b.beta = layer_b(l); b.coef = l->bwd_coef; b.act = l->act; b.cp = l->ocp;
     b.pixels = pixels; b.pix_per_block = q.pix_per_block; b.m = q.m;
+    if (window_major) {
+        const int blocks = (int)((w.total + TB - 1) / TB) < 8 * ctx->sm_count ? (int)((w.total + TB - 1) / TB) : 8 * ctx->sm_count;
+        LaunchScope s(ctx, "bn_bwd_apply_poolwin", (double)pixels * l->ocp * 8.0 + pool_bytes, 0);
+        bn_bwd_poolwin_kernel<true><<<blocks, TB, 0, ctx->stream>>>(w);
+        return aet_check_launch("bn_bwd_apply_poolwin");
+    }
     if (pool) {
         b.pool = make_pool_gather(pool);
         LaunchScope s(ctx, "bn_bwd_apply_pool", (double)pixels * l->ocp * 8.0 + pool_bytes, 0);
