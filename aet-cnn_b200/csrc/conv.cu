@@ -455,6 +455,10 @@ ConvGeom layer_geom(const aet_layer *l) {
 
 int pick_bn(int n_cols, int m_tiles, int sm_count) {
     int full = round_up(n_cols, 16);
+    if (const char *e = getenv("AET_BN")) {   // tuning aid
+        int v = atoi(e);
+        if (v >= 16 && v % 16 == 0 && v <= 256) return v < full ? v : (full <= 256 ? full : v);
+    }
     if (full <= 64) return full;
     const int cands[3] = {256, 128, 64};
     for (int i = 0; i < 3; ++i) {

@@ -147,9 +147,15 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // ------------------------------------------------------------------ TMA producer
             const int img0 = m0 / a.pix_per_img;                       // fprop/dgrad tile origin
             const int row0 = (m0 - img0 * a.pix_per_img) / a.tile_w;
-            for (int it = 0; it < nslabs; ++it) {
-                const int s = it % a.stages;
-                const uint32_t phase = (it / a.stages) & 1;
+            // CTAs walk the K slabs from different starting points: all of them read the same weight
+            // tiles, and marching in lockstep would send every SM to the same L2 lines at once.  The
+            // order is a function of the CTA index only, so results stay reproducible.
+            const int rot = (KIND == KIND_WGRAD || nslabs == 0) ? 0 : (int)((blockIdx.x * 7u + blockIdx.y * 3u) % (unsigned)nslabs);
+            for (int it0 = 0; it0 < nslabs; ++it0) {
+                int it = it0 + rot;
+                if (it >= nslabs) it -= nslabs;
+                const int s = it0 % a.stages;
+                const uint32_t phase = (it0 / a.stages) & 1;
                 if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
                 const uint32_t bar = smem_u32(&ctl.full[s]);
                 const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
@@ -291,9 +297,11 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
     return aet_check_launch(name);
 }
 
+// Input channels must fill whole 32-channel (128-byte) rows.  The filter side may be narrower than one
+// row (ocp < 32: the copy engine zero-fills the rest of the box) or a whole number of rows.
 bool tma_common_ok(const aet_layer *l) {
     return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && l->stride_x == 1 && l->stride_y == 1 &&
-           l->cp % 32 == 0 && l->ocp % 32 == 0;
+           l->cp % 32 == 0 && (l->ocp % 32 == 0 || l->ocp < 32);
 }
 
 int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
@@ -302,8 +310,7 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     cuuint32_t bw, bh, bi;
     if (!pixel_box(BM, g.OH, g.OW, &bw, &bh, &bi) || (int)bw != g.OW) return 1;
     if (g.OW > g.W || g.OH > g.H) return 1;
-    const int bn = a.bn % 32 == 0 ? a.bn : 0;
-    if (!bn) return 1;
+    const int bn = a.bn;                      // any multiple of 16: K-major rows in 8-row swizzle groups
     const CUtensorMap *ma, *mb;
     {
         cuuint64_t dims[4] = {(cuuint64_t)g.cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
@@ -342,7 +349,7 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
         cuuint64_t dims[4] = {(cuuint64_t)g.kp, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N};
         cuuint64_t str[3] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4};
         cuuint32_t box[4] = {32, bw, bh, bi};
-        AET_TRY(get_map(l, 2, a.src_a, 4, dims, str, box, false, &ma));
+        if (get_map(l, 2, a.src_a, 4, dims, str, box, false, &ma) != AET_OK) return g.kp % 32 ? 1 : AET_E_CUDA;
     }
     {
         // weights [filter][tap][cp] viewed as (c%32, filter, c/32, tap)
@@ -355,9 +362,9 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
     TmaArgs t = {};
     t.out = a.out; t.bias = nullptr; t.act = AET_LINEAR; t.bn = bn;
     t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
-    t.slabs_per_tap = g.kp / 32; t.S = g.S; t.pad = g.pad;
+    t.slabs_per_tap = (g.kp + 31) / 32; t.S = g.S; t.pad = g.pad;
     t.pix_per_img = g.H * g.W; t.tile_w = g.W; t.img_w = g.W;
-    t.total_slabs = a.k_total / 32; t.slabs_per_split = t.total_slabs;
+    t.total_slabs = g.R * g.S * t.slabs_per_tap; t.slabs_per_split = t.total_slabs;
     t.a_bytes = BM * BK * 4;
     t.tx_bytes = t.a_bytes + bn * BK * 4;
     dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
@@ -374,13 +381,15 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
     if (!pixel_box(BK, g.OH, g.OW, &bw, &bh, &bi)) return 1;
     const int bn = g.cp <= 256 ? g.cp : (g.cp % 256 == 0 ? 256 : (g.cp % 128 == 0 ? 128 : 0));
     if (!bn) return 1;
-    const int m_blocks = g.kp / 32 < 4 ? g.kp / 32 : 4;
+    const int k_blocks = (g.kp + 31) / 32;
+    const int m_blocks = k_blocks < 4 ? k_blocks : 4;
     const CUtensorMap *ma, *mb;
     {
-        cuuint64_t dims[5] = {32, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N, (cuuint64_t)g.kp / 32};
+        cuuint64_t dims[5] = {(cuuint64_t)(g.kp < 32 ? g.kp : 32), (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N,
+                              (cuuint64_t)k_blocks};
         cuuint64_t str[4] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4, 128};
         cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)m_blocks};
-        AET_TRY(get_map(l, 4, a.src_a, 5, dims, str, box, true, &ma));
+        if (get_map(l, 4, a.src_a, 5, dims, str, box, true, &ma) != AET_OK) return g.kp % 32 ? 1 : AET_E_CUDA;
     }
     {
         cuuint64_t dims[5] = {32, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N, (cuuint64_t)g.cp / 32};

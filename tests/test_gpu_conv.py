@@ -29,6 +29,8 @@ TMA_SHAPES = [
     (6, 256, 8, 8, 256, 3, 1, 1, 0),      # 256 -> 256 sweep shape, batch not a multiple of the tile
     (32, 64, 4, 4, 64, 1, 1, 0, 1),       # 1x1, eight images per 128-pixel tile
     (2, 32, 64, 64, 64, 3, 1, 1, 0),      # image rows wider than a K slab
+    (16, 256, 4, 4, 10, 1, 1, 0, 0),      # classifier conv: fewer filters than one 32-channel row
+    (8, 64, 8, 8, 20, 3, 1, 1, 1),        # 20 filters, 3x3
 ]
 
 
