@@ -82,6 +82,51 @@ __device__ __forceinline__ void st_cell(unsigned char *stage, uint32_t off, uint
     }
 }
 
+// Epilogue of one accumulator: TMEM -> registers -> shared memory (the idle pipeline stages, row
+// pitch bn+4 floats so that a quarter warp of consecutive rows hits eight distinct 16-byte bank
+// groups) -> global memory with lanes along the COLUMNS of one row.  A thread owns a TMEM lane = an
+// output row, so storing straight from registers would make every warp store touch 32 rows
+// 512 or more bytes apart (measured: 10 us for a 128x128 tile, half the kernel); through shared
+// memory every store instruction writes one contiguous row segment.
+// Each warp only re-reads the 32 rows it wrote itself: __syncwarp is the only synchronisation.
+template <bool FPROP>
+__device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
+                                                  float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
+                                                  const float *bias, int act) {
+    const int pitch = bn + 4;
+    float *mine = tile + (size_t)(warp * 32 + lane) * pitch;
+    for (int cc = 0; cc < bn; cc += 16) {
+        float v[16];
+        if (have_acc) {
+            tmem_ld16(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] = 0.f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<float4 *>(mine + cc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+    }
+    __syncwarp();
+    for (int c = lane * 4; c < bn; c += 128) {
+        const int col = col_base + c;
+        if (col >= n_cols) continue;
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (FPROP && bias) b = ldg4(bias + col);
+        for (int r = 0; r < 32; ++r) {
+            const int row = warp * 32 + r;
+            if (row >= rows_valid) break;
+            float4 o = *reinterpret_cast<const float4 *>(tile + (size_t)row * pitch + c);
+            if (FPROP) {
+                o.x = apply_act(o.x + b.x, act); o.y = apply_act(o.y + b.y, act);
+                o.z = apply_act(o.z + b.z, act); o.w = apply_act(o.w + b.w, act);
+            }
+            *reinterpret_cast<float4 *>(out + (size_t)row * out_ld + col) = o;
+        }
+    }
+    __syncwarp();
+}
+
 // Byte offset of the 16-byte cell holding M/N elements 4*mc..4*mc+3 at K index k (0..31) inside an
 // MN-major tile stored as [32-element block][32 k-rows][128 B] in the 128B / 32-byte-atom swizzle.
 __device__ __forceinline__ uint32_t mn_cell_offset(int mc, int k) {
@@ -328,67 +373,39 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
         bool ready = nslabs == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
         ready = __all_sync(0xffffffffu, ready);   // the TMEM loads below are warp-collective
         tc_fence_after_sync();
-        const int row = m0 + warp * 32 + lane;
-        const bool row_ok = row < a.n_rows;
-        float *orow = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)row * a.out_ld;
         if (ready) {
-            for (int cc = 0; cc < bn; cc += 16) {
-                float v[16];
-                if (nslabs > 0) {
-                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 16; ++q) v[q] = 0.f;
-                }
-                if (!row_ok) continue;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int col = n0 + cc + q * 4;
-                    if (col >= a.n_cols) continue;
-                    float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                    if (KIND == KIND_FPROP) {
-                        if (a.bias) {
-                            float4 b = ldg4(a.bias + col);
-                            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-                        }
-                        o.x = apply_act(o.x, a.act); o.y = apply_act(o.y, a.act);
-                        o.z = apply_act(o.z, a.act); o.w = apply_act(o.w, a.act);
-                    }
-                    *reinterpret_cast<float4 *>(orow + col) = o;
-                }
-            }
+            float *obase = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)m0 * a.out_ld;
+            store_accumulator<KIND == KIND_FPROP>(reinterpret_cast<float *>(smem), tmem, nslabs > 0, warp, lane, bn, obase,
+                                                  (size_t)a.out_ld, a.n_rows - m0, n0, a.n_cols, a.bias, a.act);
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         const int a_mn = (KIND == KIND_WGRAD) ? 1 : 0;
         const int b_mn = (KIND == KIND_FPROP) ? 0 : 1;
         const uint32_t idesc = make_idesc_tf32(BM, bn, a_mn, b_mn);
+        // Descriptors are built once; per MMA only the start-address field (16-byte units) advances.
+        // K-major: un-swizzled core matrices, two 16-byte K chunks per MMA at LBO, 8-row groups at SBO.
+        // MN-major: 128B / 32-byte-atom swizzle, 32-element blocks at LBO, 4-k atoms at SBO.
+        const uint32_t s0 = smem_u32(smem);
+        const uint64_t da0 = a_mn ? make_desc(s0, 4096, 512, LAYOUT_SW128_32B) : make_desc(s0, BM * 16, 128, LAYOUT_NONE);
+        const uint64_t db0 = b_mn ? make_desc(s0 + a_bytes, 4096, 512, LAYOUT_SW128_32B) : make_desc(s0 + a_bytes, bn * 16, 128, LAYOUT_NONE);
+        const uint64_t a_step = a_mn ? 64 : (2 * BM * 16) >> 4, b_step = b_mn ? 64 : (uint64_t)((2 * bn * 16) >> 4);
+        const uint64_t lo16 = (uint64_t)(half_bytes >> 4);
         uint32_t accumulate = 0;
         for (int it = 0; it < nslabs; ++it) {
             const int s = it % a.stages;
             const uint32_t phase = (it / a.stages) & 1;
             if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
             tc_fence_after_sync();
-            const uint32_t sa = smem_u32(smem + (size_t)s * stage_bytes);
-            const uint32_t sb = sa + a_bytes;
+            const uint64_t st16 = (uint64_t)(((uint32_t)s * stage_bytes) >> 4);
             const int k0 = k_begin + it * BK;
             int ksteps = (k_end - k0 + 7) / 8;
             if (ksteps > 4) ksteps = 4;
             for (int j = 0; j < ksteps; ++j) {
-                // K-major: un-swizzled core matrices, two 16-byte K chunks per MMA at LBO, 8-row groups at SBO.
-                // MN-major: 128B / 32-byte-atom swizzle, 32-element blocks at LBO, 4-k atoms at SBO.
-                const uint32_t a_addr = a_mn ? sa + j * 1024 : sa + j * 2 * (BM * 16);
-                const uint32_t b_addr = b_mn ? sb + j * 1024 : sb + j * 2 * (bn * 16);
-                const uint32_t a_lbo = a_mn ? 4096u : BM * 16, a_sbo = a_mn ? 512u : 128u;
-                const uint32_t b_lbo = b_mn ? 4096u : bn * 16, b_sbo = b_mn ? 512u : 128u;
-                const uint64_t a_lay = a_mn ? LAYOUT_SW128_32B : LAYOUT_NONE, b_lay = b_mn ? LAYOUT_SW128_32B : LAYOUT_NONE;
-                const uint64_t da = make_desc(a_addr, a_lbo, a_sbo, a_lay);
-                const uint64_t db = make_desc(b_addr, b_lbo, b_sbo, b_lay);
+                const uint64_t da = da0 + st16 + j * a_step, db = db0 + st16 + j * b_step;
                 if (a.x3) {
-                    const uint64_t da_lo = make_desc(a_addr + half_bytes, a_lbo, a_sbo, a_lay);
-                    const uint64_t db_lo = make_desc(b_addr + half_bytes, b_lbo, b_sbo, b_lay);
-                    mma_tf32(tmem, da_lo, db, idesc, accumulate);
-                    mma_tf32(tmem, da, db_lo, idesc, 1);
+                    mma_tf32(tmem, da + lo16, db, idesc, accumulate);
+                    mma_tf32(tmem, da, db + lo16, idesc, 1);
                     mma_tf32(tmem, da, db, idesc, 1);
                 } else {
                     mma_tf32(tmem, da, db, idesc, accumulate);
@@ -502,6 +519,7 @@ int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, do
 }  // namespace
 
 #include "conv_tma.cuh"
+#include "conv_tma_rows.cuh"
 
 int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue) {
     aet_context *ctx = l->ctx;
@@ -555,6 +573,21 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
     a.k_total = g.N * g.OH * g.OW;
     a.out_ld = a.n_cols;
     const int m_tiles = (g.K + BM - 1) / BM;
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    const size_t out_floats = (size_t)g.K * a.n_cols;
+    {
+        int rsplits = 0;
+        float *rpartial = nullptr;
+        int rr = tma_wgrad_rows(l, a, flops, &rsplits, &rpartial);
+        if (rr < 0) return rr;
+        if (rr == AET_OK) {
+            const size_t count4 = out_floats / 4;
+            LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (rsplits + 1 + (accumulate ? 1 : 0)), 0);
+            wgrad_reduce_kernel<<<(unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, ctx->stream>>>(
+                rpartial, dw, count4, rsplits, out_floats, accumulate);
+            return aet_check_launch("wgrad_reduce");
+        }
+    }
     // N tile: the multiple of 16 (<= 256) that wastes the fewest padded columns, larger on ties
     int best_bn = 16, best_pad = 1 << 30;
     const int full = round_up(a.n_cols, 16);
@@ -575,12 +608,10 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
     const int slabs_per_split = (total_slabs + want - 1) / want;
     const int splits = (total_slabs + slabs_per_split - 1) / slabs_per_split;
     a.k_per_split = slabs_per_split * BK;
-    const size_t out_floats = (size_t)g.K * a.n_cols;
     a.split_stride = (long long)out_floats;
     float *partial = nullptr;
     AET_TRY(ctx_scratch(ctx, out_floats * splits * sizeof(float), &partial));
     a.out = partial;
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
     int r = tma_wgrad(l, a, splits, flops);
     if (r == 1) {
         dim3 grid(m_tiles, n_tiles, splits);

@@ -187,58 +187,34 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         bool ready = nslabs == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
         ready = __all_sync(0xffffffffu, ready);   // the TMEM loads below are warp-collective
         tc_fence_after_sync();
-        const int row = m0 + warp * 32 + lane;
-        const bool row_ok = row < a.n_rows;
-        float *orow = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)row * a.out_ld;
         if (ready) {
-            for (int cc = 0; cc < bn; cc += 16) {
-                float v[16];
-                if (nslabs > 0) {
-                    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
-                } else {
-#pragma unroll
-                    for (int q = 0; q < 16; ++q) v[q] = 0.f;
-                }
-                if (!row_ok) continue;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int col = n0 + cc + q * 4;
-                    if (col >= a.n_cols) continue;
-                    float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                    if (KIND == KIND_FPROP) {
-                        if (a.bias) {
-                            float4 b = ldg4(a.bias + col);
-                            o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-                        }
-                        o.x = apply_act(o.x, a.act); o.y = apply_act(o.y, a.act);
-                        o.z = apply_act(o.z, a.act); o.w = apply_act(o.w, a.act);
-                    }
-                    *reinterpret_cast<float4 *>(orow + col) = o;
-                }
-            }
+            float *obase = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)m0 * a.out_ld;
+            float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            store_accumulator<KIND == KIND_FPROP>(tile, tmem, nslabs > 0, warp, lane, bn, obase, (size_t)a.out_ld, a.n_rows - m0,
+                                                  n0, a.n_cols, a.bias, a.act);
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         const int a_mn = (KIND == KIND_WGRAD) ? 1 : 0;
         const int b_mn = (KIND == KIND_FPROP) ? 0 : 1;
         const uint32_t idesc = make_idesc_tf32(BM, bn, a_mn, b_mn);
+        // descriptors are built once; per MMA only the start-address field (16-byte units) advances
+        const uint64_t da0 = a_mn ? make_desc(smem_base, 4096, 512, LAYOUT_SW128_32B) : make_desc(smem_base, 0, 1024, LAYOUT_SW128);
+        const uint64_t db0 = b_mn ? make_desc(smem_base + a.a_bytes, 4096, 512, LAYOUT_SW128_32B)
+                                  : make_desc(smem_base + a.a_bytes, 0, 1024, LAYOUT_SW128);
+        const uint64_t a_step = a_mn ? 64 : 2, b_step = b_mn ? 64 : 2;   // 1024 or 32 bytes per K step
         uint32_t accumulate = 0;
         for (int it = 0; it < nslabs; ++it) {
             const int s = it % a.stages;
             const uint32_t phase = (it / a.stages) & 1;
             if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
             tc_fence_after_sync();
-            const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
-            const uint32_t sb = sa + a.a_bytes;
+            // K-major tiles: 128B swizzle, 16-byte atoms, K advances 32 bytes per MMA inside the row.
+            // MN-major tiles: [32-element block][32 k-rows][128 B] in the 32-byte-atom swizzle.
+            const uint64_t st16 = (uint64_t)(((uint32_t)s * stage_bytes) >> 4);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                // K-major tiles: 128B swizzle, 16-byte atoms, K advances 32 bytes per MMA inside the row.
-                // MN-major tiles: [32-element block][32 k-rows][128 B] in the 32-byte-atom swizzle.
-                const uint64_t da = a_mn ? make_desc(sa + j * 1024, 4096, 512, LAYOUT_SW128_32B)
-                                         : make_desc(sa + j * 32, 0, 1024, LAYOUT_SW128);
-                const uint64_t db = b_mn ? make_desc(sb + j * 1024, 4096, 512, LAYOUT_SW128_32B)
-                                         : make_desc(sb + j * 32, 0, 1024, LAYOUT_SW128);
-                mma_tf32(tmem, da, db, idesc, accumulate);
+                mma_tf32(tmem, da0 + st16 + j * a_step, db0 + st16 + j * b_step, idesc, accumulate);
                 accumulate = 1;
             }
             mma_commit(smem_u32(&ctl.empty[s]));
