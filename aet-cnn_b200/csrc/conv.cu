@@ -92,7 +92,7 @@ __device__ __forceinline__ void st_cell(unsigned char *stage, uint32_t off, uint
 template <bool FPROP>
 __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
                                                   float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
-                                                  const float *bias, int act) {
+                                                  const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0) {
     const int pitch = bn + 4;
     float *mine = tile + (size_t)(warp * 32 + lane) * pitch;
     for (int cc = 0; cc < bn; cc += 16) {
@@ -115,13 +115,15 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
         if (FPROP && bias) b = ldg4(bias + col);
         for (int r = 0; r < 32; ++r) {
             const int row = warp * 32 + r;
-            if (row >= rows_valid) break;
+            // tiles that span several small images order their rows (h, image, w): map to the pixel index
+            const int grow = map_bi > 1 ? ((row / map_w) % map_bi) * map_pix + (row / (map_bi * map_w)) * map_w + row % map_w : row;
+            if (grow >= rows_valid) { if (map_bi > 1) continue; else break; }
             float4 o = *reinterpret_cast<const float4 *>(tile + (size_t)row * pitch + c);
             if (FPROP) {
                 o.x = apply_act(o.x + b.x, act); o.y = apply_act(o.y + b.y, act);
                 o.z = apply_act(o.z + b.z, act); o.w = apply_act(o.w + b.w, act);
             }
-            *reinterpret_cast<float4 *>(out + (size_t)row * out_ld + col) = o;
+            *reinterpret_cast<float4 *>(out + (size_t)grow * out_ld + col) = o;
         }
     }
     __syncwarp();
@@ -536,8 +538,10 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
     const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
-    int r = tma_fprop(l, a, flops);
-    if (r != 1) return r;   // 1 = shape not eligible for the TMA producer
+    int r = tma_fd_rows<KIND_FPROP>(l, a, flops);
+    if (r != 1) return r;   // 1 = shape not eligible
+    r = tma_fprop(l, a, flops);
+    if (r != 1) return r;
     dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
     return launch_gather<KIND_FPROP>(ctx, a, grid, "conv_fprop_gather", flops);
 }
@@ -556,7 +560,9 @@ int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
     const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
-    int r = tma_dgrad(l, a, flops);
+    int r = tma_fd_rows<KIND_DGRAD>(l, a, flops);
+    if (r != 1) return r;
+    r = tma_dgrad(l, a, flops);
     if (r != 1) return r;
     dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
     return launch_gather<KIND_DGRAD>(ctx, a, grid, "conv_dgrad_gather", flops);

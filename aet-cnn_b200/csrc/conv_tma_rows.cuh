@@ -210,3 +210,224 @@ int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_ou
 }
 
 }  // namespace
+
+// ---------------------------------------------------------------------------- fprop / dgrad with row sharing
+// CTA = (pixel tile, filter/channel tile).  A pipeline stage holds, for one column tap s and one
+// 32-channel slab, ONE activation super-tile of (MT*bh + R - 1) image rows and the R weight tiles of
+// taps (0..R-1, s); it is consumed by R x MT x 4 MMAs into MT accumulators (MT = 2 pixel tiles of
+// the same image share every weight tile, halving the weight traffic too).
+namespace {
+
+struct FdRowsArgs {
+    float *out;
+    const float *bias;
+    int act, bn, n_rows, n_cols, out_ld;
+    int R, S, pad, inner;          // inner = channels of the K dimension (cp for fprop, kp for dgrad)
+    int slabs_per_s;               // ceil(inner / 32)
+    int mt, bh, bi, w, pix_per_img, n_img;
+    int stages, tmem_cols;
+    uint32_t a_bytes, b_tile_bytes, tx_bytes;
+    int *status;
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(NTHREADS, 1)
+conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const FdRowsArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ SharedCtl ctl;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bn = a.bn;
+    const int n0 = blockIdx.y * bn;
+    const int m0 = blockIdx.x * BM * a.mt;                  // first pixel (in (n,h,w) order) of this CTA
+    const int img0 = m0 / a.pix_per_img;
+    const int row0 = (m0 - img0 * a.pix_per_img) / a.w;      // 0 when the tile spans whole images
+    const int nslabs = a.S * a.slabs_per_s;
+    const uint32_t stage_bytes = a.a_bytes + (uint32_t)a.R * a.b_tile_bytes;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 1);
+            mbar_init(smem_u32(&ctl.empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl.accum), 1);
+        ctl.abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = ctl.tmem_base;
+    volatile int *abort_flag = &ctl.abort_flag;
+
+    if (warp < 4) {
+        if (threadIdx.x == 0) {
+            for (int it = 0; it < nslabs; ++it) {
+                const int s = it % a.stages;
+                const uint32_t phase = (it / a.stages) & 1;
+                if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
+                const uint32_t bar = smem_u32(&ctl.full[s]);
+                const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
+                const uint32_t sb = sa + a.a_bytes;
+                mbar_arrive_expect_tx(bar, a.tx_bytes);
+                const int st = it / a.slabs_per_s, cb = it - st * a.slabs_per_s;   // column tap, channel slab
+                // fprop reads input pixel (h + r - pad, w + s - pad); dgrad reads delta pixel (h + pad - r, w + pad - s)
+                const int wx = KIND == KIND_FPROP ? st - a.pad : a.pad - st;
+                const int hy = KIND == KIND_FPROP ? row0 - a.pad : row0 + a.pad - (a.R - 1);
+                if (a.bi > 1) tma_load_4d(sa, &map_a, bar, cb * 32, wx, img0, hy);      // dims (c, w, n, h)
+                else          tma_load_4d(sa, &map_a, bar, cb * 32, wx, hy, img0);      // dims (c, w, h, n)
+                for (int r = 0; r < a.R; ++r) {
+                    const int tap = r * a.S + st;
+                    if (KIND == KIND_FPROP) tma_load_2d(sb + r * a.b_tile_bytes, &map_b, bar, tap * a.inner + cb * 32, n0);
+                    else                    tma_load_4d(sb + r * a.b_tile_bytes, &map_b, bar, 0, cb * 32, n0 / 32, tap);
+                }
+            }
+        }
+        __syncwarp();
+        bool ready = mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
+        ready = __all_sync(0xffffffffu, ready);
+        tc_fence_after_sync();
+        if (ready) {
+            float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            for (int t = 0; t < a.mt; ++t) {
+                const int mt0 = m0 + t * BM;
+                store_accumulator<KIND == KIND_FPROP>(tile, tmem + (uint32_t)(t * bn), true, warp, lane, bn,
+                                                      a.out + (size_t)mt0 * a.out_ld, (size_t)a.out_ld, a.n_rows - mt0, n0, a.n_cols,
+                                                      a.bias, a.act, a.bi, a.w, a.pix_per_img);
+            }
+        }
+    } else if (lane == 0) {
+        const int b_mn = KIND == KIND_FPROP ? 0 : 1;
+        const uint32_t idesc = make_idesc_tf32(BM, bn, 0, b_mn);
+        const uint64_t da0 = make_desc(smem_base, 0, 1024, LAYOUT_SW128);
+        const uint64_t db0 = b_mn ? make_desc(smem_base + a.a_bytes, 4096, 512, LAYOUT_SW128_32B)
+                                  : make_desc(smem_base + a.a_bytes, 0, 1024, LAYOUT_SW128);
+        const uint64_t b_step = b_mn ? 64 : 2;
+        const uint32_t img_row16 = ((uint32_t)(a.bi * a.w) * 128u) >> 4;      // one image row (of every image in the tile)
+        const uint32_t tile_rows16 = (uint32_t)a.bh * img_row16;               // one 128-pixel tile
+        const uint32_t btile16 = a.b_tile_bytes >> 4;
+        uint32_t accumulate = 0;
+        for (int it = 0; it < nslabs; ++it) {
+            const int s = it % a.stages;
+            const uint32_t phase = (it / a.stages) & 1;
+            if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
+            tc_fence_after_sync();
+            const uint64_t st16 = (uint64_t)(((uint32_t)s * stage_bytes) >> 4);
+            for (int r = 0; r < a.R; ++r) {
+                const int rr = KIND == KIND_FPROP ? r : a.R - 1 - r;
+                const uint64_t db_r = db0 + st16 + (uint64_t)(r * btile16);
+                for (int t = 0; t < a.mt; ++t) {
+                    const uint64_t da_rt = da0 + st16 + (uint64_t)(t * tile_rows16 + rr * img_row16);
+                    const uint32_t d_t = tmem + (uint32_t)(t * bn);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        mma_tf32(d_t, da_rt + (uint64_t)(j * 2), db_r + j * b_step, idesc, (accumulate | (uint32_t)(r > 0 || j > 0)));
+                }
+            }
+            accumulate = 1;
+            mma_commit(smem_u32(&ctl.empty[s]));
+        }
+        mma_commit(smem_u32(&ctl.accum));
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        tmem_dealloc(tmem, a.tmem_cols);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+    }
+}
+
+// fprop (KIND_FPROP) or dgrad (KIND_DGRAD) through the row-sharing kernel; 1 = not eligible.
+template <int KIND>
+int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
+    aet_context *ctx = l->ctx;
+    const ConvGeom &g = a.g;
+    if (!tma_common_ok(l) || getenv("AET_NO_ROWS")) return 1;
+    if (g.R < 2 || g.OH != g.H || g.OW != g.W) return 1;                 // same-size convolutions
+    const int inner = KIND == KIND_FPROP ? g.cp : g.kp;
+    if (KIND == KIND_DGRAD && !(g.kp % 32 == 0)) return 1;
+    cuuint32_t bw, bh, bi;
+    if (!pixel_box(BM, g.H, g.W, &bw, &bh, &bi) || (int)bw != g.W) return 1;
+    if (((int)bi * g.W) % 8) return 1;                                    // image rows must be whole swizzle periods
+    // The stages fill most of an SM's shared memory, so one CTA runs per SM: take the widest N tile
+    // that still gives a CTA to most SMs (wider tiles re-read the activations less often).
+    const int m_tiles = (a.n_rows + BM - 1) / BM;
+    const int full = round_up(a.n_cols, 16);
+    int bn = 0;
+    const int cands[4] = {full <= 256 ? full : 256, 128, 64, 32};
+    for (int i = 0; i < 4 && !bn; ++i) {
+        const int c = cands[i];
+        if (c > full || (KIND == KIND_DGRAD && (c % 32 || g.cp % c))) continue;
+        if (m_tiles * ((a.n_cols + c - 1) / c) >= (ctx->sm_count * 3) / 5 || c <= 64) bn = c;
+    }
+    if (!bn) return 1;
+    const int n_tiles = (a.n_cols + bn - 1) / bn;
+    // two pixel tiles per CTA when they are rows of one image and there are still enough CTAs
+    int mt = 1;
+    if (bi == 1 && g.H % (2 * (int)bh) == 0 && 2 * bn <= 512 && (m_tiles / 2) * n_tiles >= (ctx->sm_count * 3) / 4 &&
+        !getenv("AET_NO_MT2"))
+        mt = 2;
+    const int super_rows = mt * (int)bh + g.R - 1;
+    const uint32_t a_bytes = (uint32_t)super_rows * bi * g.W * 128u;
+    const uint32_t b_tile = (uint32_t)bn * 128u;
+    const size_t stage = (size_t)a_bytes + (size_t)g.R * b_tile;
+    int stages = (int)((200 * 1024) / stage);
+    if (stages > 4) stages = 4;
+    if (stages < 2) return 1;
+    if (stage * stages < (size_t)BM * (bn + 4) * 4) return 1;             // epilogue tile must fit
+    const CUtensorMap *ma, *mb;
+    const float *act = a.src_a;
+    const int ac = inner;   // channels of the A tensor
+    if (bi > 1) {
+        cuuint64_t dims[4] = {(cuuint64_t)ac, (cuuint64_t)g.W, (cuuint64_t)g.N, (cuuint64_t)g.H};
+        cuuint64_t str[3] = {(cuuint64_t)ac * 4, (cuuint64_t)g.H * g.W * ac * 4, (cuuint64_t)g.W * ac * 4};
+        cuuint32_t box[4] = {32, (cuuint32_t)g.W, bi, (cuuint32_t)super_rows};
+        AET_TRY(get_map(l, KIND == KIND_FPROP ? 8 : 10, act, 4, dims, str, box, false, &ma));
+    } else {
+        cuuint64_t dims[4] = {(cuuint64_t)ac, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
+        cuuint64_t str[3] = {(cuuint64_t)ac * 4, (cuuint64_t)g.W * ac * 4, (cuuint64_t)g.H * g.W * ac * 4};
+        cuuint32_t box[4] = {32, (cuuint32_t)g.W, (cuuint32_t)super_rows, 1};
+        AET_TRY(get_map(l, KIND == KIND_FPROP ? 8 : 10, act, 4, dims, str, box, false, &ma));
+    }
+    if (KIND == KIND_FPROP) {
+        cuuint64_t dims[2] = {(cuuint64_t)a.k_total, (cuuint64_t)g.K};
+        cuuint64_t str[1] = {(cuuint64_t)a.k_total * 4};
+        cuuint32_t box[2] = {32, (cuuint32_t)bn};
+        AET_TRY(get_map(l, 9, a.src_b, 2, dims, str, box, false, &mb));
+    } else {
+        const int taps = g.R * g.S;
+        cuuint64_t dims[4] = {32, (cuuint64_t)g.K, (cuuint64_t)g.cp / 32, (cuuint64_t)taps};
+        cuuint64_t str[3] = {(cuuint64_t)taps * g.cp * 4, 128, (cuuint64_t)g.cp * 4};
+        cuuint32_t box[4] = {32, 32, (cuuint32_t)bn / 32, 1};
+        AET_TRY(get_map(l, 11, a.src_b, 4, dims, str, box, true, &mb));
+    }
+    FdRowsArgs t = {};
+    t.out = a.out; t.bias = KIND == KIND_FPROP ? a.bias : nullptr; t.act = KIND == KIND_FPROP ? a.act : (int)AET_LINEAR;
+    t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    t.R = g.R; t.S = g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
+    t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
+    t.stages = stages; t.tmem_cols = pow2_cols(mt * bn);
+    t.a_bytes = a_bytes; t.b_tile_bytes = b_tile; t.tx_bytes = a_bytes + (uint32_t)g.R * b_tile;
+    t.status = ctx->status_dev;
+    const size_t smem_bytes = stage * stages + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        AET_CUDA(cudaFuncSetAttribute(conv_fd_rows_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set = true;
+    }
+    dim3 grid((m_tiles + mt - 1) / mt, n_tiles, 1);
+    const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
+    LaunchScope scope(ctx, name, 0, flops);
+    conv_fd_rows_kernel<KIND><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(*ma, *mb, t);
+    return aet_check_launch(name);
+}
+
+}  // namespace

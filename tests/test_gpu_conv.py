@@ -85,7 +85,8 @@ def test_conv_tma_tf32(aet, ctx, oracle, shape):
         used = kernels_used(ctx)
     finally:
         ctx.profile(0)
-    assert {"conv_fprop_tma", "conv_dgrad_tma"} <= used and ({"conv_wgrad_tma", "conv_wgrad_tma_rows"} & used), used
+    assert ({"conv_fprop_tma", "conv_fprop_tma_rows"} & used) and ({"conv_dgrad_tma", "conv_dgrad_tma_rows"} & used) and \
+        ({"conv_wgrad_tma", "conv_wgrad_tma_rows"} & used), used
     check(got, ref, TOL_TF32)
 
 
