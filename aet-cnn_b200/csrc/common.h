@@ -135,6 +135,11 @@ struct aet_layer {
     bool last_forward_train = true;
     bool fused_ready = false;          // pool: output already produced by the convolution this pass
     bool gather_pending = false;       // conv: the pool deferred its backward to this layer
+    // Network-level fusion of the classifier head conv(linear) -> avgpool -> softmax (<= 32 classes)
+    aet_layer *head_conv = nullptr, *head_avg = nullptr;   // set on the softmax layer
+    aet_layer *head_softmax = nullptr;                     // set on the avg-pool and the convolution
+    bool head_forward_pending = false;  // avg-pool: forward deferred to the softmax layer's fused kernel
+    bool head_backward_done = false;    // avg-pool / conv: delta (and bias gradient) already produced
     // TMA descriptors are built lazily per (layer, pass, operand address)
     void *tma_cache = nullptr;
 };
@@ -220,6 +225,8 @@ int k_maxpool_backward(aet_layer *l, float *prev_delta, int accumulate);
 int k_avgpool_forward(aet_layer *l, const float *x);
 int k_avgpool_backward(aet_layer *l, float *prev_delta, int accumulate);
 int k_softmax_forward(aet_layer *l, const float *x, const float *truth);
+int k_head_forward(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *truth);
+int k_head_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm);
 int k_axpy(aet_context *ctx, float *y, const float *x, float a, size_t n, int accumulate, const char *name);
 int k_dropout_forward(aet_layer *l, float *x, int generate);
 int k_dropout_backward(aet_layer *l, float *delta);

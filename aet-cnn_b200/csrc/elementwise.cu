@@ -718,6 +718,85 @@ __global__ void __launch_bounds__(1024) softmax_cost_kernel(const float *unit_lo
     }
 }
 
+// ---------------------------------------------------------------------------- fused classifier head
+// conv (no BN, linear) -> global average pool -> softmax + cross entropy, up to 32 classes: one block,
+// one warp per sample (lane = class).  The forward kernel replaces avgpool_fwd + softmax + cost, the
+// backward kernel replaces softmax backward + avgpool backward + the convolution's bias gradient.
+struct HeadArgs {
+    const float *y;        // conv output       [N][spatial][cp]
+    float *avg;            // avg-pool output   [N][cp]
+    float *p, *sm_delta, *loss;   // softmax output / delta / per-element error  [N][cp]
+    const float *truth;    // [N][cp] or null
+    float *cost;           // {sum, mean}
+    float *avg_delta;      // [N][cp]
+    float *conv_delta;     // [N][spatial][cp]
+    float *bias_grad;      // [cp], accumulated
+    int N, spatial, classes, cp, parity;
+    float temp, loss_scale;
+};
+__global__ void __launch_bounds__(1024) head_forward_kernel(const HeadArgs a) {
+    __shared__ float warp_loss[32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float lsum = 0.f;
+    for (int n = warp; n < a.N; n += 32) {
+        float v = 0.f;
+        if (lane < a.classes) {
+            const float *src = a.y + (size_t)n * a.spatial * a.cp + lane;
+            for (int i = 0; i < a.spatial; ++i) v += src[(size_t)i * a.cp];
+            v /= a.spatial;
+            a.avg[(size_t)n * a.cp + lane] = v;
+        }
+        float m = lane < a.classes ? (a.parity == AET_PARITY_CPU ? v : (float)(int)v) : -INFINITY;
+        if (a.parity == AET_PARITY_CPU && lane >= a.classes) m = -FLT_MAX;
+        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float e = lane < a.classes ? expf(v / a.temp - m / a.temp) : 0.f;
+        float sum = e;
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        float err = 0.f;
+        if (lane < a.classes) {
+            const float q = e / sum;
+            a.p[(size_t)n * a.cp + lane] = q;
+            if (a.truth) {
+                const float t = a.truth[(size_t)n * a.cp + lane];
+                err = t ? -logf(q) : 0.f;
+                a.loss[(size_t)n * a.cp + lane] = err;
+                a.sm_delta[(size_t)n * a.cp + lane] = t - q;
+            }
+        }
+        for (int o = 16; o; o >>= 1) err += __shfl_xor_sync(0xffffffffu, err, o);
+        lsum += err;
+    }
+    if (lane == 0) warp_loss[warp] = lsum;
+    __syncthreads();
+    if (threadIdx.x == 0 && a.truth) {
+        float c = 0.f;
+        for (int w = 0; w < 32; ++w) c += warp_loss[w];
+        a.cost[0] = c;
+        a.cost[1] = c / a.N;
+    }
+}
+__global__ void __launch_bounds__(1024) head_backward_kernel(const HeadArgs a) {
+    __shared__ float part[32][33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float bsum = 0.f;
+    for (int n = warp; n < a.N; n += 32) {
+        if (lane < a.classes) {
+            const float d = a.loss_scale * a.sm_delta[(size_t)n * a.cp + lane];   // softmax backward into the avg-pool delta
+            a.avg_delta[(size_t)n * a.cp + lane] = d;
+            const float g = d / a.spatial;                                        // avg-pool backward into the conv delta
+            float *dst = a.conv_delta + (size_t)n * a.spatial * a.cp + lane;
+            for (int i = 0; i < a.spatial; ++i) { dst[(size_t)i * a.cp] = g; bsum += g; }
+        }
+    }
+    part[warp][lane] = bsum;
+    __syncthreads();
+    if (warp == 0 && lane < a.classes) {
+        float t = 0.f;
+        for (int w = 0; w < 32; ++w) t += part[w][lane];
+        a.bias_grad[lane] += t;
+    }
+}
+
 // ---------------------------------------------------------------------------- small utilities
 __global__ void axpy_kernel(float *y, const float *x, float a, size_t n4, int accumulate) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1081,6 +1160,31 @@ int k_softmax_forward(aet_layer *l, const float *x, const float *truth) {
         AET_TRY(aet_check_launch("softmax_cost"));
     }
     return AET_OK;
+}
+
+static HeadArgs make_head(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *truth) {
+    HeadArgs h = {};
+    h.y = conv->output->d; h.avg = avg->output->d; h.p = sm->output->d; h.sm_delta = sm->delta->d; h.loss = sm->loss;
+    h.truth = truth; h.cost = sm->cost_dev; h.avg_delta = avg->delta->d; h.conv_delta = conv->delta ? conv->delta->d : nullptr;
+    h.bias_grad = layer_bG(conv);
+    h.N = sm->batch; h.spatial = avg->h * avg->w; h.classes = sm->c; h.cp = sm->cp; h.parity = sm->ctx->parity;
+    h.temp = sm->temperature;
+    h.loss_scale = (sm->ctx->parity == AET_PARITY_MTCS && sm->net) ? sm->net->loss_scale : 1.0f;
+    return h;
+}
+int k_head_forward(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *truth) {
+    aet_context *ctx = sm->ctx;
+    HeadArgs h = make_head(conv, avg, sm, truth);
+    LaunchScope s(ctx, "head_avgpool_softmax_xent", 4.0 * conv->batch * conv->oh * conv->ow * conv->ocp + 24.0 * sm->batch * sm->c, 0);
+    head_forward_kernel<<<1, 1024, 0, ctx->stream>>>(h);
+    return aet_check_launch("head_avgpool_softmax_xent");
+}
+int k_head_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm) {
+    aet_context *ctx = sm->ctx;
+    HeadArgs h = make_head(conv, avg, sm, nullptr);
+    LaunchScope s(ctx, "head_backward", 4.0 * conv->batch * conv->oh * conv->ow * conv->ocp + 8.0 * sm->batch * sm->c, 0);
+    head_backward_kernel<<<1, 1024, 0, ctx->stream>>>(h);
+    return aet_check_launch("head_backward");
 }
 
 int k_axpy(aet_context *ctx, float *y, const float *x, float a, size_t n, int accumulate, const char *name) {

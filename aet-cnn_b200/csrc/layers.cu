@@ -299,6 +299,11 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
         return k_maxpool_forward(l, state.input->d);
     case AET_AVGPOOL:
         l->output->lazy_zero = false;
+        l->head_forward_pending = false;
+        if (l->head_softmax && state.input == l->head_softmax->head_conv->output) {
+            l->head_forward_pending = true;    // produced by the softmax layer's fused head kernel
+            return AET_OK;
+        }
         return k_avgpool_forward(l, state.input->d);
     case AET_SOFTMAX: {
         const float *truth = nullptr;
@@ -308,7 +313,16 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
             truth = state.truth->d;
         }
         l->cost_valid = false;
-        AET_TRY(k_softmax_forward(l, state.input->d, truth));
+        if (l->head_avg && l->head_avg->head_forward_pending && state.input == l->head_avg->output) {
+            l->head_avg->head_forward_pending = false;
+            AET_TRY(k_head_forward(l->head_conv, l->head_avg, l, truth));
+        } else {
+            if (l->head_avg && l->head_avg->head_forward_pending) {   // not the fused call pattern after all
+                l->head_avg->head_forward_pending = false;
+                AET_TRY(k_avgpool_forward(l->head_avg, l->head_conv->output->d));
+            }
+            AET_TRY(k_softmax_forward(l, state.input->d, truth));
+        }
         if (truth) l->delta->lazy_zero = false;
         return AET_OK;
     }
@@ -331,7 +345,9 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     switch (l->type) {
     case AET_CONVOLUTIONAL: {
         AET_TRY(check_input(l, state.input));
-        if (l->gather_pending && l->bn && l->fused_pool) {
+        if (l->head_backward_done) {
+            l->head_backward_done = false;    // delta and bias gradient came from the fused head kernel
+        } else if (l->gather_pending && l->bn && l->fused_pool) {
             // the max-pool's backward was deferred: gather its delta inside the BN backward kernels
             l->gather_pending = false;
             AET_TRY(k_bn_backward(l, l->fused_pool));
@@ -363,6 +379,7 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
         return AET_OK;
     case AET_AVGPOOL:
         if (!pd) return AET_OK;
+        if (l->head_backward_done) { l->head_backward_done = false; return AET_OK; }
         if (l->delta->lazy_zero) { AET_TRY(aet_tensor_zero(l->delta)); l->delta->lazy_zero = false; }
         AET_TRY(k_avgpool_backward(l, pd->d, pd->lazy_zero ? 0 : 1));
         pd->lazy_zero = false;
@@ -370,6 +387,15 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     case AET_SOFTMAX: {
         if (!pd) return AET_OK;
         if (pd->cp != l->cp) return fail_invalid("softmax backward: previous delta layout mismatch");
+        if (l->head_avg && pd == l->head_avg->delta && pd->lazy_zero && l->head_conv->delta && l->head_conv->delta->lazy_zero &&
+            !l->delta->lazy_zero) {
+            AET_TRY(k_head_backward(l->head_conv, l->head_avg, l));
+            l->head_avg->head_backward_done = true;
+            l->head_conv->head_backward_done = true;
+            pd->lazy_zero = false;
+            l->head_conv->delta->lazy_zero = false;
+            return AET_OK;
+        }
         // CPU path scales by 1, MTCS path by loss_scale (dnn/SoftMaxLayer.c:293-314)
         const float ls = (l->ctx->parity == AET_PARITY_MTCS && l->net) ? l->net->loss_scale : 1.0f;
         AET_TRY(k_axpy(l->ctx, pd->d, l->delta->d, ls, (size_t)l->batch * l->cp, pd->lazy_zero ? 0 : 1, "softmax_bwd"));

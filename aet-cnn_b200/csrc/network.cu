@@ -416,6 +416,14 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
             if (prev->type == AET_CONVOLUTIONAL && prev->bn) { prev->fused_pool = l; l->fused_into = prev; }
         }
         net->layers.push_back(l);
+        if (l->type == AET_SOFTMAX && net->layers.size() >= 3 && !getenv("AET_NO_FUSE")) {
+            aet_layer *avg = net->layers[net->layers.size() - 2], *cv = net->layers[net->layers.size() - 3];
+            if (avg->type == AET_AVGPOOL && cv->type == AET_CONVOLUTIONAL && !cv->bn && cv->act == AET_LINEAR && cv->delta &&
+                l->groups == 1 && l->c <= 32) {
+                l->head_conv = cv; l->head_avg = avg;
+                avg->head_softmax = l; cv->head_softmax = l;
+            }
+        }
         c = l->oc; h = l->oh; w = l->ow;
     }
     if (net->layers.empty()) { aet_set_error("cfg: no layers"); aet_network_destroy(net); return nullptr; }
