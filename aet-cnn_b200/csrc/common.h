@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/aet_b200.h"
+#include <utility>
 
 #define AET_STATUS_TIMEOUT 1
 
@@ -192,6 +193,36 @@ struct LaunchScope {
     }
 };
 int aet_check_launch(const char *what);
+
+// Every kernel of the library is launched with programmatic stream serialization: its CTAs may be
+// scheduled (and run their prologue: barrier setup, TMEM allocation, descriptor prefetch) while the
+// previous kernel of the stream drains.  The contract each kernel keeps: no global-memory access
+// before pdl_wait(), which returns once every earlier kernel of the stream has completed and its
+// writes are visible.  pdl_trigger() after the wait lets the next kernel start scheduling, so at
+// most one kernel waits behind the running one.  AET_NO_PDL=1 in the environment launches plainly.
+bool pdl_enabled();
+void pdl_skip_next();   // the next launch_k on this thread is a plain launch (after a cross-stream event wait)
+bool pdl_take_skip();
+template <typename... KArgs, typename... Args>
+inline void launch_k(cudaStream_t stream, dim3 grid, dim3 block, size_t smem, void (*kernel)(KArgs...), Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl_enabled() && !pdl_take_skip()) ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in aet_check_launch
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// the usual kernel opening: wait for the stream's earlier kernels, then let the next one schedule
+__device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_trigger(); }
+#endif
 int ctx_scratch(aet_context *ctx, size_t bytes, float **out);
 int ctx_staging(aet_context *ctx, size_t bytes);
 

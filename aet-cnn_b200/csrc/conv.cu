@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctl.tmem_base;
+    pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp < 4) {
@@ -434,6 +435,7 @@ constexpr int RED_ELEMS = 32, RED_LANES = 16;
 __global__ void __launch_bounds__(RED_ELEMS * RED_LANES)
 wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dw, size_t count4, int splits,
                     size_t split_stride, int accumulate) {
+    pdl_enter();
     __shared__ float4 sh[RED_LANES][RED_ELEMS];
     const int e = threadIdx.x % RED_ELEMS, sl = threadIdx.x / RED_ELEMS;
     const size_t i = (size_t)blockIdx.x * RED_ELEMS + e;
@@ -496,7 +498,7 @@ int launch_gather_nb(aet_context *ctx, const ConvArgs &a, dim3 grid, size_t smem
         attr_set = true;
     }
     LaunchScope scope(ctx, name, 0, flops);
-    conv_gather_kernel<KIND, NB><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(a);
+    launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_gather_kernel<KIND, NB>, a);
     return aet_check_launch(name);
 }
 
@@ -537,7 +539,7 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     a.out_ld = g.kp;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
     int r = tma_fd_rows<KIND_FPROP>(l, a, flops);
     if (r != 1) return r;   // 1 = shape not eligible
     r = tma_fprop(l, a, flops);
@@ -559,7 +561,7 @@ int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
     a.out_ld = g.cp;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
     int r = tma_fd_rows<KIND_DGRAD>(l, a, flops);
     if (r != 1) return r;
     r = tma_dgrad(l, a, flops);
@@ -579,7 +581,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
     a.k_total = g.N * g.OH * g.OW;
     a.out_ld = a.n_cols;
     const int m_tiles = (g.K + BM - 1) / BM;
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
     const size_t out_floats = (size_t)g.K * a.n_cols;
     {
         int rsplits = 0;
@@ -589,7 +591,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
         if (rr == AET_OK) {
             const size_t count4 = out_floats / 4;
             LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (rsplits + 1 + (accumulate ? 1 : 0)), 0);
-            wgrad_reduce_kernel<<<(unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, ctx->stream>>>(
+            launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel, 
                 rpartial, dw, count4, rsplits, out_floats, accumulate);
             return aet_check_launch("wgrad_reduce");
         }
@@ -627,7 +629,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
     {
         const size_t count4 = out_floats / 4;
         LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (splits + 1 + (accumulate ? 1 : 0)), 0);
-        wgrad_reduce_kernel<<<(unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, ctx->stream>>>(partial, dw, count4, splits,
+        launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel, partial, dw, count4, splits,
                                                                                         out_floats, accumulate);
         return aet_check_launch("wgrad_reduce");
     }

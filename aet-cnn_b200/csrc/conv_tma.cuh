@@ -140,6 +140,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctl.tmem_base;
+    pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp < 4) {
@@ -269,7 +270,7 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
         attr_set[KIND] = true;
     }
     LaunchScope scope(ctx, name, 0, flops);
-    conv_tma_kernel<KIND><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(*ma, *mb, t);
+    launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_tma_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);
 }
 

@@ -63,6 +63,7 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctl.tmem_base;
+    pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp < 4) {
@@ -201,7 +202,7 @@ int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_ou
     dim3 grid(m_tiles, g.S * t.col_groups, splits);
     {
         LaunchScope scope(ctx, "conv_wgrad_tma_rows", 0, flops);
-        conv_wgrad_rows_kernel<<<grid, NTHREADS, smem_bytes, ctx->stream>>>(*ma, *mb, t);
+        launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_wgrad_rows_kernel, *ma, *mb, t);
         AET_TRY(aet_check_launch("conv_wgrad_tma_rows"));
     }
     *splits_out = splits;
@@ -265,6 +266,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctl.tmem_base;
+    pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp < 4) {
@@ -350,7 +352,7 @@ template <int KIND>
 int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (!tma_common_ok(l) || getenv("AET_NO_ROWS")) return 1;
+    if (!tma_common_ok(l) || getenv("AET_NO_ROWS") || getenv(KIND == KIND_FPROP ? "AET_NO_ROWS_F" : "AET_NO_ROWS_D")) return 1;
     if (g.R < 2 || g.OH != g.H || g.OW != g.W) return 1;                 // same-size convolutions
     const int inner = KIND == KIND_FPROP ? g.cp : g.kp;
     if (KIND == KIND_DGRAD && !(g.kp % 32 == 0)) return 1;
@@ -361,28 +363,37 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     // that still gives a CTA to most SMs (wider tiles re-read the activations less often).
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     const int full = round_up(a.n_cols, 16);
-    int bn = 0;
     const int cands[4] = {full <= 256 ? full : 256, 128, 64, 32};
+    int bn = 0, mt = 1, stages = 0, n_tiles = 0;
+    uint32_t a_bytes = 0, b_tile = 0;
+    size_t stage = 0;
     for (int i = 0; i < 4 && !bn; ++i) {
         const int c = cands[i];
         if (c > full || (KIND == KIND_DGRAD && (c % 32 || g.cp % c))) continue;
-        if (m_tiles * ((a.n_cols + c - 1) / c) >= (ctx->sm_count * 3) / 5 || c <= 64) bn = c;
+        const int nt = (a.n_cols + c - 1) / c;
+        if (!(m_tiles * nt >= (ctx->sm_count * 3) / 5 || c <= 64)) continue;
+        // two pixel tiles per CTA when they are rows of one image and there are still enough CTAs
+        int m = 1;
+        if (bi == 1 && g.H % (2 * (int)bh) == 0 && 2 * c <= 512 && (m_tiles / 2) * nt >= (ctx->sm_count * 3) / 4 &&
+            !getenv("AET_NO_MT2"))
+            m = 2;
+        for (; m >= 1; --m) {
+            const uint32_t ab = (uint32_t)(m * (int)bh + g.R - 1) * bi * g.W * 128u;
+            const size_t st = (size_t)ab + (size_t)g.R * c * 128u;
+            int ns = (int)((200 * 1024) / st);
+            if (ns > 4) ns = 4;
+            if (ns >= 2 && st * ns >= (size_t)BM * (c + 4) * 4) {   // pipeline depth and room for the epilogue tile
+                bn = c; mt = m; stages = ns; n_tiles = nt; a_bytes = ab; b_tile = (uint32_t)c * 128u; stage = st;
+                break;
+            }
+        }
     }
     if (!bn) return 1;
-    const int n_tiles = (a.n_cols + bn - 1) / bn;
-    // two pixel tiles per CTA when they are rows of one image and there are still enough CTAs
-    int mt = 1;
-    if (bi == 1 && g.H % (2 * (int)bh) == 0 && 2 * bn <= 512 && (m_tiles / 2) * n_tiles >= (ctx->sm_count * 3) / 4 &&
-        !getenv("AET_NO_MT2"))
-        mt = 2;
+    // The large stages allow one CTA per SM.  Measured on 8x8 to 16x16 images at batch 128 and 256: while the
+    // grid fits one wave this kernel matches or beats the plain TMA kernel (dgrad by 20%); with a second,
+    // partial wave the plain kernel with its smaller stages and two CTAs per SM wins by up to 40%.
+    if (((m_tiles + mt - 1) / mt) * n_tiles > ctx->sm_count && !getenv("AET_ROWS_MULTI")) return 1;
     const int super_rows = mt * (int)bh + g.R - 1;
-    const uint32_t a_bytes = (uint32_t)super_rows * bi * g.W * 128u;
-    const uint32_t b_tile = (uint32_t)bn * 128u;
-    const size_t stage = (size_t)a_bytes + (size_t)g.R * b_tile;
-    int stages = (int)((200 * 1024) / stage);
-    if (stages > 4) stages = 4;
-    if (stages < 2) return 1;
-    if (stage * stages < (size_t)BM * (bn + 4) * 4) return 1;             // epilogue tile must fit
     const CUtensorMap *ma, *mb;
     const float *act = a.src_a;
     const int ac = inner;   // channels of the A tensor
@@ -426,7 +437,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     dim3 grid((m_tiles + mt - 1) / mt, n_tiles, 1);
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
     LaunchScope scope(ctx, name, 0, flops);
-    conv_fd_rows_kernel<KIND><<<grid, NTHREADS, smem_bytes, ctx->stream>>>(*ma, *mb, t);
+    launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);
 }
 

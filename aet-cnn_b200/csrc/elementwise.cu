@@ -132,6 +132,7 @@ struct ReduceArgs {
 
 template <int MODE, bool POOL = false>
 __global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
+    pdl_enter();
     __shared__ float4 sh1[TB];
     __shared__ float4 sh2[TB];
     int cv, pl;
@@ -228,6 +229,7 @@ __device__ __forceinline__ float sel(int id, int pos, float v) { return id == po
 
 template <bool APPLY>
 __global__ void __launch_bounds__(TB) bn_bwd_poolwin_kernel(const PoolWinArgs a) {
+    pdl_enter();
     __shared__ float4 sh1[TB];
     __shared__ float4 sh2[TB];
     const unsigned cvec = (unsigned)a.cp / 4;
@@ -306,6 +308,7 @@ struct FinalizeArgs {
 // and the scale / shift gradients.  MODE 2: bias gradient.
 template <int MODE>
 __global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
+    pdl_enter();
     // A block owns 32 channels (one coalesced 128-byte row of each partial).  Its 32 warps each take
     // every 32nd block's partial; the loads of a thread are independent and issued together, the sums
     // are formed in double in a fixed order (within the thread, then over the 32 warps).
@@ -390,6 +393,7 @@ struct ApplyArgs {
     CMap m;
 };
 __global__ void __launch_bounds__(TB) bn_apply_kernel(const ApplyArgs a) {
+    pdl_enter();
     int cv, pl;
     if (!cmap_thread(a.m, cv, pl)) return;
     const int c = cv * 4;
@@ -431,6 +435,7 @@ struct BwdApplyArgs {
 };
 template <bool POOL>
 __global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) {
+    pdl_enter();
     int cv, pl;
     if (!cmap_thread(a.m, cv, pl)) return;
     const int c = cv * 4;
@@ -471,6 +476,7 @@ __global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) 
 }
 
 __global__ void eval_inv_kernel(const float *rolling_variance, float *inv, int c, int cp, int parity) {
+    pdl_enter();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= cp) return;
     float v = 0.f;
@@ -481,6 +487,7 @@ __global__ void eval_inv_kernel(const float *rolling_variance, float *inv, int c
 }
 
 __global__ void copy_first_pixel_kernel(const float *x, float *shift, int cp) {
+    pdl_enter();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < cp) shift[i] = x[i];
 }
@@ -494,6 +501,7 @@ struct PoolArgs {
     long long total;   // N*OH*OW*cvec
 };
 __global__ void __launch_bounds__(TB) maxpool_fwd_kernel(const PoolArgs a) {
+    pdl_enter();
     const long long e64 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e64 >= a.total) return;
     const unsigned e = (unsigned)e64;          // element counts stay below 2^32
@@ -538,6 +546,7 @@ struct BnPoolArgs {
     int act;
 };
 __global__ void __launch_bounds__(TB) bn_pool_fwd_kernel(const BnPoolArgs b) {
+    pdl_enter();
     const PoolArgs &a = b.p;
     const long long e64 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e64 >= a.total) return;
@@ -591,6 +600,7 @@ struct PoolBwdArgs {
 // Gather form (mtcs/MtcsMaxPoolLayer.c:295-332): every input element adds the deltas of the
 // windows whose argmax it is.
 __global__ void __launch_bounds__(TB) maxpool_bwd_kernel(const PoolBwdArgs a) {
+    pdl_enter();
     const long long e64 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e64 >= a.total) return;
     const unsigned e = (unsigned)e64;
@@ -627,6 +637,7 @@ __global__ void __launch_bounds__(TB) maxpool_bwd_kernel(const PoolBwdArgs a) {
 
 // ---------------------------------------------------------------------------- global average pool
 __global__ void avgpool_fwd_kernel(const float *x, float *y, int N, int spatial, int cp) {
+    pdl_enter();
     int e = blockIdx.x * blockDim.x + threadIdx.x;
     const int cvec = cp / 4;
     if (e >= N * cvec) return;
@@ -641,6 +652,7 @@ __global__ void avgpool_fwd_kernel(const float *x, float *y, int N, int spatial,
     st4(y + (size_t)n * cp + cv * 4, s);
 }
 __global__ void avgpool_bwd_kernel(const float *delta, float *prev, long long total4, int spatial, int cp, int accumulate) {
+    pdl_enter();
     long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= total4) return;
     const int cvec = cp / 4;
@@ -667,6 +679,7 @@ struct SoftmaxArgs {
     float temp;
 };
 __global__ void __launch_bounds__(TB) softmax_kernel(const SoftmaxArgs a) {
+    pdl_enter();
     const int unit = blockIdx.x * (TB / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (unit >= a.units) return;
@@ -703,6 +716,7 @@ __global__ void __launch_bounds__(TB) softmax_kernel(const SoftmaxArgs a) {
 }
 __global__ void __launch_bounds__(1024) softmax_cost_kernel(const float *unit_loss, int units, float *cost, float inv_batch,
                                                             float *mean_loss) {
+    pdl_enter();
     __shared__ float sh[1024];
     float s = 0.f;
     for (int i = threadIdx.x; i < units; i += 1024) s += unit_loss[i];
@@ -735,6 +749,7 @@ struct HeadArgs {
     float temp, loss_scale;
 };
 __global__ void __launch_bounds__(1024) head_forward_kernel(const HeadArgs a) {
+    pdl_enter();
     __shared__ float warp_loss[32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float lsum = 0.f;
@@ -776,6 +791,7 @@ __global__ void __launch_bounds__(1024) head_forward_kernel(const HeadArgs a) {
     }
 }
 __global__ void __launch_bounds__(1024) head_backward_kernel(const HeadArgs a) {
+    pdl_enter();
     __shared__ float part[32][33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float bsum = 0.f;
@@ -799,6 +815,7 @@ __global__ void __launch_bounds__(1024) head_backward_kernel(const HeadArgs a) {
 
 // ---------------------------------------------------------------------------- small utilities
 __global__ void axpy_kernel(float *y, const float *x, float a, size_t n4, int accumulate) {
+    pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4) return;
     float4 v = ld4(x + i * 4);
@@ -810,10 +827,12 @@ __global__ void axpy_kernel(float *y, const float *x, float a, size_t n4, int ac
     st4(y + i * 4, v);
 }
 __global__ void fill_kernel(float *p, float v, size_t n4) {
+    pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n4) st4(p + i * 4, make_float4(v, v, v, v));
 }
-__global__ void step_counter_kernel(unsigned long long *ctr) { ctr[0] += 1ull; }
+__global__ void step_counter_kernel(unsigned long long *ctr) {
+    pdl_enter(); ctr[0] += 1ull; }
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -823,6 +842,7 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
 // Counter-based uniforms: u = top 24 bits of mix64(seed + step*A + (index+1)*B).
 __global__ void dropout_fwd_kernel(float *x, float *rnd, size_t n, int c, int cp, float prob, float scale,
                                    unsigned long long seed, const unsigned long long *step, int generate) {
+    pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float r;
@@ -837,6 +857,7 @@ __global__ void dropout_fwd_kernel(float *x, float *rnd, size_t n, int c, int cp
     x[i] = r < prob ? 0.f : x[i] * scale;
 }
 __global__ void dropout_bwd_kernel(float *d, const float *rnd, size_t n, float prob, float scale) {
+    pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     d[i] = rnd[i] < prob ? 0.f : d[i] * scale;
@@ -847,6 +868,7 @@ __global__ void dropout_bwd_kernel(float *d, const float *rnd, size_t n, float p
 // Same operation order as the three reference passes (U += -decay*B*W; W += lr/B*U; U *= momentum).
 __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float *G, const int *block_seg,
                                                        const float *seg_table, const float *hyper) {
+    pdl_enter();
     const int seg = block_seg[blockIdx.x];
     const float rate = hyper[0] * seg_table[2 * seg];
     const float momentum = hyper[1];
@@ -862,6 +884,7 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
     st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
 }
 __global__ void sgd_segment_kernel(float *W, float *U, float *G, size_t n4, float rate, float momentum, float decay_term) {
+    pdl_enter();
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
     if (i >= n4) return;
     i *= 4;
@@ -876,6 +899,7 @@ __global__ void sgd_segment_kernel(float *W, float *U, float *G, size_t n4, floa
 }
 
 __global__ void param_hash_kernel(const float *p, size_t n, unsigned long long *hash) {
+    pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     unsigned long long h = 0;
     if (i < n) h = mix64((unsigned long long)__float_as_uint(p[i]) ^ ((i + 1) * 0x9E3779B97F4A7C15ull));
@@ -916,6 +940,18 @@ ReducePlan plan_apply(aet_context *ctx, long long pixels, int cp) {
 
 }  // namespace
 
+bool pdl_enabled() {
+    static const bool on = []() { const char *e = getenv("AET_NO_PDL"); return !(e && *e && *e != '0'); }();
+    return on;
+}
+static thread_local bool g_pdl_skip = false;
+void pdl_skip_next() { g_pdl_skip = true; }
+bool pdl_take_skip() {
+    const bool s = g_pdl_skip;
+    g_pdl_skip = false;
+    return s;
+}
+
 int aet_check_launch(const char *what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -939,7 +975,7 @@ int k_bn_stats(aet_layer *l, int update_rolling) {
     a.pix_per_block = p.pix_per_block; a.m = p.m;
     {
         LaunchScope s(ctx, "bn_stats", (double)pixels * l->ocp * 4.0, 0);
-        reduce2_kernel<0><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        launch_k(ctx->stream, dim3(p.blocks, p.m.cslabs), TB, 0, reduce2_kernel<0>, a);
         AET_TRY(aet_check_launch("bn_stats"));
     }
     FinalizeArgs f = {};
@@ -948,7 +984,7 @@ int k_bn_stats(aet_layer *l, int update_rolling) {
     f.mean = l->mean; f.variance = l->variance; f.inv = l->inv_std;
     f.rolling_mean = l->rolling_mean; f.rolling_variance = l->rolling_variance;
     LaunchScope s(ctx, "bn_stats_finalize", 0, 0);
-    finalize_kernel<0><<<(l->ocp + 31) / 32, 1024, 0, ctx->stream>>>(f);
+    launch_k(ctx->stream, (l->ocp + 31) / 32, 1024, 0, finalize_kernel<0>, f);
     return aet_check_launch("bn_stats_finalize");
 }
 
@@ -958,7 +994,7 @@ int k_bn_apply(aet_layer *l, int use_rolling) {
     const long long pixels = (long long)l->batch * l->oh * l->ow;
     if (use_rolling) {
         LaunchScope s(ctx, "bn_eval_inv", 0, 0);
-        eval_inv_kernel<<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(l->rolling_variance, l->inv_std, l->oc, l->ocp,
+        launch_k(ctx->stream, (l->ocp + 127) / 128, 128, 0, eval_inv_kernel, l->rolling_variance, l->inv_std, l->oc, l->ocp,
                                                                         ctx->parity);
         AET_TRY(aet_check_launch("bn_eval_inv"));
     }
@@ -969,7 +1005,7 @@ int k_bn_apply(aet_layer *l, int use_rolling) {
     a.gamma = layer_s(l); a.beta = layer_b(l);
     a.act = l->act; a.cp = l->ocp; a.pixels = pixels; a.pix_per_block = p.pix_per_block; a.m = p.m;
     LaunchScope s(ctx, "bn_apply_act", (double)pixels * l->ocp * 8.0, 0);
-    bn_apply_kernel<<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+    launch_k(ctx->stream, dim3(p.blocks, p.m.cslabs), TB, 0, bn_apply_kernel, a);
     return aet_check_launch("bn_apply_act");
 }
 
@@ -987,7 +1023,7 @@ int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling) {
     aet_context *ctx = l->ctx;
     if (use_rolling) {
         LaunchScope s(ctx, "bn_eval_inv", 0, 0);
-        eval_inv_kernel<<<(l->ocp + 127) / 128, 128, 0, ctx->stream>>>(l->rolling_variance, l->inv_std, l->oc, l->ocp,
+        launch_k(ctx->stream, (l->ocp + 127) / 128, 128, 0, eval_inv_kernel, l->rolling_variance, l->inv_std, l->oc, l->ocp,
                                                                         ctx->parity);
         AET_TRY(aet_check_launch("bn_eval_inv"));
     }
@@ -1001,7 +1037,7 @@ int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling) {
     b.act = l->act;
     const double bytes = 4.0 * pool->batch * pool->h * pool->w * pool->cp + 8.0 * pool->batch * pool->oh * pool->ow * pool->cp;
     LaunchScope s(ctx, "bn_act_maxpool_fwd", bytes, 0);
-    bn_pool_fwd_kernel<<<(unsigned)((a.total + TB - 1) / TB), TB, 0, ctx->stream>>>(b);
+    launch_k(ctx->stream, (unsigned)((a.total + TB - 1) / TB), TB, 0, bn_pool_fwd_kernel, b);
     return aet_check_launch("bn_act_maxpool_fwd");
 }
 
@@ -1034,16 +1070,16 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
         AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
         w.partial = partial;
         LaunchScope s(ctx, "bn_bwd_reduce_poolwin", (double)pixels * l->ocp * 4.0 + pool_bytes, 0);
-        bn_bwd_poolwin_kernel<false><<<p.blocks, TB, 0, ctx->stream>>>(w);
+        launch_k(ctx->stream, p.blocks, TB, 0, bn_bwd_poolwin_kernel<false>, w);
         AET_TRY(aet_check_launch("bn_bwd_reduce_poolwin"));
     } else if (pool) {
         a.pool = make_pool_gather(pool);
         LaunchScope s(ctx, "bn_bwd_reduce_pool", (double)pixels * l->ocp * 4.0 + pool_bytes, 0);
-        reduce2_kernel<1, true><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        launch_k(ctx->stream, dim3(p.blocks, p.m.cslabs), TB, 0, reduce2_kernel<1, true>, a);
         AET_TRY(aet_check_launch("bn_bwd_reduce_pool"));
     } else {
         LaunchScope s(ctx, "bn_bwd_reduce", (double)pixels * l->ocp * 8.0, 0);
-        reduce2_kernel<1><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        launch_k(ctx->stream, dim3(p.blocks, p.m.cslabs), TB, 0, reduce2_kernel<1>, a);
         AET_TRY(aet_check_launch("bn_bwd_reduce"));
     }
     FinalizeArgs f = {};
@@ -1052,7 +1088,7 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     f.g_gamma = layer_sG(l); f.g_beta = layer_bG(l); f.coef = l->bwd_coef;
     {
         LaunchScope s(ctx, "bn_bwd_finalize", 0, 0);
-        finalize_kernel<1><<<(l->ocp + 31) / 32, 1024, 0, ctx->stream>>>(f);
+        launch_k(ctx->stream, (l->ocp + 31) / 32, 1024, 0, finalize_kernel<1>, f);
         AET_TRY(aet_check_launch("bn_bwd_finalize"));
     }
     ReducePlan q = plan_apply(ctx, pixels, l->ocp);
@@ -1063,17 +1099,17 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     if (window_major) {
         const int blocks = (int)((w.total + TB - 1) / TB) < 8 * ctx->sm_count ? (int)((w.total + TB - 1) / TB) : 8 * ctx->sm_count;
         LaunchScope s(ctx, "bn_bwd_apply_poolwin", (double)pixels * l->ocp * 8.0 + pool_bytes, 0);
-        bn_bwd_poolwin_kernel<true><<<blocks, TB, 0, ctx->stream>>>(w);
+        launch_k(ctx->stream, blocks, TB, 0, bn_bwd_poolwin_kernel<true>, w);
         return aet_check_launch("bn_bwd_apply_poolwin");
     }
     if (pool) {
         b.pool = make_pool_gather(pool);
         LaunchScope s(ctx, "bn_bwd_apply_pool", (double)pixels * l->ocp * 8.0 + pool_bytes, 0);
-        bn_bwd_apply_kernel<true><<<dim3(q.blocks, q.m.cslabs), TB, 0, ctx->stream>>>(b);
+        launch_k(ctx->stream, dim3(q.blocks, q.m.cslabs), TB, 0, bn_bwd_apply_kernel<true>, b);
         return aet_check_launch("bn_bwd_apply_pool");
     }
     LaunchScope s(ctx, "bn_bwd_apply", (double)pixels * l->ocp * 12.0, 0);
-    bn_bwd_apply_kernel<false><<<dim3(q.blocks, q.m.cslabs), TB, 0, ctx->stream>>>(b);
+    launch_k(ctx->stream, dim3(q.blocks, q.m.cslabs), TB, 0, bn_bwd_apply_kernel<false>, b);
     return aet_check_launch("bn_bwd_apply");
 }
 
@@ -1089,13 +1125,13 @@ int k_bias_act_backward(aet_layer *l) {
     a.pixels = pixels; a.cp = l->ocp; a.pix_per_block = p.pix_per_block; a.m = p.m;
     {
         LaunchScope s(ctx, "bias_act_bwd", (double)pixels * l->ocp * (l->act == AET_LINEAR ? 4.0 : 12.0), 0);
-        reduce2_kernel<2><<<dim3(p.blocks, p.m.cslabs), TB, 0, ctx->stream>>>(a);
+        launch_k(ctx->stream, dim3(p.blocks, p.m.cslabs), TB, 0, reduce2_kernel<2>, a);
         AET_TRY(aet_check_launch("bias_act_bwd"));
     }
     FinalizeArgs f = {};
     f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels; f.g_beta = layer_bG(l);
     LaunchScope s(ctx, "bias_bwd_finalize", 0, 0);
-    finalize_kernel<2><<<(l->ocp + 31) / 32, 1024, 0, ctx->stream>>>(f);
+    launch_k(ctx->stream, (l->ocp + 31) / 32, 1024, 0, finalize_kernel<2>, f);
     return aet_check_launch("bias_bwd_finalize");
 }
 
@@ -1108,7 +1144,7 @@ int k_maxpool_forward(aet_layer *l, const float *x) {
     a.total = (long long)l->batch * l->oh * l->ow * (l->cp / 4);
     const double bytes = 4.0 * l->batch * l->h * l->w * l->cp + 8.0 * l->batch * l->oh * l->ow * l->cp;
     LaunchScope s(ctx, "maxpool_fwd", bytes, 0);
-    maxpool_fwd_kernel<<<(unsigned)((a.total + TB - 1) / TB), TB, 0, ctx->stream>>>(a);
+    launch_k(ctx->stream, (unsigned)((a.total + TB - 1) / TB), TB, 0, maxpool_fwd_kernel, a);
     return aet_check_launch("maxpool_fwd");
 }
 
@@ -1121,7 +1157,7 @@ int k_maxpool_backward(aet_layer *l, float *prev_delta, int accumulate) {
     a.total = (long long)l->batch * l->h * l->w * (l->cp / 4);
     const double bytes = 8.0 * l->batch * l->oh * l->ow * l->cp + (accumulate ? 8.0 : 4.0) * l->batch * l->h * l->w * l->cp;
     LaunchScope s(ctx, "maxpool_bwd", bytes, 0);
-    maxpool_bwd_kernel<<<(unsigned)((a.total + TB - 1) / TB), TB, 0, ctx->stream>>>(a);
+    launch_k(ctx->stream, (unsigned)((a.total + TB - 1) / TB), TB, 0, maxpool_bwd_kernel, a);
     return aet_check_launch("maxpool_bwd");
 }
 
@@ -1129,7 +1165,7 @@ int k_avgpool_forward(aet_layer *l, const float *x) {
     aet_context *ctx = l->ctx;
     const int total = l->batch * (l->cp / 4);
     LaunchScope s(ctx, "avgpool_fwd", 4.0 * l->batch * l->h * l->w * l->cp + 4.0 * l->batch * l->cp, 0);
-    avgpool_fwd_kernel<<<(total + 127) / 128, 128, 0, ctx->stream>>>(x, l->output->d, l->batch, l->h * l->w, l->cp);
+    launch_k(ctx->stream, (total + 127) / 128, 128, 0, avgpool_fwd_kernel, x, l->output->d, l->batch, l->h * l->w, l->cp);
     return aet_check_launch("avgpool_fwd");
 }
 
@@ -1137,7 +1173,7 @@ int k_avgpool_backward(aet_layer *l, float *prev_delta, int accumulate) {
     aet_context *ctx = l->ctx;
     const long long total4 = (long long)l->batch * l->h * l->w * (l->cp / 4);
     LaunchScope s(ctx, "avgpool_bwd", (accumulate ? 8.0 : 4.0) * l->batch * l->h * l->w * l->cp + 4.0 * l->batch * l->cp, 0);
-    avgpool_bwd_kernel<<<(unsigned)((total4 + TB - 1) / TB), TB, 0, ctx->stream>>>(l->delta->d, prev_delta, total4,
+    launch_k(ctx->stream, (unsigned)((total4 + TB - 1) / TB), TB, 0, avgpool_bwd_kernel, l->delta->d, prev_delta, total4,
                                                                                    l->h * l->w, l->cp, accumulate);
     return aet_check_launch("avgpool_bwd");
 }
@@ -1150,13 +1186,13 @@ int k_softmax_forward(aet_layer *l, const float *x, const float *truth) {
     a.parity = ctx->parity; a.temp = l->temperature;
     {
         LaunchScope s(ctx, "softmax_xent", 20.0 * l->batch * l->c, 0);
-        softmax_kernel<<<(a.units + TB / 32 - 1) / (TB / 32), TB, 0, ctx->stream>>>(a);
+        launch_k(ctx->stream, (a.units + TB / 32 - 1) / (TB / 32), TB, 0, softmax_kernel, a);
         AET_TRY(aet_check_launch("softmax_xent"));
     }
     if (truth) {
         float *mean_loss = l->net ? l->cost_dev + 1 : nullptr;
         LaunchScope s(ctx, "softmax_cost", 0, 0);
-        softmax_cost_kernel<<<1, 1024, 0, ctx->stream>>>(l->sample_loss, a.units, l->cost_dev, 1.0f / l->batch, mean_loss);
+        launch_k(ctx->stream, 1, 1024, 0, softmax_cost_kernel, l->sample_loss, a.units, l->cost_dev, 1.0f / l->batch, mean_loss);
         AET_TRY(aet_check_launch("softmax_cost"));
     }
     return AET_OK;
@@ -1176,34 +1212,34 @@ int k_head_forward(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *
     aet_context *ctx = sm->ctx;
     HeadArgs h = make_head(conv, avg, sm, truth);
     LaunchScope s(ctx, "head_avgpool_softmax_xent", 4.0 * conv->batch * conv->oh * conv->ow * conv->ocp + 24.0 * sm->batch * sm->c, 0);
-    head_forward_kernel<<<1, 1024, 0, ctx->stream>>>(h);
+    launch_k(ctx->stream, 1, 1024, 0, head_forward_kernel, h);
     return aet_check_launch("head_avgpool_softmax_xent");
 }
 int k_head_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm) {
     aet_context *ctx = sm->ctx;
     HeadArgs h = make_head(conv, avg, sm, nullptr);
     LaunchScope s(ctx, "head_backward", 4.0 * conv->batch * conv->oh * conv->ow * conv->ocp + 8.0 * sm->batch * sm->c, 0);
-    head_backward_kernel<<<1, 1024, 0, ctx->stream>>>(h);
+    launch_k(ctx->stream, 1, 1024, 0, head_backward_kernel, h);
     return aet_check_launch("head_backward");
 }
 
 int k_axpy(aet_context *ctx, float *y, const float *x, float a, size_t n, int accumulate, const char *name) {
     const size_t n4 = n / 4;
     LaunchScope s(ctx, name, (accumulate ? 12.0 : 8.0) * n, 0);
-    axpy_kernel<<<(unsigned)((n4 + TB - 1) / TB), TB, 0, ctx->stream>>>(y, x, a, n4, accumulate);
+    launch_k(ctx->stream, (unsigned)((n4 + TB - 1) / TB), TB, 0, axpy_kernel, y, x, a, n4, accumulate);
     return aet_check_launch(name);
 }
 
 int k_fill(aet_context *ctx, float *p, float v, size_t n) {
     const size_t n4 = n / 4;
     LaunchScope s(ctx, "fill", 4.0 * n, 0);
-    fill_kernel<<<(unsigned)((n4 + TB - 1) / TB), TB, 0, ctx->stream>>>(p, v, n4);
+    launch_k(ctx->stream, (unsigned)((n4 + TB - 1) / TB), TB, 0, fill_kernel, p, v, n4);
     return aet_check_launch("fill");
 }
 
 int k_step_counter(aet_context *ctx, unsigned long long *ctr) {
     LaunchScope s(ctx, "step_counter", 0, 0);
-    step_counter_kernel<<<1, 1, 0, ctx->stream>>>(ctr);
+    launch_k(ctx->stream, 1, 1, 0, step_counter_kernel, ctr);
     return aet_check_launch("step_counter");
 }
 
@@ -1211,7 +1247,7 @@ int k_dropout_forward(aet_layer *l, float *x, int generate) {
     aet_context *ctx = l->ctx;
     const size_t n = (size_t)l->batch * l->h * l->w * l->cp;
     LaunchScope s(ctx, "dropout_fwd", 12.0 * n, 0);
-    dropout_fwd_kernel<<<(unsigned)((n + TB - 1) / TB), TB, 0, ctx->stream>>>(x, l->rnd, n, l->c, l->cp, l->probability,
+    launch_k(ctx->stream, (unsigned)((n + TB - 1) / TB), TB, 0, dropout_fwd_kernel, x, l->rnd, n, l->c, l->cp, l->probability,
                                                                              1.f / (1.f - l->probability), l->seed,
                                                                              l->step_dev, generate);
     return aet_check_launch("dropout_fwd");
@@ -1221,7 +1257,7 @@ int k_dropout_backward(aet_layer *l, float *delta) {
     aet_context *ctx = l->ctx;
     const size_t n = (size_t)l->batch * l->h * l->w * l->cp;
     LaunchScope s(ctx, "dropout_bwd", 12.0 * n, 0);
-    dropout_bwd_kernel<<<(unsigned)((n + TB - 1) / TB), TB, 0, ctx->stream>>>(delta, l->rnd, n, l->probability,
+    launch_k(ctx->stream, (unsigned)((n + TB - 1) / TB), TB, 0, dropout_bwd_kernel, delta, l->rnd, n, l->probability,
                                                                              1.f / (1.f - l->probability));
     return aet_check_launch("dropout_bwd");
 }
@@ -1230,21 +1266,21 @@ int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, 
                   float decay_term) {
     const size_t n4 = count / 4;
     LaunchScope s(ctx, "sgd_segment", 24.0 * count, 0);
-    sgd_segment_kernel<<<(unsigned)((n4 + TB - 1) / TB), TB, 0, ctx->stream>>>(W, U, G, n4, lr_over_b, momentum, decay_term);
+    launch_k(ctx->stream, (unsigned)((n4 + TB - 1) / TB), TB, 0, sgd_segment_kernel, W, U, G, n4, lr_over_b, momentum, decay_term);
     return aet_check_launch("sgd_segment");
 }
 
 int k_sgd_arena(aet_network *net) {
     aet_context *ctx = net->ctx;
     LaunchScope s(ctx, "sgd_momentum", 24.0 * net->arena.used, 0);
-    sgd_arena_kernel<<<net->n_blocks, TB, 0, ctx->stream>>>(net->arena.W, net->arena.U, net->arena.G, net->block_seg,
+    launch_k(ctx->stream, net->n_blocks, TB, 0, sgd_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->block_seg,
                                                            net->seg_table, net->hyper_dev);
     return aet_check_launch("sgd_momentum");
 }
 
 int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev) {
     LaunchScope s(ctx, "param_hash", 4.0 * count, 0);
-    param_hash_kernel<<<(unsigned)((count + TB - 1) / TB), TB, 0, ctx->stream>>>(p, count,
+    launch_k(ctx->stream, (unsigned)((count + TB - 1) / TB), TB, 0, param_hash_kernel, p, count,
                                                                                 reinterpret_cast<unsigned long long *>(hash_dev));
     return aet_check_launch("param_hash");
 }
@@ -1316,10 +1352,10 @@ extern "C" int aet_backward_bias_static(const float *delta, float *bias_updates,
     a.delta = const_cast<float *>(delta);          // linear activation: the kernel does not write delta
     a.partial = st.scratch; a.act = AET_LINEAR;
     a.pixels = pixels; a.cp = channels; a.pix_per_block = p.pix_per_block; a.m = p.m;
-    reduce2_kernel<2><<<dim3(p.blocks, p.m.cslabs), TB, 0, stream>>>(a);
+    launch_k(stream, dim3(p.blocks, p.m.cslabs), TB, 0, reduce2_kernel<2>, a);
     AET_TRY(aet_check_launch("backward_bias_static (partials)"));
     FinalizeArgs f = {};
     f.partial = st.scratch; f.blocks = p.blocks; f.cp = channels; f.c = channels; f.m = pixels; f.g_beta = bias_updates;
-    finalize_kernel<2><<<(channels + 31) / 32, 1024, 0, stream>>>(f);
+    launch_k(stream, (channels + 31) / 32, 1024, 0, finalize_kernel<2>, f);
     return aet_check_launch("backward_bias_static (finalize)");
 }

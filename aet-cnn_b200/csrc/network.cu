@@ -253,6 +253,7 @@ int net_backward(aet_network *net, aet_state state) {
         if (pend_hi > pend_lo) AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
         AET_CUDA(cudaEventRecord(net->ev_comm_done, net->comm_stream));
         AET_CUDA(cudaStreamWaitEvent(net->ctx->stream, net->ev_comm_done, 0));
+        pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
     }
     return AET_OK;
 }

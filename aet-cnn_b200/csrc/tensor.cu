@@ -25,6 +25,7 @@ namespace {
 // NCHW (dense, c channels) <-> NHWC (cp channels); pad channels are written as zero.
 __global__ void nchw_to_nhwc_kernel(const float *__restrict__ src, float *__restrict__ dst, int n, int c, int h, int w,
                                     int cp) {
+    pdl_enter();
     size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)n * h * w * cp;
     if (e >= total) return;
@@ -37,6 +38,7 @@ __global__ void nchw_to_nhwc_kernel(const float *__restrict__ src, float *__rest
 }
 __global__ void nhwc_to_nchw_kernel(const float *__restrict__ src, float *__restrict__ dst, int n, int c, int h, int w,
                                     int cp) {
+    pdl_enter();
     size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)n * c * h * w;
     if (e >= total) return;
@@ -255,7 +257,7 @@ int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int
     }
     const size_t total = (size_t)n * h * w * cp;
     ctx->launches++;
-    nchw_to_nhwc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(ctx->staging, dev_nhwc, n, c, h, w, cp);
+    launch_k(ctx->stream, (unsigned)((total + 255) / 256), 256, 0, nchw_to_nhwc_kernel, ctx->staging, dev_nhwc, n, c, h, w, cp);
     AET_TRY(aet_check_launch("nchw_to_nhwc"));
     if (!async_pinned) AET_CUDA(cudaStreamSynchronize(ctx->stream));
     return AET_OK;
@@ -265,7 +267,7 @@ int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int
 int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp) {
     const size_t total = (size_t)n * h * w * cp;
     ctx->launches++;
-    nchw_to_nhwc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(dev_nchw, dev_nhwc, n, c, h, w, cp);
+    launch_k(ctx->stream, (unsigned)((total + 255) / 256), 256, 0, nchw_to_nhwc_kernel, dev_nchw, dev_nhwc, n, c, h, w, cp);
     return aet_check_launch("nchw_to_nhwc");
 }
 
@@ -274,7 +276,7 @@ int tensor_download_nchw(aet_context *ctx, const float *dev_nhwc, float *host, i
     if (dense == 0) return AET_OK;
     AET_TRY(ctx_staging(ctx, dense * sizeof(float)));
     ctx->launches++;
-    nhwc_to_nchw_kernel<<<(unsigned)((dense + 255) / 256), 256, 0, ctx->stream>>>(dev_nhwc, ctx->staging, n, c, h, w, cp);
+    launch_k(ctx->stream, (unsigned)((dense + 255) / 256), 256, 0, nhwc_to_nchw_kernel, dev_nhwc, ctx->staging, n, c, h, w, cp);
     AET_TRY(aet_check_launch("nhwc_to_nchw"));
     AET_CUDA(cudaMemcpyAsync(host, ctx->staging, dense * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     AET_CUDA(cudaStreamSynchronize(ctx->stream));

@@ -48,6 +48,15 @@ def load_package():
     return mod
 
 
+# Dense TF32 peak of this pool's B200, measured with a one-off cuBLAS TF32 8192^3 matmul probe
+# (692.3 TFLOP/s best of 10, 624.4 over a 40-launch loop); the driver-written MEASURED_PEAKS.json
+# records HBM and BF16 only.
+TF32_PEAK_TFLOPS = 692.3
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of the same
+# workload (profiles/), keyed by kernel label; null when the dominant kernel has no capture yet.
+NCU_TRAFFIC_BYTES = {}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -299,12 +308,13 @@ def main():
     top = table[0]
     avg_s = top["total_ms"] / top["launches"] / 1000.0
     if top["algo_flops"] > 0:
-        roof = dict(bound="tensor", achieved=top["algo_flops"] / avg_s / 1e12, peak=peaks["bf16_tflops"] / 2.0,
-                    unit="TFLOP/s", peak_source=peaks["source"] + " bf16 cuBLAS burst / 2 (no TF32 figure recorded)")
+        roof = dict(bound="tensor", achieved=top["algo_flops"] / avg_s / 1e12, peak=TF32_PEAK_TFLOPS, unit="TFLOP/s",
+                    peak_source="measured cuBLAS TF32 8192^3 burst on this pool (bf16 burst in MEASURED_PEAKS.json: %.0f)"
+                                % peaks["bf16_tflops"])
     else:
         roof = dict(bound="hbm", achieved=top["algo_bytes"] / avg_s / 1e9, peak=peaks["hbm_gbs"], unit="GB/s",
                     peak_source=peaks["source"] + " copy bandwidth")
-    roof.update(frac=roof["achieved"] / roof["peak"], traffic=None, kernel=top["name"],
+    roof.update(frac=roof["achieved"] / roof["peak"], traffic=NCU_TRAFFIC_BYTES.get(top["name"]), kernel=top["name"],
                 share_of_step=top["total_ms"] / total_kernel_ms, avg_us=avg_s * 1e6)
     kernels = [dict(name=r["name"], launches=r["launches"], avg_us=1000.0 * r["total_ms"] / r["launches"],
                     share=r["total_ms"] / total_kernel_ms,
