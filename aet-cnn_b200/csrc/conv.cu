@@ -108,16 +108,21 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
             *reinterpret_cast<float4 *>(mine + cc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
     }
     __syncwarp();
-    for (int c = lane * 4; c < bn; c += 128) {
+    // tiles that span several small images order their rows (h, image, w): each lane maps one row to
+    // its pixel index once (the divisions cost more than the stores), the row loop broadcasts it
+    int my_grow = warp * 32 + lane;
+    if (map_bi > 1) my_grow = ((my_grow / map_w) % map_bi) * map_pix + (my_grow / (map_bi * map_w)) * map_w + my_grow % map_w;
+    for (int c0 = 0; c0 < bn; c0 += 128) {
+        const int c = c0 + lane * 4;
         const int col = col_base + c;
-        if (col >= n_cols) continue;
+        const bool active = c < bn && col < n_cols;
         float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (FPROP && bias) b = ldg4(bias + col);
+        if (FPROP && bias && active) b = ldg4(bias + col);
         for (int r = 0; r < 32; ++r) {
             const int row = warp * 32 + r;
-            // tiles that span several small images order their rows (h, image, w): map to the pixel index
-            const int grow = map_bi > 1 ? ((row / map_w) % map_bi) * map_pix + (row / (map_bi * map_w)) * map_w + row % map_w : row;
+            const int grow = __shfl_sync(0xffffffffu, my_grow, r);
             if (grow >= rows_valid) { if (map_bi > 1) continue; else break; }
+            if (!active) continue;
             float4 o = *reinterpret_cast<const float4 *>(tile + (size_t)row * pitch + c);
             if (FPROP) {
                 o.x = apply_act(o.x + b.x, act); o.y = apply_act(o.y + b.y, act);

@@ -334,16 +334,35 @@ __global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
     }
     sh1[part][cl] = s1;
     sh2[part][cl] = s2;
+    // the finishing warp's per-channel operands are requested before the barrier, off the critical path
+    float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+    const bool live = part == 0 && c < a.c;
+    if (live) {
+        if (MODE == 0) {
+            p0 = a.shift[c];
+            if (a.update_rolling) { p1 = a.rolling_mean[c]; p2 = a.rolling_variance[c]; }
+        } else if (MODE == 1) {
+            p0 = a.variance[c]; p1 = a.gamma[c]; p2 = a.inv[c]; p3 = a.g_gamma[c];
+        } else {
+            p0 = a.g_beta[c];
+        }
+    }
     __syncthreads();
     if (part != 0 || c >= a.cp) return;
-    for (int q = 1; q < 32; ++q) { s1 += sh1[q][cl]; s2 += sh2[q][cl]; }
+    {   // fixed-order sum of the 32 warp sums in four independent chains
+        double t1[4] = {s1, 0.0, 0.0, 0.0}, t2[4] = {s2, 0.0, 0.0, 0.0};
+#pragma unroll
+        for (int q = 1; q < 32; ++q) { t1[q & 3] += sh1[q][cl]; t2[q & 3] += sh2[q][cl]; }
+        s1 = (t1[0] + t1[1]) + (t1[2] + t1[3]);
+        s2 = (t2[0] + t2[1]) + (t2[2] + t2[3]);
+    }
     const double m = (double)a.m;
     if (MODE == 0) {
         if (c >= a.c) { a.mean[c] = 0.f; a.variance[c] = 0.f; a.inv[c] = 0.f; return; }
         const double mean_sh = s1 / m;
         double ss = s2 - s1 * mean_sh;   // sum (x - mean)^2
         if (ss < 0.0) ss = 0.0;
-        const float mean = (float)(mean_sh + (double)a.shift[c]);
+        const float mean = (float)(mean_sh + (double)p0);
         float var, inv;
         if (a.parity == AET_PARITY_CPU) {
             var = (float)(ss / (m - 1.0));
@@ -355,31 +374,35 @@ __global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
         a.mean[c] = mean; a.variance[c] = var; a.inv[c] = inv;
         if (a.update_rolling) {
             const float keep = a.parity == AET_PARITY_CPU ? .9f : .99f, add = a.parity == AET_PARITY_CPU ? .1f : .01f;
-            float rm = a.rolling_mean[c] * keep; rm += add * mean;
-            float rv = a.rolling_variance[c] * keep; rv += add * var;
+            float rm = p1 * keep; rm += add * mean;
+            float rv = p2 * keep; rv += add * var;
             a.rolling_mean[c] = rm; a.rolling_variance[c] = rv;
         }
     } else if (MODE == 1) {
         if (c >= a.c) { a.coef[c] = 0.f; a.coef[a.cp + c] = 0.f; a.coef[2 * a.cp + c] = 0.f; return; }
-        const float var = a.variance[c], gam = a.gamma[c];
+        const float var = p0, gam = p1;
         const float S1 = (float)s1, S2 = (float)s2;
-        a.g_gamma[c] += S2 * a.inv[c];
+        a.g_gamma[c] = p3 + S2 * p2;
         float md, vd, k1;
+        // v^(-3/2) is formed as 1 / (v * sqrt(v)) in double: it agrees with pow() to the last few bits of
+        // the double, far below the float the product is rounded to, and costs a fraction of pow()
         if (a.parity == AET_PARITY_CPU) {
-            md = (float)((double)(gam * S1) * (-1. / sqrt((double)(var + .00001f))));
-            vd = (float)((double)(gam * S2) * (-.5 * pow((double)(var + .00001f), (double)(float)(-3. / 2.))));
-            k1 = (float)(1. / sqrt((double)(var + .00001f)));
+            const double v = (double)(var + .00001f), rs = sqrt(v);
+            md = (float)((double)(gam * S1) * (-1. / rs));
+            vd = (float)((double)(gam * S2) * (-.5 / (v * rs)));
+            k1 = (float)(1. / rs);
         } else {
             a.g_beta[c] += S1;
-            md = (gam * S1) * (-1.f / sqrtf(var + .000001f));
-            vd = (float)((double)(gam * S2) * (-.5 * (double)powf(var + .000001f, (float)(-3. / 2.))));
+            const float v = var + .000001f;
+            md = (gam * S1) * (-1.f / sqrtf(v));
+            vd = (float)((double)(gam * S2) * (-.5 * (double)(1.f / (v * sqrtf(v)))));
             k1 = 1.f / (sqrtf(var) + .000001f);
         }
         a.coef[c] = gam * k1;
         a.coef[a.cp + c] = (float)((double)vd * 2. / m);
         a.coef[2 * a.cp + c] = (float)((double)md / m);
     } else {
-        if (c < a.c) a.g_beta[c] += (float)s1;
+        if (c < a.c) a.g_beta[c] = p0 + (float)s1;
     }
 }
 
@@ -753,14 +776,27 @@ __global__ void __launch_bounds__(1024) head_forward_kernel(const HeadArgs a) {
     __shared__ float warp_loss[32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float lsum = 0.f;
-    for (int n = warp; n < a.N; n += 32) {
+    // Phase 1: the average pool with one (sample, class) pair per thread, so that the whole block has
+    // its loads in flight at once; the pixels of a pair are summed in index order as the layer does.
+    for (int e = threadIdx.x; e < a.N * a.cp; e += 1024) {
+        const int n = e / a.cp, c = e - n * a.cp;
+        if (c >= a.classes) continue;
+        const float *src = a.y + (size_t)n * a.spatial * a.cp + c;
         float v = 0.f;
-        if (lane < a.classes) {
-            const float *src = a.y + (size_t)n * a.spatial * a.cp + lane;
-            for (int i = 0; i < a.spatial; ++i) v += src[(size_t)i * a.cp];
-            v /= a.spatial;
-            a.avg[(size_t)n * a.cp + lane] = v;
+        int i = 0;
+        for (; i + 8 <= a.spatial; i += 8) {
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = src[(size_t)(i + u) * a.cp];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v += t[u];
         }
+        for (; i < a.spatial; ++i) v += src[(size_t)i * a.cp];
+        a.avg[e] = v / a.spatial;
+    }
+    __syncthreads();   // the block's own global writes are visible to it after the barrier
+    for (int n = warp; n < a.N; n += 32) {
+        const float v = lane < a.classes ? a.avg[(size_t)n * a.cp + lane] : 0.f;
         float m = lane < a.classes ? (a.parity == AET_PARITY_CPU ? v : (float)(int)v) : -INFINITY;
         if (a.parity == AET_PARITY_CPU && lane >= a.classes) m = -FLT_MAX;
         for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
