@@ -95,40 +95,59 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
                                                   const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0) {
     const int pitch = bn + 4;
     float *mine = tile + (size_t)(warp * 32 + lane) * pitch;
-    for (int cc = 0; cc < bn; cc += 16) {
-        float v[16];
+    // TMEM -> shared memory, 32 columns (two loads in flight) per wait
+    for (int cc = 0; cc < bn; cc += 32) {
+        uint32_t v[32];
+        const bool second = cc + 16 < bn;
         if (have_acc) {
-            tmem_ld16(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
+            tmem_ld16_issue(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
+            if (second) tmem_ld16_issue(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc + 16), v + 16);
+            tmem_ld_wait();
         } else {
 #pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] = 0.f;
+            for (int q = 0; q < 32; ++q) v[q] = 0u;
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<float4 *>(mine + cc + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+        for (int q = 0; q < 8; ++q)
+            if (q < 4 || second)
+                *reinterpret_cast<uint4 *>(mine + cc + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
     }
     __syncwarp();
     // tiles that span several small images order their rows (h, image, w): each lane maps one row to
-    // its pixel index once (the divisions cost more than the stores), the row loop broadcasts it
+    // its pixel index once (the divisions cost more than the stores) and the others fetch it by shuffle
     int my_grow = warp * 32 + lane;
     if (map_bi > 1) my_grow = ((my_grow / map_w) % map_bi) * map_pix + (my_grow / (map_bi * map_w)) * map_w + my_grow % map_w;
+    // shared memory -> global: a store instruction covers whole rows, 32 / lpr of them when the tile is
+    // narrower than 128 columns; four rows are read before they are written so that the latencies overlap
+    const int lpr = bn >= 128 ? 32 : bn / 4;          // lanes per row (bn is a multiple of 16)
+    const int rpi = 32 / lpr;                         // rows per instruction
+    const int sub = lane / lpr, lcol = (lane - sub * lpr) * 4;
     for (int c0 = 0; c0 < bn; c0 += 128) {
-        const int c = c0 + lane * 4;
+        const int c = c0 + lcol;
         const int col = col_base + c;
-        const bool active = c < bn && col < n_cols;
+        const bool active = c < bn && col < n_cols && sub < rpi;
         float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
         if (FPROP && bias && active) b = ldg4(bias + col);
-        for (int r = 0; r < 32; ++r) {
-            const int row = warp * 32 + r;
-            const int grow = __shfl_sync(0xffffffffu, my_grow, r);
-            if (grow >= rows_valid) { if (map_bi > 1) continue; else break; }
-            if (!active) continue;
-            float4 o = *reinterpret_cast<const float4 *>(tile + (size_t)row * pitch + c);
-            if (FPROP) {
-                o.x = apply_act(o.x + b.x, act); o.y = apply_act(o.y + b.y, act);
-                o.z = apply_act(o.z + b.z, act); o.w = apply_act(o.w + b.w, act);
+        for (int r0 = 0; r0 < 32; r0 += 4 * rpi) {
+            float4 o[4];
+            int grow[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int r = (r0 + u * rpi + sub) & 31;
+                grow[u] = __shfl_sync(0xffffffffu, my_grow, r);
+                if (r0 + u * rpi + sub >= 32) grow[u] = rows_valid;   // past the warp's rows (lpr not a divisor of 32)
+                o[u] = *reinterpret_cast<const float4 *>(tile + (size_t)(warp * 32 + r) * pitch + c * (active ? 1 : 0));
             }
-            *reinterpret_cast<float4 *>(out + (size_t)grow * out_ld + col) = o;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (!active || grow[u] >= rows_valid) continue;
+                float4 v = o[u];
+                if (FPROP) {
+                    v.x = apply_act(v.x + b.x, act); v.y = apply_act(v.y + b.y, act);
+                    v.z = apply_act(v.z + b.z, act); v.w = apply_act(v.w + b.w, act);
+                }
+                *reinterpret_cast<float4 *>(out + (size_t)grow[u] * out_ld + col) = v;
+            }
         }
     }
     __syncwarp();
@@ -529,6 +548,7 @@ int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, do
 
 #include "conv_tma.cuh"
 #include "conv_tma_rows.cuh"
+#include "conv_thin.cuh"
 
 int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue) {
     aet_context *ctx = l->ctx;
@@ -548,6 +568,8 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     int r = tma_fd_rows<KIND_FPROP>(l, a, flops);
     if (r != 1) return r;   // 1 = shape not eligible
     r = tma_fprop(l, a, flops);
+    if (r != 1) return r;
+    r = thin_fprop(l, a, flops);
     if (r != 1) return r;
     dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
     return launch_gather<KIND_FPROP>(ctx, a, grid, "conv_fprop_gather", flops);
@@ -598,6 +620,19 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
             LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (rsplits + 1 + (accumulate ? 1 : 0)), 0);
             launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel, 
                 rpartial, dw, count4, rsplits, out_floats, accumulate);
+            return aet_check_launch("wgrad_reduce");
+        }
+    }
+    {
+        int tsplits = 0;
+        float *tpartial = nullptr;
+        int tr = thin_wgrad(l, a, flops, &tsplits, &tpartial);
+        if (tr < 0) return tr;
+        if (tr == AET_OK) {
+            const size_t count4 = out_floats / 4;
+            LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (tsplits + 1 + (accumulate ? 1 : 0)), 0);
+            launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel,
+                     tpartial, dw, count4, tsplits, out_floats, accumulate);
             return aet_check_launch("wgrad_reduce");
         }
     }

@@ -1,0 +1,447 @@
+// Convolutions whose whole GEMM K extent (taps x padded input channels) fits one pipeline stage:
+// the first layer of an image network (3 channels -> cp = 4, 3x3 -> K = 36).  Included by conv.cu.
+//
+// The general gather kernel spends most of such a layer on per-CTA fixed costs (barrier and TMEM
+// setup, index divisions, an epilogue nothing overlaps) for two K slabs of work per tile.  Here a
+// CTA is persistent: it keeps the weights in shared memory, walks over pixel tiles, and splits its
+// nine warps by role so that the gather of tile i+1, the MMAs of tile i and the store of tile i-1
+// run at the same time:
+//   warps 0-3  producers: thread p owns tile row p (one output pixel) and copies its receptive
+//              field, one 16-byte cell per (tap, 4 channels), into a K-major A stage
+//   warps 4-7  epilogue: TMEM -> shared memory -> coalesced global stores (+bias, activation)
+//   warp 8     allocates TMEM (two accumulators) and issues the MMAs
+#pragma once
+
+namespace {
+
+constexpr int THIN_THREADS = 288;
+constexpr int THIN_MAX_CELLS = 32;     // K <= 128
+constexpr int THIN_MAX_STAGES = 4;
+
+struct ThinArgs {
+    ConvGeom g;
+    const float *x, *w, *bias;
+    float *y;
+    int act, bn, n_rows, n_cols, out_ld;
+    int cells;            // valid 16-byte K cells of a row (K / 4)
+    int ksteps;           // MMAs per tile (K / 8 rounded up)
+    int tiles, stages, tmem_cols;
+    int *status;
+};
+
+struct ThinCtl {
+    unsigned long long full[THIN_MAX_STAGES], empty[THIN_MAX_STAGES];
+    unsigned long long acc_full[2], acc_empty[2], weights;
+    uint32_t tmem_base;
+    int abort_flag;
+    int4 ctab[THIN_MAX_CELLS];   // cell -> {row tap, column tap, channel offset, 0}
+};
+
+__global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const ThinArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    __shared__ ThinCtl ctl;
+    const ConvGeom &g = a.g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bn = a.bn;
+    const int kcells = 2 * a.ksteps;                       // cells per row including the zero padding
+    const uint32_t b_bytes = (uint32_t)kcells * bn * 16;
+    const uint32_t a_bytes = (uint32_t)kcells * BM * 16;
+    unsigned char *smem_b = smem;
+    unsigned char *smem_a = smem + b_bytes;
+    float *staging = reinterpret_cast<float *>(smem_a + (size_t)a.stages * a_bytes);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 128);
+            mbar_init(smem_u32(&ctl.empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl.acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl.acc_empty[b]), 4);
+        }
+        mbar_init(smem_u32(&ctl.weights), 128);
+        ctl.abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (threadIdx.x < THIN_MAX_CELLS) {
+        const int k = threadIdx.x * 4, tap = k / g.cp;
+        ctl.ctab[threadIdx.x] = make_int4(tap / g.S, tap % g.S, k - tap * g.cp, 0);
+    }
+    // the padding cells (K rounded up to whole MMAs) of the weights and of every stage stay zero
+    {
+        const int pad_cells = kcells - a.cells;
+        for (int i = threadIdx.x; i < pad_cells * (bn + a.stages * BM); i += THIN_THREADS) {
+            const int kc = a.cells + i / (bn + a.stages * BM), r = i % (bn + a.stages * BM);
+            unsigned char *dst = r < bn ? smem_b + (size_t)kc * (bn * 16) + r * 16
+                                        : smem_a + (size_t)((r - bn) / BM) * a_bytes + (size_t)kc * (BM * 16) + ((r - bn) % BM) * 16;
+            *reinterpret_cast<float4 *>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        fence_proxy_async_smem();
+    }
+    if (warp == 8) {
+        tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = ctl.tmem_base;
+    pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
+    volatile int *abort_flag = &ctl.abort_flag;
+
+    if (warp >= 4 && warp < 8) {
+        // weights: K-major rows = filters, cell (row, kc) at kc * (bn * 16) + row * 16 (rows past the last
+        // filter are zero).  The epilogue warps copy them while the producers already gather the first tile.
+        for (int i = threadIdx.x - 128; i < bn * a.cells; i += 128) {
+            const int row = i / a.cells, kc = i - row * a.cells;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < g.K) v = ldg4(a.w + (size_t)row * (a.cells * 4) + kc * 4);
+            *reinterpret_cast<float4 *>(smem_b + (size_t)kc * (bn * 16) + row * 16) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&ctl.weights));
+    }
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ producers
+        const int p = threadIdx.x;
+        const int ohw = g.OH * g.OW;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x, ++it) {
+            const int s = it % a.stages;
+            const uint32_t phase = (it / a.stages) & 1;
+            const int m = tile * BM + p;
+            const bool valid = m < a.n_rows;
+            const int n = m / ohw, rem = m - n * ohw;
+            const int oh = rem / g.OW, ow = rem - oh * g.OW;
+            const int iy0 = oh * g.sy - g.pad, ix0 = ow * g.sx - g.pad;
+            const float *base = a.x + (size_t)n * g.H * g.W * g.cp;
+            unsigned char *dst = smem_a + (size_t)s * a_bytes + p * 16;
+            bool ok = true;
+            for (int c0 = 0; c0 < a.cells && ok; c0 += 16) {
+                float4 v[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (c0 + u < a.cells && valid) {
+                        const int4 e = ctl.ctab[c0 + u];
+                        const int ih = iy0 + e.x, iw = ix0 + e.y;
+                        if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+                            v[u] = ldg4(base + ((size_t)ih * g.W + iw) * g.cp + e.z);
+                    }
+                }
+                if (c0 == 0) ok = mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag);
+                if (ok) {
+#pragma unroll
+                    for (int u = 0; u < 16; ++u)
+                        if (c0 + u < a.cells) *reinterpret_cast<float4 *>(dst + (size_t)(c0 + u) * (BM * 16)) = v[u];
+                }
+            }
+            if (!ok) break;
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&ctl.full[s]));
+        }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------------ epilogue
+        const int ew = warp - 4;   // TMEM lane quarter = warp id modulo 4
+        int it = 0;
+        for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x, ++it) {
+            const int b = it & 1;
+            bool ready = mbar_wait(smem_u32(&ctl.acc_full[b]), (uint32_t)(it >> 1) & 1, abort_flag);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) break;
+            tc_fence_after_sync();
+            const int m0 = tile * BM;
+            store_accumulator<true>(staging, tmem + (uint32_t)(b * bn), true, ew, lane, bn, a.y + (size_t)m0 * a.out_ld,
+                                    (size_t)a.out_ld, a.n_rows - m0, 0, a.n_cols, a.bias, a.act);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl.acc_empty[b]));
+        }
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        const uint32_t idesc = make_idesc_tf32(BM, bn, 0, 0);
+        const uint64_t da0 = make_desc(smem_u32(smem_a), BM * 16, 128, LAYOUT_NONE);
+        const uint64_t db0 = make_desc(smem_u32(smem_b), bn * 16, 128, LAYOUT_NONE);
+        const uint64_t a_step = (uint64_t)((2 * BM * 16) >> 4), b_step = (uint64_t)((2 * bn * 16) >> 4);
+        int it = 0;
+        bool have_weights = mbar_wait(smem_u32(&ctl.weights), 0, abort_flag);
+        for (int tile = blockIdx.x; have_weights && tile < a.tiles; tile += gridDim.x, ++it) {
+            const int s = it % a.stages;
+            const int b = it & 1;
+            if (!mbar_wait(smem_u32(&ctl.acc_empty[b]), ((uint32_t)(it >> 1) & 1) ^ 1, abort_flag)) break;
+            if (!mbar_wait(smem_u32(&ctl.full[s]), (uint32_t)(it / a.stages) & 1, abort_flag)) break;
+            tc_fence_after_sync();
+            const uint64_t st16 = (uint64_t)(((uint32_t)s * a_bytes) >> 4);
+            for (int j = 0; j < a.ksteps; ++j)
+                mma_tf32(tmem + (uint32_t)(b * bn), da0 + st16 + j * a_step, db0 + j * b_step, idesc, (uint32_t)(j > 0));
+            mma_commit(smem_u32(&ctl.empty[s]));
+            mma_commit(smem_u32(&ctl.acc_full[b]));
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) {
+        tmem_dealloc(tmem, a.tmem_cols);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+    }
+}
+
+// Forward pass through the persistent thin-K kernel; 1 = not eligible.
+int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
+    aet_context *ctx = l->ctx;
+    const ConvGeom &g = a.g;
+    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || getenv("AET_NO_THIN")) return 1;
+    if (tma_common_ok(l)) return 1;                                         // wide channel counts belong to the TMA kernels
+    if (a.k_total > THIN_MAX_CELLS * 4) return 1;
+    const int bn = round_up(a.n_cols, 16);
+    if (bn > 128) return 1;                    // two accumulators of two co-resident CTAs share the 512 TMEM columns
+    ThinArgs t = {};
+    t.g = g; t.x = a.src_a; t.w = a.src_b; t.bias = a.bias; t.y = a.out; t.act = a.act;
+    t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    t.cells = a.k_total / 4; t.ksteps = (a.k_total + 7) / 8;
+    t.tiles = (a.n_rows + BM - 1) / BM;
+    t.tmem_cols = pow2_cols(2 * bn);
+    t.status = ctx->status_dev;
+    const size_t kcells = 2 * (size_t)t.ksteps;
+    const size_t b_bytes = kcells * bn * 16, a_bytes = kcells * BM * 16, staging = (size_t)BM * (bn + 4) * 4;
+    int stages = (int)((110 * 1024 - 1024 - b_bytes - staging) / a_bytes);   // two CTAs per SM when it fits
+    if (stages < 2) stages = (int)((220 * 1024 - 1024 - b_bytes - staging) / a_bytes);
+    if (stages > THIN_MAX_STAGES) stages = THIN_MAX_STAGES;
+    if (stages < 2) return 1;
+    t.stages = stages;
+    const size_t smem_bytes = b_bytes + stages * a_bytes + staging + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        AET_CUDA(cudaFuncSetAttribute(conv_fprop_thin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set = true;
+    }
+    const int resident = smem_bytes <= 110 * 1024 ? 2 : 1;
+    int grid = ctx->sm_count * resident;
+    if (grid > t.tiles) grid = t.tiles;
+    LaunchScope scope(ctx, "conv_fprop_thin", 0, flops);
+    launch_k(ctx->stream, grid, THIN_THREADS, smem_bytes, conv_fprop_thin_kernel, t);
+    return aet_check_launch("conv_fprop_thin");
+}
+
+
+// ------------------------------------------------------------------------------------ weight gradient
+// dW[filter][(tap, c)] = sum over output pixels of delta[pixel][filter] * patch[pixel][(tap, c)]: M = filters,
+// N = taps x padded channels (<= 128), K = pixels, split over the grid (a CTA owns a run of 64-pixel
+// stages and one accumulator; the partial tiles are summed by wgrad_reduce_kernel in a fixed order).
+// The delta tile arrives by TMA in the MN-major swizzle; the patches are gathered, thread = (pixel, cells).
+constexpr int THINW_PX = 64;          // pixels per stage (two 32-pixel MN-major slabs)
+constexpr int THINW_MAX_STAGES = 4;
+
+struct ThinWArgs {
+    ConvGeom g;
+    const float *x;
+    float *partial;
+    int bn, n_rows, n_cols, out_ld, cells;
+    int pixels, stages_total, stages_per_split;
+    int m_blocks;          // 32-filter blocks the TMA box brings (the MMA reads four; the rest are never stored)
+    long long split_stride;
+    int stages, tmem_cols;
+    int *status;
+};
+
+struct ThinWCtl {
+    unsigned long long full[THINW_MAX_STAGES], empty[THINW_MAX_STAGES], accum;
+    uint32_t tmem_base;
+    int abort_flag;
+    int4 ctab[THIN_MAX_CELLS];
+};
+
+__global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __grid_constant__ CUtensorMap map_a, const ThinWArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    __shared__ ThinWCtl ctl;
+    const ConvGeom &g = a.g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int bn = a.bn;
+    const uint32_t a_slab = 4 * 4096;                                  // M = 128: four 32-filter blocks of [32 k][128 B]
+    const uint32_t b_slab = (uint32_t)((bn + 31) / 32) * 4096;
+    const uint32_t a_bytes = 2 * a_slab, stage_bytes = a_bytes + 2 * b_slab;
+    const int st_begin = blockIdx.x * a.stages_per_split;
+    int st_end = st_begin + a.stages_per_split;
+    if (st_end > a.stages_total) st_end = a.stages_total;
+    const int nst = st_end > st_begin ? st_end - st_begin : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 129);   // 128 gather arrivals + the TMA issuer's expect_tx
+            mbar_init(smem_u32(&ctl.empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl.accum), 1);
+        ctl.abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_a);
+    }
+    if (threadIdx.x < THIN_MAX_CELLS) {
+        const int k = threadIdx.x * 4, tap = k / g.cp;
+        ctl.ctab[threadIdx.x] = make_int4(tap / g.S, tap % g.S, k - tap * g.cp, 0);
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = ctl.tmem_base;
+    pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
+    volatile int *abort_flag = &ctl.abort_flag;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ producers
+        const int px = threadIdx.x & (THINW_PX - 1);       // pixel of the stage
+        const int cg = threadIdx.x / THINW_PX;             // first cell; the thread takes every second cell
+        const int slab = px >> 5, kq = px & 31;
+        const int ohw = g.OH * g.OW;
+        for (int it = 0; it < nst; ++it) {
+            const int s = it % a.stages;
+            const uint32_t phase = (it / a.stages) & 1;
+            const int p0 = (st_begin + it) * THINW_PX;
+            unsigned char *stage = smem + (size_t)s * stage_bytes;
+            if (threadIdx.x == 0) {
+                if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
+                const uint32_t bar = smem_u32(&ctl.full[s]);
+                mbar_arrive_expect_tx(bar, 2u * (uint32_t)a.m_blocks * 4096u);
+                tma_load_3d(smem_u32(stage), &map_a, bar, 0, p0, 0);
+                tma_load_3d(smem_u32(stage) + a_slab, &map_a, bar, 0, p0 + 32, 0);
+            }
+            const int p = p0 + px;
+            const bool valid = p < a.pixels;
+            const int n = p / ohw, rem = p - n * ohw;
+            const int oh = rem / g.OW, ow = rem - oh * g.OW;
+            const int iy0 = oh * g.sy - g.pad, ix0 = ow * g.sx - g.pad;
+            const float *base = a.x + (size_t)n * g.H * g.W * g.cp;
+            unsigned char *dst = stage + a_bytes + (size_t)slab * b_slab;
+            bool ok = true, waited = threadIdx.x == 0;
+            // every thread passes the empty barrier before it arrives on the full one, also with no cell to copy
+            for (int c0 = cg; (c0 < a.cells || !waited) && ok; c0 += 16) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int cell = c0 + 2 * u;
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (cell < a.cells && valid) {
+                        const int4 e = ctl.ctab[cell];
+                        const int ih = iy0 + e.x, iw = ix0 + e.y;
+                        if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
+                            v[u] = ldg4(base + ((size_t)ih * g.W + iw) * g.cp + e.z);
+                    }
+                }
+                if (!waited) { ok = mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag); waited = true; }
+                if (ok) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int cell = c0 + 2 * u;
+                        if (cell < a.cells) *reinterpret_cast<float4 *>(dst + mn_cell_offset(cell, kq)) = v[u];
+                    }
+                }
+            }
+            if (!ok) break;
+            fence_proxy_async_smem();
+            mbar_arrive(smem_u32(&ctl.full[s]));
+        }
+        // ------------------------------------------------------------------ epilogue
+        bool ready = nst == 0 ? true : mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
+        ready = __all_sync(0xffffffffu, ready);
+        tc_fence_after_sync();
+        if (ready)
+            store_accumulator<false>(reinterpret_cast<float *>(smem), tmem, nst > 0, warp, lane, bn,
+                                     a.partial + (size_t)blockIdx.x * a.split_stride, (size_t)a.out_ld, a.n_rows, 0, a.n_cols,
+                                     nullptr, (int)AET_LINEAR);
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        const uint32_t idesc = make_idesc_tf32(BM, bn, 1, 1);
+        const uint32_t s0 = smem_u32(smem);
+        const uint64_t da0 = make_desc(s0, 4096, 512, LAYOUT_SW128_32B);
+        const uint64_t db0 = make_desc(s0 + a_bytes, 4096, 512, LAYOUT_SW128_32B);
+        uint32_t accumulate = 0;
+        for (int it = 0; it < nst; ++it) {
+            const int s = it % a.stages;
+            if (!mbar_wait(smem_u32(&ctl.full[s]), (uint32_t)(it / a.stages) & 1, abort_flag)) break;
+            tc_fence_after_sync();
+            const uint64_t st16 = (uint64_t)(((uint32_t)s * stage_bytes) >> 4);
+#pragma unroll
+            for (int sl = 0; sl < 2; ++sl) {
+                const uint64_t da = da0 + st16 + (uint64_t)((sl * a_slab) >> 4), db = db0 + st16 + (uint64_t)((sl * b_slab) >> 4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    mma_tf32(tmem, da + j * 64, db + j * 64, idesc, accumulate);
+                    accumulate = 1;
+                }
+            }
+            mma_commit(smem_u32(&ctl.empty[s]));
+        }
+        mma_commit(smem_u32(&ctl.accum));
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        tmem_dealloc(tmem, a.tmem_cols);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+    }
+}
+
+// Weight gradient through the thin-K kernel: fills `partial` (ctx scratch) with `*splits` tiles; 1 = not eligible.
+int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, float **partial_out) {
+    aet_context *ctx = l->ctx;
+    const ConvGeom &g = a.g;
+    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || getenv("AET_NO_THIN")) return 1;
+    if (tma_common_ok(l)) return 1;                                         // wide channel counts belong to the TMA kernels
+    if (a.n_cols > THIN_MAX_CELLS * 4 || g.K > BM) return 1;
+    if (!(g.kp % 32 == 0 || g.kp < 32)) return 1;          // whole 32-filter blocks for the TMA box
+    const int bn = round_up(a.n_cols, 16);
+    ThinWArgs t = {};
+    t.g = g; t.x = a.src_b; t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    t.cells = a.n_cols / 4;
+    t.pixels = a.k_total;
+    t.stages_total = (t.pixels + THINW_PX - 1) / THINW_PX;
+    t.m_blocks = (g.kp + 31) / 32;
+    const size_t stage = 2 * (size_t)(4 * 4096) + 2 * (size_t)((bn + 31) / 32) * 4096;
+    int stages = (int)((110 * 1024 - 1024) / stage);
+    const int resident = stages >= 2 ? 2 : 1;
+    if (stages < 2) stages = (int)((220 * 1024 - 1024) / stage);
+    if (stages > THINW_MAX_STAGES) stages = THINW_MAX_STAGES;
+    if (stages < 2 || (size_t)stages * stage < (size_t)BM * (bn + 4) * 4) return 1;
+    t.stages = stages;
+    // one CTA per resident slot, but at least four stages of work each (the partial tiles cost a reduction pass)
+    int splits = ctx->sm_count * resident;
+    if (splits > t.stages_total / 4) splits = t.stages_total / 4;
+    if (splits < 1) splits = 1;
+    t.stages_per_split = (t.stages_total + splits - 1) / splits;
+    splits = (t.stages_total + t.stages_per_split - 1) / t.stages_per_split;
+    const size_t out_floats = (size_t)g.K * a.n_cols;
+    t.split_stride = (long long)out_floats;
+    float *partial = nullptr;
+    AET_TRY(ctx_scratch(ctx, out_floats * splits * sizeof(float), &partial));
+    t.partial = partial;
+    t.tmem_cols = pow2_cols(bn);
+    t.status = ctx->status_dev;
+    const CUtensorMap *ma;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)(g.kp < 32 ? g.kp : 32), (cuuint64_t)t.pixels, (cuuint64_t)t.m_blocks};
+        cuuint64_t str[2] = {(cuuint64_t)g.kp * 4, 128};
+        cuuint32_t box[3] = {32, 32, (cuuint32_t)t.m_blocks};
+        if (get_map(l, 12, a.src_a, 3, dims, str, box, true, &ma) != AET_OK) return 1;
+    }
+    const size_t smem_bytes = stage * stages + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        AET_CUDA(cudaFuncSetAttribute(conv_wgrad_thin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set = true;
+    }
+    LaunchScope scope(ctx, "conv_wgrad_thin", 0, flops);
+    launch_k(ctx->stream, splits, NTHREADS, smem_bytes, conv_wgrad_thin_kernel, *ma, t);
+    *splits_out = splits;
+    *partial_out = partial;
+    return aet_check_launch("conv_wgrad_thin");
+}
+
+}  // namespace

@@ -139,8 +139,7 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 }
 // 32 lanes x 16 consecutive 32-bit columns -> 16 registers per thread (lane i of the warp reads
 // TMEM lane (warp%4)*32 + i).
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
-    uint32_t r[16];
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t *r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -148,7 +147,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// The registers of every tcgen05.ld issued before are valid after this.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
+    uint32_t r[16];
+    tmem_ld16_issue(taddr, r);
+    tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }

@@ -90,6 +90,34 @@ def test_conv_tma_tf32(aet, ctx, oracle, shape):
     check(got, ref, TOL_TF32)
 
 
+# few input channels: the whole K extent fits one stage of the persistent first-layer kernels
+THIN_SHAPES = [
+    (2, 3, 8, 8, 5, 3, 1, 1, 2),          # one ragged tile
+    (4, 3, 32, 32, 32, 3, 1, 1, 2),       # first layer of the reference's CPU-runnable case
+    (128, 3, 32, 32, 64, 3, 1, 1, 0),     # first layer of the benchmark network, full batch: several tiles per CTA
+    (3, 4, 9, 7, 6, 3, 2, 1, 1),          # stride 2, odd sizes
+    (2, 2, 11, 11, 3, 5, 2, 2, 0),        # 5x5 stride 2: K = 100
+    (3, 1, 28, 28, 20, 5, 1, 0, 1),       # one input channel, no padding
+    (5, 8, 6, 6, 100, 2, 1, 0, 1),        # two cells per tap, 100 filters
+]
+
+
+@pytest.mark.parametrize("shape", THIN_SHAPES)
+def test_conv_thin_tf32(aet, ctx, oracle, shape):
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=400 + shape[1])
+        used = kernels_used(ctx)
+    finally:
+        ctx.profile(0)
+    assert "conv_fprop_thin" in used, used
+    kp = (shape[4] + 3) // 4 * 4
+    if kp % 32 == 0 or kp < 32:
+        assert "conv_wgrad_thin" in used, used
+    check(got, ref, TOL_TF32)
+
+
 def test_tma_and_gather_agree_closely(aet, ctx, ctx_gather, oracle):
     """Both producers feed the same MMA with the same TF32 inputs: results differ only by summation order."""
     shape = TMA_SHAPES[1]
