@@ -18,8 +18,27 @@ constexpr int THIN_THREADS = 288;
 constexpr int THIN_MAX_CELLS = 32;     // K <= 128
 constexpr int THIN_MAX_STAGES = 4;
 
+// Division by a run-time constant as multiply-high and shift (round-up method; exact for dividends
+// below 2^31): the producers turn a pixel index into (image, row, column) once per tile.
+struct FastDiv {
+    uint32_t mul, shr, d;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f = {0u, 0u, d};
+    if (d > 1) {
+        uint32_t lg = 0;
+        while ((1ull << lg) < d) ++lg;
+        const uint32_t p = 31 + lg;
+        f.mul = (uint32_t)(((1ull << p) + d - 1) / d);
+        f.shr = p - 32;
+    }
+    return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv &f) { return f.d == 1 ? n : __umulhi(n, f.mul) >> f.shr; }
+
 struct ThinArgs {
     ConvGeom g;
+    FastDiv div_ohw, div_ow;
     const float *x, *w, *bias;
     float *y;
     int act, bn, n_rows, n_cols, out_ld;
@@ -34,7 +53,7 @@ struct ThinCtl {
     unsigned long long acc_full[2], acc_empty[2], weights;
     uint32_t tmem_base;
     int abort_flag;
-    int4 ctab[THIN_MAX_CELLS];   // cell -> {row tap, column tap, channel offset, 0}
+    int4 ctab[THIN_MAX_CELLS];   // cell -> {row tap, column tap, element offset from the receptive field's corner, 0}
 };
 
 __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const ThinArgs a) {
@@ -66,7 +85,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
     }
     if (threadIdx.x < THIN_MAX_CELLS) {
         const int k = threadIdx.x * 4, tap = k / g.cp;
-        ctl.ctab[threadIdx.x] = make_int4(tap / g.S, tap % g.S, k - tap * g.cp, 0);
+        ctl.ctab[threadIdx.x] = make_int4(tap / g.S, tap % g.S, ((tap / g.S) * g.W + tap % g.S) * g.cp + k - tap * g.cp, 0);
     }
     // the padding cells (K rounded up to whole MMAs) of the weights and of every stage stay zero
     {
@@ -106,17 +125,17 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
     if (warp < 4) {
         // ------------------------------------------------------------------ producers
         const int p = threadIdx.x;
-        const int ohw = g.OH * g.OW;
         int it = 0;
         for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x, ++it) {
             const int s = it % a.stages;
             const uint32_t phase = (it / a.stages) & 1;
-            const int m = tile * BM + p;
-            const bool valid = m < a.n_rows;
-            const int n = m / ohw, rem = m - n * ohw;
-            const int oh = rem / g.OW, ow = rem - oh * g.OW;
-            const int iy0 = oh * g.sy - g.pad, ix0 = ow * g.sx - g.pad;
-            const float *base = a.x + (size_t)n * g.H * g.W * g.cp;
+            const uint32_t m = (uint32_t)(tile * BM + p);
+            const bool valid = m < (uint32_t)a.n_rows;
+            const uint32_t n = fast_div(m, a.div_ohw), rem = m - n * (uint32_t)(g.OH * g.OW);
+            const uint32_t oh = fast_div(rem, a.div_ow), ow = rem - oh * (uint32_t)g.OW;
+            const int iy0 = (int)oh * g.sy - g.pad, ix0 = (int)ow * g.sx - g.pad;
+            // element offset of the receptive field's corner (may lie outside the image; int32: checked on the host)
+            const float *corner = a.x + (((int)n * g.H + iy0) * g.W + ix0) * g.cp;
             unsigned char *dst = smem_a + (size_t)s * a_bytes + p * 16;
             bool ok = true;
             for (int c0 = 0; c0 < a.cells && ok; c0 += 16) {
@@ -124,11 +143,9 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
 #pragma unroll
                 for (int u = 0; u < 16; ++u) {
                     v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (c0 + u < a.cells && valid) {
+                    if (c0 + u < a.cells) {
                         const int4 e = ctl.ctab[c0 + u];
-                        const int ih = iy0 + e.x, iw = ix0 + e.y;
-                        if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
-                            v[u] = ldg4(base + ((size_t)ih * g.W + iw) * g.cp + e.z);
+                        if (valid && (unsigned)(iy0 + e.x) < (unsigned)g.H && (unsigned)(ix0 + e.y) < (unsigned)g.W) v[u] = ldg4(corner + e.z);
                     }
                 }
                 if (c0 == 0) ok = mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag);
@@ -201,6 +218,8 @@ int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     ThinArgs t = {};
     t.g = g; t.x = a.src_a; t.w = a.src_b; t.bias = a.bias; t.y = a.out; t.act = a.act;
     t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    if ((double)g.N * g.H * g.W * g.cp >= 2147483648.0 || (double)a.n_rows >= 2147483648.0) return 1;   // 32-bit element offsets
+    t.div_ohw = make_fastdiv((uint32_t)(g.OH * g.OW)); t.div_ow = make_fastdiv((uint32_t)g.OW);
     t.cells = a.k_total / 4; t.ksteps = (a.k_total + 7) / 8;
     t.tiles = (a.n_rows + BM - 1) / BM;
     t.tmem_cols = pow2_cols(2 * bn);
@@ -237,6 +256,7 @@ constexpr int THINW_MAX_STAGES = 4;
 
 struct ThinWArgs {
     ConvGeom g;
+    FastDiv div_ohw, div_ow;
     const float *x;
     float *partial;
     int bn, n_rows, n_cols, out_ld, cells;
@@ -281,7 +301,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
     }
     if (threadIdx.x < THIN_MAX_CELLS) {
         const int k = threadIdx.x * 4, tap = k / g.cp;
-        ctl.ctab[threadIdx.x] = make_int4(tap / g.S, tap % g.S, k - tap * g.cp, 0);
+        ctl.ctab[threadIdx.x] = make_int4(tap / g.S, tap % g.S, ((tap / g.S) * g.W + tap % g.S) * g.cp + k - tap * g.cp, 0);
     }
     if (warp == 4) {
         tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
@@ -298,8 +318,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
         // ------------------------------------------------------------------ producers
         const int px = threadIdx.x & (THINW_PX - 1);       // pixel of the stage
         const int cg = threadIdx.x / THINW_PX;             // first cell; the thread takes every second cell
-        const int slab = px >> 5, kq = px & 31;
-        const int ohw = g.OH * g.OW;
+        const int slab = px >> 5, kq = px & 31, k3 = kq & 3;
+        const uint32_t kbase = (uint32_t)(kq >> 2) * 512u + (uint32_t)k3 * 128u;
         for (int it = 0; it < nst; ++it) {
             const int s = it % a.stages;
             const uint32_t phase = (it / a.stages) & 1;
@@ -312,13 +332,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
                 tma_load_3d(smem_u32(stage), &map_a, bar, 0, p0, 0);
                 tma_load_3d(smem_u32(stage) + a_slab, &map_a, bar, 0, p0 + 32, 0);
             }
-            const int p = p0 + px;
-            const bool valid = p < a.pixels;
-            const int n = p / ohw, rem = p - n * ohw;
-            const int oh = rem / g.OW, ow = rem - oh * g.OW;
-            const int iy0 = oh * g.sy - g.pad, ix0 = ow * g.sx - g.pad;
-            const float *base = a.x + (size_t)n * g.H * g.W * g.cp;
-            unsigned char *dst = stage + a_bytes + (size_t)slab * b_slab;
+            const uint32_t p = (uint32_t)(p0 + px);
+            const bool valid = p < (uint32_t)a.pixels;
+            const uint32_t n = fast_div(p, a.div_ohw), rem = p - n * (uint32_t)(g.OH * g.OW);
+            const uint32_t oh = fast_div(rem, a.div_ow), ow = rem - oh * (uint32_t)g.OW;
+            const int iy0 = (int)oh * g.sy - g.pad, ix0 = (int)ow * g.sx - g.pad;
+            const float *corner = a.x + (((int)n * g.H + iy0) * g.W + ix0) * g.cp;
+            unsigned char *dst = stage + a_bytes + (size_t)slab * b_slab + kbase;
             bool ok = true, waited = threadIdx.x == 0;
             // every thread passes the empty barrier before it arrives on the full one, also with no cell to copy
             for (int c0 = cg; (c0 < a.cells || !waited) && ok; c0 += 16) {
@@ -327,11 +347,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
                 for (int u = 0; u < 8; ++u) {
                     const int cell = c0 + 2 * u;
                     v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (cell < a.cells && valid) {
+                    if (cell < a.cells) {
                         const int4 e = ctl.ctab[cell];
-                        const int ih = iy0 + e.x, iw = ix0 + e.y;
-                        if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
-                            v[u] = ldg4(base + ((size_t)ih * g.W + iw) * g.cp + e.z);
+                        if (valid && (unsigned)(iy0 + e.x) < (unsigned)g.H && (unsigned)(ix0 + e.y) < (unsigned)g.W) v[u] = ldg4(corner + e.z);
                     }
                 }
                 if (!waited) { ok = mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag); waited = true; }
@@ -339,7 +357,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         const int cell = c0 + 2 * u;
-                        if (cell < a.cells) *reinterpret_cast<float4 *>(dst + mn_cell_offset(cell, kq)) = v[u];
+                        // mn_cell_offset(cell, kq) with the pixel's share (kbase) hoisted out of the stage loop
+                        if (cell < a.cells)
+                            *reinterpret_cast<float4 *>(dst + (uint32_t)(cell >> 3) * 4096u + (uint32_t)((((cell & 7) >> 1) ^ k3) * 32) + (uint32_t)(cell & 1) * 16u) = v[u];
                     }
                 }
             }
@@ -400,6 +420,8 @@ int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, f
     const int bn = round_up(a.n_cols, 16);
     ThinWArgs t = {};
     t.g = g; t.x = a.src_b; t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
+    if ((double)g.N * g.H * g.W * g.cp >= 2147483648.0 || (double)a.k_total >= 2147483648.0 - 2 * THINW_PX) return 1;   // 32-bit element offsets
+    t.div_ohw = make_fastdiv((uint32_t)(g.OH * g.OW)); t.div_ow = make_fastdiv((uint32_t)g.OW);
     t.cells = a.n_cols / 4;
     t.pixels = a.k_total;
     t.stages_total = (t.pixels + THINW_PX - 1) / THINW_PX;
