@@ -60,6 +60,16 @@ struct aet_context {
     float *scratch = nullptr;
     size_t scratch_bytes = 0;
     int *status_dev = nullptr;  // device status word written by bounded waits
+    // Second stream of a network's backward pass: the weight-gradient kernels of a layer run there,
+    // beside the data-gradient chain on `stream`, with their own scratch arena.  side_begin() forks it
+    // from `stream` and makes it the launch stream; side_end() restores `stream`; side_join() makes
+    // `stream` wait for everything queued on it.
+    cudaStream_t side_stream = nullptr, main_stream_saved = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool overlap_wgrad = false;   // set by the network around its backward pass
+    bool on_side = false, side_pending = false;
+    float *scratch_side = nullptr;
+    size_t scratch_side_bytes = 0;
     // profiling
     bool profiling = false;
     std::vector<ProfileRecord> records;
@@ -175,7 +185,7 @@ struct aet_network {
     void *comm = nullptr;
     int rank = 0, world = 1;
     cudaStream_t comm_stream = nullptr;
-    cudaEvent_t ev_grad_ready[8] = {nullptr}, ev_comm_done = nullptr;
+    cudaEvent_t ev_grad_ready[8] = {nullptr}, ev_grad_ready_side[8] = {nullptr}, ev_comm_done = nullptr;
     long launches_per_step = 0;
 };
 
@@ -224,6 +234,9 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_trigger(); }
 #endif
 int ctx_scratch(aet_context *ctx, size_t bytes, float **out);
+int side_begin(aet_context *ctx);
+void side_end(aet_context *ctx);
+int side_join(aet_context *ctx);
 int ctx_staging(aet_context *ctx, size_t bytes);
 
 // ---- layout taps (tensor.cu) ------------------------------------------------------------------

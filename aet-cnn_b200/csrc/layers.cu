@@ -360,7 +360,12 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
             if (l->bn) AET_TRY(k_bn_backward(l, nullptr));
             else AET_TRY(k_bias_act_backward(l));
         }
-        AET_TRY(conv_wgrad(l, state.input->d, l->delta->d, layer_G(l), 1));
+        // In a network's backward pass the weight gradient runs on the side stream, beside the
+        // data-gradient chain of this and the earlier layers (both only read this layer's delta).
+        if (l->ctx->overlap_wgrad) AET_TRY(side_begin(l->ctx));
+        const int wr = conv_wgrad(l, state.input->d, l->delta->d, layer_G(l), 1);
+        side_end(l->ctx);
+        AET_TRY(wr);
         if (pd) {
             AET_TRY(conv_dgrad(l, l->delta->d, pd->d));
             pd->lazy_zero = false;

@@ -219,6 +219,10 @@ int issue_allreduce(aet_network *net, size_t lo, size_t hi, int slot) {
     aet_context *ctx = net->ctx;
     AET_CUDA(cudaEventRecord(net->ev_grad_ready[slot], ctx->stream));
     AET_CUDA(cudaStreamWaitEvent(net->comm_stream, net->ev_grad_ready[slot], 0));
+    if (ctx->side_pending) {   // the weight gradients of the bucket were queued on the side stream
+        AET_CUDA(cudaEventRecord(net->ev_grad_ready_side[slot], ctx->side_stream));
+        AET_CUDA(cudaStreamWaitEvent(net->comm_stream, net->ev_grad_ready_side[slot], 0));
+    }
     float *g = net->arena.G + lo;
     int r = api->all_reduce(g, g, hi - lo, 7 /* ncclFloat32 */, 0 /* ncclSum */, net->comm, net->comm_stream);
     if (r != 0) return nccl_fail(api, r, "ncclAllReduce");
@@ -232,25 +236,34 @@ int net_backward(aet_network *net, aet_state state) {
     const size_t bucket_floats = 64 * 1024;
     size_t pend_lo = 0, pend_hi = 0;
     int slot = 0;
+    aet_context *ctx = net->ctx;
+    ctx->overlap_wgrad = !getenv("AET_NO_OVERLAP");
     for (int i = (int)net->layers.size() - 1; i >= 0; --i) {
         aet_layer *l = net->layers[i];
         state.index = i;
         if (i == 0) { state.input = original_input; state.delta = original_delta; }
         else { state.input = net->layers[i - 1]->output; state.delta = net->layers[i - 1]->delta; }
-        AET_TRY(aet_layer_backward(l, state));
-        if (dp && l->type == AET_CONVOLUTIONAL) {
+        int br = aet_layer_backward(l, state);
+        if (br == AET_OK && dp && l->type == AET_CONVOLUTIONAL) {
             const ParamSegment &last = l->bn ? l->seg_s : l->seg_b;
             const size_t lo = l->seg_w.offset, hi = last.offset + last.padded;
             if (pend_hi == pend_lo) { pend_lo = lo; pend_hi = hi; }
             else pend_lo = lo;   // layers are laid out in order, so walking backwards extends the range downwards
-            if (pend_hi - pend_lo >= bucket_floats && slot < 7) {
-                AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
+            if (br == AET_OK && pend_hi - pend_lo >= bucket_floats && slot < 7) {
+                br = issue_allreduce(net, pend_lo, pend_hi, slot++);
                 pend_lo = pend_hi = 0;
             }
         }
+        if (br != AET_OK) {   // leave the streams joined and the context in its plain state
+            ctx->overlap_wgrad = false;
+            side_join(ctx);
+            return br;
+        }
     }
+    ctx->overlap_wgrad = false;
+    if (dp && pend_hi > pend_lo) AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
+    AET_TRY(side_join(ctx));
     if (dp) {
-        if (pend_hi > pend_lo) AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
         AET_CUDA(cudaEventRecord(net->ev_comm_done, net->comm_stream));
         AET_CUDA(cudaStreamWaitEvent(net->ctx->stream, net->ev_comm_done, 0));
         pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
@@ -701,6 +714,7 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     net->comm = comm; net->rank = rank; net->world = world;
     AET_CUDA(cudaStreamCreateWithFlags(&net->comm_stream, cudaStreamNonBlocking));
     for (int i = 0; i < 8; ++i) AET_CUDA(cudaEventCreateWithFlags(&net->ev_grad_ready[i], cudaEventDisableTiming));
+    for (int i = 0; i < 8; ++i) AET_CUDA(cudaEventCreateWithFlags(&net->ev_grad_ready_side[i], cudaEventDisableTiming));
     AET_CUDA(cudaEventCreateWithFlags(&net->ev_comm_done, cudaEventDisableTiming));
     graph_drop(net);
     net->hyper_host[1] = -1.f;
@@ -716,6 +730,7 @@ extern "C" int aet_network_comm_destroy(aet_network *net) {
     if (api) api->comm_destroy(net->comm);
     net->comm = nullptr; net->world = 1; net->rank = 0;
     for (int i = 0; i < 8; ++i) if (net->ev_grad_ready[i]) { cudaEventDestroy(net->ev_grad_ready[i]); net->ev_grad_ready[i] = nullptr; }
+    for (int i = 0; i < 8; ++i) if (net->ev_grad_ready_side[i]) { cudaEventDestroy(net->ev_grad_ready_side[i]); net->ev_grad_ready_side[i] = nullptr; }
     if (net->ev_comm_done) { cudaEventDestroy(net->ev_comm_done); net->ev_comm_done = nullptr; }
     if (net->comm_stream) { cudaStreamDestroy(net->comm_stream); net->comm_stream = nullptr; }
     return AET_OK;

@@ -73,20 +73,54 @@ void prof_end(aet_context *ctx) {
 }
 
 int ctx_scratch(aet_context *ctx, size_t bytes, float **out) {
-    if (bytes > ctx->scratch_bytes) {
+    float *&buf = ctx->on_side ? ctx->scratch_side : ctx->scratch;
+    size_t &have = ctx->on_side ? ctx->scratch_side_bytes : ctx->scratch_bytes;
+    if (bytes > have) {
         if (ctx->capturing) {
-            aet_set_error("scratch arena too small during graph capture (%zu > %zu)", bytes, ctx->scratch_bytes);
+            aet_set_error("scratch arena too small during graph capture (%zu > %zu)", bytes, have);
             return AET_E_NOMEM;
         }
         AET_CUDA(cudaStreamSynchronize(ctx->stream));
-        if (ctx->scratch) cudaFree(ctx->scratch);
-        ctx->scratch = nullptr;
-        ctx->scratch_bytes = 0;
+        if (buf) cudaFree(buf);
+        buf = nullptr;
+        have = 0;
         size_t want = round_up_sz(bytes + bytes / 4, 1 << 20);
-        AET_CUDA(cudaMalloc(&ctx->scratch, want));
-        ctx->scratch_bytes = want;
+        AET_CUDA(cudaMalloc(&buf, want));
+        have = want;
     }
-    *out = ctx->scratch;
+    *out = buf;
+    return AET_OK;
+}
+
+int side_begin(aet_context *ctx) {
+    if (!ctx->side_stream) {
+        AET_CUDA(cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+        AET_CUDA(cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming));
+        AET_CUDA(cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming));
+    }
+    AET_CUDA(cudaEventRecord(ctx->ev_fork, ctx->stream));
+    AET_CUDA(cudaStreamWaitEvent(ctx->side_stream, ctx->ev_fork, 0));
+    ctx->main_stream_saved = ctx->stream;
+    ctx->stream = ctx->side_stream;
+    ctx->on_side = true;
+    ctx->side_pending = true;
+    pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
+    return AET_OK;
+}
+
+void side_end(aet_context *ctx) {
+    if (!ctx->on_side) return;
+    ctx->stream = ctx->main_stream_saved;
+    ctx->on_side = false;
+}
+
+int side_join(aet_context *ctx) {
+    side_end(ctx);
+    if (!ctx->side_pending) return AET_OK;
+    AET_CUDA(cudaEventRecord(ctx->ev_join, ctx->side_stream));
+    AET_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+    ctx->side_pending = false;
+    pdl_skip_next();
     return AET_OK;
 }
 
@@ -158,6 +192,13 @@ extern "C" void aet_context_destroy(aet_context *ctx) {
     if (ctx->staging) cudaFree(ctx->staging);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->side_stream) {
+        cudaStreamSynchronize(ctx->side_stream);
+        cudaStreamDestroy(ctx->side_stream);
+        cudaEventDestroy(ctx->ev_fork);
+        cudaEventDestroy(ctx->ev_join);
+    }
+    if (ctx->scratch_side) cudaFree(ctx->scratch_side);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
