@@ -254,12 +254,20 @@ struct ConvGeom {
     int K, OH, OW, kp;       // output activation
     int R, S, sy, sx, pad;
 };
-int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue);
+// Batch-norm statistics gathered by the forward epilogue: in `shift` (per-channel, near the data);
+// out `partial` (scratch arena, rows x [2][ocp]: sum and sum of squares of y - shift) and `rows`
+// (0 when the launch could not gather them: bias or activation in the epilogue, 3xTF32).
+struct ConvStats {
+    const float *shift;
+    float *partial;
+    int rows;
+};
+int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue, ConvStats *stats = nullptr);
 int conv_dgrad(aet_layer *l, const float *dy, float *dx);
 int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate);
 void conv_release(aet_layer *l);
 
-int k_bn_stats(aet_layer *l, int update_rolling);
+int k_bn_stats(aet_layer *l, int update_rolling, const ConvStats *from_epilogue = nullptr);
 int k_bn_apply(aet_layer *l, int use_rolling);
 int k_bn_backward(aet_layer *l, aet_layer *pool);
 int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling);

@@ -39,6 +39,9 @@ struct ConvArgs {
     const float *src_b;   // fprop: w      dgrad: w       wgrad: x
     float *out;           // fprop: y      dgrad: dx      wgrad: split-K partials
     const float *bias;    // fprop epilogue, may be null
+    const float *stat_shift;   // fprop: accumulate batch-norm statistics of the output around this per-channel shift
+    float *stat_partial;       //        into one row [2][out_ld] per CTA along M (null: off)
+    int *stat_rows_out;        // host side: the launcher stores the number of partial rows (its grid.x) here
     int act;              // fprop epilogue activation
     int bn;               // N tile (multiple of 16, <= 256)
     int n_rows, n_cols;   // valid GEMM M and N extents
@@ -53,7 +56,7 @@ struct ConvArgs {
 struct SharedCtl {
     unsigned long long full[MAX_STAGES];
     unsigned long long empty[MAX_STAGES];
-    unsigned long long accum;
+    unsigned long long accum, stat_bar;
     uint32_t tmem_base;
     int abort_flag;
     int4 jtab[64];  // wgrad: per 4-column chunk of the N tile -> {r, s, c, valid}
@@ -89,10 +92,23 @@ __device__ __forceinline__ void st_cell(unsigned char *stage, uint32_t off, uint
 // 512 or more bytes apart (measured: 10 us for a 128x128 tile, half the kernel); through shared
 // memory every store instruction writes one contiguous row segment.
 // Each warp only re-reads the 32 rows it wrote itself: __syncwarp is the only synchronisation.
+// Per-lane running sums of the batch-norm statistics a forward epilogue gathers on the way out:
+// sum (y - shift) and sum (y - shift)^2 of the lane's four columns of each 128-column chunk, over
+// every valid row the warp stores.  shift == null switches them off.
+struct StatAcc {
+    const float *shift;
+    float4 s1[2], s2[2];
+};
+__device__ __forceinline__ void stat_init(StatAcc &st, const float *shift) {
+    st.shift = shift;
+    st.s1[0] = st.s1[1] = st.s2[0] = st.s2[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 template <bool FPROP>
 __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
                                                   float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
-                                                  const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0) {
+                                                  const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0,
+                                                  StatAcc *st = nullptr) {
     const int pitch = bn + 4;
     float *mine = tile + (size_t)(warp * 32 + lane) * pitch;
     // TMEM -> shared memory, 32 columns (two loads in flight) per wait
@@ -128,6 +144,10 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
         const bool active = c < bn && col < n_cols && sub < rpi;
         float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
         if (FPROP && bias && active) b = ldg4(bias + col);
+        const bool stats = FPROP && st && st->shift;
+        float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (stats && active) sh = ldg4(st->shift + col);
+        float4 t1 = make_float4(0.f, 0.f, 0.f, 0.f), t2 = t1;
         for (int r0 = 0; r0 < 32; r0 += 4 * rpi) {
             float4 o[4];
             int grow[4];
@@ -142,6 +162,11 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
             for (int u = 0; u < 4; ++u) {
                 if (!active || grow[u] >= rows_valid) continue;
                 float4 v = o[u];
+                if (stats) {
+                    const float dx = v.x - sh.x, dy = v.y - sh.y, dz = v.z - sh.z, dw = v.w - sh.w;
+                    t1.x += dx; t1.y += dy; t1.z += dz; t1.w += dw;
+                    t2.x += dx * dx; t2.y += dy * dy; t2.z += dz * dz; t2.w += dw * dw;
+                }
                 if (FPROP) {
                     v.x = apply_act(v.x + b.x, act); v.y = apply_act(v.y + b.y, act);
                     v.z = apply_act(v.z + b.z, act); v.w = apply_act(v.w + b.w, act);
@@ -149,8 +174,59 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
                 *reinterpret_cast<float4 *>(out + (size_t)grow[u] * out_ld + col) = v;
             }
         }
+        if (stats) {   // constant indices keep the sums in registers
+            if (c0 == 0) {
+                st->s1[0].x += t1.x; st->s1[0].y += t1.y; st->s1[0].z += t1.z; st->s1[0].w += t1.w;
+                st->s2[0].x += t2.x; st->s2[0].y += t2.y; st->s2[0].z += t2.z; st->s2[0].w += t2.w;
+            } else {
+                st->s1[1].x += t1.x; st->s1[1].y += t1.y; st->s1[1].z += t1.z; st->s1[1].w += t1.w;
+                st->s2[1].x += t2.x; st->s2[1].y += t2.y; st->s2[1].z += t2.z; st->s2[1].w += t2.w;
+            }
+        }
     }
     __syncwarp();
+}
+
+// Ends a forward CTA's statistics: folds the lanes that hold the same columns, parks each epilogue
+// warp's sums in its own rows of the staging tile, and lets epilogue warp 0 add the four warps in a
+// fixed order into the CTA's partial row (row[c] = sum, row[ld + c] = sum of squares).  The wait is
+// bounded like every other; after a timeout the row is simply not written.
+__device__ __forceinline__ void stats_commit(float *tile, StatAcc &st, int warp, int lane, int bn, float *row, int ld, int cols_left,
+                                             unsigned long long *bar, volatile int *abort_flag) {
+    const int pitch = bn + 4;
+    const int lpr = bn >= 128 ? 32 : bn / 4, rpi = 32 / lpr;
+    const int sub = lane / lpr, lcol = (lane - sub * lpr) * 4;
+    float *mine = tile + (size_t)(warp * 32) * pitch;
+    for (int c0 = 0; c0 < bn; c0 += 128) {
+        const float4 o1 = c0 == 0 ? st.s1[0] : st.s1[1], o2 = c0 == 0 ? st.s2[0] : st.s2[1];
+        float4 a1 = o1, a2 = o2;
+        for (int k = 1; k < rpi; ++k) {
+            const int src = lane + k * lpr;   // lanes past the warp return their own value; only sub 0 keeps the result
+            a1.x += __shfl_sync(0xffffffffu, o1.x, src); a1.y += __shfl_sync(0xffffffffu, o1.y, src);
+            a1.z += __shfl_sync(0xffffffffu, o1.z, src); a1.w += __shfl_sync(0xffffffffu, o1.w, src);
+            a2.x += __shfl_sync(0xffffffffu, o2.x, src); a2.y += __shfl_sync(0xffffffffu, o2.y, src);
+            a2.z += __shfl_sync(0xffffffffu, o2.z, src); a2.w += __shfl_sync(0xffffffffu, o2.w, src);
+        }
+        const int c = c0 + lcol;
+        if (sub == 0 && c < bn) {
+            *reinterpret_cast<float4 *>(mine + c) = a1;
+            *reinterpret_cast<float4 *>(mine + bn + c) = a2;
+        }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(bar));
+    if (warp != 0) return;
+    if (!mbar_wait(smem_u32(bar), 0, abort_flag)) return;
+    for (int c = lane; c < bn && c < cols_left; c += 32) {
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            s1 += tile[(size_t)(w * 32) * pitch + c];
+            s2 += tile[(size_t)(w * 32) * pitch + bn + c];
+        }
+        row[c] = s1;
+        row[ld + c] = s2;
+    }
 }
 
 // Byte offset of the 16-byte cell holding M/N elements 4*mc..4*mc+3 at K index k (0..31) inside an
@@ -189,6 +265,7 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
             mbar_init(smem_u32(&ctl.empty[s]), 1);
         }
         mbar_init(smem_u32(&ctl.accum), 1);
+        mbar_init(smem_u32(&ctl.stat_bar), 4);
         ctl.abort_flag = 0;
         fence_barrier_init();
     }
@@ -402,8 +479,13 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
         tc_fence_after_sync();
         if (ready) {
             float *obase = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)m0 * a.out_ld;
+            StatAcc st;
+            stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
             store_accumulator<KIND == KIND_FPROP>(reinterpret_cast<float *>(smem), tmem, nslabs > 0, warp, lane, bn, obase,
-                                                  (size_t)a.out_ld, a.n_rows - m0, n0, a.n_cols, a.bias, a.act);
+                                                  (size_t)a.out_ld, a.n_rows - m0, n0, a.n_cols, a.bias, a.act, 1, 1, 0, &st);
+            if (KIND == KIND_FPROP && st.shift)
+                stats_commit(reinterpret_cast<float *>(smem), st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0,
+                             a.out_ld, a.n_cols - n0, &ctl.stat_bar, abort_flag);
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
@@ -550,7 +632,7 @@ int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, do
 #include "conv_tma_rows.cuh"
 #include "conv_thin.cuh"
 
-int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue) {
+int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue, ConvStats *stats) {
     aet_context *ctx = l->ctx;
     ConvArgs a = {};
     a.g = layer_geom(l);
@@ -563,6 +645,16 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     a.k_per_split = a.k_total;
     a.out_ld = g.kp;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
+    if (stats) {
+        stats->rows = 0;
+        // the statistics describe the raw convolution result: no bias or activation in this epilogue
+        if (!bias && a.act == (int)AET_LINEAR && ctx->math != AET_MATH_3XTF32 && !getenv("AET_NO_EPILOGUE_STATS")) {
+            AET_TRY(ctx_scratch(ctx, (size_t)m_tiles * 2 * g.kp * sizeof(float), &stats->partial));   // one row per CTA along M at most
+            a.stat_shift = stats->shift;
+            a.stat_partial = stats->partial;
+            a.stat_rows_out = &stats->rows;
+        }
+    }
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
     const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
     int r = tma_fd_rows<KIND_FPROP>(l, a, flops);
@@ -572,6 +664,7 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     r = thin_fprop(l, a, flops);
     if (r != 1) return r;
     dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
+    if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;
     return launch_gather<KIND_FPROP>(ctx, a, grid, "conv_fprop_gather", flops);
 }
 

@@ -40,6 +40,8 @@ struct ThinArgs {
     ConvGeom g;
     FastDiv div_ohw, div_ow;
     const float *x, *w, *bias;
+    const float *stat_shift;   // batch-norm statistics of the output (see ConvArgs)
+    float *stat_partial;
     float *y;
     int act, bn, n_rows, n_cols, out_ld;
     int cells;            // valid 16-byte K cells of a row (K / 4)
@@ -50,7 +52,7 @@ struct ThinArgs {
 
 struct ThinCtl {
     unsigned long long full[THIN_MAX_STAGES], empty[THIN_MAX_STAGES];
-    unsigned long long acc_full[2], acc_empty[2], weights;
+    unsigned long long acc_full[2], acc_empty[2], weights, stat_bar;
     uint32_t tmem_base;
     int abort_flag;
     int4 ctab[THIN_MAX_CELLS];   // cell -> {row tap, column tap, element offset from the receptive field's corner, 0}
@@ -80,6 +82,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
             mbar_init(smem_u32(&ctl.acc_empty[b]), 4);
         }
         mbar_init(smem_u32(&ctl.weights), 128);
+        mbar_init(smem_u32(&ctl.stat_bar), 4);
         ctl.abort_flag = 0;
         fence_barrier_init();
     }
@@ -162,20 +165,26 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
     } else if (warp < 8) {
         // ------------------------------------------------------------------ epilogue
         const int ew = warp - 4;   // TMEM lane quarter = warp id modulo 4
+        StatAcc st;
+        stat_init(st, a.stat_partial ? a.stat_shift : nullptr);
+        bool all_ready = true;
         int it = 0;
         for (int tile = blockIdx.x; tile < a.tiles; tile += gridDim.x, ++it) {
             const int b = it & 1;
             bool ready = mbar_wait(smem_u32(&ctl.acc_full[b]), (uint32_t)(it >> 1) & 1, abort_flag);
             ready = __all_sync(0xffffffffu, ready);
-            if (!ready) break;
+            if (!ready) { all_ready = false; break; }
             tc_fence_after_sync();
             const int m0 = tile * BM;
             store_accumulator<true>(staging, tmem + (uint32_t)(b * bn), true, ew, lane, bn, a.y + (size_t)m0 * a.out_ld,
-                                    (size_t)a.out_ld, a.n_rows - m0, 0, a.n_cols, a.bias, a.act);
+                                    (size_t)a.out_ld, a.n_rows - m0, 0, a.n_cols, a.bias, a.act, 1, 1, 0, &st);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl.acc_empty[b]));
         }
+        if (st.shift && all_ready)
+            stats_commit(staging, st, ew, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld, a.out_ld, a.n_cols, &ctl.stat_bar,
+                         abort_flag);
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         const uint32_t idesc = make_idesc_tf32(BM, bn, 0, 0);
@@ -217,6 +226,7 @@ int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     if (bn > 128) return 1;                    // two accumulators of two co-resident CTAs share the 512 TMEM columns
     ThinArgs t = {};
     t.g = g; t.x = a.src_a; t.w = a.src_b; t.bias = a.bias; t.y = a.out; t.act = a.act;
+    t.stat_shift = a.stat_shift; t.stat_partial = a.stat_partial;
     t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
     if ((double)g.N * g.H * g.W * g.cp >= 2147483648.0 || (double)a.n_rows >= 2147483648.0) return 1;   // 32-bit element offsets
     t.div_ohw = make_fastdiv((uint32_t)(g.OH * g.OW)); t.div_ow = make_fastdiv((uint32_t)g.OW);
@@ -240,6 +250,7 @@ int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     const int resident = smem_bytes <= 110 * 1024 ? 2 : 1;
     int grid = ctx->sm_count * resident;
     if (grid > t.tiles) grid = t.tiles;
+    if (a.stat_rows_out) *a.stat_rows_out = grid;
     LaunchScope scope(ctx, "conv_fprop_thin", 0, flops);
     launch_k(ctx->stream, grid, THIN_THREADS, smem_bytes, conv_fprop_thin_kernel, t);
     return aet_check_launch("conv_fprop_thin");

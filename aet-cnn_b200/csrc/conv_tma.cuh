@@ -81,6 +81,8 @@ int get_map(aet_layer *l, int tag, const void *ptr, int rank, const cuuint64_t *
 struct TmaArgs {
     float *out;
     const float *bias;
+    const float *stat_shift;   // fprop: batch-norm statistics of the output (see ConvArgs)
+    float *stat_partial;
     int act, bn, n_rows, n_cols, out_ld;
     long long split_stride;
     int slabs_per_tap;   // fprop/dgrad: inner channel count / 32
@@ -127,6 +129,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_u32(&ctl.empty[s]), 1);
         }
         mbar_init(smem_u32(&ctl.accum), 1);
+        mbar_init(smem_u32(&ctl.stat_bar), 4);
         ctl.abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_a);
@@ -191,8 +194,13 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ready) {
             float *obase = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)m0 * a.out_ld;
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            StatAcc st;
+            stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
             store_accumulator<KIND == KIND_FPROP>(tile, tmem, nslabs > 0, warp, lane, bn, obase, (size_t)a.out_ld, a.n_rows - m0,
-                                                  n0, a.n_cols, a.bias, a.act);
+                                                  n0, a.n_cols, a.bias, a.act, 1, 1, 0, &st);
+            if (KIND == KIND_FPROP && st.shift)
+                stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
+                             &ctl.stat_bar, abort_flag);
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
@@ -303,6 +311,7 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     }
     TmaArgs t = {};
     t.out = a.out; t.bias = a.bias; t.act = a.act; t.bn = bn;
+    t.stat_shift = a.stat_shift; t.stat_partial = a.stat_partial;
     t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
     t.slabs_per_tap = g.cp / 32; t.S = g.S; t.pad = g.pad;
     t.pix_per_img = g.OH * g.OW; t.tile_w = g.OW; t.img_w = g.OW;
@@ -310,6 +319,7 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     t.a_bytes = BM * BK * 4;
     t.tx_bytes = t.a_bytes + bn * BK * 4;
     dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;   // only the forward launcher is given one
     return launch_tma<KIND_FPROP>(l->ctx, ma, mb, t, grid, "conv_fprop_tma", flops);
 }
 
@@ -345,6 +355,7 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
     t.a_bytes = BM * BK * 4;
     t.tx_bytes = t.a_bytes + bn * BK * 4;
     dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;   // only the forward launcher is given one
     return launch_tma<KIND_DGRAD>(l->ctx, ma, mb, t, grid, "conv_dgrad_tma", flops);
 }
 

@@ -50,6 +50,7 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             mbar_init(smem_u32(&ctl.empty[s]), 1);
         }
         mbar_init(smem_u32(&ctl.accum), 1);
+        mbar_init(smem_u32(&ctl.stat_bar), 4);
         ctl.abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_a);
@@ -222,6 +223,8 @@ namespace {
 struct FdRowsArgs {
     float *out;
     const float *bias;
+    const float *stat_shift;   // fprop: batch-norm statistics of the output (see ConvArgs)
+    float *stat_partial;
     int act, bn, n_rows, n_cols, out_ld;
     int R, S, pad, inner;          // inner = channels of the K dimension (cp for fprop, kp for dgrad)
     int slabs_per_s;               // ceil(inner / 32)
@@ -253,6 +256,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(smem_u32(&ctl.empty[s]), 1);
         }
         mbar_init(smem_u32(&ctl.accum), 1);
+        mbar_init(smem_u32(&ctl.stat_bar), 4);
         ctl.abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_a);
@@ -298,12 +302,17 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after_sync();
         if (ready) {
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            StatAcc st;
+            stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
             for (int t = 0; t < a.mt; ++t) {
                 const int mt0 = m0 + t * BM;
                 store_accumulator<KIND == KIND_FPROP>(tile, tmem + (uint32_t)(t * bn), true, warp, lane, bn,
                                                       a.out + (size_t)mt0 * a.out_ld, (size_t)a.out_ld, a.n_rows - mt0, n0, a.n_cols,
-                                                      a.bias, a.act, a.bi, a.w, a.pix_per_img);
+                                                      a.bias, a.act, a.bi, a.w, a.pix_per_img, &st);
             }
+            if (KIND == KIND_FPROP && st.shift)
+                stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
+                             &ctl.stat_bar, abort_flag);
         }
     } else if (lane == 0) {
         const int b_mn = KIND == KIND_FPROP ? 0 : 1;
@@ -422,6 +431,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     }
     FdRowsArgs t = {};
     t.out = a.out; t.bias = KIND == KIND_FPROP ? a.bias : nullptr; t.act = KIND == KIND_FPROP ? a.act : (int)AET_LINEAR;
+    t.stat_shift = KIND == KIND_FPROP ? a.stat_shift : nullptr; t.stat_partial = KIND == KIND_FPROP ? a.stat_partial : nullptr;
     t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
     t.R = g.R; t.S = g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
@@ -435,6 +445,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         attr_set = true;
     }
     dim3 grid((m_tiles + mt - 1) / mt, n_tiles, 1);
+    if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x;
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
     LaunchScope scope(ctx, name, 0, flops);
     launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);

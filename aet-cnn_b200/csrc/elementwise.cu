@@ -998,18 +998,24 @@ int aet_check_launch(const char *what) {
 }
 
 // Batch statistics of l->x (the convolution result) into mean / variance / inv_std.
-int k_bn_stats(aet_layer *l, int update_rolling) {
+int k_bn_stats(aet_layer *l, int update_rolling, const ConvStats *from_epilogue) {
     aet_context *ctx = l->ctx;
     const long long pixels = (long long)l->batch * l->oh * l->ow;
     ReducePlan p = plan_reduce(ctx, pixels, l->ocp);
     float *partial = nullptr;
-    AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
+    const bool have = from_epilogue && from_epilogue->rows > 0;   // the convolution's epilogue already summed its tiles
+    if (have) {
+        partial = from_epilogue->partial;
+        p.blocks = from_epilogue->rows;
+    } else {
+        AET_TRY(ctx_scratch(ctx, (size_t)p.blocks * 2 * l->ocp * sizeof(float), &partial));
+    }
     // The statistics are accumulated around a per-channel shift so that the one-pass variance does
     // not cancel; any value near the data works, and the previous step's batch mean is already there.
     ReduceArgs a = {};
     a.x = l->x->d; a.shift = l->mean; a.partial = partial; a.pixels = pixels; a.cp = l->ocp;
     a.pix_per_block = p.pix_per_block; a.m = p.m;
-    {
+    if (!have) {
         LaunchScope s(ctx, "bn_stats", (double)pixels * l->ocp * 4.0, 0);
         launch_k(ctx->stream, dim3(p.blocks, p.m.cslabs), TB, 0, reduce2_kernel<0>, a);
         AET_TRY(aet_check_launch("bn_stats"));

@@ -269,8 +269,9 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
     switch (l->type) {
     case AET_CONVOLUTIONAL:
         if (l->bn) {
-            AET_TRY(conv_fprop(l, state.input->d, l->x->d, nullptr, 0));
-            if (state.train) AET_TRY(k_bn_stats(l, 1));
+            ConvStats cs = {l->mean, nullptr, 0};
+            AET_TRY(conv_fprop(l, state.input->d, l->x->d, nullptr, 0, state.train ? &cs : nullptr));
+            if (state.train) AET_TRY(k_bn_stats(l, 1, &cs));
             l->last_forward_train = state.train != 0;
             aet_layer *pool = l->fused_pool;
             if (pool && (pool->indexes || !state.train)) {

@@ -222,3 +222,42 @@ def test_tensor_roundtrip_and_padding(aet, ctx):
         t.zero()
         assert not t.read().any()
         t.close()
+
+
+# (N, C, H, W, K): first-layer kernel, row-sharing TMA kernel with two pixel tiles, TMA kernel with tiles
+# spanning several images and two filter tiles, general gather kernel with a ragged filter count
+EPILOGUE_STAT_SHAPES = [(128, 3, 32, 32, 64), (16, 64, 16, 16, 128), (32, 128, 8, 8, 256), (5, 12, 9, 7, 20), (5, 12, 9, 7, 16),
+                        (3, 8, 6, 6, 44), (2, 3, 8, 8, 5)]
+
+
+@pytest.mark.parametrize("shape", EPILOGUE_STAT_SHAPES)
+def test_bn_statistics_from_conv_epilogue_match_the_separate_pass(aet, ctx, shape):
+    """Training-mode batch statistics gathered inside the convolution's epilogue against the
+    stand-alone reduction over the stored output (same shift, same finalize): float summation order only."""
+    import os
+    import aet_cnn_b200.synth as synth
+    N, C, H, W, K = shape
+    res = {}
+    for tag in ("epilogue", "separate"):
+        if tag == "separate":
+            os.environ["AET_NO_EPILOGUE_STATS"] = "1"
+        try:
+            layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, 3, 1, 1, 1, aet.LEAKY, 1, 1)
+            layer.write(aet.P_WEIGHTS, synth.normal((K, C, 3, 3), 31, 1, 0.0, 0.2))
+            x = aet.Tensor(ctx, N, C, H, W)
+            x.write(synth.uniform((N, C, H, W), 31, 2))
+            st = aet.make_state(input=x, train=1)
+            ctx.profile(1)
+            layer.forward(st)
+            layer.forward(st)      # second pass: the shift is the first pass's batch mean
+            used = {r["name"] for r in ctx.profile_read()}
+            ctx.profile(0)
+            assert ("bn_stats" in used) == (tag == "separate"), used
+            res[tag] = (layer.read(aet.P_MEAN), layer.read(aet.P_VARIANCE), layer.read(aet.P_ROLLING_MEAN),
+                        layer.read(aet.P_OUTPUT))
+            layer.close(); x.close()
+        finally:
+            os.environ.pop("AET_NO_EPILOGUE_STATS", None)
+    for a, b in zip(res["epilogue"], res["separate"]):
+        assert np.isfinite(a).all()
+        assert rel_l2(a.ravel(), b.ravel()) < 2e-6
