@@ -1105,7 +1105,13 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
         w.mean = l->mean; w.inv = l->inv_std; w.gamma = layer_s(l); w.beta = layer_b(l); w.coef = l->bwd_coef;
         w.act = l->act; w.cp = l->ocp; w.C = pool->c; w.H = pool->h; w.W = pool->w; w.OH = pool->oh; w.OW = pool->ow;
         w.total = (unsigned)((long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4));
-        int blocks = 4 * ctx->sm_count;
+        // one wave of exactly the blocks that are resident together (the kernel is a grid-stride loop): a
+        // partial second wave would run at a fraction of the bandwidth
+        static int resident_reduce = 0;
+        if (!resident_reduce &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_reduce, bn_bwd_poolwin_kernel<false>, TB, 0) != cudaSuccess)
+            resident_reduce = 2;
+        int blocks = resident_reduce * ctx->sm_count;
         const int maxb = (int)((w.total + TB - 1) / TB);
         if (blocks > maxb) blocks = maxb;
         p.blocks = blocks;
@@ -1139,7 +1145,12 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     b.gamma = layer_s(l); b.beta = layer_b(l); b.coef = l->bwd_coef; b.act = l->act; b.cp = l->ocp;
     b.pixels = pixels; b.pix_per_block = q.pix_per_block; b.m = q.m;
     if (window_major) {
-        const int blocks = (int)((w.total + TB - 1) / TB) < 8 * ctx->sm_count ? (int)((w.total + TB - 1) / TB) : 8 * ctx->sm_count;
+        static int resident_apply = 0;
+        if (!resident_apply &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_apply, bn_bwd_poolwin_kernel<true>, TB, 0) != cudaSuccess)
+            resident_apply = 2;
+        const int want = 2 * resident_apply * ctx->sm_count;   // two full waves
+        const int blocks = (int)((w.total + TB - 1) / TB) < want ? (int)((w.total + TB - 1) / TB) : want;
         LaunchScope s(ctx, "bn_bwd_apply_poolwin", (double)pixels * l->ocp * 8.0 + pool_bytes, 0);
         launch_k(ctx->stream, blocks, TB, 0, bn_bwd_poolwin_kernel<true>, w);
         return aet_check_launch("bn_bwd_apply_poolwin");
