@@ -39,6 +39,7 @@ static inline size_t round_up_sz(size_t v, size_t m) { return (v + m - 1) / m * 
 
 struct ProfileRecord {
     const char *name;
+    int tag;              // index of the network layer the launch belongs to, or -1
     double bytes, flops;
     cudaEvent_t e0, e1;
 };
@@ -76,6 +77,7 @@ struct aet_context {
     std::vector<cudaEvent_t> event_pool;
     size_t event_next = 0;
     long launches = 0;
+    int prof_tag = -1;    // layer index stamped on profile records ("name#index" in the table)
     bool capturing = false;
 };
 

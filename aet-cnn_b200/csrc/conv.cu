@@ -656,7 +656,7 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
         }
     }
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
     int r = tma_fd_rows<KIND_FPROP>(l, a, flops);
     if (r != 1) return r;   // 1 = shape not eligible
     r = tma_fprop(l, a, flops);
@@ -681,7 +681,7 @@ int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
     a.out_ld = g.cp;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
     int r = tma_fd_rows<KIND_DGRAD>(l, a, flops);
     if (r != 1) return r;
     r = tma_dgrad(l, a, flops);
@@ -701,7 +701,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
     a.k_total = g.N * g.OH * g.OW;
     a.out_ld = a.n_cols;
     const int m_tiles = (g.K + BM - 1) / BM;
-    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S + l->index;   // + index: keeps layers apart in profiles
+    const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
     const size_t out_floats = (size_t)g.K * a.n_cols;
     {
         int rsplits = 0;

@@ -265,6 +265,7 @@ static int check_input(const aet_layer *l, const aet_tensor *in) {
 
 extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
     if (!l) return fail_invalid("null layer");
+    l->ctx->prof_tag = l->net ? l->index : -1;
     AET_TRY(check_input(l, state.input));
     switch (l->type) {
     case AET_CONVOLUTIONAL:
@@ -339,6 +340,7 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
 // ---------------------------------------------------------------------------- backward
 extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     if (!l) return fail_invalid("null layer");
+    l->ctx->prof_tag = l->net ? l->index : -1;
     if (!l->delta) return fail_invalid("layer was created with train=0");
     aet_tensor *pd = state.delta;
     if (pd && (pd->n != l->batch || pd->c != l->c || pd->h != l->h || pd->w != l->w))

@@ -277,6 +277,7 @@ int run_step(aet_network *net) {
     AET_TRY(net_forward(net, st));
     st.input = net->input;
     AET_TRY(net_backward(net, st));
+    net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(k_sgd_arena(net));
     return AET_OK;
 }
@@ -529,6 +530,7 @@ extern "C" int aet_network_backward(aet_network *net, aet_state state) {
 extern "C" int aet_network_update(aet_network *net) {
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     AET_TRY(upload_hyper(net));
+    net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(k_sgd_arena(net));
     return AET_OK;
 }

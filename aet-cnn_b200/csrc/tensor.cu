@@ -62,7 +62,7 @@ void prof_begin(aet_context *ctx, const char *name, double bytes, double flops) 
         }
     }
     ProfileRecord r;
-    r.name = name; r.bytes = bytes; r.flops = flops;
+    r.name = name; r.tag = ctx->prof_tag; r.bytes = bytes; r.flops = flops;
     r.e0 = ctx->event_pool[ctx->event_next++];
     r.e1 = ctx->event_pool[ctx->event_next++];
     cudaEventRecord(r.e0, ctx->stream);
@@ -262,13 +262,16 @@ extern "C" int aet_context_profile_read(aet_context *ctx, aet_kernel_time *table
     for (const ProfileRecord &r : ctx->records) {
         float ms = 0.f;
         if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
+        char label[sizeof(table[0].name)];
+        if (r.tag >= 0) snprintf(label, sizeof(label), "%s#%d", r.name, r.tag);   // kernels of a network carry their layer
+        else snprintf(label, sizeof(label), "%s", r.name);
         int k = 0;
         for (; k < n; ++k)
-            if (strcmp(table[k].name, r.name) == 0 && table[k].algo_bytes == r.bytes && table[k].algo_flops == r.flops) break;
+            if (strcmp(table[k].name, label) == 0 && table[k].algo_bytes == r.bytes && table[k].algo_flops == r.flops) break;
         if (k == n) {
             if (n == capacity) continue;
             memset(&table[n], 0, sizeof(table[n]));
-            strncpy(table[n].name, r.name, sizeof(table[n].name) - 1);
+            strncpy(table[n].name, label, sizeof(table[n].name) - 1);
             table[n].algo_bytes = r.bytes;
             table[n].algo_flops = r.flops;
             ++n;

@@ -54,7 +54,13 @@ def load_package():
 TF32_PEAK_TFLOPS = 692.3
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of the same
 # workload (profiles/), keyed by kernel label; null when the dominant kernel has no capture yet.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {   # "kernel label#layer index" of the small CNN at batch 128
+    "conv_fprop_thin#0": 2.17e6, "conv_wgrad_thin#0": 35.68e6,
+    "conv_fprop_tma_rows#2": 8.73e6, "conv_dgrad_tma_rows#2": 17.10e6, "conv_wgrad_tma_rows#2": 25.19e6,
+    "conv_fprop_tma_rows#4": 5.42e6, "conv_dgrad_tma_rows#4": 9.59e6, "conv_wgrad_tma_rows#4": 12.61e6,
+    "bn_act_maxpool_fwd#0": 33.58e6, "bn_bwd_reduce_poolwin#0": 50.43e6, "bn_bwd_apply_poolwin#0": 53.75e6,
+    "bn_bwd_apply_poolwin#2": 25.19e6,
+}
 
 
 def measured_peaks():
@@ -294,18 +300,26 @@ def main():
     d2h = 8
 
     # ---- per-kernel pass for the roofline (eager launches, events around each)
+    # The weight-gradient kernels stay on the main stream here, so that no kernel's time includes a
+    # concurrent neighbour's.  The dominant kernel is the largest one that does algorithmic work (the
+    # finalize launches move a few KB; their event-bracketed time is mostly the bracket).
     prof_steps = min(args.steps, 20)
     net.use_graph(False)
-    net.train_device(want_loss=False)
-    net.profile(True)
-    for _ in range(prof_steps):
+    os.environ["AET_NO_OVERLAP"] = "1"
+    try:
         net.train_device(want_loss=False)
-    table = net.profile_read()
-    net.profile(False)
+        net.profile(True)
+        for _ in range(prof_steps):
+            net.train_device(want_loss=False)
+        table = net.profile_read()
+        net.profile(False)
+    finally:
+        os.environ.pop("AET_NO_OVERLAP", None)
     peaks = measured_peaks()
     table.sort(key=lambda r: -r["total_ms"])
     total_kernel_ms = sum(r["total_ms"] for r in table) or 1.0
-    top = table[0]
+    working = [r for r in table if r["algo_flops"] > 0 or r["algo_bytes"] > 0]
+    top = working[0] if working else table[0]
     avg_s = top["total_ms"] / top["launches"] / 1000.0
     if top["algo_flops"] > 0:
         roof = dict(bound="tensor", achieved=top["algo_flops"] / avg_s / 1e12, peak=TF32_PEAK_TFLOPS, unit="TFLOP/s",
