@@ -306,22 +306,25 @@ struct FinalizeArgs {
 
 // MODE 0: statistics -> mean, variance, 1/std, rolling update.  MODE 1: BN backward coefficients
 // and the scale / shift gradients.  MODE 2: bias gradient.
+constexpr int FIN_CH = 8;   // channels per finalize block
 template <int MODE>
 __global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
     pdl_enter();
-    // A block owns 32 channels (one coalesced 128-byte row of each partial).  Its 32 warps each take
-    // every 32nd block's partial; the loads of a thread are independent and issued together, the sums
-    // are formed in double in a fixed order (within the thread, then over the 32 warps).
-    __shared__ double sh1[32][33], sh2[32][33];
-    const int cl = threadIdx.x & 31, part = threadIdx.x >> 5;
-    const int c = blockIdx.x * 32 + cl;
+    // A block owns 8 channels (one 32-byte sector of each partial row) and splits the rows over 128
+    // thread groups, so that even 600 rows are one round of independent loads per thread.  The sums
+    // are formed in double in a fixed order: within the thread, over the warp's four groups by
+    // shuffle, then over the 32 warps.
+    __shared__ double sh1[32][FIN_CH + 1], sh2[32][FIN_CH + 1];
+    const int cl = threadIdx.x & (FIN_CH - 1), part = threadIdx.x / FIN_CH;
+    const int warp = threadIdx.x >> 5;
+    const int c = blockIdx.x * FIN_CH + cl;
     double s1 = 0.0, s2 = 0.0;
     if (c < a.cp) {
-        for (int b0 = part; b0 < a.blocks; b0 += 32 * 8) {
-            float v1[8], v2[8];
+        for (int b0 = part; b0 < a.blocks; b0 += (1024 / FIN_CH) * 4) {
+            float v1[4], v2[4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int b = b0 + 32 * i;
+            for (int i = 0; i < 4; ++i) {
+                const int b = b0 + (1024 / FIN_CH) * i;
                 v1[i] = 0.f; v2[i] = 0.f;
                 if (b < a.blocks) {
                     v1[i] = __ldg(a.partial + (size_t)b * 2 * a.cp + c);
@@ -329,14 +332,18 @@ __global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { s1 += (double)v1[i]; s2 += (double)v2[i]; }
+            for (int i = 0; i < 4; ++i) { s1 += (double)v1[i]; s2 += (double)v2[i]; }
         }
     }
-    sh1[part][cl] = s1;
-    sh2[part][cl] = s2;
+#pragma unroll
+    for (int o = FIN_CH; o < 32; o <<= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    if ((threadIdx.x & 31) < FIN_CH) { sh1[warp][cl] = s1; sh2[warp][cl] = s2; }
     // the finishing warp's per-channel operands are requested before the barrier, off the critical path
     float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-    const bool live = part == 0 && c < a.c;
+    const bool live = part == 0 && c < a.c;   // threads 0..7 finish their channel
     if (live) {
         if (MODE == 0) {
             p0 = a.shift[c];
@@ -350,9 +357,9 @@ __global__ void __launch_bounds__(1024) finalize_kernel(const FinalizeArgs a) {
     __syncthreads();
     if (part != 0 || c >= a.cp) return;
     {   // fixed-order sum of the 32 warp sums in four independent chains
-        double t1[4] = {s1, 0.0, 0.0, 0.0}, t2[4] = {s2, 0.0, 0.0, 0.0};
+        double t1[4] = {0.0, 0.0, 0.0, 0.0}, t2[4] = {0.0, 0.0, 0.0, 0.0};
 #pragma unroll
-        for (int q = 1; q < 32; ++q) { t1[q & 3] += sh1[q][cl]; t2[q & 3] += sh2[q][cl]; }
+        for (int q = 0; q < 32; ++q) { t1[q & 3] += sh1[q][cl]; t2[q & 3] += sh2[q][cl]; }
         s1 = (t1[0] + t1[1]) + (t1[2] + t1[3]);
         s2 = (t2[0] + t2[1]) + (t2[2] + t2[3]);
     }
@@ -1026,7 +1033,7 @@ int k_bn_stats(aet_layer *l, int update_rolling, const ConvStats *from_epilogue)
     f.mean = l->mean; f.variance = l->variance; f.inv = l->inv_std;
     f.rolling_mean = l->rolling_mean; f.rolling_variance = l->rolling_variance;
     LaunchScope s(ctx, "bn_stats_finalize", 0, 0);
-    launch_k(ctx->stream, (l->ocp + 31) / 32, 1024, 0, finalize_kernel<0>, f);
+    launch_k(ctx->stream, (l->ocp + FIN_CH - 1) / FIN_CH, 1024, 0, finalize_kernel<0>, f);
     return aet_check_launch("bn_stats_finalize");
 }
 
@@ -1136,7 +1143,7 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     f.g_gamma = layer_sG(l); f.g_beta = layer_bG(l); f.coef = l->bwd_coef;
     {
         LaunchScope s(ctx, "bn_bwd_finalize", 0, 0);
-        launch_k(ctx->stream, (l->ocp + 31) / 32, 1024, 0, finalize_kernel<1>, f);
+        launch_k(ctx->stream, (l->ocp + FIN_CH - 1) / FIN_CH, 1024, 0, finalize_kernel<1>, f);
         AET_TRY(aet_check_launch("bn_bwd_finalize"));
     }
     ReducePlan q = plan_apply(ctx, pixels, l->ocp);
@@ -1184,7 +1191,7 @@ int k_bias_act_backward(aet_layer *l) {
     FinalizeArgs f = {};
     f.partial = partial; f.blocks = p.blocks; f.cp = l->ocp; f.c = l->oc; f.m = pixels; f.g_beta = layer_bG(l);
     LaunchScope s(ctx, "bias_bwd_finalize", 0, 0);
-    launch_k(ctx->stream, (l->ocp + 31) / 32, 1024, 0, finalize_kernel<2>, f);
+    launch_k(ctx->stream, (l->ocp + FIN_CH - 1) / FIN_CH, 1024, 0, finalize_kernel<2>, f);
     return aet_check_launch("bias_bwd_finalize");
 }
 
@@ -1409,6 +1416,6 @@ extern "C" int aet_backward_bias_static(const float *delta, float *bias_updates,
     AET_TRY(aet_check_launch("backward_bias_static (partials)"));
     FinalizeArgs f = {};
     f.partial = st.scratch; f.blocks = p.blocks; f.cp = channels; f.c = channels; f.m = pixels; f.g_beta = bias_updates;
-    launch_k(stream, (channels + 31) / 32, 1024, 0, finalize_kernel<2>, f);
+    launch_k(stream, (channels + FIN_CH - 1) / FIN_CH, 1024, 0, finalize_kernel<2>, f);
     return aet_check_launch("backward_bias_static (finalize)");
 }
