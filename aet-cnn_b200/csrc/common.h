@@ -229,6 +229,27 @@ inline void launch_k(cudaStream_t stream, dim3 grid, dim3 block, size_t smem, vo
     cfg.numAttrs = (pdl_enabled() && !pdl_take_skip()) ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in aet_check_launch
 }
+// The same with a thread-block cluster of `cluster_z` CTAs along grid z (distributed shared memory
+// between the CTAs that split one tile's K range).
+template <typename... KArgs, typename... Args>
+inline void launch_k_cluster(cudaStream_t stream, dim3 grid, dim3 block, size_t smem, int cluster_z, void (*kernel)(KArgs...),
+                             Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)cluster_z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (pdl_enabled() && !pdl_take_skip()) ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -22,6 +22,7 @@
 // warp 4 allocates TMEM and its lane 0 issues every MMA.
 #include "common.h"
 #include "umma.cuh"
+#include <cooperative_groups.h>
 
 using namespace umma;
 
@@ -104,14 +105,11 @@ __device__ __forceinline__ void stat_init(StatAcc &st, const float *shift) {
     st.s1[0] = st.s1[1] = st.s2[0] = st.s2[1] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-template <bool FPROP>
-__device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
-                                                  float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
-                                                  const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0,
-                                                  StatAcc *st = nullptr) {
+// Phase one of the epilogue: TMEM -> this warp's 32 rows of the staging tile, 32 columns (two loads in
+// flight) per wait.
+__device__ __forceinline__ void stage_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn) {
     const int pitch = bn + 4;
     float *mine = tile + (size_t)(warp * 32 + lane) * pitch;
-    // TMEM -> shared memory, 32 columns (two loads in flight) per wait
     for (int cc = 0; cc < bn; cc += 32) {
         uint32_t v[32];
         const bool second = cc + 16 < bn;
@@ -129,12 +127,21 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
                 *reinterpret_cast<uint4 *>(mine + cc + q * 4) = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
     }
     __syncwarp();
+}
+
+// Phase two: staging tile -> global memory.  `remote` (may be null) is the staging tile of the cluster's
+// other CTA, which accumulated the other half of the K range: its rows are added on the way out.
+template <bool FPROP>
+__device__ __forceinline__ void flush_tile(const float *tile, const float *remote, int warp, int lane, int bn,
+                                           float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
+                                           const float *bias, int act, int map_bi, int map_w, int map_pix, StatAcc *st) {
+    const int pitch = bn + 4;
     // tiles that span several small images order their rows (h, image, w): each lane maps one row to
     // its pixel index once (the divisions cost more than the stores) and the others fetch it by shuffle
     int my_grow = warp * 32 + lane;
     if (map_bi > 1) my_grow = ((my_grow / map_w) % map_bi) * map_pix + (my_grow / (map_bi * map_w)) * map_w + my_grow % map_w;
-    // shared memory -> global: a store instruction covers whole rows, 32 / lpr of them when the tile is
-    // narrower than 128 columns; four rows are read before they are written so that the latencies overlap
+    // a store instruction covers whole rows, 32 / lpr of them when the tile is narrower than 128
+    // columns; four rows are read before they are written so that the latencies overlap
     const int lpr = bn >= 128 ? 32 : bn / 4;          // lanes per row (bn is a multiple of 16)
     const int rpi = 32 / lpr;                         // rows per instruction
     const int sub = lane / lpr, lcol = (lane - sub * lpr) * 4;
@@ -156,7 +163,12 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
                 const int r = (r0 + u * rpi + sub) & 31;
                 grow[u] = __shfl_sync(0xffffffffu, my_grow, r);
                 if (r0 + u * rpi + sub >= 32) grow[u] = rows_valid;   // past the warp's rows (lpr not a divisor of 32)
-                o[u] = *reinterpret_cast<const float4 *>(tile + (size_t)(warp * 32 + r) * pitch + c * (active ? 1 : 0));
+                const size_t off = (size_t)(warp * 32 + r) * pitch + c * (active ? 1 : 0);
+                o[u] = *reinterpret_cast<const float4 *>(tile + off);
+                if (remote) {
+                    const float4 q = *reinterpret_cast<const float4 *>(remote + off);
+                    o[u].x += q.x; o[u].y += q.y; o[u].z += q.z; o[u].w += q.w;
+                }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -185,6 +197,15 @@ __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc
         }
     }
     __syncwarp();
+}
+
+template <bool FPROP>
+__device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
+                                                  float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
+                                                  const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0,
+                                                  StatAcc *st = nullptr) {
+    stage_accumulator(tile, tmem_acc, have_acc, warp, lane, bn);
+    flush_tile<FPROP>(tile, nullptr, warp, lane, bn, out, out_ld, rows_valid, col_base, n_cols, bias, act, map_bi, map_w, map_pix, st);
 }
 
 // Ends a forward CTA's statistics: folds the lanes that hold the same columns, parks each epilogue

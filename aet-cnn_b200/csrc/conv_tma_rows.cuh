@@ -229,6 +229,7 @@ struct FdRowsArgs {
     int R, S, pad, inner;          // inner = channels of the K dimension (cp for fprop, kp for dgrad)
     int slabs_per_s;               // ceil(inner / 32)
     int mt, bh, bi, w, pix_per_img, n_img;
+    int ksplit;                    // 1, or 2: the two CTAs of a cluster (grid z) take half of the K slabs each
     int stages, tmem_cols;
     uint32_t a_bytes, b_tile_bytes, tx_bytes;
     int *status;
@@ -247,8 +248,15 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int m0 = blockIdx.x * BM * a.mt;                  // first pixel (in (n,h,w) order) of this CTA
     const int img0 = m0 / a.pix_per_img;
     const int row0 = (m0 - img0 * a.pix_per_img) / a.w;      // 0 when the tile spans whole images
-    const int nslabs = a.S * a.slabs_per_s;
+    const int total_slabs = a.S * a.slabs_per_s;
+    // K split over a cluster of two CTAs: rank 1 adds nothing to global memory, rank 0 reads rank 1's
+    // staged accumulator through distributed shared memory and stores the sum
+    const int krank = a.ksplit > 1 ? (int)blockIdx.z : 0;
+    const int slab_begin = a.ksplit > 1 ? krank * ((total_slabs + 1) / 2) : 0;
+    const int slab_end = a.ksplit > 1 ? (krank == 0 ? (total_slabs + 1) / 2 : total_slabs) : total_slabs;
+    const int nslabs = slab_end - slab_begin;
     const uint32_t stage_bytes = a.a_bytes + (uint32_t)a.R * a.b_tile_bytes;
+    bool epilogue_ready = false;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -283,7 +291,8 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
                 const uint32_t sb = sa + a.a_bytes;
                 mbar_arrive_expect_tx(bar, a.tx_bytes);
-                const int st = it / a.slabs_per_s, cb = it - st * a.slabs_per_s;   // column tap, channel slab
+                const int slab = slab_begin + it;
+                const int st = slab / a.slabs_per_s, cb = slab - st * a.slabs_per_s;   // column tap, channel slab
                 // fprop reads input pixel (h + r - pad, w + s - pad); dgrad reads delta pixel (h + pad - r, w + pad - s)
                 const int wx = KIND == KIND_FPROP ? st - a.pad : a.pad - st;
                 const int hy = KIND == KIND_FPROP ? row0 - a.pad : row0 + a.pad - (a.R - 1);
@@ -300,7 +309,11 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ready = mbar_wait(smem_u32(&ctl.accum), 0, abort_flag);
         ready = __all_sync(0xffffffffu, ready);
         tc_fence_after_sync();
-        if (ready) {
+        epilogue_ready = ready;
+        if (ready && a.ksplit > 1) {
+            // only stage the accumulator (mt == 1 here); the sum of the two halves is stored after the cluster barrier
+            stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, warp, lane, bn);
+        } else if (ready) {
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
             StatAcc st;
             stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
@@ -348,6 +361,26 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         mma_commit(smem_u32(&ctl.accum));
     }
 
+    __syncwarp();   // the MMA warp's lanes rejoin their issuing lane before any warp-wide barrier
+    if (a.ksplit > 1) {
+        // Every thread of both CTAs reaches these two barriers whatever happened above (the role loops
+        // leave by `break`, never by `return`), so a timed-out CTA cannot strand its partner.
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                   // both staging tiles are complete
+        if (warp < 4 && krank == 0 && epilogue_ready) {
+            float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+            const float *remote = cluster.map_shared_rank(tile, 1);
+            StatAcc st;
+            stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
+            flush_tile<KIND == KIND_FPROP>(tile, remote, warp, lane, bn, a.out + (size_t)m0 * a.out_ld, (size_t)a.out_ld, a.n_rows - m0,
+                                           n0, a.n_cols, a.bias, a.act, a.bi, a.w, a.pix_per_img, &st);
+            if (KIND == KIND_FPROP && st.shift)
+                stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
+                             &ctl.stat_bar, abort_flag);
+        }
+        cluster.sync();                                   // rank 1's shared memory stays alive until rank 0 has read it
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 4) {
@@ -373,14 +406,18 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     const int full = round_up(a.n_cols, 16);
     const int cands[4] = {full <= 256 ? full : 256, 128, 64, 32};
-    int bn = 0, mt = 1, stages = 0, n_tiles = 0;
+    int bn = 0, mt = 1, stages = 0, n_tiles = 0, ksplit = 1;
     uint32_t a_bytes = 0, b_tile = 0;
     size_t stage = 0;
+    const int total_slabs = g.S * ((inner + 31) / 32);
     for (int i = 0; i < 4 && !bn; ++i) {
         const int c = cands[i];
         if (c > full || (KIND == KIND_DGRAD && (c % 32 || g.cp % c))) continue;
         const int nt = (a.n_cols + c - 1) / c;
-        if (!(m_tiles * nt >= (ctx->sm_count * 3) / 5 || c <= 64)) continue;
+        // too few tiles for the machine: keep the wide N tile (an MMA of N = 64 costs as much as one of
+        // N = 128) and let the two CTAs of a cluster take half of the K range each
+        const bool split = c >= 128 && m_tiles * nt * 2 <= ctx->sm_count && total_slabs >= 8 && !getenv("AET_NO_KSPLIT");
+        if (!(m_tiles * nt >= (ctx->sm_count * 3) / 5 || c <= 64 || split)) continue;
         // two pixel tiles per CTA when they are rows of one image and there are still enough CTAs
         int m = 1;
         if (bi == 1 && g.H % (2 * (int)bh) == 0 && 2 * c <= 512 && (m_tiles / 2) * nt >= (ctx->sm_count * 3) / 4 &&
@@ -389,10 +426,11 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         for (; m >= 1; --m) {
             const uint32_t ab = (uint32_t)(m * (int)bh + g.R - 1) * bi * g.W * 128u;
             const size_t st = (size_t)ab + (size_t)g.R * c * 128u;
-            int ns = (int)((200 * 1024) / st);
+            int ns = (int)((220 * 1024) / st);
             if (ns > 4) ns = 4;
             if (ns >= 2 && st * ns >= (size_t)BM * (c + 4) * 4) {   // pipeline depth and room for the epilogue tile
                 bn = c; mt = m; stages = ns; n_tiles = nt; a_bytes = ab; b_tile = (uint32_t)c * 128u; stage = st;
+                ksplit = (split && m == 1) ? 2 : 1;
                 break;
             }
         }
@@ -401,7 +439,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     // The large stages allow one CTA per SM.  Measured on 8x8 to 16x16 images at batch 128 and 256: while the
     // grid fits one wave this kernel matches or beats the plain TMA kernel (dgrad by 20%); with a second,
     // partial wave the plain kernel with its smaller stages and two CTAs per SM wins by up to 40%.
-    if (((m_tiles + mt - 1) / mt) * n_tiles > ctx->sm_count && !getenv("AET_ROWS_MULTI")) return 1;
+    if (((m_tiles + mt - 1) / mt) * n_tiles * ksplit > ctx->sm_count && !getenv("AET_ROWS_MULTI")) return 1;
     const int super_rows = mt * (int)bh + g.R - 1;
     const CUtensorMap *ma, *mb;
     const float *act = a.src_a;
@@ -435,7 +473,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
     t.R = g.R; t.S = g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
-    t.stages = stages; t.tmem_cols = pow2_cols(mt * bn);
+    t.stages = stages; t.tmem_cols = pow2_cols(mt * bn); t.ksplit = ksplit;
     t.a_bytes = a_bytes; t.b_tile_bytes = b_tile; t.tx_bytes = a_bytes + (uint32_t)g.R * b_tile;
     t.status = ctx->status_dev;
     const size_t smem_bytes = stage * stages + 1024;
@@ -444,11 +482,12 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         AET_CUDA(cudaFuncSetAttribute(conv_fd_rows_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
         attr_set = true;
     }
-    dim3 grid((m_tiles + mt - 1) / mt, n_tiles, 1);
+    dim3 grid((m_tiles + mt - 1) / mt, n_tiles, ksplit);
     if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x;
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
     LaunchScope scope(ctx, name, 0, flops);
-    launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
+    if (ksplit > 1) launch_k_cluster(ctx->stream, grid, NTHREADS, smem_bytes, ksplit, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
+    else launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);
 }
 
