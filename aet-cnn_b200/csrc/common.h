@@ -78,6 +78,7 @@ struct aet_context {
     size_t event_next = 0;
     long launches = 0;
     int prof_tag = -1;    // layer index stamped on profile records ("name#index" in the table)
+    bool in_network_pass = false;   // set by the network around its forward/backward loops (enables call-pattern fusions)
     bool capturing = false;
 };
 
@@ -151,6 +152,16 @@ struct aet_layer {
     // Network-level fusion of the classifier head conv(linear) -> avgpool -> softmax (<= 32 classes)
     aet_layer *head_conv = nullptr, *head_avg = nullptr;   // set on the softmax layer
     aet_layer *head_softmax = nullptr;                     // set on the avg-pool and the convolution
+    // Linear head (1x1 convolution folded into the pooled vectors; network training passes only), on the convolution:
+    bool lin_head = false;           // eligible (set when the network is wired)
+    bool lin_fwd_pending = false;    // forward deferred to the softmax layer's call
+    bool lin_used = false;           // the last forward went through the fused kernel
+    bool lin_out_stale = false;      // output tensor not formed (a host tap runs the convolution)
+    bool lin_bwd_pending = false;    // softmax/avg-pool backward deferred to this layer's backward call
+    bool lin_delta_stale = false;    // delta tensor not formed (a host tap broadcasts it)
+    aet_tensor *lin_input = nullptr; // input of the deferred forward
+    float *lin_xbar = nullptr;       // [batch][cp] pooled input
+    unsigned int *lin_ticket = nullptr;
     bool head_forward_pending = false;  // avg-pool: forward deferred to the softmax layer's fused kernel
     bool head_backward_done = false;    // avg-pool / conv: delta (and bias gradient) already produced
     // TMA descriptors are built lazily per (layer, pass, operand address)
@@ -302,6 +313,9 @@ int k_avgpool_backward(aet_layer *l, float *prev_delta, int accumulate);
 int k_softmax_forward(aet_layer *l, const float *x, const float *truth);
 int k_head_forward(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *truth);
 int k_head_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm);
+int k_linhead_forward(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *x, const float *truth);
+int k_linhead_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm, float *pd);
+int k_linhead_conv_delta(aet_layer *conv, aet_layer *avg, aet_layer *sm);
 int k_axpy(aet_context *ctx, float *y, const float *x, float a, size_t n, int accumulate, const char *name);
 int k_dropout_forward(aet_layer *l, float *x, int generate);
 int k_dropout_backward(aet_layer *l, float *delta);

@@ -849,7 +849,7 @@ __global__ void __launch_bounds__(1024) head_backward_kernel(const HeadArgs a) {
     }
     part[warp][lane] = bsum;
     __syncthreads();
-    if (warp == 0 && lane < a.classes) {
+    if (warp == 0 && lane < a.classes && a.bias_grad) {
         float t = 0.f;
         for (int w = 0; w < 32; ++w) t += part[w][lane];
         a.bias_grad[lane] += t;
@@ -857,6 +857,182 @@ __global__ void __launch_bounds__(1024) head_backward_kernel(const HeadArgs a) {
 }
 
 // ---------------------------------------------------------------------------- small utilities
+// ---------------------------------------------------------------------------- linear classifier head
+// 1x1 convolution (bias, no activation) -> global average pool -> softmax + cross entropy is linear up
+// to the softmax, so a network's training pass runs it on the pooled vectors instead of on the feature
+// map: logits[n] = W * mean_px(x[n]) + b (exact FP32, S times fewer multiplies than the convolution),
+// and backward: dx[n][px] = W^T g[n] / S for every pixel, dW = sum_n g[n] xbar[n]^T, db = sum_n g[n],
+// with g = loss_scale * (truth - p).  The convolution's own output and delta tensors are only formed
+// when a host tap asks for them.
+struct LinHeadArgs {
+    const float *x;        // convolution input [N][S][cp]
+    const float *w, *b;    // weights [classes][cp], bias
+    float *xbar;           // [N][cp] pooled input, kept for the weight gradient
+    float *avg;            // avg-pool output = logits [N][ocp]
+    float *p, *sm_delta, *loss;
+    const float *truth;
+    float *unit_loss;      // [N]
+    float *cost;           // {sum, mean}
+    unsigned int *ticket;
+    float *avg_delta;      // [N][ocp]
+    float *pd;             // delta of the convolution's input [N][S][cp], overwritten
+    float *gw, *gb;        // weight / bias gradient accumulators
+    int N, S, cp, classes, ocp, parity;
+    float temp, loss_scale;
+};
+
+__global__ void __launch_bounds__(256) linhead_forward_kernel(const LinHeadArgs a) {
+    pdl_enter();
+    extern __shared__ float xs[];           // cp pooled inputs, then 32 logits
+    __shared__ bool last;
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *xn = a.x + (size_t)n * a.S * a.cp;
+    for (int c = threadIdx.x; c < a.cp; c += 256) {
+        float s = 0.f;
+        int px = 0;
+        for (; px + 8 <= a.S; px += 8) {   // eight loads in flight; the sum keeps the pixel order
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = xn[(size_t)(px + u) * a.cp + c];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += t[u];
+        }
+        for (; px < a.S; ++px) s += xn[(size_t)px * a.cp + c];
+        s /= a.S;
+        xs[c] = s;
+        a.xbar[(size_t)n * a.cp + c] = s;
+    }
+    float *lg = xs + a.cp;
+    __syncthreads();
+    for (int k = warp; k < a.classes; k += 8) {
+        const float *wk = a.w + (size_t)k * a.cp;
+        float d = 0.f;
+        for (int c = lane; c < a.cp; c += 32) d += wk[c] * xs[c];
+        for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (lane == 0) lg[k] = d + a.b[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        const float v = lane < a.classes ? lg[lane] : 0.f;
+        if (lane < a.ocp) a.avg[(size_t)n * a.ocp + lane] = lane < a.classes ? v : 0.f;
+        float m = lane < a.classes ? (a.parity == AET_PARITY_CPU ? v : (float)(int)v) : -INFINITY;
+        if (a.parity == AET_PARITY_CPU && lane >= a.classes) m = -FLT_MAX;
+        for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float e = lane < a.classes ? expf(v / a.temp - m / a.temp) : 0.f;
+        float sum = e;
+        for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        float err = 0.f;
+        if (lane < a.classes) {
+            const float q = e / sum;
+            a.p[(size_t)n * a.ocp + lane] = q;
+            if (a.truth) {
+                const float t = a.truth[(size_t)n * a.ocp + lane];
+                err = t ? -logf(q) : 0.f;
+                a.loss[(size_t)n * a.ocp + lane] = err;
+                a.sm_delta[(size_t)n * a.ocp + lane] = t - q;
+            }
+        }
+        for (int o = 16; o; o >>= 1) err += __shfl_xor_sync(0xffffffffu, err, o);
+        if (lane == 0) {
+            a.unit_loss[n] = err;
+            __threadfence();
+            last = atomicAdd(a.ticket, 1u) == (unsigned)(a.N - 1);
+        }
+    }
+    __syncthreads();
+    if (!last || !a.truth) {
+        if (last && threadIdx.x == 0) *a.ticket = 0u;
+        return;
+    }
+    // the block that finished last adds the per-sample losses in index order
+    __threadfence();
+    if (warp == 0) {   // lane i adds samples i, i+32, ...; the lanes are combined by a fixed xor tree
+        float c = 0.f;
+        for (int i = lane; i < a.N; i += 32) c += __ldcg(a.unit_loss + i);
+        for (int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) {
+            a.cost[0] = c;
+            a.cost[1] = c / a.N;
+            *a.ticket = 0u;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) linhead_backward_kernel(const LinHeadArgs a) {
+    pdl_enter();
+    __shared__ float g[32];
+    extern __shared__ float gs[];   // weight-gradient blocks: g of every sample [N][classes], then the lane sums
+    if ((int)blockIdx.x < a.N) {
+        const int n = blockIdx.x;
+        if (threadIdx.x < 32) {
+            const float v = (int)threadIdx.x < a.classes ? a.loss_scale * a.sm_delta[(size_t)n * a.ocp + threadIdx.x] : 0.f;
+            g[threadIdx.x] = v;
+            if ((int)threadIdx.x < a.ocp) a.avg_delta[(size_t)n * a.ocp + threadIdx.x] = v;
+        }
+        __syncthreads();
+        float *dn = a.pd + (size_t)n * a.S * a.cp;
+        for (int c = threadIdx.x; c < a.cp; c += 256) {
+            float v = 0.f;
+            int k = 0;
+            for (; k + 4 <= a.classes; k += 4) {
+                const float w0 = a.w[(size_t)k * a.cp + c], w1 = a.w[(size_t)(k + 1) * a.cp + c];
+                const float w2 = a.w[(size_t)(k + 2) * a.cp + c], w3 = a.w[(size_t)(k + 3) * a.cp + c];
+                v += g[k] * w0; v += g[k + 1] * w1; v += g[k + 2] * w2; v += g[k + 3] * w3;
+            }
+            for (; k < a.classes; ++k) v += g[k] * a.w[(size_t)k * a.cp + c];
+            v /= a.S;
+            for (int px = 0; px < a.S; ++px) dn[(size_t)px * a.cp + c] = v;
+        }
+        return;
+    }
+    // weight gradient of 32 channels: eight sample lanes per channel, summed in a fixed order
+    for (int i = threadIdx.x; i < a.N * a.classes; i += 256) {
+        const int n = i / a.classes, k = i - n * a.classes;
+        gs[i] = a.loss_scale * a.sm_delta[(size_t)n * a.ocp + k];
+    }
+    __syncthreads();
+    const int cl = threadIdx.x & 31, sl = threadIdx.x >> 5;
+    const int c = ((int)blockIdx.x - a.N) * 32 + cl;
+    float acc[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) acc[k] = 0.f;
+    for (int n0 = 0; n0 < a.N; n0 += 128) {
+        float xr[16];   // sixteen samples of this lane's channel, all loads in flight together
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int n = n0 + sl + 8 * u;
+            xr[u] = (n < a.N && c < a.cp) ? a.xbar[(size_t)n * a.cp + c] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            if (k >= a.classes) break;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int n = n0 + sl + 8 * u;
+                if (n < a.N) acc[k] += gs[n * a.classes + k] * xr[u];   // the warp shares n: a broadcast read
+            }
+        }
+    }
+    float *red3 = gs + a.N * a.classes;   // [classes][8 sample lanes][32 channels]
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        if (k >= a.classes) break;
+        red3[(k * 8 + sl) * 32 + cl] = acc[k];
+    }
+    __syncthreads();
+    // warp sl finishes classes sl, sl+8, ...: its read-modify-writes of the gradient are independent
+    for (int k = sl; k < a.classes; k += 8) {
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) t += red3[(k * 8 + q) * 32 + cl];
+        if (c < a.cp) a.gw[(size_t)k * a.cp + c] += t;   // sum over pixels of (g / S) * x = g * mean_px(x)
+    }
+    if (blockIdx.x == (unsigned)a.N && (int)threadIdx.x < a.classes) {
+        float t = 0.f;
+        for (int n = 0; n < a.N; ++n) t += gs[n * a.classes + threadIdx.x];
+        a.gb[threadIdx.x] += t;
+    }
+}
 __global__ void axpy_kernel(float *y, const float *x, float a, size_t n4, int accumulate) {
     pdl_enter();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1279,6 +1455,41 @@ int k_head_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm) {
     aet_context *ctx = sm->ctx;
     HeadArgs h = make_head(conv, avg, sm, nullptr);
     LaunchScope s(ctx, "head_backward", 4.0 * conv->batch * conv->oh * conv->ow * conv->ocp + 8.0 * sm->batch * sm->c, 0);
+    launch_k(ctx->stream, 1, 1024, 0, head_backward_kernel, h);
+    return aet_check_launch("head_backward");
+}
+
+static LinHeadArgs make_linhead(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *x, const float *truth, float *pd) {
+    LinHeadArgs h = {};
+    h.x = x; h.w = layer_W(conv); h.b = layer_b(conv); h.xbar = conv->lin_xbar;
+    h.avg = avg->output->d; h.p = sm->output->d; h.sm_delta = sm->delta->d; h.loss = sm->loss; h.truth = truth;
+    h.unit_loss = sm->sample_loss; h.cost = sm->cost_dev; h.ticket = conv->lin_ticket;
+    h.avg_delta = avg->delta->d; h.pd = pd; h.gw = layer_G(conv); h.gb = layer_bG(conv);
+    h.N = sm->batch; h.S = conv->oh * conv->ow; h.cp = conv->cp; h.classes = sm->c; h.ocp = sm->cp; h.parity = sm->ctx->parity;
+    h.temp = sm->temperature;
+    h.loss_scale = (sm->ctx->parity == AET_PARITY_MTCS && sm->net) ? sm->net->loss_scale : 1.0f;
+    return h;
+}
+int k_linhead_forward(aet_layer *conv, aet_layer *avg, aet_layer *sm, const float *x, const float *truth) {
+    aet_context *ctx = sm->ctx;
+    LinHeadArgs h = make_linhead(conv, avg, sm, x, truth, nullptr);
+    LaunchScope s(ctx, "linear_head_forward", 4.0 * h.N * h.S * h.cp + 4.0 * h.classes * h.cp, 2.0 * h.N * h.classes * h.cp);
+    launch_k(ctx->stream, h.N, 256, (size_t)(h.cp + 32) * sizeof(float), linhead_forward_kernel, h);
+    return aet_check_launch("linear_head_forward");
+}
+int k_linhead_backward(aet_layer *conv, aet_layer *avg, aet_layer *sm, float *pd) {
+    aet_context *ctx = sm->ctx;
+    LinHeadArgs h = make_linhead(conv, avg, sm, nullptr, nullptr, pd);
+    LaunchScope s(ctx, "linear_head_backward", 4.0 * h.N * h.S * h.cp + 8.0 * h.classes * h.cp, 4.0 * h.N * h.classes * h.cp);
+    launch_k(ctx->stream, h.N + (h.cp + 31) / 32, 256, (size_t)(h.N + 256) * h.classes * sizeof(float), linhead_backward_kernel, h);
+    return aet_check_launch("linear_head_backward");
+}
+// The convolution delta the fused head never wrote: g / S broadcast over the pixels (no gradient side effects).
+int k_linhead_conv_delta(aet_layer *conv, aet_layer *avg, aet_layer *sm) {
+    aet_context *ctx = sm->ctx;
+    HeadArgs h = make_head(conv, avg, sm, nullptr);
+    h.bias_grad = nullptr;
+    LaunchScope s(ctx, "head_backward", 4.0 * conv->batch * conv->oh * conv->ow * conv->ocp, 0);
     launch_k(ctx->stream, 1, 1024, 0, head_backward_kernel, h);
     return aet_check_launch("head_backward");
 }

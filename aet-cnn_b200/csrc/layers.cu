@@ -245,6 +245,8 @@ extern "C" void aet_layer_destroy(aet_layer *l) {
     if (l->indexes) cudaFree(l->indexes);
     if (l->loss) cudaFree(l->loss);
     if (l->sample_loss) cudaFree(l->sample_loss);
+    if (l->lin_xbar) cudaFree(l->lin_xbar);
+    if (l->lin_ticket) cudaFree(l->lin_ticket);
     if (l->cost_dev) cudaFree(l->cost_dev);
     if (l->rnd) cudaFree(l->rnd);
     if (l->step_dev) cudaFree(l->step_dev);
@@ -287,6 +289,15 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
                 l->output_stale = false;
             }
         } else {
+            l->lin_used = false; l->lin_out_stale = false; l->lin_delta_stale = false; l->lin_bwd_pending = false;
+            if (l->lin_head && l->ctx->in_network_pass && state.train && state.truth) {
+                // classifier head of a network in training: folded into the softmax layer's call
+                l->lin_fwd_pending = true;
+                l->lin_input = state.input;
+                l->output->lazy_zero = false;
+                return AET_OK;
+            }
+            l->lin_fwd_pending = false;
             AET_TRY(conv_fprop(l, state.input->d, l->output->d, layer_b(l), 1));
         }
         l->output->lazy_zero = false;
@@ -315,6 +326,19 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
             truth = state.truth->d;
         }
         l->cost_valid = false;
+        if (l->head_conv && l->head_conv->lin_fwd_pending) {
+            aet_layer *cv = l->head_conv;
+            cv->lin_fwd_pending = false;
+            if (l->head_avg->head_forward_pending && state.input == l->head_avg->output && truth) {
+                l->head_avg->head_forward_pending = false;
+                AET_TRY(k_linhead_forward(cv, l->head_avg, l, cv->lin_input->d, truth));
+                cv->lin_used = true;
+                cv->lin_out_stale = true;
+                l->delta->lazy_zero = false;
+                return AET_OK;
+            }
+            AET_TRY(conv_fprop(cv, cv->lin_input->d, cv->output->d, layer_b(cv), 1));   // not the fused call pattern after all
+        }
         if (l->head_avg && l->head_avg->head_forward_pending && state.input == l->head_avg->output) {
             l->head_avg->head_forward_pending = false;
             AET_TRY(k_head_forward(l->head_conv, l->head_avg, l, truth));
@@ -348,6 +372,17 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     switch (l->type) {
     case AET_CONVOLUTIONAL: {
         AET_TRY(check_input(l, state.input));
+        if (l->lin_bwd_pending) {
+            // fused linear head: softmax and avg-pool backward, this layer's data, weight and bias gradients in one kernel
+            l->lin_bwd_pending = false;
+            if (!pd) return fail_invalid("linear head backward needs the previous layer's delta");
+            AET_TRY(k_linhead_backward(l, l->head_softmax->head_avg, l->head_softmax, pd->d));
+            pd->lazy_zero = false;
+            l->delta->lazy_zero = false;
+            l->lin_delta_stale = true;
+            l->head_softmax->head_avg->delta->lazy_zero = false;
+            return AET_OK;
+        }
         if (l->head_backward_done) {
             l->head_backward_done = false;    // delta and bias gradient came from the fused head kernel
         } else if (l->gather_pending && l->bn && l->fused_pool) {
@@ -388,6 +423,7 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     case AET_AVGPOOL:
         if (!pd) return AET_OK;
         if (l->head_backward_done) { l->head_backward_done = false; return AET_OK; }
+        if (l->head_softmax && l->head_softmax->head_conv->lin_bwd_pending) return AET_OK;   // done by the convolution's backward call
         if (l->delta->lazy_zero) { AET_TRY(aet_tensor_zero(l->delta)); l->delta->lazy_zero = false; }
         AET_TRY(k_avgpool_backward(l, pd->d, pd->lazy_zero ? 0 : 1));
         pd->lazy_zero = false;
@@ -395,6 +431,11 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     case AET_SOFTMAX: {
         if (!pd) return AET_OK;
         if (pd->cp != l->cp) return fail_invalid("softmax backward: previous delta layout mismatch");
+        if (l->head_conv && l->head_conv->lin_used && l->ctx->in_network_pass && pd == l->head_avg->delta && pd->lazy_zero &&
+            l->head_conv->delta->lazy_zero && !l->delta->lazy_zero && l->head_conv->index > 0) {
+            l->head_conv->lin_bwd_pending = true;   // everything happens in the convolution's backward call
+            return AET_OK;
+        }
         if (l->head_avg && pd == l->head_avg->delta && pd->lazy_zero && l->head_conv->delta && l->head_conv->delta->lazy_zero &&
             !l->delta->lazy_zero) {
             AET_TRY(k_head_backward(l->head_conv, l->head_avg, l));
@@ -525,8 +566,17 @@ extern "C" int aet_layer_read(aet_layer *l, aet_param which, void *host_v) {
             AET_TRY(k_bn_apply(l, l->last_forward_train ? 0 : 1));
             l->output_stale = false;
         }
+        if (l->lin_out_stale) {  // the linear head never ran the convolution itself
+            AET_TRY(conv_fprop(l, l->lin_input->d, l->output->d, layer_b(l), 1));
+            l->lin_out_stale = false;
+        }
         return read_tensor_or_zero(l->output, host);
-    case AET_P_DELTA: return read_tensor_or_zero(l->delta, host);
+    case AET_P_DELTA:
+        if (l->lin_delta_stale) {
+            AET_TRY(k_linhead_conv_delta(l, l->head_softmax->head_avg, l->head_softmax));
+            l->lin_delta_stale = false;
+        }
+        return read_tensor_or_zero(l->delta, host);
     case AET_P_X: return aet_tensor_read(l->x, host);
     case AET_P_X_NORM: {
         AET_TRY(aet_tensor_read(l->x, host));
@@ -580,9 +630,11 @@ extern "C" int aet_layer_write(aet_layer *l, aet_param which, const void *host_v
     case AET_P_OUTPUT:
         l->output->lazy_zero = false;
         l->output_stale = false;
+        l->lin_out_stale = false;
         return aet_tensor_write(l->output, host);
     case AET_P_DELTA:
         l->delta->lazy_zero = false;
+        l->lin_delta_stale = false;
         return aet_tensor_write(l->delta, host);
     case AET_P_X: return aet_tensor_write(l->x, host);
     case AET_P_RAND:

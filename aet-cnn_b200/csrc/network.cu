@@ -203,14 +203,17 @@ int upload_hyper(aet_network *net) {
 
 int net_forward(aet_network *net, aet_state state) {
     // dnn/NNetwork.c:382-396
-    for (size_t i = 0; i < net->layers.size(); ++i) {
+    net->ctx->in_network_pass = true;
+    int rc = AET_OK;
+    for (size_t i = 0; i < net->layers.size() && rc == AET_OK; ++i) {
         aet_layer *l = net->layers[i];
         state.index = (int)i;
         if (l->delta && state.train && l->type != AET_DROPOUT) l->delta->lazy_zero = true;   // initDelta, without the memset
-        AET_TRY(aet_layer_forward(l, state));
+        rc = aet_layer_forward(l, state);
         state.input = l->output;
     }
-    return AET_OK;
+    net->ctx->in_network_pass = false;
+    return rc;
 }
 
 int issue_allreduce(aet_network *net, size_t lo, size_t hi, int slot) {
@@ -238,6 +241,7 @@ int net_backward(aet_network *net, aet_state state) {
     int slot = 0;
     aet_context *ctx = net->ctx;
     ctx->overlap_wgrad = !getenv("AET_NO_OVERLAP");
+    ctx->in_network_pass = true;
     for (int i = (int)net->layers.size() - 1; i >= 0; --i) {
         aet_layer *l = net->layers[i];
         state.index = i;
@@ -255,12 +259,14 @@ int net_backward(aet_network *net, aet_state state) {
             }
         }
         if (br != AET_OK) {   // leave the streams joined and the context in its plain state
+            ctx->in_network_pass = false;
             ctx->overlap_wgrad = false;
             side_join(ctx);
             return br;
         }
     }
     ctx->overlap_wgrad = false;
+    ctx->in_network_pass = false;
     if (dp && pend_hi > pend_lo) AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
     AET_TRY(side_join(ctx));
     if (dp) {
@@ -437,6 +443,13 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
                 l->groups == 1 && l->c <= 32) {
                 l->head_conv = cv; l->head_avg = avg;
                 avg->head_softmax = l; cv->head_softmax = l;
+                // 1x1 classifier: the head is linear up to the softmax and can run on the pooled vectors
+                if (cv->size == 1 && cv->stride_x == 1 && cv->stride_y == 1 && cv->pad == 0 && !getenv("AET_NO_LINEAR_HEAD") &&
+                    (size_t)(cv->batch + 256) * l->c * sizeof(float) <= 40 * 1024 && (size_t)(cv->cp + 32) * sizeof(float) <= 40 * 1024 &&
+                    cudaMalloc(&cv->lin_xbar, (size_t)cv->batch * cv->cp * sizeof(float)) == cudaSuccess &&
+                    cudaMalloc(&cv->lin_ticket, sizeof(unsigned int)) == cudaSuccess &&
+                    cudaMemset(cv->lin_ticket, 0, sizeof(unsigned int)) == cudaSuccess)
+                    cv->lin_head = true;
             }
         }
         c = l->oc; h = l->oh; w = l->ow;

@@ -149,44 +149,71 @@ def test_graph_replay_is_bitwise_identical_to_eager(aet, ctx, oracle):
     assert hashes[0] == hashes[1]
 
 
+def _run_variant(aet, ctx, oracle, env):
+    """One forward + backward + two more training steps of the small CNN (batch 8) with `env` set while the network is built."""
+    import os as _os
+    batch, steps = 8, 3
+    for k, v in env.items():
+        _os.environ[k] = v
+    try:
+        net, _, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+    finally:
+        for k in env:
+            _os.environ.pop(k, None)
+    x, truth = batch_for(opts, 10, batch, 3, 0)
+    net.input.write(x); net.truth.write(truth)
+    net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    outs = [net.layer(i).read(aet.P_OUTPUT) for i in range(net.layer_count)]   # conv outputs are formed lazily
+    idx = [net.layer(i).read(aet.P_INDEXES) for i in (1, 3, 5)]
+    grads = [net.layer(i).read(aet.P_WEIGHT_UPDATES) for i in (0, 2, 4, 6)]
+    bgrads = [net.layer(6).read(aet.P_BIAS_UPDATES)]
+    sgrads = [net.layer(i).read(aet.P_SCALE_UPDATES) for i in (0, 2, 4)]
+    deltas = [net.layer(i).read(aet.P_DELTA) for i in (0, 2, 4, 5, 6, 7)]
+    net.update()
+    losses = [net.train(*batch_for(opts, 10, batch, 3, step)) for step in range(1, steps)]
+    res = dict(outs=outs, idx=idx, grads=grads, bgrads=bgrads, sgrads=sgrads, deltas=deltas, losses=losses,
+               launches=net.launches_per_step())
+    net.close()
+    return res
+
+
 def test_fused_bn_pool_path_matches_layer_by_layer(aet, ctx, oracle):
     """Inside a network a BN convolution produces the following max-pool's output itself and folds the
     pool's backward into its BN backward kernels; AET_NO_FUSE=1 runs every layer's own kernels instead.
-    Forward results are bit-identical; gradients differ only by summation order."""
-    import os as _os
-    batch, steps = 8, 3
-    results = []
-    for no_fuse in (False, True):
-        if no_fuse:
-            _os.environ["AET_NO_FUSE"] = "1"
-        try:
-            net, _, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
-        finally:
-            _os.environ.pop("AET_NO_FUSE", None)
-        x, truth = batch_for(opts, 10, batch, 3, 0)
-        net.input.write(x); net.truth.write(truth)
-        net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
-        net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
-        outs = [net.layer(i).read(aet.P_OUTPUT) for i in range(net.layer_count)]   # conv outputs are formed lazily
-        idx = [net.layer(i).read(aet.P_INDEXES) for i in (1, 3, 5)]
-        grads = [net.layer(i).read(aet.P_WEIGHT_UPDATES) for i in (0, 2, 4, 6)]
-        sgrads = [net.layer(i).read(aet.P_SCALE_UPDATES) for i in (0, 2, 4)]
-        deltas = [net.layer(i).read(aet.P_DELTA) for i in (0, 2, 4)]
-        net.update()
-        losses = [net.train(*batch_for(opts, 10, batch, 3, step)) for step in range(1, steps)]
-        results.append(dict(outs=outs, idx=idx, grads=grads, sgrads=sgrads, deltas=deltas, losses=losses,
-                            launches=net.launches_per_step()))
-        net.close()
-    f, u = results
+    Forward results are bit-identical; gradients differ only by summation order.  (The linear classifier
+    head is switched off in both runs: it changes the arithmetic, see the next test.)"""
+    f = _run_variant(aet, ctx, oracle, {"AET_NO_LINEAR_HEAD": "1"})
+    u = _run_variant(aet, ctx, oracle, {"AET_NO_FUSE": "1"})
     for a, b in zip(f["outs"], u["outs"]):
         assert np.array_equal(a, b)
     for a, b in zip(f["idx"], u["idx"]):
         assert np.array_equal(a, b)
-    for key in ("grads", "sgrads", "deltas"):
+    for key in ("grads", "bgrads", "sgrads", "deltas"):
         for a, b in zip(f[key], u[key]):
             assert rel_l2(a, b) < 2e-4, (key, rel_l2(a, b))   # FP32 partial sums grouped differently
     assert np.allclose(f["losses"], u["losses"], rtol=1e-4)
     assert f["launches"] < u["launches"]          # fewer launches when fused
+
+
+def test_linear_head_matches_the_separate_layers(aet, ctx, oracle):
+    """In a network's training pass the 1x1 classifier convolution, the global average pool and the softmax
+    run on the pooled vectors (exact FP32) instead of as a TF32 convolution over the feature map: everything
+    up to the classifier's input is bit-identical, the head's results agree within the TF32 tolerance, and
+    the convolution's own output and delta are still there when a host tap reads them."""
+    f = _run_variant(aet, ctx, oracle, {})
+    u = _run_variant(aet, ctx, oracle, {"AET_NO_LINEAR_HEAD": "1"})
+    for i, (a, b) in enumerate(zip(f["outs"], u["outs"])):
+        if i <= 6:
+            assert np.array_equal(a, b), i          # layer 6 = the convolution's lazily formed output
+        else:
+            assert rel_l2(a, b) < 1e-2, (i, rel_l2(a, b))
+    for key in ("grads", "bgrads", "sgrads", "deltas"):
+        for a, b in zip(f[key], u[key]):
+            assert np.isfinite(a).all()
+            assert rel_l2(a, b) < 1e-2, (key, rel_l2(a, b))
+    assert np.allclose(f["losses"], u["losses"], rtol=2e-2)
+    assert f["launches"] < u["launches"]
 
 
 def test_weights_file_roundtrip_and_layout(aet, ctx, oracle):
