@@ -78,17 +78,28 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.first = index, [], None, 0
 
     def start(self):
+        """Starts the poller and waits for its first sample: nvidia-smi's start-up (NVML initialisation over
+        every GPU of the box) must not fall into the timed region, where it stalls kernel launches."""
+        if os.environ.get("BENCH_NO_CLOCK_SAMPLER"):
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 15.0 and self.proc.poll() is None:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
+
+    def mark(self):
+        """Samples taken from now on (and the one just before) count: call when the timed region starts."""
+        self.first = max(0, len(self.rows) - 1)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -105,7 +116,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in self.rows[self.first:]:
             if len(r) < 6:
                 continue
             try:
@@ -265,12 +276,13 @@ def main():
     # ---- device-resident throughput (graph replay)
     net.input.write(host_batches[0][0]); net.truth.write(host_batches[0][1])
     net.use_graph(True)
+    sampler = ClockSampler(local_rank)
+    sampler.start()          # polls from here on; its start-up cost stays outside the timed region
     for _ in range(args.warmup):
         net.train_device(want_loss=False)
     ctx.check()
-    sampler = ClockSampler(local_rank)
     barrier()
-    sampler.start()
+    sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
