@@ -199,6 +199,7 @@ struct aet_network {
     int rank = 0, world = 1;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_grad_ready[8] = {nullptr}, ev_grad_ready_side[8] = {nullptr}, ev_comm_done = nullptr;
+    cudaEvent_t ev_uploaded = nullptr;   // after the H2D copies of a train step fed from the caller's pinned buffers
     long launches_per_step = 0;
 };
 

@@ -608,16 +608,34 @@ extern "C" int aet_network_last_loss(aet_network *net, float *loss) {
 extern "C" int aet_network_train_step(aet_network *net, const float *host_x, const float *host_truth, float *loss) {
     if (!net || !host_x || !host_truth) { aet_set_error("aet_network_train_step: null argument"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
-    // both uploads share the pinned mirror: stage x and truth back to back in it
     const size_t nx = net->input->count(), nt = net->truth->count();
     AET_TRY(ctx_staging(ctx, (nx + nt) * sizeof(float)));
-    AET_CUDA(cudaStreamSynchronize(ctx->stream));
-    memcpy(ctx->pinned, host_x, nx * sizeof(float));
-    memcpy(ctx->pinned + nx, host_truth, nt * sizeof(float));
-    AET_CUDA(cudaMemcpyAsync(ctx->staging, ctx->pinned, (nx + nt) * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    // Page-locked caller buffers (cudaHostAlloc / cudaHostRegister / a pinned torch tensor) are copied
+    // by DMA straight from where they are; pageable ones go through the context's pinned mirror.
+    auto pinned = [](const void *p) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+        return at.type == cudaMemoryTypeHost;
+    };
+    if (pinned(host_x) && pinned(host_truth)) {
+        AET_CUDA(cudaMemcpyAsync(ctx->staging, host_x, nx * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        AET_CUDA(cudaMemcpyAsync(ctx->staging + nx, host_truth, nt * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+        if (!loss) {   // the caller may reuse its buffers as soon as this returns: wait for the two copies (not for the step)
+            if (!net->ev_uploaded) AET_CUDA(cudaEventCreateWithFlags(&net->ev_uploaded, cudaEventDisableTiming));
+            AET_CUDA(cudaEventRecord(net->ev_uploaded, ctx->stream));
+        }
+    } else {
+        // both uploads share the pinned mirror: stage x and truth back to back in it
+        AET_CUDA(cudaStreamSynchronize(ctx->stream));
+        memcpy(ctx->pinned, host_x, nx * sizeof(float));
+        memcpy(ctx->pinned + nx, host_truth, nt * sizeof(float));
+        AET_CUDA(cudaMemcpyAsync(ctx->staging, ctx->pinned, (nx + nt) * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    }
     AET_TRY(tensor_upload_staged(ctx, net->input->d, ctx->staging, net->input->n, net->input->c, net->input->h, net->input->w, net->input->cp));
     AET_TRY(tensor_upload_staged(ctx, net->truth->d, ctx->staging + nx, net->truth->n, net->truth->c, 1, 1, net->truth->cp));
-    return aet_network_train_step_device(net, loss);
+    const int r = aet_network_train_step_device(net, loss);
+    if (!loss && net->ev_uploaded && pinned(host_x) && pinned(host_truth)) AET_CUDA(cudaEventSynchronize(net->ev_uploaded));
+    return r;
 }
 
 extern "C" int aet_network_predict(aet_network *net, const float *host_x, float *host_out) {
@@ -746,6 +764,7 @@ extern "C" int aet_network_comm_destroy(aet_network *net) {
     net->comm = nullptr; net->world = 1; net->rank = 0;
     for (int i = 0; i < 8; ++i) if (net->ev_grad_ready[i]) { cudaEventDestroy(net->ev_grad_ready[i]); net->ev_grad_ready[i] = nullptr; }
     for (int i = 0; i < 8; ++i) if (net->ev_grad_ready_side[i]) { cudaEventDestroy(net->ev_grad_ready_side[i]); net->ev_grad_ready_side[i] = nullptr; }
+    if (net->ev_uploaded) { cudaEventDestroy(net->ev_uploaded); net->ev_uploaded = nullptr; }
     if (net->ev_comm_done) { cudaEventDestroy(net->ev_comm_done); net->ev_comm_done = nullptr; }
     if (net->comm_stream) { cudaStreamDestroy(net->comm_stream); net->comm_stream = nullptr; }
     return AET_OK;

@@ -260,10 +260,17 @@ def main():
         net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
 
     batch = args.batch
-    host_batches = []
+    host_batches, pinned_keep = [], []
+
+    def pin(a):
+        """Page-locked copy of a host array (the library copies by DMA straight from such buffers)."""
+        t = torch.from_numpy(np.ascontiguousarray(a, np.float32)).pin_memory()
+        pinned_keep.append(t)
+        return t.numpy()
+
     for s in range(4):
         tid = par.shard_tensor_id(s, rank, world)
-        host_batches.append((synth.uniform((batch, 3, 32, 32), SEED, 2 * tid), synth.labels(batch, CLASSES, SEED, 2 * tid + 1)[1]))
+        host_batches.append((pin(synth.uniform((batch, 3, 32, 32), SEED, 2 * tid)), pin(synth.labels(batch, CLASSES, SEED, 2 * tid + 1)[1])))
 
     def barrier():
         torch.cuda.synchronize()
