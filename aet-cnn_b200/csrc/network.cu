@@ -742,6 +742,11 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     NcclUniqueId id;
     memcpy(&id, unique_id_128, sizeof(id));
     void *comm = nullptr;
+    // The gradient buckets are small (<= 1.2 MB on the small CNN) and overlap the backward pass: a collective
+    // kernel of 31 CTAs (NCCL's own choice at 8 ranks) takes a fifth of the SMs from convolution kernels
+    // sized to one CTA per SM.  Measured at 8 GPUs: 0.309 ms per step by default, 0.294 with at most 8 CTAs,
+    // 0.346 with 4.  A value already in the environment is left alone.
+    setenv("NCCL_MAX_CTAS", "8", 0);
     int r = api->comm_init_rank(&comm, world, id, rank);
     if (r != 0) return nccl_fail(api, r, "ncclCommInitRank");
     net->comm = comm; net->rank = rank; net->world = world;
