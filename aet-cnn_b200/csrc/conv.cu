@@ -598,6 +598,16 @@ ConvGeom layer_geom(const aet_layer *l) {
     g.N = l->batch; g.C = l->c; g.H = l->h; g.W = l->w; g.cp = l->cp;
     g.K = l->oc; g.OH = l->oh; g.OW = l->ow; g.kp = l->ocp;
     g.R = l->size; g.S = l->size; g.sy = l->stride_y; g.sx = l->stride_x; g.pad = l->pad;
+    // A filter that covers the whole unpadded map is a fully connected layer (the reference has no other kind):
+    // with NHWC activations and [filter][tap][channel] weights it IS a 1x1 convolution over H*W*cp channels of a
+    // 1x1 map, byte for byte.  Seen that way the data gradient is a plain GEMM over the batch instead of a
+    // convolution in which 35 of 36 taps of every input pixel fall outside the single output pixel.
+    if (l->size == l->h && l->size == l->w && l->pad == 0 && l->size > 1 && !getenv("AET_NO_FC_ALIAS")) {
+        g.C = g.cp = l->h * l->w * l->cp;
+        g.H = g.W = g.OH = g.OW = 1;
+        g.R = g.S = 1;
+        g.sy = g.sx = 1;
+    }
     return g;
 }
 

@@ -285,8 +285,9 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
 // Input channels must fill whole 32-channel (128-byte) rows.  The filter side may be narrower than one
 // row (ocp < 32: the copy engine zero-fills the rest of the box) or a whole number of rows.
 bool tma_common_ok(const aet_layer *l) {
-    return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && l->stride_x == 1 && l->stride_y == 1 &&
-           l->cp % 32 == 0 && (l->ocp % 32 == 0 || l->ocp < 32);
+    const ConvGeom g = layer_geom(l);   // the geometry the kernels see (a fully connected layer is a 1x1 convolution)
+    return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && g.sx == 1 && g.sy == 1 &&
+           g.cp % 32 == 0 && (g.kp % 32 == 0 || g.kp < 32);
 }
 
 int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
