@@ -57,3 +57,29 @@ def test_cfg_reader_defaults(aet):
         cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\n")  # default activation = logistic
     anet, alayers = cfgfile.network_spec(open(os.path.join(aet.CFG_DIR, "alexnet_style.cfg")).read())
     assert sum(1 for l in alayers if l["type"] == 0) == 8 and alayers[1]["pad"] == 0
+
+
+def test_every_kernel_waits_for_its_predecessor_before_touching_global_memory():
+    """Kernels are launched with programmatic stream serialization, so each one must call pdl_enter()
+    (griddepcontrol.wait) itself: a kernel without it would race with the tail of the previous launch."""
+    import re
+    csrc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "aet-cnn_b200", "csrc")
+    checked = 0
+    for fn in sorted(os.listdir(csrc)):
+        if not fn.endswith((".cu", ".cuh")):
+            continue
+        src = open(os.path.join(csrc, fn)).read()
+        for m in re.finditer(r"__global__", src):
+            start = src.find("{", src.find(")", m.start()))
+            depth, k = 0, start
+            while True:
+                if src[k] == "{":
+                    depth += 1
+                elif src[k] == "}":
+                    depth -= 1
+                    if depth == 0:
+                        break
+                k += 1
+            assert "pdl_enter()" in src[start:k], "%s: kernel at offset %d never calls pdl_enter()" % (fn, m.start())
+            checked += 1
+    assert checked >= 30
