@@ -40,7 +40,8 @@ aet_network_seen aet_network_forward aet_network_backward aet_network_update aet
 aet_network_train_step aet_network_train_step_device aet_network_last_loss aet_network_predict
 aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
-aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static""".split()
+aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static
+aet_network_comm_exchange_export aet_network_comm_exchange_attach""".split()
 
 
 class AetError(RuntimeError):
@@ -117,6 +118,7 @@ def lib():
         "aet_network_profile_read": (i, [vp, C.POINTER(KernelTime), i, C.POINTER(i)]),
         "aet_network_launches_per_step": (i, [vp]),
         "aet_comm_unique_id": (i, [vp]), "aet_network_comm_init": (i, [vp, vp, i, i]),
+        "aet_network_comm_exchange_export": (i, [vp, vp]), "aet_network_comm_exchange_attach": (i, [vp, vp]),
         "aet_network_comm_destroy": (i, [vp]),
         "aet_network_grad_arena": (i, [vp, C.POINTER(vp), C.POINTER(C.c_size_t)]),
         "aet_backward_bias_static": (i, [vp, vp, C.c_longlong, i, vp]),
@@ -436,6 +438,17 @@ class NNetwork:
     def comm_init(self, unique_id, rank, world):
         buf = C.create_string_buffer(bytes(unique_id), 128)
         _check(self.L.aet_network_comm_init(self.h, buf, rank, world))
+
+    def comm_exchange_export(self):
+        """This rank's 80-byte blob for the peer exchange of the last gradient bucket."""
+        buf = C.create_string_buffer(80)
+        _check(self.L.aet_network_comm_exchange_export(self.h, buf))
+        return buf.raw
+
+    def comm_exchange_attach(self, blobs):
+        """`blobs`: every rank's export, in rank order."""
+        raw = b"".join(bytes(b) for b in blobs)
+        _check(self.L.aet_network_comm_exchange_attach(self.h, C.create_string_buffer(raw, len(raw))))
 
     def grad_arena(self):
         p, n = C.c_void_p(), C.c_size_t()

@@ -199,6 +199,16 @@ struct aet_network {
     int rank = 0, world = 1;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_grad_ready[8] = {nullptr}, ev_grad_ready_side[8] = {nullptr}, ev_comm_done = nullptr;
+    // Peer exchange of the last gradient bucket (the first layers' gradients, ready only at the very end
+    // of backward, where a collective's latency would be fully exposed): every rank publishes its slice
+    // in a buffer its peers have mapped, and the update kernel sums the ranks' slices itself.
+    bool xchg_active = false;
+    unsigned char *xchg_local = nullptr;        // [2][16] u64 flags, then two parity buffers of xchg_cap floats
+    unsigned char *xchg_peer[16] = {nullptr};   // the same region of every rank (own entry = xchg_local)
+    size_t xchg_cap = 0;
+    unsigned long long *xchg_epoch = nullptr;   // device-side step counter
+    unsigned int *xchg_ticket = nullptr;        // blocks of the publish kernel that have finished
+    size_t tail_lo = 0, tail_n = 0;             // arena range summed through the exchange this step (0: none)
     cudaEvent_t ev_uploaded = nullptr;   // after the H2D copies of a train step fed from the caller's pinned buffers
     long launches_per_step = 0;
 };
@@ -325,6 +335,8 @@ int k_step_counter(aet_context *ctx, unsigned long long *ctr);
 int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, float lr_over_b, float momentum,
                   float decay_term);
 int k_sgd_arena(aet_network *net);
+int k_tail_publish(aet_network *net);
+constexpr size_t kXchgFlagBytes = 1024;   // 2 x 16 u64 flags, padded
 int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev);
 
 // parameter pointers

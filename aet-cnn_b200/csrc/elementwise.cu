@@ -1085,8 +1085,53 @@ __global__ void dropout_bwd_kernel(float *d, const float *rnd, size_t n, float p
 // ---------------------------------------------------------------------------- SGD with momentum
 // u = U + G (+ decay_term * w for weights); w += rate * u; U = momentum * u; G = 0.
 // Same operation order as the three reference passes (U += -decay*B*W; W += lr/B*U; U *= momentum).
+// The slice of the gradient arena that is summed over the ranks inside the update kernel.
+struct TailArgs {
+    const float *peer_buf[16];                 // rank q's published slices (parity buffers back to back)
+    const volatile unsigned long long *flags;  // local [2][16]: flags[parity][q] = epoch once q has published
+    const unsigned long long *epoch;
+    unsigned long long lo, n, cap;
+    int world;
+    int *status;
+};
+
+// Copies this rank's slice into its published buffer and raises its flag in every peer's memory: data,
+// system-wide fence, ticket; the block that takes the last ticket writes the flags.  The parity alternates
+// with the step, so a rank that runs ahead never overwrites a buffer a slower peer still reads (it cannot
+// pass the next step's wait before that peer has published there).  Block 0 advances the epoch; the
+// others read it after the ticket of the previous launch has been reset, i.e. epoch + 1 is this launch.
+struct PublishArgs {
+    unsigned long long *peer_flags[8];
+    float *buf_local;
+    unsigned long long *epoch;
+    unsigned int *ticket;
+    int rank;
+};
+__global__ void __launch_bounds__(1024) tail_publish_kernel(const float *G, const TailArgs t, const PublishArgs p) {
+    pdl_enter();
+    const unsigned long long e = *p.epoch + 1ull, parity = e & 1ull;   // *epoch is only advanced by the last block, below
+    float *dst = p.buf_local + parity * t.cap;
+    for (unsigned long long i = ((unsigned long long)blockIdx.x * 1024ull + threadIdx.x) * 4ull; i < t.n; i += (unsigned long long)gridDim.x * 4096ull)
+        st4(dst + i, ld4(G + t.lo + i));
+    __syncthreads();
+    __shared__ bool last;
+    if (threadIdx.x == 0) {
+        __threadfence_system();   // cumulative: orders the whole block's copies (joined by the barrier) before the ticket
+        last = atomicAdd(p.ticket, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    if ((int)threadIdx.x < t.world && threadIdx.x < 8) {
+        __threadfence_system();   // after the last ticket every block's copies are ordered before the flags
+
+        volatile unsigned long long *f = p.peer_flags[threadIdx.x] + parity * 16ull + (unsigned long long)p.rank;
+        *f = e;
+    }
+    if (threadIdx.x == 0) { *p.epoch = e; *p.ticket = 0u; }
+}
+
 __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float *G, const int *block_seg,
-                                                       const float *seg_table, const float *hyper) {
+                                                       const float *seg_table, const float *hyper, const TailArgs t) {
     pdl_enter();
     const int seg = block_seg[blockIdx.x];
     const float rate = hyper[0] * seg_table[2 * seg];
@@ -1094,6 +1139,38 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
     const float decay_term = seg_table[2 * seg + 1] != 0.f ? hyper[2] : 0.f;
     const size_t i = ((size_t)blockIdx.x * TB + threadIdx.x) * 4;
     float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i);
+    const size_t b0 = (size_t)blockIdx.x * TB * 4;
+    if (t.world > 1 && b0 >= t.lo && b0 < t.lo + t.n) {
+        // this block's gradients are the sum of every rank's published slice, added in rank order
+        __shared__ int ok;
+        if (threadIdx.x == 0) ok = 1;
+        __syncthreads();
+        const unsigned long long e = *t.epoch, parity = e & 1ull;
+        if ((int)threadIdx.x < t.world) {
+            const volatile unsigned long long *f = t.flags + parity * 16ull + threadIdx.x;
+            unsigned long long t0 = 0;
+            unsigned int spins = 0;
+            while (*f < e) {
+                if ((++spins & 255u) == 0u) {
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > 1000000000ull) { ok = 0; break; }   // a peer never arrived: give up after a second
+                }
+            }
+            __threadfence_system();   // acquire: the peers' slices are read after their flags (the barrier passes it on)
+        }
+        __syncthreads();
+        if (!ok) {
+            if (threadIdx.x == 0 && t.status) atomicExch(t.status, AET_STATUS_TIMEOUT);
+            return;
+        }
+        g = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int q = 0; q < t.world; ++q) {
+            const float4 v = __ldcv(reinterpret_cast<const float4 *>(t.peer_buf[q] + parity * t.cap + (i - t.lo)));
+            g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
+        }
+    }
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
     u.x += decay_term * w.x; u.y += decay_term * w.y; u.z += decay_term * w.z; u.w += decay_term * w.w;
     w.x += rate * u.x; w.y += rate * u.y; w.z += rate * u.z; w.w += rate * u.w;
@@ -1544,9 +1621,31 @@ int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, 
 int k_sgd_arena(aet_network *net) {
     aet_context *ctx = net->ctx;
     LaunchScope s(ctx, "sgd_momentum", 24.0 * net->arena.used, 0);
+    TailArgs t = {};
+    if (net->xchg_active && net->tail_n) {
+        for (int q = 0; q < net->world; ++q) t.peer_buf[q] = reinterpret_cast<const float *>(net->xchg_peer[q] + kXchgFlagBytes);
+        t.flags = reinterpret_cast<const volatile unsigned long long *>(net->xchg_local);
+        t.epoch = net->xchg_epoch; t.lo = net->tail_lo; t.n = net->tail_n; t.cap = net->xchg_cap;
+        t.world = net->world; t.status = ctx->status_dev;
+    }
     launch_k(ctx->stream, net->n_blocks, TB, 0, sgd_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->block_seg,
-                                                           net->seg_table, net->hyper_dev);
+                                                           net->seg_table, net->hyper_dev, t);
     return aet_check_launch("sgd_momentum");
+}
+
+int k_tail_publish(aet_network *net) {
+    aet_context *ctx = net->ctx;
+    TailArgs t = {};
+    t.lo = net->tail_lo; t.n = net->tail_n; t.cap = net->xchg_cap; t.world = net->world;
+    PublishArgs p = {};
+    for (int q = 0; q < net->world && q < 8; ++q) p.peer_flags[q] = reinterpret_cast<unsigned long long *>(net->xchg_peer[q]);
+    p.buf_local = reinterpret_cast<float *>(net->xchg_local + kXchgFlagBytes);
+    p.epoch = net->xchg_epoch; p.ticket = net->xchg_ticket; p.rank = net->rank;
+    int blocks = (int)((net->tail_n + 4095) / 4096);
+    if (blocks > ctx->sm_count) blocks = ctx->sm_count;
+    LaunchScope s(ctx, "grad_publish", 8.0 * net->tail_n, 0);
+    launch_k(ctx->stream, blocks, 1024, 0, tail_publish_kernel, net->arena.G, t, p);
+    return aet_check_launch("grad_publish");
 }
 
 int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev) {

@@ -242,13 +242,16 @@ int net_backward(aet_network *net, aet_state state) {
     aet_context *ctx = net->ctx;
     ctx->overlap_wgrad = !getenv("AET_NO_OVERLAP");
     ctx->in_network_pass = true;
+    // A gradient arena that fits the peer-exchange buffer is exchanged in one piece at the end of backward
+    // (one synchronisation of the ranks per step, no collective kernels beside the backward pass).
+    const bool whole = dp && net->xchg_active && net->arena.used <= net->xchg_cap;
     for (int i = (int)net->layers.size() - 1; i >= 0; --i) {
         aet_layer *l = net->layers[i];
         state.index = i;
         if (i == 0) { state.input = original_input; state.delta = original_delta; }
         else { state.input = net->layers[i - 1]->output; state.delta = net->layers[i - 1]->delta; }
         int br = aet_layer_backward(l, state);
-        if (br == AET_OK && dp && l->type == AET_CONVOLUTIONAL) {
+        if (br == AET_OK && dp && !whole && l->type == AET_CONVOLUTIONAL) {
             const ParamSegment &last = l->bn ? l->seg_s : l->seg_b;
             const size_t lo = l->seg_w.offset, hi = last.offset + last.padded;
             if (pend_hi == pend_lo) { pend_lo = lo; pend_hi = hi; }
@@ -267,13 +270,21 @@ int net_backward(aet_network *net, aet_state state) {
     }
     ctx->overlap_wgrad = false;
     ctx->in_network_pass = false;
-    if (dp && pend_hi > pend_lo) AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
+    // The last bucket holds the first layers' gradients, complete only now: a collective here would be fully
+    // exposed, so with a peer exchange attached the ranks publish it and the update kernel sums it.
+    net->tail_n = 0;
+    if (whole) { net->tail_lo = 0; net->tail_n = net->arena.used; }
+    else if (dp && pend_hi > pend_lo) {
+        if (net->xchg_active && pend_hi - pend_lo <= net->xchg_cap) { net->tail_lo = pend_lo; net->tail_n = pend_hi - pend_lo; }
+        else AET_TRY(issue_allreduce(net, pend_lo, pend_hi, slot++));
+    }
     AET_TRY(side_join(ctx));
-    if (dp) {
+    if (dp && slot > 0) {
         AET_CUDA(cudaEventRecord(net->ev_comm_done, net->comm_stream));
         AET_CUDA(cudaStreamWaitEvent(net->ctx->stream, net->ev_comm_done, 0));
         pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
     }
+    if (net->tail_n) AET_TRY(k_tail_publish(net));
     return AET_OK;
 }
 
@@ -285,6 +296,7 @@ int run_step(aet_network *net) {
     AET_TRY(net_backward(net, st));
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(k_sgd_arena(net));
+    net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
     return AET_OK;
 }
 
@@ -545,6 +557,7 @@ extern "C" int aet_network_update(aet_network *net) {
     AET_TRY(upload_hyper(net));
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(k_sgd_arena(net));
+    net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
     return AET_OK;
 }
 extern "C" float aet_network_cost(aet_network *net) {
@@ -759,11 +772,85 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     return AET_OK;
 }
 
+// ---- peer exchange of the last gradient bucket
+struct XchgBlob {            // what a rank hands to its peers (80 bytes)
+    cudaIpcMemHandle_t handle;
+    unsigned char uuid[16];  // ranks must sit on different GPUs: their update kernels wait for one another
+};
+static_assert(sizeof(XchgBlob) == 80, "exchange blob layout");
+
+extern "C" int aet_network_comm_exchange_export(aet_network *net, void *blob_80) {
+    if (!net || !blob_80) { aet_set_error("aet_network_comm_exchange_export: null argument"); return AET_E_INVALID; }
+    if (!net->comm || net->world < 2 || net->world > 8) { aet_set_error("peer exchange needs an initialised communicator of 2..8 ranks"); return AET_E_INVALID; }
+    AET_CUDA(cudaSetDevice(net->ctx->device));
+    if (!net->xchg_local) {
+        net->xchg_cap = 1024 * 1024;   // floats per parity buffer: gradient arenas up to 4 MB are exchanged whole
+        if (const char *e = getenv("AET_XCHG_CAP_FLOATS")) {   // tuning aid: a small value leaves only the last bucket to the exchange
+            const long v = atol(e);
+            if (v >= 1024 && v <= 16 * 1024 * 1024) net->xchg_cap = (size_t)v / 1024 * 1024;
+        }
+        const size_t bytes = kXchgFlagBytes + 2 * net->xchg_cap * sizeof(float);
+        AET_CUDA(cudaMalloc(&net->xchg_local, bytes));
+        AET_CUDA(cudaMemset(net->xchg_local, 0, bytes));
+        AET_CUDA(cudaMalloc(&net->xchg_epoch, sizeof(unsigned long long)));
+        AET_CUDA(cudaMemset(net->xchg_epoch, 0, sizeof(unsigned long long)));
+        AET_CUDA(cudaMalloc(&net->xchg_ticket, sizeof(unsigned int)));
+        AET_CUDA(cudaMemset(net->xchg_ticket, 0, sizeof(unsigned int)));
+        AET_CUDA(cudaDeviceSynchronize());
+    }
+    XchgBlob b;
+    memset(&b, 0, sizeof(b));
+    AET_CUDA(cudaIpcGetMemHandle(&b.handle, net->xchg_local));
+    cudaDeviceProp prop;
+    AET_CUDA(cudaGetDeviceProperties(&prop, net->ctx->device));
+    memcpy(b.uuid, &prop.uuid, 16);
+    memcpy(blob_80, &b, sizeof(b));
+    return AET_OK;
+}
+
+extern "C" int aet_network_comm_exchange_attach(aet_network *net, const void *blobs_world_x_80) {
+    if (!net || !blobs_world_x_80 || !net->xchg_local) { aet_set_error("aet_network_comm_exchange_attach: export first"); return AET_E_INVALID; }
+    const XchgBlob *b = static_cast<const XchgBlob *>(blobs_world_x_80);
+    for (int p = 0; p < net->world; ++p)
+        for (int q = p + 1; q < net->world; ++q)
+            if (memcmp(b[p].uuid, b[q].uuid, 16) == 0) {
+                aet_set_error("peer exchange refused: ranks %d and %d share a GPU (their kernels would wait for one another on one device)", p, q);
+                return AET_E_INVALID;
+            }
+    AET_CUDA(cudaSetDevice(net->ctx->device));
+    for (int q = 0; q < net->world; ++q) {
+        if (q == net->rank) { net->xchg_peer[q] = net->xchg_local; continue; }
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, b[q].handle, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            aet_set_error("cudaIpcOpenMemHandle for rank %d failed: %s", q, cudaGetErrorString(e));
+            cudaGetLastError();
+            return AET_E_CUDA;
+        }
+        net->xchg_peer[q] = static_cast<unsigned char *>(ptr);
+    }
+    net->xchg_active = true;
+    graph_drop(net);
+    return AET_OK;
+}
+
+static void xchg_release(aet_network *net) {
+    net->xchg_active = false;
+    for (int q = 0; q < 16; ++q) {
+        if (net->xchg_peer[q] && net->xchg_peer[q] != net->xchg_local) cudaIpcCloseMemHandle(net->xchg_peer[q]);
+        net->xchg_peer[q] = nullptr;
+    }
+    if (net->xchg_local) { cudaFree(net->xchg_local); net->xchg_local = nullptr; }
+    if (net->xchg_epoch) { cudaFree(net->xchg_epoch); net->xchg_epoch = nullptr; }
+    if (net->xchg_ticket) { cudaFree(net->xchg_ticket); net->xchg_ticket = nullptr; }
+}
+
 extern "C" int aet_network_comm_destroy(aet_network *net) {
     if (!net || !net->comm) return AET_OK;
     cudaStreamSynchronize(net->ctx->stream);
     cudaStreamSynchronize(net->comm_stream);
     graph_drop(net);
+    xchg_release(net);
     NcclApi *api = nccl_api();
     if (api) api->comm_destroy(net->comm);
     net->comm = nullptr; net->world = 1; net->rank = 0;

@@ -30,6 +30,16 @@ def exchange_unique_id(make_id, nbytes=128):
     return bytes(buf.cpu().numpy().tobytes())
 
 
+def all_gather_bytes(raw):
+    """Every rank's byte string (all of one length), in rank order."""
+    if not is_dist() or dist.get_world_size() == 1:
+        return [bytes(raw)]
+    mine = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(_dev())
+    parts = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, mine)
+    return [bytes(p.cpu().numpy().tobytes()) for p in parts]
+
+
 def max_over_ranks(value):
     """The slowest rank's time: multi-GPU numbers are the max over ranks, never a wall clock."""
     if not is_dist() or dist.get_world_size() == 1:

@@ -258,6 +258,10 @@ def main():
     import aet_cnn_b200.parallel as par
     if world > 1:
         net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
+        if world <= 8 and os.environ.get("AET_PEER_EXCHANGE"):
+            # opt-in: gradients summed through peer-mapped buffers inside the update kernel instead of by NCCL
+            # (measured at 8 GPUs: 0.301 ms per step against 0.294 with NCCL alone, so NCCL stays the default)
+            net.comm_exchange_attach(par.all_gather_bytes(net.comm_exchange_export()))
 
     batch = args.batch
     host_batches, pinned_keep = [], []

@@ -209,6 +209,14 @@ int   aet_network_launches_per_step(const aet_network *net);
  * layer bucket during backward on a side stream.  `unique_id` is the 128-byte ncclUniqueId. */
 int   aet_comm_unique_id(void *unique_id_128);
 int   aet_network_comm_init(aet_network *net, const void *unique_id_128, int rank, int world);
+/* Optional, after aet_network_comm_init on 2..8 ranks that sit on DIFFERENT GPUs of one box (no counterpart in
+ * the reference, which is single-GPU): the last gradient bucket of a step (the first layers', complete only when
+ * backward ends) is summed over the ranks inside the update kernel through peer-mapped buffers instead of by a
+ * collective whose latency nothing could hide.  Every rank exports an 80-byte blob (CUDA IPC handle + device
+ * UUID), the caller gathers the blobs in rank order by any host channel and hands all of them to attach.  Attach
+ * refuses ranks that share a GPU.  Without attach the bucket goes through the all-reduce like the others. */
+int   aet_network_comm_exchange_export(aet_network *net, void *blob_80);
+int   aet_network_comm_exchange_attach(aet_network *net, const void *blobs_world_x_80);
 int   aet_network_comm_destroy(aet_network *net);
 /* Device pointer and float count of the gradient arena (for callers that run their own collective). */
 int   aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count);
