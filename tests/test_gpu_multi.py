@@ -1,0 +1,28 @@
+"""Two-GPU data parallel through the C ABI (skipped on a box with one GPU): NCCL all-reduce against the peer
+exchange fused into the update kernel."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_two_ranks_nccl_and_peer_exchange_agree():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29633", os.path.join(here, "multi_gpu_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    out = json.loads(line[len("RESULT "):])
+    for mode in ("nccl", "peer"):
+        assert out[mode]["identical_across_ranks"], mode          # weights bitwise identical on both ranks
+    assert out["nccl"]["hash"] == out["peer"]["hash"]             # two ranks: the same sum either way
+    assert out["nccl"]["losses"] == out["peer"]["losses"]
