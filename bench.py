@@ -56,10 +56,10 @@ TF32_PEAK_TFLOPS = 692.3
 # workload (profiles/), keyed by kernel label; null when the dominant kernel has no capture yet.
 NCU_TRAFFIC_BYTES = {   # "kernel label#layer index" of the small CNN at batch 128
     "conv_fprop_thin#0": 2.17e6, "conv_wgrad_thin#0": 35.68e6,
-    "conv_fprop_tma_rows#2": 8.73e6, "conv_dgrad_tma_rows#2": 17.10e6, "conv_wgrad_tma_rows#2": 25.19e6,
-    "conv_fprop_tma_rows#4": 5.42e6, "conv_dgrad_tma_rows#4": 9.59e6, "conv_wgrad_tma_rows#4": 12.61e6,
-    "bn_act_maxpool_fwd#0": 33.58e6, "bn_bwd_reduce_poolwin#0": 50.43e6, "bn_bwd_apply_poolwin#0": 53.75e6,
-    "bn_bwd_apply_poolwin#2": 25.19e6,
+    "conv_fprop_tma_rows#2": 8.75e6, "conv_dgrad_tma_rows#2": 17.11e6, "conv_wgrad_tma_rows#2": 25.19e6,
+    "conv_fprop_tma_rows#4": 5.44e6, "conv_dgrad_tma_rows#4": 9.60e6, "conv_wgrad_tma_rows#4": 12.61e6,
+    "bn_act_maxpool_fwd#0": 33.58e6, "bn_bwd_reduce_poolwin#0": 50.37e6, "bn_bwd_apply_poolwin#0": 53.28e6,
+    "bn_bwd_reduce_poolwin#2": 25.18e6, "bn_bwd_apply_poolwin#2": 25.18e6, "bn_bwd_apply_poolwin#4": 12.60e6,
 }
 
 
