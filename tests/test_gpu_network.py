@@ -288,3 +288,26 @@ def test_alexnet_style_reduced_step(aet, ctx, oracle):
     for i in (0, 2, 8, 12):     # coarse: relu kinks and argmax ties upstream flip under TF32 rounding
         assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 0.2, i
     net.close()
+
+
+def test_train_step_from_pinned_and_pageable_buffers_is_the_same(aet, ctx, oracle):
+    """aet_network_train_step copies by DMA straight from page-locked caller buffers and through the
+    context's pinned mirror otherwise: same losses, same weights, bit for bit."""
+    import torch
+    batch = 8
+    hashes, losses = [], []
+    for pinned in (False, True):
+        net, _, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+        keep, ls = [], []
+        for step in range(4):
+            x, t = batch_for(opts, 10, batch, 11, step)
+            if pinned:
+                xt, tt = torch.from_numpy(x).pin_memory(), torch.from_numpy(t).pin_memory()
+                keep += [xt, tt]
+                x, t = xt.numpy(), tt.numpy()
+            ls.append(net.train(x, t))
+        ctx.check()
+        hashes.append(net.param_hash()); losses.append(ls)
+        net.close()
+    assert losses[0] == losses[1]
+    assert hashes[0] == hashes[1]
