@@ -57,7 +57,7 @@ struct ConvArgs {
 struct SharedCtl {
     unsigned long long full[MAX_STAGES];
     unsigned long long empty[MAX_STAGES];
-    unsigned long long accum, stat_bar;
+    unsigned long long accum, stat_bar, stat_bar2;
     uint32_t tmem_base;
     int abort_flag;
     int4 jtab[64];  // wgrad: per 4-column chunk of the N tile -> {r, s, c, valid}

@@ -230,13 +230,15 @@ struct FdRowsArgs {
     int slabs_per_s;               // ceil(inner / 32)
     int mt, bh, bi, w, pix_per_img, n_img;
     int ksplit;                    // 1, or 2: the two CTAs of a cluster (grid z) take half of the K slabs each
+    int par_epi;                   // mt == 2 with nine warps: warps 5-8 store the second pixel tile while warps 0-3 store the first
     int stages, tmem_cols;
     uint32_t a_bytes, b_tile_bytes, tx_bytes;
     int *status;
 };
 
+constexpr int FD_THREADS_WIDE = 288;   // five warps + a second epilogue group
 template <int KIND>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(FD_THREADS_WIDE, 1)
 conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const FdRowsArgs a) {
     extern __shared__ unsigned char smem_raw[];
@@ -265,6 +267,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         mbar_init(smem_u32(&ctl.accum), 1);
         mbar_init(smem_u32(&ctl.stat_bar), 4);
+        mbar_init(smem_u32(&ctl.stat_bar2), 4);
         ctl.abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_a);
@@ -281,7 +284,8 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
-    if (warp < 4) {
+    if (warp != 4) {
+        const int q = warp & 3, grp = warp < 4 ? 0 : 1;   // TMEM lane quarter; which pixel tile this warp stores
         if (threadIdx.x == 0) {
             for (int it = 0; it < nslabs; ++it) {
                 const int s = it % a.stages;
@@ -312,7 +316,19 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         epilogue_ready = ready;
         if (ready && a.ksplit > 1) {
             // only stage the accumulator (mt == 1 here); the sum of the two halves is stored after the cluster barrier
-            stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, warp, lane, bn);
+            stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, q, lane, bn);
+        } else if (ready && a.par_epi) {
+            // two epilogue groups, one pixel tile each, side by side in the (now idle) stage memory
+            float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))) + (size_t)grp * BM * (bn + 4);
+            StatAcc st;
+            stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
+            const int mt0 = m0 + grp * BM;
+            store_accumulator<KIND == KIND_FPROP>(tile, tmem + (uint32_t)(grp * bn), true, q, lane, bn, a.out + (size_t)mt0 * a.out_ld,
+                                                  (size_t)a.out_ld, a.n_rows - mt0, n0, a.n_cols, a.bias, a.act, a.bi, a.w,
+                                                  a.pix_per_img, &st);
+            if (KIND == KIND_FPROP && st.shift)   // each group writes its own partial row
+                stats_commit(tile, st, q, lane, bn, a.stat_partial + ((size_t)blockIdx.x * 2 + grp) * 2 * a.out_ld + n0, a.out_ld,
+                             a.n_cols - n0, grp ? &ctl.stat_bar2 : &ctl.stat_bar, abort_flag);
         } else if (ready) {
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
             StatAcc st;
@@ -474,6 +490,8 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     t.R = g.R; t.S = g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
     t.stages = stages; t.tmem_cols = pow2_cols(mt * bn); t.ksplit = ksplit;
+    t.par_epi = (mt == 2 && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && !getenv("AET_NO_PAR_EPILOGUE")) ? 1 : 0;
+    const int threads = t.par_epi ? FD_THREADS_WIDE : NTHREADS;
     t.a_bytes = a_bytes; t.b_tile_bytes = b_tile; t.tx_bytes = a_bytes + (uint32_t)g.R * b_tile;
     t.status = ctx->status_dev;
     const size_t smem_bytes = stage * stages + 1024;
@@ -483,11 +501,11 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         attr_set = true;
     }
     dim3 grid((m_tiles + mt - 1) / mt, n_tiles, ksplit);
-    if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x;
+    if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x * (t.par_epi ? 2 : 1);
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
     LaunchScope scope(ctx, name, 0, flops);
-    if (ksplit > 1) launch_k_cluster(ctx->stream, grid, NTHREADS, smem_bytes, ksplit, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
-    else launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
+    if (ksplit > 1) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, ksplit, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
+    else launch_k(ctx->stream, grid, threads, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);
 }
 
