@@ -230,6 +230,8 @@ struct FdRowsArgs {
     int slabs_per_s;               // ceil(inner / 32)
     int mt, bh, bi, w, pix_per_img, n_img;
     int ksplit;                    // 1, or 2: the two CTAs of a cluster (grid z) take half of the K slabs each
+    int smerge_S;                  // data gradient of a narrow layer: the S column taps ride in one MMA of N = S * channels
+                                   // (0 = off); the epilogue adds the S column blocks, each shifted by its tap
     int par_epi;                   // mt == 2 with nine warps: warps 5-8 store the second pixel tile while warps 0-3 store the first
     int stages, tmem_cols;
     uint32_t a_bytes, b_tile_bytes, tx_bytes;
@@ -298,13 +300,14 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int slab = slab_begin + it;
                 const int st = slab / a.slabs_per_s, cb = slab - st * a.slabs_per_s;   // column tap, channel slab
                 // fprop reads input pixel (h + r - pad, w + s - pad); dgrad reads delta pixel (h + pad - r, w + pad - s)
-                const int wx = KIND == KIND_FPROP ? st - a.pad : a.pad - st;
+                const int wx = a.smerge_S ? 0 : (KIND == KIND_FPROP ? st - a.pad : a.pad - st);
                 const int hy = KIND == KIND_FPROP ? row0 - a.pad : row0 + a.pad - (a.R - 1);
                 if (a.bi > 1) tma_load_4d(sa, &map_a, bar, cb * 32, wx, img0, hy);      // dims (c, w, n, h)
                 else          tma_load_4d(sa, &map_a, bar, cb * 32, wx, hy, img0);      // dims (c, w, h, n)
                 for (int r = 0; r < a.R; ++r) {
                     const int tap = r * a.S + st;
                     if (KIND == KIND_FPROP) tma_load_2d(sb + r * a.b_tile_bytes, &map_b, bar, tap * a.inner + cb * 32, n0);
+                    else if (a.smerge_S)    tma_load_4d(sb + r * a.b_tile_bytes, &map_b, bar, 0, cb * 32, 0, r);   // dims (n%32, filter, n/32, r)
                     else                    tma_load_4d(sb + r * a.b_tile_bytes, &map_b, bar, 0, cb * 32, n0 / 32, tap);
                 }
             }
@@ -317,6 +320,49 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (ready && a.ksplit > 1) {
             // only stage the accumulator (mt == 1 here); the sum of the two halves is stored after the cluster barrier
             stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, q, lane, bn);
+        } else if (ready && a.smerge_S) {
+            // Column taps merged into N: accumulator column block s holds the partial result that belongs to
+            // the output pixel pad - s columns further on.  The four warps of a group stage their tile, then every
+            // row adds its (up to) S neighbours' blocks; a tile is whole image rows, so the neighbours are rows
+            // +-1.. of the same tile.  With two pixel tiles the two warp groups work side by side.
+            const int pitch = bn + 4;
+            float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))) + (size_t)grp * BM * pitch;
+            const int cpn = bn / a.smerge_S;
+            const int lpr = cpn >= 128 ? 32 : cpn / 4, rpi = 32 / lpr, sub = lane / lpr, lcol = (lane - sub * lpr) * 4;
+            unsigned long long *bar = grp ? &ctl.stat_bar2 : &ctl.stat_bar;
+            stage_accumulator(tile, tmem + (uint32_t)(grp * bn), true, q, lane, bn);
+            if (lane == 0) mbar_arrive(smem_u32(bar));
+            bool ok = mbar_wait(smem_u32(bar), 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                const int mt0 = m0 + grp * BM, rows_valid = a.n_rows - mt0;
+                float *out = a.out + (size_t)mt0 * a.out_ld;
+                for (int c0 = 0; c0 < cpn; c0 += 128) {
+                    const int c = c0 + lcol;
+                    const bool active = c < cpn && c < a.n_cols && sub < rpi;
+                    for (int r0 = 0; r0 < 32; r0 += 4 * rpi) {
+                        float4 v[4];
+                        int rows[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int row = q * 32 + r0 + u * rpi + sub;
+                            rows[u] = (active && r0 + u * rpi + sub < 32 && row < rows_valid) ? row : -1;
+                            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (rows[u] < 0) continue;
+                            const int wcol = row % a.w;
+                            for (int sx = 0; sx < a.smerge_S; ++sx) {
+                                const int d = a.pad - sx;              // this block's contribution comes from column w + d
+                                if ((unsigned)(wcol + d) >= (unsigned)a.w) continue;
+                                const float4 q4 = *reinterpret_cast<const float4 *>(tile + (size_t)(row + d) * pitch + sx * cpn + c);
+                                v[u].x += q4.x; v[u].y += q4.y; v[u].z += q4.z; v[u].w += q4.w;
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (rows[u] >= 0) *reinterpret_cast<float4 *>(out + (size_t)rows[u] * a.out_ld + c) = v[u];
+                    }
+                }
+            }
         } else if (ready && a.par_epi) {
             // two epilogue groups, one pixel tile each, side by side in the (now idle) stage memory
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))) + (size_t)grp * BM * (bn + 4);
@@ -426,6 +472,24 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     uint32_t a_bytes = 0, b_tile = 0;
     size_t stage = 0;
     const int total_slabs = g.S * ((inner + 31) / 32);
+    // Data gradient of a narrow layer (few input channels): an MMA of N = 64 costs as much as one of N = 128, so the S
+    // column taps are merged into one MMA of N = S * channels; the activations then cross L2 once per channel slab
+    // instead of once per column tap, and the epilogue adds the S column blocks with their column shifts.
+    int smerge = 0;
+    if (KIND == KIND_DGRAD && bi == 1 && g.S == g.R && g.pad == (g.S - 1) / 2 && g.cp % 32 == 0 && g.cp < 128 && g.S * g.cp <= 256 &&
+        a.n_cols == g.cp && !getenv("AET_NO_SMERGE")) {
+        const int c = g.S * g.cp;
+        int m = (g.H % (2 * (int)bh) == 0 && 2 * c <= 512 && (m_tiles / 2) >= (ctx->sm_count * 3) / 4) ? 2 : 1;
+        for (; m >= 1 && !smerge; --m) {
+            const uint32_t ab = (uint32_t)(m * (int)bh + g.R - 1) * bi * g.W * 128u;
+            const size_t st = (size_t)ab + (size_t)g.R * c * 128u;
+            int ns = (int)((220 * 1024) / st);
+            if (ns > 4) ns = 4;
+            if (ns >= 2 && st * ns >= (size_t)m * BM * (c + 4) * 4 && (m_tiles + m - 1) / m <= ctx->sm_count) {   // one staging tile per pixel tile
+                bn = c; mt = m; stages = ns; n_tiles = 1; a_bytes = ab; b_tile = (uint32_t)c * 128u; stage = st; smerge = g.S;
+            }
+        }
+    }
     for (int i = 0; i < 4 && !bn; ++i) {
         const int c = cands[i];
         if (c > full || (KIND == KIND_DGRAD && (c % 32 || g.cp % c))) continue;
@@ -471,7 +535,13 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         cuuint32_t box[4] = {32, (cuuint32_t)g.W, (cuuint32_t)super_rows, 1};
         AET_TRY(get_map(l, KIND == KIND_FPROP ? 8 : 10, act, 4, dims, str, box, false, &ma));
     }
-    if (KIND == KIND_FPROP) {
+    if (smerge) {
+        const int taps = g.R * g.S;
+        cuuint64_t dims[4] = {32, (cuuint64_t)g.K, (cuuint64_t)(g.S * g.cp) / 32, (cuuint64_t)g.R};
+        cuuint64_t str[3] = {(cuuint64_t)taps * g.cp * 4, 128, (cuuint64_t)g.S * g.cp * 4};
+        cuuint32_t box[4] = {32, 32, (cuuint32_t)bn / 32, 1};
+        AET_TRY(get_map(l, 13, a.src_b, 4, dims, str, box, true, &mb));
+    } else if (KIND == KIND_FPROP) {
         cuuint64_t dims[2] = {(cuuint64_t)a.k_total, (cuuint64_t)g.K};
         cuuint64_t str[1] = {(cuuint64_t)a.k_total * 4};
         cuuint32_t box[2] = {32, (cuuint32_t)bn};
@@ -487,11 +557,12 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     t.out = a.out; t.bias = KIND == KIND_FPROP ? a.bias : nullptr; t.act = KIND == KIND_FPROP ? a.act : (int)AET_LINEAR;
     t.stat_shift = KIND == KIND_FPROP ? a.stat_shift : nullptr; t.stat_partial = KIND == KIND_FPROP ? a.stat_partial : nullptr;
     t.bn = bn; t.n_rows = a.n_rows; t.n_cols = a.n_cols; t.out_ld = a.out_ld;
-    t.R = g.R; t.S = g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
+    t.R = g.R; t.S = smerge ? 1 : g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
+    t.smerge_S = smerge;
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
     t.stages = stages; t.tmem_cols = pow2_cols(mt * bn); t.ksplit = ksplit;
-    t.par_epi = (mt == 2 && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && !getenv("AET_NO_PAR_EPILOGUE")) ? 1 : 0;
-    const int threads = t.par_epi ? FD_THREADS_WIDE : NTHREADS;
+    t.par_epi = (mt == 2 && !smerge && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && !getenv("AET_NO_PAR_EPILOGUE")) ? 1 : 0;
+    const int threads = (t.par_epi || (smerge && mt == 2)) ? FD_THREADS_WIDE : NTHREADS;
     t.a_bytes = a_bytes; t.b_tile_bytes = b_tile; t.tx_bytes = a_bytes + (uint32_t)g.R * b_tile;
     t.status = ctx->status_dev;
     const size_t smem_bytes = stage * stages + 1024;
