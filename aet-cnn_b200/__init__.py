@@ -27,7 +27,7 @@ MATH_TF32, MATH_3XTF32 = 0, 1
 # every symbol include/aet_b200.h declares
 EXPORTS = """aet_last_error aet_version aet_context_create aet_context_destroy aet_context_set_stream
 aet_context_stream aet_context_set_parity aet_context_set_math aet_context_synchronize aet_context_check
-aet_context_profile aet_context_profile_read aet_context_launch_count
+aet_context_profile aet_context_profile_read aet_context_launch_count aet_context_set_option aet_context_get_option aet_context_set_wait_limit aet_context_wait_probe
 aet_tensor_create aet_tensor_destroy aet_tensor_shape aet_tensor_write aet_tensor_read aet_tensor_zero
 aet_tensor_count aet_convolutional_layer_create aet_maxpool_layer_create aet_avgpool_layer_create
 aet_softmax_layer_create aet_dropout_layer_create aet_layer_destroy aet_layer_forward aet_layer_backward
@@ -37,7 +37,7 @@ aet_layer_save_weights aet_network_create aet_network_create_from_string aet_net
 aet_network_destroy aet_network_layer_count aet_network_layer aet_network_batch aet_network_input_shape
 aet_network_outputs aet_network_input aet_network_truth aet_network_learning_rate aet_network_set_hyper
 aet_network_seen aet_network_forward aet_network_backward aet_network_update aet_network_cost
-aet_network_train_step aet_network_train_step_device aet_network_last_loss aet_network_predict
+aet_network_train_step aet_network_train_step_async aet_network_train_step_device aet_network_last_loss aet_network_predict
 aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
 aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static
@@ -81,6 +81,9 @@ def lib():
         "aet_context_profile": (i, [vp, i]),
         "aet_context_profile_read": (i, [vp, C.POINTER(KernelTime), i, C.POINTER(i)]),
         "aet_context_launch_count": (C.c_long, [vp]),
+        "aet_context_set_option": (i, [vp, C.c_char_p, i]),
+        "aet_context_get_option": (i, [vp, C.c_char_p, C.POINTER(i)]),
+        "aet_context_set_wait_limit": (i, [vp, C.c_ulonglong]), "aet_context_wait_probe": (i, [vp]),
         "aet_tensor_create": (vp, [vp, i, i, i, i]), "aet_tensor_destroy": (None, [vp]),
         "aet_tensor_shape": (i, [vp] + [C.POINTER(i)] * 4), "aet_tensor_write": (i, [vp, vp]),
         "aet_tensor_read": (i, [vp, vp]), "aet_tensor_zero": (i, [vp]), "aet_tensor_count": (C.c_size_t, [vp]),
@@ -110,6 +113,7 @@ def lib():
         "aet_network_update": (i, [vp]), "aet_network_cost": (f, [vp]),
         "aet_network_train_step": (i, [vp, vp, vp, C.POINTER(f)]),
         "aet_network_train_step_device": (i, [vp, C.POINTER(f)]),
+        "aet_network_train_step_async": (i, [vp, vp, vp, C.POINTER(f)]),
         "aet_network_last_loss": (i, [vp, C.POINTER(f)]),
         "aet_network_predict": (i, [vp, vp, vp]), "aet_network_use_graph": (i, [vp, i]),
         "aet_network_load_weights": (i, [vp, C.c_char_p]), "aet_network_save_weights": (i, [vp, C.c_char_p]),
@@ -161,6 +165,21 @@ class Context:
 
     def set_math(self, math):
         _check(self.L.aet_context_set_math(self.h, math))
+
+    def set_option(self, name, value):
+        """Behaviour switch by name (kernel choice, fusions, stream overlap); see include/aet_b200.h."""
+        _check(self.L.aet_context_set_option(self.h, name.encode(), int(value)))
+
+    def get_option(self, name):
+        v = C.c_int()
+        _check(self.L.aet_context_get_option(self.h, name.encode(), C.byref(v)))
+        return v.value
+
+    def set_wait_limit(self, nanoseconds):
+        _check(self.L.aet_context_set_wait_limit(self.h, int(nanoseconds)))
+
+    def wait_probe(self):
+        _check(self.L.aet_context_wait_probe(self.h))
 
     def synchronize(self):
         _check(self.L.aet_context_synchronize(self.h))
@@ -392,6 +411,16 @@ class NNetwork:
         x, truth = _f32(x), _f32(truth)
         _check(self.L.aet_network_train_step(self.h, x.ctypes.data_as(C.c_void_p), truth.ctypes.data_as(C.c_void_p),
                                              C.byref(self._loss)))
+        return self._loss.value
+
+    def train_async(self, x, truth):
+        """Pipelined train step: queues this batch (its upload overlaps the previous step) and returns the
+        PREVIOUS call's mean loss (NaN on the first call).  `x` and `truth` must be float32 C-contiguous arrays;
+        page-locked ones must stay unchanged until the next call returns."""
+        if x.dtype != np.float32 or truth.dtype != np.float32 or not x.flags.c_contiguous or not truth.flags.c_contiguous:
+            raise AetError("train_async: float32 C-contiguous arrays required (the copy is asynchronous)")
+        _check(self.L.aet_network_train_step_async(self.h, x.ctypes.data_as(C.c_void_p), truth.ctypes.data_as(C.c_void_p),
+                                                   C.byref(self._loss)))
         return self._loss.value
 
     def train_device(self, want_loss=True):

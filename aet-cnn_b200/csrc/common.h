@@ -15,7 +15,11 @@
 #include "../../include/aet_b200.h"
 #include <utility>
 
-#define AET_STATUS_TIMEOUT 1
+// bits of the device status word
+#define AET_STATUS_TIMEOUT 1   // a bounded wait expired
+#define AET_STATUS_NAN 2       // the update found (and scrubbed) non-finite values
+constexpr int kPinnedFloats = 64;
+constexpr int kHyperSlots = 8;
 
 void aet_set_error(const char *fmt, ...);
 
@@ -38,14 +42,42 @@ static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 static inline size_t round_up_sz(size_t v, size_t m) { return (v + m - 1) / m * m; }
 
 struct ProfileRecord {
-    const char *name;
+    char name[40];        // kernel label, with ".variant" appended when the launcher chose among code paths
     int tag;              // index of the network layer the launch belongs to, or -1
     double bytes, flops;
     cudaEvent_t e0, e1;
 };
 
+// Behaviour switches of a context (kernel choice, fusions, overlap).  Each has a name for
+// aet_context_set_option and an environment variable that is read ONCE, when the context is created, and only
+// supplies the initial value; nothing on a launch path reads the environment.
+enum AetOption {
+    OPT_ROWS = 0,          // row-sharing TMA kernels                         AET_NO_ROWS
+    OPT_ROWS_FPROP,        //   ... for the forward pass                      AET_NO_ROWS_F
+    OPT_ROWS_DGRAD,        //   ... for the data gradient                     AET_NO_ROWS_D
+    OPT_SMERGE,            // column taps merged into the MMA's N (narrow data gradients)   AET_NO_SMERGE
+    OPT_KSPLIT,            // K range split over a two-CTA cluster            AET_NO_KSPLIT
+    OPT_MT2,               // two pixel tiles per CTA                         AET_NO_MT2
+    OPT_ROWS_MULTI,        // allow the row-sharing kernels more than one wave    AET_ROWS_MULTI
+    OPT_PAR_EPILOGUE,      // second epilogue warp group                      AET_NO_PAR_EPILOGUE
+    OPT_FC_ALIAS,          // whole-map filters run as 1x1 convolutions       AET_NO_FC_ALIAS
+    OPT_EPILOGUE_STATS,    // batch-norm statistics gathered by the convolution's epilogue   AET_NO_EPILOGUE_STATS
+    OPT_THIN,              // persistent first-layer kernels                  AET_NO_THIN
+    OPT_OVERLAP_WGRAD,     // weight-gradient kernels on a second stream      AET_NO_OVERLAP
+    OPT_WGRAD_SPLITS,      // forced K-split count of the row-sharing weight gradient (0 = automatic)   AET_WGRAD_SPLITS
+    OPT_BN_TILE,           // forced N tile of the gather / plain TMA kernels (0 = automatic)           AET_BN
+    OPT_FUSE,              // network-level fusions (BN + pool, classifier head), read when a network is built   AET_NO_FUSE
+    OPT_LINEAR_HEAD,       // classifier head on the pooled vectors, read when a network is built          AET_NO_LINEAR_HEAD
+    OPT_XCHG_CAP_FLOATS,   // capacity of the peer-exchange buffer (0 = default)   AET_XCHG_CAP_FLOATS
+    OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice)   AET_NCCL_MAX_CTAS
+    OPT_PERSISTENT,        // persistent row-sharing kernels (tile scheduler, overlapped epilogue)   AET_NO_PERSISTENT
+    OPT_COUNT
+};
+
 struct aet_context {
     int device = 0;
+    int opt[OPT_COUNT] = {0};
+    std::vector<const void *> smem_attr_done;   // kernels whose dynamic shared-memory limit was raised on this device
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     bool owns_stream = false;
@@ -189,13 +221,32 @@ struct aet_network {
     int n_blocks = 0, n_segments = 0;
     float *hyper_dev = nullptr;  // {lr/B, momentum, -decay*B*loss_scale, unused}
     float hyper_host[4] = {0, 0, 0, 0};
+    // Pinned host block (kPinnedFloats floats): [0..3] cost, mean loss, status word of a synchronous loss read;
+    // [8..15] the same triple for each of the two slots of the asynchronous step; [16..] a ring of kHyperSlots
+    // staged hyper-parameter quadruples (one per change of the learning rate, each with its own event).
     float *loss_pinned = nullptr;
-    // CUDA graph of one train step
+    cudaEvent_t hyper_ev[8] = {nullptr};
+    bool hyper_used[8] = {false};
+    int hyper_next = 0;
+    // CUDA graphs of one train step: [1] forward + backward + exchange + update, [0] forward + backward only
+    // (the calls of a `subdivisions` group that only accumulate gradients)
     bool use_graph = false;
-    cudaGraphExec_t graph_exec = nullptr;
+    cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
+    long graph_launches[2] = {0, 0};
+    int eager_runs[2] = {0, 0};
+    // Double-buffered input staging of aet_network_train_step_async: the host->device copy of step s+1 runs on
+    // `copy_stream` while step s computes; `ev_staged` orders the step after its copy, `ev_consumed` orders the
+    // next copy into a slot after the transposing kernels that read it, `ev_loss` marks a step's loss read-back.
+    cudaStream_t copy_stream = nullptr;
+    float *stage_dev[2] = {nullptr, nullptr};
+    float *stage_host[2] = {nullptr, nullptr};   // pinned mirrors, used when the caller's buffers are pageable
+    size_t stage_floats = 0;
+    cudaEvent_t ev_staged[2] = {nullptr, nullptr}, ev_consumed[2] = {nullptr, nullptr}, ev_loss[2] = {nullptr, nullptr};
+    uint64_t async_steps = 0;
     int update_batch_world = 0;  // batch * world for data parallel
     // data parallel
     void *comm = nullptr;
+    bool comm_capped = false;   // the communicator took the CTA cap
     int rank = 0, world = 1;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_grad_ready[8] = {nullptr}, ev_grad_ready_side[8] = {nullptr}, ev_comm_done = nullptr;
@@ -214,13 +265,15 @@ struct aet_network {
 };
 
 // ---- launch bookkeeping -----------------------------------------------------------------
-void prof_begin(aet_context *ctx, const char *name, double bytes, double flops);
+void prof_begin(aet_context *ctx, const char *name, double bytes, double flops, const char *variant = nullptr);
 void prof_end(aet_context *ctx);
 struct LaunchScope {
     aet_context *ctx;
-    LaunchScope(aet_context *c, const char *name, double bytes, double flops) : ctx(c) {
+    // `variant` names the code path a launcher picked (tile shape, split, epilogue form); it is appended to the
+    // label as "name.variant" so that a test can assert which path it exercised.
+    LaunchScope(aet_context *c, const char *name, double bytes, double flops, const char *variant = nullptr) : ctx(c) {
         ctx->launches++;
-        if (ctx->profiling) prof_begin(ctx, name, bytes, flops);
+        if (ctx->profiling) prof_begin(ctx, name, bytes, flops, variant);
     }
     ~LaunchScope() {
         if (ctx->profiling) prof_end(ctx);
@@ -279,6 +332,13 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_trigger(); }
 #endif
 int ctx_scratch(aet_context *ctx, size_t bytes, float **out);
+// Raises a kernel's dynamic shared-memory limit once per context (the attribute is per device, and a context is
+// one device; a process-wide flag would leave a second device's kernels at the 48 KB default).
+int ctx_smem_attr_impl(aet_context *ctx, const void *func, int bytes);
+template <typename F>
+inline int ctx_smem_attr(aet_context *ctx, F *func, int bytes = 220 * 1024) {
+    return ctx_smem_attr_impl(ctx, reinterpret_cast<const void *>(func), bytes);
+}
 int side_begin(aet_context *ctx);
 void side_end(aet_context *ctx);
 int side_join(aet_context *ctx);
@@ -333,8 +393,11 @@ int k_dropout_backward(aet_layer *l, float *delta);
 int k_fill(aet_context *ctx, float *p, float v, size_t n);
 int k_step_counter(aet_context *ctx, unsigned long long *ctr);
 int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, float lr_over_b, float momentum,
-                  float decay_term);
+                  float decay_term, int scrub);   // scrub: 0 none, 1 weights, 2 batch-norm bias / scale with try_fix_nan
 int k_sgd_arena(aet_network *net);
+int conv_set_wait_limit(unsigned long long ns);          // conv.cu: limit of the mbarrier waits of the convolution kernels
+int elementwise_set_wait_limit(unsigned long long ns);   // elementwise.cu: limit of the peer-flag wait of the update kernel
+int conv_wait_probe(aet_context *ctx);                   // conv.cu: a wait nobody satisfies (self-test of the bounded waits)
 int k_tail_publish(aet_network *net);
 constexpr size_t kXchgFlagBytes = 1024;   // 2 x 16 u64 flags, padded
 int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev);

@@ -23,6 +23,7 @@
 #include "common.h"
 #include "umma.cuh"
 #include <cooperative_groups.h>
+#include <deque>
 
 using namespace umma;
 
@@ -551,7 +552,7 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
     __syncthreads();
     if (warp == 4) {
         tmem_dealloc(tmem, a.tmem_cols);
-        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
 
@@ -602,7 +603,7 @@ ConvGeom layer_geom(const aet_layer *l) {
     // with NHWC activations and [filter][tap][channel] weights it IS a 1x1 convolution over H*W*cp channels of a
     // 1x1 map, byte for byte.  Seen that way the data gradient is a plain GEMM over the batch instead of a
     // convolution in which 35 of 36 taps of every input pixel fall outside the single output pixel.
-    if (l->size == l->h && l->size == l->w && l->pad == 0 && l->size > 1 && !getenv("AET_NO_FC_ALIAS")) {
+    if (l->size == l->h && l->size == l->w && l->pad == 0 && l->size > 1 && l->ctx->opt[OPT_FC_ALIAS]) {
         g.C = g.cp = l->h * l->w * l->cp;
         g.H = g.W = g.OH = g.OW = 1;
         g.R = g.S = 1;
@@ -611,10 +612,10 @@ ConvGeom layer_geom(const aet_layer *l) {
     return g;
 }
 
-int pick_bn(int n_cols, int m_tiles, int sm_count) {
+int pick_bn(int n_cols, int m_tiles, int sm_count, int forced) {
     int full = round_up(n_cols, 16);
-    if (const char *e = getenv("AET_BN")) {   // tuning aid
-        int v = atoi(e);
+    if (forced) {   // tuning aid (option "bn_tile")
+        int v = forced;
         if (v >= 16 && v % 16 == 0 && v <= 256) return v < full ? v : (full <= 256 ? full : v);
     }
     if (full <= 64) return full;
@@ -629,11 +630,7 @@ int pick_bn(int n_cols, int m_tiles, int sm_count) {
 
 template <int KIND, int NB>
 int launch_gather_nb(aet_context *ctx, const ConvArgs &a, dim3 grid, size_t smem_bytes, const char *name, double flops) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        AET_CUDA(cudaFuncSetAttribute(conv_gather_kernel<KIND, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set = true;
-    }
+    AET_TRY(ctx_smem_attr(ctx, conv_gather_kernel<KIND, NB>));
     LaunchScope scope(ctx, name, 0, flops);
     launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_gather_kernel<KIND, NB>, a);
     return aet_check_launch(name);
@@ -679,14 +676,14 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     if (stats) {
         stats->rows = 0;
         // the statistics describe the raw convolution result: no bias or activation in this epilogue
-        if (!bias && a.act == (int)AET_LINEAR && ctx->math != AET_MATH_3XTF32 && !getenv("AET_NO_EPILOGUE_STATS")) {
+        if (!bias && a.act == (int)AET_LINEAR && ctx->math != AET_MATH_3XTF32 && ctx->opt[OPT_EPILOGUE_STATS]) {
             AET_TRY(ctx_scratch(ctx, (size_t)m_tiles * 2 * g.kp * sizeof(float), &stats->partial));   // one row per CTA along M at most
             a.stat_shift = stats->shift;
             a.stat_partial = stats->partial;
             a.stat_rows_out = &stats->rows;
         }
     }
-    a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
+    a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count, ctx->opt[OPT_BN_TILE]);
     const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
     int r = tma_fd_rows<KIND_FPROP>(l, a, flops);
     if (r != 1) return r;   // 1 = shape not eligible
@@ -711,7 +708,7 @@ int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
     a.k_per_split = a.k_total;
     a.out_ld = g.cp;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
-    a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count);
+    a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count, ctx->opt[OPT_BN_TILE]);
     const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
     int r = tma_fd_rows<KIND_DGRAD>(l, a, flops);
     if (r != 1) return r;
@@ -800,3 +797,34 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
 }
 
 void conv_release(aet_layer *l) { tma_release(l); }
+
+int conv_set_wait_limit(unsigned long long ns) {
+    AET_CUDA(cudaMemcpyToSymbol(umma::g_wait_limit_ns, &ns, sizeof(ns)));
+    return AET_OK;
+}
+
+namespace {
+// Self-test of the bounded waits: one warp waits on an mbarrier that nothing ever arrives at, through the same
+// mbar_wait every kernel uses.  The wait runs out after the context's limit, the kernel records the status word
+// and returns normally; the context stays usable.
+__global__ void wait_probe_kernel(int *status) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    pdl_enter();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag);
+    __syncthreads();
+    if (threadIdx.x == 0 && !ok && status) atomicOr(status, AET_STATUS_TIMEOUT);
+}
+}  // namespace
+
+int conv_wait_probe(aet_context *ctx) {
+    LaunchScope scope(ctx, "wait_probe", 0, 0);
+    launch_k(ctx->stream, 1, 32, 0, wait_probe_kernel, ctx->status_dev);
+    return aet_check_launch("wait_probe");
+}

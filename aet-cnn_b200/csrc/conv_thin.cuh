@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
     __syncthreads();
     if (warp == 8) {
         tmem_dealloc(tmem, a.tmem_cols);
-        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
 
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
 int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || getenv("AET_NO_THIN")) return 1;
+    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || !ctx->opt[OPT_THIN]) return 1;
     if (tma_common_ok(l)) return 1;                                         // wide channel counts belong to the TMA kernels
     if (a.k_total > THIN_MAX_CELLS * 4) return 1;
     const int bn = round_up(a.n_cols, 16);
@@ -242,11 +242,7 @@ int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     if (stages < 2) return 1;
     t.stages = stages;
     const size_t smem_bytes = b_bytes + stages * a_bytes + staging + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        AET_CUDA(cudaFuncSetAttribute(conv_fprop_thin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set = true;
-    }
+    AET_TRY(ctx_smem_attr(ctx, conv_fprop_thin_kernel));
     const int resident = smem_bytes <= 110 * 1024 ? 2 : 1;
     int grid = ctx->sm_count * resident;
     if (grid > t.tiles) grid = t.tiles;
@@ -416,7 +412,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
     __syncthreads();
     if (warp == 4) {
         tmem_dealloc(tmem, a.tmem_cols);
-        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
 
@@ -424,7 +420,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
 int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, float **partial_out) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || getenv("AET_NO_THIN")) return 1;
+    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || !ctx->opt[OPT_THIN]) return 1;
     if (tma_common_ok(l)) return 1;                                         // wide channel counts belong to the TMA kernels
     if (a.n_cols > THIN_MAX_CELLS * 4 || g.K > BM) return 1;
     if (!(g.kp % 32 == 0 || g.kp < 32)) return 1;          // whole 32-filter blocks for the TMA box
@@ -465,11 +461,7 @@ int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, f
         if (get_map(l, 12, a.src_a, 3, dims, str, box, true, &ma) != AET_OK) return 1;
     }
     const size_t smem_bytes = stage * stages + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        AET_CUDA(cudaFuncSetAttribute(conv_wgrad_thin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set = true;
-    }
+    AET_TRY(ctx_smem_attr(ctx, conv_wgrad_thin_kernel));
     LaunchScope scope(ctx, "conv_wgrad_thin", 0, flops);
     launch_k(ctx->stream, splits, NTHREADS, smem_bytes, conv_wgrad_thin_kernel, *ma, t);
     *splits_out = splits;

@@ -41,7 +41,7 @@ struct TmaEntry {
     CUtensorMap map;
 };
 struct TmaCache {
-    std::vector<TmaEntry> entries;
+    std::deque<TmaEntry> entries;   // a deque never moves its elements: the maps handed out stay valid as the cache grows
 };
 
 // dims/strides innermost first; strides[i] is the byte stride of dim i+1.
@@ -72,7 +72,6 @@ int get_map(aet_layer *l, int tag, const void *ptr, int rank, const cuuint64_t *
         aet_set_error("cuTensorMapEncodeTiled failed with code %d (tag %d)", (int)r, tag);
         return AET_E_CUDA;
     }
-    c->entries.reserve(64);
     c->entries.push_back(e);
     *out = &c->entries.back().map;
     return AET_OK;
@@ -235,7 +234,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     if (warp == 4) {
         tmem_dealloc(tmem, a.tmem_cols);
-        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
 
@@ -272,11 +271,7 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
     if (stages < 2) stages = 2;
     t.stages = stages;
     const size_t smem_bytes = stage * stages + 1024;
-    static bool attr_set[3] = {false, false, false};
-    if (!attr_set[KIND]) {
-        AET_CUDA(cudaFuncSetAttribute(conv_tma_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set[KIND] = true;
-    }
+    AET_TRY(ctx_smem_attr(ctx, conv_tma_kernel<KIND>));
     LaunchScope scope(ctx, name, 0, flops);
     launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_tma_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);

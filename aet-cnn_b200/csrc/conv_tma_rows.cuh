@@ -126,7 +126,7 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     __syncthreads();
     if (warp == 4) {
         tmem_dealloc(tmem, a.tmem_cols);
-        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
 
@@ -134,7 +134,7 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, float **partial_out) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (!tma_common_ok(l) || getenv("AET_NO_ROWS")) return 1;
+    if (!tma_common_ok(l) || !ctx->opt[OPT_ROWS]) return 1;
     if (g.R < 2 || g.OW > 32 || g.OW % 8 || 32 % g.OW) return 1;
     const int rows = 32 / g.OW;
     if (g.OH % rows || g.OW > g.W || g.OH > g.H) return 1;
@@ -176,7 +176,7 @@ int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_ou
     // one CTA per SM (the stages fill most of its shared memory): a single wave, and no more K
     // splits than that needs, because every split costs a full partial-gradient write and read
     int want = ctx->sm_count / tiles;
-    if (const char *e = getenv("AET_WGRAD_SPLITS")) want = atoi(e);
+    if (ctx->opt[OPT_WGRAD_SPLITS] > 0) want = ctx->opt[OPT_WGRAD_SPLITS];
     if (want < 1) want = 1;
     int max_splits = t.total_slabs / 4;
     if (max_splits < 1) max_splits = 1;
@@ -195,14 +195,12 @@ int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_ou
     if (stages < 2) return 1;
     t.stages = stages;
     const size_t smem_bytes = stage * stages + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        AET_CUDA(cudaFuncSetAttribute(conv_wgrad_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set = true;
-    }
+    AET_TRY(ctx_smem_attr(ctx, conv_wgrad_rows_kernel));
     dim3 grid(m_tiles, g.S * t.col_groups, splits);
     {
-        LaunchScope scope(ctx, "conv_wgrad_tma_rows", 0, flops);
+        char variant[24];
+        snprintf(variant, sizeof(variant), "n%d_sp%d", bn, splits);
+        LaunchScope scope(ctx, "conv_wgrad_tma_rows", 0, flops, variant);
         launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_wgrad_rows_kernel, *ma, *mb, t);
         AET_TRY(aet_check_launch("conv_wgrad_tma_rows"));
     }
@@ -447,7 +445,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (warp == 4) {
         tmem_dealloc(tmem, a.tmem_cols);
-        if (lane == 0 && ctl.abort_flag && a.status) atomicExch(a.status, AET_STATUS_TIMEOUT);
+        if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
 
@@ -456,7 +454,7 @@ template <int KIND>
 int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (!tma_common_ok(l) || getenv("AET_NO_ROWS") || getenv(KIND == KIND_FPROP ? "AET_NO_ROWS_F" : "AET_NO_ROWS_D")) return 1;
+    if (!tma_common_ok(l) || !ctx->opt[OPT_ROWS] || !ctx->opt[KIND == KIND_FPROP ? OPT_ROWS_FPROP : OPT_ROWS_DGRAD]) return 1;
     if (g.R < 2 || g.OH != g.H || g.OW != g.W) return 1;                 // same-size convolutions
     const int inner = KIND == KIND_FPROP ? g.cp : g.kp;
     if (KIND == KIND_DGRAD && !(g.kp % 32 == 0)) return 1;
@@ -477,7 +475,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     // instead of once per column tap, and the epilogue adds the S column blocks with their column shifts.
     int smerge = 0;
     if (KIND == KIND_DGRAD && bi == 1 && g.S == g.R && g.pad == (g.S - 1) / 2 && g.cp % 32 == 0 && g.cp < 128 && g.S * g.cp <= 256 &&
-        a.n_cols == g.cp && !getenv("AET_NO_SMERGE")) {
+        a.n_cols == g.cp && ctx->opt[OPT_SMERGE]) {
         const int c = g.S * g.cp;
         int m = (g.H % (2 * (int)bh) == 0 && 2 * c <= 512 && (m_tiles / 2) >= (ctx->sm_count * 3) / 4) ? 2 : 1;
         for (; m >= 1 && !smerge; --m) {
@@ -496,12 +494,12 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         const int nt = (a.n_cols + c - 1) / c;
         // too few tiles for the machine: keep the wide N tile (an MMA of N = 64 costs as much as one of
         // N = 128) and let the two CTAs of a cluster take half of the K range each
-        const bool split = c >= 128 && m_tiles * nt * 2 <= ctx->sm_count && total_slabs >= 8 && !getenv("AET_NO_KSPLIT");
+        const bool split = c >= 128 && m_tiles * nt * 2 <= ctx->sm_count && total_slabs >= 8 && ctx->opt[OPT_KSPLIT];
         if (!(m_tiles * nt >= (ctx->sm_count * 3) / 5 || c <= 64 || split)) continue;
         // two pixel tiles per CTA when they are rows of one image and there are still enough CTAs
         int m = 1;
         if (bi == 1 && g.H % (2 * (int)bh) == 0 && 2 * c <= 512 && (m_tiles / 2) * nt >= (ctx->sm_count * 3) / 4 &&
-            !getenv("AET_NO_MT2"))
+            ctx->opt[OPT_MT2])
             m = 2;
         for (; m >= 1; --m) {
             const uint32_t ab = (uint32_t)(m * (int)bh + g.R - 1) * bi * g.W * 128u;
@@ -519,7 +517,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     // The large stages allow one CTA per SM.  Measured on 8x8 to 16x16 images at batch 128 and 256: while the
     // grid fits one wave this kernel matches or beats the plain TMA kernel (dgrad by 20%); with a second,
     // partial wave the plain kernel with its smaller stages and two CTAs per SM wins by up to 40%.
-    if (((m_tiles + mt - 1) / mt) * n_tiles * ksplit > ctx->sm_count && !getenv("AET_ROWS_MULTI")) return 1;
+    if (((m_tiles + mt - 1) / mt) * n_tiles * ksplit > ctx->sm_count && !ctx->opt[OPT_ROWS_MULTI]) return 1;
     const int super_rows = mt * (int)bh + g.R - 1;
     const CUtensorMap *ma, *mb;
     const float *act = a.src_a;
@@ -561,20 +559,18 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     t.smerge_S = smerge;
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
     t.stages = stages; t.tmem_cols = pow2_cols(mt * bn); t.ksplit = ksplit;
-    t.par_epi = (mt == 2 && !smerge && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && !getenv("AET_NO_PAR_EPILOGUE")) ? 1 : 0;
+    t.par_epi = (mt == 2 && !smerge && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && ctx->opt[OPT_PAR_EPILOGUE]) ? 1 : 0;
     const int threads = (t.par_epi || (smerge && mt == 2)) ? FD_THREADS_WIDE : NTHREADS;
     t.a_bytes = a_bytes; t.b_tile_bytes = b_tile; t.tx_bytes = a_bytes + (uint32_t)g.R * b_tile;
     t.status = ctx->status_dev;
     const size_t smem_bytes = stage * stages + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        AET_CUDA(cudaFuncSetAttribute(conv_fd_rows_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set = true;
-    }
+    AET_TRY(ctx_smem_attr(ctx, conv_fd_rows_kernel<KIND>));
     dim3 grid((m_tiles + mt - 1) / mt, n_tiles, ksplit);
     if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x * (t.par_epi ? 2 : 1);
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
-    LaunchScope scope(ctx, name, 0, flops);
+    char variant[24];   // e.g. "mt2e_n128x1": two pixel tiles, second epilogue group, N tile 128, one N tile
+    snprintf(variant, sizeof(variant), "%smt%d%s_n%dx%d%s", smerge ? "sm_" : "", mt, t.par_epi ? "e" : "", bn, n_tiles, ksplit > 1 ? "_ks2" : "");
+    LaunchScope scope(ctx, name, 0, flops, variant);
     if (ksplit > 1) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, ksplit, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
     else launch_k(ctx->stream, grid, threads, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);

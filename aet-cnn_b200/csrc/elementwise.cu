@@ -16,6 +16,8 @@
 //   softmax-CE   dnn/SoftMaxLayer.c:122-139,172-199, mtcs/MtcsData.c:20-29
 //   dropout      dnn/DropoutLayer.c:55-86
 //   SGD          mtcs/MtcsConvLayer.c:618-631 -> mtcs/MtcsTool.c:33-52
+#include <atomic>
+#include <mutex>
 #include <float.h>
 #include <math.h>
 
@@ -1130,13 +1132,41 @@ __global__ void __launch_bounds__(1024) tail_publish_kernel(const float *G, cons
     if (threadIdx.x == 0) { *p.epoch = e; *p.ticket = 0u; }
 }
 
+// Limit of the peer-flag wait below (nanoseconds); set per device by elementwise_set_wait_limit.
+__constant__ unsigned long long g_flag_wait_limit_ns = 1000000000ull;
+
+// Non-finite scrub of the reference's GPU update.  kind 1 = a weight segment: a NaN/Inf pending update becomes 0
+// (resetNanAndInf) and a NaN/Inf weight becomes 1 / (index + 1) (fixNanAndInf), mtcs/MtcsConvLayer.c:586-587,
+// mtcs/MtcsTool.c:77-107.  kind 2 = a bias / scale segment of a batch-norm layer with try_fix_nan: the pending
+// update becomes 1 / (index + 1), dnn/NLayer.c:318-323.  `index` is the element's position in its segment.
+// Returns true when something was replaced.
+__device__ __forceinline__ bool scrub1(float &w, float &u, int kind, size_t index) {
+    bool hit = false;
+    if (kind == 1) {
+        if (isnan(u) || isinf(u)) { u = 0.f; hit = true; }
+        if (isnan(w) || isinf(w)) { w = 1.0f / ((float)index + 1.f); hit = true; }
+    } else if (kind == 2) {
+        if (isnan(u) || isinf(u)) { u = 1.0f / ((float)index + 1.f); hit = true; }
+    }
+    return hit;
+}
+__device__ __forceinline__ bool scrub4(float4 &w, float4 &u, int kind, size_t index) {
+    bool hit = scrub1(w.x, u.x, kind, index);
+    hit |= scrub1(w.y, u.y, kind, index + 1);
+    hit |= scrub1(w.z, u.z, kind, index + 2);
+    hit |= scrub1(w.w, u.w, kind, index + 3);
+    return hit;
+}
+
+// seg_table: four floats per segment {learning-rate multiplier, decay flag, scrub kind, first block (int bits)}
 __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float *G, const int *block_seg,
-                                                       const float *seg_table, const float *hyper, const TailArgs t) {
+                                                       const float *seg_table, const float *hyper, const TailArgs t, int *status) {
     pdl_enter();
     const int seg = block_seg[blockIdx.x];
-    const float rate = hyper[0] * seg_table[2 * seg];
+    const float rate = hyper[0] * seg_table[4 * seg];
     const float momentum = hyper[1];
-    const float decay_term = seg_table[2 * seg + 1] != 0.f ? hyper[2] : 0.f;
+    const float decay_term = seg_table[4 * seg + 1] != 0.f ? hyper[2] : 0.f;
+    const int scrub = (int)seg_table[4 * seg + 2];
     const size_t i = ((size_t)blockIdx.x * TB + threadIdx.x) * 4;
     float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i);
     const size_t b0 = (size_t)blockIdx.x * TB * 4;
@@ -1155,14 +1185,14 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
                     unsigned long long now;
                     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
                     if (t0 == 0) t0 = now;
-                    else if (now - t0 > 1000000000ull) { ok = 0; break; }   // a peer never arrived: give up after a second
+                    else if (now - t0 > g_flag_wait_limit_ns) { ok = 0; break; }   // a peer never arrived: give up
                 }
             }
             __threadfence_system();   // acquire: the peers' slices are read after their flags (the barrier passes it on)
         }
         __syncthreads();
         if (!ok) {
-            if (threadIdx.x == 0 && t.status) atomicExch(t.status, AET_STATUS_TIMEOUT);
+            if (threadIdx.x == 0 && t.status) atomicOr(t.status, AET_STATUS_TIMEOUT);
             return;
         }
         g = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1172,6 +1202,10 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
         }
     }
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    if (scrub) {
+        const size_t first = (size_t)__float_as_int(seg_table[4 * seg + 3]) * TB * 4;
+        if (scrub4(w, u, scrub, i - first) && status) atomicOr(status, AET_STATUS_NAN);
+    }
     u.x += decay_term * w.x; u.y += decay_term * w.y; u.z += decay_term * w.z; u.w += decay_term * w.w;
     w.x += rate * u.x; w.y += rate * u.y; w.z += rate * u.z; w.w += rate * u.w;
     u.x *= momentum; u.y *= momentum; u.z *= momentum; u.w *= momentum;
@@ -1179,13 +1213,15 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
     st4(U + i, u);
     st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
 }
-__global__ void sgd_segment_kernel(float *W, float *U, float *G, size_t n4, float rate, float momentum, float decay_term) {
+__global__ void sgd_segment_kernel(float *W, float *U, float *G, size_t n4, float rate, float momentum, float decay_term,
+                                   int scrub, int *status) {
     pdl_enter();
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
     if (i >= n4) return;
     i *= 4;
     float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i);
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    if (scrub && scrub4(w, u, scrub, i) && status) atomicOr(status, AET_STATUS_NAN);
     u.x += decay_term * w.x; u.y += decay_term * w.y; u.z += decay_term * w.z; u.w += decay_term * w.w;
     w.x += rate * u.x; w.y += rate * u.y; w.z += rate * u.z; w.w += rate * u.w;
     u.x *= momentum; u.y *= momentum; u.z *= momentum; u.w *= momentum;
@@ -1610,11 +1646,17 @@ int k_dropout_backward(aet_layer *l, float *delta) {
     return aet_check_launch("dropout_bwd");
 }
 
+int elementwise_set_wait_limit(unsigned long long ns) {
+    AET_CUDA(cudaMemcpyToSymbol(g_flag_wait_limit_ns, &ns, sizeof(ns)));
+    return AET_OK;
+}
+
 int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, float lr_over_b, float momentum,
-                  float decay_term) {
+                  float decay_term, int scrub) {
     const size_t n4 = count / 4;
     LaunchScope s(ctx, "sgd_segment", 24.0 * count, 0);
-    launch_k(ctx->stream, (unsigned)((n4 + TB - 1) / TB), TB, 0, sgd_segment_kernel, W, U, G, n4, lr_over_b, momentum, decay_term);
+    launch_k(ctx->stream, (unsigned)((n4 + TB - 1) / TB), TB, 0, sgd_segment_kernel, W, U, G, n4, lr_over_b, momentum, decay_term,
+             scrub, ctx->status_dev);
     return aet_check_launch("sgd_segment");
 }
 
@@ -1629,7 +1671,7 @@ int k_sgd_arena(aet_network *net) {
         t.world = net->world; t.status = ctx->status_dev;
     }
     launch_k(ctx->stream, net->n_blocks, TB, 0, sgd_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->block_seg,
-                                                           net->seg_table, net->hyper_dev, t);
+                                                           net->seg_table, net->hyper_dev, t, ctx->status_dev);
     return aet_check_launch("sgd_momentum");
 }
 
@@ -1657,21 +1699,22 @@ int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_
 
 // ---------------------------------------------------------------------------- allocation-free bias gradient
 // Some hosts of this library may not allocate device memory once they are running: a training loop
-// inside a process whose memory pool was sized and handed out at start-up, a plugin called from
-// another runtime's stream callback, or a caller that is itself between cudaMalloc-free phases of a
-// latency-critical service.  For them the bias gradient (the column sums that k_bias_act_backward
-// forms with partials in the context's cudaMalloc'ed scratch arena) is also offered with its
-// partials in the fixed array below, which every GPU that loads the library holds until exit.
+// inside a process whose whole device pool was sized and handed out at start-up, or a service that has
+// entered a phase in which cudaMalloc (a device-wide synchronisation) is off limits.  For them the bias
+// gradient (the column sums that k_bias_act_backward forms with partials in the context's cudaMalloc'ed
+// scratch arena) is also offered with its partials in the fixed array below, which every GPU that loads
+// the library holds until exit.
 constexpr size_t kStaticScratchFloats = 1u << 18;   // 1 MiB
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
 namespace {
 struct StaticDeviceState {
-    bool ready = false;
-    float *scratch = nullptr;   // device address of g_static_scratch on this device
+    std::atomic<bool> ready{false};   // published with release order after `scratch` and `sm_count` are written
+    float *scratch = nullptr;         // device address of g_static_scratch on this device
     int sm_count = 0;
 };
 StaticDeviceState g_static_state[64];
+std::mutex g_static_mutex;            // serialises the first call on a device between host threads
 }  // namespace
 
 extern "C" int aet_backward_bias_static(const float *delta, float *bias_updates, long long pixels, int channels,
@@ -1691,14 +1734,18 @@ extern "C" int aet_backward_bias_static(const float *delta, float *bias_updates,
         return AET_E_INVALID;
     }
     StaticDeviceState &st = g_static_state[dev];
-    if (!st.ready) {
+    if (!st.ready.load(std::memory_order_acquire)) {
         // Host code only sees a stand-in for the __device__ array; the kernels need its device address,
-        // looked up once per device with that device current.
-        float *p = nullptr;
-        AET_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch));
-        AET_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
-        st.scratch = p;
-        st.ready = true;
+        // looked up once per device with that device current.  (With lazy module loading this lookup is
+        // also what makes the driver back the array with memory: do it at start-up.)
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!st.ready.load(std::memory_order_relaxed)) {
+            float *p = nullptr;
+            AET_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_static_scratch));
+            AET_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+            st.scratch = p;
+            st.ready.store(true, std::memory_order_release);
+        }
     }
     ReducePlan p;
     p.m = make_cmap(channels);

@@ -468,9 +468,13 @@ extern "C" int aet_layer_update(aet_layer *l, int batch, float learning_rate, fl
     // mtcs/MtcsConvLayer.c:582,618-631
     const float lr = learning_rate * l->lr_scale / loss_scale;
     const float rate = lr / batch;
-    AET_TRY(k_sgd_segment(l->ctx, layer_W(l), layer_U(l), layer_G(l), l->seg_w.padded, rate, momentum, -decay * batch * loss_scale));
-    AET_TRY(k_sgd_segment(l->ctx, layer_b(l), layer_bU(l), layer_bG(l), l->seg_b.padded, rate, momentum, 0.f));
-    if (l->bn) AET_TRY(k_sgd_segment(l->ctx, layer_s(l), layer_sU(l), layer_sG(l), l->seg_s.padded, rate, momentum, 0.f));
+    // the GPU update scrubs non-finite weights and pending weight updates first (mtcs/MtcsConvLayer.c:586-587); the
+    // CPU update does not (dnn/ConvolutionalLayer.c:959-980)
+    const int scrub_w = l->ctx->parity == AET_PARITY_MTCS ? 1 : 0;
+    const int scrub_bn = (l->bn && l->net && l->net->try_fix_nan && l->ctx->parity == AET_PARITY_MTCS) ? 2 : 0;
+    AET_TRY(k_sgd_segment(l->ctx, layer_W(l), layer_U(l), layer_G(l), l->seg_w.padded, rate, momentum, -decay * batch * loss_scale, scrub_w));
+    AET_TRY(k_sgd_segment(l->ctx, layer_b(l), layer_bU(l), layer_bG(l), l->seg_b.padded, rate, momentum, 0.f, scrub_bn));
+    if (l->bn) AET_TRY(k_sgd_segment(l->ctx, layer_s(l), layer_sU(l), layer_sG(l), l->seg_s.padded, rate, momentum, 0.f, scrub_bn));
     return AET_OK;
 }
 

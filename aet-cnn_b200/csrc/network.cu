@@ -5,6 +5,7 @@
 // parameter arena updated by one fused kernel, and the NCCL gradient all-reduce for batch
 // data-parallel training (issued per bucket on a side stream while backward continues).
 #include <dlfcn.h>
+#include <limits.h>
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -94,6 +95,16 @@ const char *kUnsupportedConvKeys[] = {"binary", "xnor", "bin_output", "sway", "r
 struct NcclUniqueId { char internal[128]; };
 typedef int (*nccl_get_unique_id_t)(NcclUniqueId *);
 typedef int (*nccl_comm_init_rank_t)(void **, int, NcclUniqueId, int);
+// Leading fields of ncclConfig_t as NCCL 2.18 published them; NCCL reads `size` and `version` and takes its own
+// defaults for the fields a caller's older layout does not have.
+struct NcclConfig218 {
+    size_t size;
+    unsigned int magic, version;
+    int blocking, cgaClusterSize, minCTAs, maxCTAs;
+    const char *netName;
+    int splitShare;
+};
+typedef int (*nccl_comm_init_rank_config_t)(void **, int, NcclUniqueId, int, NcclConfig218 *);
 typedef int (*nccl_all_reduce_t)(const void *, void *, size_t, int, int, void *, cudaStream_t);
 typedef int (*nccl_comm_destroy_t)(void *);
 typedef const char *(*nccl_get_error_string_t)(int);
@@ -101,6 +112,7 @@ struct NcclApi {
     void *handle = nullptr;
     nccl_get_unique_id_t get_unique_id = nullptr;
     nccl_comm_init_rank_t comm_init_rank = nullptr;
+    nccl_comm_init_rank_config_t comm_init_rank_config = nullptr;   // optional
     nccl_all_reduce_t all_reduce = nullptr;
     nccl_comm_destroy_t comm_destroy = nullptr;
     nccl_get_error_string_t error_string = nullptr;
@@ -118,6 +130,7 @@ NcclApi *nccl_api() {
         if (api.handle) {
             api.get_unique_id = (nccl_get_unique_id_t)dlsym(api.handle, "ncclGetUniqueId");
             api.comm_init_rank = (nccl_comm_init_rank_t)dlsym(api.handle, "ncclCommInitRank");
+            api.comm_init_rank_config = (nccl_comm_init_rank_config_t)dlsym(api.handle, "ncclCommInitRankConfig");
             api.all_reduce = (nccl_all_reduce_t)dlsym(api.handle, "ncclAllReduce");
             api.comm_destroy = (nccl_comm_destroy_t)dlsym(api.handle, "ncclCommDestroy");
             api.error_string = (nccl_get_error_string_t)dlsym(api.handle, "ncclGetErrorString");
@@ -136,12 +149,14 @@ int nccl_fail(NcclApi *api, int code, const char *what) {
 
 // ---------------------------------------------------------------------------- helpers
 float current_rate(const aet_network *net) {
-    // dnn/NNetwork.c:215-246
+    // dnn/NNetwork.c:215-246, with its types: batch_num is a size_t, so the divisions, the burn-in comparison and the
+    // sig policy's `batch_num - step` are unsigned (the difference wraps while batch_num < step, which drives the
+    // rate to 0 for gamma > 0 exactly as the reference's expression does), and pow / exp are the double functions.
     const size_t batch_num = (size_t)(net->seen / ((int64_t)net->batch * net->subdivisions));
-    if ((int)batch_num < net->burn_in) return net->learning_rate * powf((float)batch_num / net->burn_in, net->power);
+    if (batch_num < (size_t)net->burn_in) return (float)(net->learning_rate * pow((float)batch_num / net->burn_in, net->power));
     switch (net->policy) {
     case 0: return net->learning_rate;
-    case 1: return net->learning_rate * powf(net->scale, (float)(batch_num / (size_t)net->step));
+    case 1: return (float)(net->learning_rate * pow(net->scale, batch_num / (size_t)net->step));
     case 2: {
         float rate = net->learning_rate;
         for (int i = 0; i < net->num_steps; ++i) {
@@ -150,9 +165,9 @@ float current_rate(const aet_network *net) {
         }
         return rate;
     }
-    case 3: return net->learning_rate * powf(net->gamma, (float)(int)batch_num);
-    case 4: return net->learning_rate * powf(1 - (float)batch_num / net->max_batches, net->power);
-    case 5: return net->learning_rate * (float)(1. / (1. + exp((double)net->gamma * ((double)batch_num - net->step))));
+    case 3: return (float)(net->learning_rate * pow(net->gamma, (int)batch_num));
+    case 4: return (float)(net->learning_rate * pow(1 - (float)batch_num / net->max_batches, net->power));
+    case 5: return (float)(net->learning_rate * (1. / (1. + exp(net->gamma * (batch_num - (size_t)net->step)))));
     default: return net->learning_rate;
     }
 }
@@ -167,9 +182,16 @@ int build_sgd_tables(aet_network *net) {
         for (int k = 0; k < 3; ++k) {
             if (!segs[k]) continue;
             if (segs[k]->offset != block_seg.size() * 1024) { aet_set_error("internal: arena segments are not contiguous"); return AET_E_INVALID; }
+            const int first_block = (int)block_seg.size();
             for (size_t b = 0; b < segs[k]->padded / 1024; ++b) block_seg.push_back(seg_id);
+            // {learning-rate multiplier, decay flag, non-finite scrub kind, first block of the segment (int bits)}
+            const bool mtcs = net->ctx->parity == AET_PARITY_MTCS;
+            float first_bits;
+            memcpy(&first_bits, &first_block, sizeof(float));
             seg_table.push_back(l->lr_scale);
             seg_table.push_back(k == 0 ? 1.f : 0.f);
+            seg_table.push_back(!mtcs ? 0.f : (k == 0 ? 1.f : ((l->bn && net->try_fix_nan) ? 2.f : 0.f)));
+            seg_table.push_back(first_bits);
             ++seg_id;
         }
     }
@@ -196,8 +218,17 @@ int upload_hyper(aet_network *net) {
     float h[4] = {rate / net->loss_scale / update_batch, net->momentum, -net->decay * update_batch * net->loss_scale, 0.f};
     if (memcmp(h, net->hyper_host, sizeof(h)) == 0) return AET_OK;
     memcpy(net->hyper_host, h, sizeof(h));
-    memcpy(net->loss_pinned + 4, h, sizeof(h));
-    AET_CUDA(cudaMemcpyAsync(net->hyper_dev, net->loss_pinned + 4, sizeof(h), cudaMemcpyHostToDevice, net->ctx->stream));
+    // The copy is asynchronous and the host may be many steps ahead of the device: every change of the rate is
+    // staged in its own pinned slot, reused only after the copy that read it has run.
+    const int slot = net->hyper_next;
+    net->hyper_next = (slot + 1) % kHyperSlots;
+    if (!net->hyper_ev[slot]) AET_CUDA(cudaEventCreateWithFlags(&net->hyper_ev[slot], cudaEventDisableTiming));
+    if (net->hyper_used[slot]) AET_CUDA(cudaEventSynchronize(net->hyper_ev[slot]));
+    float *stage = net->loss_pinned + 16 + 4 * slot;
+    memcpy(stage, h, sizeof(h));
+    AET_CUDA(cudaMemcpyAsync(net->hyper_dev, stage, sizeof(h), cudaMemcpyHostToDevice, net->ctx->stream));
+    AET_CUDA(cudaEventRecord(net->hyper_ev[slot], net->ctx->stream));
+    net->hyper_used[slot] = true;
     return AET_OK;
 }
 
@@ -232,15 +263,17 @@ int issue_allreduce(aet_network *net, size_t lo, size_t hi, int slot) {
     return AET_OK;
 }
 
-int net_backward(aet_network *net, aet_state state) {
+// `exchange`: this backward pass completes a gradient (the last call of a `subdivisions` group): only then
+// are the accumulated gradients summed over the ranks.
+int net_backward(aet_network *net, aet_state state, bool exchange = true) {
     // dnn/NNetwork.c:627-654
     aet_tensor *original_input = state.input, *original_delta = state.delta;
-    const bool dp = net->comm != nullptr && net->world > 1;
+    const bool dp = net->comm != nullptr && net->world > 1 && exchange;
     const size_t bucket_floats = 64 * 1024;
     size_t pend_lo = 0, pend_hi = 0;
     int slot = 0;
     aet_context *ctx = net->ctx;
-    ctx->overlap_wgrad = !getenv("AET_NO_OVERLAP");
+    ctx->overlap_wgrad = ctx->opt[OPT_OVERLAP_WGRAD] != 0;
     ctx->in_network_pass = true;
     // A gradient arena that fits the peer-exchange buffer is exchanged in one piece at the end of backward
     // (one synchronisation of the ranks per step, no collective kernels beside the backward pass).
@@ -288,12 +321,15 @@ int net_backward(aet_network *net, aet_state state) {
     return AET_OK;
 }
 
-int run_step(aet_network *net) {
+// One call of NNetwork.train(InputData*, TruthData*) (dnn/NNetwork.c:740-760) and, when `final`, the update
+// that NNetwork.train(ImageData*) runs after its `subdivisions` calls (dnn/NNetwork.c:762-774).
+int run_step(aet_network *net, bool final) {
     aet_state st = {};
     st.truth = net->truth; st.input = net->input; st.delta = nullptr; st.train = 1;
     AET_TRY(net_forward(net, st));
     st.input = net->input;
-    AET_TRY(net_backward(net, st));
+    AET_TRY(net_backward(net, st, final));
+    if (!final) return AET_OK;   // gradients keep accumulating in the arena until the group's last call
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(k_sgd_arena(net));
     net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
@@ -301,10 +337,44 @@ int run_step(aet_network *net) {
 }
 
 void graph_drop(aet_network *net) {
-    if (net->graph_exec) {
-        cudaGraphExecDestroy(net->graph_exec);
-        net->graph_exec = nullptr;
+    for (int k = 0; k < 2; ++k) {
+        if (net->graph_exec[k]) {
+            cudaGraphExecDestroy(net->graph_exec[k]);
+            net->graph_exec[k] = nullptr;
+        }
+        net->eager_runs[k] = 0;
     }
+}
+
+// Queues the read-back of {cost, mean loss} and of the device status word into three pinned floats.
+int queue_loss_readback(aet_network *net, float *pinned3) {
+    aet_layer *sm = softmax_layer(net);
+    cudaStream_t s = net->ctx->stream;
+    if (sm) AET_CUDA(cudaMemcpyAsync(pinned3, sm->cost_dev, 2 * sizeof(float), cudaMemcpyDeviceToHost, s));
+    else pinned3[0] = pinned3[1] = 0.f;
+    AET_CUDA(cudaMemcpyAsync(pinned3 + 2, net->ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
+    return AET_OK;
+}
+
+// Turns the status word that came back with a loss into the call's return code.  A timed-out wait leaves the
+// step incomplete (tiles unwritten, the update partly applied): the caller must treat the weights as lost and
+// reload a checkpoint.  The non-finite flag is informational and is left for aet_context_check.
+int status_to_code(aet_network *net, const float *pinned3) {
+    int st;
+    memcpy(&st, pinned3 + 2, sizeof(int));
+    if (st & AET_STATUS_TIMEOUT) {
+        cudaMemsetAsync(net->ctx->status_dev, 0, sizeof(int), net->ctx->stream);
+        aet_set_error("a bounded device-side wait expired during the training step (status %d): the step is incomplete, "
+                      "the weights must be reloaded", st);
+        return AET_E_TIMEOUT;
+    }
+    return AET_OK;
+}
+
+bool host_pinned(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return at.type == cudaMemoryTypeHost;
 }
 
 }  // namespace
@@ -444,19 +514,19 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
         if (!l) { aet_network_destroy(net); return nullptr; }
         l->net = net;
         l->index = index;
-        if (l->type == AET_MAXPOOL && !net->layers.empty() && !getenv("AET_NO_FUSE")) {
+        if (l->type == AET_MAXPOOL && !net->layers.empty() && ctx->opt[OPT_FUSE]) {
             aet_layer *prev = net->layers.back();
             if (prev->type == AET_CONVOLUTIONAL && prev->bn) { prev->fused_pool = l; l->fused_into = prev; }
         }
         net->layers.push_back(l);
-        if (l->type == AET_SOFTMAX && net->layers.size() >= 3 && !getenv("AET_NO_FUSE")) {
+        if (l->type == AET_SOFTMAX && net->layers.size() >= 3 && ctx->opt[OPT_FUSE]) {
             aet_layer *avg = net->layers[net->layers.size() - 2], *cv = net->layers[net->layers.size() - 3];
             if (avg->type == AET_AVGPOOL && cv->type == AET_CONVOLUTIONAL && !cv->bn && cv->act == AET_LINEAR && cv->delta &&
                 l->groups == 1 && l->c <= 32) {
                 l->head_conv = cv; l->head_avg = avg;
                 avg->head_softmax = l; cv->head_softmax = l;
                 // 1x1 classifier: the head is linear up to the softmax and can run on the pooled vectors
-                if (cv->size == 1 && cv->stride_x == 1 && cv->stride_y == 1 && cv->pad == 0 && !getenv("AET_NO_LINEAR_HEAD") &&
+                if (cv->size == 1 && cv->stride_x == 1 && cv->stride_y == 1 && cv->pad == 0 && ctx->opt[OPT_LINEAR_HEAD] &&
                     (size_t)(cv->batch + 256) * l->c * sizeof(float) <= 40 * 1024 && (size_t)(cv->cp + 32) * sizeof(float) <= 40 * 1024 &&
                     cudaMalloc(&cv->lin_xbar, (size_t)cv->batch * cv->cp * sizeof(float)) == cudaSuccess &&
                     cudaMalloc(&cv->lin_ticket, sizeof(unsigned int)) == cudaSuccess &&
@@ -471,13 +541,13 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
     net->truth = aet_tensor_create(ctx, net->batch, c * h * w, 1, 1);
     bool ok = net->input && net->truth && build_sgd_tables(net) == AET_OK;
     ok = ok && cudaMalloc(&net->hyper_dev, 4 * sizeof(float)) == cudaSuccess;
-    ok = ok && cudaMallocHost(&net->loss_pinned, 16 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMallocHost(&net->loss_pinned, kPinnedFloats * sizeof(float)) == cudaSuccess;
     if (!ok) {
         if (!strlen(aet_last_error())) aet_set_error("network allocation failed");
         aet_network_destroy(net);
         return nullptr;
     }
-    memset(net->loss_pinned, 0, 16 * sizeof(float));
+    memset(net->loss_pinned, 0, kPinnedFloats * sizeof(float));
     net->hyper_host[1] = -1.f;   // force the first upload
     cudaStreamSynchronize(ctx->stream);
     return net;
@@ -512,6 +582,15 @@ extern "C" void aet_network_destroy(aet_network *net) {
     if (net->seg_table) cudaFree(net->seg_table);
     if (net->hyper_dev) cudaFree(net->hyper_dev);
     if (net->loss_pinned) cudaFreeHost(net->loss_pinned);
+    for (int k = 0; k < kHyperSlots; ++k) if (net->hyper_ev[k]) cudaEventDestroy(net->hyper_ev[k]);
+    for (int k = 0; k < 2; ++k) {
+        if (net->stage_dev[k]) cudaFree(net->stage_dev[k]);
+        if (net->stage_host[k]) cudaFreeHost(net->stage_host[k]);
+        if (net->ev_staged[k]) cudaEventDestroy(net->ev_staged[k]);
+        if (net->ev_consumed[k]) cudaEventDestroy(net->ev_consumed[k]);
+        if (net->ev_loss[k]) cudaEventDestroy(net->ev_loss[k]);
+    }
+    if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
     delete net;
 }
 
@@ -575,33 +654,41 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
     if (!net->train) { aet_set_error("network was created with train=0"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
     net->seen += net->batch;           // dnn/NNetwork.c:742
-    net->cur_iteration += 1;           // :773
-    AET_TRY(upload_hyper(net));
+    // The reference runs `subdivisions` of these calls, then ONE update with update_batch = batch * subdivisions
+    // (dnn/NNetwork.c:762-774, 667-680): weight gradients accumulate over the group's calls, and only its last
+    // call exchanges them between ranks and applies them.
+    const bool final = (net->seen / net->batch) % net->subdivisions == 0;
+    if (final) {
+        net->cur_iteration += 1;       // :773
+        AET_TRY(upload_hyper(net));
+    }
+    const int kind = final ? 1 : 0;
     aet_layer *sm = softmax_layer(net);
     if (sm) sm->cost_valid = false;
     const long before = ctx->launches;
-    if (net->use_graph && net->graph_exec && !ctx->profiling) {
-        AET_CUDA(cudaGraphLaunch(net->graph_exec, ctx->stream));
-        ctx->launches += net->launches_per_step;
-    } else if (net->use_graph && net->cur_iteration > 1 && !ctx->profiling) {
-        // the first eager step has sized every scratch buffer; capture the second one
+    if (net->use_graph && net->graph_exec[kind] && !ctx->profiling) {
+        AET_CUDA(cudaGraphLaunch(net->graph_exec[kind], ctx->stream));
+        ctx->launches += net->graph_launches[kind];
+    } else if (net->use_graph && net->eager_runs[kind] > 0 && !ctx->profiling) {
+        // an eager step of this kind has sized every scratch buffer; capture this one
         cudaGraph_t graph = nullptr;
         AET_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
         ctx->capturing = true;
-        int r = run_step(net);
+        int r = run_step(net, final);
         ctx->capturing = false;
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         if (r != AET_OK) { if (graph) cudaGraphDestroy(graph); return r; }
         if (e != cudaSuccess) { aet_set_error("graph capture failed: %s", cudaGetErrorString(e)); return AET_E_CUDA; }
-        net->launches_per_step = ctx->launches - before;
-        e = cudaGraphInstantiate(&net->graph_exec, graph, 0);
+        net->graph_launches[kind] = ctx->launches - before;
+        e = cudaGraphInstantiate(&net->graph_exec[kind], graph, 0);
         cudaGraphDestroy(graph);
-        if (e != cudaSuccess) { aet_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); net->graph_exec = nullptr; return AET_E_CUDA; }
-        AET_CUDA(cudaGraphLaunch(net->graph_exec, ctx->stream));
+        if (e != cudaSuccess) { aet_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); net->graph_exec[kind] = nullptr; return AET_E_CUDA; }
+        AET_CUDA(cudaGraphLaunch(net->graph_exec[kind], ctx->stream));
     } else {
-        AET_TRY(run_step(net));
-        net->launches_per_step = ctx->launches - before;
+        AET_TRY(run_step(net, final));
+        net->eager_runs[kind] += 1;
     }
+    if (final) net->launches_per_step = ctx->launches - before;
     if (loss) return aet_network_last_loss(net, loss);
     return AET_OK;
 }
@@ -609,13 +696,14 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
 extern "C" int aet_network_last_loss(aet_network *net, float *loss) {
     if (!net || !loss) { aet_set_error("null argument"); return AET_E_INVALID; }
     aet_layer *sm = softmax_layer(net);
-    if (!sm) { *loss = 0.f; return AET_OK; }
-    AET_CUDA(cudaMemcpyAsync(net->loss_pinned, sm->cost_dev, 2 * sizeof(float), cudaMemcpyDeviceToHost, net->ctx->stream));
+    AET_TRY(queue_loss_readback(net, net->loss_pinned));
     AET_CUDA(cudaStreamSynchronize(net->ctx->stream));
-    sm->cost_host = net->loss_pinned[0];
-    sm->cost_valid = true;
+    if (sm) {
+        sm->cost_host = net->loss_pinned[0];
+        sm->cost_valid = true;
+    }
     *loss = net->loss_pinned[1];
-    return AET_OK;
+    return status_to_code(net, net->loss_pinned);
 }
 
 extern "C" int aet_network_train_step(aet_network *net, const float *host_x, const float *host_truth, float *loss) {
@@ -625,12 +713,8 @@ extern "C" int aet_network_train_step(aet_network *net, const float *host_x, con
     AET_TRY(ctx_staging(ctx, (nx + nt) * sizeof(float)));
     // Page-locked caller buffers (cudaHostAlloc / cudaHostRegister / a pinned torch tensor) are copied
     // by DMA straight from where they are; pageable ones go through the context's pinned mirror.
-    auto pinned = [](const void *p) {
-        cudaPointerAttributes at;
-        if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
-        return at.type == cudaMemoryTypeHost;
-    };
-    if (pinned(host_x) && pinned(host_truth)) {
+    const bool pinned = host_pinned(host_x) && host_pinned(host_truth);
+    if (pinned) {
         AET_CUDA(cudaMemcpyAsync(ctx->staging, host_x, nx * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
         AET_CUDA(cudaMemcpyAsync(ctx->staging + nx, host_truth, nt * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
         if (!loss) {   // the caller may reuse its buffers as soon as this returns: wait for the two copies (not for the step)
@@ -647,8 +731,65 @@ extern "C" int aet_network_train_step(aet_network *net, const float *host_x, con
     AET_TRY(tensor_upload_staged(ctx, net->input->d, ctx->staging, net->input->n, net->input->c, net->input->h, net->input->w, net->input->cp));
     AET_TRY(tensor_upload_staged(ctx, net->truth->d, ctx->staging + nx, net->truth->n, net->truth->c, 1, 1, net->truth->cp));
     const int r = aet_network_train_step_device(net, loss);
-    if (!loss && net->ev_uploaded && pinned(host_x) && pinned(host_truth)) AET_CUDA(cudaEventSynchronize(net->ev_uploaded));
+    if (!loss && net->ev_uploaded && pinned) AET_CUDA(cudaEventSynchronize(net->ev_uploaded));
     return r;
+}
+
+// Pipelined form of aet_network_train_step.  The reference keeps the GPU fed with a host-side double buffer that
+// loader threads fill while the previous batch trains (dnn/ImageData.c:169-202) and uploads each batch before
+// its step (mtcs/MtcsIOData.c:50-52); here the double buffer is on the device: the copy of THIS call's batch
+// runs on a copy stream while the PREVIOUS call's step still computes, and nothing waits for this step.
+extern "C" int aet_network_train_step_async(aet_network *net, const float *host_x, const float *host_truth, float *previous_loss) {
+    if (!net || !host_x || !host_truth) { aet_set_error("aet_network_train_step_async: null argument"); return AET_E_INVALID; }
+    if (!net->train) { aet_set_error("network was created with train=0"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    const size_t nx = net->input->count(), nt = net->truth->count();
+    if (!net->copy_stream) {
+        AET_CUDA(cudaSetDevice(ctx->device));
+        AET_CUDA(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+        for (int k = 0; k < 2; ++k) {
+            AET_CUDA(cudaMalloc(&net->stage_dev[k], (nx + nt) * sizeof(float)));
+            AET_CUDA(cudaEventCreateWithFlags(&net->ev_staged[k], cudaEventDisableTiming));
+            AET_CUDA(cudaEventCreateWithFlags(&net->ev_consumed[k], cudaEventDisableTiming));
+            AET_CUDA(cudaEventCreateWithFlags(&net->ev_loss[k], cudaEventDisableTiming));
+        }
+        net->stage_floats = nx + nt;
+    }
+    const int slot = (int)(net->async_steps & 1), prev = slot ^ 1;
+    const bool reused = net->async_steps >= 2;
+    const float *src_x = host_x, *src_t = host_truth;
+    if (!(host_pinned(host_x) && host_pinned(host_truth))) {
+        // pageable buffers: through this slot's pinned mirror, free again once the copy of two calls ago has run
+        if (!net->stage_host[slot]) AET_CUDA(cudaMallocHost(&net->stage_host[slot], (nx + nt) * sizeof(float)));
+        if (reused) AET_CUDA(cudaEventSynchronize(net->ev_staged[slot]));
+        memcpy(net->stage_host[slot], host_x, nx * sizeof(float));
+        memcpy(net->stage_host[slot] + nx, host_truth, nt * sizeof(float));
+        src_x = net->stage_host[slot]; src_t = net->stage_host[slot] + nx;
+    }
+    if (reused) AET_CUDA(cudaStreamWaitEvent(net->copy_stream, net->ev_consumed[slot], 0));
+    AET_CUDA(cudaMemcpyAsync(net->stage_dev[slot], src_x, nx * sizeof(float), cudaMemcpyHostToDevice, net->copy_stream));
+    AET_CUDA(cudaMemcpyAsync(net->stage_dev[slot] + nx, src_t, nt * sizeof(float), cudaMemcpyHostToDevice, net->copy_stream));
+    AET_CUDA(cudaEventRecord(net->ev_staged[slot], net->copy_stream));
+    AET_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_staged[slot], 0));
+    pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
+    AET_TRY(tensor_upload_staged(ctx, net->input->d, net->stage_dev[slot], net->input->n, net->input->c, net->input->h, net->input->w, net->input->cp));
+    AET_TRY(tensor_upload_staged(ctx, net->truth->d, net->stage_dev[slot] + nx, net->truth->n, net->truth->c, 1, 1, net->truth->cp));
+    AET_CUDA(cudaEventRecord(net->ev_consumed[slot], ctx->stream));
+    AET_TRY(aet_network_train_step_device(net, nullptr));
+    float *ring = net->loss_pinned + 8 + 4 * slot;
+    AET_TRY(queue_loss_readback(net, ring));
+    AET_CUDA(cudaEventRecord(net->ev_loss[slot], ctx->stream));
+    const bool have_prev = net->async_steps >= 1;
+    net->async_steps += 1;
+    if (!have_prev) {
+        if (previous_loss) *previous_loss = NAN;
+        return AET_OK;
+    }
+    // the previous step's result: its successor is already queued, so waiting here never idles the device
+    AET_CUDA(cudaEventSynchronize(net->ev_loss[prev]));
+    const float *pr = net->loss_pinned + 8 + 4 * prev;
+    if (previous_loss) *previous_loss = pr[1];
+    return status_to_code(net, pr);
 }
 
 extern "C" int aet_network_predict(aet_network *net, const float *host_x, float *host_out) {
@@ -755,12 +896,20 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     NcclUniqueId id;
     memcpy(&id, unique_id_128, sizeof(id));
     void *comm = nullptr;
-    // The gradient buckets are small (<= 1.2 MB on the small CNN) and overlap the backward pass: a collective
-    // kernel of 31 CTAs (NCCL's own choice at 8 ranks) takes a fifth of the SMs from convolution kernels
-    // sized to one CTA per SM.  Measured at 8 GPUs: 0.309 ms per step by default, 0.294 with at most 8 CTAs,
-    // 0.346 with 4.  A value already in the environment is left alone.
-    setenv("NCCL_MAX_CTAS", "8", 0);
-    int r = api->comm_init_rank(&comm, world, id, rank);
+    // The gradient buckets are small and overlap the backward pass, whose convolution kernels are sized to one CTA
+    // per SM: the collective is capped to a few CTAs (option "nccl_max_ctas", 0 = NCCL's own choice) through this
+    // communicator's configuration, which leaves the process environment and other communicators alone.
+    int r = -1;
+    const int max_ctas = net->ctx->opt[OPT_NCCL_MAX_CTAS];
+    if (max_ctas > 0 && api->comm_init_rank_config) {
+        NcclConfig218 cfg;
+        cfg.size = sizeof(cfg); cfg.magic = 0xcafebeef; cfg.version = 21800;
+        cfg.blocking = INT_MIN; cfg.cgaClusterSize = INT_MIN; cfg.minCTAs = INT_MIN; cfg.maxCTAs = max_ctas;
+        cfg.netName = nullptr; cfg.splitShare = INT_MIN;
+        r = api->comm_init_rank_config(&comm, world, id, rank, &cfg);
+        net->comm_capped = r == 0;
+    }
+    if (r != 0) r = api->comm_init_rank(&comm, world, id, rank);
     if (r != 0) return nccl_fail(api, r, "ncclCommInitRank");
     net->comm = comm; net->rank = rank; net->world = world;
     AET_CUDA(cudaStreamCreateWithFlags(&net->comm_stream, cudaStreamNonBlocking));
@@ -785,8 +934,8 @@ extern "C" int aet_network_comm_exchange_export(aet_network *net, void *blob_80)
     AET_CUDA(cudaSetDevice(net->ctx->device));
     if (!net->xchg_local) {
         net->xchg_cap = 1024 * 1024;   // floats per parity buffer: gradient arenas up to 4 MB are exchanged whole
-        if (const char *e = getenv("AET_XCHG_CAP_FLOATS")) {   // tuning aid: a small value leaves only the last bucket to the exchange
-            const long v = atol(e);
+        {   // tuning aid (option "xchg_cap_floats"): a small value leaves only the last bucket to the exchange
+            const long v = net->ctx->opt[OPT_XCHG_CAP_FLOATS];
             if (v >= 1024 && v <= 16 * 1024 * 1024) net->xchg_cap = (size_t)v / 1024 * 1024;
         }
         const size_t bytes = kXchgFlagBytes + 2 * net->xchg_cap * sizeof(float);

@@ -4,6 +4,7 @@
 // copy plus one transposing kernel.  Replaces MtcsMem / MtcsStream call sites
 // (mtcs/MtcsTool.c:22-30, mtcs/MtcsIOData.c:15-52) and DataFactory.create*Data.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.h"
@@ -53,7 +54,7 @@ __global__ void nhwc_to_nchw_kernel(const float *__restrict__ src, float *__rest
 }  // namespace
 
 // ---------------------------------------------------------------------------- profiling
-void prof_begin(aet_context *ctx, const char *name, double bytes, double flops) {
+void prof_begin(aet_context *ctx, const char *name, double bytes, double flops, const char *variant) {
     if (ctx->event_next + 2 > ctx->event_pool.size()) {
         for (int i = 0; i < 256; ++i) {
             cudaEvent_t e;
@@ -62,7 +63,9 @@ void prof_begin(aet_context *ctx, const char *name, double bytes, double flops) 
         }
     }
     ProfileRecord r;
-    r.name = name; r.tag = ctx->prof_tag; r.bytes = bytes; r.flops = flops;
+    if (variant && *variant) snprintf(r.name, sizeof(r.name), "%s.%s", name, variant);
+    else snprintf(r.name, sizeof(r.name), "%s", name);
+    r.tag = ctx->prof_tag; r.bytes = bytes; r.flops = flops;
     r.e0 = ctx->event_pool[ctx->event_next++];
     r.e1 = ctx->event_pool[ctx->event_next++];
     cudaEventRecord(r.e0, ctx->stream);
@@ -70,6 +73,60 @@ void prof_begin(aet_context *ctx, const char *name, double bytes, double flops) 
 }
 void prof_end(aet_context *ctx) {
     if (!ctx->records.empty()) cudaEventRecord(ctx->records.back().e1, ctx->stream);
+}
+
+int ctx_smem_attr_impl(aet_context *ctx, const void *func, int bytes) {
+    for (const void *f : ctx->smem_attr_done)
+        if (f == func) return AET_OK;
+    AET_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    ctx->smem_attr_done.push_back(func);
+    return AET_OK;
+}
+
+namespace {
+struct OptionDesc {
+    const char *name, *env;
+    int def;
+    int env_value;   // value taken when the variable is set; -1: the variable's integer value
+};
+const OptionDesc kOptions[OPT_COUNT] = {
+    {"rows", "AET_NO_ROWS", 1, 0},
+    {"rows_fprop", "AET_NO_ROWS_F", 1, 0},
+    {"rows_dgrad", "AET_NO_ROWS_D", 1, 0},
+    {"smerge", "AET_NO_SMERGE", 1, 0},
+    {"ksplit", "AET_NO_KSPLIT", 1, 0},
+    {"mt2", "AET_NO_MT2", 1, 0},
+    {"rows_multi", "AET_ROWS_MULTI", 0, 1},
+    {"par_epilogue", "AET_NO_PAR_EPILOGUE", 1, 0},
+    {"fc_alias", "AET_NO_FC_ALIAS", 1, 0},
+    {"epilogue_stats", "AET_NO_EPILOGUE_STATS", 1, 0},
+    {"thin", "AET_NO_THIN", 1, 0},
+    {"overlap_wgrad", "AET_NO_OVERLAP", 1, 0},
+    {"wgrad_splits", "AET_WGRAD_SPLITS", 0, -1},
+    {"bn_tile", "AET_BN", 0, -1},
+    {"fuse", "AET_NO_FUSE", 1, 0},
+    {"linear_head", "AET_NO_LINEAR_HEAD", 1, 0},
+    {"xchg_cap_floats", "AET_XCHG_CAP_FLOATS", 0, -1},
+    {"nccl_max_ctas", "AET_NCCL_MAX_CTAS", 8, -1},
+    {"persistent", "AET_NO_PERSISTENT", 1, 0},
+};
+}  // namespace
+
+extern "C" int aet_context_set_option(aet_context *ctx, const char *name, int value) {
+    if (!ctx || !name) { aet_set_error("aet_context_set_option: null argument"); return AET_E_INVALID; }
+    if (strcmp(name, "gather_only") == 0) { ctx->conv_path = value ? 1 : 0; return AET_OK; }
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (strcmp(kOptions[i].name, name) == 0) { ctx->opt[i] = value; return AET_OK; }
+    aet_set_error("aet_context_set_option: unknown option '%s'", name);
+    return AET_E_INVALID;
+}
+extern "C" int aet_context_get_option(const aet_context *ctx, const char *name, int *value) {
+    if (!ctx || !name || !value) { aet_set_error("aet_context_get_option: null argument"); return AET_E_INVALID; }
+    if (strcmp(name, "gather_only") == 0) { *value = ctx->conv_path; return AET_OK; }
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (strcmp(kOptions[i].name, name) == 0) { *value = ctx->opt[i]; return AET_OK; }
+    aet_set_error("aet_context_get_option: unknown option '%s'", name);
+    return AET_E_INVALID;
 }
 
 int ctx_scratch(aet_context *ctx, size_t bytes, float **out) {
@@ -179,6 +236,12 @@ extern "C" aet_context *aet_context_create(int device) {
         delete ctx;
         return nullptr;
     }
+    // the environment only supplies initial values, here and nowhere else
+    for (int i = 0; i < OPT_COUNT; ++i) {
+        ctx->opt[i] = kOptions[i].def;
+        const char *e = getenv(kOptions[i].env);
+        if (e && *e) ctx->opt[i] = kOptions[i].env_value >= 0 ? kOptions[i].env_value : atoi(e);
+    }
     const char *path = getenv("AET_CONV_PATH");
     if (path && strcmp(path, "gather") == 0) ctx->conv_path = 1;
     return ctx;
@@ -240,10 +303,27 @@ extern "C" int aet_context_check(aet_context *ctx) {
     AET_CUDA(cudaMemcpy(&st, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(ctx->status_dev, 0, sizeof(int));
-        aet_set_error("a bounded device-side wait expired (status %d)", st);
-        return AET_E_TIMEOUT;
+        if (st & AET_STATUS_TIMEOUT) {
+            aet_set_error("a bounded device-side wait expired (status %d)", st);
+            return AET_E_TIMEOUT;
+        }
+        aet_set_error("non-finite values were found in weights or gradients and replaced as the reference's update does (status %d)", st);
+        return AET_E_NAN;
     }
     return AET_OK;
+}
+
+extern "C" int aet_context_set_wait_limit(aet_context *ctx, unsigned long long nanoseconds) {
+    if (!ctx || nanoseconds == 0) { aet_set_error("aet_context_set_wait_limit: bad argument"); return AET_E_INVALID; }
+    AET_CUDA(cudaSetDevice(ctx->device));
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    AET_TRY(conv_set_wait_limit(nanoseconds));
+    return elementwise_set_wait_limit(nanoseconds);
+}
+
+extern "C" int aet_context_wait_probe(aet_context *ctx) {
+    if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
+    return conv_wait_probe(ctx);
 }
 
 extern "C" int aet_context_profile(aet_context *ctx, int enable) {

@@ -1,6 +1,6 @@
 // Thin inline-PTX layer for sm_100a: mbarrier, TMA (tiled bulk tensor copies), tcgen05 MMA with
 // TMEM accumulators, and the 64-bit shared-memory matrix descriptors the MMA consumes.
-// Every wait is bounded: it gives up after about a second, records a status code and returns
+// Every wait is bounded: it gives up after a limit (one second by default), records a status code and returns
 // false so that the kernel can unwind (free its TMEM) instead of hanging the device.
 #pragma once
 #include <cuda.h>
@@ -46,8 +46,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Wall-clock limit of every device-side wait (nanoseconds).
-constexpr uint64_t kWaitLimitNs = 1000000000ull;
+// Wall-clock limit of every device-side wait (nanoseconds); one second unless the host changes it
+// (cudaMemcpyToSymbol, per device).  Read only on the slow path of a wait.
+__constant__ unsigned long long g_wait_limit_ns = 1000000000ull;
 
 // Waits for the phase with the given parity.  `abort_flag` lives in shared memory: once any
 // role of the CTA has given up, the others leave their waits quickly as well.
@@ -59,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > g_wait_limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

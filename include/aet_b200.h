@@ -96,8 +96,25 @@ void        *aet_context_stream(aet_context *ctx);
 int          aet_context_set_parity(aet_context *ctx, aet_parity_mode mode);
 int          aet_context_set_math(aet_context *ctx, aet_math_mode mode);
 int          aet_context_synchronize(aet_context *ctx);
-/* Reads and clears the device status word written by bounded waits; AET_OK or AET_E_TIMEOUT. */
+/* Behaviour switches (kernel choice, fusions, stream overlap), by name: "rows", "rows_fprop", "rows_dgrad",
+ * "smerge", "ksplit", "mt2", "rows_multi", "par_epilogue", "fc_alias", "epilogue_stats", "thin", "persistent",
+ * "overlap_wgrad", "wgrad_splits", "bn_tile", "gather_only" (take effect at the next launch), "fuse",
+ * "linear_head", "xchg_cap_floats" (read when a network is built / the exchange is exported).  The matching
+ * AET_* environment variables only give the initial values and are read once, in aet_context_create. */
+int          aet_context_set_option(aet_context *ctx, const char *name, int value);
+int          aet_context_get_option(const aet_context *ctx, const char *name, int *value);
+/* Reads and clears the device status word; AET_OK, AET_E_TIMEOUT (a bounded wait expired: results of the work
+ * in flight are incomplete) or AET_E_NAN (the update found non-finite weights or gradients and replaced them
+ * as the reference does, mtcs/MtcsConvLayer.c:586-587 -- informational, training continued). */
 int          aet_context_check(aet_context *ctx);
+/* Limit of every device-side wait (mbarrier waits of the convolution kernels, the peer-flag wait of the update
+ * kernel), in nanoseconds; one second by default.  Applies to the context's device.  After the limit a kernel
+ * gives up, frees what it holds, sets the status word and returns: nothing traps and the context stays usable.
+ * A data-parallel job whose ranks can be further apart than the limit (a rank writing a checkpoint) raises it. */
+int          aet_context_set_wait_limit(aet_context *ctx, unsigned long long nanoseconds);
+/* Self-test of that path: launches one warp that waits on a barrier nothing arrives at.  After the limit the
+ * kernel returns and aet_context_check reports AET_E_TIMEOUT. */
+int          aet_context_wait_probe(aet_context *ctx);
 /* Per-kernel device timing (CUDA events on the context stream around every launch the library
  * makes): enable, run work, read the table grouped by kernel name.  Replaces the reference's
  * wall-clock prints (dnn/Classifier.c:255,312-319). */
@@ -180,14 +197,25 @@ int   aet_network_forward(aet_network *net, aet_state state);
 int   aet_network_backward(aet_network *net, aet_state state);
 int   aet_network_update(aet_network *net);
 float aet_network_cost(aet_network *net);                      /* getNetworkCost dnn/NNetwork.c:611-624 */
-/* NNetwork.train(InputData*,TruthData*) + update (dnn/NNetwork.c:740-774), subdivisions=1:
- * host NCHW batch and one-hot truth in, mean loss out (cost / batch). Copies are asynchronous on
- * the context stream; the loss read-back is the only host synchronisation. */
+/* NNetwork.train(InputData*,TruthData*) (dnn/NNetwork.c:740-760): host NCHW batch and one-hot truth in, mean
+ * loss of this batch out (cost / batch).  With [net] subdivisions = S > 1 the weight gradients accumulate over S
+ * calls and the S-th call runs the update with update_batch = batch * S, as NNetwork.train(ImageData*) does
+ * (dnn/NNetwork.c:762-774).  Copies are asynchronous on the context stream; the loss read-back is the only host
+ * synchronisation; AET_E_TIMEOUT is returned when a bounded device-side wait expired during the step. */
 int   aet_network_train_step(aet_network *net, const float *host_x, const float *host_truth, float *loss);
 /* Same step on data already resident in the network's input/truth tensors.  When `loss` is NULL
  * nothing is read back (the loss stays in device memory until aet_network_last_loss). */
 int   aet_network_train_step_device(aet_network *net, float *loss);
 int   aet_network_last_loss(aet_network *net, float *loss);
+/* Pipelined aet_network_train_step: the device-side double buffer that stands for the reference's loader double
+ * buffer (dnn/ImageData.c:169-202) and per-step upload (mtcs/MtcsIOData.c:50-52).  The host->device copy of this
+ * call's batch runs on a copy stream while the previous call's step computes; the call waits for nothing of its
+ * own step and returns the PREVIOUS call's mean loss in `previous_loss` (NaN on the first call; NULL to skip).
+ * Page-locked buffers are read by DMA until the NEXT call (or aet_network_last_loss) returns: keep them
+ * unchanged until then (alternate two); pageable buffers are copied before the call returns.
+ * aet_network_last_loss drains the pipeline.  The first call allocates the two staging slots.
+ * Returns AET_E_TIMEOUT when the previous step's kernels gave up a bounded wait. */
+int   aet_network_train_step_async(aet_network *net, const float *host_x, const float *host_truth, float *previous_loss);
 /* NNetwork.predict (dnn/NNetwork.c:411-428): forward with train=0, copy the last layer's output. */
 int   aet_network_predict(aet_network *net, const float *host_x, float *host_out);
 /* Capture forward+backward+update into a CUDA graph that later train steps replay (0 = off). */
@@ -223,9 +251,9 @@ int   aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count)
 
 /* ------------------------------------------------------------------ allocation-free entry point
  * No counterpart in the reference (its kernels need no scratch; ours reduce in two stages).
- * For callers that must not allocate device memory while they run -- a process whose device pool is
- * fixed at start-up, a plugin invoked from another runtime's callback, a service between
- * allocation-free phases -- this computes the bias gradient
+ * For callers that must not allocate device memory while they run -- a process whose whole device
+ * pool is sized and handed out at start-up, a service inside a phase where cudaMalloc (which
+ * synchronises the device) is off limits -- this computes the bias gradient
  *     bias_updates[c] += sum over p of delta[p][c]
  * with the stage-one partial sums held in a fixed 1 MiB __device__ array inside the library instead
  * of the context's cudaMalloc'ed scratch arena.  It calls no cudaMalloc / cudaFree.
@@ -236,9 +264,12 @@ int   aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count)
  *                 part, more when `pixels` is small), otherwise AET_E_INVALID
  *   cuda_stream   cudaStream_t to launch on (NULL = the legacy default stream)
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress) with
- * that device current; make that first call outside any stream capture.  All calls on a device share
- * the one array: calls whose kernels may overlap on the GPU (different streams) race -- serialise
- * them.  Nothing in the array has to be cleared between calls. */
+ * that device current; under lazy module loading that lookup is also when the driver backs the
+ * array with memory.  So make one warm-up call per device at start-up, while allocation is still
+ * allowed and outside any stream capture; host threads may race on it (it is serialised inside).
+ * The address is cached for the life of the process: do not call cudaDeviceReset between calls.
+ * All calls on a device share the one array: calls whose kernels may overlap on the GPU (different
+ * streams) race -- serialise them.  Nothing in the array has to be cleared between calls. */
 int   aet_backward_bias_static(const float *delta, float *bias_updates, long long pixels, int channels, void *cuda_stream);
 
 #ifdef __cplusplus

@@ -781,3 +781,39 @@ void aeto_fill_uniform(float *dst, size_t n, uint64_t seed, uint64_t tensor_id) 
 void aeto_fill_normal(float *dst, size_t n, uint64_t seed, uint64_t tensor_id, float mean, float stddev) {
     aet_rng_fill_normal(dst, n, seed, tensor_id, mean, stddev);
 }
+
+/* ------------------------------------------------------------------ learning-rate schedule
+ * dnn/NNetwork.c:215-246, expression by expression: batch_num is a size_t there, so `batch_num / step`,
+ * `batch_num < burn_in` and `batch_num - step` are unsigned arithmetic (the sig policy's difference wraps
+ * while batch_num < step), and pow / exp are the double functions. */
+float aeto_current_rate(size_t batch_num, int policy, float learning_rate, int burn_in, float power, int step, float scale,
+                        const int *steps, const float *scales, int num_steps, float gamma, int max_batches) {
+    int i;
+    float rate;
+    if (batch_num < (size_t)burn_in) return (float)(learning_rate * pow((float)batch_num / burn_in, power));
+    switch (policy) {
+    case 0: return learning_rate;
+    case 1: return (float)(learning_rate * pow(scale, batch_num / step));
+    case 2:
+        rate = learning_rate;
+        for (i = 0; i < num_steps; ++i) {
+            if ((size_t)steps[i] > batch_num) return rate;
+            rate *= scales[i];
+        }
+        return rate;
+    case 3: return (float)(learning_rate * pow(gamma, (int)batch_num));
+    case 4: return (float)(learning_rate * pow(1 - (float)batch_num / max_batches, power));
+    case 5: return (float)(learning_rate * (1. / (1. + exp(gamma * (batch_num - step)))));
+    default: return learning_rate;
+    }
+}
+
+/* mtcs/MtcsTool.c:77-107 */
+void aeto_fix_nan_and_inf(float *v, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (isnan(v[i]) || isinf(v[i])) v[i] = 1.0f / (fabsf((float)i) + 1);
+}
+void aeto_reset_nan_and_inf(float *v, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (isnan(v[i]) || isinf(v[i])) v[i] = 0;
+}

@@ -110,6 +110,14 @@ float  aeto_net_cost(const aeto_net *net);
 /* forward + backward + update; returns cost / batch like NNetwork.train (subdivisions = 1). */
 float  aeto_net_train_step(aeto_net *net, const float *x, const float *truth, float lr, float momentum, float decay);
 
+/* NNetwork.getCurrentRate, dnn/NNetwork.c:215-246 (policy: 0 constant, 1 step, 2 steps, 3 exp, 4 poly, 5 sig;
+ * the RANDOM policy is not restated).  batch_num = seen / (batch * subdivisions). */
+float  aeto_current_rate(size_t batch_num, int policy, float learning_rate, int burn_in, float power, int step, float scale,
+                         const int *steps, const float *scales, int num_steps, float gamma, int max_batches);
+/* fix_nan_and_inf / reset_nan_and_inf of the GPU update, mtcs/MtcsTool.c:77-107 */
+void   aeto_fix_nan_and_inf(float *v, size_t n);
+void   aeto_reset_nan_and_inf(float *v, size_t n);
+
 /* synthetic tensors (aet_rng.h) exposed for bindings */
 void aeto_fill_uniform(float *dst, size_t n, uint64_t seed, uint64_t tensor_id);
 void aeto_fill_normal(float *dst, size_t n, uint64_t seed, uint64_t tensor_id, float mean, float stddev);

@@ -89,6 +89,11 @@ class Oracle:
         L.aeto_net_cost.restype = C.c_float
         L.aeto_net_train_step.argtypes = [C.c_void_p, _f, _f, C.c_float, C.c_float, C.c_float]
         L.aeto_net_train_step.restype = C.c_float
+        L.aeto_current_rate.argtypes = [C.c_size_t, C.c_int, C.c_float, C.c_int, C.c_float, C.c_int, C.c_float, _i, _f, C.c_int,
+                                        C.c_float, C.c_int]
+        L.aeto_current_rate.restype = C.c_float
+        L.aeto_fix_nan_and_inf.argtypes = [_f, C.c_size_t]
+        L.aeto_reset_nan_and_inf.argtypes = [_f, C.c_size_t]
         L.aeto_fill_uniform.argtypes = [_f, C.c_size_t, C.c_uint64, C.c_uint64]
         L.aeto_fill_normal.argtypes = [_f, C.c_size_t, C.c_uint64, C.c_uint64, C.c_float, C.c_float]
 
@@ -222,6 +227,25 @@ class Oracle:
         p, u = _arr(p).copy(), _arr(u).copy()
         self.lib.aeto_sgd_plain(_fp(p), _fp(u), p.size, batch, lr, momentum)
         return p, u
+
+    def current_rate(self, batch_num, policy, learning_rate, burn_in=0, power=4.0, step=1, scale=1.0, steps=(), scales=(),
+                     gamma=1.0, max_batches=0):
+        """NNetwork.getCurrentRate; policy 0 constant, 1 step, 2 steps, 3 exp, 4 poly, 5 sig."""
+        st = np.ascontiguousarray(steps, np.int32)
+        sc = np.ascontiguousarray(scales, np.float32)
+        n = min(st.size, sc.size)
+        return self.lib.aeto_current_rate(batch_num, policy, learning_rate, burn_in, power, step, scale,
+                                          st.ctypes.data_as(_i) if n else None, _fp(sc) if n else None, n, gamma, max_batches)
+
+    def fix_nan_and_inf(self, v):
+        v = _arr(v).copy().reshape(-1)
+        self.lib.aeto_fix_nan_and_inf(_fp(v), v.size)
+        return v
+
+    def reset_nan_and_inf(self, v):
+        v = _arr(v).copy().reshape(-1)
+        self.lib.aeto_reset_nan_and_inf(_fp(v), v.size)
+        return v
 
     def dropout_forward(self, x, r, probability):
         x = _arr(x).copy()

@@ -1,6 +1,7 @@
-"""Python reader of the Darknet-style cfg subset the library accepts; same keys and defaults as the
-C reader (csrc/network.cu), which follows dnn/NetworkFactory.c:77-173,328-354,543-601,671-824.
-Used by the tests and the benchmark to describe the same network to the CPU oracle."""
+"""TEST INFRASTRUCTURE ONLY -- Python reader of the Darknet-style cfg subset the library accepts; same keys and
+defaults as the library's C reader, which follows dnn/NetworkFactory.c:77-173,328-354,543-601,671-824.
+Describes a network to the CPU oracle (tests, the smoke check and the benchmark's CPU-baseline legs);
+the product package never imports it."""
 
 ACT = {"linear": 0, "relu": 1, "leaky": 2}
 CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4

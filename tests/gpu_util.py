@@ -1,4 +1,7 @@
 """Helpers shared by the GPU parity tests: run one layer through the C ABI and through the oracle."""
+import os
+from concurrent.futures import ThreadPoolExecutor
+
 import numpy as np
 
 from oracle import binding as ob
@@ -7,8 +10,35 @@ TOL_TF32 = 1e-2      # relative L2, TF32 inputs with FP32 accumulation
 TOL_3X = 1e-5        # relative L2, 3xTF32 split
 
 
-def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bias=True, want_dx=True):
-    """Forward + backward of one convolution (no BN) on the GPU and in the oracle; returns both result dicts."""
+def _chunks(n, parts):
+    step = max(1, (n + parts - 1) // parts)
+    return [(i, min(n, i + step)) for i in range(0, n, step)]
+
+
+def oracle_conv_forward_mt(oracle, x, w, stride, pad):
+    """The oracle's per-image convolution loop run over slices of the batch on host threads (images are
+    independent in the forward pass, so the result is the single-thread one bit for bit)."""
+    parts = _chunks(x.shape[0], os.cpu_count() or 1)
+    with ThreadPoolExecutor(len(parts)) as ex:
+        ys = list(ex.map(lambda r: oracle.conv_forward(x[r[0]:r[1]], w, stride, stride, pad), parts))
+    return np.concatenate(ys, 0)
+
+
+def oracle_conv_backward_mt(oracle, x, w, d, stride, pad, need_dx=True):
+    """Backward over slices of the batch on host threads: dX is per image (exact); dW is the sum of the
+    slices' weight gradients in slice order (FP32 grouping differs from the one-thread loop by rounding only)."""
+    parts = _chunks(x.shape[0], os.cpu_count() or 1)
+    with ThreadPoolExecutor(len(parts)) as ex:
+        rs = list(ex.map(lambda r: oracle.conv_backward(x[r[0]:r[1]], w, d[r[0]:r[1]], stride, stride, pad, need_dx=need_dx), parts))
+    dw = rs[0][0].astype(np.float64)
+    for r in rs[1:]:
+        dw += r[0]
+    return dw.astype(np.float32), (np.concatenate([r[1] for r in rs], 0) if need_dx else None)
+
+
+def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bias=True, want_dx=True, threads=False):
+    """Forward + backward of one convolution (no BN) on the GPU and in the oracle; returns both result dicts.
+    threads=True runs the oracle's per-image loops over batch slices on all host cores (full-size cases)."""
     import aet_cnn_b200.synth as synth
     oh, ow = (H + 2 * pad - size) // stride + 1, (W + 2 * pad - size) // stride + 1
     x = synth.uniform((N, C, H, W), seed, 1)
@@ -36,16 +66,26 @@ def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bia
         dxt.close()
 
     mode = ob.MODE_MTCS
-    y = oracle.activate(oracle.add_bias(oracle.conv_forward(x, w, stride, stride, pad), b), act, mode)
+    conv = oracle_conv_forward_mt(oracle, x, w, stride, pad) if threads else oracle.conv_forward(x, w, stride, stride, pad)
+    y = oracle.activate(oracle.add_bias(conv, b), act, mode)
     # The activation gradient is a step function of the layer's stored output.  Backward parity is
     # taken on identical inputs, so the mask comes from the output the device stored: a TF32-rounded
     # value next to a kink may sit on the other side of it, which changes that element's gradient
     # tenfold and says nothing about the backward kernels.
     d = oracle.gradient(got["y"], act, dy)
-    dw, dx = oracle.conv_backward(x, w, d, stride, stride, pad, need_dx=want_dx)
+    if threads:
+        dw, dx = oracle_conv_backward_mt(oracle, x, w, d, stride, pad, need_dx=want_dx)
+    else:
+        dw, dx = oracle.conv_backward(x, w, d, stride, stride, pad, need_dx=want_dx)
     ref = dict(y=y, dw=dw, dx=dx, db=oracle.backward_bias(d))
     return got, ref
 
 
 def kernels_used(ctx):
+    """Kernel labels of the profiled launches without their ".variant" suffix."""
+    return {r["name"].split(".")[0] for r in ctx.profile_read()}
+
+
+def variants_used(ctx):
+    """Full labels ("kernel.variant") of the profiled launches: which code path each launcher picked."""
     return {r["name"] for r in ctx.profile_read()}

@@ -10,10 +10,11 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import bench  # noqa: E402
 
 aet = bench.load_package()
-import aet_cnn_b200.cfgfile as cfgfile  # noqa: E402
+from oracle import cfgfile  # noqa: E402
 import aet_cnn_b200.parallel as par  # noqa: E402
 import aet_cnn_b200.synth as synth  # noqa: E402
 
@@ -23,7 +24,7 @@ def run(mode, rank, world, local_rank, steps=4, batch=16):
     opts, specs = cfgfile.network_spec(text, batch)
     ctx = aet.Context(local_rank)
     net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
-    bench.init_weights(aet, synth, cfgfile, net, specs, 3)
+    bench.init_weights(aet, synth, net, 3)
     net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
     if mode == "peer":
         net.comm_exchange_attach(par.all_gather_bytes(net.comm_exchange_export()))
@@ -39,11 +40,58 @@ def run(mode, rank, world, local_rank, steps=4, batch=16):
     return dict(hash=h, identical_across_ranks=same, losses=losses)
 
 
+def oracle_check(rank, world, local_rank, steps=2, batch=8):
+    """Two data-parallel steps on the GPUs (3xTF32 math, NCCL exchange) against the same two steps emulated with the
+    CPU oracle: one oracle network per rank, gradients summed over the ranks, update with the global batch.
+    Returns the relative L2 error of every convolution's weights and of the weight CHANGE since initialisation
+    (the part the exchange is responsible for)."""
+    import numpy as np
+    from oracle import binding as ob
+    from dp_oracle import dp_step, grad_keys, sum_in_place
+    text = open(os.path.join(aet.CFG_DIR, "cifar_small.cfg")).read()
+    opts, specs = cfgfile.network_spec(text, batch)
+    ctx = aet.Context(local_rank, math=aet.MATH_3XTF32)
+    net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+    bench.init_weights(aet, synth, net, 3)
+    convs = [i for i, s in enumerate(specs) if s["type"] == cfgfile.CONV]
+    w0 = {i: net.layer(i).read(aet.P_WEIGHTS) for i in convs}
+    net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
+    for s in range(steps):
+        tid = par.shard_tensor_id(s, rank, world)
+        net.train(synth.uniform((batch, 3, 32, 32), 7, 2 * tid), synth.labels(batch, 10, 7, 2 * tid + 1)[1])
+    ctx.check()
+    got = {i: net.layer(i).read(aet.P_WEIGHTS) for i in convs}
+    net.close(); ctx.close()
+    errs = {}
+    if rank == 0:
+        oracle = ob.Oracle("acc64")
+        nets = []
+        for r in range(world):
+            o = oracle.net(specs, batch, 3, 32, 32, mode=ob.MODE_MTCS)
+            for i in convs:
+                o.set_param(i, ob.P_WEIGHTS, w0[i])
+            nets.append(o)
+        keys = grad_keys(ob, specs)
+        for s in range(steps):
+            batches = []
+            for r in range(world):
+                tid = par.shard_tensor_id(s, r, world)
+                batches.append((synth.uniform((batch, 3, 32, 32), 7, 2 * tid), synth.labels(batch, 10, 7, 2 * tid + 1)[1]))
+            dp_step(ob, nets, batches, world, sum_in_place, keys, opts["learning_rate"], opts["momentum"], opts["decay"])
+        for i in convs:
+            ref = nets[0].param(i, ob.P_WEIGHTS).astype(np.float64)
+            g, z = got[i].ravel().astype(np.float64), w0[i].ravel().astype(np.float64)
+            errs[str(i)] = dict(weights=float(np.linalg.norm(g - ref) / np.linalg.norm(ref)),
+                                change=float(np.linalg.norm((g - z) - (ref - z)) / np.linalg.norm(ref - z)))
+    return errs
+
+
 def main():
     rank, world, local_rank = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     out = {m: run(m, rank, world, local_rank) for m in ("nccl", "peer")}
+    out["oracle"] = oracle_check(rank, world, local_rank)
     if rank == 0:
         print("RESULT " + json.dumps(out), flush=True)
     dist.barrier()

@@ -44,7 +44,7 @@ def test_null_arguments_return_errors_not_crashes(aet):
 
 
 def test_cfg_reader_defaults(aet):
-    import aet_cnn_b200.cfgfile as cfgfile
+    from oracle import cfgfile
     text = open(os.path.join(aet.CFG_DIR, "cifar_small.cfg")).read()
     net, layers = cfgfile.network_spec(text)
     assert net["batch"] == 128 and (net["c"], net["h"], net["w"]) == (3, 32, 32)

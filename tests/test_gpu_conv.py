@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import rel_l2
-from gpu_util import TOL_3X, TOL_TF32, conv_case, kernels_used
+from gpu_util import TOL_3X, TOL_TF32, conv_case, kernels_used, variants_used
 
 pytestmark = pytest.mark.gpu
 
@@ -46,9 +46,8 @@ def check(got, ref, tol):
 
 @pytest.fixture(scope="module")
 def ctx_gather(aet):
-    os.environ["AET_CONV_PATH"] = "gather"
     c = aet.Context(0)
-    del os.environ["AET_CONV_PATH"]
+    c.set_option("gather_only", 1)
     yield c
     c.close()
 
@@ -115,6 +114,62 @@ def test_conv_thin_tf32(aet, ctx, oracle, shape):
     kp = (shape[4] + 3) // 4 * 4
     if kp % 32 == 0 or kp < 32:
         assert "conv_wgrad_thin" in used, used
+    check(got, ref, TOL_TF32)
+
+
+# The benchmark network's second and third convolution at the benchmark's batch (128 images per GPU): above
+# ~111 images the row-sharing launcher switches to other code paths than at small batches (two pixel tiles per
+# CTA with a second epilogue warp group, column taps merged into the MMA's N for the narrow data gradient, K
+# split over a two-CTA cluster, two filter tiles), so these shapes are checked at that size and the path each
+# launch took is asserted by its label.  N = 112 is the smallest batch above the two-tile threshold.
+BENCH_SHAPES = [
+    # shape, {kernel: variant} expected on a 148-SM part
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1",
+                                          "conv_wgrad_tma_rows": "n64_sp49"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2",
+                                         "conv_wgrad_tma_rows": "n128_sp24"}),
+    ((112, 64, 16, 16, 128, 3, 1, 1, 0), {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
+]
+
+
+@pytest.mark.parametrize("shape,variants", BENCH_SHAPES)
+def test_conv_benchmark_shapes_at_benchmark_batch(aet, ctx, oracle, shape, variants):
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=500 + shape[0], threads=True)
+        used = variants_used(ctx)
+    finally:
+        ctx.profile(0)
+    for kernel, variant in variants.items():
+        assert kernel + "." + variant in used, (kernel, variant, sorted(used))
+    check(got, ref, TOL_TF32)
+
+
+# The per-shape sweep of the reference's benchmark list at its batch of 256 (fprop + dgrad + wgrad each).
+SWEEP_SHAPES = [
+    (256, 3, 32, 32, 64, 3, 1, 1, 0),
+    (256, 64, 16, 16, 128, 3, 1, 1, 0),
+    (256, 128, 8, 8, 256, 3, 1, 1, 0),
+    (256, 256, 8, 8, 256, 3, 1, 1, 0),
+    (256, 256, 4, 4, 10, 1, 1, 0, 0),
+]
+
+
+@pytest.mark.parametrize("shape", SWEEP_SHAPES)
+def test_conv_sweep_shapes_at_batch_256(aet, ctx, oracle, shape):
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=600 + shape[1], threads=True)
+        used = kernels_used(ctx)
+        print("sweep shape", shape, "->", sorted(variants_used(ctx)))
+    finally:
+        ctx.profile(0)
+    # every sweep shape is on a TMA or first-layer kernel; only the 3-channel layer's data gradient (which a
+    # network never asks for: nothing precedes its first layer) goes through the gather producer
+    allowed = {"conv_dgrad_gather"} if shape[1] < 32 else set()
+    assert not any("gather" in k for k in used - allowed), used
     check(got, ref, TOL_TF32)
 
 

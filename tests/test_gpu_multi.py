@@ -1,5 +1,5 @@
 """Two-GPU data parallel through the C ABI (skipped on a box with one GPU): NCCL all-reduce against the peer
-exchange fused into the update kernel."""
+exchange fused into the update kernel, and the data-parallel weights against the CPU oracle's emulation of the ranks."""
 import json
 import os
 import subprocess
@@ -26,3 +26,7 @@ def test_two_ranks_nccl_and_peer_exchange_agree():
         assert out[mode]["identical_across_ranks"], mode          # weights bitwise identical on both ranks
     assert out["nccl"]["hash"] == out["peer"]["hash"]             # two ranks: the same sum either way
     assert out["nccl"]["losses"] == out["peer"]["losses"]
+    # the data-parallel result itself against the CPU oracle's emulation of the two ranks (3xTF32 math, two steps)
+    assert out["oracle"], out
+    for layer, e in out["oracle"].items():
+        assert e["weights"] < 1e-4 and e["change"] < 5e-2, (layer, e)

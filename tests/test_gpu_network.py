@@ -15,14 +15,14 @@ pytestmark = pytest.mark.gpu
 PARAMS = ["P_WEIGHTS", "P_BIASES", "P_SCALES", "P_ROLLING_MEAN", "P_ROLLING_VARIANCE", "P_WEIGHT_UPDATES"]
 
 
-def build_pair(aet, ctx, oracle, cfg_name, batch, mode=ob.MODE_MTCS, seed=20241):
-    import aet_cnn_b200.cfgfile as cfgfile
+def build_pair(aet, ctx, oracle, cfg_name, batch, mode=ob.MODE_MTCS, seed=20241, threads=1):
+    from oracle import cfgfile
     import aet_cnn_b200.synth as synth
     text = open(os.path.join(aet.CFG_DIR, cfg_name)).read()
     ctx.set_parity(mode)
     net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
     opts, specs = cfgfile.network_spec(text, batch)
-    onet = oracle.net(specs, batch, opts["c"], opts["h"], opts["w"], mode=mode)
+    onet = oracle.net(specs, batch, opts["c"], opts["h"], opts["w"], mode=mode, threads=threads)
     cin = opts["c"]
     for i, s in enumerate(specs):
         if s["type"] != cfgfile.CONV:
@@ -90,23 +90,39 @@ def test_small_cnn_training_matches_oracle(aet, ctx, oracle64, mode):
         ctx.set_parity(ob.MODE_MTCS)
 
 
-def test_small_cnn_tf32_first_step_layerwise(aet, ctx, oracle):
-    """Default TF32 math on the whole network: activations within 1e-2 of the FP32 oracle, and every
-    convolution's backward kernels within 1e-2 when the oracle is given the SAME inputs the device
-    kernels consumed (the layer's input activations and its post-BN-backward delta)."""
-    import aet_cnn_b200.cfgfile as cfgfile
-    batch = 16
-    net, onet, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+# code path of every row-sharing launch of the small CNN at the benchmark batch on a 148-SM part
+BENCH_VARIANTS = {"conv_fprop_tma_rows.mt2e_n128x1#2", "conv_dgrad_tma_rows.sm_mt2_n192x1#2", "conv_wgrad_tma_rows.n64_sp49#2",
+                  "conv_fprop_tma_rows.mt1_n128x2#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
+
+
+@pytest.mark.parametrize("batch", [16, 128])
+def test_small_cnn_tf32_first_step_layerwise(aet, ctx, oracle, batch):
+    """Default TF32 math on the whole network: activations and batch statistics within 1e-2 of the FP32
+    oracle, and every convolution's backward kernels within 1e-2 when the oracle is given the SAME inputs
+    the device kernels consumed (the layer's input activations and its post-BN-backward delta).  Batch 128
+    is the benchmark's: the launchers pick other code paths there than at 16, asserted by their labels."""
+    from oracle import cfgfile
+    from gpu_util import oracle_conv_backward_mt
+    net, onet, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch, threads=os.cpu_count() or 1)
     x, truth = batch_for(opts, 10, batch, 7, 0)
     net.input.write(x); net.truth.write(truth)
+    ctx.profile(1)
     net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
     net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    labels = {r["name"] for r in ctx.profile_read()}
+    ctx.profile(0)
+    if batch == 128:
+        assert BENCH_VARIANTS <= labels, sorted(labels)
     onet.forward(x, truth)
     onet.backward(x)
     ctx.check()
     for i in range(net.layer_count):
         got = net.layer(i).read(aet.P_OUTPUT)
         assert rel_l2(got, onet.param(i, ob.P_OUTPUT)) < 1e-2, i
+        if specs[i]["type"] == cfgfile.CONV and specs[i]["batch_normalize"]:
+            # statistics gathered by the convolution's epilogue (two partial rows per CTA at batch 128)
+            assert rel_l2(net.layer(i).read(aet.P_MEAN), onet.param(i, ob.P_MEAN)) < 1e-2, i
+            assert rel_l2(net.layer(i).read(aet.P_VARIANCE), onet.param(i, ob.P_VARIANCE)) < 1e-2, i
     assert abs(net.cost() - onet.cost()) < 1e-2 * abs(onet.cost())
     # the softmax delta's support (the labels) is integer data: exact
     assert np.array_equal(net.layer(8).read(aet.P_LOSS) != 0, onet.param(8, ob.P_LOSS) != 0)
@@ -123,12 +139,51 @@ def test_small_cnn_tf32_first_step_layerwise(aet, ctx, oracle):
         xin = x if i == 0 else net.layer(i - 1).read(aet.P_OUTPUT).reshape(batch, c, h, w)
         delta = net.layer(i).read(aet.P_DELTA).reshape(batch, oc, oh, ow)      # as consumed by wgrad / dgrad
         wts = net.layer(i).read(aet.P_WEIGHTS).reshape(oc, c, s["size"], s["size"])
-        dw, dx = oracle.conv_backward(xin, wts, delta, s["stride_x"], s["stride_y"], s["pad"], need_dx=i > 0)
+        dw, dx = oracle_conv_backward_mt(oracle, xin, wts, delta, s["stride_x"], s["pad"], need_dx=i > 0)
         assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), dw) < 1e-2, ("wgrad", i)
         if i > 0:
             assert rel_l2(net.layer(i - 1).read(aet.P_DELTA), dx) < 1e-2, ("dgrad", i)
         # coarse whole-network agreement (kink / argmax flips upstream change ~sqrt(flip fraction) of it)
         assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 0.2, i
+    net.close()
+
+
+def test_small_cnn_100_steps_at_batch_128_track_the_oracle(aet, ctx):
+    """The reference's small-CNN training case at its stated size: batch 128, 100 SGD steps (lr 0.1, momentum 0.9,
+    decay 5e-4), a fresh synthetic batch every step, default TF32 math with CUDA-graph replay, against the CPU
+    oracle (its timing build on all host cores: same formulas, summation order as the compiler leaves it).
+    After the first step (before the piecewise network has had time to amplify rounding) every parameter agrees
+    within 1e-2.  Over the run the two trajectories are separate samples of a chaotic map (leaky kinks, argmax
+    flips), so the loss curves are compared as curves: every step within 2 % of the oracle's loss, the mean
+    relative difference over the 100 steps within 0.2 % (measured: 0.24 % at the worst step, 0.02 % mean)."""
+    from oracle import cfgfile
+    batch, steps = 128, 100
+    fast = ob.Oracle("fast")
+    net, onet, opts, specs = build_pair(aet, ctx, fast, "cifar_small.cfg", batch, threads=os.cpu_count() or 1)
+    net.use_graph(True)
+    gl, ol = [], []
+    for step in range(steps):
+        x, truth = batch_for(opts, 10, batch, 20241, step)
+        gl.append(net.train(x, truth))
+        ol.append(onet.train_step(x, truth, opts["learning_rate"], opts["momentum"], opts["decay"]))
+        if step == 0:
+            for i, s in enumerate(specs):
+                if s["type"] != cfgfile.CONV:
+                    continue
+                for pname in ("P_WEIGHTS", "P_SCALES", "P_ROLLING_MEAN", "P_ROLLING_VARIANCE"):
+                    ref = onet.param(i, getattr(ob, pname))
+                    if ref is None or not np.any(ref):
+                        continue
+                    err = rel_l2(net.layer(i).read(getattr(aet, pname)), ref)
+                    assert err < 1e-2, (i, pname, err)
+    ctx.check()
+    gl, ol = np.array(gl), np.array(ol)
+    rel = np.abs(gl - ol) / np.abs(ol)
+    print("100-step loss curve: first %.4f/%.4f last %.4f/%.4f, max rel diff %.3e at step %d, mean rel diff %.3e"
+          % (gl[0], ol[0], gl[-1], ol[-1], rel.max(), int(rel.argmax()), rel.mean()))
+    assert np.isfinite(gl).all()
+    assert rel[0] < 1e-3
+    assert rel.max() < 0.02 and rel.mean() < 0.002
     net.close()
 
 
@@ -149,17 +204,18 @@ def test_graph_replay_is_bitwise_identical_to_eager(aet, ctx, oracle):
     assert hashes[0] == hashes[1]
 
 
-def _run_variant(aet, ctx, oracle, env):
-    """One forward + backward + two more training steps of the small CNN (batch 8) with `env` set while the network is built."""
-    import os as _os
+def _run_variant(aet, ctx, oracle, options):
+    """One forward + backward + two more training steps of the small CNN (batch 8) with the context `options`
+    (name -> value) in force while the network is built."""
     batch, steps = 8, 3
-    for k, v in env.items():
-        _os.environ[k] = v
+    saved = {k: ctx.get_option(k) for k in options}
+    for k, v in options.items():
+        ctx.set_option(k, v)
     try:
         net, _, opts, specs = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
     finally:
-        for k in env:
-            _os.environ.pop(k, None)
+        for k, v in saved.items():
+            ctx.set_option(k, v)
     x, truth = batch_for(opts, 10, batch, 3, 0)
     net.input.write(x); net.truth.write(truth)
     net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
@@ -180,11 +236,11 @@ def _run_variant(aet, ctx, oracle, env):
 
 def test_fused_bn_pool_path_matches_layer_by_layer(aet, ctx, oracle):
     """Inside a network a BN convolution produces the following max-pool's output itself and folds the
-    pool's backward into its BN backward kernels; AET_NO_FUSE=1 runs every layer's own kernels instead.
+    pool's backward into its BN backward kernels; the context option "fuse" = 0 runs every layer's own kernels instead.
     Forward results are bit-identical; gradients differ only by summation order.  (The linear classifier
     head is switched off in both runs: it changes the arithmetic, see the next test.)"""
-    f = _run_variant(aet, ctx, oracle, {"AET_NO_LINEAR_HEAD": "1"})
-    u = _run_variant(aet, ctx, oracle, {"AET_NO_FUSE": "1"})
+    f = _run_variant(aet, ctx, oracle, {"linear_head": 0})
+    u = _run_variant(aet, ctx, oracle, {"fuse": 0})
     for a, b in zip(f["outs"], u["outs"]):
         assert np.array_equal(a, b)
     for a, b in zip(f["idx"], u["idx"]):
@@ -202,7 +258,7 @@ def test_linear_head_matches_the_separate_layers(aet, ctx, oracle):
     up to the classifier's input is bit-identical, the head's results agree within the TF32 tolerance, and
     the convolution's own output and delta are still there when a host tap reads them."""
     f = _run_variant(aet, ctx, oracle, {})
-    u = _run_variant(aet, ctx, oracle, {"AET_NO_LINEAR_HEAD": "1"})
+    u = _run_variant(aet, ctx, oracle, {"linear_head": 0})
     for i, (a, b) in enumerate(zip(f["outs"], u["outs"])):
         if i <= 6:
             assert np.array_equal(a, b), i          # layer 6 = the convolution's lazily formed output
@@ -266,7 +322,7 @@ def test_bad_cfg_is_rejected(aet, ctx):
 def test_alexnet_style_reduced_step(aet, ctx, oracle):
     """The AlexNet-style network (11x11/4, 5x5, FC as convolution, dropout) at batch 4, one step,
     the dropout masks shared with the oracle."""
-    import aet_cnn_b200.cfgfile as cfgfile
+    from oracle import cfgfile
     batch = 4
     net, onet, opts, specs = build_pair(aet, ctx, oracle, "alexnet_style.cfg", batch)
     x, truth = batch_for(opts, 1000, batch, 11, 0)

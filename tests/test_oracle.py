@@ -238,3 +238,24 @@ def test_network_train_step_lowers_loss_and_threads_agree(oracle, aet):
         losses[threads] = [net.train_step(x, truth, 0.05, 0.9, 5e-4) for _ in range(8)]
     assert losses[1][-1] < losses[1][0]
     assert np.allclose(losses[1], losses[3], rtol=1e-4)
+
+
+def test_learning_rate_schedule_known_values(oracle):
+    """NNetwork.getCurrentRate (dnn/NNetwork.c:215-246) on hand-computed points."""
+    lr = 0.1
+    assert oracle.current_rate(7, 0, lr) == pytest.approx(0.1)
+    assert oracle.current_rate(2, 0, lr, burn_in=4, power=2.0) == pytest.approx(0.1 * (2 / 4) ** 2)
+    assert oracle.current_rate(7, 1, lr, step=3, scale=0.5) == pytest.approx(0.1 * 0.5 ** 2)          # 7 / 3 = 2
+    assert oracle.current_rate(5, 2, lr, steps=(2, 5, 7), scales=(0.5, 0.1, 2.0)) == pytest.approx(0.1 * 0.5 * 0.1)
+    assert oracle.current_rate(1, 2, lr, steps=(2, 5, 7), scales=(0.5, 0.1, 2.0)) == pytest.approx(0.1)
+    assert oracle.current_rate(3, 3, lr, gamma=0.9) == pytest.approx(0.1 * 0.9 ** 3)
+    assert oracle.current_rate(5, 4, lr, max_batches=20, power=3.0) == pytest.approx(0.1 * (1 - 5 / 20) ** 3)
+    assert oracle.current_rate(6, 5, lr, gamma=0.7, step=4) == pytest.approx(0.1 / (1 + np.exp(0.7 * 2)))
+    # batch_num - step is unsigned in the reference: below `step` it wraps, exp overflows and the rate is 0
+    assert oracle.current_rate(2, 5, lr, gamma=0.7, step=4) == 0.0
+
+
+def test_non_finite_scrub_known_values(oracle):
+    v = np.array([1.0, np.nan, -np.inf, 2.0], np.float32)
+    assert np.array_equal(oracle.reset_nan_and_inf(v), np.array([1.0, 0.0, 0.0, 2.0], np.float32))
+    assert np.array_equal(oracle.fix_nan_and_inf(v), np.array([1.0, 0.5, 1.0 / 3.0, 2.0], np.float32))

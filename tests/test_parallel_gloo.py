@@ -36,26 +36,14 @@ def _make_net(ob, oracle, synth, batch):
 GRADS = [(0, "P_WEIGHT_UPDATES"), (0, "P_BIAS_UPDATES"), (0, "P_SCALE_UPDATES"), (2, "P_WEIGHT_UPDATES"), (2, "P_BIAS_UPDATES")]
 
 
-def _dp_step(ob, nets, batches, world, reduce_fn, lr=0.05, mom=0.9, decay=5e-4):
-    """One data-parallel step over `nets` (one per emulated rank held by this process)."""
-    carries = []
-    for net, (x, t) in zip(nets, batches):
-        carry = {k: net.param(k[0], getattr(ob, k[1])).copy() for k in GRADS}
-        for k in GRADS:
-            net.param(k[0], getattr(ob, k[1]))[:] = 0          # this step's gradient only
-        net.forward(x, t)
-        net.backward(x)
-        carries.append(carry)
-    for k in GRADS:
-        reduce_fn([net.param(k[0], getattr(ob, k[1])) for net in nets])
-    for net, carry in zip(nets, carries):
-        for k in GRADS:
-            net.param(k[0], getattr(ob, k[1]))[:] += carry[k]  # momentum history is per rank and identical
-        net.update(nets[0].batch * world, lr, mom, decay)
+def _dp_step(ob, nets, batches, world, reduce_fn):
+    from dp_oracle import dp_step
+    dp_step(ob, nets, batches, world, reduce_fn, GRADS)
 
 
 def _worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     import torch.distributed as dist
     dist.init_process_group("gloo", rank=rank, world_size=world)
