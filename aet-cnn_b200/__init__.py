@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libaet_b200.so")
 CFG_DIR = os.path.join(HERE, "cfg")
 
-LINEAR, RELU, LEAKY = 0, 1, 2
+LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU = range(14)
 CONVOLUTIONAL, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
 PARITY_CPU, PARITY_MTCS = 0, 1
 MATH_TF32, MATH_3XTF32 = 0, 1
@@ -37,7 +37,7 @@ aet_layer_save_weights aet_network_create aet_network_create_from_string aet_net
 aet_network_destroy aet_network_layer_count aet_network_layer aet_network_batch aet_network_input_shape
 aet_network_outputs aet_network_input aet_network_truth aet_network_learning_rate aet_network_set_hyper
 aet_network_seen aet_network_forward aet_network_backward aet_network_update aet_network_cost
-aet_network_train_step aet_network_train_step_async aet_network_train_step_device aet_network_last_loss aet_network_predict
+aet_network_augment_input aet_network_fuse_conv_batchnorm aet_network_predict_topk aet_network_validate aet_network_train_step aet_network_train_step_async aet_network_train_step_device aet_network_last_loss aet_network_predict
 aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
 aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static
@@ -52,6 +52,12 @@ class State(C.Structure):
     """dnn/NLayer.h:21-29 NetworkState."""
     _fields_ = [("truth", C.c_void_p), ("input", C.c_void_p), ("delta", C.c_void_p), ("workspace", C.c_void_p),
                 ("train", C.c_int), ("index", C.c_int)]
+
+
+class Augment(C.Structure):
+    """aet_augment: the per-image draws of the reference's augmentation chain."""
+    _fields_ = [("rad", C.c_float), ("scale", C.c_float), ("dx", C.c_float), ("dy", C.c_float), ("aspect", C.c_float),
+                ("flip", C.c_int), ("dhue", C.c_float), ("dsat", C.c_float), ("dexp", C.c_float)]
 
 
 class KernelTime(C.Structure):
@@ -115,7 +121,10 @@ def lib():
         "aet_network_train_step_device": (i, [vp, C.POINTER(f)]),
         "aet_network_train_step_async": (i, [vp, vp, vp, C.POINTER(f)]),
         "aet_network_last_loss": (i, [vp, C.POINTER(f)]),
-        "aet_network_predict": (i, [vp, vp, vp]), "aet_network_use_graph": (i, [vp, i]),
+        "aet_network_predict": (i, [vp, vp, vp]),
+        "aet_network_augment_input": (i, [vp, vp, i, i, vp]),
+        "aet_network_fuse_conv_batchnorm": (i, [vp]), "aet_network_predict_topk": (i, [vp, vp, i, vp]),
+        "aet_network_validate": (i, [vp, vp, vp, i, i, C.POINTER(f), C.POINTER(f)]), "aet_network_use_graph": (i, [vp, i]),
         "aet_network_load_weights": (i, [vp, C.c_char_p]), "aet_network_save_weights": (i, [vp, C.c_char_p]),
         "aet_network_param_hash": (i, [vp, C.POINTER(C.c_uint64)]),
         "aet_network_profile": (i, [vp, i]),
@@ -436,6 +445,35 @@ class NNetwork:
         out = np.empty((self.batch, self.outputs), np.float32)
         _check(self.L.aet_network_predict(self.h, x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p)))
         return out
+
+    def augment_input(self, src, params):
+        """Device-side rotate/crop + flip + HSV distortion of `src` [batch][c][sh][sw] into the network's input tensor;
+        `params` is a list of dicts with the aet_augment fields (one per image)."""
+        src = _f32(src)
+        arr = (Augment * len(params))()
+        for a, p in zip(arr, params):
+            for k, v in p.items():
+                setattr(a, k, v)
+        _check(self.L.aet_network_augment_input(self.h, src.ctypes.data_as(C.c_void_p), src.shape[2], src.shape[3], arr))
+
+    def fuse_conv_batchnorm(self):
+        """NNetwork.fuseConvBatchnorm: fold BN into the convolutions (inference only afterwards)."""
+        _check(self.L.aet_network_fuse_conv_batchnorm(self.h))
+
+    def predict_topk(self, x, k):
+        x = _f32(x)
+        out = np.empty((self.batch, min(k, self.outputs)), np.int32)
+        _check(self.L.aet_network_predict_topk(self.h, x.ctypes.data_as(C.c_void_p), k, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def validate(self, images, class_ids, k):
+        """Top-1 and top-k accuracy over `images` [count][c][h][w] (Classifier.validateSingle's loop)."""
+        images = _f32(images)
+        ids = np.ascontiguousarray(class_ids, np.int32)
+        t1, tk = C.c_float(), C.c_float()
+        _check(self.L.aet_network_validate(self.h, images.ctypes.data_as(C.c_void_p), ids.ctypes.data_as(C.c_void_p),
+                                           len(ids), k, C.byref(t1), C.byref(tk)))
+        return t1.value, tk.value
 
     def use_graph(self, enable=True):
         _check(self.L.aet_network_use_graph(self.h, int(enable)))

@@ -12,9 +12,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libaet_b200.so")
 SOURCES = ["tensor.cu", "elementwise.cu", "conv.cu", "layers.cu", "network.cu"]
-HEADERS = ["common.h", "umma.cuh", "conv_tma.cuh", "conv_tma_rows.cuh", "conv_thin.cuh", os.path.join("..", "..", "include", "aet_b200.h")]
+HEADERS = ["common.h", "umma.cuh", "activation.cuh", "conv_tma.cuh", "conv_tma_rows.cuh", "conv_thin.cuh", os.path.join("..", "..", "include", "aet_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
-              "--use_fast_math=false" if False else "-Xptxas", "-v"]
+              "-Xptxas", "-v"]
 
 
 def _stale(target, deps):

@@ -70,7 +70,8 @@ enum AetOption {
     OPT_LINEAR_HEAD,       // classifier head on the pooled vectors, read when a network is built          AET_NO_LINEAR_HEAD
     OPT_XCHG_CAP_FLOATS,   // capacity of the peer-exchange buffer (0 = default)   AET_XCHG_CAP_FLOATS
     OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice)   AET_NCCL_MAX_CTAS
-    OPT_PERSISTENT,        // persistent row-sharing kernels (tile scheduler, overlapped epilogue)   AET_NO_PERSISTENT
+    OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
+    OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels   AET_NO_PAIR
     OPT_COUNT
 };
 
@@ -146,7 +147,11 @@ struct aet_layer {
     int batch = 0, c = 0, h = 0, w = 0, cp = 0;         // input
     int oc = 0, oh = 0, ow = 0, ocp = 0;                // output
     int size = 1, stride_x = 1, stride_y = 1, pad = 0;  // conv / pool (pool: pad = padding)
+    int dilation = 1;                                   // conv: tap spacing (`groups`, below, is a convolution's channel groups too:
+                                                        // dnn/ConvolutionalLayer.c:716-722)
+    int cg = 0, cgp = 0;                                // conv: input channels of one group and their padded count
     int bn = 0, train = 1;
+    int flipped = 0;      // the weights record of a .weights file is stored transposed (dnn/ConvolutionalLayer.c:483-485)
     aet_activation act = AET_LINEAR;
     float lr_scale = 1.0f;
     aet_tensor *output = nullptr, *delta = nullptr, *x = nullptr;  // x: conv result before BN
@@ -211,6 +216,7 @@ struct aet_network {
     std::vector<int> steps;
     std::vector<float> scales;
     int64_t seen = 0, cur_iteration = 0;
+    bool bn_fused = false;   // fuseConvBatchnorm ran: inference only from here on
     float loss_scale = 1.0f;
     int try_fix_nan = 0;
     aet_tensor *input = nullptr, *truth = nullptr;
@@ -304,11 +310,11 @@ inline void launch_k(cudaStream_t stream, dim3 grid, dim3 block, size_t smem, vo
     cfg.numAttrs = (pdl_enabled() && !pdl_take_skip()) ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in aet_check_launch
 }
-// The same with a thread-block cluster of `cluster_z` CTAs along grid z (distributed shared memory
-// between the CTAs that split one tile's K range).
+// The same with a thread-block cluster of `cluster_x` x 1 x `cluster_z` CTAs: along z the CTAs that split one
+// tile's K range (distributed shared memory), along x the CTA pair that shares its B tiles (cta_group::2 MMAs).
 template <typename... KArgs, typename... Args>
-inline void launch_k_cluster(cudaStream_t stream, dim3 grid, dim3 block, size_t smem, int cluster_z, void (*kernel)(KArgs...),
-                             Args &&...args) {
+inline void launch_k_cluster(cudaStream_t stream, dim3 grid, dim3 block, size_t smem, int cluster_x, int cluster_z,
+                             void (*kernel)(KArgs...), Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -316,7 +322,7 @@ inline void launch_k_cluster(cudaStream_t stream, dim3 grid, dim3 block, size_t 
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.x = (unsigned)cluster_x;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = (unsigned)cluster_z;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -355,9 +361,12 @@ int vector_download(aet_context *ctx, const float *dev, float *host, size_t coun
 
 // ---- kernels (launchers return AET_OK or an error) ----------------------------------------------
 struct ConvGeom {
-    int N, C, H, W, cp;      // input activation
-    int K, OH, OW, kp;       // output activation
+    int N, C, H, W, cp;      // input activation (C, cp: the channels one GEMM sees -- one group's)
+    int K, OH, OW, kp;       // output activation (K, kp: one group's filters)
     int R, S, sy, sx, pad;
+    int xs, ys;              // floats between consecutive pixels of the input / output tensors (the whole layer's padded
+                             // channel counts; equal to cp / kp unless the layer has channel groups)
+    int dil;                 // spacing of the filter taps; the padding in pixels is pad * dil (dnn/Im2Col.c:65-103)
 };
 // Batch-norm statistics gathered by the forward epilogue: in `shift` (per-channel, near the data);
 // out `partial` (scratch arena, rows x [2][ocp]: sum and sum of squares of y - shift) and `rows`
@@ -401,6 +410,9 @@ int conv_wait_probe(aet_context *ctx);                   // conv.cu: a wait nobo
 int k_tail_publish(aet_network *net);
 constexpr size_t kXchgFlagBytes = 1024;   // 2 x 16 u64 flags, padded
 int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev);
+int k_augment(aet_context *ctx, const float *src_nchw, int n, int c, int sh, int sw, float *dst_nhwc, int size, int cp,
+              const aet_augment *params_dev);
+int k_top_k(aet_context *ctx, const float *scores, int samples, int n, int ld, int k, int *index_dev);
 
 // parameter pointers
 static inline float *layer_W(aet_layer *l) { return l->arena->W + l->seg_w.offset; }

@@ -22,6 +22,7 @@
 // warp 4 allocates TMEM and its lane 0 issues every MMA.
 #include "common.h"
 #include "umma.cuh"
+#include "activation.cuh"
 #include <cooperative_groups.h>
 #include <deque>
 
@@ -64,11 +65,7 @@ struct SharedCtl {
     int4 jtab[64];  // wgrad: per 4-column chunk of the N tile -> {r, s, c, valid}
 };
 
-__device__ __forceinline__ float apply_act(float v, int act) {
-    if (act == AET_LEAKY) return v > 0.f ? v : 0.1f * v;
-    if (act == AET_RELU) return v > 0.f ? v : 0.f;
-    return v;
-}
+__device__ __forceinline__ float apply_act(float v, int act) { return act_forward(v, act); }
 
 __device__ __forceinline__ float4 ldg4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
 
@@ -135,7 +132,9 @@ __device__ __forceinline__ void stage_accumulator(float *tile, uint32_t tmem_acc
 template <bool FPROP>
 __device__ __forceinline__ void flush_tile(const float *tile, const float *remote, int warp, int lane, int bn,
                                            float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
-                                           const float *bias, int act, int map_bi, int map_w, int map_pix, StatAcc *st) {
+                                           const float *bias, int act, int map_bi, int map_w, int map_pix, StatAcc *st,
+                                           int row_lo = 0, int row_hi = 32) {
+    // [row_lo, row_hi): the part of this warp's 32 rows to store (multiples of 16; the whole block by default)
     const int pitch = bn + 4;
     // tiles that span several small images order their rows (h, image, w): each lane maps one row to
     // its pixel index once (the divisions cost more than the stores) and the others fetch it by shuffle
@@ -156,14 +155,14 @@ __device__ __forceinline__ void flush_tile(const float *tile, const float *remot
         float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
         if (stats && active) sh = ldg4(st->shift + col);
         float4 t1 = make_float4(0.f, 0.f, 0.f, 0.f), t2 = t1;
-        for (int r0 = 0; r0 < 32; r0 += 4 * rpi) {
+        for (int r0 = row_lo; r0 < row_hi; r0 += 4 * rpi) {
             float4 o[4];
             int grow[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int r = (r0 + u * rpi + sub) & 31;
                 grow[u] = __shfl_sync(0xffffffffu, my_grow, r);
-                if (r0 + u * rpi + sub >= 32) grow[u] = rows_valid;   // past the warp's rows (lpr not a divisor of 32)
+                if (r0 + u * rpi + sub >= row_hi) grow[u] = rows_valid;   // past the rows to store (lpr not a divisor of 32)
                 const size_t off = (size_t)(warp * 32 + r) * pitch + c * (active ? 1 : 0);
                 o[u] = *reinterpret_cast<const float4 *>(tile + off);
                 if (remote) {
@@ -329,15 +328,15 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
                         int rem = m - n * g.OH * g.OW;
                         int oh = rem / g.OW, ow = rem - oh * g.OW;
                         rinfo_base[i] = n * g.H * g.W;
-                        rinfo_y[i] = oh * g.sy - g.pad;
-                        rinfo_x[i] = ow * g.sx - g.pad;
+                        rinfo_y[i] = oh * g.sy - g.pad * g.dil;
+                        rinfo_x[i] = ow * g.sx - g.pad * g.dil;
                     } else {
                         int n = m / (g.H * g.W);
                         int rem = m - n * g.H * g.W;
                         int h = rem / g.W, w = rem - h * g.W;
                         rinfo_base[i] = n * g.OH * g.OW;
-                        rinfo_y[i] = h + g.pad;
-                        rinfo_x[i] = w + g.pad;
+                        rinfo_y[i] = h + g.pad * g.dil;
+                        rinfo_x[i] = w + g.pad * g.dil;
                     }
                 } else {
                     rinfo_base[i] = 0;
@@ -381,15 +380,15 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
                         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (kvalid) {
                             if (KIND == KIND_FPROP) {
-                                int ih = rinfo_y[i] + r, iw = rinfo_x[i] + sx_;
+                                int ih = rinfo_y[i] + r * g.dil, iw = rinfo_x[i] + sx_ * g.dil;
                                 if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
-                                    v = ldg4(a.src_a + ((size_t)(rinfo_base[i] + ih * g.W + iw) * g.cp + ch));
+                                    v = ldg4(a.src_a + ((size_t)(rinfo_base[i] + ih * g.W + iw) * g.xs + ch));
                             } else {
-                                int th = rinfo_y[i] - r, tw = rinfo_x[i] - sx_;
+                                int th = rinfo_y[i] - r * g.dil, tw = rinfo_x[i] - sx_ * g.dil;
                                 if (th >= 0 && tw >= 0) {
                                     int oh = th / g.sy, ow = tw / g.sx;
                                     if (oh * g.sy == th && ow * g.sx == tw && oh < g.OH && ow < g.OW)
-                                        v = ldg4(a.src_a + ((size_t)(rinfo_base[i] + oh * g.OW + ow) * g.kp + ch));
+                                        v = ldg4(a.src_a + ((size_t)(rinfo_base[i] + oh * g.OW + ow) * g.ys + ch));
                                 }
                             }
                         }
@@ -408,7 +407,7 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
                     const int mc = i * 4 + mn_c;
                     const int ko = m0 + mc * 4;
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (pvalid && ko < g.kp) v = ldg4(a.src_a + ((size_t)p * g.kp + ko));
+                    if (pvalid && ko < g.kp) v = ldg4(a.src_a + ((size_t)p * g.ys + ko));
                     va[i] = v;
                     oa[i] = mn_cell_offset(mc, kq);
                 }
@@ -465,8 +464,8 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
                     int rem = p - n * g.OH * g.OW;
                     int oh = rem / g.OW, ow = rem - oh * g.OW;
                     nb = n * g.H * g.W;
-                    ih0 = oh * g.sy - g.pad;
-                    iw0 = ow * g.sx - g.pad;
+                    ih0 = oh * g.sy - g.pad * g.dil;
+                    iw0 = ow * g.sx - g.pad * g.dil;
                 }
 #pragma unroll
                 for (int i = 0; i < NB; ++i) {
@@ -475,9 +474,9 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
                     const int4 e = ctl.jtab[mc];
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (pvalid && e.w) {
-                        int ih = ih0 + e.x, iw = iw0 + e.y;
+                        int ih = ih0 + e.x * g.dil, iw = iw0 + e.y * g.dil;
                         if ((unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W)
-                            v = ldg4(a.src_b + ((size_t)(nb + ih * g.W + iw) * g.cp + e.z));
+                            v = ldg4(a.src_b + ((size_t)(nb + ih * g.W + iw) * g.xs + e.z));
                     }
                     vb[i] = v;
                     ob[i] = mn_cell_offset(mc, kq);
@@ -556,36 +555,58 @@ __global__ void __launch_bounds__(NTHREADS, NB <= 4 ? 3 : 1) conv_gather_kernel(
     }
 }
 
-// Fixed-order second stage of the split-K weight gradient: dw (+)= sum over splits.  A block owns
-// 32 float4 outputs; its 16 split lanes each add every 16th partial, then lane 0 adds the 16
-// lane sums in order, so the result does not depend on scheduling.
-constexpr int RED_ELEMS = 32, RED_LANES = 16;
-__global__ void __launch_bounds__(RED_ELEMS * RED_LANES)
+// Fixed-order second stage of the split-K weight gradient: dw (+)= sum over splits.  `lanes` (a power of two, at
+// most 32) threads of a warp share one float4 of the output: lane p sums splits p, p + lanes, ... with eight loads in
+// flight, then the lanes are folded by a fixed xor tree, so the result does not depend on scheduling.  Large outputs
+// run with lanes = 1, small ones with many splits (a first layer's 9 x 4 taps) with up to 32.  The partials were
+// written by the kernel just before and sit in L2.
+constexpr int RED_THREADS = 256;
+__global__ void __launch_bounds__(RED_THREADS)
 wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dw, size_t count4, int splits,
-                    size_t split_stride, int accumulate) {
+                    size_t split_stride, int accumulate, int lanes) {
     pdl_enter();
-    __shared__ float4 sh[RED_LANES][RED_ELEMS];
-    const int e = threadIdx.x % RED_ELEMS, sl = threadIdx.x / RED_ELEMS;
-    const size_t i = (size_t)blockIdx.x * RED_ELEMS + e;
+    const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t i = t / (size_t)lanes;
+    const int p0 = (int)(t - i * (size_t)lanes);
+    const bool live = i < count4;
+    const float4 *p = reinterpret_cast<const float4 *>(partial) + (live ? i : 0);
+    const size_t stride4 = split_stride / 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (i < count4)
-        for (int s = sl; s < splits; s += RED_LANES) {
-            float4 v = __ldg(reinterpret_cast<const float4 *>(partial + (size_t)s * split_stride) + i);
+    if (live) {
+        int s = p0;
+        for (; s + 7 * lanes < splits; s += 8 * lanes) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __ldcg(p + (size_t)(s + k * lanes) * stride4);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { acc.x += v[k].x; acc.y += v[k].y; acc.z += v[k].z; acc.w += v[k].w; }
+        }
+        for (; s < splits; s += lanes) {
+            const float4 v = __ldcg(p + (size_t)s * stride4);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-    sh[sl][e] = acc;
-    __syncthreads();
-    if (sl != 0 || i >= count4) return;
-    for (int q = 1; q < RED_LANES; ++q) {
-        float4 v = sh[q][e];
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
-    float4 *o = reinterpret_cast<float4 *>(dw) + i;
+    for (int o = 1; o < lanes; o <<= 1) {   // whole warps reach this: lanes divides 32 and the grid is whole warps
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+    }
+    if (!live || p0 != 0) return;
+    float4 *o4 = reinterpret_cast<float4 *>(dw) + i;
     if (accumulate) {
-        float4 p = *o;
-        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        const float4 q = *o4;
+        acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
     }
-    *o = acc;
+    *o4 = acc;
+}
+int launch_wgrad_reduce(aet_context *ctx, const float *partial, float *dw, size_t out_floats, int splits, int accumulate) {
+    const size_t count4 = out_floats / 4;
+    int lanes = 1;
+    while (lanes < 32 && count4 * (size_t)lanes < 65536 && lanes * 2 <= splits) lanes <<= 1;
+    LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (splits + 1 + (accumulate ? 1 : 0)), 0);
+    const size_t threads = count4 * (size_t)lanes;
+    launch_k(ctx->stream, (unsigned)((threads + RED_THREADS - 1) / RED_THREADS), RED_THREADS, 0, wgrad_reduce_kernel, partial, dw, count4,
+             splits, out_floats, accumulate, lanes);
+    return aet_check_launch("wgrad_reduce");
 }
 
 int pow2_cols(int n) {
@@ -599,12 +620,17 @@ ConvGeom layer_geom(const aet_layer *l) {
     g.N = l->batch; g.C = l->c; g.H = l->h; g.W = l->w; g.cp = l->cp;
     g.K = l->oc; g.OH = l->oh; g.OW = l->ow; g.kp = l->ocp;
     g.R = l->size; g.S = l->size; g.sy = l->stride_y; g.sx = l->stride_x; g.pad = l->pad;
+    g.xs = l->cp; g.ys = l->ocp; g.dil = l->dilation;
+    if (l->groups > 1) {   // one group's GEMM: its own channels and filters, pixels still a whole layer's channel count apart
+        g.C = l->cg; g.cp = l->cgp;
+        g.K = l->oc / l->groups; g.kp = g.K;
+    }
     // A filter that covers the whole unpadded map is a fully connected layer (the reference has no other kind):
     // with NHWC activations and [filter][tap][channel] weights it IS a 1x1 convolution over H*W*cp channels of a
     // 1x1 map, byte for byte.  Seen that way the data gradient is a plain GEMM over the batch instead of a
     // convolution in which 35 of 36 taps of every input pixel fall outside the single output pixel.
-    if (l->size == l->h && l->size == l->w && l->pad == 0 && l->size > 1 && l->ctx->opt[OPT_FC_ALIAS]) {
-        g.C = g.cp = l->h * l->w * l->cp;
+    if (l->size == l->h && l->size == l->w && l->pad == 0 && l->size > 1 && l->groups == 1 && l->ctx->opt[OPT_FC_ALIAS]) {
+        g.C = g.cp = g.xs = l->h * l->w * l->cp;
         g.H = g.W = g.OH = g.OW = 1;
         g.R = g.S = 1;
         g.sy = g.sx = 1;
@@ -660,24 +686,28 @@ int launch_gather(aet_context *ctx, ConvArgs &a, dim3 grid, const char *name, do
 #include "conv_tma_rows.cuh"
 #include "conv_thin.cuh"
 
-int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue, ConvStats *stats) {
+// Channel groups (dnn/ConvolutionalLayer.c:716-722, 913-946): group j convolves input channels [j*C/G, (j+1)*C/G) with
+// filters [j*K/G, (j+1)*K/G).  With channels innermost a group is a column slice of every pixel row, so each group is
+// one implicit GEMM over the same pixels with pointers moved by the slice and the pixel pitch left at the layer's.
+static int conv_fprop_one(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue, ConvStats *stats, int gi) {
     aet_context *ctx = l->ctx;
     ConvArgs a = {};
     a.g = layer_geom(l);
     const ConvGeom &g = a.g;
-    a.src_a = x; a.src_b = layer_W(l); a.out = y; a.bias = bias;
+    a.src_a = x + (size_t)gi * g.C; a.src_b = layer_W(l) + (size_t)gi * g.K * g.R * g.S * g.cp; a.out = y + (size_t)gi * g.K;
+    a.bias = bias ? bias + (size_t)gi * g.K : nullptr;
     a.act = act_in_epilogue ? (int)l->act : (int)AET_LINEAR;
     a.n_rows = g.N * g.OH * g.OW;
     a.n_cols = g.kp;
     a.k_total = g.R * g.S * g.cp;
     a.k_per_split = a.k_total;
-    a.out_ld = g.kp;
+    a.out_ld = g.ys;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     if (stats) {
         stats->rows = 0;
         // the statistics describe the raw convolution result: no bias or activation in this epilogue
         if (!bias && a.act == (int)AET_LINEAR && ctx->math != AET_MATH_3XTF32 && ctx->opt[OPT_EPILOGUE_STATS]) {
-            AET_TRY(ctx_scratch(ctx, (size_t)m_tiles * 2 * g.kp * sizeof(float), &stats->partial));   // one row per CTA along M at most
+            AET_TRY(ctx_scratch(ctx, (size_t)m_tiles * 4 * g.kp * sizeof(float), &stats->partial));   // at most two rows per pixel tile
             a.stat_shift = stats->shift;
             a.stat_partial = stats->partial;
             a.stat_rows_out = &stats->rows;
@@ -696,17 +726,24 @@ int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int ac
     return launch_gather<KIND_FPROP>(ctx, a, grid, "conv_fprop_gather", flops);
 }
 
-int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
+int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue, ConvStats *stats) {
+    if (l->groups == 1) return conv_fprop_one(l, x, y, bias, act_in_epilogue, stats, 0);
+    if (stats) stats->rows = 0;   // grouped layers take their batch statistics from the stand-alone reduction
+    for (int gi = 0; gi < l->groups; ++gi) AET_TRY(conv_fprop_one(l, x, y, bias, act_in_epilogue, nullptr, gi));
+    return AET_OK;
+}
+
+static int conv_dgrad_one(aet_layer *l, const float *dy, float *dx, int gi) {
     aet_context *ctx = l->ctx;
     ConvArgs a = {};
     a.g = layer_geom(l);
     const ConvGeom &g = a.g;
-    a.src_a = dy; a.src_b = layer_W(l); a.out = dx;
+    a.src_a = dy + (size_t)gi * g.K; a.src_b = layer_W(l) + (size_t)gi * g.K * g.R * g.S * g.cp; a.out = dx + (size_t)gi * g.C;
     a.n_rows = g.N * g.H * g.W;
     a.n_cols = g.cp;
     a.k_total = g.R * g.S * g.kp;
     a.k_per_split = a.k_total;
-    a.out_ld = g.cp;
+    a.out_ld = g.xs;
     const int m_tiles = (a.n_rows + BM - 1) / BM;
     a.bn = pick_bn(a.n_cols, m_tiles, ctx->sm_count, ctx->opt[OPT_BN_TILE]);
     const double flops = 2.0 * g.N * g.OH * g.OW * (double)g.K * g.C * g.R * g.S;
@@ -718,12 +755,18 @@ int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
     return launch_gather<KIND_DGRAD>(ctx, a, grid, "conv_dgrad_gather", flops);
 }
 
-int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate) {
+int conv_dgrad(aet_layer *l, const float *dy, float *dx) {
+    for (int gi = 0; gi < l->groups; ++gi) AET_TRY(conv_dgrad_one(l, dy, dx, gi));
+    return AET_OK;
+}
+
+static int conv_wgrad_one(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate, int gi) {
     aet_context *ctx = l->ctx;
     ConvArgs a = {};
     a.g = layer_geom(l);
     const ConvGeom &g = a.g;
-    a.src_a = dy; a.src_b = x;
+    a.src_a = dy + (size_t)gi * g.K; a.src_b = x + (size_t)gi * g.C;
+    dw += (size_t)gi * g.K * g.R * g.S * g.cp;
     a.n_rows = g.K;
     a.n_cols = g.R * g.S * g.cp;
     a.k_total = g.N * g.OH * g.OW;
@@ -737,11 +780,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
         int rr = tma_wgrad_rows(l, a, flops, &rsplits, &rpartial);
         if (rr < 0) return rr;
         if (rr == AET_OK) {
-            const size_t count4 = out_floats / 4;
-            LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (rsplits + 1 + (accumulate ? 1 : 0)), 0);
-            launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel, 
-                rpartial, dw, count4, rsplits, out_floats, accumulate);
-            return aet_check_launch("wgrad_reduce");
+            return launch_wgrad_reduce(ctx, rpartial, dw, out_floats, rsplits, accumulate);
         }
     }
     {
@@ -750,11 +789,7 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
         int tr = thin_wgrad(l, a, flops, &tsplits, &tpartial);
         if (tr < 0) return tr;
         if (tr == AET_OK) {
-            const size_t count4 = out_floats / 4;
-            LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (tsplits + 1 + (accumulate ? 1 : 0)), 0);
-            launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel,
-                     tpartial, dw, count4, tsplits, out_floats, accumulate);
-            return aet_check_launch("wgrad_reduce");
+            return launch_wgrad_reduce(ctx, tpartial, dw, out_floats, tsplits, accumulate);
         }
     }
     // N tile: the multiple of 16 (<= 256) that wastes the fewest padded columns, larger on ties
@@ -787,13 +822,12 @@ int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int acc
         r = launch_gather<KIND_WGRAD>(ctx, a, grid, "conv_wgrad_gather", flops);
     }
     if (r != AET_OK) return r;
-    {
-        const size_t count4 = out_floats / 4;
-        LaunchScope scope(ctx, "wgrad_reduce", (double)out_floats * 4.0 * (splits + 1 + (accumulate ? 1 : 0)), 0);
-        launch_k(ctx->stream, (unsigned)((count4 + RED_ELEMS - 1) / RED_ELEMS), RED_ELEMS * RED_LANES, 0, wgrad_reduce_kernel, partial, dw, count4, splits,
-                                                                                        out_floats, accumulate);
-        return aet_check_launch("wgrad_reduce");
-    }
+    return launch_wgrad_reduce(ctx, partial, dw, out_floats, splits, accumulate);
+}
+
+int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate) {
+    for (int gi = 0; gi < l->groups; ++gi) AET_TRY(conv_wgrad_one(l, x, dy, dw, accumulate, gi));
+    return AET_OK;
 }
 
 void conv_release(aet_layer *l) { tma_release(l); }

@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
 int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || !ctx->opt[OPT_THIN]) return 1;
+    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || !ctx->opt[OPT_THIN] || l->groups > 1 || l->dilation > 1) return 1;
     if (tma_common_ok(l)) return 1;                                         // wide channel counts belong to the TMA kernels
     if (a.k_total > THIN_MAX_CELLS * 4) return 1;
     const int bn = round_up(a.n_cols, 16);
@@ -420,7 +420,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
 int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, float **partial_out) {
     aet_context *ctx = l->ctx;
     const ConvGeom &g = a.g;
-    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || !ctx->opt[OPT_THIN]) return 1;
+    if (ctx->conv_path != 0 || ctx->math == AET_MATH_3XTF32 || !ctx->opt[OPT_THIN] || l->groups > 1 || l->dilation > 1) return 1;
     if (tma_common_ok(l)) return 1;                                         // wide channel counts belong to the TMA kernels
     if (a.n_cols > THIN_MAX_CELLS * 4 || g.K > BM) return 1;
     if (!(g.kp % 32 == 0 || g.kp < 32)) return 1;          // whole 32-filter blocks for the TMA box

@@ -281,7 +281,7 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
 // row (ocp < 32: the copy engine zero-fills the rest of the box) or a whole number of rows.
 bool tma_common_ok(const aet_layer *l) {
     const ConvGeom g = layer_geom(l);   // the geometry the kernels see (a fully connected layer is a 1x1 convolution)
-    return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && g.sx == 1 && g.sy == 1 &&
+    return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && l->groups == 1 && l->dilation == 1 && g.sx == 1 && g.sy == 1 &&
            g.cp % 32 == 0 && (g.kp % 32 == 0 || g.kp < 32);
 }
 

@@ -198,7 +198,7 @@ int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_ou
     AET_TRY(ctx_smem_attr(ctx, conv_wgrad_rows_kernel));
     dim3 grid(m_tiles, g.S * t.col_groups, splits);
     {
-        char variant[24];
+        char variant[40];
         snprintf(variant, sizeof(variant), "n%d_sp%d", bn, splits);
         LaunchScope scope(ctx, "conv_wgrad_tma_rows", 0, flops, variant);
         launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_wgrad_rows_kernel, *ma, *mb, t);
@@ -231,13 +231,18 @@ struct FdRowsArgs {
     int smerge_S;                  // data gradient of a narrow layer: the S column taps ride in one MMA of N = S * channels
                                    // (0 = off); the epilogue adds the S column blocks, each shifted by its tap
     int par_epi;                   // mt == 2 with nine warps: warps 5-8 store the second pixel tile while warps 0-3 store the first
+    int rotate;                    // every CTA starts its K slabs at another offset (spreads the reads of the shared weight tiles)
+    int pair;                      // the two CTAs of a cluster along grid x form a cta_group::2 pair: MMAs of M = 256 issued by the
+                                   // even CTA, each CTA loading its own pixel tiles and half of every weight tile
     int stages, tmem_cols;
     uint32_t a_bytes, b_tile_bytes, tx_bytes;
     int *status;
 };
 
 constexpr int FD_THREADS_WIDE = 288;   // five warps + a second epilogue group
-template <int KIND>
+// PAIR: the cta_group::2 form.  It is a separate instantiation because a kernel that contains cta_group::2
+// instructions can only be launched as a cluster of CTA pairs.
+template <int KIND, bool PAIR>
 __global__ void __launch_bounds__(FD_THREADS_WIDE, 1)
 conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const FdRowsArgs a) {
@@ -259,6 +264,12 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int nslabs = slab_end - slab_begin;
     const uint32_t stage_bytes = a.a_bytes + (uint32_t)a.R * a.b_tile_bytes;
     bool epilogue_ready = false;
+    // Cluster shapes: (1,1,2) K split only, (2,1,1) a CTA pair, (2,1,2) two pairs that split K.  Ranks run x first,
+    // so a pair is ranks {0,1} or {2,3} and the K-split partner of rank r is r ^ 2 (r ^ 1 without pairs).
+    const uint32_t crank = (PAIR || a.ksplit > 1) ? cluster_ctarank() : 0u;
+    const uint32_t prank = PAIR ? (crank & 1u) : 0u;        // rank inside the CTA pair; 0 = the CTA that issues the MMAs
+    const uint32_t pair_base = crank & ~1u;                 // cluster rank of this pair's leader
+    const bool leader = prank == 0u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -274,32 +285,57 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         prefetch_tensormap(&map_b);
     }
     if (warp == 4) {
-        tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(smem_u32(&ctl.tmem_base), a.tmem_cols); tmem_relinquish_pair(); }
+        else { tmem_alloc(smem_u32(&ctl.tmem_base), a.tmem_cols); tmem_relinquish(); }
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctl.tmem_base;
+    // A pair's leader writes into its partner's TMEM and arrives on its partner's barriers: both CTAs must have
+    // finished the set-up above before either goes on.
+    if (PAIR) cooperative_groups::this_cluster().sync();
     pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp != 4) {
         const int q = warp & 3, grp = warp < 4 ? 0 : 1;   // TMEM lane quarter; which pixel tile this warp stores
         if (threadIdx.x == 0) {
+            const int rot = (a.rotate && nslabs > 0) ? (int)(((blockIdx.x >> (PAIR ? 1 : 0)) * 5u + blockIdx.y * 3u) % (unsigned)nslabs) : 0;
             for (int it = 0; it < nslabs; ++it) {
                 const int s = it % a.stages;
                 const uint32_t phase = (it / a.stages) & 1;
                 if (!mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag)) break;
-                const uint32_t bar = smem_u32(&ctl.full[s]);
                 const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
                 const uint32_t sb = sa + a.a_bytes;
-                mbar_arrive_expect_tx(bar, a.tx_bytes);
-                const int slab = slab_begin + it;
+                // CTAs walk their K slabs from different starting points: all of them read the same weight tiles, and in
+                // lockstep every SM would ask the same L2 lines at the same moment.  The order depends on the CTA index
+                // only, so results stay reproducible (a pair's two CTAs share their order).
+                int itr = it + rot;
+                if (itr >= nslabs) itr -= nslabs;
+                const int slab = slab_begin + itr;
                 const int st = slab / a.slabs_per_s, cb = slab - st * a.slabs_per_s;   // column tap, channel slab
                 // fprop reads input pixel (h + r - pad, w + s - pad); dgrad reads delta pixel (h + pad - r, w + pad - s)
                 const int wx = a.smerge_S ? 0 : (KIND == KIND_FPROP ? st - a.pad : a.pad - st);
                 const int hy = KIND == KIND_FPROP ? row0 - a.pad : row0 + a.pad - (a.R - 1);
+                if (PAIR) {
+                    // Both CTAs' copies complete on the LEADER's barrier, which expects the bytes of both; this CTA
+                    // brings its own pixel tiles and its half of the N rows of every weight tile.
+                    const uint32_t bar = map_to_cta(smem_u32(&ctl.full[s]), pair_base);
+                    if (leader) mbar_arrive_expect_tx(smem_u32(&ctl.full[s]), 2u * a.tx_bytes);
+                    const int half = (int)prank * (bn / 2);
+                    if (a.bi > 1) tma_load_4d_pair(sa, &map_a, bar, cb * 32, wx, img0, hy);
+                    else          tma_load_4d_pair(sa, &map_a, bar, cb * 32, wx, hy, img0);
+                    for (int r = 0; r < a.R; ++r) {
+                        const int tap = r * a.S + st;
+                        if (KIND == KIND_FPROP) tma_load_2d_pair(sb + r * a.b_tile_bytes, &map_b, bar, tap * a.inner + cb * 32, n0 + half);
+                        else if (a.smerge_S)    tma_load_4d_pair(sb + r * a.b_tile_bytes, &map_b, bar, 0, cb * 32, half / 32, r);
+                        else                    tma_load_4d_pair(sb + r * a.b_tile_bytes, &map_b, bar, 0, cb * 32, (n0 + half) / 32, tap);
+                    }
+                    continue;
+                }
+                const uint32_t bar = smem_u32(&ctl.full[s]);
+                mbar_arrive_expect_tx(bar, a.tx_bytes);
                 if (a.bi > 1) tma_load_4d(sa, &map_a, bar, cb * 32, wx, img0, hy);      // dims (c, w, n, h)
                 else          tma_load_4d(sa, &map_a, bar, cb * 32, wx, hy, img0);      // dims (c, w, h, n)
                 for (int r = 0; r < a.R; ++r) {
@@ -318,8 +354,50 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (ready && a.ksplit > 1) {
             // only stage the accumulator (mt == 1 here); the sum of the two halves is stored after the cluster barrier
             stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, q, lane, bn);
+        } else if (ready && a.smerge_S && 32 % a.w == 0 && bn / a.smerge_S <= 128) {
+            // Column taps merged into N: accumulator column block sx holds the partial result that belongs to the
+            // output pixel (pad - sx) columns further on, i.e. to the TMEM lane (pad - sx) rows away.  A warp's 32
+            // lanes are whole image rows here (the image width divides 32), so every neighbour a lane needs sits
+            // in the same warp, and the lanes at an image row's ends are exactly those whose neighbour falls outside
+            // the image: the column blocks are combined with warp shuffles straight out of the TMEM registers, and
+            // only the finished cpn-wide tile goes through shared memory for the coalesced store.
+            const int cpn = bn / a.smerge_S;                 // output channels
+            const int pitch = cpn + 4;
+            float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))) + (size_t)grp * BM * pitch;
+            float *mine = tile + (size_t)(q * 32 + lane) * pitch;
+            const int wcol = lane % a.w;
+            const uint32_t tbase = tmem + (uint32_t)(grp * bn) + ((uint32_t)(q * 32) << 16);
+            for (int c0 = 0; c0 < cpn; c0 += 16) {
+                float acc[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+                for (int sx0 = 0; sx0 < a.smerge_S; sx0 += 3) {          // three column blocks in flight per wait
+                    uint32_t v[3][16];
+#pragma unroll
+                    for (int k = 0; k < 3; ++k)
+                        if (sx0 + k < a.smerge_S) tmem_ld16_issue(tbase + (uint32_t)((sx0 + k) * cpn + c0), v[k]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int k = 0; k < 3; ++k) {
+                        if (sx0 + k >= a.smerge_S) break;
+                        const int d = a.pad - (sx0 + k);             // this block's values belong d lanes down
+                        const bool ok = (unsigned)(wcol + d) < (unsigned)a.w;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float t = __shfl_sync(0xffffffffu, __uint_as_float(v[k][i]), (lane + d) & 31);
+                            acc[i] += ok ? t : 0.f;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) *reinterpret_cast<float4 *>(mine + c0 + 4 * i) = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+            }
+            __syncwarp();
+            const int mt0 = m0 + grp * BM;
+            flush_tile<false>(tile, nullptr, q, lane, cpn, a.out + (size_t)mt0 * a.out_ld, (size_t)a.out_ld, a.n_rows - mt0, 0, a.n_cols,
+                              nullptr, (int)AET_LINEAR, 1, 1, 0, nullptr);
         } else if (ready && a.smerge_S) {
-            // Column taps merged into N: accumulator column block s holds the partial result that belongs to
+            // General form (image rows wider than a warp): accumulator column block s holds the partial result that belongs to
             // the output pixel pad - s columns further on.  The four warps of a group stage their tile, then every
             // row adds its (up to) S neighbours' blocks; a tile is whole image rows, so the neighbours are rows
             // +-1.. of the same tile.  With two pixel tiles the two warp groups work side by side.
@@ -387,9 +465,9 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
                              &ctl.stat_bar, abort_flag);
         }
-    } else if (lane == 0) {
+    } else if (lane == 0 && leader) {
         const int b_mn = KIND == KIND_FPROP ? 0 : 1;
-        const uint32_t idesc = make_idesc_tf32(BM, bn, 0, b_mn);
+        const uint32_t idesc = make_idesc_tf32(PAIR ? 2 * BM : BM, bn, 0, b_mn);
         const uint64_t da0 = make_desc(smem_base, 0, 1024, LAYOUT_SW128);
         const uint64_t db0 = b_mn ? make_desc(smem_base + a.a_bytes, 4096, 512, LAYOUT_SW128_32B)
                                   : make_desc(smem_base + a.a_bytes, 0, 1024, LAYOUT_SW128);
@@ -410,15 +488,23 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int t = 0; t < a.mt; ++t) {
                     const uint64_t da_rt = da0 + st16 + (uint64_t)(t * tile_rows16 + rr * img_row16);
                     const uint32_t d_t = tmem + (uint32_t)(t * bn);
+                    if (PAIR) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        mma_tf32(d_t, da_rt + (uint64_t)(j * 2), db_r + j * b_step, idesc, (accumulate | (uint32_t)(r > 0 || j > 0)));
+                        for (int j = 0; j < 4; ++j)
+                            mma_tf32_pair(d_t, da_rt + (uint64_t)(j * 2), db_r + j * b_step, idesc, (accumulate | (uint32_t)(r > 0 || j > 0)));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            mma_tf32(d_t, da_rt + (uint64_t)(j * 2), db_r + j * b_step, idesc, (accumulate | (uint32_t)(r > 0 || j > 0)));
+                    }
                 }
             }
             accumulate = 1;
-            mma_commit(smem_u32(&ctl.empty[s]));
+            if (PAIR) mma_commit_pair(smem_u32(&ctl.empty[s]), (uint16_t)(3u << pair_base));   // frees the stage in both CTAs
+            else mma_commit(smem_u32(&ctl.empty[s]));
         }
-        mma_commit(smem_u32(&ctl.accum));
+        if (PAIR) mma_commit_pair(smem_u32(&ctl.accum), (uint16_t)(3u << pair_base));
+        else mma_commit(smem_u32(&ctl.accum));
     }
 
     __syncwarp();   // the MMA warp's lanes rejoin their issuing lane before any warp-wide barrier
@@ -428,23 +514,32 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         namespace cg = cooperative_groups;
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();                                   // both staging tiles are complete
-        if (warp < 4 && krank == 0 && epilogue_ready) {
+        if (warp < 4 && epilogue_ready) {
+            // Each CTA stores half of the tile's rows (its 16-row half of every warp's 32-row block) as the sum of its
+            // own and its partner's staged accumulator, read through distributed shared memory: a + b on one side,
+            // b + a on the other, the same bits.
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
-            const float *remote = cluster.map_shared_rank(tile, 1);
+            const float *remote = cluster.map_shared_rank(tile, PAIR ? (crank ^ 2u) : (crank ^ 1u));
             StatAcc st;
             stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
             flush_tile<KIND == KIND_FPROP>(tile, remote, warp, lane, bn, a.out + (size_t)m0 * a.out_ld, (size_t)a.out_ld, a.n_rows - m0,
-                                           n0, a.n_cols, a.bias, a.act, a.bi, a.w, a.pix_per_img, &st);
-            if (KIND == KIND_FPROP && st.shift)
-                stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
-                             &ctl.stat_bar, abort_flag);
+                                           n0, a.n_cols, a.bias, a.act, a.bi, a.w, a.pix_per_img, &st, krank * 16, krank * 16 + 16);
+            cluster.sync();                               // the partner has read this CTA's staged tile: it may be reused
+            if (KIND == KIND_FPROP && st.shift)           // one partial row per CTA of the pair
+                stats_commit(tile, st, warp, lane, bn, a.stat_partial + ((size_t)blockIdx.x * 2 + krank) * 2 * a.out_ld + n0, a.out_ld,
+                             a.n_cols - n0, &ctl.stat_bar, abort_flag);
+        } else {
+            cluster.sync();                               // (the warps that store nothing keep the barrier count whole)
         }
-        cluster.sync();                                   // rank 1's shared memory stays alive until rank 0 has read it
     }
     tc_fence_before_sync();
     __syncthreads();
+    // the pair's TMEM is released together, once both CTAs have read their accumulators (every thread of both
+    // CTAs gets here whatever happened above)
+    if (PAIR) cooperative_groups::this_cluster().sync();
     if (warp == 4) {
-        tmem_dealloc(tmem, a.tmem_cols);
+        if (PAIR) tmem_dealloc_pair(tmem, a.tmem_cols);
+        else tmem_dealloc(tmem, a.tmem_cols);
         if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
 }
@@ -481,7 +576,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         for (; m >= 1 && !smerge; --m) {
             const uint32_t ab = (uint32_t)(m * (int)bh + g.R - 1) * bi * g.W * 128u;
             const size_t st = (size_t)ab + (size_t)g.R * c * 128u;
-            int ns = (int)((220 * 1024) / st);
+            int ns = (int)((218 * 1024) / st);
             if (ns > 4) ns = 4;
             if (ns >= 2 && st * ns >= (size_t)m * BM * (c + 4) * 4 && (m_tiles + m - 1) / m <= ctx->sm_count) {   // one staging tile per pixel tile
                 bn = c; mt = m; stages = ns; n_tiles = 1; a_bytes = ab; b_tile = (uint32_t)c * 128u; stage = st; smerge = g.S;
@@ -504,7 +599,7 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         for (; m >= 1; --m) {
             const uint32_t ab = (uint32_t)(m * (int)bh + g.R - 1) * bi * g.W * 128u;
             const size_t st = (size_t)ab + (size_t)g.R * c * 128u;
-            int ns = (int)((220 * 1024) / st);
+            int ns = (int)((218 * 1024) / st);
             if (ns > 4) ns = 4;
             if (ns >= 2 && st * ns >= (size_t)BM * (c + 4) * 4) {   // pipeline depth and room for the epilogue tile
                 bn = c; mt = m; stages = ns; n_tiles = nt; a_bytes = ab; b_tile = (uint32_t)c * 128u; stage = st;
@@ -514,6 +609,23 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         }
     }
     if (!bn) return 1;
+    // CTA pairs (cta_group::2): the two CTAs of a cluster along grid x run MMAs of M = 256 together and each loads only half
+    // of every weight tile, so the weights cross L2 -> SM once per pair.  Measured, the main loops of these kernels run at
+    // the L2 -> SM bandwidth (about 70 GB/s per SM with every SM pulling), not at the tensor pipe's rate, so fewer bytes per
+    // FLOP is what shortens them.  Needs an even number of CTAs along x and half tiles that are whole swizzle blocks.
+    int pair = 0;
+    {
+        const int gx = (m_tiles + mt - 1) / mt;
+        const bool halves_ok = KIND == KIND_FPROP ? bn % 16 == 0 : bn % 64 == 0;
+        if (ctx->opt[OPT_PAIR] && gx % 2 == 0 && halves_ok && m_tiles % mt == 0) {
+            const uint32_t bt = (uint32_t)(bn / 2) * 128u;
+            const size_t st = (size_t)a_bytes + (size_t)g.R * bt;
+            int ns = (int)((218 * 1024) / st);   // + 1 KB of alignment slack stays inside the 220 KB the kernel may use
+            if (ns > MAX_STAGES) ns = MAX_STAGES;
+            const size_t need = (size_t)(mt == 2 ? 2 : 1) * BM * (bn + 4) * 4;   // staging tile(s) of the epilogue
+            if (ns >= 2 && st * ns >= need) { pair = 1; b_tile = bt; stage = st; stages = ns; }
+        }
+    }
     // The large stages allow one CTA per SM.  Measured on 8x8 to 16x16 images at batch 128 and 256: while the
     // grid fits one wave this kernel matches or beats the plain TMA kernel (dgrad by 20%); with a second,
     // partial wave the plain kernel with its smaller stages and two CTAs per SM wins by up to 40%.
@@ -533,22 +645,23 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         cuuint32_t box[4] = {32, (cuuint32_t)g.W, (cuuint32_t)super_rows, 1};
         AET_TRY(get_map(l, KIND == KIND_FPROP ? 8 : 10, act, 4, dims, str, box, false, &ma));
     }
+    const int bnb = pair ? bn / 2 : bn;   // N rows of a weight tile one CTA brings
     if (smerge) {
         const int taps = g.R * g.S;
         cuuint64_t dims[4] = {32, (cuuint64_t)g.K, (cuuint64_t)(g.S * g.cp) / 32, (cuuint64_t)g.R};
         cuuint64_t str[3] = {(cuuint64_t)taps * g.cp * 4, 128, (cuuint64_t)g.S * g.cp * 4};
-        cuuint32_t box[4] = {32, 32, (cuuint32_t)bn / 32, 1};
+        cuuint32_t box[4] = {32, 32, (cuuint32_t)bnb / 32, 1};
         AET_TRY(get_map(l, 13, a.src_b, 4, dims, str, box, true, &mb));
     } else if (KIND == KIND_FPROP) {
         cuuint64_t dims[2] = {(cuuint64_t)a.k_total, (cuuint64_t)g.K};
         cuuint64_t str[1] = {(cuuint64_t)a.k_total * 4};
-        cuuint32_t box[2] = {32, (cuuint32_t)bn};
+        cuuint32_t box[2] = {32, (cuuint32_t)bnb};
         AET_TRY(get_map(l, 9, a.src_b, 2, dims, str, box, false, &mb));
     } else {
         const int taps = g.R * g.S;
         cuuint64_t dims[4] = {32, (cuuint64_t)g.K, (cuuint64_t)g.cp / 32, (cuuint64_t)taps};
         cuuint64_t str[3] = {(cuuint64_t)taps * g.cp * 4, 128, (cuuint64_t)g.cp * 4};
-        cuuint32_t box[4] = {32, 32, (cuuint32_t)bn / 32, 1};
+        cuuint32_t box[4] = {32, 32, (cuuint32_t)bnb / 32, 1};
         AET_TRY(get_map(l, 11, a.src_b, 4, dims, str, box, true, &mb));
     }
     FdRowsArgs t = {};
@@ -560,19 +673,24 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
     t.stages = stages; t.tmem_cols = pow2_cols(mt * bn); t.ksplit = ksplit;
     t.par_epi = (mt == 2 && !smerge && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && ctx->opt[OPT_PAR_EPILOGUE]) ? 1 : 0;
+    t.pair = pair;
+    t.rotate = ctx->opt[OPT_ROTATE];
     const int threads = (t.par_epi || (smerge && mt == 2)) ? FD_THREADS_WIDE : NTHREADS;
     t.a_bytes = a_bytes; t.b_tile_bytes = b_tile; t.tx_bytes = a_bytes + (uint32_t)g.R * b_tile;
     t.status = ctx->status_dev;
     const size_t smem_bytes = stage * stages + 1024;
-    AET_TRY(ctx_smem_attr(ctx, conv_fd_rows_kernel<KIND>));
+    if (pair) AET_TRY(ctx_smem_attr(ctx, conv_fd_rows_kernel<KIND, true>));
+    else AET_TRY(ctx_smem_attr(ctx, conv_fd_rows_kernel<KIND, false>));
     dim3 grid((m_tiles + mt - 1) / mt, n_tiles, ksplit);
-    if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x * (t.par_epi ? 2 : 1);
+    if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x * ((t.par_epi || ksplit > 1) ? 2 : 1);
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
-    char variant[24];   // e.g. "mt2e_n128x1": two pixel tiles, second epilogue group, N tile 128, one N tile
-    snprintf(variant, sizeof(variant), "%smt%d%s_n%dx%d%s", smerge ? "sm_" : "", mt, t.par_epi ? "e" : "", bn, n_tiles, ksplit > 1 ? "_ks2" : "");
+    char variant[40];   // e.g. "mt2e_n128x1_p2": two pixel tiles, second epilogue group, N tile 128, one N tile, CTA pairs
+    snprintf(variant, sizeof(variant), "%smt%d%s_n%dx%d%s%s", smerge ? "sm_" : "", mt, t.par_epi ? "e" : "", bn, n_tiles, ksplit > 1 ? "_ks2" : "",
+             pair ? "_p2" : "");
     LaunchScope scope(ctx, name, 0, flops, variant);
-    if (ksplit > 1) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, ksplit, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
-    else launch_k(ctx->stream, grid, threads, smem_bytes, conv_fd_rows_kernel<KIND>, *ma, *mb, t);
+    if (pair) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, 2, ksplit, conv_fd_rows_kernel<KIND, true>, *ma, *mb, t);
+    else if (ksplit > 1) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, 1, ksplit, conv_fd_rows_kernel<KIND, false>, *ma, *mb, t);
+    else launch_k(ctx->stream, grid, threads, smem_bytes, conv_fd_rows_kernel<KIND, false>, *ma, *mb, t);
     return aet_check_launch(name);
 }
 

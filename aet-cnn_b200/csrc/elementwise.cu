@@ -22,6 +22,7 @@
 #include <math.h>
 
 #include "common.h"
+#include "activation.cuh"
 
 namespace {
 
@@ -48,17 +49,9 @@ __device__ __forceinline__ bool cmap_thread(const CMap &m, int &cv, int &pl) {
     return pl < m.pl_count && cv < m.cvec;
 }
 
-__device__ __forceinline__ float act_fwd(float v, int act) {
-    if (act == AET_LEAKY) return v > 0.f ? v : 0.1f * v;
-    if (act == AET_RELU) return v > 0.f ? v : 0.f;
-    return v;
-}
+__device__ __forceinline__ float act_fwd(float v, int act) { return act_forward(v, act); }
 // Gradient of the activation evaluated on its OUTPUT, as the reference does (dnn/Activation.h:99,104).
-__device__ __forceinline__ float act_grad(float y, int act) {
-    if (act == AET_LEAKY) return y > 0.f ? 1.f : 0.1f;
-    if (act == AET_RELU) return y > 0.f ? 1.f : 0.f;
-    return 1.f;
-}
+__device__ __forceinline__ float act_grad(float y, int act) { return act_gradient(y, act); }
 __device__ __forceinline__ float bn_val(float x, float mean, float inv, float g, float b) {
     return __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(x, mean), inv), g), b);
 }
@@ -1239,6 +1232,105 @@ __global__ void param_hash_kernel(const float *p, size_t n, unsigned long long *
     if ((threadIdx.x & 31) == 0) atomicAdd(hash, h);   // integer addition: order-independent
 }
 
+// Image augmentation: NImage.rotateCrop + flip + distort (dnn/NImage.c:138-157,201-337,346-362,551-572) fused into one pass,
+// one thread per output pixel (all channels).  Source NCHW as uploaded, destination the network input (NHWC, padded).
+// The coordinate arithmetic keeps the reference's double intermediates; sampling and colour math are float as there.
+__device__ __forceinline__ float aug_pixel(const float *im, int w, int h, int x, int y) {
+    return (x < 0 || x >= w || y < 0 || y >= h) ? 0.f : __ldg(im + (size_t)y * w + x);
+}
+__device__ __forceinline__ float aug_bilinear(const float *im, int w, int h, float x, float y) {
+    const int ix = (int)floorf(x), iy = (int)floorf(y);
+    const float dx = x - ix, dy = y - iy;
+    // products and sums in the reference's order, without contraction into fused multiply-adds
+    float val = __fmul_rn(__fmul_rn(1 - dy, 1 - dx), aug_pixel(im, w, h, ix, iy));
+    val = __fadd_rn(val, __fmul_rn(__fmul_rn(dy, 1 - dx), aug_pixel(im, w, h, ix, iy + 1)));
+    val = __fadd_rn(val, __fmul_rn(__fmul_rn(1 - dy, dx), aug_pixel(im, w, h, ix + 1, iy)));
+    val = __fadd_rn(val, __fmul_rn(__fmul_rn(dy, dx), aug_pixel(im, w, h, ix + 1, iy + 1)));
+    return val;
+}
+__global__ void augment_kernel(const float *__restrict__ src, int n, int c, int sh, int sw, float *__restrict__ dst, int size, int cp,
+                               const aet_augment *__restrict__ params) {
+    pdl_enter();
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= (size_t)n * size * size) return;
+    const int x = (int)(e % size);
+    const int y = (int)((e / size) % size);
+    const int b = (int)(e / ((size_t)size * size));
+    const aet_augment p = params[b];
+    const int w = size, h = size;
+    const float cx = (float)(sw / 2.0), cy = (float)(sh / 2.0);
+    const float cr = (float)cos((double)p.rad), sr = (float)sin((double)p.rad);
+    const float dx1 = p.dx / p.scale * p.aspect, dy1 = p.dy / p.scale;
+    const int xs = p.flip ? w - 1 - x : x;      // the flipped crop's pixel x is the crop's pixel w-1-x
+    const float rx = (float)((double)cr * (((double)xs - w / 2.) / p.scale * p.aspect + dx1) - (double)sr * (((double)y - h / 2.) / p.scale + dy1) + cx);
+    const float ry = (float)((double)sr * (((double)xs - w / 2.) / p.scale * p.aspect + dx1) + (double)cr * (((double)y - h / 2.) / p.scale + dy1) + cy);
+    float *out = dst + e * cp;
+    const float *img = src + (size_t)b * c * sh * sw;
+    if (c != 3) {
+        for (int k = 0; k < cp; ++k) out[k] = k < c ? aug_bilinear(img + (size_t)k * sh * sw, sw, sh, rx, ry) : 0.f;
+        return;
+    }
+    float r = aug_bilinear(img, sw, sh, rx, ry), g = aug_bilinear(img + (size_t)sh * sw, sw, sh, rx, ry),
+          bl = aug_bilinear(img + (size_t)2 * sh * sw, sw, sh, rx, ry);
+    // RGB -> HSV
+    const float mx = fmaxf(r, fmaxf(g, bl)), mn = fminf(r, fminf(g, bl));
+    const float delta = mx - mn;
+    float hh, ss, vv = mx;
+    if (mx == 0.f) { ss = 0.f; hh = 0.f; }
+    else {
+        ss = delta / mx;
+        if (r == mx) hh = (g - bl) / delta;
+        else if (g == mx) hh = 2.f + (bl - r) / delta;
+        else hh = 4.f + (r - g) / delta;
+        if (hh < 0.f) hh += 6.f;
+        hh = (float)((double)hh / 6.);
+    }
+    ss = __fmul_rn(ss, p.dsat);
+    vv = __fmul_rn(vv, p.dexp);
+    hh = __fadd_rn(hh, p.dhue);
+    if (hh > 1.f) hh -= 1.f;
+    if (hh < 0.f) hh += 1.f;
+    // HSV -> RGB
+    const float hq = __fmul_rn(6.f, hh);
+    if (ss == 0.f) { r = g = bl = vv; }
+    else {
+        const int index = (int)floorf(hq);
+        const float f = hq - index;
+        const float pp = __fmul_rn(vv, 1.f - ss);
+        const float q = __fmul_rn(vv, 1.f - __fmul_rn(ss, f));
+        const float t = __fmul_rn(vv, 1.f - __fmul_rn(ss, 1.f - f));
+        if (index == 0) { r = vv; g = t; bl = pp; }
+        else if (index == 1) { r = q; g = vv; bl = pp; }
+        else if (index == 2) { r = pp; g = vv; bl = t; }
+        else if (index == 3) { r = pp; g = q; bl = vv; }
+        else if (index == 4) { r = t; g = pp; bl = vv; }
+        else { r = vv; g = pp; bl = q; }
+    }
+    *reinterpret_cast<float4 *>(out) = make_float4(fminf(fmaxf(r, 0.f), 1.f), fminf(fmaxf(g, 0.f), 1.f), fminf(fmaxf(bl, 0.f), 1.f), 0.f);
+}
+
+// DnnUtils.topK (dnn/DnnUtils.c:463-477), one thread per sample running the reference's own insertion loop, so ties
+// and order come out exactly as there: index[j] = position of the j-th largest score, strict '>' comparisons.
+__global__ void top_k_kernel(const float *__restrict__ scores, int samples, int n, int ld, int k, int *__restrict__ index) {
+    pdl_enter();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= samples) return;
+    const float *a = scores + (size_t)s * ld;
+    int *idx = index + (size_t)s * k;
+    for (int j = 0; j < k; ++j) idx[j] = -1;
+    for (int i = 0; i < n; ++i) {
+        int curr = i;
+        for (int j = 0; j < k; ++j) {
+            if (idx[j] < 0 || a[curr] > a[idx[j]]) {
+                const int swap = curr;
+                curr = idx[j];
+                idx[j] = swap;
+            }
+            if (curr < 0) break;   // an empty slot was filled: the remaining slots are empty too and stay so
+        }
+    }
+}
+
 struct ReducePlan {
     CMap m;
     int blocks;
@@ -1688,6 +1780,20 @@ int k_tail_publish(aet_network *net) {
     LaunchScope s(ctx, "grad_publish", 8.0 * net->tail_n, 0);
     launch_k(ctx->stream, blocks, 1024, 0, tail_publish_kernel, net->arena.G, t, p);
     return aet_check_launch("grad_publish");
+}
+
+int k_augment(aet_context *ctx, const float *src_nchw, int n, int c, int sh, int sw, float *dst_nhwc, int size, int cp,
+              const aet_augment *params_dev) {
+    const size_t px = (size_t)n * size * size;
+    LaunchScope s(ctx, "augment", 4.0 * n * c * sh * sw + 4.0 * px * cp, 0);
+    launch_k(ctx->stream, (unsigned)((px + TB - 1) / TB), TB, 0, augment_kernel, src_nchw, n, c, sh, sw, dst_nhwc, size, cp, params_dev);
+    return aet_check_launch("augment");
+}
+
+int k_top_k(aet_context *ctx, const float *scores, int samples, int n, int ld, int k, int *index_dev) {
+    LaunchScope s(ctx, "top_k", 4.0 * samples * n, 0);
+    launch_k(ctx->stream, (unsigned)((samples + 63) / 64), 64, 0, top_k_kernel, scores, samples, n, ld, k, index_dev);
+    return aet_check_launch("top_k");
 }
 
 int k_param_hash(aet_context *ctx, const float *p, size_t count, uint64_t *hash_dev) {

@@ -57,7 +57,8 @@ int read_tensor_or_zero(aet_tensor *t, float *host) {
 
 }  // namespace
 
-size_t conv_param_floats(int c, int n, int size, int batch_normalize) {
+size_t conv_param_floats(int c, int n, int size, int batch_normalize, int groups) {
+    c /= groups > 0 ? groups : 1;
     const int cp = round_up(c, 4);
     size_t total = round_up_sz((size_t)n * size * size * cp, 1024) + round_up_sz((size_t)round_up(n, 4), 1024);
     if (batch_normalize) total += round_up_sz((size_t)round_up(n, 4), 1024);
@@ -80,9 +81,19 @@ aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, 
                                 int size, int stride_x, int stride_y, int dilation, int padding, aet_activation activation,
                                 int batch_normalize, int train, int index) {
     if (!ctx) { aet_set_error("null context"); return nullptr; }
-    if (groups != 1 || dilation != 1) { aet_set_error("convolutional: only groups=1, dilation=1 are supported"); return nullptr; }
+    if (groups < 1 || dilation < 1) { aet_set_error("convolutional: groups and dilation must be positive"); return nullptr; }
+    if (groups > 1 && (c % groups || n % groups || (c / groups) % 4 || (n / groups) % 4)) {
+        aet_set_error("convolutional: groups=%d needs channels/groups and filters/groups to be multiples of 4 (got %d, %d)", groups, c, n);
+        return nullptr;
+    }
+    if (dilation > 1 && (size % 2 == 0 || padding != size / 2)) {
+        // the reference sizes the output from `padding` but gathers with padding * dilation (dnn/ConvolutionalLayer.c:337-343,
+        // 795-801): the two only agree for odd filters padded by size / 2, which is what its cfgs use
+        aet_set_error("convolutional: dilation > 1 needs an odd size with padding = size/2");
+        return nullptr;
+    }
     if (batch_normalize != 0 && batch_normalize != 1) { aet_set_error("convolutional: batch_normalize must be 0 or 1"); return nullptr; }
-    if (activation != AET_LINEAR && activation != AET_RELU && activation != AET_LEAKY) { aet_set_error("convolutional: unsupported activation"); return nullptr; }
+    if ((int)activation < 0 || (int)activation >= AET_ACTIVATION_COUNT) { aet_set_error("convolutional: unsupported activation"); return nullptr; }
     if (batch <= 0 || h <= 0 || w <= 0 || c <= 0 || n <= 0 || size <= 0 || stride_x <= 0 || stride_y <= 0 || padding < 0) {
         aet_set_error("convolutional: bad geometry");
         return nullptr;
@@ -95,12 +106,13 @@ aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, 
     l->oc = n; l->oh = oh; l->ow = ow; l->ocp = round_up(n, 4);
     l->size = size; l->stride_x = stride_x; l->stride_y = stride_y; l->pad = padding;
     l->bn = batch_normalize; l->act = activation; l->train = train;
+    l->groups = groups; l->dilation = dilation; l->cg = c / groups; l->cgp = round_up(c / groups, 4);
     if (!arena) {
-        if (arena_create(&l->own_arena, conv_param_floats(c, n, size, batch_normalize)) != AET_OK) { delete l; return nullptr; }
+        if (arena_create(&l->own_arena, conv_param_floats(c, n, size, batch_normalize, groups)) != AET_OK) { delete l; return nullptr; }
         arena = &l->own_arena;
     }
     l->arena = arena;
-    l->seg_w = arena_take(arena, (size_t)n * size * size * l->cp);
+    l->seg_w = arena_take(arena, (size_t)n * size * size * l->cgp);
     l->seg_b = arena_take(arena, (size_t)l->ocp);
     if (batch_normalize) l->seg_s = arena_take(arena, (size_t)l->ocp);
     if (arena->used > arena->capacity) { aet_set_error("parameter arena overflow"); delete l; return nullptr; }
@@ -127,14 +139,14 @@ aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, 
     // Initial weights: scale * U(-1,1), scale = sqrt(2/(size*size*c)) as dnn/WeightData.c:153-167,
     // from a counter-based generator instead of rand().
     {
-        std::vector<float> wts((size_t)n * c * size * size);
-        const float scale = sqrtf(2.f / (size * size * c));
+        std::vector<float> wts((size_t)n * (c / groups) * size * size);
+        const float scale = sqrtf(2.f / (size * size * c / groups));   // dnn/ConvolutionalLayer.c:233
         for (size_t i = 0; i < wts.size(); ++i) {
             uint64_t z = mix64(0xA17C0DEULL + (uint64_t)index * 0x632BE59BD9B4E019ULL + (i + 1) * 0x9E3779B97F4A7C15ULL);
             float u = (float)(z >> 40) * (1.0f / 16777216.0f);
             wts[i] = scale * (2.f * u - 1.f);
         }
-        if (tensor_upload_nchw(ctx, layer_W(l), wts.data(), n, c, size, size, l->cp, false) != AET_OK) {
+        if (tensor_upload_nchw(ctx, layer_W(l), wts.data(), n, c / groups, size, size, l->cgp, false) != AET_OK) {
             aet_layer_destroy(l);
             return nullptr;
         }
@@ -478,6 +490,32 @@ extern "C" int aet_layer_update(aet_layer *l, int batch, float learning_rate, fl
     return AET_OK;
 }
 
+// ConvolutionalLayer.fuseConvBatchnorm (dnn/ConvolutionalLayer.c:983-1003): the rolling statistics and the scale are
+// folded into biases and weights, in double on the host exactly as the reference computes them (a one-off step before
+// inference, not a hot path), and the layer becomes a plain convolution + bias + activation.
+int conv_layer_fuse_batchnorm(aet_layer *l) {
+    if (!l || l->type != AET_CONVOLUTIONAL || !l->bn) return AET_OK;
+    const size_t nw = aet_layer_param_count(l, AET_P_WEIGHTS);
+    std::vector<float> b(l->oc), s(l->oc), rm(l->oc), rv(l->oc), w(nw);
+    AET_TRY(aet_layer_read(l, AET_P_BIASES, b.data()));
+    AET_TRY(aet_layer_read(l, AET_P_SCALES, s.data()));
+    AET_TRY(aet_layer_read(l, AET_P_ROLLING_MEAN, rm.data()));
+    AET_TRY(aet_layer_read(l, AET_P_ROLLING_VARIANCE, rv.data()));
+    AET_TRY(aet_layer_read(l, AET_P_WEIGHTS, w.data()));
+    const size_t filter_size = nw / (size_t)l->oc;
+    for (int f = 0; f < l->oc; ++f) {
+        b[f] = b[f] - (double)s[f] * rm[f] / (sqrt((double)rv[f] + .00001));
+        const double precomputed = s[f] / (sqrt((double)rv[f] + .00001));
+        for (size_t i = 0; i < filter_size; ++i) w[(size_t)f * filter_size + i] *= precomputed;
+    }
+    AET_TRY(aet_layer_write(l, AET_P_BIASES, b.data()));
+    AET_TRY(aet_layer_write(l, AET_P_WEIGHTS, w.data()));
+    l->bn = 0;
+    l->output_stale = false;
+    if (l->fused_pool) { l->fused_pool->fused_into = nullptr; l->fused_pool->fused_ready = false; l->fused_pool = nullptr; }
+    return AET_OK;
+}
+
 extern "C" int aet_layer_init_delta(aet_layer *l) {
     if (!l) return fail_invalid("null layer");
     if (!l->delta || l->type == AET_DROPOUT) return AET_OK;
@@ -514,7 +552,7 @@ extern "C" size_t aet_layer_param_count(const aet_layer *l, aet_param which) {
     const size_t act = (size_t)l->batch * l->oc * l->oh * l->ow;
     switch (which) {
     case AET_P_WEIGHTS: case AET_P_WEIGHT_UPDATES:
-        return l->type == AET_CONVOLUTIONAL ? (size_t)l->oc * l->c * l->size * l->size : 0;
+        return l->type == AET_CONVOLUTIONAL ? (size_t)l->oc * l->cg * l->size * l->size : 0;
     case AET_P_BIASES: case AET_P_BIAS_UPDATES:
         return l->type == AET_CONVOLUTIONAL ? (size_t)l->oc : 0;
     case AET_P_SCALES: case AET_P_SCALE_UPDATES: case AET_P_ROLLING_MEAN: case AET_P_ROLLING_VARIANCE:
@@ -545,15 +583,15 @@ extern "C" int aet_layer_read(aet_layer *l, aet_param which, void *host_v) {
     if (aet_layer_param_count(l, which) == 0) return fail_invalid("aet_layer_read: this layer has no such buffer");
     float *host = static_cast<float *>(host_v);
     aet_context *ctx = l->ctx;
-    const size_t nw = (size_t)l->oc * l->c * l->size * l->size;
+    const size_t nw = (size_t)l->oc * l->cg * l->size * l->size;
     switch (which) {
     case AET_P_WEIGHTS:
-        return tensor_download_nchw(ctx, layer_W(l), host, l->oc, l->c, l->size, l->size, l->cp);
+        return tensor_download_nchw(ctx, layer_W(l), host, l->oc, l->cg, l->size, l->size, l->cgp);
     case AET_P_WEIGHT_UPDATES: {
         // what the reference's weight_updates holds: carried momentum plus the pending gradient
-        AET_TRY(tensor_download_nchw(ctx, layer_U(l), host, l->oc, l->c, l->size, l->size, l->cp));
+        AET_TRY(tensor_download_nchw(ctx, layer_U(l), host, l->oc, l->cg, l->size, l->size, l->cgp));
         std::vector<float> g(nw);
-        AET_TRY(tensor_download_nchw(ctx, layer_G(l), g.data(), l->oc, l->c, l->size, l->size, l->cp));
+        AET_TRY(tensor_download_nchw(ctx, layer_G(l), g.data(), l->oc, l->cg, l->size, l->size, l->cgp));
         for (size_t i = 0; i < nw; ++i) host[i] += g[i];
         return AET_OK;
     }
@@ -618,9 +656,9 @@ extern "C" int aet_layer_write(aet_layer *l, aet_param which, const void *host_v
     aet_context *ctx = l->ctx;
     switch (which) {
     case AET_P_WEIGHTS:
-        return tensor_upload_nchw(ctx, layer_W(l), host, l->oc, l->c, l->size, l->size, l->cp, false);
+        return tensor_upload_nchw(ctx, layer_W(l), host, l->oc, l->cg, l->size, l->size, l->cgp, false);
     case AET_P_WEIGHT_UPDATES:
-        AET_TRY(tensor_upload_nchw(ctx, layer_U(l), host, l->oc, l->c, l->size, l->size, l->cp, false));
+        AET_TRY(tensor_upload_nchw(ctx, layer_U(l), host, l->oc, l->cg, l->size, l->size, l->cgp, false));
         AET_CUDA(cudaMemsetAsync(layer_G(l), 0, l->seg_w.padded * sizeof(float), ctx->stream));
         return AET_OK;
     case AET_P_BIASES: return write_vec(l, layer_b(l), host, l->oc, nullptr);
@@ -680,5 +718,12 @@ extern "C" int aet_layer_load_weights(aet_layer *l, void *fpv) {
     }
     std::vector<float> wts(aet_layer_param_count(l, AET_P_WEIGHTS));
     if (fread(wts.data(), sizeof(float), wts.size(), fp) != wts.size()) { aet_set_error("weights file: unexpected end (layer %d weights)", l->index); return AET_E_IO; }
+    if (l->flipped) {   // stored as [(c * size * size) rows][filters]: transposeMatrix of dnn/ConvolutionalLayer.c:444-454,483-485
+        const size_t rows = (size_t)l->cg * l->size * l->size, cols = (size_t)l->oc;
+        std::vector<float> t(wts.size());
+        for (size_t x = 0; x < rows; ++x)
+            for (size_t y = 0; y < cols; ++y) t[y * rows + x] = wts[x * cols + y];
+        wts.swap(t);
+    }
     return aet_layer_write(l, AET_P_WEIGHTS, wts.data());
 }

@@ -17,7 +17,8 @@
 aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, int h, int w, int c, int n, int groups,
                                 int size, int stride_x, int stride_y, int dilation, int padding, aet_activation activation,
                                 int batch_normalize, int train, int index);
-size_t conv_param_floats(int c, int n, int size, int batch_normalize);
+size_t conv_param_floats(int c, int n, int size, int batch_normalize, int groups);
+int conv_layer_fuse_batchnorm(aet_layer *l);
 void arena_destroy(ParamArena *a);
 int arena_create_public(ParamArena *a, size_t floats);
 
@@ -76,20 +77,21 @@ std::string opt_str(const Section &s, const char *key, const char *def) {
 }
 
 int parse_activation(const std::string &a, aet_activation *out) {
-    if (a == "linear") *out = AET_LINEAR;
-    else if (a == "relu") *out = AET_RELU;
-    else if (a == "leaky") *out = AET_LEAKY;
-    else {
-        aet_set_error("activation '%s' is outside the supported set (linear, relu, leaky); note the reference's "
-                      "default for a missing key is 'logistic'", a.c_str());
-        return AET_E_INVALID;
-    }
-    return AET_OK;
+    // dnn/Activation.c:105-124, restricted to the types whose gradient is a function of the output
+    static const struct { const char *name; aet_activation act; } table[] = {
+        {"linear", AET_LINEAR}, {"relu", AET_RELU}, {"leaky", AET_LEAKY}, {"logistic", AET_LOGISTIC}, {"relu6", AET_RELU6},
+        {"relie", AET_RELIE}, {"ramp", AET_RAMP}, {"tanh", AET_TANH}, {"plse", AET_PLSE}, {"elu", AET_ELU}, {"loggy", AET_LOGGY},
+        {"hardtan", AET_HARDTAN}, {"lhtan", AET_LHTAN}, {"selu", AET_SELU}};
+    for (const auto &e : table)
+        if (a == e.name) { *out = e.act; return AET_OK; }
+    aet_set_error("activation '%s' is outside the supported set (linear, relu, leaky, logistic, relu6, relie, ramp, tanh, plse, "
+                  "elu, loggy, hardtan, lhtan, selu)", a.c_str());
+    return AET_E_INVALID;
 }
 
 const char *kUnsupportedConvKeys[] = {"binary", "xnor", "bin_output", "sway", "rotate", "stretch", "stretch_sway",
                                       "antialiasing", "assisted_excitation", "cbn", "coordconv", "grad_centr", "reverse",
-                                      "share_index", "flipped"};
+                                      "share_index"};
 
 // ---------------------------------------------------------------------------- NCCL through dlopen
 struct NcclUniqueId { char internal[128]; };
@@ -444,7 +446,7 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
                 if (sy < 1) sy = stride;
                 int padding = opt_int(s, "padding", 0);
                 if (opt_int(s, "pad", 0)) padding = size / 2;
-                arena_floats += conv_param_floats(c, n, size, opt_int(s, "batch_normalize", 0));
+                arena_floats += conv_param_floats(c, n, size, opt_int(s, "batch_normalize", 0), opt_int(s, "groups", 1));
                 h = (h + 2 * padding - size) / (sy > 0 ? sy : 1) + 1;
                 w = (w + 2 * padding - size) / (sx > 0 ? sx : 1) + 1;
                 c = n;
@@ -485,7 +487,10 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
             if (parse_activation(opt_str(s, "activation", "logistic"), &act) != AET_OK) { aet_network_destroy(net); return nullptr; }
             l = conv_layer_create_in(ctx, &net->arena, net->batch, h, w, c, n, groups, size, sx, sy, dilation, padding, act,
                                      opt_int(s, "batch_normalize", 0), train, index);
-            if (l) l->lr_scale = opt_float(s, "learning_rate", 1.f);
+            if (l) {
+                l->lr_scale = opt_float(s, "learning_rate", 1.f);
+                l->flipped = opt_int(s, "flipped", 0);
+            }
         } else if (s.name == "maxpool" || s.name == "max") {
             const int stride = opt_int(s, "stride", 1), sx = opt_int(s, "stride_x", stride), sy = opt_int(s, "stride_y", stride);
             const int size = opt_int(s, "size", stride), padding = opt_int(s, "padding", size - 1);
@@ -652,6 +657,7 @@ extern "C" float aet_network_cost(aet_network *net) {
 extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     if (!net->train) { aet_set_error("network was created with train=0"); return AET_E_INVALID; }
+    if (net->bn_fused) { aet_set_error("batch-norm layers were fused into their convolutions: this network only predicts"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
     net->seen += net->batch;           // dnn/NNetwork.c:742
     // The reference runs `subdivisions` of these calls, then ONE update with update_batch = batch * subdivisions
@@ -801,6 +807,91 @@ extern "C" int aet_network_predict(aet_network *net, const float *host_x, float 
     return aet_tensor_read(net->layers.back()->output, host_out);
 }
 
+// NNetwork.fuseConvBatchnorm (dnn/NNetwork.c:272-290), the convolutional branch.
+extern "C" int aet_network_fuse_conv_batchnorm(aet_network *net) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    graph_drop(net);
+    for (aet_layer *l : net->layers)
+        if (l->type == AET_CONVOLUTIONAL && l->bn) AET_TRY(conv_layer_fuse_batchnorm(l));
+    net->bn_fused = true;
+    return AET_OK;
+}
+
+// Forward with train = 0 on a host batch, then DnnUtils.topK (dnn/DnnUtils.c:463-477) per sample on the device.
+extern "C" int aet_network_predict_topk(aet_network *net, const float *host_x, int k, int *host_indexes) {
+    if (!net || !host_x || !host_indexes || k <= 0) { aet_set_error("aet_network_predict_topk: bad argument"); return AET_E_INVALID; }
+    aet_layer *last = net->layers.back();
+    const int classes = last->oc * last->oh * last->ow;
+    if (last->oh != 1 || last->ow != 1) { aet_set_error("aet_network_predict_topk: the last layer must be 1x1 spatial"); return AET_E_INVALID; }
+    if (k > classes) k = classes;
+    AET_TRY(aet_tensor_write(net->input, host_x));
+    aet_state st = {};
+    st.input = net->input; st.train = 0;
+    AET_TRY(net_forward(net, st));
+    float *scratch = nullptr;
+    AET_TRY(ctx_scratch(net->ctx, (size_t)net->batch * k * sizeof(int), &scratch));
+    int *idx = reinterpret_cast<int *>(scratch);
+    AET_TRY(k_top_k(net->ctx, last->output->d, net->batch, classes, last->ocp, k, idx));
+    AET_CUDA(cudaMemcpyAsync(host_indexes, idx, (size_t)net->batch * k * sizeof(int), cudaMemcpyDeviceToHost, net->ctx->stream));
+    AET_CUDA(cudaStreamSynchronize(net->ctx->stream));
+    return AET_OK;
+}
+
+// The accuracy loop of Classifier.validateSingle (dnn/Classifier.c:359-464) over images already decoded, resized
+// and cropped by the caller: predict, top-k, count hits.  top1 = avg_acc / count, topk = avg_topk / count.
+extern "C" int aet_network_validate(aet_network *net, const float *host_images, const int *class_ids, int count, int k,
+                                    float *top1, float *topk) {
+    if (!net || !host_images || !class_ids || count <= 0 || k <= 0) { aet_set_error("aet_network_validate: bad argument"); return AET_E_INVALID; }
+    const size_t per = (size_t)net->c * net->h * net->w;
+    aet_layer *last = net->layers.back();
+    const int classes = last->oc;
+    if (k > classes) k = classes;       // "if (topk > classes) topk = classes", :399-400
+    std::vector<float> batch(per * net->batch, 0.f);
+    std::vector<int> idx((size_t)net->batch * k);
+    double avg_acc = 0, avg_topk = 0;
+    for (int base = 0; base < count; base += net->batch) {
+        const int n = count - base < net->batch ? count - base : net->batch;
+        memcpy(batch.data(), host_images + (size_t)base * per, (size_t)n * per * sizeof(float));
+        if (n < net->batch) memset(batch.data() + (size_t)n * per, 0, (size_t)(net->batch - n) * per * sizeof(float));
+        AET_TRY(aet_network_predict_topk(net, batch.data(), k, idx.data()));
+        for (int i = 0; i < n; ++i) {
+            const int *ix = idx.data() + (size_t)i * k;
+            if (ix[0] == class_ids[base + i]) avg_acc += 1;
+            for (int j = 0; j < k; ++j)
+                if (ix[j] == class_ids[base + i]) avg_topk += 1;
+        }
+    }
+    if (top1) *top1 = (float)(avg_acc / count);
+    if (topk) *topk = (float)(avg_topk / count);
+    return AET_OK;
+}
+
+// The augmentation chain of ImageData.loadImageAugmentPaths (dnn/ImageData.c:56-73) on the device: upload the source
+// images and the per-image draws, one kernel writes the network's input tensor.
+extern "C" int aet_network_augment_input(aet_network *net, const float *host_src, int src_h, int src_w, const aet_augment *params) {
+    if (!net || !host_src || !params || src_h <= 0 || src_w <= 0) { aet_set_error("aet_network_augment_input: bad argument"); return AET_E_INVALID; }
+    if (net->w != net->h) { aet_set_error("aet_network_augment_input: only square network inputs (the crop is size x size)"); return AET_E_INVALID; }
+    aet_context *ctx = net->ctx;
+    const size_t src_floats = (size_t)net->batch * net->c * src_h * src_w;
+    const size_t par_floats = ((size_t)net->batch * sizeof(aet_augment) + sizeof(float) - 1) / sizeof(float);
+    AET_TRY(ctx_staging(ctx, (src_floats + par_floats) * sizeof(float)));
+    const bool pinned = host_pinned(host_src);
+    if (pinned) {
+        AET_CUDA(cudaMemcpyAsync(ctx->staging, host_src, src_floats * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+        AET_CUDA(cudaStreamSynchronize(ctx->stream));
+        memcpy(ctx->pinned, host_src, src_floats * sizeof(float));
+        AET_CUDA(cudaMemcpyAsync(ctx->staging, ctx->pinned, src_floats * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    }
+    memcpy(ctx->pinned + src_floats, params, (size_t)net->batch * sizeof(aet_augment));
+    AET_CUDA(cudaMemcpyAsync(ctx->staging + src_floats, ctx->pinned + src_floats, par_floats * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    AET_TRY(k_augment(ctx, ctx->staging, net->batch, net->c, src_h, src_w, net->input->d, net->w, net->input->cp,
+                      reinterpret_cast<const aet_augment *>(ctx->staging + src_floats)));
+    net->input->lazy_zero = false;
+    AET_CUDA(cudaStreamSynchronize(ctx->stream));   // the pinned mirror and the caller's buffers are free again
+    return AET_OK;
+}
+
 extern "C" int aet_network_use_graph(aet_network *net, int enable) {
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     net->use_graph = enable != 0;
@@ -838,7 +929,8 @@ extern "C" int aet_network_load_weights(aet_network *net, const char *path) {
         if (fread(&seen, sizeof(int32_t), 1, fp) != 1) { fclose(fp); aet_set_error("weights file: short header"); return AET_E_IO; }
         net->seen = seen;
     }
-    if (header[0] > 1000 || header[1] > 1000) { fclose(fp); aet_set_error("weights file: transposed ('flipped') files are not supported"); return AET_E_IO; }
+    // (the reference derives a whole-file `transpose` flag from major/minor > 1000 at dnn/NNetwork.c:92 and never uses
+    // it; transposed records are a per-layer property, the cfg key `flipped`)
     net->cur_iteration = net->seen / ((int64_t)net->batch * net->subdivisions);
     int r = AET_OK;
     for (size_t i = 0; r == AET_OK && i < net->layers.size(); ++i) r = aet_layer_load_weights(net->layers[i], fp);

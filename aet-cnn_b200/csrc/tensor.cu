@@ -108,7 +108,8 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"linear_head", "AET_NO_LINEAR_HEAD", 1, 0},
     {"xchg_cap_floats", "AET_XCHG_CAP_FLOATS", 0, -1},
     {"nccl_max_ctas", "AET_NCCL_MAX_CTAS", 8, -1},
-    {"persistent", "AET_NO_PERSISTENT", 1, 0},
+    {"rotate", "AET_NO_ROTATE", 1, 0},
+    {"pair", "AET_NO_PAIR", 1, 0},
 };
 }  // namespace
 

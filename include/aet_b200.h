@@ -35,8 +35,13 @@ extern "C" {
 #define AET_E_NCCL      (-6)
 #define AET_E_NAN       (-7)   /* non-finite values detected (try_fix_nan diagnostics) */
 
-/* dnn/Activation.h:15-19 (only the types on the hot path) */
-typedef enum { AET_LINEAR = 0, AET_RELU = 1, AET_LEAKY = 2 } aet_activation;
+/* dnn/Activation.h:15-19: the types whose gradient is a function of the output (dnn/Activation.h:41-113).  The
+ * first three are the hot path's; cfg names are the reference's ("logistic", "relu6", "relie", "ramp", "tanh",
+ * "plse", "elu", "loggy", "hardtan", "lhtan", "selu").  stair, gelu, swish, mish and the channel normalisations
+ * are not built. */
+typedef enum { AET_LINEAR = 0, AET_RELU = 1, AET_LEAKY = 2, AET_LOGISTIC = 3, AET_RELU6 = 4, AET_RELIE = 5, AET_RAMP = 6,
+               AET_TANH = 7, AET_PLSE = 8, AET_ELU = 9, AET_LOGGY = 10, AET_HARDTAN = 11, AET_LHTAN = 12, AET_SELU = 13 } aet_activation;
+#define AET_ACTIVATION_COUNT 14
 /* dnn/NLayer.c:30-60 layer kinds that NetworkFactory.createLayer instantiates on the hot path */
 typedef enum { AET_CONVOLUTIONAL = 0, AET_MAXPOOL = 1, AET_AVGPOOL = 2, AET_SOFTMAX = 3, AET_DROPOUT = 4 } aet_layer_type;
 /* Which of the reference's two numerically different back ends the formulas follow:
@@ -97,7 +102,7 @@ int          aet_context_set_parity(aet_context *ctx, aet_parity_mode mode);
 int          aet_context_set_math(aet_context *ctx, aet_math_mode mode);
 int          aet_context_synchronize(aet_context *ctx);
 /* Behaviour switches (kernel choice, fusions, stream overlap), by name: "rows", "rows_fprop", "rows_dgrad",
- * "smerge", "ksplit", "mt2", "rows_multi", "par_epilogue", "fc_alias", "epilogue_stats", "thin", "persistent",
+ * "smerge", "ksplit", "mt2", "rows_multi", "par_epilogue", "fc_alias", "epilogue_stats", "thin", "pair", "rotate",
  * "overlap_wgrad", "wgrad_splits", "bn_tile", "gather_only" (take effect at the next launch), "fuse",
  * "linear_head", "xchg_cap_floats" (read when a network is built / the exchange is exported).  The matching
  * AET_* environment variables only give the initial values and are read once, in aet_context_create. */
@@ -218,6 +223,31 @@ int   aet_network_last_loss(aet_network *net, float *loss);
 int   aet_network_train_step_async(aet_network *net, const float *host_x, const float *host_truth, float *previous_loss);
 /* NNetwork.predict (dnn/NNetwork.c:411-428): forward with train=0, copy the last layer's output. */
 int   aet_network_predict(aet_network *net, const float *host_x, float *host_out);
+/* NNetwork.fuseConvBatchnorm (dnn/NNetwork.c:272-290, dnn/ConvolutionalLayer.c:983-1003): folds every batch-norm
+ * layer's rolling statistics and scale into its convolution's biases and weights; afterwards the network only
+ * predicts (training calls return AET_E_INVALID).  Run it after aet_network_load_weights, as the reference's
+ * validation and prediction entry points do (dnn/Classifier.c:372-374). */
+int   aet_network_fuse_conv_batchnorm(aet_network *net);
+/* predict + DnnUtils.topK (dnn/DnnUtils.c:463-477): host_indexes[batch][k] = class indexes by descending score. */
+int   aet_network_predict_topk(aet_network *net, const float *host_x, int k, int *host_indexes);
+/* The accuracy loop of Classifier.validateSingle (dnn/Classifier.c:431-462) over `count` images the caller has
+ * already decoded and cropped to the network's input ([count][c][h][w]); class_ids[count] are the true classes.
+ * top1 = share of images whose best class is right, topk = share with the right class among the best k. */
+int   aet_network_validate(aet_network *net, const float *host_images, const int *class_ids, int count, int k,
+                           float *top1, float *topk);
+/* Device-side image augmentation: the per-image chain of ImageData.loadImageAugmentPaths (dnn/ImageData.c:56-73) --
+ * NImage.rotateCrop with bilinear sampling (dnn/NImage.c:138-157,551-572), NImage.flip (:346-362), NImage.distort in HSV
+ * (:201-337) -- as ONE kernel that reads the uploaded source images and writes the network's input tensor, instead of
+ * the reference's host loops followed by an upload of the finished batch.  The random draws stay with the caller
+ * (one aet_augment per image, drawn as the reference draws them: :1016-1035 for rad/scale/dx/dy/aspect, :339-344 for
+ * dhue/dsat/dexp), so a run is reproducible and checkable.  Source images: host FP32 [batch][c][src_h][src_w], all of
+ * one size; the crop is net width x net height (square networks: the reference's final resize is then the identity). */
+typedef struct aet_augment {
+    float rad, scale, dx, dy, aspect;   /* rotateCrop(rad, scale, size, size, dx, dy, aspect) */
+    int   flip;                         /* mirror left-right */
+    float dhue, dsat, dexp;             /* distort(dhue, dsat, dexp); ignored unless channels == 3 */
+} aet_augment;
+int   aet_network_augment_input(aet_network *net, const float *host_src, int src_h, int src_w, const aet_augment *params);
 /* Capture forward+backward+update into a CUDA graph that later train steps replay (0 = off). */
 int   aet_network_use_graph(aet_network *net, int enable);
 /* NNetwork.loadWeights / saveWeights (dnn/NNetwork.c:64-147): Darknet .weights container. */

@@ -204,23 +204,76 @@ void aeto_backward_bias(float *bias_updates, const float *delta, int batch, int 
 
 /* dnn/Activation.h:53,56,61 (CPU scalar definitions; `.1*x` is a double product) and
  * dnn/mtcs/MtcsActivation.c:112-117 (`.1f*x`). */
-void aeto_activate(float *y, size_t count, int activation, int mode) {
-    if (activation == AETO_LINEAR) return;
-    for (size_t i = 0; i < count; ++i) {
-        float v = y[i];
-        if (activation == AETO_RELU) y[i] = v * (v > 0);
-        else if (mode == AETO_MODE_CPU) y[i] = (v > 0) ? v : (float)(.1 * v);
-        else y[i] = (v > 0) ? v : .1f * v;
+/* Scalar activations, dnn/Activation.h:41-113 (CPU, double intermediates where the reference's literals are double)
+ * and mtcs/MtcsActivation.c:17-103 (GPU, float).  Numbering: AETO_LINEAR 0, RELU 1, LEAKY 2, then LOGISTIC 3,
+ * RELU6 4, RELIE 5, RAMP 6, TANH 7, PLSE 8, ELU 9, LOGGY 10, HARDTAN 11, LHTAN 12, SELU 13. */
+static float act_cpu(float x, int a) {
+    switch (a) {
+    case 0: return x;
+    case 1: return x * (x > 0);
+    case 2: return (x > 0) ? x : .1 * x;
+    case 3: return 1. / (1. + exp(-x));
+    case 4: return fminf(fmaxf(x, 0), 6);                       /* the CPU class has no relu6; GPU form */
+    case 5: return (x > 0) ? x : .01 * x;
+    case 6: return x * (x > 0) + .1 * x;
+    case 7: return (exp(2 * x) - 1) / (exp(2 * x) + 1);
+    case 8: if (x < -4) return .01 * (x + 4); if (x > 4) return .01 * (x - 4) + 1; return .125 * x + .5;
+    case 9: return (x >= 0) * x + (x < 0) * (exp(x) - 1);
+    case 10: return 2. / (1. + exp(-x)) - 1;
+    case 11: if (x < -1) return -1; if (x > 1) return 1; return x;
+    case 12: if (x < 0) return .001 * x; if (x > 1) return .001 * (x - 1) + 1; return x;
+    case 13: return (x >= 0) * 1.0507 * x + (x < 0) * 1.0507 * 1.6732 * (exp(x) - 1);
+    default: return x;
+    }
+}
+static float act_mtcs(float x, int a) {
+    switch (a) {
+    case 0: return x;
+    case 1: return x * (x > 0);
+    case 2: return (x > 0) ? x : .1f * x;
+    case 3: return 1.f / (1.f + expf(-x));
+    case 4: return fminf(fmaxf(x, 0), 6);
+    case 5: return (x > 0) ? x : .01f * x;
+    case 6: return x * (x > 0) + .1f * x;
+    case 7: return (2 / (1 + expf(-2 * x)) - 1);
+    case 8: if (x < -4) return .01f * (x + 4); if (x > 4) return .01f * (x - 4) + 1; return .125f * x + .5f;
+    case 9: return (x >= 0) * x + (x < 0) * (expf(x) - 1);
+    case 10: return 2.f / (1.f + expf(-x)) - 1;
+    case 11: if (x < -1) return -1; if (x > 1) return 1; return x;
+    case 12: if (x < 0) return .001 * x; if (x > 1) return .001 * (x - 1) + 1; return x;
+    case 13: return (x >= 0) * 1.0507f * x + (x < 0) * 1.0507f * 1.6732f * (expf(x) - 1);
+    default: return x;
+    }
+}
+static float act_grad(float x, int a) {   /* on the activation's output; the same in both back ends */
+    switch (a) {
+    case 0: return 1;
+    case 1: return (x > 0);
+    case 2: return (x > 0) ? 1 : .1;
+    case 3: return (1 - x) * x;
+    case 4: return (x > 0 && x < 6);
+    case 5: return (x > 0) ? 1 : .01;
+    case 6: return (x > 0) + .1;
+    case 7: return 1 - x * x;
+    case 8: return (x < 0 || x > 1) ? .01 : .125;
+    case 9: return (x >= 0) + (x < 0) * (x + 1);
+    case 10: { float y = (x + 1.) / 2.; return 2 * (1 - y) * y; }
+    case 11: if (x > -1 && x < 1) return 1; return 0;
+    case 12: if (x > 0 && x < 1) return 1; return .001;
+    case 13: return (x >= 0) * 1.0507 + (x < 0) * (x + 1.0507 * 1.6732);
+    default: return 1;
     }
 }
 
-/* dnn/Activation.h:87,99,104 and dnn/Activation.c:233-239: delta *= f'(output). */
+void aeto_activate(float *y, size_t count, int activation, int mode) {
+    if (activation == AETO_LINEAR) return;
+    for (size_t i = 0; i < count; ++i) y[i] = mode == AETO_MODE_CPU ? act_cpu(y[i], activation) : act_mtcs(y[i], activation);
+}
+
+/* dnn/Activation.h:87-113 and dnn/Activation.c:233-239: delta *= f'(output). */
 void aeto_gradient(const float *y, size_t count, int activation, float *delta) {
     if (activation == AETO_LINEAR) return;
-    for (size_t i = 0; i < count; ++i) {
-        float g = (activation == AETO_RELU) ? (float)(y[i] > 0) : ((y[i] > 0) ? 1.0f : .1f);
-        delta[i] *= g;
-    }
+    for (size_t i = 0; i < count; ++i) delta[i] *= act_grad(y[i], activation);
 }
 
 /* ------------------------------------------------------------------ batch norm forward
@@ -816,4 +869,238 @@ void aeto_fix_nan_and_inf(float *v, size_t n) {
 void aeto_reset_nan_and_inf(float *v, size_t n) {
     for (size_t i = 0; i < n; ++i)
         if (isnan(v[i]) || isinf(v[i])) v[i] = 0;
+}
+
+/* dnn/ConvolutionalLayer.c:983-1003 */
+void aeto_fuse_conv_batchnorm(float *biases, const float *scales, const float *rolling_mean, const float *rolling_variance,
+                              float *weights, int filters, size_t filter_size) {
+    for (int f = 0; f < filters; ++f) {
+        biases[f] = biases[f] - (double)scales[f] * rolling_mean[f] / (sqrt((double)rolling_variance[f] + .00001));
+        double precomputed = scales[f] / (sqrt((double)rolling_variance[f] + .00001));
+        for (size_t i = 0; i < filter_size; ++i) {
+            size_t w_index = (size_t)f * filter_size + i;
+            weights[w_index] *= precomputed;
+        }
+    }
+}
+
+/* dnn/DnnUtils.c:463-477 */
+void aeto_top_k(const float *a, int n, int k, int *index) {
+    int i, j;
+    for (j = 0; j < k; ++j) index[j] = -1;
+    for (i = 0; i < n; ++i) {
+        int curr = i;
+        for (j = 0; j < k; ++j) {
+            if ((index[j] < 0) || a[curr] > a[index[j]]) {
+                int swap = curr;
+                curr = index[j];
+                index[j] = swap;
+            }
+        }
+    }
+}
+
+/* dnn/ConvolutionalLayer.c:444-454 */
+void aeto_transpose_matrix(float *a, int rows, int cols) {
+    float *transpose = (float *)calloc((size_t)rows * cols, sizeof(float));
+    for (int x = 0; x < rows; ++x)
+        for (int y = 0; y < cols; ++y) transpose[(size_t)y * rows + x] = a[(size_t)x * cols + y];
+    memcpy(a, transpose, (size_t)rows * cols * sizeof(float));
+    free(transpose);
+}
+
+/* ------------------------------------------------------------------ image augmentation (dnn/NImage.c) */
+static float img_pixel_extend(const float *im, int w, int h, int c, int x, int y, int k) {   /* :138-144 */
+    if (x < 0 || x >= w || y < 0 || y >= h) return 0;
+    if (k < 0 || k >= c) return 0;
+    return im[(size_t)k * h * w + (size_t)y * w + x];
+}
+static float img_bilinear(const float *im, int w, int h, int c, float x, float y, int k) {     /* :146-157 */
+    int ix = (int)floorf(x);
+    int iy = (int)floorf(y);
+    float dx = x - ix;
+    float dy = y - iy;
+    float val = (1 - dy) * (1 - dx) * img_pixel_extend(im, w, h, c, ix, iy, k) +
+                dy * (1 - dx) * img_pixel_extend(im, w, h, c, ix, iy + 1, k) +
+                (1 - dy) * dx * img_pixel_extend(im, w, h, c, ix + 1, iy, k) +
+                dy * dx * img_pixel_extend(im, w, h, c, ix + 1, iy + 1, k);
+    return val;
+}
+static float three_way_max(float a, float b, float c) { return (a > b) ? ((a > c) ? a : c) : ((b > c) ? b : c); }
+static float three_way_min(float a, float b, float c) { return (a < b) ? ((a < c) ? a : c) : ((b < c) ? b : c); }
+
+void aeto_augment_image(const float *src, int c, int sh, int sw, float *dst, int size, float rad, float s, float dx, float dy,
+                        float aspect, int flip, float dhue, float dsat, float dexp) {
+    const int w = size, h = size;
+    /* rotateCrop :551-572 */
+    float cx = sw / 2.0;
+    float cy = sh / 2.0;
+    float cr = cos(rad);
+    float sr = sin(rad);
+    float dx1 = dx / s * aspect;
+    float dy1 = dy / s;
+    for (int k = 0; k < c; ++k)
+        for (int y = 0; y < h; ++y)
+            for (int x = 0; x < w; ++x) {
+                float rx = cr * ((x - w / 2.) / s * aspect + dx1) - sr * ((y - h / 2.) / s + dy1) + cx;
+                float ry = sr * ((x - w / 2.) / s * aspect + dx1) + cr * ((y - h / 2.) / s + dy1) + cy;
+                dst[(size_t)k * h * w + (size_t)y * w + x] = img_bilinear(src, sw, sh, c, rx, ry, k);
+            }
+    /* flip :346-362 */
+    if (flip)
+        for (int k = 0; k < c; ++k)
+            for (int i = 0; i < h; ++i)
+                for (int j = 0; j < w / 2; ++j) {
+                    size_t index = j + (size_t)w * (i + (size_t)h * k), fl = (w - j - 1) + (size_t)w * (i + (size_t)h * k);
+                    float swap = dst[fl];
+                    dst[fl] = dst[index];
+                    dst[index] = swap;
+                }
+    if (c != 3) return;
+    /* distort :323-337 */
+    const size_t wh = (size_t)w * h;
+    for (size_t p = 0; p < wh; ++p) {
+        float r = dst[p], g = dst[wh + p], b = dst[2 * wh + p];
+        float hh, ss, vv;
+        /* rgbToHsv :201-243 */
+        float max = three_way_max(r, g, b);
+        float min = three_way_min(r, g, b);
+        float delta = max - min;
+        vv = max;
+        if (max == 0) {
+            ss = 0;
+            hh = 0;
+        } else {
+            ss = delta / max;
+            if (r == max) hh = (g - b) / delta;
+            else if (g == max) hh = 2 + (b - r) / delta;
+            else hh = 4 + (r - g) / delta;
+            if (hh < 0) hh += 6;
+            hh = hh / 6.;
+        }
+        ss = ss * dsat;       /* scaleChannel(1, sat) */
+        vv = vv * dexp;       /* scaleChannel(2, val) */
+        hh = hh + dhue;
+        if (hh > 1) hh -= 1;
+        if (hh < 0) hh += 1;
+        /* hsvToRgb :245-291 */
+        float hq = 6 * hh;
+        if (ss == 0) {
+            r = g = b = vv;
+        } else {
+            int index = floor(hq);
+            float f = hq - index;
+            float pp = vv * (1 - ss);
+            float q = vv * (1 - ss * f);
+            float t = vv * (1 - ss * (1 - f));
+            if (index == 0) { r = vv; g = t; b = pp; }
+            else if (index == 1) { r = q; g = vv; b = pp; }
+            else if (index == 2) { r = pp; g = vv; b = t; }
+            else if (index == 3) { r = pp; g = q; b = vv; }
+            else if (index == 4) { r = t; g = pp; b = vv; }
+            else { r = vv; g = pp; b = q; }
+        }
+        /* constrainImage :309-318 */
+        float out[3] = {r, g, b};
+        for (int k = 0; k < 3; ++k) {
+            if (out[k] < 0) out[k] = 0;
+            if (out[k] > 1) out[k] = 1;
+            dst[k * wh + p] = out[k];
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ groups and dilation
+ * im2col_cpu_ext / col2im_cpu_ext, dnn/Im2Col.c:65-103 and :155-192. */
+static void im2col_ext(const float *data_im, int channels, int height, int width, int kernel_h, int kernel_w, int pad_h, int pad_w,
+                       int stride_h, int stride_w, int dilation_h, int dilation_w, float *data_col) {
+    const int output_h = (height + 2 * pad_h - (dilation_h * (kernel_h - 1) + 1)) / stride_h + 1;
+    const int output_w = (width + 2 * pad_w - (dilation_w * (kernel_w - 1) + 1)) / stride_w + 1;
+    const int channel_size = height * width;
+    for (int channel = channels; channel--; data_im += channel_size)
+        for (int kernel_row = 0; kernel_row < kernel_h; kernel_row++)
+            for (int kernel_col = 0; kernel_col < kernel_w; kernel_col++) {
+                int input_row = -pad_h + kernel_row * dilation_h;
+                for (int output_rows = output_h; output_rows; output_rows--) {
+                    if ((unsigned)input_row >= (unsigned)height) {
+                        for (int output_col = output_w; output_col; output_col--) *(data_col++) = 0;
+                    } else {
+                        int input_col = -pad_w + kernel_col * dilation_w;
+                        for (int output_col = output_w; output_col; output_col--) {
+                            *(data_col++) = ((unsigned)input_col < (unsigned)width) ? data_im[input_row * width + input_col] : 0;
+                            input_col += stride_w;
+                        }
+                    }
+                    input_row += stride_h;
+                }
+            }
+}
+static void col2im_ext(const float *data_col, int channels, int height, int width, int kernel_h, int kernel_w, int pad_h, int pad_w,
+                       int stride_h, int stride_w, int dilation_h, int dilation_w, float *data_im) {
+    memset(data_im, 0, sizeof(float) * (size_t)height * width * channels);
+    const int output_h = (height + 2 * pad_h - (dilation_h * (kernel_h - 1) + 1)) / stride_h + 1;
+    const int output_w = (width + 2 * pad_w - (dilation_w * (kernel_w - 1) + 1)) / stride_w + 1;
+    const int channel_size = height * width;
+    for (int channel = channels; channel--; data_im += channel_size)
+        for (int kernel_row = 0; kernel_row < kernel_h; kernel_row++)
+            for (int kernel_col = 0; kernel_col < kernel_w; kernel_col++) {
+                int input_row = -pad_h + kernel_row * dilation_h;
+                for (int output_rows = output_h; output_rows; output_rows--) {
+                    if ((unsigned)input_row >= (unsigned)height) {
+                        data_col += output_w;
+                    } else {
+                        int input_col = -pad_w + kernel_col * dilation_w;
+                        for (int output_col = output_w; output_col; output_col--) {
+                            if ((unsigned)input_col < (unsigned)width) data_im[input_row * width + input_col] += *data_col;
+                            data_col++;
+                            input_col += stride_w;
+                        }
+                    }
+                    input_row += stride_h;
+                }
+            }
+}
+
+/* dnn/ConvolutionalLayer.c:703-806, FP32 branch */
+void aeto_conv_forward_ex(const float *x, const float *weights, float *y, float *workspace, int batch, int c, int h, int w,
+                          int nf, int size, int stride_x, int stride_y, int pad, int groups, int dilation) {
+    const int out_h = aeto_conv_out(h, size, stride_y, pad), out_w = aeto_conv_out(w, size, stride_x, pad);
+    const int m = nf / groups, k = size * size * c / groups, n = out_h * out_w;
+    const size_t nweights = (size_t)nf * k;
+    memset(y, 0, sizeof(float) * (size_t)batch * nf * n);
+    for (int i = 0; i < batch; ++i)
+        for (int j = 0; j < groups; ++j) {
+            const float *im = x + (size_t)(i * groups + j) * (c / groups) * h * w;
+            const float *a = weights + j * nweights / groups;
+            const float *b = im;
+            float *cc = y + (size_t)(i * groups + j) * n * m;
+            if (!(size == 1 && stride_x == 1 && stride_y == 1 && dilation == 1)) {
+                im2col_ext(im, c / groups, h, w, size, size, pad * dilation, pad * dilation, stride_y, stride_x, dilation, dilation, workspace);
+                b = workspace;
+            }
+            aeto_gemm(0, 0, m, n, k, 1, a, k, b, n, 1, cc, n);
+        }
+}
+
+/* dnn/ConvolutionalLayer.c:909-947 */
+void aeto_conv_backward_ex(const float *x, const float *weights, const float *delta, float *dw, float *dx, float *workspace,
+                           int batch, int c, int h, int w, int nf, int size, int stride_x, int stride_y, int pad, int groups,
+                           int dilation) {
+    const int out_h = aeto_conv_out(h, size, stride_y, pad), out_w = aeto_conv_out(w, size, stride_x, pad);
+    const int m = nf / groups, n = size * size * c / groups, k = out_h * out_w;
+    const size_t nweights = (size_t)nf * n;
+    for (int i = 0; i < batch; ++i)
+        for (int j = 0; j < groups; ++j) {
+            const float *a = delta + (size_t)(i * groups + j) * m * k;
+            float *cc = dw + j * nweights / groups;
+            const float *im = x + (size_t)(i * groups + j) * (c / groups) * h * w;
+            im2col_ext(im, c / groups, h, w, size, size, pad * dilation, pad * dilation, stride_y, stride_x, dilation, dilation, workspace);
+            aeto_gemm(0, 1, m, n, k, 1, a, k, workspace, k, 1, cc, n);
+            if (dx) {
+                const float *wa = weights + j * nweights / groups;
+                aeto_gemm(1, 0, n, k, m, 1, wa, n, a, k, 0, workspace, k);
+                col2im_ext(workspace, c / groups, h, w, size, size, pad * dilation, pad * dilation, stride_y, stride_x, dilation, dilation,
+                           dx + (size_t)(i * groups + j) * (c / groups) * h * w);
+            }
+        }
 }

@@ -118,6 +118,31 @@ float  aeto_current_rate(size_t batch_num, int policy, float learning_rate, int 
 void   aeto_fix_nan_and_inf(float *v, size_t n);
 void   aeto_reset_nan_and_inf(float *v, size_t n);
 
+/* ConvolutionalLayer.fuseConvBatchnorm, dnn/ConvolutionalLayer.c:983-1003: folds the rolling statistics and the
+ * scale into biases and weights (inference). */
+void   aeto_fuse_conv_batchnorm(float *biases, const float *scales, const float *rolling_mean, const float *rolling_variance,
+                                float *weights, int filters, size_t filter_size);
+/* DnnUtils.topK, dnn/DnnUtils.c:463-477: indexes of the k largest of a[0..n) in descending order (strict >). */
+void   aeto_top_k(const float *a, int n, int k, int *index);
+/* ConvolutionalLayer.transposeMatrix, dnn/ConvolutionalLayer.c:444-454 (the `flipped` weights layout). */
+void   aeto_transpose_matrix(float *a, int rows, int cols);
+
+/* The per-image augmentation chain of ImageData.loadImageAugmentPaths (dnn/ImageData.c:56-73) with its random draws
+ * given as inputs: NImage.rotateCrop (dnn/NImage.c:551-572, bilinear sampling :138-157) into a size x size crop,
+ * NImage.flip (:346-362) when `flip`, NImage.distort (:323-337: RGB->HSV :201-243, scale S and V, shift hue,
+ * HSV->RGB :245-291, clamp to [0,1]) for 3-channel images.  src [c][sh][sw] -> dst [c][size][size]. */
+void   aeto_augment_image(const float *src, int c, int sh, int sw, float *dst, int size, float rad, float scale, float dx, float dy,
+                          float aspect, int flip, float dhue, float dsat, float dexp);
+
+/* Convolution with channel groups and dilated taps: dnn/ConvolutionalLayer.c:703-806 (forward) and :909-947 (backward)
+ * with im2col_cpu_ext / col2im_cpu_ext (dnn/Im2Col.c:65-103,155-192; padding in pixels = pad * dilation).
+ * weights [n][c/groups][size][size].  The output size is the layer's own formula (aeto_conv_out with `pad`). */
+void   aeto_conv_forward_ex(const float *x, const float *weights, float *y, float *workspace, int batch, int c, int h, int w,
+                            int n, int size, int stride_x, int stride_y, int pad, int groups, int dilation);
+void   aeto_conv_backward_ex(const float *x, const float *weights, const float *delta, float *dw, float *dx, float *workspace,
+                             int batch, int c, int h, int w, int n, int size, int stride_x, int stride_y, int pad, int groups,
+                             int dilation);
+
 /* synthetic tensors (aet_rng.h) exposed for bindings */
 void aeto_fill_uniform(float *dst, size_t n, uint64_t seed, uint64_t tensor_id);
 void aeto_fill_normal(float *dst, size_t n, uint64_t seed, uint64_t tensor_id, float mean, float stddev);

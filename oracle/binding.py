@@ -10,7 +10,7 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LINEAR, RELU, LEAKY = 0, 1, 2
+LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU = range(14)
 MODE_CPU, MODE_MTCS = 0, 1
 CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
 (P_WEIGHTS, P_WEIGHT_UPDATES, P_BIASES, P_BIAS_UPDATES, P_SCALES, P_SCALE_UPDATES, P_ROLLING_MEAN,
@@ -58,6 +58,8 @@ class Oracle:
         L.aeto_conv_workspace.restype = C.c_size_t
         L.aeto_conv_forward.argtypes = [_f, _f, _f, _f] + [C.c_int] * 9
         L.aeto_conv_backward.argtypes = [_f, _f, _f, _f, _f, _f] + [C.c_int] * 9
+        L.aeto_conv_forward_ex.argtypes = [_f, _f, _f, _f] + [C.c_int] * 11
+        L.aeto_conv_backward_ex.argtypes = [_f, _f, _f, _f, _f, _f] + [C.c_int] * 11
         L.aeto_add_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.aeto_backward_bias.argtypes = [_f, _f, C.c_int, C.c_int, C.c_int]
         L.aeto_activate.argtypes = [_f, C.c_size_t, C.c_int, C.c_int]
@@ -94,6 +96,10 @@ class Oracle:
         L.aeto_current_rate.restype = C.c_float
         L.aeto_fix_nan_and_inf.argtypes = [_f, C.c_size_t]
         L.aeto_reset_nan_and_inf.argtypes = [_f, C.c_size_t]
+        L.aeto_fuse_conv_batchnorm.argtypes = [_f, _f, _f, _f, _f, C.c_int, C.c_size_t]
+        L.aeto_top_k.argtypes = [_f, C.c_int, C.c_int, _i]
+        L.aeto_transpose_matrix.argtypes = [_f, C.c_int, C.c_int]
+        L.aeto_augment_image.argtypes = [_f, C.c_int, C.c_int, C.c_int, _f, C.c_int] + [C.c_float] * 5 + [C.c_int] + [C.c_float] * 3
         L.aeto_fill_uniform.argtypes = [_f, C.c_size_t, C.c_uint64, C.c_uint64]
         L.aeto_fill_normal.argtypes = [_f, C.c_size_t, C.c_uint64, C.c_uint64, C.c_float, C.c_float]
 
@@ -112,7 +118,7 @@ class Oracle:
     def conv_out(self, n, size, stride, pad):
         return self.lib.aeto_conv_out(n, size, stride, pad)
 
-    def conv_forward(self, x, w, stride_x=1, stride_y=None, pad=0):
+    def conv_forward(self, x, w, stride_x=1, stride_y=None, pad=0, groups=1, dilation=1):
         stride_y = stride_x if stride_y is None else stride_y
         x, w = _arr(x), _arr(w)
         b, c, h, wd = x.shape
@@ -120,10 +126,13 @@ class Oracle:
         oh, ow = self.conv_out(h, size, stride_y, pad), self.conv_out(wd, size, stride_x, pad)
         y = np.zeros((b, n, oh, ow), np.float32)
         ws = np.zeros(max(1, self.lib.aeto_conv_workspace(c, h, wd, size, stride_x, stride_y, pad)), np.float32)
-        self.lib.aeto_conv_forward(_fp(x), _fp(w), _fp(y), _fp(ws), b, c, h, wd, n, size, stride_x, stride_y, pad)
+        if groups == 1 and dilation == 1:
+            self.lib.aeto_conv_forward(_fp(x), _fp(w), _fp(y), _fp(ws), b, c, h, wd, n, size, stride_x, stride_y, pad)
+        else:
+            self.lib.aeto_conv_forward_ex(_fp(x), _fp(w), _fp(y), _fp(ws), b, c, h, wd, n, size, stride_x, stride_y, pad, groups, dilation)
         return y
 
-    def conv_backward(self, x, w, delta, stride_x=1, stride_y=None, pad=0, dw=None, need_dx=True):
+    def conv_backward(self, x, w, delta, stride_x=1, stride_y=None, pad=0, dw=None, need_dx=True, groups=1, dilation=1):
         stride_y = stride_x if stride_y is None else stride_y
         x, w, delta = _arr(x), _arr(w), _arr(delta)
         b, c, h, wd = x.shape
@@ -131,8 +140,12 @@ class Oracle:
         dw = np.zeros_like(w) if dw is None else _arr(dw).copy()
         dx = np.zeros_like(x) if need_dx else None
         ws = np.zeros(max(1, self.lib.aeto_conv_workspace(c, h, wd, size, stride_x, stride_y, pad)), np.float32)
-        self.lib.aeto_conv_backward(_fp(x), _fp(w), _fp(delta), _fp(dw), _fp(dx) if need_dx else None, _fp(ws),
-                                    b, c, h, wd, n, size, stride_x, stride_y, pad)
+        if groups == 1 and dilation == 1:
+            self.lib.aeto_conv_backward(_fp(x), _fp(w), _fp(delta), _fp(dw), _fp(dx) if need_dx else None, _fp(ws),
+                                        b, c, h, wd, n, size, stride_x, stride_y, pad)
+        else:
+            self.lib.aeto_conv_backward_ex(_fp(x), _fp(w), _fp(delta), _fp(dw), _fp(dx) if need_dx else None, _fp(ws),
+                                           b, c, h, wd, n, size, stride_x, stride_y, pad, groups, dilation)
         return dw, dx
 
     def add_bias(self, y, b):
@@ -246,6 +259,32 @@ class Oracle:
         v = _arr(v).copy().reshape(-1)
         self.lib.aeto_reset_nan_and_inf(_fp(v), v.size)
         return v
+
+    def fuse_conv_batchnorm(self, biases, scales, rolling_mean, rolling_variance, weights):
+        """Returns (biases, weights) after ConvolutionalLayer.fuseConvBatchnorm; weights [filters][...]."""
+        b, w = _arr(biases).copy(), _arr(weights).copy()
+        self.lib.aeto_fuse_conv_batchnorm(_fp(b), _fp(_arr(scales)), _fp(_arr(rolling_mean)), _fp(_arr(rolling_variance)),
+                                          _fp(w), b.size, w.size // b.size)
+        return b, w
+
+    def top_k(self, a, k):
+        a = _arr(a).reshape(-1)
+        idx = np.zeros(k, np.int32)
+        self.lib.aeto_top_k(_fp(a), a.size, k, idx.ctypes.data_as(_i))
+        return idx
+
+    def transpose_matrix(self, a, rows, cols):
+        a = _arr(a).copy().reshape(-1)
+        self.lib.aeto_transpose_matrix(_fp(a), rows, cols)
+        return a
+
+    def augment_image(self, src, size, rad, scale, dx, dy, aspect, flip, dhue, dsat, dexp):
+        """rotateCrop + flip + distort of one image [c][sh][sw] into [c][size][size] (dnn/NImage.c)."""
+        src = _arr(src)
+        c, sh, sw = src.shape
+        dst = np.zeros((c, size, size), np.float32)
+        self.lib.aeto_augment_image(_fp(src), c, sh, sw, _fp(dst), size, rad, scale, dx, dy, aspect, int(flip), dhue, dsat, dexp)
+        return dst
 
     def dropout_forward(self, x, r, probability):
         x = _arr(x).copy()

@@ -3,7 +3,8 @@ defaults as the library's C reader, which follows dnn/NetworkFactory.c:77-173,32
 Describes a network to the CPU oracle (tests, the smoke check and the benchmark's CPU-baseline legs);
 the product package never imports it."""
 
-ACT = {"linear": 0, "relu": 1, "leaky": 2}
+ACT = {"linear": 0, "relu": 1, "leaky": 2, "logistic": 3, "relu6": 4, "relie": 5, "ramp": 6, "tanh": 7, "plse": 8, "elu": 9,
+       "loggy": 10, "hardtan": 11, "lhtan": 12, "selu": 13}
 CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
 
 

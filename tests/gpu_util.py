@@ -36,17 +36,18 @@ def oracle_conv_backward_mt(oracle, x, w, d, stride, pad, need_dx=True):
     return dw.astype(np.float32), (np.concatenate([r[1] for r in rs], 0) if need_dx else None)
 
 
-def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bias=True, want_dx=True, threads=False):
+def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bias=True, want_dx=True, threads=False, groups=1,
+              dilation=1):
     """Forward + backward of one convolution (no BN) on the GPU and in the oracle; returns both result dicts.
     threads=True runs the oracle's per-image loops over batch slices on all host cores (full-size cases)."""
     import aet_cnn_b200.synth as synth
     oh, ow = (H + 2 * pad - size) // stride + 1, (W + 2 * pad - size) // stride + 1
     x = synth.uniform((N, C, H, W), seed, 1)
-    w = synth.normal((K, C, size, size), seed, 2, 0.0, float(np.sqrt(2.0 / (size * size * C))))
+    w = synth.normal((K, C // groups, size, size), seed, 2, 0.0, float(np.sqrt(2.0 / (size * size * C // groups))))
     b = synth.normal((K,), seed, 3, 0.0, 0.1) if bias else np.zeros(K, np.float32)
     dy = synth.normal((N, K, oh, ow), seed, 4)
 
-    layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, size, stride, stride, pad, act, 0, 1)
+    layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, size, stride, stride, pad, act, 0, 1, groups=groups, dilation=dilation)
     layer.write(aet.P_WEIGHTS, w)
     layer.write(aet.P_BIASES, b)
     xin = aet.Tensor(ctx, N, C, H, W)
@@ -66,7 +67,10 @@ def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bia
         dxt.close()
 
     mode = ob.MODE_MTCS
-    conv = oracle_conv_forward_mt(oracle, x, w, stride, pad) if threads else oracle.conv_forward(x, w, stride, stride, pad)
+    if threads:
+        conv = oracle_conv_forward_mt(oracle, x, w, stride, pad)
+    else:
+        conv = oracle.conv_forward(x, w, stride, stride, pad, groups=groups, dilation=dilation)
     y = oracle.activate(oracle.add_bias(conv, b), act, mode)
     # The activation gradient is a step function of the layer's stored output.  Backward parity is
     # taken on identical inputs, so the mask comes from the output the device stored: a TF32-rounded
@@ -76,7 +80,7 @@ def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bia
     if threads:
         dw, dx = oracle_conv_backward_mt(oracle, x, w, d, stride, pad, need_dx=want_dx)
     else:
-        dw, dx = oracle.conv_backward(x, w, d, stride, stride, pad, need_dx=want_dx)
+        dw, dx = oracle.conv_backward(x, w, d, stride, stride, pad, need_dx=want_dx, groups=groups, dilation=dilation)
     ref = dict(y=y, dw=dw, dx=dx, db=oracle.backward_bias(d))
     return got, ref
 

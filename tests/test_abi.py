@@ -53,8 +53,10 @@ def test_cfg_reader_defaults(aet):
     assert layers[1]["pad"] == 1            # maxpool default padding = size - 1
     net2, _ = cfgfile.network_spec("[net]\nbatch=64\nsubdivisions=4\nchannels=3\nheight=8\nwidth=8\n")
     assert net2["batch"] == 16              # [net] batch is divided by subdivisions
+    _, dl = cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\n")
+    assert dl[0]["activation"] == 3         # the reference's default activation is logistic (dnn/NetworkFactory.c:103)
     with pytest.raises(KeyError):
-        cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\n")  # default activation = logistic
+        cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\nactivation=mish\n")
     anet, alayers = cfgfile.network_spec(open(os.path.join(aet.CFG_DIR, "alexnet_style.cfg")).read())
     assert sum(1 for l in alayers if l["type"] == 0) == 8 and alayers[1]["pad"] == 0
 

@@ -123,26 +123,34 @@ def test_conv_thin_tf32(aet, ctx, oracle, shape):
 # split over a two-CTA cluster, two filter tiles), so these shapes are checked at that size and the path each
 # launch took is asserted by its label.  N = 112 is the smallest batch above the two-tile threshold.
 BENCH_SHAPES = [
-    # shape, {kernel: variant} expected on a 148-SM part
-    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1",
-                                          "conv_wgrad_tma_rows": "n64_sp49"}),
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2",
-                                         "conv_wgrad_tma_rows": "n128_sp24"}),
-    ((112, 64, 16, 16, 128, 3, 1, 1, 0), {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
+    # shape, CTA pairs on/off, {kernel: variant} expected on a 148-SM part
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), 1, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2",
+                                             "conv_wgrad_tma_rows": "n64_sp49"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), 1, {"conv_fprop_tma_rows": "mt1_n128x2_p2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2_p2",
+                                            "conv_wgrad_tma_rows": "n128_sp24"}),
+    ((112, 64, 16, 16, 128, 3, 1, 1, 0), 1, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2"}),
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), 0, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), 0, {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2"}),
+    ((16, 64, 16, 16, 128, 3, 1, 1, 1), 1, {"conv_fprop_tma_rows": "*_p2", "conv_dgrad_tma_rows": "*_p2"}),    # pairs at a small batch
 ]
 
 
-@pytest.mark.parametrize("shape,variants", BENCH_SHAPES)
-def test_conv_benchmark_shapes_at_benchmark_batch(aet, ctx, oracle, shape, variants):
+@pytest.mark.parametrize("shape,pair,variants", BENCH_SHAPES)
+def test_conv_benchmark_shapes_at_benchmark_batch(aet, ctx, oracle, shape, pair, variants):
     ctx.set_math(aet.MATH_TF32)
+    ctx.set_option("pair", pair)
     ctx.profile(1)
     try:
         got, ref = conv_case(aet, ctx, oracle, *shape, seed=500 + shape[0], threads=True)
         used = variants_used(ctx)
     finally:
         ctx.profile(0)
+        ctx.set_option("pair", 1)
     for kernel, variant in variants.items():
-        assert kernel + "." + variant in used, (kernel, variant, sorted(used))
+        if variant.startswith("*"):
+            assert any(u.startswith(kernel + ".") and u.endswith(variant[1:]) for u in used), (kernel, variant, sorted(used))
+        else:
+            assert kernel + "." + variant in used, (kernel, variant, sorted(used))
     check(got, ref, TOL_TF32)
 
 
@@ -171,6 +179,56 @@ def test_conv_sweep_shapes_at_batch_256(aet, ctx, oracle, shape):
     allowed = {"conv_dgrad_gather"} if shape[1] < 32 else set()
     assert not any("gather" in k for k in used - allowed), used
     check(got, ref, TOL_TF32)
+
+
+# every activation whose gradient is a function of its output (dnn/Activation.h:41-113), numbered as in the C ABI
+ACTIVATIONS = list(range(3, 14))
+
+
+@pytest.mark.parametrize("act", ACTIVATIONS)
+def test_conv_activation_family(aet, ctx, oracle, act):
+    """Forward value and the gradient through the activation (evaluated on the stored output) for the activations
+    beyond linear / relu / leaky, in a convolution's epilogue and backward kernels, TMA and gather producers."""
+    for shape in [(4, 32, 8, 8, 32, 3, 1, 1), (2, 3, 9, 7, 6, 3, 2, 1)]:
+        got, ref = conv_case(aet, ctx, oracle, *shape, act, seed=700 + act)
+        check(got, ref, TOL_TF32)
+
+
+def test_conv_bn_with_logistic_and_elu_matches_oracle_network(aet, ctx, oracle64):
+    """BN layers recompute the activation and its gradient from the saved convolution result: a two-layer network with
+    logistic and elu activations against the oracle, 3xTF32 math."""
+    import aet_cnn_b200.synth as synth
+    from oracle import binding as ob
+    from oracle import cfgfile
+    text = ("[net]\nbatch=4\nheight=8\nwidth=8\nchannels=3\nlearning_rate=0.01\nmomentum=0.9\ndecay=0.0005\n"
+            "[convolutional]\nfilters=8\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=logistic\n"
+            "[maxpool]\nsize=2\nstride=2\n"
+            "[convolutional]\nfilters=12\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=elu\n"
+            "[convolutional]\nfilters=5\nsize=1\nstride=1\npad=0\nactivation=tanh\n[avgpool]\n[softmax]\n")
+    opts, specs = cfgfile.network_spec(text)
+    ctx.set_math(aet.MATH_3XTF32)
+    try:
+        net = aet.NNetwork(ctx, cfg_text=text, train=1)
+        onet = oracle64.net(specs, 4, 3, 8, 8, mode=ob.MODE_MTCS)
+        cin = 3
+        for i, s in enumerate(specs):
+            if s["type"] == cfgfile.CONV:
+                w = synth.normal((s["filters"], cin, s["size"], s["size"]), 13, 50 + i, 0.0, 0.3)
+                net.layer(i).write(aet.P_WEIGHTS, w); onet.set_param(i, ob.P_WEIGHTS, w)
+                cin = s["filters"]
+        for step in range(3):
+            x = synth.uniform((4, 3, 8, 8), 13, 2 * step)
+            _, t = synth.labels(4, 5, 13, 2 * step + 1)
+            loss = net.train(x, t)
+            oloss = onet.train_step(x, t, opts["learning_rate"], opts["momentum"], opts["decay"])
+            assert abs(loss - oloss) <= 1e-4 * abs(oloss), (step, loss, oloss)
+        for i, s in enumerate(specs):
+            if s["type"] == cfgfile.CONV:
+                assert rel_l2(net.layer(i).read(aet.P_WEIGHTS), onet.param(i, ob.P_WEIGHTS)) < 1e-4, i
+        ctx.check()
+        net.close()
+    finally:
+        ctx.set_math(aet.MATH_TF32)
 
 
 def test_tma_and_gather_agree_closely(aet, ctx, ctx_gather, oracle):
@@ -208,9 +266,34 @@ def test_reference_single_conv_case_full_size(aet, ctx, oracle):
     check(got, ref, TOL_TF32)
 
 
+# (N, C, H, W, K, size, stride, pad, act, groups, dilation)
+GROUP_DILATION_SHAPES = [
+    None,
+    (2, 16, 8, 8, 16, 3, 1, 1, 1, 4, 1),       # four groups of 4 channels -> 4 filters
+    (2, 64, 8, 8, 64, 3, 1, 1, 2, 2, 1),       # two groups of 32 -> 32
+    (2, 16, 6, 6, 32, 1, 1, 0, 0, 2, 1),       # grouped 1x1
+    (2, 8, 8, 8, 8, 3, 2, 1, 1, 2, 1),         # grouped, stride 2
+    (2, 4, 12, 12, 8, 3, 1, 1, 2, 1, 2),       # dilation 2
+    (2, 32, 10, 10, 32, 3, 1, 1, 0, 1, 3),     # dilation 3 on a TMA-eligible channel count (runs on the gather producer)
+    (2, 16, 11, 9, 16, 5, 1, 2, 1, 2, 2),      # groups and dilation together, 5x5
+]
+
+
+@pytest.mark.parametrize("shape", GROUP_DILATION_SHAPES[1:])
+def test_conv_groups_and_dilation(aet, ctx, oracle, shape):
+    """Channel groups (dnn/ConvolutionalLayer.c:716-722) and dilated taps (dnn/Im2Col.c:65-103): output, dX, dW, db."""
+    *base, groups, dilation = shape
+    got, ref = conv_case(aet, ctx, oracle, *base, seed=800 + base[1] + groups, groups=groups, dilation=dilation)
+    check(got, ref, TOL_TF32)
+
+
 def test_bad_arguments_are_rejected(aet, ctx):
     with pytest.raises(aet.AetError):
-        aet.ConvolutionalLayer(ctx, 1, 8, 8, 3, 4, 3, groups=2)
+        aet.ConvolutionalLayer(ctx, 1, 8, 8, 3, 4, 3, groups=2)                # 3 channels do not split in two
+    with pytest.raises(aet.AetError):
+        aet.ConvolutionalLayer(ctx, 1, 8, 8, 8, 12, 3, groups=2)               # 6 filters per group: not a multiple of 4
+    with pytest.raises(aet.AetError):
+        aet.ConvolutionalLayer(ctx, 1, 8, 8, 8, 8, 4, 1, 1, 1, dilation=2)     # dilation needs an odd filter padded by size/2
     with pytest.raises(aet.AetError):
         aet.ConvolutionalLayer(ctx, 1, 2, 2, 3, 4, 5)                   # empty output
     layer = aet.ConvolutionalLayer(ctx, 1, 8, 8, 3, 4, 3, 1, 1, 1)

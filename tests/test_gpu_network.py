@@ -91,8 +91,8 @@ def test_small_cnn_training_matches_oracle(aet, ctx, oracle64, mode):
 
 
 # code path of every row-sharing launch of the small CNN at the benchmark batch on a 148-SM part
-BENCH_VARIANTS = {"conv_fprop_tma_rows.mt2e_n128x1#2", "conv_dgrad_tma_rows.sm_mt2_n192x1#2", "conv_wgrad_tma_rows.n64_sp49#2",
-                  "conv_fprop_tma_rows.mt1_n128x2#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
+BENCH_VARIANTS = {"conv_fprop_tma_rows.mt2e_n128x1_p2#2", "conv_dgrad_tma_rows.sm_mt2_n192x1_p2#2", "conv_wgrad_tma_rows.n64_sp49#2",
+                  "conv_fprop_tma_rows.mt1_n128x2_p2#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2_p2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
 
 
 @pytest.mark.parametrize("batch", [16, 128])
@@ -311,7 +311,7 @@ def test_weights_file_roundtrip_and_layout(aet, ctx, oracle):
 
 def test_bad_cfg_is_rejected(aet, ctx):
     for text in ["[convolutional]\nfilters=2\n",
-                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\n",          # logistic default
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\nactivation=mish\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[yolo]\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nactivation=leaky\nxnor=1\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[softmax]\n"]:

@@ -220,6 +220,37 @@ def test_pipelined_train_step_is_the_synchronous_step_with_the_loss_one_call_lat
         net.close()
 
 
+@pytest.mark.parametrize("channels", [3, 1])
+def test_device_augmentation_matches_the_reference_chain(aet, ctx, oracle, channels):
+    """rotate/scale/shift crop with bilinear sampling, left-right flip and HSV distortion (dnn/NImage.c) fused in one
+    kernel that writes the network input, against the oracle's restatement image by image.  The draws are inputs on
+    both sides.  Values are in [0,1]; float arithmetic in the same order, so the bound is a few ulps of 1."""
+    import aet_cnn_b200.synth as synth
+    batch, size, sh, sw = 6, 8, 19, 23
+    text = tiny_cfg(batch=batch).replace("channels=3", "channels=%d" % channels)
+    net = aet.NNetwork(ctx, cfg_text=text, train=1)
+    src = synth.uniform((batch, channels, sh, sw), 77, 1)
+    rng = np.random.default_rng(5)
+    params = []
+    for b in range(batch):
+        params.append(dict(rad=float(rng.uniform(-0.4, 0.4)) if b else 0.0, scale=float(rng.uniform(0.4, 1.3)),
+                           dx=float(rng.uniform(-3, 3)), dy=float(rng.uniform(-3, 3)), aspect=float(rng.uniform(0.8, 1.25)),
+                           flip=int(b % 2), dhue=float(rng.uniform(-0.1, 0.1)), dsat=float(rng.uniform(0.7, 1.5)),
+                           dexp=float(rng.uniform(0.7, 1.5))))
+    net.augment_input(src, params)
+    got = net.input.read()
+    for b in range(batch):
+        want = oracle.augment_image(src[b], size, **params[b])
+        assert np.abs(got[b] - want).max() < 2e-6, (b, np.abs(got[b] - want).max())
+    assert got.min() >= 0.0 and (channels != 3 or got.max() <= 1.0)
+    # the augmented batch trains like any other input
+    _, t = synth.labels(batch, 5, 77, 2)
+    net.truth.write(t)
+    loss = net.train_device()
+    assert np.isfinite(loss)
+    net.close()
+
+
 def test_option_switches(aet, ctx):
     assert ctx.get_option("rows") == 1
     ctx.set_option("rows", 0)

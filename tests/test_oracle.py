@@ -259,3 +259,13 @@ def test_non_finite_scrub_known_values(oracle):
     v = np.array([1.0, np.nan, -np.inf, 2.0], np.float32)
     assert np.array_equal(oracle.reset_nan_and_inf(v), np.array([1.0, 0.0, 0.0, 2.0], np.float32))
     assert np.array_equal(oracle.fix_nan_and_inf(v), np.array([1.0, 0.5, 1.0 / 3.0, 2.0], np.float32))
+
+
+def test_inference_helpers_known_values(oracle):
+    """fuseConvBatchnorm, topK and transposeMatrix on hand-computed cases."""
+    b, w = oracle.fuse_conv_batchnorm([1.0, -2.0], [2.0, 0.5], [0.5, 1.0], [3.99999, 0.24999], np.array([[1.0, 2.0], [4.0, -8.0]], np.float32))
+    assert np.allclose(b, [1.0 - 2.0 * 0.5 / 2.0, -2.0 - 0.5 * 1.0 / 0.5], rtol=1e-6)
+    assert np.allclose(w, [[1.0, 2.0], [4.0, -8.0]], rtol=1e-6)              # scale / sqrt(var + 1e-5) = 1 for both filters
+    assert list(oracle.top_k(np.array([0.1, 0.7, 0.05, 0.15], np.float32), 2)) == [1, 3]
+    assert list(oracle.top_k(np.array([0.2, 0.2, 0.6], np.float32), 3)) == [2, 1, 0]      # a displaced entry falls behind its equals
+    assert list(oracle.transpose_matrix([1, 2, 3, 4, 5, 6], 2, 3)) == [1, 4, 2, 5, 3, 6]
