@@ -62,7 +62,7 @@ class Augment(C.Structure):
 
 class KernelTime(C.Structure):
     _fields_ = [("name", C.c_char * 48), ("launches", C.c_int), ("total_ms", C.c_double), ("algo_bytes", C.c_double),
-                ("algo_flops", C.c_double)]
+                ("algo_flops", C.c_double), ("span_ms", C.c_double)]
 
 
 _lib = None
@@ -203,7 +203,7 @@ class Context:
         tab = (KernelTime * capacity)()
         n = C.c_int()
         _check(self.L.aet_context_profile_read(self.h, tab, capacity, C.byref(n)))
-        return [dict(name=t.name.decode(), launches=t.launches, total_ms=t.total_ms, algo_bytes=t.algo_bytes,
+        return [dict(name=t.name.decode(), launches=t.launches, total_ms=t.total_ms, span_ms=t.span_ms, algo_bytes=t.algo_bytes,
                      algo_flops=t.algo_flops) for t in tab[:n.value]]
 
     def launch_count(self):
@@ -496,7 +496,7 @@ class NNetwork:
         tab = (KernelTime * capacity)()
         n = C.c_int()
         _check(self.L.aet_network_profile_read(self.h, tab, capacity, C.byref(n)))
-        return [dict(name=t.name.decode(), launches=t.launches, total_ms=t.total_ms, algo_bytes=t.algo_bytes,
+        return [dict(name=t.name.decode(), launches=t.launches, total_ms=t.total_ms, span_ms=t.span_ms, algo_bytes=t.algo_bytes,
                      algo_flops=t.algo_flops) for t in tab[:n.value]]
 
     def launches_per_step(self):

@@ -18,7 +18,7 @@
 // bits of the device status word
 #define AET_STATUS_TIMEOUT 1   // a bounded wait expired
 #define AET_STATUS_NAN 2       // the update found (and scrubbed) non-finite values
-constexpr int kPinnedFloats = 64;
+constexpr int kPinnedFloats = 16 + 8 * 8;
 constexpr int kHyperSlots = 8;
 
 void aet_set_error(const char *fmt, ...);
@@ -41,7 +41,12 @@ void aet_set_error(const char *fmt, ...);
 static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 static inline size_t round_up_sz(size_t v, size_t m) { return (v + m - 1) / m * m; }
 
+// Device-side duration of a profiled launch: the kernels that support it record the earliest entry and the latest
+// exit of their CTAs (%globaltimer) in a slot of this array, so that the table can show, beside the event-bracketed
+// time of a launch, how long its CTAs were actually on the machine.
+constexpr int kMaxSpanSlots = 4096;
 struct ProfileRecord {
+    int span_slot;        // index into the context's span array, or -1
     char name[40];        // kernel label, with ".variant" appended when the launcher chose among code paths
     int tag;              // index of the network layer the launch belongs to, or -1
     double bytes, flops;
@@ -70,8 +75,10 @@ enum AetOption {
     OPT_LINEAR_HEAD,       // classifier head on the pooled vectors, read when a network is built          AET_NO_LINEAR_HEAD
     OPT_XCHG_CAP_FLOATS,   // capacity of the peer-exchange buffer (0 = default)   AET_XCHG_CAP_FLOATS
     OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice)   AET_NCCL_MAX_CTAS
+    OPT_DUAL_ACC,          // two accumulators per tile when a CTA owns one tile (row-sharing kernels; off by default)   AET_DUAL_ACC
     OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
-    OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels   AET_NO_PAIR
+    OPT_STEM,              // first convolution + BN + 2x2 max-pool: weight gradient from the pool-sized tensors   AET_NO_STEM
+    OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels; off by default   AET_PAIR
     OPT_COUNT
 };
 
@@ -106,6 +113,8 @@ struct aet_context {
     size_t scratch_side_bytes = 0;
     // profiling
     bool profiling = false;
+    unsigned long long *span_dev = nullptr;   // [kMaxSpanSlots][2]: first CTA entry, last CTA exit (ns)
+    unsigned long long *span_ptr = nullptr;   // slot of the launch being issued (null: not profiling / table full)
     std::vector<ProfileRecord> records;
     std::vector<cudaEvent_t> event_pool;
     size_t event_next = 0;
@@ -135,6 +144,7 @@ struct ParamSegment {
 
 struct ParamArena {
     float *W = nullptr, *U = nullptr, *G = nullptr;  // values, momentum, per-step gradient
+    float *M = nullptr, *V = nullptr;                // Adam's first and second moments (allocated for adam=1 networks)
     size_t capacity = 0, used = 0;
     bool owns = false;
 };
@@ -201,6 +211,19 @@ struct aet_layer {
     unsigned int *lin_ticket = nullptr;
     bool head_forward_pending = false;  // avg-pool: forward deferred to the softmax layer's fused kernel
     bool head_backward_done = false;    // avg-pool / conv: delta (and bias gradient) already produced
+    // First convolution of an image network with BN and a fused 2x2 max-pool (network training passes): the weight
+    // gradient is formed from the pool-sized tensors and the Gram matrix of the input patches; the full-resolution
+    // delta is never written.
+    bool stem = false;               // eligible (set when the network is wired)
+    bool stem_gram_ready = false;    // this pass's Gram matrix is queued (on the side stream when the pass overlaps)
+    bool stem_delta_stale = false;   // delta tensor not formed (a host tap runs the BN backward apply pass)
+    float *stem_ymax = nullptr;      // [batch][pool oh][pool ow][ocp] convolution result at each window's argmax
+    unsigned char *stem_code = nullptr;   // same shape: the argmax's position inside its window (0..3 row-major, 4: none)
+    int stem_resident = 0;           // resident blocks per SM of the pool-sized pass (queried once)
+    float *stem_partial = nullptr;   // per block: BN sums [2][ocp], then first-term sums [ocp][36]
+    float *stem_gram_partial = nullptr;   // per-block Gram sums [blocks][81][16]
+    double *stem_gram = nullptr;          // Gram sums over the batch [81][16]
+    int stem_blocks = 0, stem_blocks_used = 0, stem_gram_blocks = 0;
     // TMA descriptors are built lazily per (layer, pass, operand address)
     void *tma_cache = nullptr;
 };
@@ -225,8 +248,10 @@ struct aet_network {
     int *block_seg = nullptr;    // per 1024-float block: segment id
     float *seg_table = nullptr;  // per segment: lr multiplier, decay flag
     int n_blocks = 0, n_segments = 0;
-    float *hyper_dev = nullptr;  // {lr/B, momentum, -decay*B*loss_scale, unused}
-    float hyper_host[4] = {0, 0, 0, 0};
+    float *hyper_dev = nullptr;  // {lr/B, momentum, -decay*B*loss_scale, unused, then for Adam: rate, -decay*B, 1-B1^t, 1-B2^t}
+    float hyper_host[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int adam = 0;                // [net] adam=1: Adam instead of SGD with momentum (mtcs/MtcsConvLayer.c:494-524,600-612)
+    float B1 = .9f, B2 = .999f, eps = .000001f;
     // Pinned host block (kPinnedFloats floats): [0..3] cost, mean loss, status word of a synchronous loss read;
     // [8..15] the same triple for each of the two slots of the asynchronous step; [16..] a ring of kHyperSlots
     // staged hyper-parameter quadruples (one per change of the learning rate, each with its own event).
@@ -283,6 +308,7 @@ struct LaunchScope {
     }
     ~LaunchScope() {
         if (ctx->profiling) prof_end(ctx);
+        ctx->span_ptr = nullptr;
     }
 };
 int aet_check_launch(const char *what);
@@ -332,6 +358,21 @@ inline void launch_k_cluster(cudaStream_t stream, dim3 grid, dim3 block, size_t 
     cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 #ifdef __CUDACC__
+// first CTA entry / last CTA exit of a profiled launch (see kMaxSpanSlots); one thread per CTA, two atomics in all
+__device__ __forceinline__ void span_begin(unsigned long long *span) {
+    if (span && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMin(span, t);
+    }
+}
+__device__ __forceinline__ void span_end(unsigned long long *span) {
+    if (span && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMax(span + 1, t);
+    }
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // the usual kernel opening: wait for the stream's earlier kernels, then let the next one schedule
@@ -385,6 +426,12 @@ int k_bn_stats(aet_layer *l, int update_rolling, const ConvStats *from_epilogue 
 int k_bn_apply(aet_layer *l, int use_rolling);
 int k_bn_backward(aet_layer *l, aet_layer *pool);
 int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling);
+bool stem_backward_eligible(const aet_layer *l, const aet_layer *pool);
+int stem_alloc(aet_layer *l, aet_layer *pool);
+int k_stem_gram(aet_layer *l, const float *x_in);
+int k_stem_backward(aet_layer *l, aet_layer *pool, const float *x_in);
+int k_stem_finish(aet_layer *l, float *dw, int accumulate);
+int k_stem_delta(aet_layer *l, aet_layer *pool);
 int k_bias_act_backward(aet_layer *l);
 int k_maxpool_forward(aet_layer *l, const float *x);
 int k_maxpool_backward(aet_layer *l, float *prev_delta, int accumulate);
@@ -404,6 +451,7 @@ int k_step_counter(aet_context *ctx, unsigned long long *ctr);
 int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, float lr_over_b, float momentum,
                   float decay_term, int scrub);   // scrub: 0 none, 1 weights, 2 batch-norm bias / scale with try_fix_nan
 int k_sgd_arena(aet_network *net);
+int k_adam_arena(aet_network *net);
 int conv_set_wait_limit(unsigned long long ns);          // conv.cu: limit of the mbarrier waits of the convolution kernels
 int elementwise_set_wait_limit(unsigned long long ns);   // elementwise.cu: limit of the peer-flag wait of the update kernel
 int conv_wait_probe(aet_context *ctx);                   // conv.cu: a wait nobody satisfies (self-test of the bounded waits)

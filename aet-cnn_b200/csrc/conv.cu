@@ -105,7 +105,10 @@ __device__ __forceinline__ void stat_init(StatAcc &st, const float *shift) {
 
 // Phase one of the epilogue: TMEM -> this warp's 32 rows of the staging tile, 32 columns (two loads in
 // flight) per wait.
-__device__ __forceinline__ void stage_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn) {
+// `tmem_acc2` (0 = none): a second accumulator of the same tile holding the other half of the K steps (the MMA issuer
+// alternates between the two so that consecutive MMAs do not depend on each other); the two are added on the way.
+__device__ __forceinline__ void stage_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
+                                                  uint32_t tmem_acc2 = 0) {
     const int pitch = bn + 4;
     float *mine = tile + (size_t)(warp * 32 + lane) * pitch;
     for (int cc = 0; cc < bn; cc += 32) {
@@ -114,7 +117,17 @@ __device__ __forceinline__ void stage_accumulator(float *tile, uint32_t tmem_acc
         if (have_acc) {
             tmem_ld16_issue(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, v);
             if (second) tmem_ld16_issue(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc + 16), v + 16);
-            tmem_ld_wait();
+            if (tmem_acc2) {
+                uint32_t w[32];
+                tmem_ld16_issue(tmem_acc2 + ((uint32_t)(warp * 32) << 16) + (uint32_t)cc, w);
+                if (second) tmem_ld16_issue(tmem_acc2 + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc + 16), w + 16);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 32; ++q)
+                    if (q < 16 || second) v[q] = __float_as_uint(__uint_as_float(v[q]) + __uint_as_float(w[q]));
+            } else {
+                tmem_ld_wait();
+            }
         } else {
 #pragma unroll
             for (int q = 0; q < 32; ++q) v[q] = 0u;
@@ -203,8 +216,8 @@ template <bool FPROP>
 __device__ __forceinline__ void store_accumulator(float *tile, uint32_t tmem_acc, bool have_acc, int warp, int lane, int bn,
                                                   float *out, size_t out_ld, int rows_valid, int col_base, int n_cols,
                                                   const float *bias, int act, int map_bi = 1, int map_w = 1, int map_pix = 0,
-                                                  StatAcc *st = nullptr) {
-    stage_accumulator(tile, tmem_acc, have_acc, warp, lane, bn);
+                                                  StatAcc *st = nullptr, uint32_t tmem_acc2 = 0) {
+    stage_accumulator(tile, tmem_acc, have_acc, warp, lane, bn, tmem_acc2);
     flush_tile<FPROP>(tile, nullptr, warp, lane, bn, out, out_ld, rows_valid, col_base, n_cols, bias, act, map_bi, map_w, map_pix, st);
 }
 

@@ -48,6 +48,7 @@ struct ThinArgs {
     int ksteps;           // MMAs per tile (K / 8 rounded up)
     int tiles, stages, tmem_cols;
     int *status;
+    unsigned long long *span;   // profiling: first CTA entry / last CTA exit (null: off)
 };
 
 struct ThinCtl {
@@ -62,6 +63,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ ThinCtl ctl;
+    span_begin(a.span);
     const ConvGeom &g = a.g;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bn = a.bn;
@@ -213,6 +215,7 @@ __global__ void __launch_bounds__(THIN_THREADS, 2) conv_fprop_thin_kernel(const 
         tmem_dealloc(tmem, a.tmem_cols);
         if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
+    span_end(a.span);
 }
 
 // Forward pass through the persistent thin-K kernel; 1 = not eligible.
@@ -248,6 +251,7 @@ int thin_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     if (grid > t.tiles) grid = t.tiles;
     if (a.stat_rows_out) *a.stat_rows_out = grid;
     LaunchScope scope(ctx, "conv_fprop_thin", 0, flops);
+    t.span = ctx->span_ptr;
     launch_k(ctx->stream, grid, THIN_THREADS, smem_bytes, conv_fprop_thin_kernel, t);
     return aet_check_launch("conv_fprop_thin");
 }
@@ -272,6 +276,7 @@ struct ThinWArgs {
     long long split_stride;
     int stages, tmem_cols;
     int *status;
+    unsigned long long *span;   // profiling: first CTA entry / last CTA exit (null: off)
 };
 
 struct ThinWCtl {
@@ -285,6 +290,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ ThinWCtl ctl;
+    span_begin(a.span);
     const ConvGeom &g = a.g;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bn = a.bn;
@@ -414,6 +420,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) conv_wgrad_thin_kernel(const __gr
         tmem_dealloc(tmem, a.tmem_cols);
         if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
+    span_end(a.span);
 }
 
 // Weight gradient through the thin-K kernel: fills `partial` (ctx scratch) with `*splits` tiles; 1 = not eligible.
@@ -463,6 +470,7 @@ int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, f
     const size_t smem_bytes = stage * stages + 1024;
     AET_TRY(ctx_smem_attr(ctx, conv_wgrad_thin_kernel));
     LaunchScope scope(ctx, "conv_wgrad_thin", 0, flops);
+    t.span = ctx->span_ptr;
     launch_k(ctx->stream, splits, NTHREADS, smem_bytes, conv_wgrad_thin_kernel, *ma, t);
     *splits_out = splits;
     *partial_out = partial;

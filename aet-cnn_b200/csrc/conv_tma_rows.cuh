@@ -25,6 +25,7 @@ struct RowsArgs {
     int stages, tmem_cols;
     uint32_t a_bytes, b_bytes, tx_bytes, b_lbo;
     int *status;
+    unsigned long long *span;   // profiling: first CTA entry / last CTA exit (null: off)
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -32,6 +33,7 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                        const RowsArgs a) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ SharedCtl ctl;
+    span_begin(a.span);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BM;
@@ -108,7 +110,19 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t phase = (it / a.stages) & 1;
             if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
             tc_fence_after_sync();
-            const uint64_t st16 = (uint64_t)(((uint32_t)s * stage_bytes) >> 4);
+            const uint32_t st16 = ((uint32_t)s * stage_bytes) >> 4;
+            if (a.R == 3) {
+                // The issuing thread sets the pace (an MMA leaves it about 77 clocks): everything unrolled, only the
+                // descriptors' low words computed, consecutive MMAs to different accumulators.
+                const uint32_t a_lo = (uint32_t)da0 + st16, b_lo = (uint32_t)db0 + st16;
+                const uint64_t a_hi = da0 & 0xffffffff00000000ull, b_hi = db0 & 0xffffffff00000000ull;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int r = 0; r < 3; ++r)
+                        mma_tf32(tmem + (uint32_t)(r * bn), a_hi | (uint64_t)(a_lo + (uint32_t)(j * 64)),
+                                 b_hi | (uint64_t)(b_lo + (uint32_t)r * row16 + (uint32_t)(j * 64)), idesc, j > 0 ? 1u : accumulate);
+            } else
             for (int r = 0; r < a.R; ++r) {
                 const uint64_t db_r = db0 + st16 + (uint64_t)(r * row16);
                 const uint32_t d_r = tmem + (uint32_t)(r * bn);
@@ -128,6 +142,7 @@ conv_wgrad_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tmem_dealloc(tmem, a.tmem_cols);
         if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
+    span_end(a.span);
 }
 
 // Returns AET_OK (launched; *splits_out and *partial_out set), 1 (not eligible), or an error.
@@ -201,6 +216,7 @@ int tma_wgrad_rows(aet_layer *l, const ConvArgs &a, double flops, int *splits_ou
         char variant[40];
         snprintf(variant, sizeof(variant), "n%d_sp%d", bn, splits);
         LaunchScope scope(ctx, "conv_wgrad_tma_rows", 0, flops, variant);
+        t.span = ctx->span_ptr;
         launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_wgrad_rows_kernel, *ma, *mb, t);
         AET_TRY(aet_check_launch("conv_wgrad_tma_rows"));
     }
@@ -231,15 +247,46 @@ struct FdRowsArgs {
     int smerge_S;                  // data gradient of a narrow layer: the S column taps ride in one MMA of N = S * channels
                                    // (0 = off); the epilogue adds the S column blocks, each shifted by its tap
     int par_epi;                   // mt == 2 with nine warps: warps 5-8 store the second pixel tile while warps 0-3 store the first
+    int dual_acc;                  // mt == 1: two accumulators per tile (even / odd K steps), added by the epilogue
     int rotate;                    // every CTA starts its K slabs at another offset (spreads the reads of the shared weight tiles)
     int pair;                      // the two CTAs of a cluster along grid x form a cta_group::2 pair: MMAs of M = 256 issued by the
                                    // even CTA, each CTA loading its own pixel tiles and half of every weight tile
     int stages, tmem_cols;
     uint32_t a_bytes, b_tile_bytes, tx_bytes;
     int *status;
+    unsigned long long *span;   // profiling: first CTA entry / last CTA exit (null: off)
 };
 
 constexpr int FD_THREADS_WIDE = 288;   // five warps + a second epilogue group
+
+// The MMAs of one pipeline stage, issued by one thread.  A lone thread issues an instruction every few clocks, and an
+// MMA of 128 x N x 8 leaves the tensor pipe only about 77 clocks per instruction: with run-time loop bounds and
+// 64-bit descriptor arithmetic the issuing thread, not the tensor pipe, sets the pace.  So the tap count R and the
+// tiles per CTA MT are compile-time here (everything unrolls, offsets become immediates), only the low word of a
+// descriptor -- the start-address field sits in its low 14 bits -- is computed per MMA, and consecutive MMAs go to
+// different accumulators where there are two.
+// DUAL (with MT = 1): even and odd K steps go to two accumulators of the one tile, which the epilogue adds.
+template <int KIND, bool PAIR, int R, int MT, bool DUAL = false>
+__device__ __forceinline__ void issue_stage_mmas(uint32_t tmem, int bn, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t img_row16, uint32_t tile_rows16, uint32_t btile16, uint32_t b_step,
+                                                 uint32_t idesc, uint32_t accumulate) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int rr = KIND == KIND_FPROP ? r : R - 1 - r;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int t = 0; t < MT; ++t) {
+                const uint64_t da = ((uint64_t)a_hi << 32) | (uint64_t)(a_lo + (uint32_t)t * tile_rows16 + (uint32_t)rr * img_row16 + (uint32_t)(j * 2));
+                const uint64_t db = ((uint64_t)b_hi << 32) | (uint64_t)(b_lo + (uint32_t)r * btile16 + (uint32_t)j * b_step);
+                const uint32_t acc = (r > 0 || j > (DUAL ? 1 : 0)) ? 1u : accumulate;
+                const uint32_t d = tmem + (uint32_t)((DUAL ? (j & 1) : t) * bn);
+                if (PAIR) mma_tf32_pair(d, da, db, idesc, acc);
+                else mma_tf32(d, da, db, idesc, acc);
+            }
+        }
+    }
+}
 // PAIR: the cta_group::2 form.  It is a separate instantiation because a kernel that contains cta_group::2
 // instructions can only be launched as a cluster of CTA pairs.
 template <int KIND, bool PAIR>
@@ -248,6 +295,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const FdRowsArgs a) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ SharedCtl ctl;
+    span_begin(a.span);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bn = a.bn;
@@ -353,7 +401,8 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         epilogue_ready = ready;
         if (ready && a.ksplit > 1) {
             // only stage the accumulator (mt == 1 here); the sum of the two halves is stored after the cluster barrier
-            stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, q, lane, bn);
+            stage_accumulator(reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw))), tmem, true, q, lane, bn,
+                              a.dual_acc ? tmem + (uint32_t)bn : 0u);
         } else if (ready && a.smerge_S && 32 % a.w == 0 && bn / a.smerge_S <= 128) {
             // Column taps merged into N: accumulator column block sx holds the partial result that belongs to the
             // output pixel (pad - sx) columns further on, i.e. to the TMEM lane (pad - sx) rows away.  A warp's 32
@@ -459,7 +508,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int mt0 = m0 + t * BM;
                 store_accumulator<KIND == KIND_FPROP>(tile, tmem + (uint32_t)(t * bn), true, warp, lane, bn,
                                                       a.out + (size_t)mt0 * a.out_ld, (size_t)a.out_ld, a.n_rows - mt0, n0, a.n_cols,
-                                                      a.bias, a.act, a.bi, a.w, a.pix_per_img, &st);
+                                                      a.bias, a.act, a.bi, a.w, a.pix_per_img, &st, a.dual_acc ? tmem + (uint32_t)bn : 0u);
             }
             if (KIND == KIND_FPROP && st.shift)
                 stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
@@ -481,7 +530,18 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t phase = (it / a.stages) & 1;
             if (!mbar_wait(smem_u32(&ctl.full[s]), phase, abort_flag)) break;
             tc_fence_after_sync();
-            const uint64_t st16 = (uint64_t)(((uint32_t)s * stage_bytes) >> 4);
+            const uint32_t st16 = ((uint32_t)s * stage_bytes) >> 4;
+            if (a.R == 3 && a.mt <= 2) {
+                // the common 3x3 case: fully unrolled (the low words cannot carry into the descriptors' high words: start
+                // addresses stay below 2^14 sixteen-byte units)
+                const uint32_t a_lo = (uint32_t)da0 + st16, b_lo = (uint32_t)db0 + st16;
+                if (a.mt == 2) issue_stage_mmas<KIND, PAIR, 3, 2>(tmem, bn, a_lo, (uint32_t)(da0 >> 32), b_lo, (uint32_t)(db0 >> 32), img_row16,
+                                                                  tile_rows16, btile16, (uint32_t)b_step, idesc, accumulate);
+                else if (a.dual_acc) issue_stage_mmas<KIND, PAIR, 3, 1, true>(tmem, bn, a_lo, (uint32_t)(da0 >> 32), b_lo, (uint32_t)(db0 >> 32),
+                                                                             img_row16, tile_rows16, btile16, (uint32_t)b_step, idesc, accumulate);
+                else issue_stage_mmas<KIND, PAIR, 3, 1>(tmem, bn, a_lo, (uint32_t)(da0 >> 32), b_lo, (uint32_t)(db0 >> 32), img_row16,
+                                                        tile_rows16, btile16, (uint32_t)b_step, idesc, accumulate);
+            } else
             for (int r = 0; r < a.R; ++r) {
                 const int rr = KIND == KIND_FPROP ? r : a.R - 1 - r;
                 const uint64_t db_r = db0 + st16 + (uint64_t)(r * btile16);
@@ -542,6 +602,7 @@ conv_fd_rows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         else tmem_dealloc(tmem, a.tmem_cols);
         if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
+    span_end(a.span);
 }
 
 // fprop (KIND_FPROP) or dgrad (KIND_DGRAD) through the row-sharing kernel; 1 = not eligible.
@@ -671,7 +732,9 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     t.R = g.R; t.S = smerge ? 1 : g.S; t.pad = g.pad; t.inner = inner; t.slabs_per_s = (inner + 31) / 32;
     t.smerge_S = smerge;
     t.mt = mt; t.bh = (int)bh; t.bi = (int)bi; t.w = g.W; t.pix_per_img = g.H * g.W; t.n_img = g.N;
-    t.stages = stages; t.tmem_cols = pow2_cols(mt * bn); t.ksplit = ksplit;
+    // one pixel tile per CTA: its K steps alternate between two accumulators (3x3 filters, whose issue path is unrolled)
+    t.dual_acc = (mt == 1 && !smerge && g.R == 3 && 2 * bn <= 512 && ctx->opt[OPT_DUAL_ACC]) ? 1 : 0;
+    t.stages = stages; t.tmem_cols = pow2_cols((t.dual_acc ? 2 : mt) * bn); t.ksplit = ksplit;
     t.par_epi = (mt == 2 && !smerge && stage * stages >= 2 * (size_t)BM * (bn + 4) * 4 && ctx->opt[OPT_PAR_EPILOGUE]) ? 1 : 0;
     t.pair = pair;
     t.rotate = ctx->opt[OPT_ROTATE];
@@ -685,9 +748,10 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
     if (KIND == KIND_FPROP && a.stat_rows_out) *a.stat_rows_out = (int)grid.x * ((t.par_epi || ksplit > 1) ? 2 : 1);
     const char *name = KIND == KIND_FPROP ? "conv_fprop_tma_rows" : "conv_dgrad_tma_rows";
     char variant[40];   // e.g. "mt2e_n128x1_p2": two pixel tiles, second epilogue group, N tile 128, one N tile, CTA pairs
-    snprintf(variant, sizeof(variant), "%smt%d%s_n%dx%d%s%s", smerge ? "sm_" : "", mt, t.par_epi ? "e" : "", bn, n_tiles, ksplit > 1 ? "_ks2" : "",
-             pair ? "_p2" : "");
+    snprintf(variant, sizeof(variant), "%smt%d%s%s_n%dx%d%s%s", smerge ? "sm_" : "", mt, t.par_epi ? "e" : "", t.dual_acc ? "d" : "", bn, n_tiles,
+             ksplit > 1 ? "_ks2" : "", pair ? "_p2" : "");
     LaunchScope scope(ctx, name, 0, flops, variant);
+    t.span = ctx->span_ptr;
     if (pair) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, 2, ksplit, conv_fd_rows_kernel<KIND, true>, *ma, *mb, t);
     else if (ksplit > 1) launch_k_cluster(ctx->stream, grid, threads, smem_bytes, 1, ksplit, conv_fd_rows_kernel<KIND, false>, *ma, *mb, t);
     else launch_k(ctx->stream, grid, threads, smem_bytes, conv_fd_rows_kernel<KIND, false>, *ma, *mb, t);

@@ -250,14 +250,36 @@ __global__ void __launch_bounds__(TB) bn_bwd_poolwin_kernel(const PoolWinArgs a)
         for (int t = 0; t < 4; ++t) v[t] = ld4(a.x + offs[t]);
         // reference numbering of the window's top-left input, channel c
         const int pos00 = 2 * ow + a.W * (2 * oh + a.H * (c + n * a.C));
+        // Only a window's argmax input receives the pool's delta: per channel the tap t it sits at follows from the
+        // stored index, and the activation gradient is evaluated for that one input instead of all four
+        // (the other three contribute exact zeros to the sums, and only their (x - mean) term to the apply pass).
+        int tsel[4];
+        float qa[4];
+        {
+            const int ids[4] = {id.x, id.y, id.z, id.w};
+            const float dvs[4] = {dv.x, dv.y, dv.z, dv.w};
+            const float means[4] = {mean.x, mean.y, mean.z, mean.w}, invs[4] = {inv.x, inv.y, inv.z, inv.w};
+            const float gams[4] = {gam.x, gam.y, gam.z, gam.w}, bets[4] = {bet.x, bet.y, bet.z, bet.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int d = ids[k] - (pos00 + k * hw);
+                const int t = d == 0 ? 0 : (d == 1 ? 1 : (d == a.W ? 2 : (d == a.W + 1 ? 3 : -1)));
+                const float x0 = k == 0 ? v[0].x : (k == 1 ? v[0].y : (k == 2 ? v[0].z : v[0].w));
+                const float x1 = k == 0 ? v[1].x : (k == 1 ? v[1].y : (k == 2 ? v[1].z : v[1].w));
+                const float x2 = k == 0 ? v[2].x : (k == 1 ? v[2].y : (k == 2 ? v[2].z : v[2].w));
+                const float x3 = k == 0 ? v[3].x : (k == 1 ? v[3].y : (k == 2 ? v[3].z : v[3].w));
+                const float xa = t == 0 ? x0 : (t == 1 ? x1 : (t == 2 ? x2 : x3));
+                tsel[k] = t;
+                qa[k] = t >= 0 ? dvs[k] * act_grad(act_fwd(bn_val(xa, means[k], invs[k], gams[k], bets[k]), a.act), a.act) : 0.f;
+            }
+        }
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            const int pos = pos00 + (t & 1) + (t >> 1) * a.W;
             float4 q;
-            q.x = sel(id.x, pos, dv.x) * act_grad(act_fwd(bn_val(v[t].x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
-            q.y = sel(id.y, pos + hw, dv.y) * act_grad(act_fwd(bn_val(v[t].y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
-            q.z = sel(id.z, pos + 2 * hw, dv.z) * act_grad(act_fwd(bn_val(v[t].z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
-            q.w = sel(id.w, pos + 3 * hw, dv.w) * act_grad(act_fwd(bn_val(v[t].w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+            q.x = tsel[0] == t ? qa[0] : 0.f;
+            q.y = tsel[1] == t ? qa[1] : 0.f;
+            q.z = tsel[2] == t ? qa[2] : 0.f;
+            q.w = tsel[3] == t ? qa[3] : 0.f;
             if (APPLY) {
                 q.x = q.x * ka.x + (v[t].x - mean.x) * kb.x + kc.x;
                 q.y = q.y * ka.y + (v[t].y - mean.y) * kb.y + kc.y;
@@ -569,6 +591,8 @@ struct BnPoolArgs {
     PoolArgs p;
     const float *mean, *inv, *gamma, *beta;
     int act;
+    float *ymax;           // optional: the convolution result (before BN) at each window's argmax, same layout as the pool output
+    unsigned char *code;   // with ymax: the argmax's position inside the window (0..3 row-major; 4: none)
 };
 __global__ void __launch_bounds__(TB) bn_pool_fwd_kernel(const BnPoolArgs b) {
     pdl_enter();
@@ -588,6 +612,38 @@ __global__ void __launch_bounds__(TB) bn_pool_fwd_kernel(const BnPoolArgs b) {
     const int c = cv * 4;
     const float4 mean = __ldg(reinterpret_cast<const float4 *>(b.mean + c)), inv = __ldg(reinterpret_cast<const float4 *>(b.inv + c));
     const float4 gam = __ldg(reinterpret_cast<const float4 *>(b.gamma + c)), bet = __ldg(reinterpret_cast<const float4 *>(b.beta + c));
+    if (a.size == 2 && a.sx == 2 && a.sy == 2 && a.off == 0 && 2 * oh + 1 < a.H && 2 * ow + 1 < a.W) {
+        // The usual 2x2 / stride-2 window, wholly inside the map: its four taps are requested before any of them is
+        // used (four independent 16-byte loads per thread instead of a chain of dependent ones), then compared in the
+        // same (row, column) order with the same strict '>' as the general loop below.
+        const size_t i00 = ((size_t)(n * a.H + 2 * oh) * a.W + 2 * ow) * a.cp + c;
+        float4 t[4] = {ld4(a.x + i00), ld4(a.x + i00 + a.cp), ld4(a.x + i00 + (size_t)a.W * a.cp), ld4(a.x + i00 + (size_t)a.W * a.cp + a.cp)};
+        const int hw = a.H * a.W;
+        const int base00 = 2 * ow + a.W * (2 * oh + a.H * (c + n * a.C));
+        float4 raw = make_float4(0.f, 0.f, 0.f, 0.f);
+        uchar4 cd = make_uchar4(4, 4, 4, 4);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float4 v = t[k];
+            v.x = act_fwd(bn_val(v.x, mean.x, inv.x, gam.x, bet.x), b.act);
+            v.y = act_fwd(bn_val(v.y, mean.y, inv.y, gam.y, bet.y), b.act);
+            v.z = act_fwd(bn_val(v.z, mean.z, inv.z, gam.z, bet.z), b.act);
+            v.w = act_fwd(bn_val(v.w, mean.w, inv.w, gam.w, bet.w), b.act);
+            const int base = base00 + (k & 1) + (k >> 1) * a.W;
+            if (v.x > mx.x) { mx.x = v.x; mi.x = base; raw.x = t[k].x; cd.x = (unsigned char)k; }
+            if (v.y > mx.y) { mx.y = v.y; mi.y = base + hw; raw.y = t[k].y; cd.y = (unsigned char)k; }
+            if (v.z > mx.z) { mx.z = v.z; mi.z = base + 2 * hw; raw.z = t[k].z; cd.z = (unsigned char)k; }
+            if (v.w > mx.w) { mx.w = v.w; mi.w = base + 3 * hw; raw.w = t[k].w; cd.w = (unsigned char)k; }
+        }
+        if (b.ymax) {
+            if (c + 1 >= a.C) cd.y = 4;   // pad channels
+            if (c + 2 >= a.C) cd.z = 4;
+            if (c + 3 >= a.C) cd.w = 4;
+            const size_t o = ((size_t)(n * a.OH + oh) * a.OW + ow) * a.cp + c;
+            st4(b.ymax + o, raw);
+            *reinterpret_cast<uchar4 *>(b.code + o) = cd;
+        }
+    } else
     for (int l = 0; l < a.size; ++l)
         for (int m = 0; m < a.size; ++m) {
             const int ch = a.off + oh * a.sy + l, cw = a.off + ow * a.sx + m;
@@ -1206,6 +1262,45 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
     st4(U + i, u);
     st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
 }
+// Adam, mtcs/MtcsConvLayer.c:494-524 (adam_update_gpu), the reference's eight launches per parameter array in one pass:
+//   m *= B1; v *= B2; d += (-decay*batch) * w; m += (1-B1) * d; d *= d; v += (1-B2) * d;
+//   w += rate * (m / (1-B1^t)) / (sqrtf(v / (1-B2^t)) + eps); d = 0
+// The reference applies the same routine, decay included, to weights, biases and scales (:600-612).  d = U + G: the
+// pending-update buffer carries nothing between steps under Adam.  hyper[4..7] = {rate, -decay*batch, 1-B1^t, 1-B2^t}.
+__global__ void __launch_bounds__(TB) adam_arena_kernel(float *W, float *U, float *G, float *M, float *V, const int *block_seg,
+                                                        const float *seg_table, const float *hyper, float B1, float B2, float eps,
+                                                        int *status) {
+    pdl_enter();
+    const int seg = block_seg[blockIdx.x];
+    const float rate = hyper[4] * seg_table[4 * seg];
+    const float decay_term = hyper[5], c1 = hyper[6], c2 = hyper[7];
+    const int scrub = (int)seg_table[4 * seg + 2];
+    const size_t i = ((size_t)blockIdx.x * TB + threadIdx.x) * 4;
+    float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i), m = ld4(M + i), v = ld4(V + i);
+    u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    if (scrub) {
+        const size_t first = (size_t)__float_as_int(seg_table[4 * seg + 3]) * TB * 4;
+        if (scrub4(w, u, scrub, i - first) && status) atomicOr(status, AET_STATUS_NAN);
+    }
+    float *wp = &w.x, *up = &u.x, *mp = &m.x, *vp = &v.x;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float mm = __fmul_rn(mp[k], B1), vv = __fmul_rn(vp[k], B2);
+        float d = __fadd_rn(up[k], __fmul_rn(decay_term, wp[k]));
+        mm = __fadd_rn(mm, __fmul_rn(1.f - B1, d));
+        d = __fmul_rn(d, d);
+        vv = __fadd_rn(vv, __fmul_rn(1.f - B2, d));
+        const float mhat = mm / c1, vhat = vv / c2;
+        wp[k] = wp[k] + rate * mhat / (sqrtf(vhat) + eps);
+        mp[k] = mm; vp[k] = vv;
+    }
+    st4(W + i, w);
+    st4(M + i, m);
+    st4(V + i, v);
+    st4(U + i, make_float4(0.f, 0.f, 0.f, 0.f));
+    st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
+}
+
 __global__ void sgd_segment_kernel(float *W, float *U, float *G, size_t n4, float rate, float momentum, float decay_term,
                                    int scrub, int *status) {
     pdl_enter();
@@ -1465,7 +1560,9 @@ int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling) {
     a.total = (long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4);
     b.mean = use_rolling ? l->rolling_mean : l->mean; b.inv = l->inv_std; b.gamma = layer_s(l); b.beta = layer_b(l);
     b.act = l->act;
-    const double bytes = 4.0 * pool->batch * pool->h * pool->w * pool->cp + 8.0 * pool->batch * pool->oh * pool->ow * pool->cp;
+    b.ymax = (l->stem && !use_rolling) ? l->stem_ymax : nullptr;   // eligible layers have even maps: every window takes the 2x2 branch
+    b.code = l->stem_code;
+    const double bytes = 4.0 * pool->batch * pool->h * pool->w * pool->cp + (b.ymax ? 13.0 : 8.0) * pool->batch * pool->oh * pool->ow * pool->cp;
     LaunchScope s(ctx, "bn_act_maxpool_fwd", bytes, 0);
     launch_k(ctx->stream, (unsigned)((a.total + TB - 1) / TB), TB, 0, bn_pool_fwd_kernel, b);
     return aet_check_launch("bn_act_maxpool_fwd");
@@ -1553,6 +1650,23 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     launch_k(ctx->stream, dim3(q.blocks, q.m.cslabs), TB, 0, bn_bwd_apply_kernel<false>, b);
     return aet_check_launch("bn_bwd_apply");
 }
+
+// The full-resolution delta of a layer whose backward went through the pool-sized path: the BN backward apply pass with
+// the coefficients that pass left behind (host taps only).
+int k_stem_delta(aet_layer *l, aet_layer *pool) {
+    aet_context *ctx = l->ctx;
+    PoolWinArgs w = {};
+    w.x = l->x->d; w.dx = l->delta->d; w.pdelta = pool->delta->d; w.pidx = pool->indexes;
+    w.mean = l->mean; w.inv = l->inv_std; w.gamma = layer_s(l); w.beta = layer_b(l); w.coef = l->bwd_coef;
+    w.act = l->act; w.cp = l->ocp; w.C = pool->c; w.H = pool->h; w.W = pool->w; w.OH = pool->oh; w.OW = pool->ow;
+    w.total = (unsigned)((long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4));
+    const int blocks = (int)((w.total + TB - 1) / TB) < 8 * ctx->sm_count ? (int)((w.total + TB - 1) / TB) : 8 * ctx->sm_count;
+    LaunchScope s(ctx, "bn_bwd_apply_poolwin", 0, 0);
+    launch_k(ctx->stream, blocks, TB, 0, bn_bwd_poolwin_kernel<true>, w);
+    return aet_check_launch("bn_bwd_apply_poolwin");
+}
+
+#include "stem.cuh"
 
 // Convolution without BN: delta *= act'(output) in place and the bias gradient accumulates.
 int k_bias_act_backward(aet_layer *l) {
@@ -1765,6 +1879,15 @@ int k_sgd_arena(aet_network *net) {
     launch_k(ctx->stream, net->n_blocks, TB, 0, sgd_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->block_seg,
                                                            net->seg_table, net->hyper_dev, t, ctx->status_dev);
     return aet_check_launch("sgd_momentum");
+}
+
+int k_adam_arena(aet_network *net) {
+    aet_context *ctx = net->ctx;
+    if (net->xchg_active && net->tail_n) { aet_set_error("Adam does not take its gradients through the peer exchange"); return AET_E_INVALID; }
+    LaunchScope s(ctx, "adam", 40.0 * net->arena.used, 0);
+    launch_k(ctx->stream, net->n_blocks, TB, 0, adam_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->arena.M, net->arena.V,
+             net->block_seg, net->seg_table, net->hyper_dev, net->B1, net->B2, net->eps, ctx->status_dev);
+    return aet_check_launch("adam");
 }
 
 int k_tail_publish(aet_network *net) {

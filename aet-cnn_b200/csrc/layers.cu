@@ -70,8 +70,10 @@ void arena_destroy(ParamArena *a) {
         if (a->W) cudaFree(a->W);
         if (a->U) cudaFree(a->U);
         if (a->G) cudaFree(a->G);
+        if (a->M) cudaFree(a->M);
+        if (a->V) cudaFree(a->V);
     }
-    a->W = a->U = a->G = nullptr;
+    a->W = a->U = a->G = a->M = a->V = nullptr;
 }
 
 int arena_create_public(ParamArena *a, size_t floats) { return arena_create(a, floats); }
@@ -257,6 +259,11 @@ extern "C" void aet_layer_destroy(aet_layer *l) {
     if (l->indexes) cudaFree(l->indexes);
     if (l->loss) cudaFree(l->loss);
     if (l->sample_loss) cudaFree(l->sample_loss);
+    if (l->stem_ymax) cudaFree(l->stem_ymax);
+    if (l->stem_code) cudaFree(l->stem_code);
+    if (l->stem_partial) cudaFree(l->stem_partial);
+    if (l->stem_gram_partial) cudaFree(l->stem_gram_partial);
+    if (l->stem_gram) cudaFree(l->stem_gram);
     if (l->lin_xbar) cudaFree(l->lin_xbar);
     if (l->lin_ticket) cudaFree(l->lin_ticket);
     if (l->cost_dev) cudaFree(l->cost_dev);
@@ -292,6 +299,16 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
             if (pool && (pool->indexes || !state.train)) {
                 // the following max-pool is produced here; the full-resolution activated output is
                 // only materialised if a host tap asks for it
+                l->stem_gram_ready = false;
+                l->stem_delta_stale = false;
+                if (l->stem && state.train && l->ctx->in_network_pass && l->ctx->opt[OPT_OVERLAP_WGRAD]) {
+                    // the Gram matrix of the input patches depends on the input alone: it runs beside the forward pass
+                    AET_TRY(side_begin(l->ctx));
+                    const int gr = k_stem_gram(l, state.input->d);
+                    side_end(l->ctx);
+                    AET_TRY(gr);
+                    l->stem_gram_ready = true;
+                }
                 AET_TRY(k_bn_pool_forward(l, pool, state.train ? 0 : 1));
                 l->output_stale = true;
                 pool->fused_ready = true;
@@ -397,6 +414,19 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
         }
         if (l->head_backward_done) {
             l->head_backward_done = false;    // delta and bias gradient came from the fused head kernel
+        } else if (l->gather_pending && l->bn && l->fused_pool && l->stem && !pd && l->ctx->in_network_pass && l->last_forward_train) {
+            // first layer: scale / shift gradients and the weight gradient straight from the pool-sized tensors
+            l->gather_pending = false;
+            if (!l->stem_gram_ready) AET_TRY(k_stem_gram(l, state.input->d));
+            l->stem_gram_ready = false;
+            AET_TRY(k_stem_backward(l, l->fused_pool, state.input->d));
+            if (l->ctx->overlap_wgrad) AET_TRY(side_begin(l->ctx));   // behind the Gram kernels, after the pool-sized pass
+            const int fr = k_stem_finish(l, layer_G(l), 1);
+            side_end(l->ctx);
+            AET_TRY(fr);
+            l->delta->lazy_zero = false;
+            l->stem_delta_stale = true;
+            return AET_OK;
         } else if (l->gather_pending && l->bn && l->fused_pool) {
             // the max-pool's backward was deferred: gather its delta inside the BN backward kernels
             l->gather_pending = false;
@@ -614,6 +644,10 @@ extern "C" int aet_layer_read(aet_layer *l, aet_param which, void *host_v) {
         }
         return read_tensor_or_zero(l->output, host);
     case AET_P_DELTA:
+        if (l->stem_delta_stale) {
+            AET_TRY(k_stem_delta(l, l->fused_pool));
+            l->stem_delta_stale = false;
+        }
         if (l->lin_delta_stale) {
             AET_TRY(k_linhead_conv_delta(l, l->head_softmax->head_avg, l->head_softmax));
             l->lin_delta_stale = false;
@@ -677,6 +711,7 @@ extern "C" int aet_layer_write(aet_layer *l, aet_param which, const void *host_v
     case AET_P_DELTA:
         l->delta->lazy_zero = false;
         l->lin_delta_stale = false;
+        l->stem_delta_stale = false;
         return aet_tensor_write(l->delta, host);
     case AET_P_X: return aet_tensor_write(l->x, host);
     case AET_P_RAND:

@@ -217,7 +217,16 @@ int upload_hyper(aet_network *net) {
     const int world = net->world > 0 ? net->world : 1;
     const int update_batch = net->batch * net->subdivisions * world;
     const float rate = current_rate(net);
-    float h[4] = {rate / net->loss_scale / update_batch, net->momentum, -net->decay * update_batch * net->loss_scale, 0.f};
+    float h[8] = {rate / net->loss_scale / update_batch, net->momentum, -net->decay * update_batch * net->loss_scale, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (net->adam) {
+        // adam_update_gpu(w, d, m, v, B1, B2, eps, decay, learning_rate, n, batch, t), mtcs/MtcsConvLayer.c:494-524: the rate is
+        // not divided by the batch, the decay term is -decay*batch, t is the current batch number (NNetwork.c:700)
+        const int t = (int)(net->seen / ((int64_t)net->batch * net->subdivisions));
+        h[4] = rate / net->loss_scale;
+        h[5] = -net->decay * update_batch;
+        h[6] = 1.f - powf(net->B1, (float)t);
+        h[7] = 1.f - powf(net->B2, (float)t);
+    }
     if (memcmp(h, net->hyper_host, sizeof(h)) == 0) return AET_OK;
     memcpy(net->hyper_host, h, sizeof(h));
     // The copy is asynchronous and the host may be many steps ahead of the device: every change of the rate is
@@ -226,7 +235,7 @@ int upload_hyper(aet_network *net) {
     net->hyper_next = (slot + 1) % kHyperSlots;
     if (!net->hyper_ev[slot]) AET_CUDA(cudaEventCreateWithFlags(&net->hyper_ev[slot], cudaEventDisableTiming));
     if (net->hyper_used[slot]) AET_CUDA(cudaEventSynchronize(net->hyper_ev[slot]));
-    float *stage = net->loss_pinned + 16 + 4 * slot;
+    float *stage = net->loss_pinned + 16 + 8 * slot;
     memcpy(stage, h, sizeof(h));
     AET_CUDA(cudaMemcpyAsync(net->hyper_dev, stage, sizeof(h), cudaMemcpyHostToDevice, net->ctx->stream));
     AET_CUDA(cudaEventRecord(net->hyper_ev[slot], net->ctx->stream));
@@ -333,7 +342,7 @@ int run_step(aet_network *net, bool final) {
     AET_TRY(net_backward(net, st, final));
     if (!final) return AET_OK;   // gradients keep accumulating in the arena until the group's last call
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
-    if (net->n_blocks) AET_TRY(k_sgd_arena(net));
+    if (net->n_blocks) AET_TRY(net->adam ? k_adam_arena(net) : k_sgd_arena(net));
     net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
     return AET_OK;
 }
@@ -405,6 +414,12 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
     if (batch_override > 0) { net->batch = batch_override; net->subdivisions = 1; }
     net->loss_scale = opt_float(ns, "loss_scale", 1.f);
     net->try_fix_nan = opt_int(ns, "try_fix_nan", 0);
+    net->adam = opt_int(ns, "adam", 0);               // dnn/NetworkFactory.c:719-724
+    if (net->adam) {
+        net->B1 = opt_float(ns, "B1", .9f);
+        net->B2 = opt_float(ns, "B2", .999f);
+        net->eps = opt_float(ns, "eps", .000001f);
+    }
     net->h = opt_int(ns, "height", 0); net->w = opt_int(ns, "width", 0); net->c = opt_int(ns, "channels", 0);
     net->power = opt_float(ns, "power", 4.f);
     net->burn_in = opt_int(ns, "burn_in", 0);
@@ -521,7 +536,10 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
         l->index = index;
         if (l->type == AET_MAXPOOL && !net->layers.empty() && ctx->opt[OPT_FUSE]) {
             aet_layer *prev = net->layers.back();
-            if (prev->type == AET_CONVOLUTIONAL && prev->bn) { prev->fused_pool = l; l->fused_into = prev; }
+            if (prev->type == AET_CONVOLUTIONAL && prev->bn) {
+                prev->fused_pool = l; l->fused_into = prev;
+                if (prev->index == 0 && stem_backward_eligible(prev, l) && stem_alloc(prev, l) == AET_OK) prev->stem = true;
+            }
         }
         net->layers.push_back(l);
         if (l->type == AET_SOFTMAX && net->layers.size() >= 3 && ctx->opt[OPT_FUSE]) {
@@ -545,7 +563,14 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
     net->input = aet_tensor_create(ctx, net->batch, net->c, net->h, net->w);
     net->truth = aet_tensor_create(ctx, net->batch, c * h * w, 1, 1);
     bool ok = net->input && net->truth && build_sgd_tables(net) == AET_OK;
-    ok = ok && cudaMalloc(&net->hyper_dev, 4 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&net->hyper_dev, 8 * sizeof(float)) == cudaSuccess;
+    if (ok && net->adam) {
+        ok = cudaMalloc(&net->arena.M, net->arena.capacity * sizeof(float)) == cudaSuccess &&
+             cudaMalloc(&net->arena.V, net->arena.capacity * sizeof(float)) == cudaSuccess &&
+             cudaMemset(net->arena.M, 0, net->arena.capacity * sizeof(float)) == cudaSuccess &&
+             cudaMemset(net->arena.V, 0, net->arena.capacity * sizeof(float)) == cudaSuccess;
+        cudaDeviceSynchronize();
+    }
     ok = ok && cudaMallocHost(&net->loss_pinned, kPinnedFloats * sizeof(float)) == cudaSuccess;
     if (!ok) {
         if (!strlen(aet_last_error())) aet_set_error("network allocation failed");
@@ -640,7 +665,7 @@ extern "C" int aet_network_update(aet_network *net) {
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     AET_TRY(upload_hyper(net));
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
-    if (net->n_blocks) AET_TRY(k_sgd_arena(net));
+    if (net->n_blocks) AET_TRY(net->adam ? k_adam_arena(net) : k_sgd_arena(net));
     net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
     return AET_OK;
 }

@@ -63,6 +63,11 @@ void prof_begin(aet_context *ctx, const char *name, double bytes, double flops, 
         }
     }
     ProfileRecord r;
+    r.span_slot = -1;
+    if (ctx->span_dev && ctx->records.size() < (size_t)kMaxSpanSlots) {
+        r.span_slot = (int)ctx->records.size();
+        ctx->span_ptr = ctx->span_dev + 2 * (size_t)r.span_slot;
+    }
     if (variant && *variant) snprintf(r.name, sizeof(r.name), "%s.%s", name, variant);
     else snprintf(r.name, sizeof(r.name), "%s", name);
     r.tag = ctx->prof_tag; r.bytes = bytes; r.flops = flops;
@@ -108,8 +113,10 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"linear_head", "AET_NO_LINEAR_HEAD", 1, 0},
     {"xchg_cap_floats", "AET_XCHG_CAP_FLOATS", 0, -1},
     {"nccl_max_ctas", "AET_NCCL_MAX_CTAS", 8, -1},
+    {"dual_acc", "AET_DUAL_ACC", 0, 1},
     {"rotate", "AET_NO_ROTATE", 1, 0},
-    {"pair", "AET_NO_PAIR", 1, 0},
+    {"stem", "AET_NO_STEM", 1, 0},
+    {"pair", "AET_PAIR", 0, 1},
 };
 }  // namespace
 
@@ -264,6 +271,7 @@ extern "C" void aet_context_destroy(aet_context *ctx) {
     }
     if (ctx->scratch_side) cudaFree(ctx->scratch_side);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->span_dev) cudaFree(ctx->span_dev);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -333,16 +341,33 @@ extern "C" int aet_context_profile(aet_context *ctx, int enable) {
     ctx->profiling = enable != 0;
     ctx->records.clear();
     ctx->event_next = 0;
+    ctx->span_ptr = nullptr;
+    if (enable) {
+        if (!ctx->span_dev) AET_CUDA(cudaMalloc(&ctx->span_dev, (size_t)kMaxSpanSlots * 2 * sizeof(unsigned long long)));
+        std::vector<unsigned long long> init((size_t)kMaxSpanSlots * 2);
+        for (int i = 0; i < kMaxSpanSlots; ++i) { init[2 * i] = ~0ull; init[2 * i + 1] = 0ull; }
+        AET_CUDA(cudaMemcpy(ctx->span_dev, init.data(), init.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice));
+    }
     return AET_OK;
 }
 
 extern "C" int aet_context_profile_read(aet_context *ctx, aet_kernel_time *table, int capacity, int *count) {
     if (!ctx || !table || !count) { aet_set_error("null argument"); return AET_E_INVALID; }
     AET_CUDA(cudaStreamSynchronize(ctx->stream));
+    std::vector<unsigned long long> spans;
+    if (ctx->span_dev) {
+        spans.resize((size_t)kMaxSpanSlots * 2);
+        AET_CUDA(cudaMemcpy(spans.data(), ctx->span_dev, spans.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    }
     int n = 0;
     for (const ProfileRecord &r : ctx->records) {
         float ms = 0.f;
         if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
+        double span_ms = 0.0;
+        if (r.span_slot >= 0 && !spans.empty()) {
+            const unsigned long long t0 = spans[2 * (size_t)r.span_slot], t1 = spans[2 * (size_t)r.span_slot + 1];
+            if (t0 != ~0ull && t1 > t0) span_ms = (double)(t1 - t0) * 1e-6;
+        }
         char label[sizeof(table[0].name)];
         if (r.tag >= 0) snprintf(label, sizeof(label), "%s#%d", r.name, r.tag);   // kernels of a network carry their layer
         else snprintf(label, sizeof(label), "%s", r.name);
@@ -359,6 +384,7 @@ extern "C" int aet_context_profile_read(aet_context *ctx, aet_kernel_time *table
         }
         table[k].launches += 1;
         table[k].total_ms += ms;
+        table[k].span_ms += span_ms;
     }
     *count = n;
     return AET_OK;

@@ -307,7 +307,14 @@ def roofline_of(table, peaks, tf32_burst, tf32_loop):
                     peak_source=peaks["source"] + " copy bandwidth (MEASURED_PEAKS.json)", algo_per_launch=top["algo_bytes"])
     roof.update(frac=roof["achieved"] / roof["peak"], traffic=NCU_TRAFFIC_BYTES.get(top["name"]), kernel=top["name"],
                 share_of_step=top["total_ms"] / total_kernel_ms, avg_us=avg_s * 1e6)
+    if top.get("span_ms", 0) > 0 and top["algo_flops"] > 0:
+        # the same launches on the device's own clock: last CTA exit - first CTA entry, without the launch latency and
+        # the event bracket that `avg_us` (and `achieved`, `frac`) include
+        span_s = top["span_ms"] / top["launches"] / 1000.0
+        roof["device_span_us"] = span_s * 1e6
+        roof["frac_device_span"] = top["algo_flops"] / span_s / 1e12 / roof["peak"]
     kernels = [dict(name=r["name"], launches=r["launches"], avg_us=1000.0 * r["total_ms"] / r["launches"],
+                    span_us=(1000.0 * r["span_ms"] / r["launches"]) if r.get("span_ms", 0) > 0 else None,
                     share=r["total_ms"] / total_kernel_ms,
                     gbs=(r["algo_bytes"] / (r["total_ms"] / r["launches"] / 1000.0) / 1e9) if r["algo_bytes"] else None,
                     tflops=(r["algo_flops"] / (r["total_ms"] / r["launches"] / 1000.0) / 1e12) if r["algo_flops"] else None)

@@ -102,7 +102,7 @@ int          aet_context_set_parity(aet_context *ctx, aet_parity_mode mode);
 int          aet_context_set_math(aet_context *ctx, aet_math_mode mode);
 int          aet_context_synchronize(aet_context *ctx);
 /* Behaviour switches (kernel choice, fusions, stream overlap), by name: "rows", "rows_fprop", "rows_dgrad",
- * "smerge", "ksplit", "mt2", "rows_multi", "par_epilogue", "fc_alias", "epilogue_stats", "thin", "pair", "rotate",
+ * "smerge", "ksplit", "mt2", "rows_multi", "par_epilogue", "fc_alias", "epilogue_stats", "thin", "pair", "rotate", "dual_acc",
  * "overlap_wgrad", "wgrad_splits", "bn_tile", "gather_only" (take effect at the next launch), "fuse",
  * "linear_head", "xchg_cap_floats" (read when a network is built / the exchange is exported).  The matching
  * AET_* environment variables only give the initial values and are read once, in aet_context_create. */
@@ -129,6 +129,8 @@ typedef struct aet_kernel_time {
     double total_ms;
     double algo_bytes;   /* algorithmic bytes moved per launch (HBM-bound kernels), else 0 */
     double algo_flops;   /* algorithmic FLOPs per launch (tensor-bound kernels), else 0 */
+    double span_ms;      /* convolution kernels: sum over the launches of (last CTA exit - first CTA entry) on the device's
+                          * own clock, i.e. the time without launch latency and event brackets; 0 where not recorded */
 } aet_kernel_time;
 int          aet_context_profile(aet_context *ctx, int enable);
 int          aet_context_profile_read(aet_context *ctx, aet_kernel_time *table, int capacity, int *count);

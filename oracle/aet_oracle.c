@@ -1104,3 +1104,20 @@ void aeto_conv_backward_ex(const float *x, const float *weights, const float *de
             }
         }
 }
+
+/* mtcs/MtcsConvLayer.c:494-524 (scal, scal, axpy, axpy, mul, axpy, adam_kernel, fill), element by element */
+void aeto_adam_update(float *w, float *d, float *m, float *v, float B1, float B2, float eps, float decay, float rate, size_t n,
+                      int batch, int t) {
+    for (size_t i = 0; i < n; ++i) {
+        m[i] *= B1;
+        v[i] *= B2;
+        d[i] += (-decay * batch) * w[i];
+        m[i] += (1 - B1) * d[i];
+        d[i] = d[i] * d[i];
+        v[i] += (1 - B2) * d[i];
+        float mhat = m[i] / (1.f - powf(B1, t));
+        float vhat = v[i] / (1.f - powf(B2, t));
+        w[i] = w[i] + rate * mhat / (sqrtf(vhat) + eps);
+        d[i] = 0;
+    }
+}

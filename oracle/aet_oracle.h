@@ -143,6 +143,10 @@ void   aeto_conv_backward_ex(const float *x, const float *weights, const float *
                              int batch, int c, int h, int w, int n, int size, int stride_x, int stride_y, int pad, int groups,
                              int dilation);
 
+/* adam_update_gpu, mtcs/MtcsConvLayer.c:494-524: one parameter array; d (the pending update) is zeroed. */
+void   aeto_adam_update(float *w, float *d, float *m, float *v, float B1, float B2, float eps, float decay, float rate, size_t n,
+                        int batch, int t);
+
 /* synthetic tensors (aet_rng.h) exposed for bindings */
 void aeto_fill_uniform(float *dst, size_t n, uint64_t seed, uint64_t tensor_id);
 void aeto_fill_normal(float *dst, size_t n, uint64_t seed, uint64_t tensor_id, float mean, float stddev);

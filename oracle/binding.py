@@ -100,6 +100,7 @@ class Oracle:
         L.aeto_top_k.argtypes = [_f, C.c_int, C.c_int, _i]
         L.aeto_transpose_matrix.argtypes = [_f, C.c_int, C.c_int]
         L.aeto_augment_image.argtypes = [_f, C.c_int, C.c_int, C.c_int, _f, C.c_int] + [C.c_float] * 5 + [C.c_int] + [C.c_float] * 3
+        L.aeto_adam_update.argtypes = [_f, _f, _f, _f, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, C.c_size_t, C.c_int, C.c_int]
         L.aeto_fill_uniform.argtypes = [_f, C.c_size_t, C.c_uint64, C.c_uint64]
         L.aeto_fill_normal.argtypes = [_f, C.c_size_t, C.c_uint64, C.c_uint64, C.c_float, C.c_float]
 
@@ -285,6 +286,10 @@ class Oracle:
         dst = np.zeros((c, size, size), np.float32)
         self.lib.aeto_augment_image(_fp(src), c, sh, sw, _fp(dst), size, rad, scale, dx, dy, aspect, int(flip), dhue, dsat, dexp)
         return dst
+
+    def adam_update(self, w, d, m, v, B1, B2, eps, decay, rate, batch, t):
+        """In place on float32 numpy arrays (views of the oracle network's storage are fine)."""
+        self.lib.aeto_adam_update(_fp(w), _fp(d), _fp(m), _fp(v), B1, B2, eps, decay, rate, w.size, batch, t)
 
     def dropout_forward(self, x, r, probability):
         x = _arr(x).copy()

@@ -123,29 +123,37 @@ def test_conv_thin_tf32(aet, ctx, oracle, shape):
 # split over a two-CTA cluster, two filter tiles), so these shapes are checked at that size and the path each
 # launch took is asserted by its label.  N = 112 is the smallest batch above the two-tile threshold.
 BENCH_SHAPES = [
-    # shape, CTA pairs on/off, {kernel: variant} expected on a 148-SM part
-    ((128, 64, 16, 16, 128, 3, 1, 1, 2), 1, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2",
-                                             "conv_wgrad_tma_rows": "n64_sp49"}),
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), 1, {"conv_fprop_tma_rows": "mt1_n128x2_p2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2_p2",
-                                            "conv_wgrad_tma_rows": "n128_sp24"}),
-    ((112, 64, 16, 16, 128, 3, 1, 1, 0), 1, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2"}),
-    ((128, 64, 16, 16, 128, 3, 1, 1, 2), 0, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), 0, {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2"}),
-    ((16, 64, 16, 16, 128, 3, 1, 1, 1), 1, {"conv_fprop_tma_rows": "*_p2", "conv_dgrad_tma_rows": "*_p2"}),    # pairs at a small batch
+    # shape, context options, {kernel: variant} expected on a 148-SM part
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {}, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1",
+                                              "conv_wgrad_tma_rows": "n64_sp49"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {}, {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2",
+                                             "conv_wgrad_tma_rows": "n128_sp24"}),
+    ((112, 64, 16, 16, 128, 3, 1, 1, 0), {}, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
+    # CTA pairs (cta_group::2 MMAs, each CTA loading half of the filter tile), off by default
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {"pair": 1}, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"pair": 1}, {"conv_fprop_tma_rows": "mt1_n128x2_p2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2_p2"}),
+    ((16, 64, 16, 16, 128, 3, 1, 1, 1), {"pair": 1}, {"conv_fprop_tma_rows": "*_p2", "conv_dgrad_tma_rows": "*_p2"}),
+    # two accumulators per tile (alternate filter rows), off by default; also without the rotated K order
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"dual_acc": 1}, {"conv_fprop_tma_rows": "mt1d_n128x2", "conv_dgrad_tma_rows": "mt1d_n128x1_ks2"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"dual_acc": 1, "pair": 1, "rotate": 0},
+     {"conv_fprop_tma_rows": "mt1d_n128x2_p2", "conv_dgrad_tma_rows": "mt1d_n128x1_ks2_p2"}),
 ]
 
 
-@pytest.mark.parametrize("shape,pair,variants", BENCH_SHAPES)
-def test_conv_benchmark_shapes_at_benchmark_batch(aet, ctx, oracle, shape, pair, variants):
+@pytest.mark.parametrize("shape,options,variants", BENCH_SHAPES)
+def test_conv_benchmark_shapes_at_benchmark_batch(aet, ctx, oracle, shape, options, variants):
     ctx.set_math(aet.MATH_TF32)
-    ctx.set_option("pair", pair)
+    saved = {name: ctx.get_option(name) for name in options}
+    for name, value in options.items():
+        ctx.set_option(name, value)
     ctx.profile(1)
     try:
         got, ref = conv_case(aet, ctx, oracle, *shape, seed=500 + shape[0], threads=True)
         used = variants_used(ctx)
     finally:
         ctx.profile(0)
-        ctx.set_option("pair", 1)
+        for name, value in saved.items():
+            ctx.set_option(name, value)
     for kernel, variant in variants.items():
         if variant.startswith("*"):
             assert any(u.startswith(kernel + ".") and u.endswith(variant[1:]) for u in used), (kernel, variant, sorted(used))

@@ -91,8 +91,8 @@ def test_small_cnn_training_matches_oracle(aet, ctx, oracle64, mode):
 
 
 # code path of every row-sharing launch of the small CNN at the benchmark batch on a 148-SM part
-BENCH_VARIANTS = {"conv_fprop_tma_rows.mt2e_n128x1_p2#2", "conv_dgrad_tma_rows.sm_mt2_n192x1_p2#2", "conv_wgrad_tma_rows.n64_sp49#2",
-                  "conv_fprop_tma_rows.mt1_n128x2_p2#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2_p2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
+BENCH_VARIANTS = {"conv_fprop_tma_rows.mt2e_n128x1#2", "conv_dgrad_tma_rows.sm_mt2_n192x1#2", "conv_wgrad_tma_rows.n64_sp49#2",
+                  "conv_fprop_tma_rows.mt1_n128x2#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
 
 
 @pytest.mark.parametrize("batch", [16, 128])
@@ -238,8 +238,9 @@ def test_fused_bn_pool_path_matches_layer_by_layer(aet, ctx, oracle):
     """Inside a network a BN convolution produces the following max-pool's output itself and folds the
     pool's backward into its BN backward kernels; the context option "fuse" = 0 runs every layer's own kernels instead.
     Forward results are bit-identical; gradients differ only by summation order.  (The linear classifier
-    head is switched off in both runs: it changes the arithmetic, see the next test.)"""
-    f = _run_variant(aet, ctx, oracle, {"linear_head": 0})
+    head and the first layer's pool-sized backward are switched off in both runs: they change the arithmetic and
+    have their own tests below.)"""
+    f = _run_variant(aet, ctx, oracle, {"linear_head": 0, "stem": 0})
     u = _run_variant(aet, ctx, oracle, {"fuse": 0})
     for a, b in zip(f["outs"], u["outs"]):
         assert np.array_equal(a, b)
@@ -250,6 +251,109 @@ def test_fused_bn_pool_path_matches_layer_by_layer(aet, ctx, oracle):
             assert rel_l2(a, b) < 2e-4, (key, rel_l2(a, b))   # FP32 partial sums grouped differently
     assert np.allclose(f["losses"], u["losses"], rtol=1e-4)
     assert f["launches"] < u["launches"]          # fewer launches when fused
+
+
+STEM_CFG = """[net]
+batch={batch}
+width={w}
+height={h}
+channels={c}
+learning_rate=0.1
+momentum=0.9
+decay=0.0005
+policy=constant
+max_batches=1000
+
+[convolutional]
+filters={k}
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation={act}
+
+[maxpool]
+size=2
+stride=2
+
+[convolutional]
+filters=10
+size=1
+stride=1
+pad=0
+activation=linear
+
+[avgpool]
+
+[softmax]
+groups=1
+"""
+
+
+@pytest.mark.parametrize("batch,c,h,w,k,act,mode", [
+    (128, 3, 32, 32, 64, "leaky", ob.MODE_MTCS),     # the benchmark network's first layer
+    (5, 3, 24, 40, 64, "relu", ob.MODE_MTCS),        # ragged: rows not a multiple of the Gram strip, non-square
+    (7, 1, 16, 16, 64, "leaky", ob.MODE_CPU),        # one input channel, the CPU classes' formulas
+    (3, 2, 10, 6, 128, "logistic", ob.MODE_MTCS),    # 512 threads per block, a slow-path activation
+    (2, 3, 8, 80, 64, "leaky", ob.MODE_MTCS),        # three chunks of windows per pool row, the last one partial
+])
+def test_first_layer_pool_sized_backward(aet, ctx, oracle64, batch, c, h, w, k, act, mode):
+    """The first convolution (BN, fused 2x2 max-pool) takes its scale / shift / weight gradients from the pool-sized
+    tensors and the Gram matrix of the input patches instead of forming the full-resolution delta.  Against the FP64
+    oracle and against the general path (option "stem" = 0), 3xTF32 math: the same gradients to 2e-5 of their norm;
+    the delta a host tap reads afterwards is the general path's."""
+    from oracle import cfgfile
+    import aet_cnn_b200.synth as synth
+    text = STEM_CFG.format(batch=batch, c=c, h=h, w=w, k=k, act=act)
+    ctx.set_math(aet.MATH_3XTF32)
+    ctx.set_parity(mode)
+    x = synth.uniform((batch, c, h, w), 77, 0)
+    _, truth = synth.labels(batch, 10, 77, 1)
+    w0 = synth.normal((k, c, 3, 3), 77, 2, 0.0, float(np.sqrt(2.0 / (9 * c))))
+    w1 = synth.normal((10, k, 1, 1), 77, 3, 0.0, float(np.sqrt(2.0 / k)))
+    res = {}
+    try:
+        for stem in (1, 0):
+            ctx.set_option("stem", stem)
+            net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+            ctx.set_option("stem", 1)
+            net.layer(0).write(aet.P_WEIGHTS, w0)
+            net.layer(2).write(aet.P_WEIGHTS, w1)
+            net.input.write(x); net.truth.write(truth)
+            ctx.profile(1)
+            net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+            net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+            records = ctx.profile_read()
+            ctx.profile(0)
+            names = {r["name"].split(".")[0].split("#")[0] for r in records}
+            full = [r["name"] for r in records]
+            assert ("stem_bwd_sparse" in names) == bool(stem), sorted(names)
+            assert any(n.startswith("conv_wgrad") and n.endswith("#0") for n in full) != bool(stem), sorted(full)
+            res[stem] = {p: net.layer(0).read(getattr(aet, p)) for p in ("P_WEIGHT_UPDATES", "P_SCALE_UPDATES", "P_BIAS_UPDATES", "P_DELTA")}
+            ctx.check()
+            # a second pass accumulates on top of the first (the gradient arena is only cleared by the update)
+            net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+            net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+            twice = net.layer(0).read(aet.P_WEIGHT_UPDATES)
+            assert rel_l2(twice, 2 * res[stem]["P_WEIGHT_UPDATES"]) < 1e-5
+            net.close()
+    finally:
+        ctx.set_option("stem", 1)
+        ctx.set_math(aet.MATH_TF32)
+        ctx.set_parity(ob.MODE_MTCS)
+    opts, specs = cfgfile.network_spec(text, batch)
+    onet = oracle64.net(specs, batch, c, h, w, mode=mode, threads=os.cpu_count() or 1)
+    onet.set_param(0, ob.P_WEIGHTS, w0)
+    onet.set_param(2, ob.P_WEIGHTS, w1)
+    onet.forward(x, truth)
+    onet.backward(x)
+    for p in ("P_WEIGHT_UPDATES", "P_SCALE_UPDATES"):
+        ref = onet.param(0, getattr(ob, p))
+        assert rel_l2(res[1][p], ref) < 2e-5, (p, rel_l2(res[1][p], ref), rel_l2(res[0][p], ref))
+        assert rel_l2(res[1][p], res[0][p]) < 2e-4, (p, rel_l2(res[1][p], res[0][p]))   # the general path's 3xTF32 GEMM is the looser one
+    if mode == ob.MODE_MTCS:
+        assert rel_l2(res[1]["P_BIAS_UPDATES"], res[0]["P_BIAS_UPDATES"]) < 2e-5
+    assert rel_l2(res[1]["P_DELTA"], res[0]["P_DELTA"]) < 1e-5
 
 
 def test_linear_head_matches_the_separate_layers(aet, ctx, oracle):

@@ -148,6 +148,43 @@ def test_subdivisions_accumulate_gradients_and_update_once(aet, ctx, oracle64, s
         ctx.set_math(aet.MATH_TF32)
 
 
+def test_adam_update_matches_the_reference_routine(aet, ctx, oracle64):
+    """[net] adam=1: adam_update_gpu (mtcs/MtcsConvLayer.c:494-524) applied to weights, biases and scales, against the
+    oracle's gradients (3xTF32 math) pushed through the restated routine, four steps."""
+    import aet_cnn_b200.synth as synth
+    batch = 4
+    text = tiny_cfg(batch=batch, extra="policy=constant\nadam=1\nB1=0.9\nB2=0.999\neps=0.000001")
+    opts, specs = cfgfile.network_spec(text)
+    ctx.set_math(aet.MATH_3XTF32)
+    try:
+        net = aet.NNetwork(ctx, cfg_text=text, train=1)
+        onet = oracle64.net(specs, batch, 3, 8, 8, mode=ob.MODE_MTCS)
+        w0 = synth.normal((8, 3, 3, 3), 19, 1, 0.0, 0.3)
+        w2 = synth.normal((5, 8, 1, 1), 19, 2, 0.0, 0.3)
+        net.layer(0).write(aet.P_WEIGHTS, w0); net.layer(2).write(aet.P_WEIGHTS, w2)
+        onet.set_param(0, ob.P_WEIGHTS, w0); onet.set_param(2, ob.P_WEIGHTS, w2)
+        pairs = [(0, ob.P_WEIGHTS, ob.P_WEIGHT_UPDATES), (0, ob.P_BIASES, ob.P_BIAS_UPDATES), (0, ob.P_SCALES, ob.P_SCALE_UPDATES),
+                 (2, ob.P_WEIGHTS, ob.P_WEIGHT_UPDATES), (2, ob.P_BIASES, ob.P_BIAS_UPDATES)]
+        mom = {k: (np.zeros(onet.param(k[0], k[1]).size, np.float32), np.zeros(onet.param(k[0], k[1]).size, np.float32)) for k in pairs}
+        for step in range(4):
+            x = synth.uniform((batch, 3, 8, 8), 19, 10 + 2 * step)
+            _, t = synth.labels(batch, 5, 19, 11 + 2 * step)
+            loss = net.train(x, t)
+            onet.forward(x, t)
+            onet.backward(x)
+            assert loss == pytest.approx(onet.cost() / batch, rel=2e-4)
+            for k in pairs:
+                oracle64.adam_update(onet.param(k[0], k[1]), onet.param(k[0], k[2]), mom[k][0], mom[k][1], 0.9, 0.999, 1e-6,
+                                     opts["decay"], opts["learning_rate"], batch, step + 1)
+            for layer, wsel, _ in pairs:
+                got = net.layer(layer).read({ob.P_WEIGHTS: aet.P_WEIGHTS, ob.P_BIASES: aet.P_BIASES, ob.P_SCALES: aet.P_SCALES}[wsel])
+                assert rel_l2(got, onet.param(layer, wsel)) < 2e-4, (step, layer, wsel)
+        ctx.check()
+        net.close()
+    finally:
+        ctx.set_math(aet.MATH_TF32)
+
+
 def test_update_scrubs_non_finite_values_like_the_reference_gpu_update(aet, ctx, oracle):
     """mtcs/MtcsConvLayer.c:586-587: before the update, NaN/Inf pending weight updates become 0 and NaN/Inf weights
     become 1/(index+1); the status word then reports AET_E_NAN (informational).  The CPU formulation does not scrub."""
