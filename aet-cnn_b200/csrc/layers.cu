@@ -420,10 +420,10 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
             if (!l->stem_gram_ready) AET_TRY(k_stem_gram(l, state.input->d));
             l->stem_gram_ready = false;
             AET_TRY(k_stem_backward(l, l->fused_pool, state.input->d));
-            if (l->ctx->overlap_wgrad) AET_TRY(side_begin(l->ctx));   // behind the Gram kernels, after the pool-sized pass
-            const int fr = k_stem_finish(l, layer_G(l), 1);
-            side_end(l->ctx);
-            AET_TRY(fr);
+            // The Gram kernels were queued on the side stream during the forward pass and the later layers' weight
+            // gradients behind them; this is the last kernel of the backward pass, so the streams join here.
+            AET_TRY(side_join(l->ctx));
+            AET_TRY(k_stem_finish(l, layer_G(l), 1));
             l->delta->lazy_zero = false;
             l->stem_delta_stale = true;
             return AET_OK;

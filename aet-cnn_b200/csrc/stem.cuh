@@ -55,12 +55,12 @@ __device__ __forceinline__ unsigned mulhi_div(unsigned n, unsigned mul, unsigned
 // at once, 16-byte loads) around the argmax pixel to its 27 accumulators.  The items' inputs arrive by cp.async two
 // items ahead into three rotating shared-memory buffers, so one barrier per item is enough: the buffer refilled in
 // iteration i was last read in iteration i - 1.
-template <int THREADS, int MINB>
+template <int THREADS, int MINB, int UNROLL>
 __global__ void __launch_bounds__(THREADS, MINB) stem_bwd_sparse_kernel(const StemSparseArgs a) {
     extern __shared__ float4 stem_smem[];
     span_begin(a.span);
     pdl_enter();
-    const int ocp = a.ocp;
+    constexpr int ocp = THREADS / 4;
     // per buffer: dv[16][ocp] floats, ym[16][ocp] floats, px[4][34] float4, code[16][ocp] bytes
     const int buf_bytes = STEM_WIN * ocp * 9 + 4 * STEM_COLS * 16;
     unsigned char *smem = reinterpret_cast<unsigned char *>(stem_smem);
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(THREADS, MINB) stem_bwd_sparse_kernel(const St
         const unsigned char *cds = buf + STEM_WIN * ocp * 8 + 4 * STEM_COLS * 16;
         const int chunk = item - (int)mulhi_div((unsigned)item, a.div_chunks_mul, a.div_chunks_shr) * a.chunks;
         const int wlim = a.OW - chunk * STEM_WIN;   // windows of this item inside the row
-#pragma unroll
+#pragma unroll UNROLL
         for (int u = 0; u < STEM_WIN / 4; ++u) {
             const int w = g + 4 * u;
             const int cd = cds[w * ocp + k];
@@ -238,19 +238,32 @@ __global__ void __launch_bounds__(STEM_GRAM_COMBOS * STEM_GRAM_ROWS) stem_gram_k
     span_end(a.span);
 }
 
-// Sums the Gram partials of all blocks, in double and in a fixed order: 8 threads per entry.
-__global__ void __launch_bounds__(256) stem_gram_finish_kernel(const float *partial, int blocks, double *gram) {
+// Sums the Gram partials of all blocks, in double and in a fixed order: 32 threads per entry, four independent loads
+// in flight per thread.
+__global__ void __launch_bounds__(1024) stem_gram_finish_kernel(const float *partial, int blocks, double *gram) {
     pdl_enter();
-    __shared__ double part[8][32];
+    __shared__ double part[32][33];
     const int i = threadIdx.x & 31, lane = threadIdx.x >> 5;
     const int e = blockIdx.x * 32 + i;
-    double s = 0.0;
-    if (e < STEM_GRAM_PART)
-        for (int b = lane; b < blocks; b += 8) s += (double)__ldg(partial + (size_t)b * STEM_GRAM_PART + e);
-    part[lane][i] = s;
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    if (e < STEM_GRAM_PART) {
+        const float *src = partial + e;
+        int b = lane;
+        for (; b + 96 < blocks; b += 128) {
+            const float v0 = __ldg(src + (size_t)b * STEM_GRAM_PART), v1 = __ldg(src + (size_t)(b + 32) * STEM_GRAM_PART);
+            const float v2 = __ldg(src + (size_t)(b + 64) * STEM_GRAM_PART), v3 = __ldg(src + (size_t)(b + 96) * STEM_GRAM_PART);
+            s0 += (double)v0; s1 += (double)v1; s2 += (double)v2; s3 += (double)v3;
+        }
+        for (; b < blocks; b += 32) s0 += (double)__ldg(src + (size_t)b * STEM_GRAM_PART);
+    }
+    part[lane][i] = (s0 + s1) + (s2 + s3);
     __syncthreads();
-    if (lane == 0 && e < STEM_GRAM_PART)
-        gram[e] = ((part[0][i] + part[1][i]) + (part[2][i] + part[3][i])) + ((part[4][i] + part[5][i]) + (part[6][i] + part[7][i]));
+    if (lane == 0 && e < STEM_GRAM_PART) {
+        double t[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+        for (int q = 0; q < 32; ++q) t[q & 3] += part[q][i];
+        gram[e] = (t[0] + t[1]) + (t[2] + t[3]);
+    }
 }
 
 struct StemFinishArgs {
@@ -294,24 +307,39 @@ __device__ __forceinline__ void bn_bwd_channel(double s1, double s2, double m, i
 // dW[k][t] = ka * T1[k][t] + kb * sum_u W[k][u] (G[u][t] - S[u] S[t] / pixels) + kc * S[t].
 __global__ void __launch_bounds__(STEM_TAPS * STEM_FIN_LANES) stem_bwd_finish_kernel(const StemFinishArgs a) {
     pdl_enter();
+    __shared__ double gram[STEM_GRAM_PART];
     __shared__ double part[STEM_FIN_LANES][STEM_TAPS];
-    __shared__ double colsum[STEM_TAPS];
     __shared__ float wk[STEM_TAPS];
     __shared__ double ssum[2][2];
     __shared__ float kcoef[3];
     const int k = blockIdx.x, t = threadIdx.x % STEM_TAPS, lane = threadIdx.x / STEM_TAPS;
     const int warp = threadIdx.x >> 5, wl = threadIdx.x & 31;
-    if (lane == 0) {
-        wk[t] = a.w[(size_t)k * STEM_TAPS + t];
-        colsum[t] = (t & 3) < 3 ? a.gram[STEM_GRAM_COMBOS * STEM_GRAM_ENTRY + (t >> 2) * 3 + (t & 3)] : 0.0;
+    for (int i = threadIdx.x; i < STEM_GRAM_PART; i += blockDim.x) gram[i] = a.gram[i];
+    if (lane == 0) wk[t] = a.w[(size_t)k * STEM_TAPS + t];
+    {
+        const float *src = a.partial_t + (size_t)k * STEM_TAPS + t;
+        const size_t stride = (size_t)a.ocp * STEM_TAPS;
+        double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+        int b = lane;
+        for (; b + 3 * STEM_FIN_LANES < a.blocks; b += 4 * STEM_FIN_LANES) {
+            const float v0 = __ldg(src + b * stride), v1 = __ldg(src + (b + STEM_FIN_LANES) * stride);
+            const float v2 = __ldg(src + (b + 2 * STEM_FIN_LANES) * stride), v3 = __ldg(src + (b + 3 * STEM_FIN_LANES) * stride);
+            s0 += (double)v0; s1 += (double)v1; s2 += (double)v2; s3 += (double)v3;
+        }
+        for (; b < a.blocks; b += STEM_FIN_LANES) s0 += (double)__ldg(src + b * stride);
+        part[lane][t] = (s0 + s1) + (s2 + s3);
     }
-    double s = 0.0;
-    for (int b = lane; b < a.blocks; b += STEM_FIN_LANES) s += (double)__ldg(a.partial_t + ((size_t)b * a.ocp + k) * STEM_TAPS + t);
-    part[lane][t] = s;
-    if (warp >= 14 && warp < 18) {   // four warps past the tap lanes' first rows: S1 and S2, two warps each
+    if (warp >= 14 && warp < 18) {   // the last four warps also form S1 and S2, two warps each
         const int which = (warp - 14) >> 1, half = (warp - 14) & 1;
-        double v = 0.0;
-        for (int b = half * 32 + wl; b < a.blocks; b += 64) v += (double)__ldg(a.partial_s + (size_t)b * 2 * a.ocp + which * a.ocp + k);
+        const float *src = a.partial_s + which * a.ocp + k;
+        double v0 = 0.0, v1 = 0.0;
+        int b = half * 32 + wl;
+        for (; b + 64 < a.blocks; b += 128) {
+            const float x0 = __ldg(src + (size_t)b * 2 * a.ocp), x1 = __ldg(src + (size_t)(b + 64) * 2 * a.ocp);
+            v0 += (double)x0; v1 += (double)x1;
+        }
+        for (; b < a.blocks; b += 64) v0 += (double)__ldg(src + (size_t)b * 2 * a.ocp);
+        double v = v0 + v1;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         if (wl == 0) ssum[which][half] = v;
@@ -329,17 +357,21 @@ __global__ void __launch_bounds__(STEM_TAPS * STEM_FIN_LANES) stem_bwd_finish_ke
     double t1 = 0.0;
 #pragma unroll
     for (int q = 0; q < STEM_FIN_LANES; ++q) t1 += part[q][t];
-    double wg = 0.0, ws = 0.0;
+    const double *colsum = gram + STEM_GRAM_COMBOS * STEM_GRAM_ENTRY;   // [(r, s)][3]
     const int rb = t / 12, sb = (t >> 2) % 3, cb = t & 3;
-    for (int u = 0; u < STEM_TAPS; ++u) {
-        if ((u & 3) == 3) continue;
-        const int ra = u / 12, sa = (u >> 2) % 3, ca = u & 3;
-        const double wu = (double)wk[u];
-        if (cb < 3) wg += wu * a.gram[((ra * 3 + rb) * 3 + sb) * STEM_GRAM_ENTRY + (sa * 3 + ca) * 3 + cb];
-        ws += wu * colsum[u];
+    double wg = 0.0, ws = 0.0;
+    if (cb < 3) {
+        for (int u = 0; u < STEM_TAPS; ++u) {
+            if ((u & 3) == 3) continue;
+            const int ra = u / 12, sa = (u >> 2) % 3, ca = u & 3;
+            const double wu = (double)wk[u];
+            wg += wu * gram[((ra * 3 + rb) * 3 + sb) * STEM_GRAM_ENTRY + (sa * 3 + ca) * 3 + cb];
+            ws += wu * colsum[(u >> 2) * 3 + ca];
+        }
     }
-    const double t2 = wg - ws * colsum[t] / a.pixels;
-    float v = cb == 3 ? 0.f : (float)((double)kcoef[0] * t1 + (double)kcoef[1] * t2 + (double)kcoef[2] * colsum[t]);
+    const double st = cb < 3 ? colsum[(t >> 2) * 3 + cb] : 0.0;
+    const double t2 = wg - ws * st / a.pixels;
+    float v = cb == 3 ? 0.f : (float)((double)kcoef[0] * t1 + (double)kcoef[1] * t2 + (double)kcoef[2] * st);
     float *dst = a.dw + (size_t)k * STEM_TAPS + t;
     if (a.accumulate) v += *dst;
     *dst = v;
@@ -384,7 +416,7 @@ int k_stem_gram(aet_layer *l, const float *x_in) {
         AET_TRY(aet_check_launch("stem_gram"));
     }
     LaunchScope s(ctx, "stem_gram_finish", 0, 0);
-    launch_k(ctx->stream, (STEM_GRAM_PART + 31) / 32, 256, 0, stem_gram_finish_kernel, (const float *)l->stem_gram_partial, blocks, l->stem_gram);
+    launch_k(ctx->stream, (STEM_GRAM_PART + 31) / 32, 1024, 0, stem_gram_finish_kernel, (const float *)l->stem_gram_partial, blocks, l->stem_gram);
     return aet_check_launch("stem_gram_finish");
 }
 
@@ -405,7 +437,7 @@ int k_stem_backward(aet_layer *l, aet_layer *pool, const float *x_in) {
     a.items = l->batch * pool->oh * a.chunks;
     stem_fastdiv((unsigned)a.chunks, a.div_chunks_mul, a.div_chunks_shr);
     stem_fastdiv((unsigned)pool->oh, a.div_oh_mul, a.div_oh_shr);
-    void (*kernel)(const StemSparseArgs) = threads <= 256 ? stem_bwd_sparse_kernel<256, 2> : stem_bwd_sparse_kernel<512, 1>;
+    void (*kernel)(const StemSparseArgs) = threads <= 256 ? stem_bwd_sparse_kernel<256, 3, 1> : stem_bwd_sparse_kernel<512, 1, 2>;
     AET_TRY(ctx_smem_attr(ctx, kernel, 160 * 1024));
     if (!l->stem_resident &&
         (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&l->stem_resident, kernel, threads, smem) != cudaSuccess || l->stem_resident < 1))
