@@ -74,7 +74,7 @@ enum AetOption {
     OPT_FUSE,              // network-level fusions (BN + pool, classifier head), read when a network is built   AET_NO_FUSE
     OPT_LINEAR_HEAD,       // classifier head on the pooled vectors, read when a network is built          AET_NO_LINEAR_HEAD
     OPT_XCHG_CAP_FLOATS,   // capacity of the peer-exchange buffer (0 = default)   AET_XCHG_CAP_FLOATS
-    OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice)   AET_NCCL_MAX_CTAS
+    OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice, -1 = by rank count)   AET_NCCL_MAX_CTAS
     OPT_DUAL_ACC,          // two accumulators per tile when a CTA owns one tile (row-sharing kernels; off by default)   AET_DUAL_ACC
     OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
     OPT_STEM,              // first convolution + BN + 2x2 max-pool: weight gradient from the pool-sized tensors   AET_NO_STEM
@@ -290,6 +290,7 @@ struct aet_network {
     size_t xchg_cap = 0;
     unsigned long long *xchg_epoch = nullptr;   // device-side step counter
     unsigned int *xchg_ticket = nullptr;        // blocks of the publish kernel that have finished
+    int *xchg_gate = nullptr;                   // 1 / 0: this step's slices of all ranks arrived / the wait ran out
     size_t tail_lo = 0, tail_n = 0;             // arena range summed through the exchange this step (0: none)
     cudaEvent_t ev_uploaded = nullptr;   // after the H2D copies of a train step fed from the caller's pinned buffers
     long launches_per_step = 0;

@@ -1144,6 +1144,7 @@ struct TailArgs {
     unsigned long long lo, n, cap;
     int world;
     int *status;
+    int *gate;   // written by tail_wait_kernel: 1 = every rank's slice of this step has arrived, 0 = the wait ran out
 };
 
 // Copies this rank's slice into its published buffer and raises its flag in every peer's memory: data,
@@ -1207,6 +1208,34 @@ __device__ __forceinline__ bool scrub4(float4 &w, float4 &u, int kind, size_t in
     return hit;
 }
 
+// One warp waits (bounded) until every rank has published its slice of this step and leaves the verdict in `gate`
+// for the update kernel that follows: a wait that runs out must stop the WHOLE update, not the blocks that happened
+// to notice, or the parameters would be left half updated.
+__global__ void tail_wait_kernel(const TailArgs t) {
+    pdl_enter();
+    const unsigned long long e = *t.epoch, parity = e & 1ull;
+    bool ok = true;
+    if ((int)threadIdx.x < t.world) {
+        const volatile unsigned long long *f = t.flags + parity * 16ull + threadIdx.x;
+        unsigned long long t0 = 0;
+        unsigned int spins = 0;
+        while (*f < e) {
+            if ((++spins & 255u) == 0u) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > g_flag_wait_limit_ns) { ok = false; break; }   // a peer never arrived: give up
+            }
+        }
+    }
+    const bool all_ok = __all_sync(0xffffffffu, ok);
+    __threadfence_system();   // acquire: the update kernel reads the peers' slices after their flags
+    if (threadIdx.x == 0) {
+        *t.gate = all_ok ? 1 : 0;
+        if (!all_ok && t.status) atomicOr(t.status, AET_STATUS_TIMEOUT);
+    }
+}
+
 // seg_table: four floats per segment {learning-rate multiplier, decay flag, scrub kind, first block (int bits)}
 __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float *G, const int *block_seg,
                                                        const float *seg_table, const float *hyper, const TailArgs t, int *status) {
@@ -1219,35 +1248,18 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
     const size_t i = ((size_t)blockIdx.x * TB + threadIdx.x) * 4;
     float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i);
     const size_t b0 = (size_t)blockIdx.x * TB * 4;
-    if (t.world > 1 && b0 >= t.lo && b0 < t.lo + t.n) {
-        // this block's gradients are the sum of every rank's published slice, added in rank order
-        __shared__ int ok;
-        if (threadIdx.x == 0) ok = 1;
-        __syncthreads();
-        const unsigned long long e = *t.epoch, parity = e & 1ull;
-        if ((int)threadIdx.x < t.world) {
-            const volatile unsigned long long *f = t.flags + parity * 16ull + threadIdx.x;
-            unsigned long long t0 = 0;
-            unsigned int spins = 0;
-            while (*f < e) {
-                if ((++spins & 255u) == 0u) {
-                    unsigned long long now;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                    if (t0 == 0) t0 = now;
-                    else if (now - t0 > g_flag_wait_limit_ns) { ok = 0; break; }   // a peer never arrived: give up
-                }
+    if (t.world > 1) {
+        // A peer's gradients never arrived (tail_wait_kernel gave up): no block updates anything, so that the
+        // parameters of this rank stay those of the last complete step.
+        if (*t.gate == 0) return;
+        if (b0 >= t.lo && b0 < t.lo + t.n) {
+            // this block's gradients are the sum of every rank's published slice, added in rank order
+            const unsigned long long parity = *t.epoch & 1ull;
+            g = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < t.world; ++q) {
+                const float4 v = __ldcv(reinterpret_cast<const float4 *>(t.peer_buf[q] + parity * t.cap + (i - t.lo)));
+                g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
             }
-            __threadfence_system();   // acquire: the peers' slices are read after their flags (the barrier passes it on)
-        }
-        __syncthreads();
-        if (!ok) {
-            if (threadIdx.x == 0 && t.status) atomicOr(t.status, AET_STATUS_TIMEOUT);
-            return;
-        }
-        g = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int q = 0; q < t.world; ++q) {
-            const float4 v = __ldcv(reinterpret_cast<const float4 *>(t.peer_buf[q] + parity * t.cap + (i - t.lo)));
-            g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
         }
     }
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
@@ -1874,7 +1886,9 @@ int k_sgd_arena(aet_network *net) {
         for (int q = 0; q < net->world; ++q) t.peer_buf[q] = reinterpret_cast<const float *>(net->xchg_peer[q] + kXchgFlagBytes);
         t.flags = reinterpret_cast<const volatile unsigned long long *>(net->xchg_local);
         t.epoch = net->xchg_epoch; t.lo = net->tail_lo; t.n = net->tail_n; t.cap = net->xchg_cap;
-        t.world = net->world; t.status = ctx->status_dev;
+        t.world = net->world; t.status = ctx->status_dev; t.gate = net->xchg_gate;
+        launch_k(ctx->stream, 1, 32, 0, tail_wait_kernel, t);
+        AET_TRY(aet_check_launch("grad_wait"));
     }
     launch_k(ctx->stream, net->n_blocks, TB, 0, sgd_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->block_seg,
                                                            net->seg_table, net->hyper_dev, t, ctx->status_dev);

@@ -86,12 +86,46 @@ def oracle_check(rank, world, local_rank, steps=2, batch=8):
     return errs
 
 
+def absent_peer(rank, world, local_rank, batch=16):
+    """A rank that sits out a step, seen from the other rank (peer exchange attached, 50 ms wait limit): the update's
+    gate kernel waits for a slice that is never published, gives up, and the whole update is skipped - the step
+    reports AET_E_TIMEOUT and the parameters are bit for bit those of the last complete step.  The absent rank leaves
+    between steps with nothing in flight; the ranks meet again on the host."""
+    text = open(os.path.join(aet.CFG_DIR, "cifar_small.cfg")).read()
+    ctx = aet.Context(local_rank)
+    net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+    bench.init_weights(aet, synth, net, 3)
+    net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
+    net.comm_exchange_attach(par.all_gather_bytes(net.comm_exchange_export()))
+    ctx.set_wait_limit(50 * 1000 * 1000)
+    x, truth = synth.uniform((batch, 3, 32, 32), 9, rank), synth.labels(batch, 10, 9, 100 + rank)[1]
+    for _ in range(2):
+        net.train(x, truth)
+    ctx.check()
+    before = net.param_hash()
+    torch.cuda.synchronize()
+    dist.barrier()
+    res = {}
+    if rank == 0:
+        message = ""
+        try:
+            net.train(x, truth)
+        except Exception as e:   # noqa: BLE001 - the binding raises its own error type with the status code in the text
+            message = str(e)
+        res = dict(message=message, unchanged=net.param_hash() == before)
+    torch.cuda.synchronize()
+    dist.barrier()
+    net.close(); ctx.close()
+    return res
+
+
 def main():
     rank, world, local_rank = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     out = {m: run(m, rank, world, local_rank) for m in ("nccl", "peer")}
     out["oracle"] = oracle_check(rank, world, local_rank)
+    out["absent_peer"] = absent_peer(rank, world, local_rank)
     if rank == 0:
         print("RESULT " + json.dumps(out), flush=True)
     dist.barrier()

@@ -1,5 +1,6 @@
 """Two-GPU data parallel through the C ABI (skipped on a box with one GPU): NCCL all-reduce against the peer
-exchange fused into the update kernel, and the data-parallel weights against the CPU oracle's emulation of the ranks."""
+exchange fused into the update kernel, the data-parallel weights against the CPU oracle's emulation of the ranks, and
+a peer that never publishes its gradients (bounded wait, whole update skipped, AET_E_TIMEOUT)."""
 import json
 import os
 import subprocess
@@ -30,3 +31,6 @@ def test_two_ranks_nccl_and_peer_exchange_agree():
     assert out["oracle"], out
     for layer, e in out["oracle"].items():
         assert e["weights"] < 1e-4 and e["change"] < 5e-2, (layer, e)
+    # a rank that sits out a step: the other rank's update is skipped as a whole and the step reports the timeout
+    assert "aet error -5" in out["absent_peer"]["message"], out["absent_peer"]
+    assert out["absent_peer"]["unchanged"], out["absent_peer"]
