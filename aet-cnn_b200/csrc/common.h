@@ -262,13 +262,16 @@ struct aet_network {
     // CUDA graphs of one train step: [1] forward + backward + exchange + update, [0] forward + backward only
     // (the calls of a `subdivisions` group that only accumulate gradients)
     bool use_graph = false;
-    cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
-    long graph_launches[2] = {0, 0};
+    // and each of them once per input slot (the asynchronous step alternates between two input / truth tensors)
+    cudaGraphExec_t graph_exec[4] = {nullptr, nullptr, nullptr, nullptr};
+    long graph_launches[4] = {0, 0, 0, 0};
+    int cur_slot = 0;                                          // input slot of the step being queued
+    aet_tensor *input_alt = nullptr, *truth_alt = nullptr;     // slot 1 (slot 0 = `input`, `truth`)
     int eager_runs[2] = {0, 0};
     // Double-buffered input staging of aet_network_train_step_async: the host->device copy of step s+1 runs on
     // `copy_stream` while step s computes; `ev_staged` orders the step after its copy, `ev_consumed` orders the
     // next copy into a slot after the transposing kernels that read it, `ev_loss` marks a step's loss read-back.
-    cudaStream_t copy_stream = nullptr;
+    cudaStream_t copy_stream = nullptr, loss_stream = nullptr;
     float *stage_dev[2] = {nullptr, nullptr};
     float *stage_host[2] = {nullptr, nullptr};   // pinned mirrors, used when the caller's buffers are pageable
     size_t stage_floats = 0;
@@ -395,7 +398,8 @@ int ctx_staging(aet_context *ctx, size_t bytes);
 // ---- layout taps (tensor.cu) ------------------------------------------------------------------
 int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int n, int c, int h, int w, int cp,
                        bool async_pinned);
-int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp);
+int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp,
+                         cudaStream_t stream = nullptr);   // stream: null = the context's
 int tensor_download_nchw(aet_context *ctx, const float *dev_nhwc, float *host, int n, int c, int h, int w, int cp);
 int tensor_download_nchw_int(aet_context *ctx, const int *dev_nhwc, int *host, int n, int c, int h, int w, int cp);
 int vector_upload(aet_context *ctx, float *dev, const float *host, size_t count);

@@ -670,10 +670,9 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
         }
     }
     if (!bn) return 1;
-    // CTA pairs (cta_group::2): the two CTAs of a cluster along grid x run MMAs of M = 256 together and each loads only half
-    // of every weight tile, so the weights cross L2 -> SM once per pair.  Measured, the main loops of these kernels run at
-    // the L2 -> SM bandwidth (about 70 GB/s per SM with every SM pulling), not at the tensor pipe's rate, so fewer bytes per
-    // FLOP is what shortens them.  Needs an even number of CTAs along x and half tiles that are whole swizzle blocks.
+    // CTA pairs (cta_group::2, option "pair"): the two CTAs of a cluster along grid x run MMAs of M = 256 together and each
+    // loads only half of every weight tile, so the weights cross L2 -> SM once per pair.  Needs an even number of CTAs
+    // along x and half tiles that are whole swizzle blocks.
     int pair = 0;
     {
         const int gx = (m_tiles + mt - 1) / mt;
@@ -687,9 +686,8 @@ int tma_fd_rows(aet_layer *l, const ConvArgs &a, double flops) {
             if (ns >= 2 && st * ns >= need) { pair = 1; b_tile = bt; stage = st; stages = ns; }
         }
     }
-    // The large stages allow one CTA per SM.  Measured on 8x8 to 16x16 images at batch 128 and 256: while the
-    // grid fits one wave this kernel matches or beats the plain TMA kernel (dgrad by 20%); with a second,
-    // partial wave the plain kernel with its smaller stages and two CTAs per SM wins by up to 40%.
+    // The large stages allow one CTA per SM, so this kernel is for grids of at most one wave; a grid that needs a
+    // second, partial wave goes to the plain TMA kernel, whose smaller stages let two CTAs share an SM.
     if (((m_tiles + mt - 1) / mt) * n_tiles * ksplit > ctx->sm_count && !ctx->opt[OPT_ROWS_MULTI]) return 1;
     const int super_rows = mt * (int)bh + g.R - 1;
     const CUtensorMap *ma, *mb;

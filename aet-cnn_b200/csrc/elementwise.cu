@@ -220,7 +220,6 @@ struct PoolWinArgs {
     int act, cp, C, H, W, OH, OW;
     unsigned total;          // N*OH*OW*cvec
 };
-__device__ __forceinline__ float sel(int id, int pos, float v) { return id == pos ? v : 0.f; }
 
 template <bool APPLY>
 __global__ void __launch_bounds__(TB) bn_bwd_poolwin_kernel(const PoolWinArgs a) {
@@ -531,12 +530,6 @@ __global__ void eval_inv_kernel(const float *rolling_variance, float *inv, int c
         v = parity == AET_PARITY_CPU ? (float)(1.0 / (sqrt((double)rolling_variance[i]) + (double).000001f))
                                      : 1.0f / sqrtf(rolling_variance[i] + .00001f);
     inv[i] = v;
-}
-
-__global__ void copy_first_pixel_kernel(const float *x, float *shift, int cp) {
-    pdl_enter();
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < cp) shift[i] = x[i];
 }
 
 // ---------------------------------------------------------------------------- max pool

@@ -348,19 +348,19 @@ int run_step(aet_network *net, bool final) {
 }
 
 void graph_drop(aet_network *net) {
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < 4; ++k) {
         if (net->graph_exec[k]) {
             cudaGraphExecDestroy(net->graph_exec[k]);
             net->graph_exec[k] = nullptr;
         }
-        net->eager_runs[k] = 0;
     }
+    net->eager_runs[0] = net->eager_runs[1] = 0;
 }
 
 // Queues the read-back of {cost, mean loss} and of the device status word into three pinned floats.
-int queue_loss_readback(aet_network *net, float *pinned3) {
+int queue_loss_readback(aet_network *net, float *pinned3, cudaStream_t stream = nullptr) {
     aet_layer *sm = softmax_layer(net);
-    cudaStream_t s = net->ctx->stream;
+    cudaStream_t s = stream ? stream : net->ctx->stream;
     if (sm) AET_CUDA(cudaMemcpyAsync(pinned3, sm->cost_dev, 2 * sizeof(float), cudaMemcpyDeviceToHost, s));
     else pinned3[0] = pinned3[1] = 0.f;
     AET_CUDA(cudaMemcpyAsync(pinned3 + 2, net->ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
@@ -607,6 +607,8 @@ extern "C" void aet_network_destroy(aet_network *net) {
     for (size_t i = net->layers.size(); i-- > 0;) aet_layer_destroy(net->layers[i]);
     aet_tensor_destroy(net->input);
     aet_tensor_destroy(net->truth);
+    if (net->input_alt) aet_tensor_destroy(net->input_alt);
+    if (net->truth_alt) aet_tensor_destroy(net->truth_alt);
     arena_destroy(&net->arena);
     if (net->block_seg) cudaFree(net->block_seg);
     if (net->seg_table) cudaFree(net->seg_table);
@@ -621,6 +623,7 @@ extern "C" void aet_network_destroy(aet_network *net) {
         if (net->ev_loss[k]) cudaEventDestroy(net->ev_loss[k]);
     }
     if (net->copy_stream) cudaStreamDestroy(net->copy_stream);
+    if (net->loss_stream) cudaStreamDestroy(net->loss_stream);
     delete net;
 }
 
@@ -697,9 +700,10 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
     aet_layer *sm = softmax_layer(net);
     if (sm) sm->cost_valid = false;
     const long before = ctx->launches;
-    if (net->use_graph && net->graph_exec[kind] && !ctx->profiling) {
-        AET_CUDA(cudaGraphLaunch(net->graph_exec[kind], ctx->stream));
-        ctx->launches += net->graph_launches[kind];
+    const int gi = kind + 2 * net->cur_slot;   // a graph holds its tensors' addresses: one per input slot
+    if (net->use_graph && net->graph_exec[gi] && !ctx->profiling) {
+        AET_CUDA(cudaGraphLaunch(net->graph_exec[gi], ctx->stream));
+        ctx->launches += net->graph_launches[gi];
     } else if (net->use_graph && net->eager_runs[kind] > 0 && !ctx->profiling) {
         // an eager step of this kind has sized every scratch buffer; capture this one
         cudaGraph_t graph = nullptr;
@@ -710,11 +714,11 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         if (r != AET_OK) { if (graph) cudaGraphDestroy(graph); return r; }
         if (e != cudaSuccess) { aet_set_error("graph capture failed: %s", cudaGetErrorString(e)); return AET_E_CUDA; }
-        net->graph_launches[kind] = ctx->launches - before;
-        e = cudaGraphInstantiate(&net->graph_exec[kind], graph, 0);
+        net->graph_launches[gi] = ctx->launches - before;
+        e = cudaGraphInstantiate(&net->graph_exec[gi], graph, 0);
         cudaGraphDestroy(graph);
-        if (e != cudaSuccess) { aet_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); net->graph_exec[kind] = nullptr; return AET_E_CUDA; }
-        AET_CUDA(cudaGraphLaunch(net->graph_exec[kind], ctx->stream));
+        if (e != cudaSuccess) { aet_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); net->graph_exec[gi] = nullptr; return AET_E_CUDA; }
+        AET_CUDA(cudaGraphLaunch(net->graph_exec[gi], ctx->stream));
     } else {
         AET_TRY(run_step(net, final));
         net->eager_runs[kind] += 1;
@@ -778,6 +782,7 @@ extern "C" int aet_network_train_step_async(aet_network *net, const float *host_
     if (!net->copy_stream) {
         AET_CUDA(cudaSetDevice(ctx->device));
         AET_CUDA(cudaStreamCreateWithFlags(&net->copy_stream, cudaStreamNonBlocking));
+        AET_CUDA(cudaStreamCreateWithFlags(&net->loss_stream, cudaStreamNonBlocking));
         for (int k = 0; k < 2; ++k) {
             AET_CUDA(cudaMalloc(&net->stage_dev[k], (nx + nt) * sizeof(float)));
             AET_CUDA(cudaEventCreateWithFlags(&net->ev_staged[k], cudaEventDisableTiming));
@@ -797,19 +802,36 @@ extern "C" int aet_network_train_step_async(aet_network *net, const float *host_
         memcpy(net->stage_host[slot] + nx, host_truth, nt * sizeof(float));
         src_x = net->stage_host[slot]; src_t = net->stage_host[slot] + nx;
     }
+    // Slot 1 has input and truth tensors of its own, so that the copy stream can also TRANSPOSE the batch of the
+    // next step while this step still reads its input (the first layer's backward does, to the end of the step).
+    if (slot == 1 && !net->input_alt) {
+        net->input_alt = aet_tensor_create(ctx, net->input->n, net->input->c, net->input->h, net->input->w);
+        net->truth_alt = aet_tensor_create(ctx, net->truth->n, net->truth->c, 1, 1);
+        if (!net->input_alt || !net->truth_alt) return AET_E_NOMEM;
+    }
+    aet_tensor *in = slot ? net->input_alt : net->input, *tr = slot ? net->truth_alt : net->truth;
     if (reused) AET_CUDA(cudaStreamWaitEvent(net->copy_stream, net->ev_consumed[slot], 0));
     AET_CUDA(cudaMemcpyAsync(net->stage_dev[slot], src_x, nx * sizeof(float), cudaMemcpyHostToDevice, net->copy_stream));
     AET_CUDA(cudaMemcpyAsync(net->stage_dev[slot] + nx, src_t, nt * sizeof(float), cudaMemcpyHostToDevice, net->copy_stream));
+    AET_TRY(tensor_upload_staged(ctx, in->d, net->stage_dev[slot], in->n, in->c, in->h, in->w, in->cp, net->copy_stream));
+    AET_TRY(tensor_upload_staged(ctx, tr->d, net->stage_dev[slot] + nx, tr->n, tr->c, 1, 1, tr->cp, net->copy_stream));
+    in->lazy_zero = false; tr->lazy_zero = false;
     AET_CUDA(cudaEventRecord(net->ev_staged[slot], net->copy_stream));
     AET_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_staged[slot], 0));
     pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
-    AET_TRY(tensor_upload_staged(ctx, net->input->d, net->stage_dev[slot], net->input->n, net->input->c, net->input->h, net->input->w, net->input->cp));
-    AET_TRY(tensor_upload_staged(ctx, net->truth->d, net->stage_dev[slot] + nx, net->truth->n, net->truth->c, 1, 1, net->truth->cp));
-    AET_CUDA(cudaEventRecord(net->ev_consumed[slot], ctx->stream));
-    AET_TRY(aet_network_train_step_device(net, nullptr));
+    if (net->async_steps >= 1) AET_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_loss[prev], 0));
+    aet_tensor *in0 = net->input, *tr0 = net->truth;
+    net->input = in; net->truth = tr; net->cur_slot = slot;
+    const int sr = aet_network_train_step_device(net, nullptr);
+    net->input = in0; net->truth = tr0; net->cur_slot = 0;
+    AET_TRY(sr);
+    AET_CUDA(cudaEventRecord(net->ev_consumed[slot], ctx->stream));   // the step has read the slot's tensors to its end
+    // The loss travels back on a stream of its own, so that the steps stay back to back on the main stream; the next
+    // step waits (above) for this copy before its head kernel may overwrite the cost.
     float *ring = net->loss_pinned + 8 + 4 * slot;
-    AET_TRY(queue_loss_readback(net, ring));
-    AET_CUDA(cudaEventRecord(net->ev_loss[slot], ctx->stream));
+    AET_CUDA(cudaStreamWaitEvent(net->loss_stream, net->ev_consumed[slot], 0));
+    AET_TRY(queue_loss_readback(net, ring, net->loss_stream));
+    AET_CUDA(cudaEventRecord(net->ev_loss[slot], net->loss_stream));
     const bool have_prev = net->async_steps >= 1;
     net->async_steps += 1;
     if (!have_prev) {
@@ -1017,8 +1039,8 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     // per SM: the collective is capped to a few CTAs (option "nccl_max_ctas", 0 = NCCL's own choice) through this
     // communicator's configuration, which leaves the process environment and other communicators alone.
     int r = -1;
-    // Option value -1 (the default) picks by the number of ranks: with two ranks NCCL's own choice measured faster
-    // (0.263 against 0.282 ms per step), with eight a cap of 8 CTAs did (0.294 against 0.309).
+    // Option value -1 (the default) picks by the number of ranks: NCCL's own choice for two ranks, a cap of 8 CTAs
+    // beyond (more ranks make NCCL ask for more CTAs than the backward pass can spare).
     int max_ctas = net->ctx->opt[OPT_NCCL_MAX_CTAS];
     if (max_ctas < 0) max_ctas = world <= 2 ? 0 : 8;
     if (max_ctas > 0 && api->comm_init_rank_config) {

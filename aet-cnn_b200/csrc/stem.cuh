@@ -25,7 +25,7 @@ constexpr int STEM_GRAM_ENTRY = 28;    // 27 products per combo (+ 1 pad), in th
 constexpr int STEM_GRAM_PART = STEM_GRAM_COMBOS * STEM_GRAM_ENTRY + 28;   // + column sums [(rb, sb)][channel] (27, + 1 pad)
 constexpr int STEM_WIN = 16;           // pool windows per work item of the sparse pass
 constexpr int STEM_COLS = 2 * STEM_WIN + 2;   // input columns under them, with the border
-constexpr int STEM_FIN_LANES = 16;     // threads per tap in the finishing kernel
+constexpr int STEM_FIN_LANES = 28;     // threads per tap in the finishing kernel (36 x 28 = 1008 threads)
 
 struct StemSparseArgs {
     const float *x;               // layer input [N][H][W][4]
@@ -329,8 +329,8 @@ __global__ void __launch_bounds__(STEM_TAPS * STEM_FIN_LANES) stem_bwd_finish_ke
         for (; b < a.blocks; b += STEM_FIN_LANES) s0 += (double)__ldg(src + b * stride);
         part[lane][t] = (s0 + s1) + (s2 + s3);
     }
-    if (warp >= 14 && warp < 18) {   // the last four warps also form S1 and S2, two warps each
-        const int which = (warp - 14) >> 1, half = (warp - 14) & 1;
+    if (warp < 4) {   // the first four warps also form S1 and S2, two warps each
+        const int which = warp >> 1, half = warp & 1;
         const float *src = a.partial_s + which * a.ocp + k;
         double v0 = 0.0, v1 = 0.0;
         int b = half * 32 + wl;

@@ -415,10 +415,12 @@ int tensor_upload_nchw(aet_context *ctx, float *dev_nhwc, const float *host, int
 }
 
 // Transposes a dense NCHW image already resident in device memory into the NHWC tensor.
-int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp) {
+int tensor_upload_staged(aet_context *ctx, float *dev_nhwc, const float *dev_nchw, int n, int c, int h, int w, int cp,
+                         cudaStream_t stream) {
     const size_t total = (size_t)n * h * w * cp;
-    ctx->launches++;
-    launch_k(ctx->stream, (unsigned)((total + 255) / 256), 256, 0, nchw_to_nhwc_kernel, dev_nchw, dev_nhwc, n, c, h, w, cp);
+    if (stream) pdl_skip_next();   // behind a copy on another stream: a plain launch
+    else ctx->launches++;
+    launch_k(stream ? stream : ctx->stream, (unsigned)((total + 255) / 256), 256, 0, nchw_to_nhwc_kernel, dev_nchw, dev_nhwc, n, c, h, w, cp);
     return aet_check_launch("nchw_to_nhwc");
 }
 
