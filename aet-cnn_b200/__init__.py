@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(HERE, "libaet_b200.so")
 CFG_DIR = os.path.join(HERE, "cfg")
 
 LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU = range(14)
-CONVOLUTIONAL, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
+CONVOLUTIONAL, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT, SHORTCUT = 0, 1, 2, 3, 4, 5
 PARITY_CPU, PARITY_MTCS = 0, 1
 MATH_TF32, MATH_3XTF32 = 0, 1
 (P_WEIGHTS, P_WEIGHT_UPDATES, P_BIASES, P_BIAS_UPDATES, P_SCALES, P_SCALE_UPDATES, P_ROLLING_MEAN,
@@ -30,7 +30,7 @@ aet_context_stream aet_context_set_parity aet_context_set_math aet_context_synch
 aet_context_profile aet_context_profile_read aet_context_launch_count aet_context_set_option aet_context_get_option aet_context_set_wait_limit aet_context_wait_probe
 aet_tensor_create aet_tensor_destroy aet_tensor_shape aet_tensor_write aet_tensor_read aet_tensor_zero
 aet_tensor_count aet_convolutional_layer_create aet_maxpool_layer_create aet_avgpool_layer_create
-aet_softmax_layer_create aet_dropout_layer_create aet_layer_destroy aet_layer_forward aet_layer_backward
+aet_softmax_layer_create aet_dropout_layer_create aet_shortcut_layer_create aet_layer_destroy aet_layer_forward aet_layer_backward
 aet_layer_update aet_layer_init_delta aet_layer_output aet_layer_delta aet_layer_kind aet_layer_out_shape
 aet_layer_cost aet_layer_param_count aet_layer_read aet_layer_write aet_layer_load_weights
 aet_layer_save_weights aet_network_create aet_network_create_from_string aet_network_create_ex
@@ -98,6 +98,7 @@ def lib():
         "aet_avgpool_layer_create": (vp, [vp, i, i, i, i]),
         "aet_softmax_layer_create": (vp, [vp, i, i, i, f]),
         "aet_dropout_layer_create": (vp, [vp, i, i, f, vp]),
+        "aet_shortcut_layer_create": (vp, [vp, i, i, i, i, i, C.POINTER(vp), i, i]),
         "aet_layer_destroy": (None, [vp]),
         "aet_layer_forward": (i, [vp, State]), "aet_layer_backward": (i, [vp, State]),
         "aet_layer_update": (i, [vp, i, f, f, f, f]), "aet_layer_init_delta": (i, [vp]),
@@ -322,7 +323,7 @@ class Layer:
 
 
 class ConvolutionalLayer(Layer):
-    """dnn/ConvolutionalLayer.h:87-91 (supported branch: groups=1, dilation=1, FP32)."""
+    """dnn/ConvolutionalLayer.h:87-91 (FP32; channel groups, dilation and unequal strides included)."""
 
     def __init__(self, ctx, batch, h, w, c, n, size, stride_x=1, stride_y=None, padding=0, activation=LINEAR,
                  batch_normalize=0, train=1, groups=1, dilation=1):
@@ -354,6 +355,15 @@ class SoftMaxLayer(Layer):
 class DropoutLayer(Layer):
     def __init__(self, ctx, batch, inputs, probability, prev):
         super().__init__(ctx, ctx.L.aet_dropout_layer_create(ctx.h, batch, inputs, probability, prev.h))
+
+
+class ShortcutLayer(Layer):
+    """ShortcutLayer without weights (dnn/ShortcutLayer.c): activation(input + outputs of `sources`)."""
+
+    def __init__(self, ctx, batch, h, w, c, sources, activation=LINEAR, train=1):
+        arr = (C.c_void_p * len(sources))(*[s.h for s in sources])
+        super().__init__(ctx, ctx.L.aet_shortcut_layer_create(ctx.h, batch, h, w, c, len(sources), arr, activation, train))
+        self.sources = list(sources)
 
 
 class NNetwork:

@@ -224,6 +224,9 @@ struct aet_layer {
     float *stem_gram_partial = nullptr;   // per-block Gram sums [blocks][81][16]
     double *stem_gram = nullptr;          // Gram sums over the batch [81][16]
     int stem_blocks = 0, stem_blocks_used = 0, stem_gram_blocks = 0;
+    // shortcut: the layers whose outputs are added to the input
+    aet_layer *from[4] = {nullptr, nullptr, nullptr, nullptr};
+    int n_from = 0;
     // TMA descriptors are built lazily per (layer, pass, operand address)
     void *tma_cache = nullptr;
 };
@@ -431,6 +434,8 @@ int k_bn_stats(aet_layer *l, int update_rolling, const ConvStats *from_epilogue 
 int k_bn_apply(aet_layer *l, int use_rolling);
 int k_bn_backward(aet_layer *l, aet_layer *pool);
 int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling);
+int k_shortcut_forward(aet_layer *l, const float *in);
+int k_shortcut_backward(aet_layer *l, aet_tensor *pd);
 bool stem_backward_eligible(const aet_layer *l, const aet_layer *pool);
 int stem_alloc(aet_layer *l, aet_layer *pool);
 int k_stem_gram(aet_layer *l, const float *x_in);

@@ -1673,6 +1673,104 @@ int k_stem_delta(aet_layer *l, aet_layer *pool) {
 
 #include "stem.cuh"
 
+// ---------------------------------------------------------------------------- shortcut (residual add)
+struct ShortcutArgs {
+    const float *in;        // forward: layer input; backward: unused
+    float *out;             // forward: output; backward: this layer's delta (scaled in place by the activation gradient)
+    const float *y;         // backward: this layer's output
+    float *add[4];          // forward: the sources' outputs; backward: the sources' deltas
+    int add_cp[4], add_lazy[4];
+    float *pd;              // backward: previous layer's delta (may be null)
+    int pd_lazy;
+    int n, C, cp, act;
+    long long total;        // pixels * cp / 4
+};
+// out = act(in + sum_i add_i) over the channels both tensors have; pad lanes stay zero.
+__global__ void __launch_bounds__(TB) shortcut_fwd_kernel(const ShortcutArgs a) {
+    pdl_enter();
+    const long long e = (long long)blockIdx.x * TB + threadIdx.x;
+    if (e >= a.total) return;
+    const int cvec = a.cp / 4;
+    const long long p = e / cvec;
+    const int c = (int)(e % cvec) * 4;
+    float4 v = ld4(a.in + p * a.cp + c);
+    for (int i = 0; i < a.n; ++i)
+        if (c < a.add_cp[i]) {
+            const float4 q = ld4(a.add[i] + p * a.add_cp[i] + c);
+            v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+        }
+    v.x = c < a.C ? act_fwd(v.x, a.act) : 0.f;
+    v.y = c + 1 < a.C ? act_fwd(v.y, a.act) : 0.f;
+    v.z = c + 2 < a.C ? act_fwd(v.z, a.act) : 0.f;
+    v.w = c + 3 < a.C ? act_fwd(v.w, a.act) : 0.f;
+    st4(a.out + p * a.cp + c, v);
+}
+// d = delta * act'(y) (written back), added to the previous delta and to every source's delta (overwriting where
+// nothing has been written yet).  A source with more channels than this layer is zeroed by the host first.
+__global__ void __launch_bounds__(TB) shortcut_bwd_kernel(const ShortcutArgs a) {
+    pdl_enter();
+    const long long e = (long long)blockIdx.x * TB + threadIdx.x;
+    if (e >= a.total) return;
+    const int cvec = a.cp / 4;
+    const long long p = e / cvec;
+    const int c = (int)(e % cvec) * 4;
+    const size_t o = (size_t)p * a.cp + c;
+    float4 d = ld4(a.out + o);
+    const float4 y = ld4(a.y + o);
+    d.x *= act_grad(y.x, a.act); d.y *= act_grad(y.y, a.act); d.z *= act_grad(y.z, a.act); d.w *= act_grad(y.w, a.act);
+    if (c + 1 >= a.C) d.y = 0.f;
+    if (c + 2 >= a.C) d.z = 0.f;
+    if (c + 3 >= a.C) d.w = 0.f;
+    if (a.act != AET_LINEAR) st4(a.out + o, d);
+    if (a.pd) {
+        float4 q = d;
+        if (!a.pd_lazy) { const float4 t = ld4(a.pd + o); q.x += t.x; q.y += t.y; q.z += t.z; q.w += t.w; }
+        st4(a.pd + o, q);
+    }
+    for (int i = 0; i < a.n; ++i)
+        if (c < a.add_cp[i]) {
+            float *dst = a.add[i] + (size_t)p * a.add_cp[i] + c;
+            float4 q = d;
+            if (!a.add_lazy[i]) { const float4 t = ld4(dst); q.x += t.x; q.y += t.y; q.z += t.z; q.w += t.w; }
+            st4(dst, q);
+        }
+}
+
+int k_shortcut_forward(aet_layer *l, const float *in) {
+    aet_context *ctx = l->ctx;
+    ShortcutArgs a = {};
+    a.in = in; a.out = l->output->d; a.n = l->n_from; a.C = l->c; a.cp = l->cp; a.act = l->act;
+    for (int i = 0; i < l->n_from; ++i) { a.add[i] = l->from[i]->output->d; a.add_cp[i] = l->from[i]->ocp; }
+    a.total = (long long)l->batch * l->h * l->w * (l->cp / 4);
+    LaunchScope s(ctx, "shortcut_fwd", 4.0 * (2 + l->n_from) * l->batch * l->h * l->w * l->cp, 0);
+    launch_k(ctx->stream, (unsigned)((a.total + TB - 1) / TB), TB, 0, shortcut_fwd_kernel, a);
+    return aet_check_launch("shortcut_fwd");
+}
+
+int k_shortcut_backward(aet_layer *l, aet_tensor *pd) {
+    aet_context *ctx = l->ctx;
+    ShortcutArgs a = {};
+    a.out = l->delta->d; a.y = l->output->d; a.n = l->n_from; a.C = l->c; a.cp = l->cp; a.act = l->act;
+    a.pd = pd ? pd->d : nullptr; a.pd_lazy = pd && pd->lazy_zero ? 1 : 0;
+    for (int i = 0; i < l->n_from; ++i) {
+        aet_tensor *fd = l->from[i]->delta;
+        if (fd->lazy_zero && (l->from[i]->ocp > l->cp || fd == (pd ? pd : nullptr))) {
+            // wider than this layer (its other channels must read as zero), or the very tensor `pd` names (it must
+            // receive the delta twice, as the reference adds it twice): start from explicit zeros
+            AET_TRY(aet_tensor_zero(fd));
+            fd->lazy_zero = false;
+            if (fd == pd) a.pd_lazy = 0;
+        }
+        a.add[i] = fd->d; a.add_cp[i] = l->from[i]->ocp; a.add_lazy[i] = fd->lazy_zero ? 1 : 0;
+        fd->lazy_zero = false;
+    }
+    if (pd) pd->lazy_zero = false;
+    a.total = (long long)l->batch * l->h * l->w * (l->cp / 4);
+    LaunchScope s(ctx, "shortcut_bwd", 4.0 * (3 + 2 * l->n_from) * l->batch * l->h * l->w * l->cp, 0);
+    launch_k(ctx->stream, (unsigned)((a.total + TB - 1) / TB), TB, 0, shortcut_bwd_kernel, a);
+    return aet_check_launch("shortcut_bwd");
+}
+
 // Convolution without BN: delta *= act'(output) in place and the bias gradient accumulates.
 int k_bias_act_backward(aet_layer *l) {
     aet_context *ctx = l->ctx;

@@ -246,6 +246,33 @@ extern "C" aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int 
     return l;
 }
 
+extern "C" aet_layer *aet_shortcut_layer_create(aet_context *ctx, int batch, int h, int w, int c, int n, aet_layer *const *from,
+                                                aet_activation activation, int train) {
+    if (!ctx || batch <= 0 || h <= 0 || w <= 0 || c <= 0 || n < 1 || n > 4 || !from) {
+        aet_set_error("shortcut: bad arguments (1 to 4 source layers)");
+        return nullptr;
+    }
+    if ((int)activation < 0 || (int)activation >= AET_ACTIVATION_COUNT) { aet_set_error("shortcut: unknown activation"); return nullptr; }
+    for (int i = 0; i < n; ++i) {
+        const aet_layer *f = from[i];
+        if (!f || !f->output || f->batch != batch || f->oh != h || f->ow != w) {   // dnn/NetworkFactory.c:234
+            aet_set_error("shortcut: source %d must be a layer with a %dx%d output map", i, h, w);
+            return nullptr;
+        }
+        if (train && !f->delta) { aet_set_error("shortcut: source %d has no delta (created with train=0)", i); return nullptr; }
+    }
+    aet_layer *l = new aet_layer();
+    l->ctx = ctx; l->type = AET_SHORTCUT; l->act = activation; l->train = train;
+    l->batch = batch; l->c = c; l->h = h; l->w = w; l->cp = round_up(c, 4);
+    l->oc = c; l->oh = h; l->ow = w; l->ocp = l->cp;
+    l->n_from = n;
+    for (int i = 0; i < n; ++i) l->from[i] = from[i];
+    l->output = aet_tensor_create(ctx, batch, c, h, w);
+    if (train) l->delta = aet_tensor_create(ctx, batch, c, h, w);
+    if (!l->output || (train && !l->delta)) { aet_layer_destroy(l); return nullptr; }
+    return l;
+}
+
 extern "C" void aet_layer_destroy(aet_layer *l) {
     if (!l) return;
     if (l->ctx) cudaStreamSynchronize(l->ctx->stream);
@@ -381,6 +408,9 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
         if (truth) l->delta->lazy_zero = false;
         return AET_OK;
     }
+    case AET_SHORTCUT:
+        l->output->lazy_zero = false;
+        return k_shortcut_forward(l, state.input->d);
     case AET_DROPOUT:
         if (!state.train) return AET_OK;
         if (state.input != l->prev->output) return fail_invalid("dropout: state.input must be the previous layer's output");
@@ -493,6 +523,9 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
         pd->lazy_zero = false;
         return AET_OK;
     }
+    case AET_SHORTCUT:
+        if (l->delta->lazy_zero) { AET_TRY(aet_tensor_zero(l->delta)); l->delta->lazy_zero = false; }
+        return k_shortcut_backward(l, pd);
     case AET_DROPOUT:
         if (!pd) return AET_OK;
         if (pd != l->prev->delta) return fail_invalid("dropout: state.delta must be the previous layer's delta");

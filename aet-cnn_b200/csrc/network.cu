@@ -526,6 +526,38 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
             if (opt_int(s, "dropblock", 0)) { aet_set_error("cfg line %d: dropblock is outside the supported hot path", s.line); aet_network_destroy(net); return nullptr; }
             l = aet_dropout_layer_create(ctx, net->batch, c * h * w, opt_float(s, "probability", .2f), net->layers.back());
             if (l) l->seed = 0xD509ULL + 0x9E3779B97F4A7C15ULL * (uint64_t)(index + 1);
+        } else if (s.name == "shortcut") {
+            // dnn/NetworkFactory.c:175-246: from = i[,j...] (negative = relative to this layer), activation default linear
+            if (net->layers.empty()) { aet_set_error("cfg line %d: shortcut cannot be the first layer", s.line); aet_network_destroy(net); return nullptr; }
+            if (opt_str(s, "weights_type", "none") != "none") { aet_set_error("cfg line %d: shortcut weights are outside the supported hot path", s.line); aet_network_destroy(net); return nullptr; }
+            aet_activation a;
+            if (parse_activation(opt_str(s, "activation", "linear"), &a) != AET_OK) { aet_network_destroy(net); return nullptr; }
+            std::string from = opt_str(s, "from", "");
+            aet_layer *src[4];
+            int nsrc = 0;
+            size_t pos = 0;
+            while (pos < from.size() && nsrc < 5) {
+                size_t comma = from.find(',', pos);
+                std::string tok = from.substr(pos, comma == std::string::npos ? std::string::npos : comma - pos);
+                pos = comma == std::string::npos ? from.size() : comma + 1;
+                if (tok.empty()) continue;
+                int idx = atoi(tok.c_str());
+                if (idx < 0) idx += index;
+                if (idx < 0 || idx >= index || nsrc == 4) { nsrc = 5; break; }
+                src[nsrc++] = net->layers[idx];
+            }
+            if (nsrc < 1 || nsrc > 4) { aet_set_error("cfg line %d: shortcut needs from = 1 to 4 earlier layers", s.line); aet_network_destroy(net); return nullptr; }
+            for (int q = 0; q < nsrc; ++q) {
+                // a source's full-resolution output and delta must exist: it leaves the call-pattern fusions
+                aet_layer *f = src[q];
+                if (f->fused_pool) { f->fused_pool->fused_into = nullptr; f->fused_pool = nullptr; f->stem = false; }
+                f->lin_head = false;
+            }
+            {   // so does the layer in front of the shortcut (its output is this layer's input and its delta receives ours)
+                aet_layer *f = net->layers.back();
+                if (f->fused_pool) { f->fused_pool->fused_into = nullptr; f->fused_pool = nullptr; f->stem = false; }
+            }
+            l = aet_shortcut_layer_create(ctx, net->batch, h, w, c, nsrc, src, a, train);
         } else {
             aet_set_error("cfg line %d: layer type [%s] is outside the supported hot path", s.line, s.name.c_str());
             aet_network_destroy(net);

@@ -43,7 +43,7 @@ typedef enum { AET_LINEAR = 0, AET_RELU = 1, AET_LEAKY = 2, AET_LOGISTIC = 3, AE
                AET_TANH = 7, AET_PLSE = 8, AET_ELU = 9, AET_LOGGY = 10, AET_HARDTAN = 11, AET_LHTAN = 12, AET_SELU = 13 } aet_activation;
 #define AET_ACTIVATION_COUNT 14
 /* dnn/NLayer.c:30-60 layer kinds that NetworkFactory.createLayer instantiates on the hot path */
-typedef enum { AET_CONVOLUTIONAL = 0, AET_MAXPOOL = 1, AET_AVGPOOL = 2, AET_SOFTMAX = 3, AET_DROPOUT = 4 } aet_layer_type;
+typedef enum { AET_CONVOLUTIONAL = 0, AET_MAXPOOL = 1, AET_AVGPOOL = 2, AET_SOFTMAX = 3, AET_DROPOUT = 4, AET_SHORTCUT = 5 } aet_layer_type;
 /* Which of the reference's two numerically different back ends the formulas follow:
  * the CPU classes (dnn/NormData.c, dnn/DeltaData.c, ...) or the MTCS kernels (mtcs/...). */
 typedef enum { AET_PARITY_CPU = 0, AET_PARITY_MTCS = 1 } aet_parity_mode;
@@ -161,6 +161,13 @@ aet_layer *aet_avgpool_layer_create(aet_context *ctx, int batch, int w, int h, i
 aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int inputs, int groups, float temperature);
 /* Dropout works in place on `prev`'s output and delta (dnn/NetworkFactory.c:644-650). */
 aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int inputs, float probability, aet_layer *prev);
+/* ShortcutLayer without weights (dnn/ShortcutLayer.c:272-407 forward, :132-250 backward; factory dnn/NetworkFactory.c:175-246
+ * with weights_type = none): output = activation(input + sum of the outputs of `from[0..n)`), n <= 4; a source with fewer
+ * channels adds to the first of them, one with more contributes its first `c` channels (the reference compares flat
+ * NCHW indices with the source's output count); all maps must be h x w.  backward: delta *= activation gradient, then
+ * delta is ADDED to state.delta and to every source layer's delta.  The swish / mish forms are not restated. */
+aet_layer *aet_shortcut_layer_create(aet_context *ctx, int batch, int h, int w, int c, int n, aet_layer *const *from,
+                                     aet_activation activation, int train);
 void       aet_layer_destroy(aet_layer *l);
 
 /* NLayer.forward / backward / update / initDelta (dnn/NLayer.h:159-173). */

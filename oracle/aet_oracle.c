@@ -732,6 +732,29 @@ static void conv_backward_mt(aeto_net *net, olayer *L, const float *in, float *p
                        L->c, L->h, L->w, L->s.filters, L->s.size, L->s.stride_x, L->s.stride_y, L->s.pad);
 }
 
+/* dnn/ShortcutLayer.c:272-353 with weights == NULL: the per-sample loops of forwardMultilayer */
+void aeto_shortcut_forward(const float *in, float *out, int batch, size_t outputs, int n, const float *const *add,
+                           const size_t *add_outputs) {
+    for (int b = 0; b < batch; ++b)
+        for (size_t j = 0; j < outputs; ++j) {
+            float v = in[(size_t)b * outputs + j];
+            for (int i = 0; i < n; ++i)
+                if (j < add_outputs[i]) v += add[i][(size_t)b * add_outputs[i] + j];
+            out[(size_t)b * outputs + j] = v;
+        }
+}
+/* dnn/ShortcutLayer.c:132-230 with weights == NULL */
+void aeto_shortcut_backward(const float *delta, float *delta_out, int batch, size_t outputs, int n, float *const *layer_delta,
+                            const size_t *add_outputs) {
+    for (int b = 0; b < batch; ++b)
+        for (size_t j = 0; j < outputs; ++j) {
+            const float d = delta[(size_t)b * outputs + j];
+            if (delta_out) delta_out[(size_t)b * outputs + j] += d;
+            for (int i = 0; i < n; ++i)
+                if (j < add_outputs[i]) layer_delta[i][(size_t)b * add_outputs[i] + j] += d;
+        }
+}
+
 void aeto_net_forward(aeto_net *net, const float *x, const float *truth, int train) {
     const float *in = x;
     net->truth = truth;
@@ -764,6 +787,14 @@ void aeto_net_forward(aeto_net *net, const float *x, const float *truth, int tra
         case AETO_DROPOUT:
             if (train) aeto_dropout_forward(L->output, L->rnd, (size_t)net->batch * L->inputs, L->s.probability);
             break;
+        case AETO_SHORTCUT: {
+            const float *add[4];
+            size_t add_outputs[4];
+            for (int q = 0; q < L->s.n_from; ++q) { add[q] = net->l[L->s.from[q]].output; add_outputs[q] = net->l[L->s.from[q]].outputs; }
+            aeto_shortcut_forward(in, L->output, net->batch, L->outputs, L->s.n_from, add, add_outputs);
+            aeto_activate(L->output, act, L->s.activation, net->mode);
+            break;
+        }
         }
         in = L->output;
     }
@@ -798,6 +829,14 @@ void aeto_net_backward(aeto_net *net, const float *x, float *input_delta) {
         case AETO_DROPOUT:
             if (pd) aeto_dropout_backward(pd, L->rnd, (size_t)net->batch * L->inputs, L->s.probability);
             break;
+        case AETO_SHORTCUT: {
+            float *ld[4];
+            size_t add_outputs[4];
+            for (int q = 0; q < L->s.n_from; ++q) { ld[q] = net->l[L->s.from[q]].delta; add_outputs[q] = net->l[L->s.from[q]].outputs; }
+            aeto_gradient(L->output, act, L->s.activation, L->delta);   /* dnn/ShortcutLayer.c:232-243 */
+            aeto_shortcut_backward(L->delta, pd, net->batch, L->outputs, L->s.n_from, ld, add_outputs);
+            break;
+        }
         }
     }
 }

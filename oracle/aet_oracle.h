@@ -25,7 +25,7 @@ extern "C" {
 
 enum { AETO_LINEAR = 0, AETO_RELU = 1, AETO_LEAKY = 2 };
 enum { AETO_MODE_CPU = 0, AETO_MODE_MTCS = 1 };
-enum { AETO_CONV = 0, AETO_MAXPOOL = 1, AETO_AVGPOOL = 2, AETO_SOFTMAX = 3, AETO_DROPOUT = 4 };
+enum { AETO_CONV = 0, AETO_MAXPOOL = 1, AETO_AVGPOOL = 2, AETO_SOFTMAX = 3, AETO_DROPOUT = 4, AETO_SHORTCUT = 5 };
 
 /* ---- primitives ---- */
 void aeto_gemm(int TA, int TB, int M, int N, int K, float ALPHA, const float *A, int lda,
@@ -75,6 +75,14 @@ void aeto_softmax_backward(const float *delta, float *prev_delta, size_t count, 
 void aeto_dropout_forward(float *x, const float *r, size_t count, float probability);
 void aeto_dropout_backward(float *delta, const float *r, size_t count, float probability);
 
+/* ---- shortcut without weights: dnn/ShortcutLayer.c:272-407 (forward), :132-250 (backward), per sample ----
+ * out[j] = in[j] + sum_i add_i[j] for j < add_outputs_i, then the activation; backward: delta *= gradient(out),
+ * delta_out[j] += delta[j], layer_delta_i[j] += delta[j] for j < add_outputs_i. */
+void aeto_shortcut_forward(const float *in, float *out, int batch, size_t outputs, int n, const float *const *add,
+                           const size_t *add_outputs);
+void aeto_shortcut_backward(const float *delta, float *delta_out, int batch, size_t outputs, int n, float *const *layer_delta,
+                            const size_t *add_outputs);
+
 /* ---- SGD with momentum ---- */
 void aeto_sgd_weights(float *w, float *u, size_t count, int batch, float lr, float momentum, float decay);
 void aeto_sgd_plain(float *p, float *u, size_t count, int batch, float lr, float momentum);
@@ -88,6 +96,7 @@ typedef struct aeto_layer_spec {
     float temperature;   /* softmax */
     int groups;          /* softmax groups */
     float learning_rate_scale;
+    int n_from, from[4]; /* shortcut: absolute indexes of the layers whose outputs are added */
 } aeto_layer_spec;
 
 typedef struct aeto_net aeto_net;

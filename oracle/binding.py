@@ -12,7 +12,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU = range(14)
 MODE_CPU, MODE_MTCS = 0, 1
-CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
+CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT, SHORTCUT = 0, 1, 2, 3, 4, 5
 (P_WEIGHTS, P_WEIGHT_UPDATES, P_BIASES, P_BIAS_UPDATES, P_SCALES, P_SCALE_UPDATES, P_ROLLING_MEAN,
  P_ROLLING_VARIANCE, P_MEAN, P_VARIANCE, P_OUTPUT, P_DELTA, P_X, P_X_NORM, P_INDEXES, P_LOSS, P_RAND) = range(17)
 
@@ -24,7 +24,7 @@ class LayerSpec(C.Structure):
     _fields_ = [("type", C.c_int), ("filters", C.c_int), ("size", C.c_int), ("stride_x", C.c_int),
                 ("stride_y", C.c_int), ("pad", C.c_int), ("batch_normalize", C.c_int), ("activation", C.c_int),
                 ("probability", C.c_float), ("temperature", C.c_float), ("groups", C.c_int),
-                ("learning_rate_scale", C.c_float)]
+                ("learning_rate_scale", C.c_float), ("n_from", C.c_int), ("from_", C.c_int * 4)]
 
 
 def build(variant="parity"):
@@ -76,6 +76,8 @@ class Oracle:
         L.aeto_softmax_backward.argtypes = [_f, _f, C.c_size_t, C.c_float]
         L.aeto_dropout_forward.argtypes = [_f, _f, C.c_size_t, C.c_float]
         L.aeto_dropout_backward.argtypes = [_f, _f, C.c_size_t, C.c_float]
+        L.aeto_shortcut_forward.argtypes = [_f, _f, C.c_int, C.c_size_t, C.c_int, C.POINTER(_f), C.POINTER(C.c_size_t)]
+        L.aeto_shortcut_backward.argtypes = [_f, _f, C.c_int, C.c_size_t, C.c_int, C.POINTER(_f), C.POINTER(C.c_size_t)]
         L.aeto_sgd_weights.argtypes = [_f, _f, C.c_size_t, C.c_int, C.c_float, C.c_float, C.c_float]
         L.aeto_sgd_plain.argtypes = [_f, _f, C.c_size_t, C.c_int, C.c_float, C.c_float]
         L.aeto_net_create.argtypes = [C.POINTER(LayerSpec)] + [C.c_int] * 7
@@ -296,6 +298,24 @@ class Oracle:
         self.lib.aeto_dropout_forward(_fp(x), _fp(_arr(r)), x.size, probability)
         return x
 
+    def shortcut_forward(self, x, adds):
+        """x: [batch, outputs]; adds: list of [batch, outputs_i].  Returns input + sources, before the activation."""
+        x = _arr(x)
+        adds = [_arr(a) for a in adds]
+        out = np.empty_like(x)
+        ptrs = (_f * len(adds))(*[_fp(a) for a in adds])
+        sizes = (C.c_size_t * len(adds))(*[a.shape[1] for a in adds])
+        self.lib.aeto_shortcut_forward(_fp(x), _fp(out), x.shape[0], x.shape[1], len(adds), ptrs, sizes)
+        return out
+
+    def shortcut_backward(self, delta, delta_out, layer_deltas):
+        """Adds delta [batch, outputs] into delta_out (or None) and into every layer_deltas[i] [batch, outputs_i], in place."""
+        delta = _arr(delta)
+        ptrs = (_f * len(layer_deltas))(*[_fp(a) for a in layer_deltas])
+        sizes = (C.c_size_t * len(layer_deltas))(*[a.shape[1] for a in layer_deltas])
+        self.lib.aeto_shortcut_backward(_fp(delta), _fp(delta_out) if delta_out is not None else None, delta.shape[0],
+                                        delta.shape[1], len(layer_deltas), ptrs, sizes)
+
     def net(self, specs, batch, c, h, w, mode=MODE_MTCS, threads=1):
         return OracleNet(self, specs, batch, c, h, w, mode, threads)
 
@@ -308,7 +328,12 @@ class OracleNet:
         arr = (LayerSpec * len(specs))()
         for s, d in zip(arr, specs):
             for k, v in d.items():
-                setattr(s, k, v)
+                if k == "from":
+                    s.n_from = len(v)
+                    for q, idx in enumerate(v):
+                        s.from_[q] = idx
+                else:
+                    setattr(s, k, v)
             if not s.stride_y:
                 s.stride_y = s.stride_x
         self.n, self.batch = len(specs), batch

@@ -5,7 +5,7 @@ the product package never imports it."""
 
 ACT = {"linear": 0, "relu": 1, "leaky": 2, "logistic": 3, "relu6": 4, "relie": 5, "ramp": 6, "tanh": 7, "plse": 8, "elu": 9,
        "loggy": 10, "hardtan": 11, "lhtan": 12, "selu": 13}
-CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT = 0, 1, 2, 3, 4
+CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT, SHORTCUT = 0, 1, 2, 3, 4, 5
 
 
 def parse(text):
@@ -59,6 +59,11 @@ def network_spec(text, batch=0):
             layers.append(dict(type=SOFTMAX, groups=int(s.get("groups", 1)), temperature=float(s.get("temperature", 1))))
         elif name == "dropout":
             layers.append(dict(type=DROPOUT, probability=float(s.get("probability", .2))))
+        elif name == "shortcut":
+            index = len(layers)
+            src = [int(t) for t in s["from"].split(",") if t.strip()]
+            layers.append(dict(type=SHORTCUT, activation=ACT[s.get("activation", "linear")],
+                               **{"from": [i + index if i < 0 else i for i in src]}))
         else:
             raise ValueError("unsupported layer type [%s]" % name)
     return net, layers

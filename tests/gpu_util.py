@@ -39,15 +39,17 @@ def oracle_conv_backward_mt(oracle, x, w, d, stride, pad, need_dx=True):
 def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bias=True, want_dx=True, threads=False, groups=1,
               dilation=1):
     """Forward + backward of one convolution (no BN) on the GPU and in the oracle; returns both result dicts.
-    threads=True runs the oracle's per-image loops over batch slices on all host cores (full-size cases)."""
+    threads=True runs the oracle's per-image loops over batch slices on all host cores (full-size cases).
+    `stride` may be a pair (stride_x, stride_y) (dnn/ConvolutionalLayer.c:703-715)."""
     import aet_cnn_b200.synth as synth
-    oh, ow = (H + 2 * pad - size) // stride + 1, (W + 2 * pad - size) // stride + 1
+    sx, sy = stride if isinstance(stride, tuple) else (stride, stride)
+    oh, ow = (H + 2 * pad - size) // sy + 1, (W + 2 * pad - size) // sx + 1
     x = synth.uniform((N, C, H, W), seed, 1)
     w = synth.normal((K, C // groups, size, size), seed, 2, 0.0, float(np.sqrt(2.0 / (size * size * C // groups))))
     b = synth.normal((K,), seed, 3, 0.0, 0.1) if bias else np.zeros(K, np.float32)
     dy = synth.normal((N, K, oh, ow), seed, 4)
 
-    layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, size, stride, stride, pad, act, 0, 1, groups=groups, dilation=dilation)
+    layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, size, sx, sy, pad, act, 0, 1, groups=groups, dilation=dilation)
     layer.write(aet.P_WEIGHTS, w)
     layer.write(aet.P_BIASES, b)
     xin = aet.Tensor(ctx, N, C, H, W)
@@ -70,7 +72,7 @@ def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bia
     if threads:
         conv = oracle_conv_forward_mt(oracle, x, w, stride, pad)
     else:
-        conv = oracle.conv_forward(x, w, stride, stride, pad, groups=groups, dilation=dilation)
+        conv = oracle.conv_forward(x, w, sx, sy, pad, groups=groups, dilation=dilation)
     y = oracle.activate(oracle.add_bias(conv, b), act, mode)
     # The activation gradient is a step function of the layer's stored output.  Backward parity is
     # taken on identical inputs, so the mask comes from the output the device stored: a TF32-rounded
@@ -80,7 +82,7 @@ def conv_case(aet, ctx, oracle, N, C, H, W, K, size, stride, pad, act, seed, bia
     if threads:
         dw, dx = oracle_conv_backward_mt(oracle, x, w, d, stride, pad, need_dx=want_dx)
     else:
-        dw, dx = oracle.conv_backward(x, w, d, stride, stride, pad, need_dx=want_dx, groups=groups, dilation=dilation)
+        dw, dx = oracle.conv_backward(x, w, d, sx, sy, pad, need_dx=want_dx, groups=groups, dilation=dilation)
     ref = dict(y=y, dw=dw, dx=dx, db=oracle.backward_bias(d))
     return got, ref
 

@@ -295,6 +295,17 @@ def test_conv_groups_and_dilation(aet, ctx, oracle, shape):
     check(got, ref, TOL_TF32)
 
 
+@pytest.mark.parametrize("shape", [
+    (3, 8, 12, 12, 16, 3, (2, 1), 1, 1),     # stride_x = 2, stride_y = 1
+    (3, 8, 12, 12, 16, 3, (1, 2), 1, 2),     # stride_x = 1, stride_y = 2
+    (2, 32, 9, 14, 32, 5, (3, 2), 2, 1),     # 5x5, both strides different, ragged map
+])
+def test_conv_unequal_strides(aet, ctx, oracle, shape):
+    """stride_x != stride_y (dnn/ConvolutionalLayer.c:703-715, the cfg keys stride_x / stride_y): output, dX, dW, db."""
+    got, ref = conv_case(aet, ctx, oracle, *shape, seed=900 + shape[1])
+    check(got, ref, TOL_TF32)
+
+
 def test_bad_arguments_are_rejected(aet, ctx):
     with pytest.raises(aet.AetError):
         aet.ConvolutionalLayer(ctx, 1, 8, 8, 3, 4, 3, groups=2)                # 3 channels do not split in two

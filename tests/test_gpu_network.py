@@ -356,6 +356,149 @@ def test_first_layer_pool_sized_backward(aet, ctx, oracle64, batch, c, h, w, k, 
     assert rel_l2(res[1]["P_DELTA"], res[0]["P_DELTA"]) < 1e-5
 
 
+RESNET_CFG = """[net]
+batch={batch}
+width=16
+height=16
+channels=3
+learning_rate=0.05
+momentum=0.9
+decay=0.0005
+policy=constant
+max_batches=1000
+
+[convolutional]
+filters=32
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+
+[maxpool]
+size=2
+stride=2
+
+[convolutional]
+filters=32
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+
+[convolutional]
+filters=32
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=linear
+
+[shortcut]
+from=-3
+activation=leaky
+
+[convolutional]
+filters=64
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+
+[maxpool]
+size=2
+stride=2
+
+[convolutional]
+filters=20
+size=1
+stride=1
+pad=0
+activation=linear
+
+[convolutional]
+filters=24
+size=1
+stride=1
+pad=0
+activation=leaky
+
+[shortcut]
+from=6,-2
+activation={act2}
+
+[convolutional]
+filters=10
+size=1
+stride=1
+pad=0
+activation=linear
+
+[avgpool]
+
+[softmax]
+groups=1
+"""
+
+
+@pytest.mark.parametrize("act2", ["linear", "relu"])
+def test_residual_network_matches_oracle(aet, ctx, oracle64, act2):
+    """ResNet-style cfg: a shortcut over a two-convolution block (source = a max-pool layer), and a second shortcut with
+    two sources, one with more channels than the layer (64 against 24: its first 24 are added) and one with fewer (20:
+    it reaches the first 20 channels) (dnn/ShortcutLayer.c, dnn/NetworkFactory.c:175-246).  3xTF32 math against the FP64 oracle: every layer's output, the
+    deltas the shortcuts write into their sources, every weight gradient, and four SGD steps of losses."""
+    from oracle import cfgfile
+    import aet_cnn_b200.synth as synth
+    batch = 6
+    text = RESNET_CFG.format(batch=batch, act2=act2)
+    ctx.set_math(aet.MATH_3XTF32)
+    try:
+        net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+        opts, specs = cfgfile.network_spec(text, batch)
+        assert specs[4]["from"] == [1] and specs[9]["from"] == [6, 7]
+        onet = oracle64.net(specs, batch, 3, 16, 16, threads=os.cpu_count() or 1)
+        cin = 3
+        for i, s in enumerate(specs):
+            if s["type"] == cfgfile.CONV:
+                w = synth.normal((s["filters"], cin, s["size"], s["size"]), 31, i, 0.0, float(np.sqrt(2.0 / (s["size"] ** 2 * cin))))
+                net.layer(i).write(aet.P_WEIGHTS, w)
+                onet.set_param(i, ob.P_WEIGHTS, w)
+                cin = s["filters"]
+        x = synth.uniform((batch, 3, 16, 16), 31, 100)
+        _, truth = synth.labels(batch, 10, 31, 101)
+        net.input.write(x); net.truth.write(truth)
+        ctx.profile(1)
+        net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+        net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+        names = {r["name"].split("#")[0] for r in ctx.profile_read()}
+        ctx.profile(0)
+        assert "shortcut_fwd" in names and "shortcut_bwd" in names, sorted(names)
+        onet.forward(x, truth); onet.backward(x)
+        ctx.check()
+        for i in range(net.layer_count):
+            assert rel_l2(net.layer(i).read(aet.P_OUTPUT), onet.param(i, ob.P_OUTPUT)) < 2e-5, ("output", i)
+        for i in (1, 3, 4, 6, 7, 8, 9):   # the sources' deltas and the shortcuts' own
+            assert rel_l2(net.layer(i).read(aet.P_DELTA), onet.param(i, ob.P_DELTA)) < 2e-4, ("delta", i)
+        for i, s in enumerate(specs):
+            if s["type"] == cfgfile.CONV:
+                assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 2e-4, ("wgrad", i)
+        net.update()
+        onet.update(batch, opts["learning_rate"], opts["momentum"], opts["decay"])
+        net.use_graph(True)
+        for step in range(1, 5):
+            xs = synth.uniform((batch, 3, 16, 16), 31, 100 + 2 * step)
+            _, ts = synth.labels(batch, 10, 31, 101 + 2 * step)
+            got = net.train(xs, ts)
+            want = onet.train_step(xs, ts, opts["learning_rate"], opts["momentum"], opts["decay"])
+            assert abs(got - want) < 2e-3 * abs(want), (step, got, want)
+        ctx.check()
+        net.close()
+    finally:
+        ctx.set_math(aet.MATH_TF32)
+
+
 def test_linear_head_matches_the_separate_layers(aet, ctx, oracle):
     """In a network's training pass the 1x1 classifier convolution, the global average pool and the softmax
     run on the pooled vectors (exact FP32) instead of as a TF32 convolution over the feature map: everything

@@ -269,3 +269,86 @@ def test_inference_helpers_known_values(oracle):
     assert list(oracle.top_k(np.array([0.1, 0.7, 0.05, 0.15], np.float32), 2)) == [1, 3]
     assert list(oracle.top_k(np.array([0.2, 0.2, 0.6], np.float32), 3)) == [2, 1, 0]      # a displaced entry falls behind its equals
     assert list(oracle.transpose_matrix([1, 2, 3, 4, 5, 6], 2, 3)) == [1, 4, 2, 5, 3, 6]
+
+
+def test_shortcut_known_values(oracle):
+    """ShortcutLayer without weights (dnn/ShortcutLayer.c:272-353, :132-230): sources are added over the flat per-sample
+    index range they have, so a narrower source reaches only the first channels; backward adds the delta to the
+    previous delta and to every source's delta over the same range."""
+    x = np.arange(12, dtype=np.float32).reshape(2, 6)
+    wide = 10 * np.ones((2, 8), np.float32)
+    narrow = np.array([[1, 2, 3], [4, 5, 6]], np.float32)
+    out = oracle.shortcut_forward(x, [wide, narrow])
+    want = x + 10
+    want[:, :3] += narrow
+    assert np.array_equal(out, want)
+    delta = np.arange(12, dtype=np.float32).reshape(2, 6) + 1
+    pd = np.ones((2, 6), np.float32)
+    dw, dn = np.zeros((2, 8), np.float32), np.full((2, 3), 2, np.float32)
+    oracle.shortcut_backward(delta, pd, [dw, dn])
+    assert np.array_equal(pd, delta + 1)
+    assert np.array_equal(dw[:, :6], delta) and np.all(dw[:, 6:] == 0)
+    assert np.array_equal(dn, delta[:, :3] + 2)
+
+
+def test_residual_network_gradient_by_finite_differences(oracle64):
+    """A residual block (conv, conv, shortcut from the first conv) through the whole-network oracle: the shortcut's
+    output is activation(conv 2 + conv 1), and the weight gradient of the convolution behind the block agrees with
+    central differences of the cost (the block's forward is what the differences exercise)."""
+    from oracle import cfgfile
+    text = """[net]
+batch=2
+height=4
+width=4
+channels=2
+[convolutional]
+filters=4
+size=3
+stride=1
+pad=1
+activation=leaky
+[convolutional]
+filters=4
+size=3
+stride=1
+pad=1
+activation=leaky
+[shortcut]
+from=-2
+activation=leaky
+[convolutional]
+filters=3
+size=1
+stride=1
+pad=0
+activation=linear
+[avgpool]
+[softmax]
+"""
+    opts, specs = cfgfile.network_spec(text, 2)
+    assert specs[2]["type"] == cfgfile.SHORTCUT and specs[2]["from"] == [0]
+    net = oracle64.net(specs, 2, 2, 4, 4)
+    rng = np.random.default_rng(5)
+    for i in (0, 1, 3):
+        w = net.param(i, ob.P_WEIGHTS)
+        net.set_param(i, ob.P_WEIGHTS, rng.normal(0, .5, w.shape).astype(np.float32))
+    x = rng.uniform(0, 1, (2, 2, 4, 4)).astype(np.float32)
+    truth = np.zeros((2, 3), np.float32); truth[0, 1] = truth[1, 2] = 1
+    net.forward(x, truth); net.backward(x)
+    # forward: the shortcut's output is leaky(conv2 + conv1)
+    o0, o1, o2 = (net.param(i, ob.P_OUTPUT).astype(np.float64) for i in (0, 1, 2))
+    pre = o0 + o1
+    assert np.allclose(o2, np.where(pre > 0, pre, .1 * pre), atol=1e-6)
+    # backward on the unaffected last convolution: central differences of the cost
+    g = net.param(3, ob.P_WEIGHT_UPDATES).copy()
+    w3 = net.param(3, ob.P_WEIGHTS).copy()
+    eps = 1e-3
+    for k in range(0, w3.size, 5):
+        wp, wm = w3.copy(), w3.copy()
+        wp.flat[k] += eps; wm.flat[k] -= eps
+        net.set_param(3, ob.P_WEIGHTS, wp); net.forward(x, truth); cp = net.cost()
+        net.set_param(3, ob.P_WEIGHTS, wm); net.forward(x, truth); cm = net.cost()
+        num = (cp - cm) / (2 * eps)
+        # weight_updates accumulate the NEGATIVE gradient of the cost (the update adds them)
+        assert abs(-g.flat[k] - num) < 2e-3 * max(1.0, abs(num)), (k, g.flat[k], num)
+    net.set_param(3, ob.P_WEIGHTS, w3)
