@@ -396,6 +396,12 @@ inline int ctx_smem_attr(aet_context *ctx, F *func, int bytes = 220 * 1024) {
 int side_begin(aet_context *ctx);
 void side_end(aet_context *ctx);
 int side_join(aet_context *ctx);
+// Entry points make their context's device the calling thread's current one: a process may hold contexts on several
+// GPUs (or another library may have switched the device), and allocations and launches follow the current device.
+static inline void ctx_enter(const aet_context *ctx) {
+    int d = -1;
+    if (ctx && cudaGetDevice(&d) == cudaSuccess && d != ctx->device) cudaSetDevice(ctx->device);
+}
 int ctx_staging(aet_context *ctx, size_t bytes);
 
 // ---- layout taps (tensor.cu) ------------------------------------------------------------------

@@ -159,12 +159,14 @@ aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, 
 extern "C" aet_layer *aet_convolutional_layer_create(aet_context *ctx, int batch, int h, int w, int c, int n, int groups,
                                                      int size, int stride_x, int stride_y, int dilation, int padding,
                                                      aet_activation activation, int batch_normalize, int train) {
+    ctx_enter(ctx);
     return conv_layer_create_in(ctx, nullptr, batch, h, w, c, n, groups, size, stride_x, stride_y, dilation, padding,
                                 activation, batch_normalize, train, 0);
 }
 
 extern "C" aet_layer *aet_maxpool_layer_create(aet_context *ctx, int batch, int h, int w, int c, int size, int stride_x,
                                                int stride_y, int padding, int train) {
+    ctx_enter(ctx);
     if (!ctx || batch <= 0 || h <= 0 || w <= 0 || c <= 0 || size <= 0 || stride_x <= 0 || stride_y <= 0 || padding < 0) {
         aet_set_error("maxpool: bad geometry");
         return nullptr;
@@ -190,6 +192,7 @@ extern "C" aet_layer *aet_maxpool_layer_create(aet_context *ctx, int batch, int 
 }
 
 extern "C" aet_layer *aet_avgpool_layer_create(aet_context *ctx, int batch, int w, int h, int c) {
+    ctx_enter(ctx);
     if (!ctx || batch <= 0 || h <= 0 || w <= 0 || c <= 0) { aet_set_error("avgpool: bad geometry"); return nullptr; }
     aet_layer *l = new aet_layer();
     l->ctx = ctx; l->type = AET_AVGPOOL;
@@ -202,6 +205,7 @@ extern "C" aet_layer *aet_avgpool_layer_create(aet_context *ctx, int batch, int 
 }
 
 extern "C" aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int inputs, int groups, float temperature) {
+    ctx_enter(ctx);
     if (!ctx || batch <= 0 || inputs <= 0 || groups <= 0 || inputs % groups || !(temperature > 0.f)) {
         aet_set_error("softmax: bad arguments");
         return nullptr;
@@ -224,6 +228,7 @@ extern "C" aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int 
 }
 
 extern "C" aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int inputs, float probability, aet_layer *prev) {
+    ctx_enter(ctx);
     if (!ctx || !prev || !prev->output || batch != prev->batch || inputs != prev->oc * prev->oh * prev->ow ||
         !(probability >= 0.f && probability < 1.f)) {
         aet_set_error("dropout: bad arguments (needs the previous layer and a matching input count)");
@@ -248,6 +253,7 @@ extern "C" aet_layer *aet_dropout_layer_create(aet_context *ctx, int batch, int 
 
 extern "C" aet_layer *aet_shortcut_layer_create(aet_context *ctx, int batch, int h, int w, int c, int n, aet_layer *const *from,
                                                 aet_activation activation, int train) {
+    ctx_enter(ctx);
     if (!ctx || batch <= 0 || h <= 0 || w <= 0 || c <= 0 || n < 1 || n > 4 || !from) {
         aet_set_error("shortcut: bad arguments (1 to 4 source layers)");
         return nullptr;
@@ -274,6 +280,7 @@ extern "C" aet_layer *aet_shortcut_layer_create(aet_context *ctx, int batch, int
 }
 
 extern "C" void aet_layer_destroy(aet_layer *l) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l) return;
     if (l->ctx) cudaStreamSynchronize(l->ctx->stream);
     conv_release(l);
@@ -312,6 +319,7 @@ static int check_input(const aet_layer *l, const aet_tensor *in) {
 }
 
 extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l) return fail_invalid("null layer");
     l->ctx->prof_tag = l->net ? l->index : -1;
     AET_TRY(check_input(l, state.input));
@@ -422,6 +430,7 @@ extern "C" int aet_layer_forward(aet_layer *l, aet_state state) {
 
 // ---------------------------------------------------------------------------- backward
 extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l) return fail_invalid("null layer");
     l->ctx->prof_tag = l->net ? l->index : -1;
     if (!l->delta) return fail_invalid("layer was created with train=0");
@@ -537,6 +546,7 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
 
 // ---------------------------------------------------------------------------- update
 extern "C" int aet_layer_update(aet_layer *l, int batch, float learning_rate, float momentum, float decay, float loss_scale) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l) return fail_invalid("null layer");
     if (l->type != AET_CONVOLUTIONAL) return AET_OK;
     if (batch <= 0 || !(loss_scale > 0.f)) return fail_invalid("update: batch and loss_scale must be positive");
@@ -599,6 +609,7 @@ extern "C" int aet_layer_out_shape(const aet_layer *l, int *c, int *h, int *w) {
 }
 
 extern "C" float aet_layer_cost(aet_layer *l) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l || l->type != AET_SOFTMAX) return 0.f;
     if (!l->cost_valid) {
         float v = 0.f;
@@ -642,6 +653,7 @@ static int read_vec_sum(aet_layer *l, const float *a, const float *b, float *hos
 }
 
 extern "C" int aet_layer_read(aet_layer *l, aet_param which, void *host_v) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l || !host_v) return fail_invalid("aet_layer_read: null argument");
     if (aet_layer_param_count(l, which) == 0) return fail_invalid("aet_layer_read: this layer has no such buffer");
     float *host = static_cast<float *>(host_v);
@@ -717,6 +729,7 @@ static int write_vec(aet_layer *l, float *dev, const float *host, size_t n, floa
 }
 
 extern "C" int aet_layer_write(aet_layer *l, aet_param which, const void *host_v) {
+    ctx_enter(l ? l->ctx : nullptr);
     if (!l || !host_v) return fail_invalid("aet_layer_write: null argument");
     if (aet_layer_param_count(l, which) == 0) return fail_invalid("aet_layer_write: this layer has no such buffer");
     const float *host = static_cast<const float *>(host_v);

@@ -392,6 +392,7 @@ bool host_pinned(const void *p) {
 
 // ---------------------------------------------------------------------------- creation
 extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_text, int train, int batch_override) {
+    ctx_enter(ctx);
     if (!ctx || !cfg_text) { aet_set_error("aet_network_create: null argument"); return nullptr; }
     std::vector<Section> secs;
     if (parse_cfg(cfg_text, secs) != AET_OK) return nullptr;
@@ -632,6 +633,7 @@ extern "C" aet_network *aet_network_create(aet_context *ctx, const char *cfg_pat
 }
 
 extern "C" void aet_network_destroy(aet_network *net) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) return;
     if (net->ctx) cudaStreamSynchronize(net->ctx->stream);
     aet_network_comm_destroy(net);
@@ -689,14 +691,17 @@ extern "C" int64_t aet_network_seen(const aet_network *net) { return net ? net->
 
 // ---------------------------------------------------------------------------- forward / backward / update
 extern "C" int aet_network_forward(aet_network *net, aet_state state) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     return net_forward(net, state);
 }
 extern "C" int aet_network_backward(aet_network *net, aet_state state) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     return net_backward(net, state);
 }
 extern "C" int aet_network_update(aet_network *net) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     AET_TRY(upload_hyper(net));
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
@@ -705,6 +710,7 @@ extern "C" int aet_network_update(aet_network *net) {
     return AET_OK;
 }
 extern "C" float aet_network_cost(aet_network *net) {
+    ctx_enter(net ? net->ctx : nullptr);
     // dnn/NNetwork.c:611-624
     if (!net) return 0.f;
     float sum = 0.f;
@@ -715,6 +721,7 @@ extern "C" float aet_network_cost(aet_network *net) {
 }
 
 extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     if (!net->train) { aet_set_error("network was created with train=0"); return AET_E_INVALID; }
     if (net->bn_fused) { aet_set_error("batch-norm layers were fused into their convolutions: this network only predicts"); return AET_E_INVALID; }
@@ -761,6 +768,7 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
 }
 
 extern "C" int aet_network_last_loss(aet_network *net, float *loss) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !loss) { aet_set_error("null argument"); return AET_E_INVALID; }
     aet_layer *sm = softmax_layer(net);
     AET_TRY(queue_loss_readback(net, net->loss_pinned));
@@ -774,6 +782,7 @@ extern "C" int aet_network_last_loss(aet_network *net, float *loss) {
 }
 
 extern "C" int aet_network_train_step(aet_network *net, const float *host_x, const float *host_truth, float *loss) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !host_x || !host_truth) { aet_set_error("aet_network_train_step: null argument"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
     const size_t nx = net->input->count(), nt = net->truth->count();
@@ -807,6 +816,7 @@ extern "C" int aet_network_train_step(aet_network *net, const float *host_x, con
 // its step (mtcs/MtcsIOData.c:50-52); here the double buffer is on the device: the copy of THIS call's batch
 // runs on a copy stream while the PREVIOUS call's step still computes, and nothing waits for this step.
 extern "C" int aet_network_train_step_async(aet_network *net, const float *host_x, const float *host_truth, float *previous_loss) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !host_x || !host_truth) { aet_set_error("aet_network_train_step_async: null argument"); return AET_E_INVALID; }
     if (!net->train) { aet_set_error("network was created with train=0"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
@@ -878,6 +888,7 @@ extern "C" int aet_network_train_step_async(aet_network *net, const float *host_
 }
 
 extern "C" int aet_network_predict(aet_network *net, const float *host_x, float *host_out) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !host_x || !host_out) { aet_set_error("aet_network_predict: null argument"); return AET_E_INVALID; }
     AET_TRY(aet_tensor_write(net->input, host_x));
     aet_state st = {};
@@ -888,6 +899,7 @@ extern "C" int aet_network_predict(aet_network *net, const float *host_x, float 
 
 // NNetwork.fuseConvBatchnorm (dnn/NNetwork.c:272-290), the convolutional branch.
 extern "C" int aet_network_fuse_conv_batchnorm(aet_network *net) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     graph_drop(net);
     for (aet_layer *l : net->layers)
@@ -898,6 +910,7 @@ extern "C" int aet_network_fuse_conv_batchnorm(aet_network *net) {
 
 // Forward with train = 0 on a host batch, then DnnUtils.topK (dnn/DnnUtils.c:463-477) per sample on the device.
 extern "C" int aet_network_predict_topk(aet_network *net, const float *host_x, int k, int *host_indexes) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !host_x || !host_indexes || k <= 0) { aet_set_error("aet_network_predict_topk: bad argument"); return AET_E_INVALID; }
     aet_layer *last = net->layers.back();
     const int classes = last->oc * last->oh * last->ow;
@@ -920,6 +933,7 @@ extern "C" int aet_network_predict_topk(aet_network *net, const float *host_x, i
 // and cropped by the caller: predict, top-k, count hits.  top1 = avg_acc / count, topk = avg_topk / count.
 extern "C" int aet_network_validate(aet_network *net, const float *host_images, const int *class_ids, int count, int k,
                                     float *top1, float *topk) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !host_images || !class_ids || count <= 0 || k <= 0) { aet_set_error("aet_network_validate: bad argument"); return AET_E_INVALID; }
     const size_t per = (size_t)net->c * net->h * net->w;
     aet_layer *last = net->layers.back();
@@ -948,6 +962,7 @@ extern "C" int aet_network_validate(aet_network *net, const float *host_images, 
 // The augmentation chain of ImageData.loadImageAugmentPaths (dnn/ImageData.c:56-73) on the device: upload the source
 // images and the per-image draws, one kernel writes the network's input tensor.
 extern "C" int aet_network_augment_input(aet_network *net, const float *host_src, int src_h, int src_w, const aet_augment *params) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !host_src || !params || src_h <= 0 || src_w <= 0) { aet_set_error("aet_network_augment_input: bad argument"); return AET_E_INVALID; }
     if (net->w != net->h) { aet_set_error("aet_network_augment_input: only square network inputs (the crop is size x size)"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
@@ -972,6 +987,7 @@ extern "C" int aet_network_augment_input(aet_network *net, const float *host_src
 }
 
 extern "C" int aet_network_use_graph(aet_network *net, int enable) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
     net->use_graph = enable != 0;
     if (!enable) graph_drop(net);
@@ -1017,7 +1033,69 @@ extern "C" int aet_network_load_weights(aet_network *net, const char *path) {
     return r;
 }
 
+// Momentum side file.  The .weights container carries no momentum buffers, so a run resumed from it differs from an
+// uninterrupted one (dnn/NNetwork.c:112-147 saves only biases, scales, rolling statistics and weights).  This optional
+// file holds what is missing: "AETM", int32 version = 1, uint64 seen, then per convolutional layer in layer order the
+// records bias_updates[K], then for batch-norm layers scale_updates[K] and the last batch mean[K] (the next step's
+// statistics are accumulated around it, so it decides their rounding), then weight_updates[K*C/groups*k*k], all FP32
+// in the .weights file's element order.
+extern "C" int aet_network_save_momentum(aet_network *net, const char *path) {
+    if (!net || !path) { aet_set_error("null argument"); return AET_E_INVALID; }
+    FILE *fp = fopen(path, "wb");
+    if (!fp) { aet_set_error("cannot open %s for writing", path); return AET_E_IO; }
+    const int32_t version = 1;
+    const uint64_t seen = (uint64_t)net->seen;
+    bool ok = fwrite("AETM", 1, 4, fp) == 4 && fwrite(&version, sizeof(version), 1, fp) == 1 && fwrite(&seen, sizeof(seen), 1, fp) == 1;
+    int r = AET_OK;
+    std::vector<float> v;
+    for (size_t i = 0; ok && r == AET_OK && i < net->layers.size(); ++i) {
+        aet_layer *l = net->layers[i];
+        if (l->type != AET_CONVOLUTIONAL) continue;
+        const aet_param order[4] = {AET_P_BIAS_UPDATES, AET_P_SCALE_UPDATES, AET_P_MEAN, AET_P_WEIGHT_UPDATES};
+        for (int k = 0; k < 4 && ok && r == AET_OK; ++k) {
+            if ((k == 1 || k == 2) && !l->bn) continue;
+            v.resize(aet_layer_param_count(l, order[k]));
+            r = aet_layer_read(l, order[k], v.data());
+            if (r == AET_OK) ok = fwrite(v.data(), sizeof(float), v.size(), fp) == v.size();
+        }
+    }
+    fclose(fp);
+    if (!ok) { aet_set_error("momentum file: short write"); return AET_E_IO; }
+    return r;
+}
+
+extern "C" int aet_network_load_momentum(aet_network *net, const char *path) {
+    if (!net || !path) { aet_set_error("null argument"); return AET_E_INVALID; }
+    FILE *fp = fopen(path, "rb");
+    if (!fp) { aet_set_error("cannot open momentum file %s", path); return AET_E_IO; }
+    char magic[4];
+    int32_t version = 0;
+    uint64_t seen = 0;
+    if (fread(magic, 1, 4, fp) != 4 || memcmp(magic, "AETM", 4) != 0 || fread(&version, sizeof(version), 1, fp) != 1 || version != 1 ||
+        fread(&seen, sizeof(seen), 1, fp) != 1) {
+        fclose(fp);
+        aet_set_error("momentum file %s: bad header", path);
+        return AET_E_IO;
+    }
+    int r = AET_OK;
+    std::vector<float> v;
+    for (size_t i = 0; r == AET_OK && i < net->layers.size(); ++i) {
+        aet_layer *l = net->layers[i];
+        if (l->type != AET_CONVOLUTIONAL) continue;
+        const aet_param order[4] = {AET_P_BIAS_UPDATES, AET_P_SCALE_UPDATES, AET_P_MEAN, AET_P_WEIGHT_UPDATES};
+        for (int k = 0; k < 4 && r == AET_OK; ++k) {
+            if ((k == 1 || k == 2) && !l->bn) continue;
+            v.resize(aet_layer_param_count(l, order[k]));
+            if (fread(v.data(), sizeof(float), v.size(), fp) != v.size()) { aet_set_error("momentum file: unexpected end (layer %d)", l->index); r = AET_E_IO; break; }
+            r = aet_layer_write(l, order[k], v.data());
+        }
+    }
+    fclose(fp);
+    return r;
+}
+
 extern "C" int aet_network_param_hash(aet_network *net, uint64_t *hash) {
+    ctx_enter(net ? net->ctx : nullptr);
     if (!net || !hash) { aet_set_error("null argument"); return AET_E_INVALID; }
     aet_context *ctx = net->ctx;
     uint64_t *dev = nullptr;

@@ -301,11 +301,13 @@ extern "C" int aet_context_set_math(aet_context *ctx, aet_math_mode mode) {
     return AET_OK;
 }
 extern "C" int aet_context_synchronize(aet_context *ctx) {
+    ctx_enter(ctx);
     if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
     AET_CUDA(cudaStreamSynchronize(ctx->stream));
     return AET_OK;
 }
 extern "C" int aet_context_check(aet_context *ctx) {
+    ctx_enter(ctx);
     if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
     int st = 0;
     AET_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -331,11 +333,13 @@ extern "C" int aet_context_set_wait_limit(aet_context *ctx, unsigned long long n
 }
 
 extern "C" int aet_context_wait_probe(aet_context *ctx) {
+    ctx_enter(ctx);
     if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
     return conv_wait_probe(ctx);
 }
 
 extern "C" int aet_context_profile(aet_context *ctx, int enable) {
+    ctx_enter(ctx);
     if (!ctx) { aet_set_error("null context"); return AET_E_INVALID; }
     AET_CUDA(cudaStreamSynchronize(ctx->stream));
     ctx->profiling = enable != 0;
@@ -352,6 +356,7 @@ extern "C" int aet_context_profile(aet_context *ctx, int enable) {
 }
 
 extern "C" int aet_context_profile_read(aet_context *ctx, aet_kernel_time *table, int capacity, int *count) {
+    ctx_enter(ctx);
     if (!ctx || !table || !count) { aet_set_error("null argument"); return AET_E_INVALID; }
     AET_CUDA(cudaStreamSynchronize(ctx->stream));
     std::vector<unsigned long long> spans;
@@ -454,6 +459,7 @@ int vector_download(aet_context *ctx, const float *dev, float *host, size_t coun
 
 // ---------------------------------------------------------------------------- tensors
 extern "C" aet_tensor *aet_tensor_create(aet_context *ctx, int batch, int c, int h, int w) {
+    ctx_enter(ctx);
     if (!ctx || batch <= 0 || c <= 0 || h <= 0 || w <= 0) {
         aet_set_error("aet_tensor_create: bad shape %d x %d x %d x %d", batch, c, h, w);
         return nullptr;
@@ -470,6 +476,7 @@ extern "C" aet_tensor *aet_tensor_create(aet_context *ctx, int batch, int c, int
     return t;
 }
 extern "C" void aet_tensor_destroy(aet_tensor *t) {
+    ctx_enter(t ? t->ctx : nullptr);
     if (!t) return;
     if (t->owns && t->d) {
         cudaStreamSynchronize(t->ctx->stream);
@@ -487,14 +494,17 @@ extern "C" int aet_tensor_shape(const aet_tensor *t, int *batch, int *c, int *h,
 }
 extern "C" size_t aet_tensor_count(const aet_tensor *t) { return t ? t->count() : 0; }
 extern "C" int aet_tensor_write(aet_tensor *t, const float *host_nchw) {
+    ctx_enter(t ? t->ctx : nullptr);
     if (!t || !host_nchw) { aet_set_error("aet_tensor_write: null argument"); return AET_E_INVALID; }
     return tensor_upload_nchw(t->ctx, t->d, host_nchw, t->n, t->c, t->h, t->w, t->cp, false);
 }
 extern "C" int aet_tensor_read(const aet_tensor *t, float *host_nchw) {
+    ctx_enter(t ? t->ctx : nullptr);
     if (!t || !host_nchw) { aet_set_error("aet_tensor_read: null argument"); return AET_E_INVALID; }
     return tensor_download_nchw(t->ctx, t->d, host_nchw, t->n, t->c, t->h, t->w, t->cp);
 }
 extern "C" int aet_tensor_zero(aet_tensor *t) {
+    ctx_enter(t ? t->ctx : nullptr);
     if (!t) { aet_set_error("null tensor"); return AET_E_INVALID; }
     AET_CUDA(cudaMemsetAsync(t->d, 0, t->elems() * sizeof(float), t->ctx->stream));
     return AET_OK;

@@ -262,6 +262,12 @@ int   aet_network_use_graph(aet_network *net, int enable);
 /* NNetwork.loadWeights / saveWeights (dnn/NNetwork.c:64-147): Darknet .weights container. */
 int   aet_network_load_weights(aet_network *net, const char *path);
 int   aet_network_save_weights(aet_network *net, const char *path);
+/* Optional side file with the step-to-step state the .weights container leaves out (bias / scale / weight updates and,
+ * for batch-norm layers, the last batch mean, per convolutional layer in the .weights file's order), so that a run
+ * resumed from both files continues bit for bit.
+ * No reference counterpart: dnn/NNetwork.c:112-147 does not save them. */
+int   aet_network_save_momentum(aet_network *net, const char *path);
+int   aet_network_load_momentum(aet_network *net, const char *path);
 /* 64-bit hash of all weights, biases, scales and momentum buffers (data-parallel consistency check). */
 int   aet_network_param_hash(aet_network *net, uint64_t *hash);
 /* Per-kernel device timing of the next train steps (aet_context_profile on the network's context;

@@ -34,3 +34,29 @@ def test_two_ranks_nccl_and_peer_exchange_agree():
     # a rank that sits out a step: the other rank's update is skipped as a whole and the step reports the timeout
     assert "aet error -5" in out["absent_peer"]["message"], out["absent_peer"]
     assert out["absent_peer"]["unchanged"], out["absent_peer"]
+
+
+def test_two_contexts_on_two_devices_in_one_process(aet):
+    """One process, one context per GPU (the ABI allows it): kernels that need the large dynamic shared-memory opt-in
+    must get it on BOTH devices (function attributes are per device), and the same training steps give the same
+    parameters on either GPU."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import aet_cnn_b200.synth as synth
+    text = open(os.path.join(aet.CFG_DIR, "cifar_small.cfg")).read()
+    batch = 128          # the benchmark's batch: the row-sharing and thin kernels with > 48 KB of shared memory run
+    x = [synth.uniform((batch, 3, 32, 32), 5, 2 * s) for s in range(2)]
+    t = [synth.labels(batch, 10, 5, 2 * s + 1)[1] for s in range(2)]
+    hashes, losses = [], []
+    for dev in (0, 1):
+        ctx = aet.Context(dev)
+        net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+        import bench
+        bench.init_weights(aet, synth, net, 3)
+        losses.append([net.train(x[s], t[s]) for s in range(2)])
+        ctx.check()
+        hashes.append(net.param_hash())
+        net.close(); ctx.close()
+    assert hashes[0] == hashes[1]
+    assert losses[0] == losses[1]

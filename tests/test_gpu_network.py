@@ -556,6 +556,46 @@ def test_weights_file_roundtrip_and_layout(aet, ctx, oracle):
     net.close()
 
 
+def test_resume_from_weights_and_momentum_files_is_bit_exact(aet, ctx, oracle):
+    """A run stopped after three steps and resumed in a fresh network from the .weights file plus the momentum side file
+    continues exactly like the uninterrupted run (same parameter hash after three more steps); from the .weights file
+    alone it does not (the reference's container has no momentum buffers, dnn/NNetwork.c:112-147)."""
+    batch = 8
+
+    def steps(net, opts, first, last):
+        for s in range(first, last):
+            net.train(*batch_for(opts, 10, batch, 11, s))
+
+    net, _, opts, _ = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+    steps(net, opts, 0, 3)
+    with tempfile.TemporaryDirectory() as d:
+        wpath, mpath = os.path.join(d, "a.weights"), os.path.join(d, "a.momentum")
+        net.save_weights(wpath)
+        net.save_momentum(mpath)
+        steps(net, opts, 3, 6)
+        want = net.param_hash()
+        net.close()
+        hashes = {}
+        for with_momentum in (True, False):
+            fresh, _, _, _ = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+            fresh.load_weights(wpath)
+            if with_momentum:
+                fresh.load_momentum(mpath)
+            steps(fresh, opts, 3, 6)
+            hashes[with_momentum] = fresh.param_hash()
+            fresh.close()
+        with open(mpath, "rb") as f:
+            assert f.read(4) == b"AETM"
+        with pytest.raises(aet.AetError):
+            net2, _, _, _ = build_pair(aet, ctx, oracle, "cifar_small.cfg", batch)
+            try:
+                net2.load_momentum(wpath)       # not a momentum file
+            finally:
+                net2.close()
+    assert hashes[True] == want
+    assert hashes[False] != want
+
+
 def test_bad_cfg_is_rejected(aet, ctx):
     for text in ["[convolutional]\nfilters=2\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\nactivation=mish\n",
