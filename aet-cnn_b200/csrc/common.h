@@ -78,6 +78,7 @@ enum AetOption {
     OPT_DUAL_ACC,          // two accumulators per tile when a CTA owns one tile (row-sharing kernels; off by default)   AET_DUAL_ACC
     OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
     OPT_STEM,              // first convolution + BN + 2x2 max-pool: weight gradient from the pool-sized tensors   AET_NO_STEM
+    OPT_RAGGED,            // TMA kernels on maps whose rows do not divide the tile (13x13, 27x27)   AET_NO_RAGGED
     OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels; off by default   AET_PAIR
     OPT_COUNT
 };

@@ -87,8 +87,13 @@ struct TmaArgs {
     int slabs_per_tap;   // fprop/dgrad: inner channel count / 32
     int S, pad;
     int pix_per_img, tile_w, img_w;  // M-tile (fprop/dgrad) or K-slab (wgrad) decomposition
+    // Maps whose rows do not divide the tile ("ragged": 13x13, 27x27): an M tile (fprop/dgrad) or K slab (wgrad) is
+    // `rows_t` whole rows of ONE image, `tiles_per_img` of them per image; the tile's remaining rows stay unused
+    // (M: never stored; K: zero in both operands).  0 = dense tiling.
+    int tiles_per_img, rows_t, img_h;
     int total_slabs, slabs_per_split;
     int col_blocks;      // wgrad: N tiles per tap
+    int m_blocks;        // wgrad: 32-filter blocks of the A operand per stage
     int stages, tmem_cols;
     uint32_t tx_bytes, a_bytes;
     int *status;
@@ -103,7 +108,22 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM;
+    int m0 = blockIdx.x * BM;
+    int rows_here = a.n_rows - m0;          // rows of this M tile that exist
+    int img0 = 0, row0 = 0;                 // fprop/dgrad tile origin
+    if (KIND != KIND_WGRAD) {
+        if (a.tiles_per_img) {
+            img0 = blockIdx.x / a.tiles_per_img;
+            row0 = (blockIdx.x - img0 * a.tiles_per_img) * a.rows_t;
+            int rows = a.img_h - row0;
+            if (rows > a.rows_t) rows = a.rows_t;
+            m0 = img0 * a.pix_per_img + row0 * a.tile_w;
+            rows_here = rows * a.tile_w;
+        } else {
+            img0 = m0 / a.pix_per_img;
+            row0 = (m0 - img0 * a.pix_per_img) / a.tile_w;
+        }
+    }
     const int bn = a.bn;
     int n0 = blockIdx.y * bn;   // GEMM column of this tile
     int tap_w = 0, cblk_w = 0;  // wgrad: tap and channel block of this N tile
@@ -142,14 +162,21 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctl.tmem_base;
+    if (KIND == KIND_WGRAD && a.tiles_per_img) {
+        // ragged K slabs: the copies fill only the first rows_t * width pixel rows of every 32-row slab; the rest
+        // must read as zero in both operands, so the stages start out cleared
+        float4 *z = reinterpret_cast<float4 *>(smem_raw + (smem_base - smem_u32(smem_raw)));
+        const uint32_t n16 = (uint32_t)a.stages * stage_bytes / 16;
+        for (uint32_t i = threadIdx.x; i < n16; i += NTHREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        fence_proxy_async_smem();
+        __syncthreads();
+    }
     pdl_enter();   // everything above touched only shared memory, TMEM and kernel parameters
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp < 4) {
         if (threadIdx.x == 0) {
             // ------------------------------------------------------------------ TMA producer
-            const int img0 = m0 / a.pix_per_img;                       // fprop/dgrad tile origin
-            const int row0 = (m0 - img0 * a.pix_per_img) / a.tile_w;
             // CTAs walk the K slabs from different starting points: all of them read the same weight
             // tiles, and marching in lockstep would send every SM to the same L2 lines at once.  The
             // order is a function of the CTA index only, so results stay reproducible.
@@ -174,6 +201,16 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int r = tap / a.S, sx = tap - r * a.S;
                     tma_load_4d(sa, &map_a, bar, kb * 32, a.pad - sx, row0 + a.pad - r, img0);
                     tma_load_4d(sb, &map_b, bar, 0, kb * 32, n0 / 32, tap);
+                } else if (a.tiles_per_img) {
+                    // ragged: one copy per 32-element block of each operand (a block is 4 KB in the swizzled layout,
+                    // a copy of several blocks would pack them at the box's own, smaller, pitch)
+                    const int sl = slab_begin + it;
+                    const int img = sl / a.tiles_per_img;
+                    const int oh0 = (sl - img * a.tiles_per_img) * a.rows_t;
+                    const int r = tap_w / a.S, sx = tap_w - r * a.S;
+                    for (int q = 0; q < a.m_blocks; ++q) tma_load_5d(sa + q * 4096u, &map_a, bar, 0, 0, oh0, img, m0 / 32 + q);
+                    for (int q = 0; q < bn / 32; ++q)
+                        tma_load_5d(sb + q * 4096u, &map_b, bar, 0, sx - a.pad, oh0 + r - a.pad, img, cblk_w * (bn / 32) + q);
                 } else {
                     const int p0 = (slab_begin + it) * BK;
                     const int img = p0 / a.pix_per_img;
@@ -195,7 +232,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
             StatAcc st;
             stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
-            store_accumulator<KIND == KIND_FPROP>(tile, tmem, nslabs > 0, warp, lane, bn, obase, (size_t)a.out_ld, a.n_rows - m0,
+            store_accumulator<KIND == KIND_FPROP>(tile, tmem, nslabs > 0, warp, lane, bn, obase, (size_t)a.out_ld, rows_here,
                                                   n0, a.n_cols, a.bias, a.act, 1, 1, 0, &st);
             if (KIND == KIND_FPROP && st.shift)
                 stats_commit(tile, st, warp, lane, bn, a.stat_partial + (size_t)blockIdx.x * 2 * a.out_ld + n0, a.out_ld, a.n_cols - n0,
@@ -259,6 +296,17 @@ bool pixel_box(int tile, int h, int w, cuuint32_t *bw, cuuint32_t *bh, cuuint32_
     return bw[0] <= 256 && bh[0] <= 256 && bi[0] <= 256;
 }
 
+// Ragged tiling of an h x w map: `tile` / w whole rows per tile (at least one), ceil(h / rows) tiles per image.
+// Refused when the tiles would be less than half full (tiny maps): the dense gather kernel is the better choice
+// there, and the forward statistics scratch is sized for at most two tiles per 128 pixels.
+bool ragged_box(int tile, int h, int w, int *rows, int *per_img) {
+    if (w <= 0 || h <= 0 || w > tile) return false;
+    *rows = tile / w;
+    if (*rows > h) *rows = h;
+    *per_img = (h + *rows - 1) / *rows;
+    return 2 * h * w >= *per_img * tile;
+}
+
 template <int KIND>
 int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, TmaArgs &t, dim3 grid, const char *name,
                double flops) {
@@ -279,17 +327,23 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
 
 // Input channels must fill whole 32-channel (128-byte) rows.  The filter side may be narrower than one
 // row (ocp < 32: the copy engine zero-fills the rest of the box) or a whole number of rows.
-bool tma_common_ok(const aet_layer *l) {
+// (The forward pass reads the filters as rows of a K-major tile, so any filter count works there: rows past the last
+// filter are zero-filled by the copy.)
+bool tma_common_ok(const aet_layer *l, bool filters_inner = true) {
     const ConvGeom g = layer_geom(l);   // the geometry the kernels see (a fully connected layer is a 1x1 convolution)
     return l->ctx->conv_path == 0 && l->ctx->math == AET_MATH_TF32 && l->groups == 1 && l->dilation == 1 && g.sx == 1 && g.sy == 1 &&
-           g.cp % 32 == 0 && (g.kp % 32 == 0 || g.kp < 32);
+           g.cp % 32 == 0 && (!filters_inner || g.kp % 32 == 0 || g.kp < 32);
 }
 
 int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     const ConvGeom &g = a.g;
-    if (!tma_common_ok(l)) return 1;
+    if (!tma_common_ok(l, false)) return 1;
     cuuint32_t bw, bh, bi;
-    if (!pixel_box(BM, g.OH, g.OW, &bw, &bh, &bi) || (int)bw != g.OW) return 1;
+    int rows_t = 0, per_img = 0;
+    if (!pixel_box(BM, g.OH, g.OW, &bw, &bh, &bi) || (int)bw != g.OW) {
+        if (!l->ctx->opt[OPT_RAGGED] || !ragged_box(BM, g.OH, g.OW, &rows_t, &per_img)) return 1;
+        bw = (cuuint32_t)g.OW; bh = (cuuint32_t)rows_t; bi = 1;
+    }
     if (g.OW > g.W || g.OH > g.H) return 1;
     const int bn = a.bn;                      // any multiple of 16: K-major rows in 8-row swizzle groups
     const CUtensorMap *ma, *mb;
@@ -313,10 +367,11 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     t.pix_per_img = g.OH * g.OW; t.tile_w = g.OW; t.img_w = g.OW;
     t.total_slabs = a.k_total / 32; t.slabs_per_split = t.total_slabs;
     t.a_bytes = BM * BK * 4;
-    t.tx_bytes = t.a_bytes + bn * BK * 4;
-    dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    t.tx_bytes = (uint32_t)(bw * bh * bi) * BK * 4 + bn * BK * 4;
+    t.tiles_per_img = per_img; t.rows_t = rows_t; t.img_h = g.OH;
+    dim3 grid(per_img ? g.N * per_img : (a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
     if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;   // only the forward launcher is given one
-    return launch_tma<KIND_FPROP>(l->ctx, ma, mb, t, grid, "conv_fprop_tma", flops);
+    return launch_tma<KIND_FPROP>(l->ctx, ma, mb, t, grid, per_img ? "conv_fprop_tma.ragged" : "conv_fprop_tma", flops);
 }
 
 int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
@@ -324,9 +379,18 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
     if (!tma_common_ok(l)) return 1;
     if (g.OH != g.H || g.OW != g.W) return 1;   // same-size convolutions only
     cuuint32_t bw, bh, bi;
-    if (!pixel_box(BM, g.H, g.W, &bw, &bh, &bi) || (int)bw != g.W) return 1;
-    const int bn = a.bn % 32 == 0 ? a.bn : 0;
-    if (!bn || g.cp % bn) return 1;
+    int rows_t = 0, per_img = 0;
+    if (!pixel_box(BM, g.H, g.W, &bw, &bh, &bi) || (int)bw != g.W) {
+        if (!l->ctx->opt[OPT_RAGGED] || !ragged_box(BM, g.H, g.W, &rows_t, &per_img)) return 1;
+        bw = (cuuint32_t)g.W; bh = (cuuint32_t)rows_t; bi = 1;
+    }
+    // N tile: whole 32-channel blocks that divide the channel count; the caller's choice when it qualifies, otherwise
+    // the widest divisor up to 256 (384 channels -> 192, 96 -> 96)
+    int bn = (a.bn % 32 == 0 && g.cp % a.bn == 0) ? a.bn : 0;
+    if (!bn)
+        for (int c = 256; c >= 32; c -= 32)
+            if (g.cp % c == 0) { bn = c; break; }
+    if (!bn) return 1;
     const CUtensorMap *ma, *mb;
     {
         cuuint64_t dims[4] = {(cuuint64_t)g.kp, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N};
@@ -349,10 +413,11 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
     t.pix_per_img = g.H * g.W; t.tile_w = g.W; t.img_w = g.W;
     t.total_slabs = g.R * g.S * t.slabs_per_tap; t.slabs_per_split = t.total_slabs;
     t.a_bytes = BM * BK * 4;
-    t.tx_bytes = t.a_bytes + bn * BK * 4;
-    dim3 grid((a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    t.tx_bytes = (uint32_t)(bw * bh * bi) * BK * 4 + bn * BK * 4;
+    t.tiles_per_img = per_img; t.rows_t = rows_t; t.img_h = g.H;
+    dim3 grid(per_img ? g.N * per_img : (a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
     if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;   // only the forward launcher is given one
-    return launch_tma<KIND_DGRAD>(l->ctx, ma, mb, t, grid, "conv_dgrad_tma", flops);
+    return launch_tma<KIND_DGRAD>(l->ctx, ma, mb, t, grid, per_img ? "conv_dgrad_tma.ragged" : "conv_dgrad_tma", flops);
 }
 
 // `a.out` already points at the split-K partial buffer sized for `splits_hint` splits of the
@@ -362,7 +427,11 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
     if (!tma_common_ok(l)) return 1;
     if (g.OW > g.W || g.OH > g.H) return 1;
     cuuint32_t bw, bh, bi;
-    if (!pixel_box(BK, g.OH, g.OW, &bw, &bh, &bi)) return 1;
+    int rows_t = 0, per_img = 0;
+    if (!pixel_box(BK, g.OH, g.OW, &bw, &bh, &bi)) {
+        if (!l->ctx->opt[OPT_RAGGED] || g.OW != g.W || g.OH != g.H || g.kp % 32 || !ragged_box(BK, g.OH, g.OW, &rows_t, &per_img)) return 1;
+        bw = (cuuint32_t)g.OW; bh = (cuuint32_t)rows_t; bi = 1;
+    }
     const int bn = g.cp <= 256 ? g.cp : (g.cp % 256 == 0 ? 256 : (g.cp % 128 == 0 ? 128 : 0));
     if (!bn) return 1;
     const int k_blocks = (g.kp + 31) / 32;
@@ -372,13 +441,13 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
         cuuint64_t dims[5] = {(cuuint64_t)(g.kp < 32 ? g.kp : 32), (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N,
                               (cuuint64_t)k_blocks};
         cuuint64_t str[4] = {(cuuint64_t)g.kp * 4, (cuuint64_t)g.OW * g.kp * 4, (cuuint64_t)g.OH * g.OW * g.kp * 4, 128};
-        cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)m_blocks};
+        cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)(per_img ? 1 : m_blocks)};
         if (get_map(l, 4, a.src_a, 5, dims, str, box, true, &ma) != AET_OK) return g.kp % 32 ? 1 : AET_E_CUDA;
     }
     {
         cuuint64_t dims[5] = {32, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N, (cuuint64_t)g.cp / 32};
         cuuint64_t str[4] = {(cuuint64_t)g.cp * 4, (cuuint64_t)g.W * g.cp * 4, (cuuint64_t)g.H * g.W * g.cp * 4, 128};
-        cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)bn / 32};
+        cuuint32_t box[5] = {32, bw, bh, bi, (cuuint32_t)(per_img ? 1 : bn / 32)};
         AET_TRY(get_map(l, 5, a.src_b, 5, dims, str, box, true, &mb));
     }
     TmaArgs t = {};
@@ -390,11 +459,19 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
     t.total_slabs = (a.k_total + BK - 1) / BK;
     t.slabs_per_split = a.k_per_split / BK;
     t.col_blocks = g.cp / bn;
+    t.m_blocks = m_blocks;
     t.a_bytes = BM * BK * 4;                                   // stage slot; the copy fills m_blocks * 4 KB of it
     t.tx_bytes = (uint32_t)m_blocks * 4096 + (uint32_t)bn * BK * 4;
+    if (per_img) {
+        // slabs are rows_t rows of one image; the split count and the partial buffer stay the caller's
+        t.tiles_per_img = per_img; t.rows_t = rows_t; t.img_h = g.OH;
+        t.total_slabs = g.N * per_img;
+        t.slabs_per_split = (t.total_slabs + splits_hint - 1) / splits_hint;
+        t.tx_bytes = (uint32_t)(m_blocks + bn / 32) * (uint32_t)(bw * bh) * 128u;
+    }
     const int m_tiles = (g.K + BM - 1) / BM;
     dim3 grid(m_tiles, g.R * g.S * t.col_blocks, splits_hint);
-    return launch_tma<KIND_WGRAD>(l->ctx, ma, mb, t, grid, "conv_wgrad_tma", flops);
+    return launch_tma<KIND_WGRAD>(l->ctx, ma, mb, t, grid, per_img ? "conv_wgrad_tma.ragged" : "conv_wgrad_tma", flops);
 }
 
 void tma_release(aet_layer *l) {

@@ -47,8 +47,7 @@ class Oracle:
     def __init__(self, variant="parity"):
         name = {"parity": "libaet_oracle.so", "acc64": "libaet_oracle_acc64.so", "fast": "libaet_oracle_fast.so"}[variant]
         path = os.path.join(HERE, "_build", name)
-        if not os.path.exists(path):
-            build("fast" if variant == "fast" else "parity")
+        build("fast" if variant == "fast" else "parity")   # make rebuilds only what is older than its sources
         L = self.lib = C.CDLL(path)
         L.aeto_gemm.argtypes = [C.c_int] * 5 + [C.c_float, _f, C.c_int, _f, C.c_int, C.c_float, _f, C.c_int]
         L.aeto_im2col.argtypes = [_f] + [C.c_int] * 9 + [_f]

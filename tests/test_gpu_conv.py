@@ -89,6 +89,65 @@ def test_conv_tma_tf32(aet, ctx, oracle, shape):
     check(got, ref, TOL_TF32)
 
 
+# Maps whose rows do not divide the 128-pixel tile / 32-pixel slab (the 27x27 and 13x13 maps of an AlexNet-style
+# network): the TMA kernels tile them as whole rows of one image and leave the rest of the tile unused.
+RAGGED_SHAPES = [
+    (4, 96, 27, 27, 256, 5, 1, 2, 1),      # AlexNet-style conv 2: 5x5, 4 rows per tile, 7 tiles per image (the last one 3 rows)
+    (4, 256, 13, 13, 384, 3, 1, 1, 1),     # conv 3: 9 rows per tile, 2 tiles per image; 384 filters = three 128-filter tiles
+    (5, 384, 13, 13, 256, 3, 1, 1, 2),     # conv 5
+    (3, 64, 13, 13, 64, 3, 1, 1, 2),       # one N tile, odd batch
+    (2, 32, 7, 20, 32, 3, 1, 1, 0),        # non-square: 6 + 1 rows
+    (2, 64, 9, 100, 32, 1, 1, 0, 1),       # one row per tile (w > 64), 1x1
+]
+
+
+@pytest.mark.parametrize("shape", RAGGED_SHAPES)
+def test_conv_tma_ragged_maps(aet, ctx, oracle, shape):
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=700 + shape[1], threads=shape[1] >= 96)
+        used = variants_used(ctx)
+    finally:
+        ctx.profile(0)
+    names = {u.split("#")[0] for u in used}
+    want = {"conv_fprop_tma.ragged", "conv_dgrad_tma.ragged"}
+    if shape[3] <= 32:          # a weight-gradient K slab is 32 pixels: rows wider than that stay on the gather kernel
+        want.add("conv_wgrad_tma.ragged")
+    assert want <= names, sorted(names)
+    check(got, ref, TOL_TF32)
+    # and the same shapes with the option off go to the gather kernel and agree with it closely
+    ctx.set_option("ragged", 0)
+    ctx.profile(1)
+    try:
+        alt, _ = conv_case(aet, ctx, oracle, *shape, seed=700 + shape[1], threads=shape[1] >= 96)
+        used = kernels_used(ctx)
+    finally:
+        ctx.profile(0)
+        ctx.set_option("ragged", 1)
+    assert "conv_fprop_gather" in used, used
+    for key in ("y", "dw", "dx", "db"):
+        assert rel_l2(got[key], alt[key]) < 2e-3, key
+
+
+@pytest.mark.parametrize("shape", [
+    (8, 256, 1, 1, 1000, 1, 1, 0, 0),      # a 1000-class fully connected layer as a 1x1 convolution
+    (3, 64, 8, 8, 100, 3, 1, 1, 2),        # 100 filters, 3x3
+])
+def test_conv_tma_forward_takes_any_filter_count(aet, ctx, oracle, shape):
+    """The forward TMA kernel reads the filters as rows of its second operand, so their count need not be a multiple
+    of 32 (rows past the last filter are zero-filled by the copy); the gradients of such a layer use the other kernels."""
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=750 + shape[4])
+        used = kernels_used(ctx)
+    finally:
+        ctx.profile(0)
+    assert {"conv_fprop_tma", "conv_fprop_tma_rows"} & used, used
+    check(got, ref, TOL_TF32)
+
+
 # few input channels: the whole K extent fits one stage of the persistent first-layer kernels
 THIN_SHAPES = [
     (2, 3, 8, 8, 5, 3, 1, 1, 2),          # one ragged tile

@@ -499,6 +499,83 @@ def test_residual_network_matches_oracle(aet, ctx, oracle64, act2):
         ctx.set_math(aet.MATH_TF32)
 
 
+RAGGED_BN_CFG = """[net]
+batch=6
+width=13
+height=13
+channels=32
+learning_rate=0.05
+momentum=0.9
+decay=0.0005
+
+[convolutional]
+filters=64
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+
+[convolutional]
+filters=32
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+
+[convolutional]
+filters=10
+size=1
+stride=1
+pad=0
+activation=linear
+
+[avgpool]
+
+[softmax]
+groups=1
+"""
+
+
+def test_batchnorm_statistics_from_ragged_tiles(aet, ctx, oracle):
+    """BN convolutions on 13x13 maps: the TMA forward kernel tiles each image as 9 + 4 rows and its epilogue's batch
+    statistics must count exactly the pixels that exist.  Default TF32 math against the oracle: means, variances,
+    outputs, weight gradients."""
+    from oracle import cfgfile
+    import aet_cnn_b200.synth as synth
+    batch = 6
+    net = aet.NNetwork(ctx, cfg_text=RAGGED_BN_CFG, train=1, batch=batch)
+    opts, specs = cfgfile.network_spec(RAGGED_BN_CFG, batch)
+    onet = oracle.net(specs, batch, 32, 13, 13, threads=os.cpu_count() or 1)
+    cin = 32
+    for i, s in enumerate(specs):
+        if s["type"] == cfgfile.CONV:
+            w = synth.normal((s["filters"], cin, s["size"], s["size"]), 41, i, 0.0, float(np.sqrt(2.0 / (s["size"] ** 2 * cin))))
+            net.layer(i).write(aet.P_WEIGHTS, w)
+            onet.set_param(i, ob.P_WEIGHTS, w)
+            cin = s["filters"]
+    x = synth.uniform((batch, 32, 13, 13), 41, 100)
+    _, truth = synth.labels(batch, 10, 41, 101)
+    net.input.write(x); net.truth.write(truth)
+    ctx.profile(1)
+    net.forward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    net.backward(aet.make_state(input=net.input, truth=net.truth, train=1))
+    names = {r["name"].split("#")[0] for r in ctx.profile_read()}
+    ctx.profile(0)
+    assert {"conv_fprop_tma.ragged", "conv_dgrad_tma.ragged", "conv_wgrad_tma.ragged"} <= names, sorted(names)
+    assert "bn_stats" not in names, sorted(names)      # the statistics came out of the convolution's epilogue
+    onet.forward(x, truth); onet.backward(x)
+    ctx.check()
+    for i in (0, 1):
+        assert rel_l2(net.layer(i).read(aet.P_MEAN), onet.param(i, ob.P_MEAN)) < 1e-2, i
+        assert rel_l2(net.layer(i).read(aet.P_VARIANCE), onet.param(i, ob.P_VARIANCE)) < 1e-2, i
+        assert rel_l2(net.layer(i).read(aet.P_OUTPUT), onet.param(i, ob.P_OUTPUT)) < 1e-2, i
+    for i in (0, 1, 2):
+        assert rel_l2(net.layer(i).read(aet.P_WEIGHT_UPDATES), onet.param(i, ob.P_WEIGHT_UPDATES)) < 5e-2, i
+    net.close()
+
+
 def test_linear_head_matches_the_separate_layers(aet, ctx, oracle):
     """In a network's training pass the 1x1 classifier convolution, the global average pool and the softmax
     run on the pooled vectors (exact FP32) instead of as a TF32 convolution over the feature map: everything
