@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libaet_b200.so")
 CFG_DIR = os.path.join(HERE, "cfg")
 
-LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU = range(14)
+LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU, SWISH, MISH = range(16)
 CONVOLUTIONAL, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT, SHORTCUT = 0, 1, 2, 3, 4, 5
 PARITY_CPU, PARITY_MTCS = 0, 1
 MATH_TF32, MATH_3XTF32 = 0, 1

@@ -20,6 +20,11 @@ __host__ __device__ __noinline__ static float act_forward_other(float x, int act
     case AET_HARDTAN: return x < -1.f ? -1.f : (x > 1.f ? 1.f : x);
     case AET_LHTAN: return x < 0.f ? .001f * x : (x > 1.f ? .001f * (x - 1.f) + 1.f : x);
     case AET_SELU: return (x >= 0.f) * 1.0507f * x + (x < 0.f) * 1.0507f * 1.6732f * (expf(x) - 1.f);
+    case AET_SWISH: return x * (1.f / (1.f + expf(-x)));                                  // dnn/IOData.c:75-88
+    case AET_MISH: {                                                                      // dnn/IOData.c:92-105
+        const float sp = x > 20.f ? x : (x < -20.f ? expf(x) : logf(expf(x) + 1.f));       // softplus, threshold 20
+        return x * (2.f / (1.f + expf(-2.f * sp)) - 1.f);
+    }
     default: return x;
     }
 }
@@ -52,4 +57,24 @@ __host__ __device__ __forceinline__ float act_gradient(float y, int act) {
     if (act == AET_RELU) return y > 0.f ? 1.f : 0.f;
     if (act == AET_LINEAR) return 1.f;
     return act_gradient_other(y, act);
+}
+
+// swish and mish: d activation / d input as a function of the INPUT v (dnn/Activation.c:303-330; the reference keeps
+// sigmoid(v), respectively v, in a side buffer for this, the kernels here recompute v)
+__host__ __device__ __noinline__ static float act_gradient_input_other(float v, int act) {
+    if (act == AET_SWISH) {
+        const float sg = 1.f / (1.f + expf(-v)), sw = v * sg;
+        return sw + sg * (1.f - sw);
+    }
+    const float sp = v > 20.f ? v : (v < -20.f ? expf(v) : logf(expf(v) + 1.f));
+    const float grad_sp = 1.f - expf(-sp);
+    const float tsp = tanhf(sp);
+    const float grad_tsp = (1.f - tsp * tsp) * grad_sp;
+    return v * grad_tsp + tsp;
+}
+__host__ __device__ __forceinline__ bool act_needs_input(int act) { return act >= AET_SWISH; }
+// gradient of any supported activation from the value before the activation
+__host__ __device__ __forceinline__ float act_gradient_pre(float v, int act) {
+    if (act < AET_SWISH) return act_gradient(act_forward(v, act), act);
+    return act_gradient_input_other(v, act);
 }

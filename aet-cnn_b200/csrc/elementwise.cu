@@ -172,10 +172,10 @@ __global__ void __launch_bounds__(TB) reduce2_kernel(const ReduceArgs a) {
                 } else if (MODE == 1) {
                     const float4 t = v[u];
                     float4 q = d[u];
-                    q.x *= act_grad(act_fwd(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
-                    q.y *= act_grad(act_fwd(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
-                    q.z *= act_grad(act_fwd(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
-                    q.w *= act_grad(act_fwd(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+                    q.x *= act_gradient_pre(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act);
+                    q.y *= act_gradient_pre(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act);
+                    q.z *= act_gradient_pre(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act);
+                    q.w *= act_gradient_pre(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act);
                     s1.x += q.x; s1.y += q.y; s1.z += q.z; s1.w += q.w;
                     s2.x += q.x * (t.x - mean.x); s2.y += q.y * (t.y - mean.y);
                     s2.z += q.z * (t.z - mean.z); s2.w += q.w * (t.w - mean.w);
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(TB) bn_bwd_poolwin_kernel(const PoolWinArgs a)
                 const float x3 = k == 0 ? v[3].x : (k == 1 ? v[3].y : (k == 2 ? v[3].z : v[3].w));
                 const float xa = t == 0 ? x0 : (t == 1 ? x1 : (t == 2 ? x2 : x3));
                 tsel[k] = t;
-                qa[k] = t >= 0 ? dvs[k] * act_grad(act_fwd(bn_val(xa, means[k], invs[k], gams[k], bets[k]), a.act), a.act) : 0.f;
+                qa[k] = t >= 0 ? dvs[k] * act_gradient_pre(bn_val(xa, means[k], invs[k], gams[k], bets[k]), a.act) : 0.f;
             }
         }
 #pragma unroll
@@ -508,10 +508,10 @@ __global__ void __launch_bounds__(TB) bn_bwd_apply_kernel(const BwdApplyArgs a) 
             if (p >= p1) continue;
             const float4 t = v[u];
             float4 q = d[u];
-            q.x *= act_grad(act_fwd(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act), a.act);
-            q.y *= act_grad(act_fwd(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act), a.act);
-            q.z *= act_grad(act_fwd(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act), a.act);
-            q.w *= act_grad(act_fwd(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act), a.act);
+            q.x *= act_gradient_pre(bn_val(t.x, mean.x, inv.x, gam.x, bet.x), a.act);
+            q.y *= act_gradient_pre(bn_val(t.y, mean.y, inv.y, gam.y, bet.y), a.act);
+            q.z *= act_gradient_pre(bn_val(t.z, mean.z, inv.z, gam.z, bet.z), a.act);
+            q.w *= act_gradient_pre(bn_val(t.w, mean.w, inv.w, gam.w, bet.w), a.act);
             q.x = q.x * ka.x + (t.x - mean.x) * kb.x + kc.x;
             q.y = q.y * ka.y + (t.y - mean.y) * kb.y + kc.y;
             q.z = q.z * ka.z + (t.z - mean.z) * kb.z + kc.z;

@@ -9,6 +9,7 @@
 #include <string.h>
 
 #include "common.h"
+#include "activation.cuh"
 
 namespace {
 
@@ -96,6 +97,11 @@ aet_layer *conv_layer_create_in(aet_context *ctx, ParamArena *arena, int batch, 
     }
     if (batch_normalize != 0 && batch_normalize != 1) { aet_set_error("convolutional: batch_normalize must be 0 or 1"); return nullptr; }
     if ((int)activation < 0 || (int)activation >= AET_ACTIVATION_COUNT) { aet_set_error("convolutional: unsupported activation"); return nullptr; }
+    if (act_needs_input(activation) && !batch_normalize) {
+        aet_set_error("convolutional: swish / mish need batch_normalize=1 (their gradient is formed from the value before the "
+                      "activation, which only the batch-norm backward kernels recompute)");
+        return nullptr;
+    }
     if (batch <= 0 || h <= 0 || w <= 0 || c <= 0 || n <= 0 || size <= 0 || stride_x <= 0 || stride_y <= 0 || padding < 0) {
         aet_set_error("convolutional: bad geometry");
         return nullptr;
@@ -258,7 +264,10 @@ extern "C" aet_layer *aet_shortcut_layer_create(aet_context *ctx, int batch, int
         aet_set_error("shortcut: bad arguments (1 to 4 source layers)");
         return nullptr;
     }
-    if ((int)activation < 0 || (int)activation >= AET_ACTIVATION_COUNT) { aet_set_error("shortcut: unknown activation"); return nullptr; }
+    if ((int)activation < 0 || (int)activation >= AET_ACTIVATION_COUNT || act_needs_input(activation)) {
+        aet_set_error("shortcut: unsupported activation (swish / mish are not restated for shortcut layers)");
+        return nullptr;
+    }
     for (int i = 0; i < n; ++i) {
         const aet_layer *f = from[i];
         if (!f || !f->output || f->batch != batch || f->oh != h || f->ow != w) {   // dnn/NetworkFactory.c:234

@@ -77,15 +77,15 @@ std::string opt_str(const Section &s, const char *key, const char *def) {
 }
 
 int parse_activation(const std::string &a, aet_activation *out) {
-    // dnn/Activation.c:105-124, restricted to the types whose gradient is a function of the output
+    // dnn/Activation.c:105-124, restricted to the types this library restates
     static const struct { const char *name; aet_activation act; } table[] = {
         {"linear", AET_LINEAR}, {"relu", AET_RELU}, {"leaky", AET_LEAKY}, {"logistic", AET_LOGISTIC}, {"relu6", AET_RELU6},
         {"relie", AET_RELIE}, {"ramp", AET_RAMP}, {"tanh", AET_TANH}, {"plse", AET_PLSE}, {"elu", AET_ELU}, {"loggy", AET_LOGGY},
-        {"hardtan", AET_HARDTAN}, {"lhtan", AET_LHTAN}, {"selu", AET_SELU}};
+        {"hardtan", AET_HARDTAN}, {"lhtan", AET_LHTAN}, {"selu", AET_SELU}, {"swish", AET_SWISH}, {"mish", AET_MISH}};
     for (const auto &e : table)
         if (a == e.name) { *out = e.act; return AET_OK; }
     aet_set_error("activation '%s' is outside the supported set (linear, relu, leaky, logistic, relu6, relie, ramp, tanh, plse, "
-                  "elu, loggy, hardtan, lhtan, selu)", a.c_str());
+                  "elu, loggy, hardtan, lhtan, selu, swish, mish)", a.c_str());
     return AET_E_INVALID;
 }
 
@@ -300,7 +300,10 @@ int net_backward(aet_network *net, aet_state state, bool exchange = true) {
             const size_t lo = l->seg_w.offset, hi = last.offset + last.padded;
             if (pend_hi == pend_lo) { pend_lo = lo; pend_hi = hi; }
             else pend_lo = lo;   // layers are laid out in order, so walking backwards extends the range downwards
-            if (br == AET_OK && pend_hi - pend_lo >= bucket_floats && slot < 7) {
+            // A bucket is sent as soon as it is full, unless what is left below it is small: the collectives of one
+            // communicator run one after the other, so a separate small last bucket would queue behind this one and
+            // add its whole latency to the end of the step; together they are one collective.
+            if (br == AET_OK && pend_hi - pend_lo >= bucket_floats && pend_lo >= bucket_floats / 2 && slot < 7) {
                 br = issue_allreduce(net, pend_lo, pend_hi, slot++);
                 pend_lo = pend_hi = 0;
             }

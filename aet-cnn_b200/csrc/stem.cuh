@@ -117,8 +117,7 @@ __global__ void __launch_bounds__(THREADS, MINB) stem_bwd_sparse_kernel(const St
             const int cd = cds[w * ocp + k];
             const float ym = yms[w * ocp + k], dv = dvs[w * ocp + k];
             const float xm = __fsub_rn(ym, mean);
-            const float y = act_fwd(__fadd_rn(__fmul_rn(__fmul_rn(xm, inv), gam), bet), a.act);
-            const float q = (cd < 4 && w < wlim) ? dv * act_grad(y, a.act) : 0.f;
+            const float q = (cd < 4 && w < wlim) ? dv * act_gradient_pre(__fadd_rn(__fmul_rn(__fmul_rn(xm, inv), gam), bet), a.act) : 0.f;
             s1 += q;
             s2 = fmaf(q, xm, s2);
             // the argmax pixel's receptive-field corner in nb: row cd>>1, column 2*window + (cd&1)

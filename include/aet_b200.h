@@ -35,13 +35,16 @@ extern "C" {
 #define AET_E_NCCL      (-6)
 #define AET_E_NAN       (-7)   /* non-finite values detected (try_fix_nan diagnostics) */
 
-/* dnn/Activation.h:15-19: the types whose gradient is a function of the output (dnn/Activation.h:41-113).  The
- * first three are the hot path's; cfg names are the reference's ("logistic", "relu6", "relie", "ramp", "tanh",
- * "plse", "elu", "loggy", "hardtan", "lhtan", "selu").  stair, gelu, swish, mish and the channel normalisations
- * are not built. */
+/* dnn/Activation.h:15-19.  The first fourteen have gradients that are functions of the OUTPUT (dnn/Activation.h:41-113);
+ * the first three are the hot path's; cfg names are the reference's ("logistic", "relu6", "relie", "ramp", "tanh",
+ * "plse", "elu", "loggy", "hardtan", "lhtan", "selu").  swish and mish (dnn/IOData.c:75-105, dnn/Activation.c:303-330)
+ * need the value BEFORE the activation for their gradient: they are taken by batch-normalised convolutions, whose
+ * backward kernels recompute that value from the stored convolution result; other layers reject them.  stair, gelu,
+ * hard_mish and the channel normalisations are not built. */
 typedef enum { AET_LINEAR = 0, AET_RELU = 1, AET_LEAKY = 2, AET_LOGISTIC = 3, AET_RELU6 = 4, AET_RELIE = 5, AET_RAMP = 6,
-               AET_TANH = 7, AET_PLSE = 8, AET_ELU = 9, AET_LOGGY = 10, AET_HARDTAN = 11, AET_LHTAN = 12, AET_SELU = 13 } aet_activation;
-#define AET_ACTIVATION_COUNT 14
+               AET_TANH = 7, AET_PLSE = 8, AET_ELU = 9, AET_LOGGY = 10, AET_HARDTAN = 11, AET_LHTAN = 12, AET_SELU = 13,
+               AET_SWISH = 14, AET_MISH = 15 } aet_activation;
+#define AET_ACTIVATION_COUNT 16
 /* dnn/NLayer.c:30-60 layer kinds that NetworkFactory.createLayer instantiates on the hot path */
 typedef enum { AET_CONVOLUTIONAL = 0, AET_MAXPOOL = 1, AET_AVGPOOL = 2, AET_SOFTMAX = 3, AET_DROPOUT = 4, AET_SHORTCUT = 5 } aet_layer_type;
 /* Which of the reference's two numerically different back ends the formulas follow:

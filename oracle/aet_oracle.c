@@ -207,6 +207,14 @@ void aeto_backward_bias(float *bias_updates, const float *delta, int batch, int 
 /* Scalar activations, dnn/Activation.h:41-113 (CPU, double intermediates where the reference's literals are double)
  * and mtcs/MtcsActivation.c:17-103 (GPU, float).  Numbering: AETO_LINEAR 0, RELU 1, LEAKY 2, then LOGISTIC 3,
  * RELU6 4, RELIE 5, RAMP 6, TANH 7, PLSE 8, ELU 9, LOGGY 10, HARDTAN 11, LHTAN 12, SELU 13. */
+/* dnn/Activation.h:108-113 (softplus_activate) and :69 (tanh_activate) */
+static float softplus_ref(float x, float threshold) {
+    if (x > threshold) return x;
+    else if (x < -threshold) return expf(x);
+    return logf(expf(x) + 1);
+}
+static float tanh_ref(float x) { return (2 / (1 + expf(-2 * x)) - 1); }
+
 static float act_cpu(float x, int a) {
     switch (a) {
     case 0: return x;
@@ -223,6 +231,8 @@ static float act_cpu(float x, int a) {
     case 11: if (x < -1) return -1; if (x > 1) return 1; return x;
     case 12: if (x < 0) return .001 * x; if (x > 1) return .001 * (x - 1) + 1; return x;
     case 13: return (x >= 0) * 1.0507 * x + (x < 0) * 1.0507 * 1.6732 * (exp(x) - 1);
+    case 14: { float sg = 1. / (1. + exp(-x)); return x * sg; }                                  /* dnn/IOData.c:75-88 */
+    case 15: return x * tanh_ref(softplus_ref(x, 20));                                          /* dnn/IOData.c:92-105 */
     default: return x;
     }
 }
@@ -242,6 +252,8 @@ static float act_mtcs(float x, int a) {
     case 11: if (x < -1) return -1; if (x > 1) return 1; return x;
     case 12: if (x < 0) return .001 * x; if (x > 1) return .001 * (x - 1) + 1; return x;
     case 13: return (x >= 0) * 1.0507f * x + (x < 0) * 1.0507f * 1.6732f * (expf(x) - 1);
+    case 14: { float sg = 1.f / (1.f + expf(-x)); return x * sg; }
+    case 15: return x * tanh_ref(softplus_ref(x, 20));
     default: return x;
     }
 }
@@ -274,6 +286,27 @@ void aeto_activate(float *y, size_t count, int activation, int mode) {
 void aeto_gradient(const float *y, size_t count, int activation, float *delta) {
     if (activation == AETO_LINEAR) return;
     for (size_t i = 0; i < count; ++i) delta[i] *= act_grad(y[i], activation);
+}
+
+/* swish and mish, dnn/Activation.c:303-330: the gradient needs what the forward pass kept in `activation_input`
+ * (sigmoid(v) for swish, v itself for mish); here `v` is the value before the activation for both. */
+void aeto_gradient_input(const float *y, const float *v, size_t count, int activation, float *delta) {
+    for (size_t i = 0; i < count; ++i) {
+        if (activation == 14) {
+            float sigmoid = 1.f / (1.f + expf(-v[i]));   /* logistic_activate, as activateArraySwish stored it */
+            float swish = y[i];
+            delta[i] *= swish + sigmoid * (1 - swish);
+        } else if (activation == 15) {
+            const float MISH_THRESHOLD = 20.0f;
+            float inp = v[i];
+            const float sp = softplus_ref(inp, MISH_THRESHOLD);
+            const float grad_sp = 1 - exp(-sp);
+            const float tsp = tanh(sp);
+            const float grad_tsp = (1 - tsp * tsp) * grad_sp;
+            const float grad = inp * grad_tsp + tsp;
+            delta[i] *= grad;
+        }
+    }
 }
 
 /* ------------------------------------------------------------------ batch norm forward
@@ -547,6 +580,7 @@ typedef struct olayer {
     float *output, *delta;
     float *weights, *weight_updates, *biases, *bias_updates, *scales, *scale_updates;
     float *mean, *variance, *rolling_mean, *rolling_variance, *mean_delta, *variance_delta, *x, *x_norm;
+    float *act_input;   /* swish / mish: the value before the activation */
     int *indexes;
     float *loss, *rnd;
     float cost;
@@ -636,7 +670,7 @@ void aeto_net_free(aeto_net *net) {
         free(L->weights); free(L->weight_updates); free(L->biases); free(L->bias_updates);
         free(L->scales); free(L->scale_updates); free(L->mean); free(L->variance);
         free(L->rolling_mean); free(L->rolling_variance); free(L->mean_delta); free(L->variance_delta);
-        free(L->x); free(L->x_norm); free(L->indexes); free(L->loss); free(L->rnd);
+        free(L->x); free(L->x_norm); free(L->indexes); free(L->loss); free(L->rnd); free(L->act_input);
     }
     free(net->l); free(net->workspace); free(net);
 }
@@ -770,6 +804,10 @@ void aeto_net_forward(aeto_net *net, const float *x, const float *truth, int tra
                                 L->mean, L->variance, L->rolling_mean, L->rolling_variance, L->x, L->x_norm);
             else
                 aeto_add_bias(L->output, L->biases, net->batch, L->oc, L->oh * L->ow);
+            if (L->s.activation >= 14) {   /* swish / mish keep the value before the activation (dnn/ConvolutionalLayer.c:764-772) */
+                if (!L->act_input) L->act_input = (float *)xcalloc(act, sizeof(float));
+                memcpy(L->act_input, L->output, act * sizeof(float));
+            }
             aeto_activate(L->output, act, L->s.activation, net->mode);
             break;
         case AETO_MAXPOOL:
@@ -808,7 +846,8 @@ void aeto_net_backward(aeto_net *net, const float *x, float *input_delta) {
         const size_t act = (size_t)net->batch * L->outputs;
         switch (L->s.type) {
         case AETO_CONV:
-            aeto_gradient(L->output, act, L->s.activation, L->delta);
+            if (L->s.activation >= 14) aeto_gradient_input(L->output, L->act_input, act, L->s.activation, L->delta);
+            else aeto_gradient(L->output, act, L->s.activation, L->delta);
             if (L->s.batch_normalize)
                 aeto_bn_backward(net->mode, L->delta, L->x, L->x_norm, L->mean, L->variance, L->scales,
                                  L->scale_updates, L->bias_updates, L->mean_delta, L->variance_delta,

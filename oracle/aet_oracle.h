@@ -48,6 +48,9 @@ void aeto_add_bias(float *y, const float *biases, int batch, int n, int spatial)
 void aeto_backward_bias(float *bias_updates, const float *delta, int batch, int n, int spatial);
 void aeto_activate(float *y, size_t count, int activation, int mode);
 void aeto_gradient(const float *y, size_t count, int activation, float *delta);
+/* swish (14) and mish (15): delta *= f'(v) formed as dnn/Activation.c:303-330 does, from the output y and the value
+ * before the activation v. */
+void aeto_gradient_input(const float *y, const float *v, size_t count, int activation, float *delta);
 
 /* ---- batch norm ---- */
 void aeto_bn_forward(int mode, int train, float *y, int batch, int c, int spatial,

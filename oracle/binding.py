@@ -10,7 +10,7 @@ import subprocess
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU = range(14)
+LINEAR, RELU, LEAKY, LOGISTIC, RELU6, RELIE, RAMP, TANH, PLSE, ELU, LOGGY, HARDTAN, LHTAN, SELU, SWISH, MISH = range(16)
 MODE_CPU, MODE_MTCS = 0, 1
 CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT, SHORTCUT = 0, 1, 2, 3, 4, 5
 (P_WEIGHTS, P_WEIGHT_UPDATES, P_BIASES, P_BIAS_UPDATES, P_SCALES, P_SCALE_UPDATES, P_ROLLING_MEAN,
@@ -75,6 +75,7 @@ class Oracle:
         L.aeto_softmax_backward.argtypes = [_f, _f, C.c_size_t, C.c_float]
         L.aeto_dropout_forward.argtypes = [_f, _f, C.c_size_t, C.c_float]
         L.aeto_dropout_backward.argtypes = [_f, _f, C.c_size_t, C.c_float]
+        L.aeto_gradient_input.argtypes = [_f, _f, C.c_size_t, C.c_int, _f]
         L.aeto_shortcut_forward.argtypes = [_f, _f, C.c_int, C.c_size_t, C.c_int, C.POINTER(_f), C.POINTER(C.c_size_t)]
         L.aeto_shortcut_backward.argtypes = [_f, _f, C.c_int, C.c_size_t, C.c_int, C.POINTER(_f), C.POINTER(C.c_size_t)]
         L.aeto_sgd_weights.argtypes = [_f, _f, C.c_size_t, C.c_int, C.c_float, C.c_float, C.c_float]
@@ -171,6 +172,12 @@ class Oracle:
     def gradient(self, y, activation, delta):
         d = _arr(delta).copy()
         self.lib.aeto_gradient(_fp(_arr(y)), d.size, activation, _fp(d))
+        return d
+
+    def gradient_input(self, y, v, activation, delta):
+        """swish / mish: delta * f'(v) from the output y and the value before the activation v."""
+        d = _arr(delta).copy()
+        self.lib.aeto_gradient_input(_fp(_arr(y)), _fp(_arr(v)), d.size, activation, _fp(d))
         return d
 
     def bn_forward(self, mode, train, x, scales, biases, rolling_mean, rolling_variance):

@@ -4,7 +4,7 @@ Describes a network to the CPU oracle (tests, the smoke check and the benchmark'
 the product package never imports it."""
 
 ACT = {"linear": 0, "relu": 1, "leaky": 2, "logistic": 3, "relu6": 4, "relie": 5, "ramp": 6, "tanh": 7, "plse": 8, "elu": 9,
-       "loggy": 10, "hardtan": 11, "lhtan": 12, "selu": 13}
+       "loggy": 10, "hardtan": 11, "lhtan": 12, "selu": 13, "swish": 14, "mish": 15}
 CONV, MAXPOOL, AVGPOOL, SOFTMAX, DROPOUT, SHORTCUT = 0, 1, 2, 3, 4, 5
 
 

@@ -56,7 +56,7 @@ def test_cfg_reader_defaults(aet):
     _, dl = cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\n")
     assert dl[0]["activation"] == 3         # the reference's default activation is logistic (dnn/NetworkFactory.c:103)
     with pytest.raises(KeyError):
-        cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\nactivation=mish\n")
+        cfgfile.network_spec("[net]\nchannels=1\nheight=4\nwidth=4\n[convolutional]\nfilters=2\nactivation=gelu\n")
     anet, alayers = cfgfile.network_spec(open(os.path.join(aet.CFG_DIR, "alexnet_style.cfg")).read())
     assert sum(1 for l in alayers if l["type"] == 0) == 8 and alayers[1]["pad"] == 0
 

@@ -261,17 +261,20 @@ def test_conv_activation_family(aet, ctx, oracle, act):
         check(got, ref, TOL_TF32)
 
 
-def test_conv_bn_with_logistic_and_elu_matches_oracle_network(aet, ctx, oracle64):
+@pytest.mark.parametrize("act1,act2", [("logistic", "elu"), ("swish", "mish"), ("mish", "swish")])
+def test_conv_bn_with_other_activations_matches_oracle_network(aet, ctx, oracle64, act1, act2):
     """BN layers recompute the activation and its gradient from the saved convolution result: a two-layer network with
-    logistic and elu activations against the oracle, 3xTF32 math."""
+    output-gradient activations (logistic, elu) and with the two whose gradient needs the value before the activation
+    (swish, mish: dnn/IOData.c:75-105, dnn/Activation.c:303-330) against the oracle, 3xTF32 math.  The first layer's
+    2x2 pool is fused, so both the window-major and the plain BN backward kernels see these activations."""
     import aet_cnn_b200.synth as synth
     from oracle import binding as ob
     from oracle import cfgfile
     text = ("[net]\nbatch=4\nheight=8\nwidth=8\nchannels=3\nlearning_rate=0.01\nmomentum=0.9\ndecay=0.0005\n"
-            "[convolutional]\nfilters=8\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=logistic\n"
+            "[convolutional]\nfilters=8\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=%s\n"
             "[maxpool]\nsize=2\nstride=2\n"
-            "[convolutional]\nfilters=12\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=elu\n"
-            "[convolutional]\nfilters=5\nsize=1\nstride=1\npad=0\nactivation=tanh\n[avgpool]\n[softmax]\n")
+            "[convolutional]\nfilters=12\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=%s\n"
+            "[convolutional]\nfilters=5\nsize=1\nstride=1\npad=0\nactivation=tanh\n[avgpool]\n[softmax]\n") % (act1, act2)
     opts, specs = cfgfile.network_spec(text)
     ctx.set_math(aet.MATH_3XTF32)
     try:

@@ -296,6 +296,7 @@ groups=1
     (7, 1, 16, 16, 64, "leaky", ob.MODE_CPU),        # one input channel, the CPU classes' formulas
     (3, 2, 10, 6, 128, "logistic", ob.MODE_MTCS),    # 512 threads per block, a slow-path activation
     (2, 3, 8, 80, 64, "leaky", ob.MODE_MTCS),        # three chunks of windows per pool row, the last one partial
+    (4, 3, 12, 12, 64, "mish", ob.MODE_MTCS),        # gradient from the value before the activation
 ])
 def test_first_layer_pool_sized_backward(aet, ctx, oracle64, batch, c, h, w, k, act, mode):
     """The first convolution (BN, fused 2x2 max-pool) takes its scale / shift / weight gradients from the pool-sized
@@ -675,6 +676,8 @@ def test_resume_from_weights_and_momentum_files_is_bit_exact(aet, ctx, oracle):
 
 def test_bad_cfg_is_rejected(aet, ctx):
     for text in ["[convolutional]\nfilters=2\n",
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\nactivation=gelu\n",
+                 # swish / mish only on batch-normalised convolutions
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\nactivation=mish\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[yolo]\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nactivation=leaky\nxnor=1\n",

@@ -352,3 +352,26 @@ activation=linear
         # weight_updates accumulate the NEGATIVE gradient of the cost (the update adds them)
         assert abs(-g.flat[k] - num) < 2e-3 * max(1.0, abs(num)), (k, g.flat[k], num)
     net.set_param(3, ob.P_WEIGHTS, w3)
+
+
+def test_swish_and_mish_known_values(oracle):
+    """swish = v * sigmoid(v), mish = v * tanh(softplus(v)) (dnn/IOData.c:75-105) and their gradients
+    (dnn/Activation.c:303-330) against float64 closed forms and central differences."""
+    v = np.linspace(-6, 6, 49).astype(np.float32)
+    v64 = v.astype(np.float64)
+    sig = 1 / (1 + np.exp(-v64))
+    sp = np.log1p(np.exp(v64))
+    want = {ob.SWISH: v64 * sig, ob.MISH: v64 * np.tanh(sp)}
+    for act in (ob.SWISH, ob.MISH):
+        for mode in (ob.MODE_MTCS, ob.MODE_CPU):
+            y = oracle.activate(v.copy(), act, mode)
+            assert np.allclose(y, want[act], rtol=2e-6, atol=2e-6), act
+        eps = 1e-4
+        f = (lambda t: t / (1 + np.exp(-t))) if act == ob.SWISH else (lambda t: t * np.tanh(np.log1p(np.exp(t))))
+        num = (f(v64 + eps) - f(v64 - eps)) / (2 * eps)
+        g = oracle.gradient_input(oracle.activate(v.copy(), act, ob.MODE_MTCS), v, act, np.ones_like(v))
+        assert np.allclose(g, num, rtol=1e-4, atol=1e-5), act
+    # the thresholds of softplus (dnn/Activation.h:108-113): above 20 the input passes through, below -20 it is exp(v),
+    # whose tanh the reference's float formula 2 / (1 + expf(-2x)) - 1 rounds to zero
+    big = oracle.activate(np.array([25.0, -25.0], np.float32), ob.MISH, ob.MODE_MTCS)
+    assert big[0] == 25.0 and abs(big[1]) < 1e-9
