@@ -38,7 +38,7 @@ aet_network_destroy aet_network_layer_count aet_network_layer aet_network_batch 
 aet_network_outputs aet_network_input aet_network_truth aet_network_learning_rate aet_network_set_hyper
 aet_network_seen aet_network_forward aet_network_backward aet_network_update aet_network_cost
 aet_network_augment_input aet_network_fuse_conv_batchnorm aet_network_predict_topk aet_network_validate aet_network_train_step aet_network_train_step_async aet_network_train_step_device aet_network_last_loss aet_network_predict
-aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_load_momentum aet_network_save_momentum aet_network_param_hash
+aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_load_momentum aet_network_save_momentum aet_network_comm_exposed aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
 aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static
 aet_network_comm_exchange_export aet_network_comm_exchange_attach""".split()
@@ -128,6 +128,7 @@ def lib():
         "aet_network_validate": (i, [vp, vp, vp, i, i, C.POINTER(f), C.POINTER(f)]), "aet_network_use_graph": (i, [vp, i]),
         "aet_network_load_weights": (i, [vp, C.c_char_p]), "aet_network_save_weights": (i, [vp, C.c_char_p]),
         "aet_network_load_momentum": (i, [vp, C.c_char_p]), "aet_network_save_momentum": (i, [vp, C.c_char_p]),
+        "aet_network_comm_exposed": (i, [vp, C.POINTER(C.c_double), C.POINTER(C.c_longlong)]),
         "aet_network_param_hash": (i, [vp, C.POINTER(C.c_uint64)]),
         "aet_network_profile": (i, [vp, i]),
         "aet_network_profile_read": (i, [vp, C.POINTER(KernelTime), i, C.POINTER(i)]),
@@ -523,6 +524,13 @@ class NNetwork:
     def comm_init(self, unique_id, rank, world):
         buf = C.create_string_buffer(bytes(unique_id), 128)
         _check(self.L.aet_network_comm_init(self.h, buf, rank, world))
+
+    def comm_exposed(self):
+        """(mean microseconds per step the main stream waited for the gradient collectives, steps counted); needs the
+        context option "comm_stamps"."""
+        us, n = C.c_double(), C.c_longlong()
+        _check(self.L.aet_network_comm_exposed(self.h, C.byref(us), C.byref(n)))
+        return us.value, n.value
 
     def comm_exchange_export(self):
         """This rank's 80-byte blob for the peer exchange of the last gradient bucket."""

@@ -78,6 +78,7 @@ enum AetOption {
     OPT_DUAL_ACC,          // two accumulators per tile when a CTA owns one tile (row-sharing kernels; off by default)   AET_DUAL_ACC
     OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
     OPT_STEM,              // first convolution + BN + 2x2 max-pool: weight gradient from the pool-sized tensors   AET_NO_STEM
+    OPT_COMM_STAMPS,       // time the main stream's wait for the gradient collectives (aet_network_comm_exposed)   AET_COMM_STAMPS
     OPT_RAGGED,            // TMA kernels on maps whose rows do not divide the tile (13x13, 27x27)   AET_NO_RAGGED
     OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels; off by default   AET_PAIR
     OPT_COUNT
@@ -297,6 +298,7 @@ struct aet_network {
     size_t xchg_cap = 0;
     unsigned long long *xchg_epoch = nullptr;   // device-side step counter
     unsigned int *xchg_ticket = nullptr;        // blocks of the publish kernel that have finished
+    unsigned long long *comm_stamp_dev = nullptr;   // {last stamp, summed wait in ns, waits counted, unused}
     int *xchg_gate = nullptr;                   // 1 / 0: this step's slices of all ranks arrived / the wait ran out
     size_t tail_lo = 0, tail_n = 0;             // arena range summed through the exchange this step (0: none)
     cudaEvent_t ev_uploaded = nullptr;   // after the H2D copies of a train step fed from the caller's pinned buffers
@@ -443,6 +445,7 @@ int k_bn_backward(aet_layer *l, aet_layer *pool);
 int k_bn_pool_forward(aet_layer *l, aet_layer *pool, int use_rolling);
 int k_shortcut_forward(aet_layer *l, const float *in);
 int k_shortcut_backward(aet_layer *l, aet_tensor *pd);
+int k_comm_stamp(aet_context *ctx, unsigned long long *dev4, int after);
 bool stem_backward_eligible(const aet_layer *l, const aet_layer *pool);
 int stem_alloc(aet_layer *l, aet_layer *pool);
 int k_stem_gram(aet_layer *l, const float *x_in);

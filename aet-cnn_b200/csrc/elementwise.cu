@@ -1995,6 +1995,19 @@ int k_adam_arena(aet_network *net) {
     return aet_check_launch("adam");
 }
 
+__global__ void comm_stamp_kernel(unsigned long long *d, int after) {
+    pdl_enter();
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (!after) d[0] = now;
+    else { d[1] += now - d[0]; d[2] += 1; }
+}
+int k_comm_stamp(aet_context *ctx, unsigned long long *dev4, int after) {
+    LaunchScope s(ctx, "comm_stamp", 0, 0);
+    launch_k(ctx->stream, 1, 1, 0, comm_stamp_kernel, dev4, after);
+    return aet_check_launch("comm_stamp");
+}
+
 int k_tail_publish(aet_network *net) {
     aet_context *ctx = net->ctx;
     TailArgs t = {};

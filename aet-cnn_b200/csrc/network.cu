@@ -327,9 +327,14 @@ int net_backward(aet_network *net, aet_state state, bool exchange = true) {
     }
     AET_TRY(side_join(ctx));
     if (dp && slot > 0) {
+        // Option "comm_stamps": one-thread kernels read %globaltimer before and after the wait for the collectives, and
+        // the second adds the difference to a running sum - how long the main stream sat idle for communication.
+        const bool stamps = ctx->opt[OPT_COMM_STAMPS] != 0 && net->comm_stamp_dev;
+        if (stamps) AET_TRY(k_comm_stamp(ctx, net->comm_stamp_dev, 0));
         AET_CUDA(cudaEventRecord(net->ev_comm_done, net->comm_stream));
         AET_CUDA(cudaStreamWaitEvent(net->ctx->stream, net->ev_comm_done, 0));
         pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
+        if (stamps) AET_TRY(k_comm_stamp(ctx, net->comm_stamp_dev, 1));
     }
     if (net->tail_n) AET_TRY(k_tail_publish(net));
     return AET_OK;
@@ -1171,8 +1176,27 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     for (int i = 0; i < 8; ++i) AET_CUDA(cudaEventCreateWithFlags(&net->ev_grad_ready[i], cudaEventDisableTiming));
     for (int i = 0; i < 8; ++i) AET_CUDA(cudaEventCreateWithFlags(&net->ev_grad_ready_side[i], cudaEventDisableTiming));
     AET_CUDA(cudaEventCreateWithFlags(&net->ev_comm_done, cudaEventDisableTiming));
+    AET_CUDA(cudaMalloc(&net->comm_stamp_dev, 4 * sizeof(unsigned long long)));
+    AET_CUDA(cudaMemset(net->comm_stamp_dev, 0, 4 * sizeof(unsigned long long)));
     graph_drop(net);
     net->hyper_host[1] = -1.f;
+    return AET_OK;
+}
+
+// Mean time per step the main stream waited for the gradient collectives since the last call (context option
+// "comm_stamps" = 1, set before the step's graph is captured); resets the counters.
+extern "C" int aet_network_comm_exposed(aet_network *net, double *mean_microseconds, long long *steps) {
+    if (!net || !mean_microseconds) { aet_set_error("aet_network_comm_exposed: null argument"); return AET_E_INVALID; }
+    ctx_enter(net->ctx);
+    *mean_microseconds = 0.0;
+    if (steps) *steps = 0;
+    if (!net->comm_stamp_dev) return AET_OK;
+    unsigned long long h[4] = {0, 0, 0, 0};
+    AET_CUDA(cudaStreamSynchronize(net->ctx->stream));
+    AET_CUDA(cudaMemcpy(h, net->comm_stamp_dev, sizeof(h), cudaMemcpyDeviceToHost));
+    AET_CUDA(cudaMemset(net->comm_stamp_dev, 0, sizeof(h)));
+    if (h[2]) *mean_microseconds = (double)h[1] / (double)h[2] / 1000.0;
+    if (steps) *steps = (long long)h[2];
     return AET_OK;
 }
 
@@ -1265,6 +1289,7 @@ extern "C" int aet_network_comm_destroy(aet_network *net) {
     for (int i = 0; i < 8; ++i) if (net->ev_grad_ready_side[i]) { cudaEventDestroy(net->ev_grad_ready_side[i]); net->ev_grad_ready_side[i] = nullptr; }
     if (net->ev_uploaded) { cudaEventDestroy(net->ev_uploaded); net->ev_uploaded = nullptr; }
     if (net->ev_comm_done) { cudaEventDestroy(net->ev_comm_done); net->ev_comm_done = nullptr; }
+    if (net->comm_stamp_dev) { cudaFree(net->comm_stamp_dev); net->comm_stamp_dev = nullptr; }
     if (net->comm_stream) { cudaStreamDestroy(net->comm_stream); net->comm_stream = nullptr; }
     return AET_OK;
 }

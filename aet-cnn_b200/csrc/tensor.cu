@@ -116,6 +116,7 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"dual_acc", "AET_DUAL_ACC", 0, 1},
     {"rotate", "AET_NO_ROTATE", 1, 0},
     {"stem", "AET_NO_STEM", 1, 0},
+    {"comm_stamps", "AET_COMM_STAMPS", 0, 1},
     {"ragged", "AET_NO_RAGGED", 1, 0},
     {"pair", "AET_PAIR", 0, 1},
 };

@@ -505,6 +505,24 @@ def main():
         weights_identical = weights_identical and all(bool(torch.equal(p, parts[0])) for p in parts)
         hash_steps_checked = len(hashes)
 
+    # ---- N > 1: how long the main stream waits for the gradient collectives (device clock around the wait, graph replay)
+    comm = None
+    if world > 1:
+        ctx.set_option("comm_stamps", 1)
+        net.use_graph(False); net.use_graph(True)       # the stamps are part of the captured step
+        for _ in range(4):
+            net.train_device(want_loss=False)
+        net.comm_exposed()                              # reset after the eager + capture steps
+        barrier()
+        for _ in range(min(args.steps, 100)):
+            net.train_device(want_loss=False)
+        exposed_us, counted = net.comm_exposed()
+        ctx.set_option("comm_stamps", 0)
+        net.use_graph(False); net.use_graph(True)
+        comm = {"exposed_us_per_step": max_over_ranks(exposed_us), "steps": counted,
+                "method": "two one-thread kernels read %globaltimer before and after the main stream's wait for the "
+                          "all-reduces; mean over the steps, max over ranks"}
+
     # ---- per-kernel pass for the roofline (eager launches, events around each)
     # The weight-gradient kernels stay on the main stream here, so that no kernel's time includes a
     # concurrent neighbour's.  The dominant kernel is the largest one that does algorithmic work.
@@ -548,7 +566,7 @@ def main():
                         "call": "aet_network_train_step_async: host->device copy of step s+1 on a copy stream during step s, "
                                 "loss of step s read back during step s+1"},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "conv_layers": conv_all, "cpu_baseline": cpu,
-                "final_loss": final_loss, "weights_identical_across_ranks": weights_identical,
+                "comm": comm, "final_loss": final_loss, "weights_identical_across_ranks": weights_identical,
                 "hash_checked_every_step_for": hash_steps_checked, "kernels": kernels}
         if failed:
             line["failed"] = failed

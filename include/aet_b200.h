@@ -285,6 +285,10 @@ int   aet_network_launches_per_step(const aet_network *net);
  * layer bucket during backward on a side stream.  `unique_id` is the 128-byte ncclUniqueId. */
 int   aet_comm_unique_id(void *unique_id_128);
 int   aet_network_comm_init(aet_network *net, const void *unique_id_128, int rank, int world);
+/* Measurement aid: mean time per step (microseconds) the main stream waited for the gradient collectives since the last
+ * call, and the number of steps counted.  Needs the context option "comm_stamps" = 1 before the step's graph is
+ * captured (two one-thread kernels per step read the device clock around the wait). */
+int   aet_network_comm_exposed(aet_network *net, double *mean_microseconds, long long *steps);
 /* Optional, after aet_network_comm_init on 2..8 ranks that sit on DIFFERENT GPUs of one box (no counterpart in
  * the reference, which is single-GPU): the last gradient bucket of a step (the first layers', complete only when
  * backward ends) is summed over the ranks inside the update kernel through peer-mapped buffers instead of by a

@@ -23,6 +23,8 @@ def run(mode, rank, world, local_rank, steps=4, batch=16):
     text = open(os.path.join(aet.CFG_DIR, "cifar_small.cfg")).read()
     opts, specs = cfgfile.network_spec(text, batch)
     ctx = aet.Context(local_rank)
+    if mode == "nccl":
+        ctx.set_option("comm_stamps", 1)      # time the main stream's wait for the collectives (two extra tiny kernels)
     net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
     bench.init_weights(aet, synth, net, 3)
     net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
@@ -36,8 +38,9 @@ def run(mode, rank, world, local_rank, steps=4, batch=16):
     ctx.check()
     h = net.param_hash()
     same = par.hashes_identical(h)
+    exposed = net.comm_exposed()
     net.close(); ctx.close()
-    return dict(hash=h, identical_across_ranks=same, losses=losses)
+    return dict(hash=h, identical_across_ranks=same, losses=losses, comm_exposed=exposed)
 
 
 def oracle_check(rank, world, local_rank, steps=2, batch=8):
