@@ -79,6 +79,7 @@ enum AetOption {
     OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
     OPT_STEM,              // first convolution + BN + 2x2 max-pool: weight gradient from the pool-sized tensors   AET_NO_STEM
     OPT_COMM_STAMPS,       // time the main stream's wait for the gradient collectives (aet_network_comm_exposed)   AET_COMM_STAMPS
+    OPT_MERGE_TAIL,        // a small last gradient bucket rides with the one before it   AET_NO_MERGE_TAIL
     OPT_RAGGED,            // TMA kernels on maps whose rows do not divide the tile (13x13, 27x27)   AET_NO_RAGGED
     OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels; off by default   AET_PAIR
     OPT_COUNT

@@ -303,7 +303,7 @@ int net_backward(aet_network *net, aet_state state, bool exchange = true) {
             // A bucket is sent as soon as it is full, unless what is left below it is small: the collectives of one
             // communicator run one after the other, so a separate small last bucket would queue behind this one and
             // add its whole latency to the end of the step; together they are one collective.
-            if (br == AET_OK && pend_hi - pend_lo >= bucket_floats && pend_lo >= bucket_floats / 2 && slot < 7) {
+            if (br == AET_OK && pend_hi - pend_lo >= bucket_floats && (pend_lo >= bucket_floats / 2 || !ctx->opt[OPT_MERGE_TAIL]) && slot < 7) {
                 br = issue_allreduce(net, pend_lo, pend_hi, slot++);
                 pend_lo = pend_hi = 0;
             }

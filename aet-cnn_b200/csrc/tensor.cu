@@ -117,6 +117,7 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"rotate", "AET_NO_ROTATE", 1, 0},
     {"stem", "AET_NO_STEM", 1, 0},
     {"comm_stamps", "AET_COMM_STAMPS", 0, 1},
+    {"merge_tail", "AET_NO_MERGE_TAIL", 1, 0},
     {"ragged", "AET_NO_RAGGED", 1, 0},
     {"pair", "AET_PAIR", 0, 1},
 };
