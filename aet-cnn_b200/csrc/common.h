@@ -74,7 +74,7 @@ enum AetOption {
     OPT_FUSE,              // network-level fusions (BN + pool, classifier head), read when a network is built   AET_NO_FUSE
     OPT_LINEAR_HEAD,       // classifier head on the pooled vectors, read when a network is built          AET_NO_LINEAR_HEAD
     OPT_XCHG_CAP_FLOATS,   // capacity of the peer-exchange buffer (0 = default)   AET_XCHG_CAP_FLOATS
-    OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice, -1 = by rank count)   AET_NCCL_MAX_CTAS
+    OPT_NCCL_MAX_CTAS,     // CTA cap of the gradient all-reduce's communicator (0 = NCCL's choice)   AET_NCCL_MAX_CTAS
     OPT_DUAL_ACC,          // two accumulators per tile when a CTA owns one tile (row-sharing kernels; off by default)   AET_DUAL_ACC
     OPT_ROTATE,            // CTAs start their K loops at different slabs (row-sharing kernels)   AET_NO_ROTATE
     OPT_STEM,              // first convolution + BN + 2x2 max-pool: weight gradient from the pool-sized tensors   AET_NO_STEM

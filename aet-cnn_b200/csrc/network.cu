@@ -1154,13 +1154,10 @@ extern "C" int aet_network_comm_init(aet_network *net, const void *unique_id_128
     memcpy(&id, unique_id_128, sizeof(id));
     void *comm = nullptr;
     // The gradient buckets are small and overlap the backward pass, whose convolution kernels are sized to one CTA
-    // per SM: the collective is capped to a few CTAs (option "nccl_max_ctas", 0 = NCCL's own choice) through this
+    // per SM: the collective can be capped to a few CTAs (option "nccl_max_ctas", 0 = NCCL's own choice) through this
     // communicator's configuration, which leaves the process environment and other communicators alone.
     int r = -1;
-    // Option value -1 (the default) picks by the number of ranks: NCCL's own choice for two ranks, a cap of 8 CTAs
-    // beyond (more ranks make NCCL ask for more CTAs than the backward pass can spare).
-    int max_ctas = net->ctx->opt[OPT_NCCL_MAX_CTAS];
-    if (max_ctas < 0) max_ctas = world <= 2 ? 0 : 8;
+    const int max_ctas = net->ctx->opt[OPT_NCCL_MAX_CTAS];   // 0 (the default): NCCL's own choice
     if (max_ctas > 0 && api->comm_init_rank_config) {
         NcclConfig218 cfg;
         cfg.size = sizeof(cfg); cfg.magic = 0xcafebeef; cfg.version = 21800;

@@ -112,7 +112,7 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"fuse", "AET_NO_FUSE", 1, 0},
     {"linear_head", "AET_NO_LINEAR_HEAD", 1, 0},
     {"xchg_cap_floats", "AET_XCHG_CAP_FLOATS", 0, -1},
-    {"nccl_max_ctas", "AET_NCCL_MAX_CTAS", -1, -1},
+    {"nccl_max_ctas", "AET_NCCL_MAX_CTAS", 0, -1},
     {"dual_acc", "AET_DUAL_ACC", 0, 1},
     {"rotate", "AET_NO_ROTATE", 1, 0},
     {"stem", "AET_NO_STEM", 1, 0},
