@@ -1754,7 +1754,7 @@ int k_shortcut_backward(aet_layer *l, aet_tensor *pd) {
     a.pd = pd ? pd->d : nullptr; a.pd_lazy = pd && pd->lazy_zero ? 1 : 0;
     for (int i = 0; i < l->n_from; ++i) {
         aet_tensor *fd = l->from[i]->delta;
-        if (fd->lazy_zero && (l->from[i]->ocp > l->cp || fd == (pd ? pd : nullptr))) {
+        if (fd->lazy_zero && (l->from[i]->ocp > l->cp || fd == pd)) {
             // wider than this layer (its other channels must read as zero), or the very tensor `pd` names (it must
             // receive the delta twice, as the reference adds it twice): start from explicit zeros
             AET_TRY(aet_tensor_zero(fd));
