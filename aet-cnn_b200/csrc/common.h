@@ -112,6 +112,7 @@ struct aet_context {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     bool overlap_wgrad = false;   // set by the network around its backward pass
     bool on_side = false, side_pending = false;
+    int resident_bn_reduce = 0, resident_bn_apply = 0;   // resident blocks per SM of the window-major BN backward kernels (queried once)
     float *scratch_side = nullptr;
     size_t scratch_side_bytes = 0;
     // profiling

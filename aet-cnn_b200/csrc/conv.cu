@@ -764,6 +764,8 @@ static int conv_dgrad_one(aet_layer *l, const float *dy, float *dx, int gi) {
     if (r != 1) return r;
     r = tma_dgrad(l, a, flops);
     if (r != 1) return r;
+    r = narrow_dgrad(l, a, flops);
+    if (r != 1) return r;
     dim3 grid(m_tiles, (a.n_cols + a.bn - 1) / a.bn, 1);
     return launch_gather<KIND_DGRAD>(ctx, a, grid, "conv_dgrad_gather", flops);
 }

@@ -477,4 +477,119 @@ int thin_wgrad(aet_layer *l, const ConvArgs &a, double flops, int *splits_out, f
     return aet_check_launch("conv_wgrad_thin");
 }
 
+
+// Data gradient of a layer with at most 4 input channels (cp = 4): N = 4 is far below what an MMA tile can use (the
+// general kernel pads it to 16 columns of a 128-row tile and spends its time gathering), and the work is small:
+//     dx[n][h][w][c] = sum over taps (r, s) and filters k of  dy[n][h + pad - r][w + pad - s][k] * W[k][r][s][c]
+// in exact FP32 on the CUDA cores.  Sixteen lanes share four neighbouring input pixels of one row: lane g takes the
+// filters 4g..4g+3 (and every 64 further on), so the sixteen 16-byte loads of one dy pixel are one contiguous 256-byte
+// read; per filter row the lanes load the S + 3 dy columns the four pixels touch and the row's S taps of weights once
+// (from shared memory, laid out so that the lanes' reads do not collide) and every value feeds all the pixels that
+// use it; the lanes' partial sums meet in a shuffle tree at the end.
+struct NarrowDgradArgs {
+    const float *dy, *w;
+    float *dx;
+    int N, H, W, K, OH, OW, R, pad, ys, xs;
+    long long quads;   // groups of four pixels (W is a multiple of 4)
+};
+constexpr int NARROW_THREADS = 256, NARROW_LANES = 16, NARROW_QUADS = 2;   // 16 lane groups per block, 2 quads each
+template <int S>
+__global__ void __launch_bounds__(NARROW_THREADS) conv_dgrad_narrow_kernel(const NarrowDgradArgs a) {
+    extern __shared__ float4 narrow_w[];
+    const int taps = a.R * S;
+    pdl_enter();
+    // filter k of a tap sits at [tap][k % 4][k / 4]: the lanes of a group (consecutive k / 4) read consecutive 16-byte cells
+    const int kq_count = a.K / 4;
+    for (int i = threadIdx.x; i < taps * a.K; i += NARROW_THREADS) {
+        const int tap = i / a.K, k = i - tap * a.K;
+        narrow_w[(size_t)(tap * 4 + (k & 3)) * kq_count + (k >> 2)] = *reinterpret_cast<const float4 *>(a.w + ((size_t)k * taps + tap) * 4);
+    }
+    __syncthreads();
+    const int g = threadIdx.x & (NARROW_LANES - 1), grp = threadIdx.x / NARROW_LANES;
+    const long long base = ((long long)blockIdx.x * (NARROW_THREADS / NARROW_LANES) + grp) * NARROW_QUADS;
+    constexpr int COLS = S + 3;
+    for (int j = 0; j < NARROW_QUADS; ++j) {
+        const long long quad = base + j;
+        const bool live = quad < a.quads;          // uniform over the 16 lanes of a group; all 32 lanes reach the shuffles
+        const long long p = (live ? quad : 0) * 4;
+        const int w0 = (int)(p % a.W), h = (int)((p / a.W) % a.H), n = (int)(p / ((long long)a.W * a.H));
+        float4 acc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 4 * g; k < a.K; k += 4 * NARROW_LANES) {
+            for (int r = 0; r < a.R; ++r) {
+                const int oh = h + a.pad - r;
+                if (!live || oh < 0 || oh >= a.OH) continue;
+                // column c is output column w0 + pad - (S - 1) + c; pixel i meets it through tap s = i + S - 1 - c
+                float4 d[COLS];
+                const float *row = a.dy + (size_t)((size_t)n * a.OH + oh) * a.OW * a.ys + k;
+#pragma unroll
+                for (int c = 0; c < COLS; ++c) {
+                    const int ow = w0 + a.pad - (S - 1) + c;
+                    d[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (ow >= 0 && ow < a.OW) d[c] = __ldg(reinterpret_cast<const float4 *>(row + (size_t)ow * a.ys));
+                }
+                float4 wv[S][4];
+#pragma unroll
+                for (int t = 0; t < S; ++t) {
+                    const float4 *wt = narrow_w + (size_t)(r * S + t) * a.K + (k >> 2);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) wv[t][q] = wt[q * kq_count];
+                }
+#pragma unroll
+                for (int c = 0; c < COLS; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int t = i + S - 1 - c;
+                        if (t < 0 || t >= S) continue;
+                        const float4 v = d[c];
+                        acc[i].x = fmaf(v.x, wv[t][0].x, acc[i].x); acc[i].y = fmaf(v.x, wv[t][0].y, acc[i].y); acc[i].z = fmaf(v.x, wv[t][0].z, acc[i].z); acc[i].w = fmaf(v.x, wv[t][0].w, acc[i].w);
+                        acc[i].x = fmaf(v.y, wv[t][1].x, acc[i].x); acc[i].y = fmaf(v.y, wv[t][1].y, acc[i].y); acc[i].z = fmaf(v.y, wv[t][1].z, acc[i].z); acc[i].w = fmaf(v.y, wv[t][1].w, acc[i].w);
+                        acc[i].x = fmaf(v.z, wv[t][2].x, acc[i].x); acc[i].y = fmaf(v.z, wv[t][2].y, acc[i].y); acc[i].z = fmaf(v.z, wv[t][2].z, acc[i].z); acc[i].w = fmaf(v.z, wv[t][2].w, acc[i].w);
+                        acc[i].x = fmaf(v.w, wv[t][3].x, acc[i].x); acc[i].y = fmaf(v.w, wv[t][3].y, acc[i].y); acc[i].z = fmaf(v.w, wv[t][3].z, acc[i].z); acc[i].w = fmaf(v.w, wv[t][3].w, acc[i].w);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int o = NARROW_LANES / 2; o > 0; o >>= 1) {
+                acc[i].x += __shfl_xor_sync(0xffffffffu, acc[i].x, o); acc[i].y += __shfl_xor_sync(0xffffffffu, acc[i].y, o);
+                acc[i].z += __shfl_xor_sync(0xffffffffu, acc[i].z, o); acc[i].w += __shfl_xor_sync(0xffffffffu, acc[i].w, o);
+            }
+        }
+        // lane i of the group stores pixel i
+        if (live && g < 4) {
+            const float4 v = g == 0 ? acc[0] : (g == 1 ? acc[1] : (g == 2 ? acc[2] : acc[3]));
+            *reinterpret_cast<float4 *>(a.dx + (size_t)(p + g) * a.xs) = v;
+        }
+    }
+}
+
+template <int S>
+static int narrow_dgrad_launch(aet_context *ctx, const NarrowDgradArgs &t, size_t smem, double flops) {
+    AET_TRY(ctx_smem_attr(ctx, conv_dgrad_narrow_kernel<S>, 96 * 1024));
+    const long long per_block = (NARROW_THREADS / NARROW_LANES) * NARROW_QUADS;
+    LaunchScope scope(ctx, "conv_dgrad_narrow", 0, flops);
+    launch_k(ctx->stream, (unsigned)((t.quads + per_block - 1) / per_block), NARROW_THREADS, smem, conv_dgrad_narrow_kernel<S>, t);
+    return aet_check_launch("conv_dgrad_narrow");
+}
+
+// Data gradient through the narrow-channel kernel; 1 = not eligible.
+int narrow_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
+    aet_context *ctx = l->ctx;
+    const ConvGeom &g = a.g;
+    if (ctx->conv_path != 0 || !ctx->opt[OPT_THIN] || l->groups > 1 || g.dil > 1 || g.sx != 1 || g.sy != 1) return 1;
+    if (g.cp != 4 || g.xs != 4 || g.kp % 4 || g.K != g.kp || g.W % 4) return 1;
+    if (g.S != 3 && g.S != 5) return 1;
+    const size_t smem = (size_t)g.R * g.S * g.kp * sizeof(float4);
+    if (smem > 96 * 1024) return 1;
+    NarrowDgradArgs t = {};
+    t.dy = a.src_a; t.w = a.src_b; t.dx = a.out;
+    t.N = g.N; t.H = g.H; t.W = g.W; t.K = g.kp; t.OH = g.OH; t.OW = g.OW; t.R = g.R; t.pad = g.pad; t.ys = g.ys; t.xs = g.xs;
+    t.quads = (long long)g.N * g.H * g.W / 4;
+    return g.S == 3 ? narrow_dgrad_launch<3>(ctx, t, smem, flops) : narrow_dgrad_launch<5>(ctx, t, smem, flops);
+}
+
 }  // namespace

@@ -1597,7 +1597,7 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
         w.total = (unsigned)((long long)pool->batch * pool->oh * pool->ow * (pool->cp / 4));
         // one wave of exactly the blocks that are resident together (the kernel is a grid-stride loop): a
         // partial second wave would run at a fraction of the bandwidth
-        static int resident_reduce = 0;
+        int &resident_reduce = ctx->resident_bn_reduce;   // per context: occupancy is a property of the device
         if (!resident_reduce &&
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_reduce, bn_bwd_poolwin_kernel<false>, TB, 0) != cudaSuccess)
             resident_reduce = 2;
@@ -1635,7 +1635,7 @@ int k_bn_backward(aet_layer *l, aet_layer *pool) {
     b.gamma = layer_s(l); b.beta = layer_b(l); b.coef = l->bwd_coef; b.act = l->act; b.cp = l->ocp;
     b.pixels = pixels; b.pix_per_block = q.pix_per_block; b.m = q.m;
     if (window_major) {
-        static int resident_apply = 0;
+        int &resident_apply = ctx->resident_bn_apply;
         if (!resident_apply &&
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident_apply, bn_bwd_poolwin_kernel<true>, TB, 0) != cudaSuccess)
             resident_apply = 2;

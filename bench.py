@@ -284,10 +284,17 @@ def run_reference(args, rank):
     line = {"impl": "reference", "metric": "train images/sec", "value": value, "unit": "images/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * dt / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl["text"], "batch_per_gpu": wl["batch"], "sample_batch": batch},
+            "config": workload_config(wl, wl["batch"], max(1, args.gpus)), "sample_batch": batch,
             "cpu_baseline": {"value": value, "unit": "images/s", "cores": use_threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def workload_config(wl, batch, world):
+    """The `config` object of the JSON line, the same for both arms: it names the workload, nothing about how an arm ran it."""
+    return {"workload": wl["text"], "batch_per_gpu": batch, "global_batch": batch * world,
+            "parallelism": "dp%d" % world if world > 1 else "single",
+            "l2": "per-step working set (activations + deltas, ~250 MB at batch 128) exceeds the 126 MB L2; no explicit flush"}
 
 
 def roofline_of(table, peaks, tf32_burst, tf32_loop):
@@ -554,10 +561,8 @@ def main():
         line = {"metric": "train images/sec", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "tf32 (fp32 storage and accumulation)", "data": "synthetic",
-                "config": {"workload": wl["text"], "batch_per_gpu": batch, "global_batch": batch * world,
-                           "parallelism": "dp%d" % world if world > 1 else "single",
-                           "l2": "per-step working set (activations + deltas, ~250 MB at batch 128) exceeds the 126 MB L2; no explicit flush",
-                           "execution": "CUDA graph replay of forward+backward+allreduce+update",
+                "config": workload_config(wl, batch, world),
+                "method": {"execution": "CUDA graph replay of forward+backward+allreduce+update",
                            "timing": "median of %d repeats of the %d-step loop, each bracketed by barrier+synchronize, max over ranks"
                                      % (repeats, args.steps)},
                 "repeats": repeats, "ms_per_step_min": min(times) / args.steps, "ms_per_step_max": max(times) / args.steps,

@@ -157,6 +157,7 @@ THIN_SHAPES = [
     (2, 2, 11, 11, 3, 5, 2, 2, 0),        # 5x5 stride 2: K = 100
     (3, 1, 28, 28, 20, 5, 1, 0, 1),       # one input channel, no padding
     (5, 8, 6, 6, 100, 2, 1, 0, 1),        # two cells per tap, 100 filters
+    (2, 3, 12, 16, 8, 5, 1, 2, 0),        # 5x5 with padding: the narrow data-gradient kernel's second instantiation
 ]
 
 
@@ -241,10 +242,11 @@ def test_conv_sweep_shapes_at_batch_256(aet, ctx, oracle, shape):
         print("sweep shape", shape, "->", sorted(variants_used(ctx)))
     finally:
         ctx.profile(0)
-    # every sweep shape is on a TMA or first-layer kernel; only the 3-channel layer's data gradient (which a
-    # network never asks for: nothing precedes its first layer) goes through the gather producer
-    allowed = {"conv_dgrad_gather"} if shape[1] < 32 else set()
-    assert not any("gather" in k for k in used - allowed), used
+    # every sweep shape is on a TMA or first-layer kernel; the 3-channel layer's data gradient (which a network never
+    # asks for: nothing precedes its first layer) has a CUDA-core kernel of its own
+    assert not any("gather" in k for k in used), used
+    if shape[1] < 32:
+        assert "conv_dgrad_narrow" in used, used
     check(got, ref, TOL_TF32)
 
 
