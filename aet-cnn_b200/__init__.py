@@ -38,7 +38,7 @@ aet_network_destroy aet_network_layer_count aet_network_layer aet_network_batch 
 aet_network_outputs aet_network_input aet_network_truth aet_network_learning_rate aet_network_set_hyper
 aet_network_seen aet_network_forward aet_network_backward aet_network_update aet_network_cost
 aet_network_augment_input aet_network_fuse_conv_batchnorm aet_network_predict_topk aet_network_validate aet_network_train_step aet_network_train_step_async aet_network_train_step_device aet_network_last_loss aet_network_predict
-aet_network_use_graph aet_network_load_weights aet_network_save_weights aet_network_load_momentum aet_network_save_momentum aet_network_comm_exposed aet_network_param_hash
+aet_network_use_graph aet_network_load_weights aet_network_load_weights_upto aet_network_save_weights aet_network_load_momentum aet_network_save_momentum aet_network_comm_exposed aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
 aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static
 aet_network_comm_exchange_export aet_network_comm_exchange_attach""".split()
@@ -126,7 +126,7 @@ def lib():
         "aet_network_augment_input": (i, [vp, vp, i, i, vp]),
         "aet_network_fuse_conv_batchnorm": (i, [vp]), "aet_network_predict_topk": (i, [vp, vp, i, vp]),
         "aet_network_validate": (i, [vp, vp, vp, i, i, C.POINTER(f), C.POINTER(f)]), "aet_network_use_graph": (i, [vp, i]),
-        "aet_network_load_weights": (i, [vp, C.c_char_p]), "aet_network_save_weights": (i, [vp, C.c_char_p]),
+        "aet_network_load_weights": (i, [vp, C.c_char_p]), "aet_network_load_weights_upto": (i, [vp, C.c_char_p, i]), "aet_network_save_weights": (i, [vp, C.c_char_p]),
         "aet_network_load_momentum": (i, [vp, C.c_char_p]), "aet_network_save_momentum": (i, [vp, C.c_char_p]),
         "aet_network_comm_exposed": (i, [vp, C.POINTER(C.c_double), C.POINTER(C.c_longlong)]),
         "aet_network_param_hash": (i, [vp, C.POINTER(C.c_uint64)]),
@@ -490,8 +490,9 @@ class NNetwork:
     def use_graph(self, enable=True):
         _check(self.L.aet_network_use_graph(self.h, int(enable)))
 
-    def load_weights(self, path):
-        _check(self.L.aet_network_load_weights(self.h, path.encode()))
+    def load_weights(self, path, cutoff=-1):
+        """NNetwork.loadWeights(filename, cutoff): only the layers in front of index `cutoff` (-1: all)."""
+        _check(self.L.aet_network_load_weights_upto(self.h, path.encode(), int(cutoff)))
 
     def save_weights(self, path):
         _check(self.L.aet_network_save_weights(self.h, path.encode()))

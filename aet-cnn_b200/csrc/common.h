@@ -168,6 +168,12 @@ struct aet_layer {
     int flipped = 0;      // the weights record of a .weights file is stored transposed (dnn/ConvolutionalLayer.c:483-485)
     aet_activation act = AET_LINEAR;
     float lr_scale = 1.0f;
+    // generic per-layer cfg keys (dnn/NetworkFactory.c:926-934): stopbackward ends the network's backward walk before this
+    // layer (dnn/NNetwork.c:648); the layers in front of the last such layer only run forward and are never updated
+    // (dnn/NetworkFactory.c:979-991: onlyforward = 1, train = 0); dont_update = N skips the update while the iteration
+    // number is <= N (dnn/NNetwork.c:703, the GPU path only); dontload skips the layer's record of a .weights file
+    // (dnn/NNetwork.c:95), dontloadscales its batch-norm block (dnn/ConvolutionalLayer.c:468)
+    int stopbackward = 0, onlyforward = 0, dont_update = 0, dontload = 0, dontloadscales = 0;
     aet_tensor *output = nullptr, *delta = nullptr, *x = nullptr;  // x: conv result before BN
     // parameters (slices of an arena)
     ParamArena *arena = nullptr;
@@ -253,7 +259,10 @@ struct aet_network {
     ParamArena arena;
     // SGD launch tables
     int *block_seg = nullptr;    // per 1024-float block: segment id
-    float *seg_table = nullptr;  // per segment: lr multiplier, decay flag
+    float *seg_table = nullptr;  // per segment: lr multiplier (negative: the segment is not updated now), decay flag, ...
+    std::vector<float> seg_host;         // host copy of seg_table with the layers' own multipliers
+    std::vector<aet_layer *> seg_layer;  // owner of each segment
+    std::vector<unsigned char> seg_skip; // which segments the device table currently marks as not updated
     int n_blocks = 0, n_segments = 0;
     float *hyper_dev = nullptr;  // {lr/B, momentum, -decay*B*loss_scale, unused, then for Adam: rate, -decay*B, 1-B1^t, 1-B2^t}
     float hyper_host[8] = {0, 0, 0, 0, 0, 0, 0, 0};

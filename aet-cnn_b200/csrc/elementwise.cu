@@ -1234,6 +1234,7 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
                                                        const float *seg_table, const float *hyper, const TailArgs t, int *status) {
     pdl_enter();
     const int seg = block_seg[blockIdx.x];
+    const bool frozen = seg_table[4 * seg] < 0.f;   // not updated now: the gradient joins the pending update, nothing else moves
     const float rate = hyper[0] * seg_table[4 * seg];
     const float momentum = hyper[1];
     const float decay_term = seg_table[4 * seg + 1] != 0.f ? hyper[2] : 0.f;
@@ -1256,6 +1257,11 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
         }
     }
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    if (frozen) {
+        st4(U + i, u);
+        st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        return;
+    }
     if (scrub) {
         const size_t first = (size_t)__float_as_int(seg_table[4 * seg + 3]) * TB * 4;
         if (scrub4(w, u, scrub, i - first) && status) atomicOr(status, AET_STATUS_NAN);
@@ -1283,6 +1289,11 @@ __global__ void __launch_bounds__(TB) adam_arena_kernel(float *W, float *U, floa
     const size_t i = ((size_t)blockIdx.x * TB + threadIdx.x) * 4;
     float4 w = ld4(W + i), u = ld4(U + i), g = ld4(G + i), m = ld4(M + i), v = ld4(V + i);
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;
+    if (seg_table[4 * seg] < 0.f) {   // not updated now: the gradient joins the pending update, nothing else moves
+        st4(U + i, u);
+        st4(G + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        return;
+    }
     if (scrub) {
         const size_t first = (size_t)__float_as_int(seg_table[4 * seg + 3]) * TB * 4;
         if (scrub4(w, u, scrub, i - first) && status) atomicOr(status, AET_STATUS_NAN);

@@ -802,7 +802,7 @@ extern "C" int aet_layer_load_weights(aet_layer *l, void *fpv) {
     if (l->type != AET_CONVOLUTIONAL) return AET_OK;
     std::vector<float> v(l->oc);
     const aet_param order[4] = {AET_P_BIASES, AET_P_SCALES, AET_P_ROLLING_MEAN, AET_P_ROLLING_VARIANCE};
-    for (int i = 0; i < (l->bn ? 4 : 1); ++i) {
+    for (int i = 0; i < ((l->bn && !l->dontloadscales) ? 4 : 1); ++i) {   // dontloadscales: no batch-norm block (dnn/ConvolutionalLayer.c:468)
         if (fread(v.data(), sizeof(float), v.size(), fp) != v.size()) { aet_set_error("weights file: unexpected end (layer %d)", l->index); return AET_E_IO; }
         AET_TRY(aet_layer_write(l, order[i], v.data()));
     }

@@ -194,6 +194,7 @@ int build_sgd_tables(aet_network *net) {
             seg_table.push_back(k == 0 ? 1.f : 0.f);
             seg_table.push_back(!mtcs ? 0.f : (k == 0 ? 1.f : ((l->bn && net->try_fix_nan) ? 2.f : 0.f)));
             seg_table.push_back(first_bits);
+            net->seg_layer.push_back(l);
             ++seg_id;
         }
     }
@@ -204,6 +205,32 @@ int build_sgd_tables(aet_network *net) {
     AET_CUDA(cudaMalloc(&net->seg_table, seg_table.size() * sizeof(float)));
     AET_CUDA(cudaMemcpy(net->block_seg, block_seg.data(), block_seg.size() * sizeof(int), cudaMemcpyHostToDevice));
     AET_CUDA(cudaMemcpy(net->seg_table, seg_table.data(), seg_table.size() * sizeof(float), cudaMemcpyHostToDevice));
+    net->seg_host = seg_table;
+    net->seg_skip.assign(seg_id, 0);
+    return AET_OK;
+}
+
+// Which layers the coming update leaves alone (dnn/NNetwork.c:667-709): layers with train == 0 in both paths; in the GPU
+// path also a layer whose dont_update is not yet below the iteration number.  A skipped segment keeps its weights and adds
+// the step's gradient to its pending update, which is what the reference's single weight_updates buffer does when
+// update() is not called.  The table changes rarely; the copy is ordered on the main stream like the kernels that read it.
+int refresh_update_mask(aet_network *net) {
+    if (net->seg_layer.empty()) return AET_OK;
+    // (an update asked for before any training call counts as iteration 1, so that a bare aet_network_update still updates)
+    const int64_t iteration = std::max<int64_t>(1, net->seen / ((int64_t)net->batch * net->subdivisions));
+    const bool mtcs = net->ctx->parity == AET_PARITY_MTCS;
+    bool changed = false;
+    for (size_t sgi = 0; sgi < net->seg_layer.size(); ++sgi) {
+        const aet_layer *l = net->seg_layer[sgi];
+        const unsigned char skip = (l->train == 0 || (mtcs && !((int64_t)l->dont_update < iteration))) ? 1 : 0;
+        if (skip != net->seg_skip[sgi]) { net->seg_skip[sgi] = skip; changed = true; }
+    }
+    if (!changed) return AET_OK;
+    std::vector<float> t = net->seg_host;
+    for (size_t sgi = 0; sgi < net->seg_skip.size(); ++sgi)
+        if (net->seg_skip[sgi]) t[4 * sgi] = -1.f;
+    // pageable source: the runtime stages it before the call returns, the copy itself runs in stream order
+    AET_CUDA(cudaMemcpyAsync(net->seg_table, t.data(), t.size() * sizeof(float), cudaMemcpyHostToDevice, net->ctx->stream));
     return AET_OK;
 }
 
@@ -214,6 +241,7 @@ aet_layer *softmax_layer(aet_network *net) {
 }
 
 int upload_hyper(aet_network *net) {
+    AET_TRY(refresh_update_mask(net));
     const int world = net->world > 0 ? net->world : 1;
     const int update_batch = net->batch * net->subdivisions * world;
     const float rate = current_rate(net);
@@ -294,6 +322,8 @@ int net_backward(aet_network *net, aet_state state, bool exchange = true) {
         state.index = i;
         if (i == 0) { state.input = original_input; state.delta = original_delta; }
         else { state.input = net->layers[i - 1]->output; state.delta = net->layers[i - 1]->delta; }
+        if (l->stopbackward) break;      // dnn/NNetwork.c:648-651
+        if (l->onlyforward) continue;
         int br = aet_layer_backward(l, state);
         if (br == AET_OK && dp && !whole && l->type == AET_CONVOLUTIONAL) {
             const ParamSegment &last = l->bn ? l->seg_s : l->seg_b;
@@ -575,6 +605,18 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
         if (!l) { aet_network_destroy(net); return nullptr; }
         l->net = net;
         l->index = index;
+        // keys every layer type takes (dnn/NetworkFactory.c:926-934)
+        l->stopbackward = opt_int(s, "stopbackward", 0) == 1;
+        l->dont_update = opt_int(s, "dont_update", 0);
+        l->dontload = opt_int(s, "dontload", 0);
+        l->dontloadscales = opt_int(s, "dontloadscales", 0);
+        for (const char *k : {"onlyforward", "train_only_bn", "burnin_update", "clip"})
+            if (opt_float(s, k, 0.f) != 0.f) {
+                net->layers.push_back(l);   // owned by the network from here on
+                aet_set_error("cfg line %d: layer option '%s' is outside the supported hot path", s.line, k);
+                aet_network_destroy(net);
+                return nullptr;
+            }
         if (l->type == AET_MAXPOOL && !net->layers.empty() && ctx->opt[OPT_FUSE]) {
             aet_layer *prev = net->layers.back();
             if (prev->type == AET_CONVOLUTIONAL && prev->bn) {
@@ -601,6 +643,26 @@ extern "C" aet_network *aet_network_create_ex(aet_context *ctx, const char *cfg_
         c = l->oc; h = l->oh; w = l->ow;
     }
     if (net->layers.empty()) { aet_set_error("cfg: no layers"); aet_network_destroy(net); return nullptr; }
+    if (train) {
+        // dnn/NetworkFactory.c:883-896,979-991: the layers in front of the LAST stopbackward layer only run forward and are
+        // never updated; that layer itself keeps train = 1 (its update runs on gradients nothing ever writes)
+        int last_stop = -1;
+        for (aet_layer *l : net->layers)
+            if (l->stopbackward) last_stop = l->index;
+        for (int k = 0; k < last_stop; ++k) { net->layers[k]->onlyforward = 1; net->layers[k]->train = 0; }
+        // the fused classifier head computes three layers' backward in the softmax layer's call: undo it when the walk
+        // stops inside the head
+        aet_layer *sm = softmax_layer(net);
+        if (sm && sm->head_conv && last_stop >= sm->head_conv->index) {
+            sm->head_conv->lin_head = false;
+            sm->head_conv->head_softmax = nullptr;
+            sm->head_avg->head_softmax = nullptr;
+            sm->head_conv = nullptr; sm->head_avg = nullptr;
+        }
+        // so does the first layer's backward from the pool-sized tensors, which the pool layer's call prepares
+        for (aet_layer *l : net->layers)
+            if (l->index <= last_stop && l->stem) l->stem = false;
+    }
     net->input = aet_tensor_create(ctx, net->batch, net->c, net->h, net->w);
     net->truth = aet_tensor_create(ctx, net->batch, c * h * w, 1, 1);
     bool ok = net->input && net->truth && build_sgd_tables(net) == AET_OK;
@@ -1017,7 +1079,9 @@ extern "C" int aet_network_save_weights(aet_network *net, const char *path) {
     return r;
 }
 
-extern "C" int aet_network_load_weights(aet_network *net, const char *path) {
+extern "C" int aet_network_load_weights(aet_network *net, const char *path) { return aet_network_load_weights_upto(net, path, -1); }
+
+extern "C" int aet_network_load_weights_upto(aet_network *net, const char *path, int cutoff) {
     if (!net || !path) { aet_set_error("null argument"); return AET_E_INVALID; }
     FILE *fp = fopen(path, "rb");
     if (!fp) { aet_set_error("cannot open weights file %s", path); return AET_E_IO; }
@@ -1036,7 +1100,17 @@ extern "C" int aet_network_load_weights(aet_network *net, const char *path) {
     // it; transposed records are a per-layer property, the cfg key `flipped`)
     net->cur_iteration = net->seen / ((int64_t)net->batch * net->subdivisions);
     int r = AET_OK;
-    for (size_t i = 0; r == AET_OK && i < net->layers.size(); ++i) r = aet_layer_load_weights(net->layers[i], fp);
+    // dnn/NNetwork.c:93-108: layers marked dontload are passed over without consuming anything, and a file that ends at a
+    // record boundary (a backbone cut off with `partial`) leaves the remaining layers as they are
+    const size_t upto = cutoff < 0 ? net->layers.size() : std::min(net->layers.size(), (size_t)cutoff);
+    for (size_t i = 0; r == AET_OK && i < upto; ++i) {
+        aet_layer *l = net->layers[i];
+        if (l->dontload || l->type != AET_CONVOLUTIONAL) continue;
+        const int ch = fgetc(fp);
+        if (ch == EOF) break;
+        ungetc(ch, fp);
+        r = aet_layer_load_weights(l, fp);
+    }
     fclose(fp);
     return r;
 }

@@ -264,6 +264,10 @@ int   aet_network_augment_input(aet_network *net, const float *host_src, int src
 int   aet_network_use_graph(aet_network *net, int enable);
 /* NNetwork.loadWeights / saveWeights (dnn/NNetwork.c:64-147): Darknet .weights container. */
 int   aet_network_load_weights(aet_network *net, const char *path);
+/* loadWeights(filename, cutoff) (dnn/NNetwork.c:64-110): only the layers in front of index `cutoff` are read (-1: all).
+ * Layers whose cfg section says dontload = 1 are passed over; dontloadscales = 1 skips a layer's batch-norm block; a
+ * file that ends at a layer boundary leaves the remaining layers untouched. */
+int   aet_network_load_weights_upto(aet_network *net, const char *path, int cutoff);
 int   aet_network_save_weights(aet_network *net, const char *path);
 /* Optional side file with the step-to-step state the .weights container leaves out (bias / scale / weight updates and,
  * for batch-norm layers, the last batch mean, per convolutional layer in the .weights file's order), so that a run

@@ -592,6 +592,8 @@ struct aeto_net {
     float *workspace;
     size_t workspace_elems;
     const float *truth;
+    int last_stop;        /* index of the last layer with stopbackward (-1: none) */
+    long iteration;       /* updates requested so far through aeto_net_train_step (seen / batch) */
 };
 
 aeto_net *aeto_net_create(const aeto_layer_spec *specs, int nlayers, int batch, int c, int h, int w,
@@ -600,6 +602,9 @@ aeto_net *aeto_net_create(const aeto_layer_spec *specs, int nlayers, int batch, 
     net->n = nlayers; net->batch = batch; net->c = c; net->h = h; net->w = w; net->mode = mode;
     net->threads = threads < 1 ? 1 : threads;
     net->l = (olayer *)xcalloc((size_t)nlayers, sizeof(olayer));
+    net->last_stop = -1;
+    for (int i = 0; i < nlayers; ++i)
+        if (specs[i].stopbackward == 1) net->last_stop = i;
     int cc = c, hh = h, ww = w;
     for (int i = 0; i < nlayers; ++i) {
         olayer *L = &net->l[i];
@@ -844,6 +849,8 @@ void aeto_net_backward(aeto_net *net, const float *x, float *input_delta) {
         const float *in = (i == 0) ? x : net->l[i - 1].output;
         float *pd = (i == 0) ? input_delta : net->l[i - 1].delta;
         const size_t act = (size_t)net->batch * L->outputs;
+        if (L->s.stopbackward == 1) break;     /* dnn/NNetwork.c:648 */
+        if (i < net->last_stop) continue;      /* onlyforward, dnn/NNetwork.c:650 with dnn/NetworkFactory.c:979-991 */
         switch (L->s.type) {
         case AETO_CONV:
             if (L->s.activation >= 14) aeto_gradient_input(L->output, L->act_input, act, L->s.activation, L->delta);
@@ -884,6 +891,10 @@ void aeto_net_update(aeto_net *net, int update_batch, float lr, float momentum, 
     for (int i = 0; i < net->n; ++i) {
         olayer *L = &net->l[i];
         if (L->s.type != AETO_CONV) continue;
+        if (i < net->last_stop) continue;      /* train == 0, dnn/NNetwork.c:672,688 */
+        /* dnn/NNetwork.c:703, updateMTCS only: updateCPU (:667-680) does not look at dont_update */
+        /* (an update asked for before any training call counts as iteration 1, so that a bare update still updates) */
+        if (net->mode == AETO_MODE_MTCS && !((long)L->s.dont_update < (net->iteration > 0 ? net->iteration : 1))) continue;
         float rate = lr * (L->s.learning_rate_scale != 0 ? L->s.learning_rate_scale : 1.0f);
         aeto_sgd_weights(L->weights, L->weight_updates, L->nweights, update_batch, rate, momentum, decay);
         aeto_sgd_plain(L->biases, L->bias_updates, (size_t)L->oc, update_batch, rate, momentum);
@@ -902,6 +913,7 @@ float aeto_net_train_step(aeto_net *net, const float *x, const float *truth, flo
     aeto_net_forward(net, x, truth, 1);
     aeto_net_backward(net, x, NULL);
     float cost = aeto_net_cost(net);
+    net->iteration += 1;   /* seen += batch before forward (dnn/NNetwork.c:742); iteration_num = seen / batch at the update */
     aeto_net_update(net, net->batch, lr, momentum, decay);
     return cost / net->batch;
 }

@@ -100,6 +100,9 @@ typedef struct aeto_layer_spec {
     int groups;          /* softmax groups */
     float learning_rate_scale;
     int n_from, from[4]; /* shortcut: absolute indexes of the layers whose outputs are added */
+    int stopbackward;    /* dnn/NNetwork.c:648: the backward walk ends before this layer; the layers in front of the LAST
+                          * such layer only run forward and are never updated (dnn/NetworkFactory.c:979-991) */
+    int dont_update;     /* dnn/NNetwork.c:703 (GPU path only): no update while the iteration number is <= this */
 } aeto_layer_spec;
 
 typedef struct aeto_net aeto_net;

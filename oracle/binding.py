@@ -24,7 +24,8 @@ class LayerSpec(C.Structure):
     _fields_ = [("type", C.c_int), ("filters", C.c_int), ("size", C.c_int), ("stride_x", C.c_int),
                 ("stride_y", C.c_int), ("pad", C.c_int), ("batch_normalize", C.c_int), ("activation", C.c_int),
                 ("probability", C.c_float), ("temperature", C.c_float), ("groups", C.c_int),
-                ("learning_rate_scale", C.c_float), ("n_from", C.c_int), ("from_", C.c_int * 4)]
+                ("learning_rate_scale", C.c_float), ("n_from", C.c_int), ("from_", C.c_int * 4),
+                ("stopbackward", C.c_int), ("dont_update", C.c_int)]
 
 
 def build(variant="parity"):

@@ -66,4 +66,7 @@ def network_spec(text, batch=0):
                                **{"from": [i + index if i < 0 else i for i in src]}))
         else:
             raise ValueError("unsupported layer type [%s]" % name)
+        # keys every layer type takes (dnn/NetworkFactory.c:926-934)
+        layers[-1]["stopbackward"] = int(int(s.get("stopbackward", 0)) == 1)
+        layers[-1]["dont_update"] = int(s.get("dont_update", 0))
     return net, layers

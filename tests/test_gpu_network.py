@@ -681,6 +681,9 @@ def test_bad_cfg_is_rejected(aet, ctx):
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nsize=3\nactivation=mish\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[yolo]\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nactivation=leaky\nxnor=1\n",
+                 # per-layer keys that would change the training loop and are not restated
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nactivation=leaky\nonlyforward=1\n",
+                 "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[convolutional]\nfilters=4\nactivation=leaky\ntrain_only_bn=1\n",
                  "[net]\nbatch=2\nheight=8\nwidth=8\nchannels=3\n[softmax]\n"]:
         with pytest.raises(aet.AetError):
             aet.NNetwork(ctx, cfg_text=text)
@@ -734,3 +737,166 @@ def test_train_step_from_pinned_and_pageable_buffers_is_the_same(aet, ctx, oracl
         net.close()
     assert losses[0] == losses[1]
     assert hashes[0] == hashes[1]
+
+
+FREEZE_CFG = """[net]
+batch={batch}
+height=16
+width=16
+channels=3
+learning_rate=0.05
+momentum=0.9
+decay=0.01
+[convolutional]
+filters=64
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+[maxpool]
+size=2
+stride=2
+[convolutional]
+filters=32
+size=3
+stride=1
+pad=1
+batch_normalize=1
+activation=leaky
+{stop}
+[convolutional]
+filters=32
+size=3
+stride=1
+pad=1
+activation=relu
+{hold}
+[convolutional]
+filters=5
+size=1
+stride=1
+pad=0
+activation=linear
+{head}
+[avgpool]
+[softmax]
+"""
+
+
+@pytest.mark.parametrize("mode", [ob.MODE_MTCS, ob.MODE_CPU])
+@pytest.mark.parametrize("where", ["middle", "head"])
+def test_stopbackward_and_dont_update_match_oracle(aet, ctx, oracle64, mode, where):
+    """Fine-tuning keys (dnn/NetworkFactory.c:883-896,926-934,979-991; dnn/NNetwork.c:648-651,667-709): the backward walk
+    ends before the last stopbackward layer, the layers in front of it only run forward and keep their weights bit for
+    bit, that layer itself is still updated (weight decay on a gradient nothing writes), and dont_update = 2 holds a
+    layer's weights for two iterations in the GPU parity mode while its gradients keep accumulating (the CPU update
+    loop ignores the key).  With the key on the classifier convolution the fused head is taken apart.  Five steps, so the
+    steps after the second run as CUDA-graph replays and the held layer is released inside the replayed graph."""
+    from oracle import cfgfile
+    import aet_cnn_b200.synth as synth
+    batch = 6
+    text = FREEZE_CFG.format(batch=batch, stop="stopbackward=1" if where == "middle" else "",
+                             hold="dont_update=2", head="stopbackward=1" if where == "head" else "")
+    ctx.set_math(aet.MATH_3XTF32)
+    ctx.set_parity(mode)
+    try:
+        net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
+        opts, specs = cfgfile.network_spec(text, batch)
+        stop = 2 if where == "middle" else 4
+        assert specs[stop]["stopbackward"] == 1 and specs[3]["dont_update"] == 2
+        onet = oracle64.net(specs, batch, 3, 16, 16, mode=mode)
+        cin, start = 3, {}
+        for i, s in enumerate(specs):
+            if s["type"] == cfgfile.CONV:
+                w = synth.normal((s["filters"], cin, s["size"], s["size"]), 77, i, 0.0, float(np.sqrt(2.0 / (s["size"] ** 2 * cin))))
+                net.layer(i).write(aet.P_WEIGHTS, w)
+                onet.set_param(i, ob.P_WEIGHTS, w)
+                start[i] = w.ravel().copy()
+                cin = s["filters"]
+        held = []
+        for step in range(5):
+            x = synth.uniform((batch, 3, 16, 16), 77, 100 + 2 * step)
+            _, t = synth.labels(batch, 5, 77, 101 + 2 * step)
+            loss = net.train(x, t)
+            oloss = onet.train_step(x, t, opts["learning_rate"], opts["momentum"], opts["decay"])
+            assert abs(loss - oloss) <= 1e-4 * abs(oloss), (step, loss, oloss)
+            held.append(np.array_equal(net.layer(3).read(aet.P_WEIGHTS), start[3]))
+        for i in start:
+            got, want = net.layer(i).read(aet.P_WEIGHTS), onet.param(i, ob.P_WEIGHTS)
+            assert rel_l2(got, want) < 1e-4, (i, rel_l2(got, want))
+            if i < stop:
+                assert np.array_equal(got, start[i]), i              # frozen: not one bit moved
+                assert not np.any(net.layer(i).read(aet.P_WEIGHT_UPDATES)), i
+            elif i == stop:
+                # updated without a gradient: five steps of momentum-accumulated weight decay, nothing else
+                assert not np.array_equal(got, start[i])
+                assert np.array_equal(net.layer(i).read(aet.P_BIASES), np.zeros(specs[i]["filters"], np.float32))
+        if where == "middle":
+            # layer 3 sits behind the stop layer, so it trains: held for two iterations in the GPU mode only
+            assert held == ([True, True, False, False, False] if mode == ob.MODE_MTCS else [False] * 5), held
+        else:
+            assert all(held)                                         # in front of the stop layer: never updated
+        ctx.check()
+        net.close()
+    finally:
+        ctx.set_math(aet.MATH_TF32)
+        ctx.set_parity(ob.MODE_MTCS)
+
+
+def test_weights_file_partial_loads(aet, ctx, oracle):
+    """loadWeights(filename, cutoff) with the per-layer keys dontload and dontloadscales (dnn/NNetwork.c:64-110,
+    dnn/ConvolutionalLayer.c:455-486): a cutoff reads only the first layers, a dontload layer is passed over without
+    consuming its record, dontloadscales reads biases and weights with no batch-norm block between them, and a file that
+    ends at a record boundary (a backbone saved with fewer layers) leaves the remaining layers as they were."""
+    import aet_cnn_b200.synth as synth
+    cfg = ("[net]\nbatch=2\nheight=8\nwidth=8\nchannels=4\n"
+           "[convolutional]\nfilters=4\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=leaky\n{k0}\n"
+           "[convolutional]\nfilters=4\nsize=3\nstride=1\npad=1\nbatch_normalize=1\nactivation=leaky\n{k1}\n"
+           "[convolutional]\nfilters=3\nsize=1\nstride=1\npad=0\nactivation=linear\n[avgpool]\n[softmax]\n")
+    src = aet.NNetwork(ctx, cfg_text=cfg.format(k0="", k1=""), train=1)
+    for i, n in ((0, 4), (1, 4), (2, 3)):
+        src.layer(i).write(aet.P_WEIGHTS, synth.normal(src.layer(i).read(aet.P_WEIGHTS).shape, 5, i, 0.0, 0.5))
+        src.layer(i).write(aet.P_BIASES, synth.uniform((n,), 5, 10 + i))
+        if i < 2:
+            src.layer(i).write(aet.P_SCALES, 1 + synth.uniform((n,), 5, 20 + i))
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "src.weights")
+        src.save_weights(path)
+
+        def fresh(k0="", k1=""):
+            net = aet.NNetwork(ctx, cfg_text=cfg.format(k0=k0, k1=k1), train=1)
+            return net, [net.layer(i).read(aet.P_WEIGHTS) for i in range(3)]
+
+        def same(a, b, i, what):
+            return np.array_equal(a.layer(i).read(what), b.layer(i).read(what))
+
+        net, init = fresh()
+        net.load_weights(path, cutoff=1)                             # layer 0 only
+        assert same(net, src, 0, aet.P_WEIGHTS) and same(net, src, 0, aet.P_SCALES)
+        assert np.array_equal(net.layer(1).read(aet.P_WEIGHTS), init[1]) and np.array_equal(net.layer(2).read(aet.P_WEIGHTS), init[2])
+        net.close()
+
+        net, init = fresh(k0="dontload=1")                           # record 0 lands in layer 1 (same shape)
+        net.load_weights(path, cutoff=2)
+        assert np.array_equal(net.layer(0).read(aet.P_WEIGHTS), init[0])
+        assert np.array_equal(net.layer(1).read(aet.P_WEIGHTS), src.layer(0).read(aet.P_WEIGHTS))
+        assert np.array_equal(net.layer(1).read(aet.P_SCALES), src.layer(0).read(aet.P_SCALES))
+        net.close()
+
+        # a file whose only record has no batch-norm block, and which ends there
+        short = os.path.join(d, "short.weights")
+        bias = synth.uniform((4,), 6, 0)
+        wts = synth.normal((4, 4, 3, 3), 6, 1, 0.0, 0.5)
+        with open(short, "wb") as f:
+            np.array([0, 2, 5], np.int32).tofile(f)
+            np.array([128], np.uint64).tofile(f)
+            bias.tofile(f)
+            wts.tofile(f)
+        net, init = fresh(k0="dontloadscales=1")
+        net.load_weights(short)
+        assert np.array_equal(net.layer(0).read(aet.P_BIASES), bias) and np.array_equal(net.layer(0).read(aet.P_WEIGHTS), wts.ravel())
+        assert np.array_equal(net.layer(0).read(aet.P_SCALES), np.ones(4, np.float32))
+        assert np.array_equal(net.layer(1).read(aet.P_WEIGHTS), init[1]) and np.array_equal(net.layer(2).read(aet.P_WEIGHTS), init[2])
+        net.close()
+    src.close()

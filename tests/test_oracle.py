@@ -375,3 +375,40 @@ def test_swish_and_mish_known_values(oracle):
     # whose tanh the reference's float formula 2 / (1 + expf(-2x)) - 1 rounds to zero
     big = oracle.activate(np.array([25.0, -25.0], np.float32), ob.MISH, ob.MODE_MTCS)
     assert big[0] == 25.0 and abs(big[1]) < 1e-9
+
+
+def test_stopbackward_freezes_the_front_and_dont_update_holds_a_layer(oracle):
+    """dnn/NetworkFactory.c:883-896,979-991 and dnn/NNetwork.c:648-651,667-709: layers in front of the last stopbackward
+    layer never change; that layer sees no gradient but is still updated, so each step multiplies in the momentum-fed
+    decay: after one step W' = W * (1 - lr * decay); dont_update = 1 holds a trained layer for the first iteration of
+    the GPU update loop and releases the accumulated gradient on the second; the CPU loop does not know the key."""
+    from oracle import cfgfile
+    text = ("[net]\nbatch=4\nheight=6\nwidth=6\nchannels=2\nlearning_rate=0.1\nmomentum=0.9\ndecay=0.01\n"
+            "[convolutional]\nfilters=3\nsize=3\nstride=1\npad=1\nactivation=leaky\n"
+            "[convolutional]\nfilters=3\nsize=3\nstride=1\npad=1\nactivation=leaky\nstopbackward=1\n"
+            "[convolutional]\nfilters=4\nsize=3\nstride=1\npad=1\nactivation=leaky\ndont_update=1\n"
+            "[convolutional]\nfilters=3\nsize=1\nstride=1\npad=0\nactivation=linear\n[avgpool]\n[softmax]\n")
+    opts, specs = cfgfile.network_spec(text)
+    rng = np.random.default_rng(3)
+    for mode in (ob.MODE_MTCS, ob.MODE_CPU):
+        net = oracle.net(specs, 4, 2, 6, 6, mode=mode)
+        start, cin = {}, 2
+        for i, s in enumerate(specs):
+            if s["type"] == cfgfile.CONV:
+                start[i] = rng.normal(0, 0.4, (s["filters"], cin, s["size"], s["size"])).astype(np.float32)
+                net.set_param(i, ob.P_WEIGHTS, start[i])
+                start[i] = start[i].ravel()
+                cin = s["filters"]
+        x = rng.uniform(-1, 1, (4, 2, 6, 6)).astype(np.float32)
+        t = np.eye(3, dtype=np.float32)[[0, 1, 2, 1]]
+        net.train_step(x, t, 0.1, 0.9, 0.01)
+        assert np.array_equal(net.param(0, ob.P_WEIGHTS), start[0])
+        np.testing.assert_allclose(net.param(1, ob.P_WEIGHTS), start[1] * np.float32(1 - 0.1 * 0.01), rtol=1e-6)
+        assert np.array_equal(net.param(2, ob.P_WEIGHTS), start[2]) == (mode == ob.MODE_MTCS)
+        assert not np.array_equal(net.param(3, ob.P_WEIGHTS), start[3])
+        pending = net.param(2, ob.P_WEIGHT_UPDATES).copy()
+        if mode == ob.MODE_MTCS:
+            assert np.any(pending)                     # the gradient of the held step waits in weight_updates
+        net.train_step(x, t, 0.1, 0.9, 0.01)
+        assert not np.array_equal(net.param(2, ob.P_WEIGHTS), start[2])
+        assert np.array_equal(net.param(0, ob.P_WEIGHTS), start[0]) and not np.any(net.param(0, ob.P_WEIGHT_UPDATES))
