@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libaet_b200.so")
 SOURCES = ["tensor.cu", "elementwise.cu", "conv.cu", "layers.cu", "network.cu"]
-HEADERS = ["common.h", "umma.cuh", "activation.cuh", "conv_tma.cuh", "conv_tma_rows.cuh", "conv_thin.cuh", "stem.cuh", os.path.join("..", "..", "include", "aet_b200.h")]
+HEADERS = ["common.h", "umma.cuh", "activation.cuh", "conv_tma.cuh", "conv_tma_rows.cuh", "conv_thin.cuh", "stem.cuh", "conv_s2d.cuh", os.path.join("..", "..", "include", "aet_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]
 

@@ -58,7 +58,7 @@ struct ProfileRecord {
 // supplies the initial value; nothing on a launch path reads the environment.
 enum AetOption {
     OPT_ROWS = 0,          // row-sharing TMA kernels                         AET_NO_ROWS
-    OPT_ROWS_FPROP,        //   ... for the forward pass                      AET_NO_ROWS_F
+    OPT_ROWS_FPROP,        //   ... for the forward pass (off: the plain TMA kernel measures faster there)   AET_ROWS_F
     OPT_ROWS_DGRAD,        //   ... for the data gradient                     AET_NO_ROWS_D
     OPT_SMERGE,            // column taps merged into the MMA's N (narrow data gradients)   AET_NO_SMERGE
     OPT_KSPLIT,            // K range split over a two-CTA cluster            AET_NO_KSPLIT
@@ -82,6 +82,7 @@ enum AetOption {
     OPT_MERGE_TAIL,        // a small last gradient bucket rides with the one before it   AET_NO_MERGE_TAIL
     OPT_RAGGED,            // TMA kernels on maps whose rows do not divide the tile (13x13, 27x27)   AET_NO_RAGGED
     OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels; off by default   AET_PAIR
+    OPT_S2D,               // large strided first-layer filters regrouped into stride-1 convolutions                AET_NO_S2D
     OPT_COUNT
 };
 
@@ -189,6 +190,7 @@ struct aet_layer {
     int groups = 1;
     float temperature = 1.0f;
     float *loss = nullptr, *sample_loss = nullptr, *cost_dev = nullptr;
+    float *cost_base = nullptr;   // two {cost, mean loss} records, one per input slot of the asynchronous step; cost_dev points at the one in use
     float cost_host = 0.0f;
     bool cost_valid = false;
     // dropout
@@ -239,6 +241,10 @@ struct aet_layer {
     int n_from = 0;
     // TMA descriptors are built lazily per (layer, pass, operand address)
     void *tma_cache = nullptr;
+    // large strided first-layer filter run as a stride-1 convolution over a regrouped input (conv_s2d.cuh)
+    aet_layer *s2d = nullptr;        // the regrouped layer: geometry, regrouped weights and their gradient
+    float *s2d_x = nullptr;          // the regrouped input
+    const float *s2d_src = nullptr;  // which input s2d_x was last made from
 };
 
 struct aet_network {

@@ -739,7 +739,13 @@ static int conv_fprop_one(aet_layer *l, const float *x, float *y, const float *b
     return launch_gather<KIND_FPROP>(ctx, a, grid, "conv_fprop_gather", flops);
 }
 
+#include "conv_s2d.cuh"
+
 int conv_fprop(aet_layer *l, const float *x, float *y, const float *bias, int act_in_epilogue, ConvStats *stats) {
+    {
+        const int r = s2d_fprop(l, x, y, bias, act_in_epilogue, stats);   // large strided first-layer filters: regrouped to stride 1
+        if (r != 1) return r;
+    }
     if (l->groups == 1) return conv_fprop_one(l, x, y, bias, act_in_epilogue, stats, 0);
     if (stats) stats->rows = 0;   // grouped layers take their batch statistics from the stand-alone reduction
     for (int gi = 0; gi < l->groups; ++gi) AET_TRY(conv_fprop_one(l, x, y, bias, act_in_epilogue, nullptr, gi));
@@ -841,11 +847,18 @@ static int conv_wgrad_one(aet_layer *l, const float *x, const float *dy, float *
 }
 
 int conv_wgrad(aet_layer *l, const float *x, const float *dy, float *dw, int accumulate) {
+    {
+        const int r = s2d_wgrad(l, x, dy, dw, accumulate);
+        if (r != 1) return r;
+    }
     for (int gi = 0; gi < l->groups; ++gi) AET_TRY(conv_wgrad_one(l, x, dy, dw, accumulate, gi));
     return AET_OK;
 }
 
-void conv_release(aet_layer *l) { tma_release(l); }
+void conv_release(aet_layer *l) {
+    s2d_release(l);
+    tma_release(l);
+}
 
 int conv_set_wait_limit(unsigned long long ns) {
     AET_CUDA(cudaMemcpyToSymbol(umma::g_wait_limit_ns, &ns, sizeof(ns)));

@@ -91,12 +91,17 @@ struct TmaArgs {
     // `rows_t` whole rows of ONE image, `tiles_per_img` of them per image; the tile's remaining rows stay unused
     // (M: never stored; K: zero in both operands).  0 = dense tiling.
     int tiles_per_img, rows_t, img_h;
+    // wgrad on maps wider than a K slab whose width is no multiple of it (55, 56, 112 ...): a slab is 32 columns of ONE
+    // row, `row_slabs` of them per row; the last one reaches past the row's end, where the copy engine fills zeros
+    // into the delta operand, so the extra products vanish.  0 = off.
+    int row_slabs;
     int total_slabs, slabs_per_split;
     int col_blocks;      // wgrad: N tiles per tap
     int m_blocks;        // wgrad: 32-filter blocks of the A operand per stage
     int stages, tmem_cols;
     uint32_t tx_bytes, a_bytes;
     int *status;
+    unsigned long long *span;   // profiling: first CTA entry / last CTA exit (null: off)
 };
 
 template <int KIND>
@@ -104,6 +109,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TmaArgs a) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ SharedCtl ctl;
+    span_begin(a.span);
     // 128-byte swizzled tiles must start on a 1024-byte boundary
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
@@ -212,10 +218,19 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     for (int q = 0; q < bn / 32; ++q)
                         tma_load_5d(sb + q * 4096u, &map_b, bar, 0, sx - a.pad, oh0 + r - a.pad, img, cblk_w * (bn / 32) + q);
                 } else {
-                    const int p0 = (slab_begin + it) * BK;
-                    const int img = p0 / a.pix_per_img;
-                    const int rem = p0 - img * a.pix_per_img;
-                    const int oh0 = rem / a.img_w, ow0 = rem - oh0 * a.img_w;
+                    int img, oh0, ow0;
+                    if (a.row_slabs) {
+                        const int sl = slab_begin + it, row = sl / a.row_slabs;
+                        ow0 = (sl - row * a.row_slabs) * BK;
+                        img = row / a.img_h;
+                        oh0 = row - img * a.img_h;
+                    } else {
+                        const int p0 = (slab_begin + it) * BK;
+                        img = p0 / a.pix_per_img;
+                        const int rem = p0 - img * a.pix_per_img;
+                        oh0 = rem / a.img_w;
+                        ow0 = rem - oh0 * a.img_w;
+                    }
                     const int r = tap_w / a.S, sx = tap_w - r * a.S;
                     tma_load_5d(sa, &map_a, bar, 0, ow0, oh0, img, m0 / 32);
                     tma_load_5d(sb, &map_b, bar, 0, ow0 + sx - a.pad, oh0 + r - a.pad, img, cblk_w * (bn / 32));
@@ -273,6 +288,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tmem_dealloc(tmem, a.tmem_cols);
         if (lane == 0 && ctl.abort_flag && a.status) atomicOr(a.status, AET_STATUS_TIMEOUT);
     }
+    span_end(a.span);
 }
 
 // A 128-pixel (or `tile`-pixel) run of consecutive (n,h,w) pixels is a box iff it is whole rows
@@ -321,6 +337,7 @@ int launch_tma(aet_context *ctx, const CUtensorMap *ma, const CUtensorMap *mb, T
     const size_t smem_bytes = stage * stages + 1024;
     AET_TRY(ctx_smem_attr(ctx, conv_tma_kernel<KIND>));
     LaunchScope scope(ctx, name, 0, flops);
+    t.span = ctx->span_ptr;
     launch_k(ctx->stream, grid, NTHREADS, smem_bytes, conv_tma_kernel<KIND>, *ma, *mb, t);
     return aet_check_launch(name);
 }
@@ -428,9 +445,16 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
     if (g.OW > g.W || g.OH > g.H) return 1;
     cuuint32_t bw, bh, bi;
     int rows_t = 0, per_img = 0;
+    int row_slabs = 0;
     if (!pixel_box(BK, g.OH, g.OW, &bw, &bh, &bi)) {
-        if (!l->ctx->opt[OPT_RAGGED] || g.OW != g.W || g.OH != g.H || g.kp % 32 || !ragged_box(BK, g.OH, g.OW, &rows_t, &per_img)) return 1;
-        bw = (cuuint32_t)g.OW; bh = (cuuint32_t)rows_t; bi = 1;
+        if (!l->ctx->opt[OPT_RAGGED]) return 1;
+        if (g.OW > BK) {
+            row_slabs = (g.OW + BK - 1) / BK;   // 32-column slabs of one row, the last one zero-filled past the row's end
+            bw = BK; bh = 1; bi = 1;
+        } else {
+            if (g.OW != g.W || g.OH != g.H || g.kp % 32 || !ragged_box(BK, g.OH, g.OW, &rows_t, &per_img)) return 1;
+            bw = (cuuint32_t)g.OW; bh = (cuuint32_t)rows_t; bi = 1;
+        }
     }
     const int bn = g.cp <= 256 ? g.cp : (g.cp % 256 == 0 ? 256 : (g.cp % 128 == 0 ? 128 : 0));
     if (!bn) return 1;
@@ -469,9 +493,14 @@ int tma_wgrad(aet_layer *l, ConvArgs &a, int splits_hint, double flops) {
         t.slabs_per_split = (t.total_slabs + splits_hint - 1) / splits_hint;
         t.tx_bytes = (uint32_t)(m_blocks + bn / 32) * (uint32_t)(bw * bh) * 128u;
     }
+    if (row_slabs) {
+        t.row_slabs = row_slabs; t.img_h = g.OH;
+        t.total_slabs = g.N * g.OH * row_slabs;
+        t.slabs_per_split = (t.total_slabs + splits_hint - 1) / splits_hint;
+    }
     const int m_tiles = (g.K + BM - 1) / BM;
     dim3 grid(m_tiles, g.R * g.S * t.col_blocks, splits_hint);
-    return launch_tma<KIND_WGRAD>(l->ctx, ma, mb, t, grid, per_img ? "conv_wgrad_tma.ragged" : "conv_wgrad_tma", flops);
+    return launch_tma<KIND_WGRAD>(l->ctx, ma, mb, t, grid, per_img ? "conv_wgrad_tma.ragged" : (row_slabs ? "conv_wgrad_tma.wide" : "conv_wgrad_tma"), flops);
 }
 
 void tma_release(aet_layer *l) {

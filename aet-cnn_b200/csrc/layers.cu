@@ -227,7 +227,8 @@ extern "C" aet_layer *aet_softmax_layer_create(aet_context *ctx, int batch, int 
     const size_t n = (size_t)batch * l->cp;
     ok = ok && cudaMalloc(&l->loss, n * sizeof(float)) == cudaSuccess && cudaMemset(l->loss, 0, n * sizeof(float)) == cudaSuccess;
     ok = ok && cudaMalloc(&l->sample_loss, (size_t)batch * groups * sizeof(float)) == cudaSuccess;
-    ok = ok && cudaMalloc(&l->cost_dev, 4 * sizeof(float)) == cudaSuccess && cudaMemset(l->cost_dev, 0, 4 * sizeof(float)) == cudaSuccess;
+    ok = ok && cudaMalloc(&l->cost_base, 8 * sizeof(float)) == cudaSuccess && cudaMemset(l->cost_base, 0, 8 * sizeof(float)) == cudaSuccess;
+    l->cost_dev = l->cost_base;
     if (!ok) { aet_set_error("softmax: allocation failed"); aet_layer_destroy(l); return nullptr; }
     cudaDeviceSynchronize();
     return l;
@@ -309,7 +310,7 @@ extern "C" void aet_layer_destroy(aet_layer *l) {
     if (l->stem_gram) cudaFree(l->stem_gram);
     if (l->lin_xbar) cudaFree(l->lin_xbar);
     if (l->lin_ticket) cudaFree(l->lin_ticket);
-    if (l->cost_dev) cudaFree(l->cost_dev);
+    if (l->cost_base) cudaFree(l->cost_base);
     if (l->rnd) cudaFree(l->rnd);
     if (l->step_dev) cudaFree(l->step_dev);
     arena_destroy(&l->own_arena);

@@ -807,7 +807,10 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
     }
     const int kind = final ? 1 : 0;
     aet_layer *sm = softmax_layer(net);
-    if (sm) sm->cost_valid = false;
+    if (sm) {
+        sm->cost_valid = false;
+        sm->cost_dev = sm->cost_base + 4 * net->cur_slot;   // each input slot's graph writes a cost record of its own
+    }
     const long before = ctx->launches;
     const int gi = kind + 2 * net->cur_slot;   // a graph holds its tensors' addresses: one per input slot
     if (net->use_graph && net->graph_exec[gi] && !ctx->profiling) {
@@ -931,15 +934,16 @@ extern "C" int aet_network_train_step_async(aet_network *net, const float *host_
     AET_CUDA(cudaEventRecord(net->ev_staged[slot], net->copy_stream));
     AET_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_staged[slot], 0));
     pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
-    if (net->async_steps >= 1) AET_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_loss[prev], 0));
+    // the step overwrites this slot's cost record: the read-back of two calls ago (long finished) must have run; the
+    // previous step's read-back uses the other record, so the steps stay back to back
+    if (reused) AET_CUDA(cudaStreamWaitEvent(ctx->stream, net->ev_loss[slot], 0));
     aet_tensor *in0 = net->input, *tr0 = net->truth;
     net->input = in; net->truth = tr; net->cur_slot = slot;
     const int sr = aet_network_train_step_device(net, nullptr);
     net->input = in0; net->truth = tr0; net->cur_slot = 0;
     AET_TRY(sr);
     AET_CUDA(cudaEventRecord(net->ev_consumed[slot], ctx->stream));   // the step has read the slot's tensors to its end
-    // The loss travels back on a stream of its own, so that the steps stay back to back on the main stream; the next
-    // step waits (above) for this copy before its head kernel may overwrite the cost.
+    // The loss travels back on a stream of its own, so that the steps stay back to back on the main stream.
     float *ring = net->loss_pinned + 8 + 4 * slot;
     AET_CUDA(cudaStreamWaitEvent(net->loss_stream, net->ev_consumed[slot], 0));
     AET_TRY(queue_loss_readback(net, ring, net->loss_stream));

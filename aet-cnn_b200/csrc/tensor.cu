@@ -96,7 +96,7 @@ struct OptionDesc {
 };
 const OptionDesc kOptions[OPT_COUNT] = {
     {"rows", "AET_NO_ROWS", 1, 0},
-    {"rows_fprop", "AET_NO_ROWS_F", 1, 0},
+    {"rows_fprop", "AET_ROWS_F", 0, 1},
     {"rows_dgrad", "AET_NO_ROWS_D", 1, 0},
     {"smerge", "AET_NO_SMERGE", 1, 0},
     {"ksplit", "AET_NO_KSPLIT", 1, 0},
@@ -120,6 +120,7 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"merge_tail", "AET_NO_MERGE_TAIL", 1, 0},
     {"ragged", "AET_NO_RAGGED", 1, 0},
     {"pair", "AET_PAIR", 0, 1},
+    {"s2d", "AET_NO_S2D", 1, 0},
 };
 }  // namespace
 

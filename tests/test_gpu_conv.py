@@ -98,6 +98,8 @@ RAGGED_SHAPES = [
     (3, 64, 13, 13, 64, 3, 1, 1, 2),       # one N tile, odd batch
     (2, 32, 7, 20, 32, 3, 1, 1, 0),        # non-square: 6 + 1 rows
     (2, 64, 9, 100, 32, 1, 1, 0, 1),       # one row per tile (w > 64), 1x1
+    (2, 32, 12, 40, 64, 3, 1, 1, 2),       # rows wider than a weight-gradient K slab: two 32-column slabs per row
+    (1, 64, 56, 56, 64, 3, 1, 1, 1),       # a 56x56 map (ResNet-style): two rows per forward tile, 32 + 24 columns per slab pair
 ]
 
 
@@ -112,8 +114,8 @@ def test_conv_tma_ragged_maps(aet, ctx, oracle, shape):
         ctx.profile(0)
     names = {u.split("#")[0] for u in used}
     want = {"conv_fprop_tma.ragged", "conv_dgrad_tma.ragged"}
-    if shape[3] <= 32:          # a weight-gradient K slab is 32 pixels: rows wider than that stay on the gather kernel
-        want.add("conv_wgrad_tma.ragged")
+    # a weight-gradient K slab is 32 pixels: narrower maps are tiled as whole rows, wider ones as 32-column pieces of a row
+    want.add("conv_wgrad_tma.ragged" if shape[3] <= 32 else "conv_wgrad_tma.wide")
     assert want <= names, sorted(names)
     check(got, ref, TOL_TF32)
     # and the same shapes with the option off go to the gather kernel and agree with it closely
@@ -183,19 +185,23 @@ def test_conv_thin_tf32(aet, ctx, oracle, shape):
 # split over a two-CTA cluster, two filter tiles), so these shapes are checked at that size and the path each
 # launch took is asserted by its label.  N = 112 is the smallest batch above the two-tile threshold.
 BENCH_SHAPES = [
-    # shape, context options, {kernel: variant} expected on a 148-SM part
-    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {}, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1",
-                                              "conv_wgrad_tma_rows": "n64_sp49"}),
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {}, {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2",
-                                             "conv_wgrad_tma_rows": "n128_sp24"}),
-    ((112, 64, 16, 16, 128, 3, 1, 1, 0), {}, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
+    # shape, context options, {kernel: variant} expected on a 148-SM part ("" = the kernel has no variants)
+    # defaults: forward on the plain TMA kernel, data and weight gradient on the row-sharing kernels
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {}, {"conv_fprop_tma": "", "conv_dgrad_tma_rows": "sm_mt2_n192x1", "conv_wgrad_tma_rows": "n64_sp49"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {}, {"conv_fprop_tma": "", "conv_dgrad_tma_rows": "mt1_n128x1_ks2", "conv_wgrad_tma_rows": "n128_sp24"}),
+    # the row-sharing forward kernel (option rows_fprop)
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {"rows_fprop": 1}, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1",
+                                                             "conv_wgrad_tma_rows": "n64_sp49"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"rows_fprop": 1}, {"conv_fprop_tma_rows": "mt1_n128x2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2",
+                                                            "conv_wgrad_tma_rows": "n128_sp24"}),
+    ((112, 64, 16, 16, 128, 3, 1, 1, 0), {"rows_fprop": 1}, {"conv_fprop_tma_rows": "mt2e_n128x1", "conv_dgrad_tma_rows": "sm_mt2_n192x1"}),
     # CTA pairs (cta_group::2 MMAs, each CTA loading half of the filter tile), off by default
-    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {"pair": 1}, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2"}),
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"pair": 1}, {"conv_fprop_tma_rows": "mt1_n128x2_p2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2_p2"}),
-    ((16, 64, 16, 16, 128, 3, 1, 1, 1), {"pair": 1}, {"conv_fprop_tma_rows": "*_p2", "conv_dgrad_tma_rows": "*_p2"}),
+    ((128, 64, 16, 16, 128, 3, 1, 1, 2), {"pair": 1, "rows_fprop": 1}, {"conv_fprop_tma_rows": "mt2e_n128x1_p2", "conv_dgrad_tma_rows": "sm_mt2_n192x1_p2"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"pair": 1, "rows_fprop": 1}, {"conv_fprop_tma_rows": "mt1_n128x2_p2", "conv_dgrad_tma_rows": "mt1_n128x1_ks2_p2"}),
+    ((16, 64, 16, 16, 128, 3, 1, 1, 1), {"pair": 1, "rows_fprop": 1}, {"conv_fprop_tma_rows": "*_p2", "conv_dgrad_tma_rows": "*_p2"}),
     # two accumulators per tile (alternate filter rows), off by default; also without the rotated K order
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"dual_acc": 1}, {"conv_fprop_tma_rows": "mt1d_n128x2", "conv_dgrad_tma_rows": "mt1d_n128x1_ks2"}),
-    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"dual_acc": 1, "pair": 1, "rotate": 0},
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"dual_acc": 1, "rows_fprop": 1}, {"conv_fprop_tma_rows": "mt1d_n128x2", "conv_dgrad_tma_rows": "mt1d_n128x1_ks2"}),
+    ((128, 128, 8, 8, 256, 3, 1, 1, 2), {"dual_acc": 1, "pair": 1, "rotate": 0, "rows_fprop": 1},
      {"conv_fprop_tma_rows": "mt1d_n128x2_p2", "conv_dgrad_tma_rows": "mt1d_n128x1_ks2_p2"}),
 ]
 
@@ -215,7 +221,9 @@ def test_conv_benchmark_shapes_at_benchmark_batch(aet, ctx, oracle, shape, optio
         for name, value in saved.items():
             ctx.set_option(name, value)
     for kernel, variant in variants.items():
-        if variant.startswith("*"):
+        if variant == "":
+            assert kernel in used, (kernel, sorted(used))
+        elif variant.startswith("*"):
             assert any(u.startswith(kernel + ".") and u.endswith(variant[1:]) for u in used), (kernel, variant, sorted(used))
         else:
             assert kernel + "." + variant in used, (kernel, variant, sorted(used))
@@ -230,6 +238,50 @@ SWEEP_SHAPES = [
     (256, 256, 8, 8, 256, 3, 1, 1, 0),
     (256, 256, 4, 4, 10, 1, 1, 0, 0),
 ]
+
+
+# Large strided filters on an image (the thin-K kernels stop at K = 128): regrouped into s x s pixel blocks they are
+# stride-1 convolutions over s*s*4 channels, which the TMA kernels run (conv_s2d.cuh).
+S2D_SHAPES = [
+    (4, 3, 47, 47, 16, 11, 4, 0, 1),      # AlexNet-style first layer, reduced: 3x3 block taps on a 12x12 regrouped map, 64 channels
+    (3, 3, 59, 59, 96, 11, 4, 0, 1),      # ... with its 96 filters (a whole number of 32-filter blocks: TMA weight gradient)
+    (2, 3, 23, 27, 32, 7, 2, 3, 2),       # 7x7 stride 2 with padding (ResNet-style stem): 4x4 block taps, 16 -> 32 channels
+    (2, 1, 38, 38, 8, 6, 3, 1, 0),        # one input channel, stride 3 (36 -> 64 channels), even filter
+    (5, 4, 30, 30, 40, 8, 2, 0, 1),       # filter size a multiple of the stride
+    (4, 3, 22, 22, 64, 8, 2, 0, 2),       # 8x8 output map: the weight gradient is regrouped too
+    (2, 3, 71, 71, 32, 11, 4, 0, 1),      # 16x16 output map, 11x11 / 4
+]
+S2D_WGRAD = S2D_SHAPES[-2:]
+
+
+@pytest.mark.parametrize("shape", S2D_SHAPES)
+def test_conv_regrouped_strided_first_layer(aet, ctx, oracle, shape):
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=900 + shape[5])
+        used = kernels_used(ctx)
+    finally:
+        ctx.profile(0)
+    assert {"conv_s2d_input", "conv_s2d_weights"} <= used, used
+    assert {"conv_fprop_tma", "conv_fprop_tma_rows"} & used and "conv_fprop_gather" not in used, used
+    # the weight gradient is regrouped only where its 32-pixel K slabs tile the output map
+    print("regrouped shape", shape, "->", sorted(used))
+    if shape in S2D_WGRAD:
+        assert "conv_s2d_fold" in used and {"conv_wgrad_tma", "conv_wgrad_tma_rows"} & used and "conv_wgrad_gather" not in used, used
+    check(got, ref, TOL_TF32)
+    # with the option off the same layer runs on the gather kernel and agrees closely
+    ctx.set_option("s2d", 0)
+    ctx.profile(1)
+    try:
+        plain, _ = conv_case(aet, ctx, oracle, *shape, seed=900 + shape[5])
+        used = kernels_used(ctx)
+    finally:
+        ctx.profile(0)
+        ctx.set_option("s2d", 1)
+    assert "conv_fprop_gather" in used and "conv_s2d_input" not in used, used
+    for k in ("y", "dw"):
+        assert rel_l2(got[k].ravel(), plain[k].ravel()) <= 2e-3, k
 
 
 @pytest.mark.parametrize("shape", SWEEP_SHAPES)

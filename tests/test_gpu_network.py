@@ -90,9 +90,9 @@ def test_small_cnn_training_matches_oracle(aet, ctx, oracle64, mode):
         ctx.set_parity(ob.MODE_MTCS)
 
 
-# code path of every row-sharing launch of the small CNN at the benchmark batch on a 148-SM part
-BENCH_VARIANTS = {"conv_fprop_tma_rows.mt2e_n128x1#2", "conv_dgrad_tma_rows.sm_mt2_n192x1#2", "conv_wgrad_tma_rows.n64_sp49#2",
-                  "conv_fprop_tma_rows.mt1_n128x2#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
+# code path of every TMA convolution launch of the small CNN at the benchmark batch on a 148-SM part
+BENCH_VARIANTS = {"conv_fprop_tma#2", "conv_dgrad_tma_rows.sm_mt2_n192x1#2", "conv_wgrad_tma_rows.n64_sp49#2",
+                  "conv_fprop_tma#4", "conv_dgrad_tma_rows.mt1_n128x1_ks2#4", "conv_wgrad_tma_rows.n128_sp24#4"}
 
 
 @pytest.mark.parametrize("batch", [16, 128])
