@@ -64,6 +64,12 @@ __device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<floa
 // a kernel of its own: the BN backward kernels fetch "the delta the pool would have scattered here"
 // on the fly from the pool's (4x smaller) delta and argmax tensors.  Same gather rule as
 // maxpool_bwd_kernel (mtcs/MtcsMaxPoolLayer.c:295-332).
+// windows [o * stride, o * stride + size) that contain coordinate v (already shifted by the pool's offset): first and last o
+__device__ __forceinline__ int window_first(int v, int size, int stride) {
+    const int t = v - size + 1;
+    return t <= 0 ? 0 : (t + stride - 1) / stride;
+}
+__device__ __forceinline__ int window_last(int v, int stride) { return v < 0 ? -1 : v / stride; }
 struct PoolGather {
     const float *delta;   // pool layer delta  [N][OH][OW][cp]
     const int *idx;       // pool argmax       [N][OH][OW][cp], reference numbering
@@ -92,11 +98,12 @@ __device__ __forceinline__ float4 pool_gather(const PoolGather &g, long long p, 
         }
         return d;
     }
-    const int area_x = (g.size - 1) / g.sx, area_y = (g.size - 1) / g.sy;
-    for (int l = -area_y; l < area_y + 1; ++l)
-        for (int m = -area_x; m < area_x + 1; ++m) {
-            const int ow = (j - g.off) / g.sx + m, oh = (i - g.off) / g.sy + l;
-            if (ow < 0 || ow >= g.OW || oh < 0 || oh >= g.OH) continue;
+    // The reference walks every window within (size - 1) / stride of the pixel's own; an argmax can only name a pixel
+    // inside its window, so the windows that do not contain the pixel add nothing and are not read.
+    const int oh_lo = window_first(i - g.off, g.size, g.sy), oh_hi = min(window_last(i - g.off, g.sy), g.OH - 1);
+    const int ow_lo = window_first(j - g.off, g.size, g.sx), ow_hi = min(window_last(j - g.off, g.sx), g.OW - 1);
+    for (int oh = oh_lo; oh <= oh_hi; ++oh)
+        for (int ow = ow_lo; ow <= ow_hi; ++ow) {
             const size_t o = ((size_t)(n * g.OH + oh) * g.OW + ow) * cp + c;
             const int4 id = __ldg(reinterpret_cast<const int4 *>(g.idx + o));
             const float4 dv = __ldg(reinterpret_cast<const float4 *>(g.delta + o));
@@ -685,14 +692,14 @@ __global__ void __launch_bounds__(TB) maxpool_bwd_kernel(const PoolBwdArgs a) {
     const int i = (int)(p % (unsigned)a.H);
     const int n = (int)(p / (unsigned)a.H);
     const int c = cv * 4;
-    const int area_x = (a.size - 1) / a.sx, area_y = (a.size - 1) / a.sy;
     const int hw = a.H * a.W;
     const int my = j + a.W * (i + a.H * (c + n * a.C));
     float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int l = -area_y; l < area_y + 1; ++l)
-        for (int m = -area_x; m < area_x + 1; ++m) {
-            const int ow = (j - a.off) / a.sx + m, oh = (i - a.off) / a.sy + l;
-            if (ow < 0 || ow >= a.OW || oh < 0 || oh >= a.OH) continue;
+    // only the windows that contain the pixel can name it (see pool_gather); same order as the reference's walk
+    const int oh_lo = window_first(i - a.off, a.size, a.sy), oh_hi = min(window_last(i - a.off, a.sy), a.OH - 1);
+    const int ow_lo = window_first(j - a.off, a.size, a.sx), ow_hi = min(window_last(j - a.off, a.sx), a.OW - 1);
+    for (int oh = oh_lo; oh <= oh_hi; ++oh)
+        for (int ow = ow_lo; ow <= ow_hi; ++ow) {
             const size_t o = ((size_t)(n * a.OH + oh) * a.OW + ow) * a.cp + c;
             const int4 id = *reinterpret_cast<const int4 *>(a.idx + o);
             const float4 dv = ld4(a.delta + o);
