@@ -181,7 +181,37 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     volatile int *abort_flag = &ctl.abort_flag;
 
     if (warp < 4) {
-        if (threadIdx.x == 0) {
+        if (KIND == KIND_WGRAD && a.tiles_per_img) {
+            // ------------------------------------------------------------------ TMA producer, ragged K slabs
+            // A slab is one copy per 32-element block of each operand (a block is 4 KB in the swizzled layout, a copy
+            // of several blocks would pack them at the box's own, smaller, pitch): seven small copies for four MMAs.
+            // Issued by one thread they set the pace of the loop, so the lanes of warp 0 issue one copy each.
+            if (warp == 0) {
+                const int ncopies = a.m_blocks + bn / 32;
+                const int r = tap_w / a.S, sx = tap_w - r * a.S;
+                for (int it = 0; it < nslabs; ++it) {
+                    const int s = it % a.stages;
+                    const uint32_t phase = (it / a.stages) & 1;
+                    bool ok = mbar_wait(smem_u32(&ctl.empty[s]), phase ^ 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const uint32_t bar = smem_u32(&ctl.full[s]);
+                    const uint32_t sa = smem_base + (uint32_t)s * stage_bytes;
+                    const uint32_t sb = sa + a.a_bytes;
+                    if (lane == 0) mbar_arrive_expect_tx(bar, a.tx_bytes);
+                    __syncwarp();   // the transaction count is announced before any copy can complete
+                    const int sl = slab_begin + it;
+                    const int img = sl / a.tiles_per_img;
+                    const int oh0 = (sl - img * a.tiles_per_img) * a.rows_t;
+                    if (lane < a.m_blocks) {
+                        tma_load_5d(sa + lane * 4096u, &map_a, bar, 0, 0, oh0, img, m0 / 32 + lane);
+                    } else if (lane < ncopies) {
+                        const int q = lane - a.m_blocks;
+                        tma_load_5d(sb + q * 4096u, &map_b, bar, 0, sx - a.pad, oh0 + r - a.pad, img, cblk_w * (bn / 32) + q);
+                    }
+                }
+            }
+        } else if (threadIdx.x == 0) {
             // ------------------------------------------------------------------ TMA producer
             // CTAs walk the K slabs from different starting points: all of them read the same weight
             // tiles, and marching in lockstep would send every SM to the same L2 lines at once.  The
@@ -207,16 +237,6 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const int r = tap / a.S, sx = tap - r * a.S;
                     tma_load_4d(sa, &map_a, bar, kb * 32, a.pad - sx, row0 + a.pad - r, img0);
                     tma_load_4d(sb, &map_b, bar, 0, kb * 32, n0 / 32, tap);
-                } else if (a.tiles_per_img) {
-                    // ragged: one copy per 32-element block of each operand (a block is 4 KB in the swizzled layout,
-                    // a copy of several blocks would pack them at the box's own, smaller, pitch)
-                    const int sl = slab_begin + it;
-                    const int img = sl / a.tiles_per_img;
-                    const int oh0 = (sl - img * a.tiles_per_img) * a.rows_t;
-                    const int r = tap_w / a.S, sx = tap_w - r * a.S;
-                    for (int q = 0; q < a.m_blocks; ++q) tma_load_5d(sa + q * 4096u, &map_a, bar, 0, 0, oh0, img, m0 / 32 + q);
-                    for (int q = 0; q < bn / 32; ++q)
-                        tma_load_5d(sb + q * 4096u, &map_b, bar, 0, sx - a.pad, oh0 + r - a.pad, img, cblk_w * (bn / 32) + q);
                 } else {
                     int img, oh0, ow0;
                     if (a.row_slabs) {
