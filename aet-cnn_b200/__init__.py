@@ -41,7 +41,7 @@ aet_network_augment_input aet_network_fuse_conv_batchnorm aet_network_predict_to
 aet_network_use_graph aet_network_load_weights aet_network_load_weights_upto aet_network_save_weights aet_network_load_momentum aet_network_save_momentum aet_network_comm_exposed aet_network_param_hash
 aet_network_profile aet_network_profile_read aet_network_launches_per_step aet_comm_unique_id
 aet_network_comm_init aet_network_comm_destroy aet_network_grad_arena aet_backward_bias_static
-aet_network_comm_exchange_export aet_network_comm_exchange_attach""".split()
+aet_network_comm_exchange_export aet_network_comm_exchange_attach aet_network_comm_exchange_detach""".split()
 
 
 class AetError(RuntimeError):
@@ -134,7 +134,7 @@ def lib():
         "aet_network_profile_read": (i, [vp, C.POINTER(KernelTime), i, C.POINTER(i)]),
         "aet_network_launches_per_step": (i, [vp]),
         "aet_comm_unique_id": (i, [vp]), "aet_network_comm_init": (i, [vp, vp, i, i]),
-        "aet_network_comm_exchange_export": (i, [vp, vp]), "aet_network_comm_exchange_attach": (i, [vp, vp]),
+        "aet_network_comm_exchange_export": (i, [vp, vp]), "aet_network_comm_exchange_attach": (i, [vp, vp]), "aet_network_comm_exchange_detach": (i, [vp]),
         "aet_network_comm_destroy": (i, [vp]),
         "aet_network_grad_arena": (i, [vp, C.POINTER(vp), C.POINTER(C.c_size_t)]),
         "aet_backward_bias_static": (i, [vp, vp, C.c_longlong, i, vp]),
@@ -543,6 +543,10 @@ class NNetwork:
         """`blobs`: every rank's export, in rank order."""
         raw = b"".join(bytes(b) for b in blobs)
         _check(self.L.aet_network_comm_exchange_attach(self.h, C.create_string_buffer(raw, len(raw))))
+
+    def comm_exchange_detach(self):
+        """Back to the collectives alone (all ranks together)."""
+        _check(self.L.aet_network_comm_exchange_detach(self.h))
 
     def grad_arena(self):
         p, n = C.c_void_p(), C.c_size_t()

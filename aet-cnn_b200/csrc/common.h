@@ -316,6 +316,7 @@ struct aet_network {
     unsigned long long *xchg_epoch = nullptr;   // device-side step counter
     unsigned int *xchg_ticket = nullptr;        // blocks of the publish kernel that have finished
     unsigned long long *comm_stamp_dev = nullptr;   // {last stamp, summed wait in ns, waits counted, unused}
+    bool comm_stamped = false;                  // this step's backward already bracketed a wait for collectives
     int *xchg_gate = nullptr;                   // 1 / 0: this step's slices of all ranks arrived / the wait ran out
     size_t tail_lo = 0, tail_n = 0;             // arena range summed through the exchange this step (0: none)
     cudaEvent_t ev_uploaded = nullptr;   // after the H2D copies of a train step fed from the caller's pinned buffers

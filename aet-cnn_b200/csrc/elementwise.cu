@@ -1987,6 +1987,19 @@ int k_sgd_segment(aet_context *ctx, float *W, float *U, float *G, size_t count, 
     return aet_check_launch("sgd_segment");
 }
 
+__global__ void comm_stamp_kernel(unsigned long long *d, int after) {
+    pdl_enter();
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (!after) d[0] = now;
+    else { d[1] += now - d[0]; if (after == 1) d[2] += 1; }   // after == 2: a second bracket of the same step
+}
+int k_comm_stamp(aet_context *ctx, unsigned long long *dev4, int after) {
+    LaunchScope s(ctx, "comm_stamp", 0, 0);
+    launch_k(ctx->stream, 1, 1, 0, comm_stamp_kernel, dev4, after);
+    return aet_check_launch("comm_stamp");
+}
+
 int k_sgd_arena(aet_network *net) {
     aet_context *ctx = net->ctx;
     LaunchScope s(ctx, "sgd_momentum", 24.0 * net->arena.used, 0);
@@ -1996,9 +2009,14 @@ int k_sgd_arena(aet_network *net) {
         t.flags = reinterpret_cast<const volatile unsigned long long *>(net->xchg_local);
         t.epoch = net->xchg_epoch; t.lo = net->tail_lo; t.n = net->tail_n; t.cap = net->xchg_cap;
         t.world = net->world; t.status = ctx->status_dev; t.gate = net->xchg_gate;
+        // option "comm_stamps": the wait for the peers' slices counts as exposed communication like the wait for a collective
+        const bool stamps = ctx->opt[OPT_COMM_STAMPS] != 0 && net->comm_stamp_dev;
+        if (stamps) launch_k(ctx->stream, 1, 1, 0, comm_stamp_kernel, net->comm_stamp_dev, 0);
         launch_k(ctx->stream, 1, 32, 0, tail_wait_kernel, t);
+        if (stamps) launch_k(ctx->stream, 1, 1, 0, comm_stamp_kernel, net->comm_stamp_dev, net->comm_stamped ? 2 : 1);
         AET_TRY(aet_check_launch("grad_wait"));
     }
+    net->comm_stamped = false;
     launch_k(ctx->stream, net->n_blocks, TB, 0, sgd_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->block_seg,
                                                            net->seg_table, net->hyper_dev, t, ctx->status_dev);
     return aet_check_launch("sgd_momentum");
@@ -2011,19 +2029,6 @@ int k_adam_arena(aet_network *net) {
     launch_k(ctx->stream, net->n_blocks, TB, 0, adam_arena_kernel, net->arena.W, net->arena.U, net->arena.G, net->arena.M, net->arena.V,
              net->block_seg, net->seg_table, net->hyper_dev, net->B1, net->B2, net->eps, ctx->status_dev);
     return aet_check_launch("adam");
-}
-
-__global__ void comm_stamp_kernel(unsigned long long *d, int after) {
-    pdl_enter();
-    unsigned long long now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    if (!after) d[0] = now;
-    else { d[1] += now - d[0]; d[2] += 1; }
-}
-int k_comm_stamp(aet_context *ctx, unsigned long long *dev4, int after) {
-    LaunchScope s(ctx, "comm_stamp", 0, 0);
-    launch_k(ctx->stream, 1, 1, 0, comm_stamp_kernel, dev4, after);
-    return aet_check_launch("comm_stamp");
 }
 
 int k_tail_publish(aet_network *net) {

@@ -365,6 +365,7 @@ int net_backward(aet_network *net, aet_state state, bool exchange = true) {
         AET_CUDA(cudaStreamWaitEvent(net->ctx->stream, net->ev_comm_done, 0));
         pdl_skip_next();   // the kernel after a cross-stream wait is launched plainly
         if (stamps) AET_TRY(k_comm_stamp(ctx, net->comm_stamp_dev, 1));
+        net->comm_stamped = stamps;
     }
     if (net->tail_n) AET_TRY(k_tail_publish(net));
     return AET_OK;
@@ -1336,6 +1337,19 @@ extern "C" int aet_network_comm_exchange_attach(aet_network *net, const void *bl
     }
     net->xchg_active = true;
     graph_drop(net);
+    return AET_OK;
+}
+
+// Back to the collectives alone (the mapped buffers stay until the network is destroyed).  Every rank must take the
+// same path, so a launcher whose attach failed on any rank detaches on all of them.
+extern "C" int aet_network_comm_exchange_detach(aet_network *net) {
+    if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    ctx_enter(net->ctx);
+    if (net->xchg_active) {
+        AET_CUDA(cudaStreamSynchronize(net->ctx->stream));
+        net->xchg_active = false;
+        graph_drop(net);
+    }
     return AET_OK;
 }
 

@@ -428,9 +428,24 @@ def main():
     import aet_cnn_b200.parallel as par
     if world > 1:
         net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
-        if world <= 8 and os.environ.get("AET_PEER_EXCHANGE"):
-            # opt-in: gradients summed through peer-mapped buffers inside the update kernel instead of by NCCL
-            net.comm_exchange_attach(par.all_gather_bytes(net.comm_exchange_export()))
+        exchange = "nccl"
+        if world <= 8 and not os.environ.get("AET_NO_PEER_EXCHANGE"):
+            # One box, at most 8 ranks: the gradients are summed through peer-mapped buffers inside the update kernel
+            # (a gradient arena of up to 4 MB whole, otherwise its last bucket) instead of by the last collective; at 8
+            # GPUs this step is 12 us shorter than with NCCL alone.  Every rank must take the same path, so the ranks
+            # agree on whether the attach worked everywhere and fall back to NCCL together if it did not.
+            ok = 1
+            try:
+                net.comm_exchange_attach(par.all_gather_bytes(net.comm_exchange_export()))
+            except aet.AetError as e:
+                ok = 0
+                sys.stderr.write("rank %d: peer exchange not attached (%s)\n" % (rank, e))
+            flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 1:
+                exchange = "peer"
+            else:
+                net.comm_exchange_detach()
 
     host_batches, pinned_keep = [], []
 
@@ -526,9 +541,9 @@ def main():
         exposed_us, counted = net.comm_exposed()
         ctx.set_option("comm_stamps", 0)
         net.use_graph(False); net.use_graph(True)
-        comm = {"exposed_us_per_step": max_over_ranks(exposed_us), "steps": counted,
-                "method": "two one-thread kernels read %globaltimer before and after the main stream's wait for the "
-                          "all-reduces; mean over the steps, max over ranks"}
+        comm = {"exposed_us_per_step": max_over_ranks(exposed_us), "steps": counted, "gradient_exchange": exchange,
+                "method": "two one-thread kernels read %globaltimer before and after the main stream's waits for the "
+                          "all-reduces and for the peers' gradient slices; mean over the steps, max over ranks"}
 
     # ---- per-kernel pass for the roofline (eager launches, events around each)
     # The weight-gradient kernels stay on the main stream here, so that no kernel's time includes a

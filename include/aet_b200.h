@@ -301,6 +301,8 @@ int   aet_network_comm_exposed(aet_network *net, double *mean_microseconds, long
  * refuses ranks that share a GPU.  Without attach the bucket goes through the all-reduce like the others. */
 int   aet_network_comm_exchange_export(aet_network *net, void *blob_80);
 int   aet_network_comm_exchange_attach(aet_network *net, const void *blobs_world_x_80);
+/* Back to the collectives alone.  Every rank must take the same path: when the attach failed on any rank, all detach. */
+int   aet_network_comm_exchange_detach(aet_network *net);
 int   aet_network_comm_destroy(aet_network *net);
 /* Device pointer and float count of the gradient arena (for callers that run their own collective). */
 int   aet_network_grad_arena(aet_network *net, void **device_ptr, size_t *count);

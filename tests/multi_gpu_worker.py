@@ -23,8 +23,7 @@ def run(mode, rank, world, local_rank, steps=4, batch=16):
     text = open(os.path.join(aet.CFG_DIR, "cifar_small.cfg")).read()
     opts, specs = cfgfile.network_spec(text, batch)
     ctx = aet.Context(local_rank)
-    if mode == "nccl":
-        ctx.set_option("comm_stamps", 1)      # time the main stream's wait for the collectives (two extra tiny kernels)
+    ctx.set_option("comm_stamps", 1)          # time the main stream's waits for the exchange (two extra tiny kernels each)
     net = aet.NNetwork(ctx, cfg_text=text, train=1, batch=batch)
     bench.init_weights(aet, synth, net, 3)
     net.comm_init(par.exchange_unique_id(aet.comm_unique_id), rank, world)
@@ -32,7 +31,9 @@ def run(mode, rank, world, local_rank, steps=4, batch=16):
         net.comm_exchange_attach(par.all_gather_bytes(net.comm_exchange_export()))
     net.use_graph(True)
     losses = []
-    for s in range(steps):
+    for s in range(steps + 1):
+        if mode == "peer" and s == steps:
+            net.comm_exchange_detach()        # the last step goes through the collectives again
         tid = par.shard_tensor_id(s, rank, world)
         losses.append(net.train(synth.uniform((batch, 3, 32, 32), 7, 2 * tid), synth.labels(batch, 10, 7, 2 * tid + 1)[1]))
     ctx.check()

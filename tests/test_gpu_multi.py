@@ -27,8 +27,10 @@ def test_two_ranks_nccl_and_peer_exchange_agree():
         assert out[mode]["identical_across_ranks"], mode          # weights bitwise identical on both ranks
     assert out["nccl"]["hash"] == out["peer"]["hash"]             # two ranks: the same sum either way (and the stamps change nothing)
     us, counted = out["nccl"]["comm_exposed"]
-    assert counted == 4 and 0.0 <= us < 1e5, out["nccl"]["comm_exposed"]    # one wait per step, a plausible duration
-    assert out["peer"]["comm_exposed"][1] == 0                    # no collective, nothing to wait for
+    assert counted == 5 and 0.0 <= us < 1e5, out["nccl"]["comm_exposed"]    # one wait per step, a plausible duration
+    # peer exchange: the wait for the peers' slices is bracketed the same way (four steps), then one step after the detach
+    us, counted = out["peer"]["comm_exposed"]
+    assert counted == 5 and 0.0 <= us < 1e5, out["peer"]["comm_exposed"]
     assert out["nccl"]["losses"] == out["peer"]["losses"]
     # the data-parallel result itself against the CPU oracle's emulation of the two ranks (3xTF32 math, two steps)
     assert out["oracle"], out
