@@ -1256,11 +1256,15 @@ __global__ void __launch_bounds__(TB) sgd_arena_kernel(float *W, float *U, float
         if (b0 >= t.lo && b0 < t.lo + t.n) {
             // this block's gradients are the sum of every rank's published slice, added in rank order
             const unsigned long long parity = *t.epoch & 1ull;
+            // (all ranks' loads are issued before the first sum: one NVLink round trip instead of one per rank)
+            float4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < t.world) v[q] = __ldcv(reinterpret_cast<const float4 *>(t.peer_buf[q] + parity * t.cap + (i - t.lo)));
             g = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int q = 0; q < t.world; ++q) {
-                const float4 v = __ldcv(reinterpret_cast<const float4 *>(t.peer_buf[q] + parity * t.cap + (i - t.lo)));
-                g.x += v.x; g.y += v.y; g.z += v.z; g.w += v.w;
-            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (q < t.world) { g.x += v[q].x; g.y += v[q].y; g.z += v[q].z; g.w += v[q].w; }
         }
     }
     u.x += g.x; u.y += g.y; u.z += g.z; u.w += g.w;

@@ -1316,6 +1316,7 @@ extern "C" int aet_network_comm_exchange_export(aet_network *net, void *blob_80)
 
 extern "C" int aet_network_comm_exchange_attach(aet_network *net, const void *blobs_world_x_80) {
     if (!net || !blobs_world_x_80 || !net->xchg_local) { aet_set_error("aet_network_comm_exchange_attach: export first"); return AET_E_INVALID; }
+    if (net->adam) { aet_set_error("peer exchange refused: the Adam update takes its gradients from the collectives only"); return AET_E_INVALID; }
     const XchgBlob *b = static_cast<const XchgBlob *>(blobs_world_x_80);
     for (int p = 0; p < net->world; ++p)
         for (int q = p + 1; q < net->world; ++q)
