@@ -413,7 +413,9 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
 
 int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
     const ConvGeom &g = a.g;
-    if (!tma_common_ok(l)) return 1;
+    // the filters are the K dimension here: a count that is no multiple of 32 ends in a slab whose tail the copy engine
+    // zero-fills in both operands (the delta's channel dimension and the weight view's filter dimension end there)
+    if (!tma_common_ok(l, false)) return 1;
     if (g.OH != g.H || g.OW != g.W) return 1;   // same-size convolutions only
     cuuint32_t bw, bh, bi;
     int rows_t = 0, per_img = 0;

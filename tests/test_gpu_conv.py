@@ -135,10 +135,12 @@ def test_conv_tma_ragged_maps(aet, ctx, oracle, shape):
 @pytest.mark.parametrize("shape", [
     (8, 256, 1, 1, 1000, 1, 1, 0, 0),      # a 1000-class fully connected layer as a 1x1 convolution
     (3, 64, 8, 8, 100, 3, 1, 1, 2),        # 100 filters, 3x3
+    (4, 96, 13, 13, 50, 3, 1, 1, 1),       # 50 filters (two K slabs, the second 18 wide) on a ragged map
 ])
 def test_conv_tma_forward_takes_any_filter_count(aet, ctx, oracle, shape):
-    """The forward TMA kernel reads the filters as rows of its second operand, so their count need not be a multiple
-    of 32 (rows past the last filter are zero-filled by the copy); the gradients of such a layer use the other kernels."""
+    """The forward TMA kernel reads the filters as rows of its second operand and the data-gradient kernel as its K
+    dimension, so their count need not be a multiple of 32 (what lies past the last filter is zero-filled by the copy);
+    the weight gradient of such a layer uses the other kernels."""
     ctx.set_math(aet.MATH_TF32)
     ctx.profile(1)
     try:
@@ -147,6 +149,7 @@ def test_conv_tma_forward_takes_any_filter_count(aet, ctx, oracle, shape):
     finally:
         ctx.profile(0)
     assert {"conv_fprop_tma", "conv_fprop_tma_rows"} & used, used
+    assert {"conv_dgrad_tma", "conv_dgrad_tma_rows"} & used and "conv_dgrad_gather" not in used, used
     check(got, ref, TOL_TF32)
 
 
