@@ -83,6 +83,7 @@ enum AetOption {
     OPT_RAGGED,            // TMA kernels on maps whose rows do not divide the tile (13x13, 27x27)   AET_NO_RAGGED
     OPT_PAIR,              // CTA pairs sharing the weight tiles (cta_group::2 MMAs) in the row-sharing kernels; off by default   AET_PAIR
     OPT_S2D,               // large strided first-layer filters regrouped into stride-1 convolutions                AET_NO_S2D
+    OPT_FD_SPLIT,          // forward / data gradient of layers with few tiles and a long K loop split over the grid   AET_NO_FD_SPLIT
     OPT_COUNT
 };
 

@@ -622,6 +622,37 @@ int launch_wgrad_reduce(aet_context *ctx, const float *partial, float *dw, size_
     return aet_check_launch("wgrad_reduce");
 }
 
+// Second stage of a split-K forward pass: y = activation(sum over splits + bias), four output columns per thread.
+// `ld` floats per output row (a multiple of 4), bias indexed by column; fixed summation order.
+__global__ void __launch_bounds__(RED_THREADS)
+fprop_reduce_kernel(const float *__restrict__ partial, float *__restrict__ y, const float *__restrict__ bias, size_t count4, int ld4,
+                    int splits, size_t split_stride, int act) {
+    pdl_enter();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count4) return;
+    const float4 *p = reinterpret_cast<const float4 *>(partial) + i;
+    const size_t stride4 = split_stride / 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        const float4 v = __ldcg(p + (size_t)s * stride4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias) {
+        const float4 b = ldg4(bias + (i % (size_t)ld4) * 4);
+        acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+    }
+    acc.x = act_forward(acc.x, act); acc.y = act_forward(acc.y, act); acc.z = act_forward(acc.z, act); acc.w = act_forward(acc.w, act);
+    reinterpret_cast<float4 *>(y)[i] = acc;
+}
+
+int launch_fprop_reduce(aet_context *ctx, const float *partial, float *y, const float *bias, size_t out_floats, int ld, int splits, int act) {
+    const size_t count4 = out_floats / 4;
+    LaunchScope scope(ctx, "fprop_reduce", (double)out_floats * 4.0 * (splits + 1), 0);
+    launch_k(ctx->stream, (unsigned)((count4 + RED_THREADS - 1) / RED_THREADS), RED_THREADS, 0, fprop_reduce_kernel, partial, y, bias, count4,
+             ld / 4, splits, out_floats, act);
+    return aet_check_launch("fprop_reduce");
+}
+
 int pow2_cols(int n) {
     int c = 32;
     while (c < n) c <<= 1;

@@ -139,7 +139,8 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         n0 = tap_w * (a.col_blocks * bn) + cblk_w * bn;
     }
     int slab_begin = 0, nslabs = a.total_slabs;
-    if (KIND == KIND_WGRAD) {
+    const bool split_k = KIND == KIND_WGRAD || gridDim.z > 1;   // forward / data gradient of a layer with few tiles: see fd_splits
+    if (split_k) {
         slab_begin = blockIdx.z * a.slabs_per_split;
         nslabs = a.total_slabs - slab_begin;
         if (nslabs > a.slabs_per_split) nslabs = a.slabs_per_split;
@@ -228,12 +229,14 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t sb = sa + a.a_bytes;
                 mbar_arrive_expect_tx(bar, a.tx_bytes);
                 if (KIND == KIND_FPROP) {
-                    const int tap = it / a.slabs_per_tap, cb = it - tap * a.slabs_per_tap;
+                    const int ig = slab_begin + it;
+                    const int tap = ig / a.slabs_per_tap, cb = ig - tap * a.slabs_per_tap;
                     const int r = tap / a.S, sx = tap - r * a.S;
                     tma_load_4d(sa, &map_a, bar, cb * 32, sx - a.pad, row0 + r - a.pad, img0);
-                    tma_load_2d(sb, &map_b, bar, it * 32, n0);
+                    tma_load_2d(sb, &map_b, bar, ig * 32, n0);
                 } else if (KIND == KIND_DGRAD) {
-                    const int tap = it / a.slabs_per_tap, kb = it - tap * a.slabs_per_tap;
+                    const int ig = slab_begin + it;
+                    const int tap = ig / a.slabs_per_tap, kb = ig - tap * a.slabs_per_tap;
                     const int r = tap / a.S, sx = tap - r * a.S;
                     tma_load_4d(sa, &map_a, bar, kb * 32, a.pad - sx, row0 + a.pad - r, img0);
                     tma_load_4d(sb, &map_b, bar, 0, kb * 32, n0 / 32, tap);
@@ -263,7 +266,7 @@ conv_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         ready = __all_sync(0xffffffffu, ready);   // the TMEM loads below are warp-collective
         tc_fence_after_sync();
         if (ready) {
-            float *obase = a.out + (KIND == KIND_WGRAD ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)m0 * a.out_ld;
+            float *obase = a.out + (split_k ? (size_t)blockIdx.z * a.split_stride : 0) + (size_t)m0 * a.out_ld;
             float *tile = reinterpret_cast<float *>(smem_raw + (smem_base - smem_u32(smem_raw)));
             StatAcc st;
             stat_init(st, KIND == KIND_FPROP ? a.stat_partial ? a.stat_shift : nullptr : nullptr);
@@ -372,6 +375,18 @@ bool tma_common_ok(const aet_layer *l, bool filters_inner = true) {
            g.cp % 32 == 0 && (!filters_inner || g.kp % 32 == 0 || g.kp < 32);
 }
 
+// A forward pass or data gradient with few output tiles and a long K loop (a fully connected layer at the training
+// batch: one 128-row tile, thousands of K slabs) leaves most SMs idle and is bound by what the few CTAs can pull from
+// L2.  Its K range is then split over blockIdx.z like the weight gradient's, the partial tiles go to scratch and a
+// second kernel sums them (and adds bias and activation).  Returns the split count (1 = do not split).
+int fd_splits(const aet_context *ctx, int ctas, int total_slabs) {
+    if (!ctx->opt[OPT_FD_SPLIT] || ctas * 2 > ctx->sm_count || total_slabs < 32) return 1;
+    int splits = ctx->sm_count / ctas;
+    if (splits > 8) splits = 8;
+    while (splits > 1 && total_slabs / splits < 16) --splits;
+    return splits;
+}
+
 int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     const ConvGeom &g = a.g;
     if (!tma_common_ok(l, false)) return 1;
@@ -382,7 +397,15 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
         bw = (cuuint32_t)g.OW; bh = (cuuint32_t)rows_t; bi = 1;
     }
     if (g.OW > g.W || g.OH > g.H) return 1;
-    const int bn = a.bn;                      // any multiple of 16: K-major rows in 8-row swizzle groups
+    int bn = a.bn;                            // any multiple of 16: K-major rows in 8-row swizzle groups
+    const int m_tiles_f = per_img ? g.N * per_img : (a.n_rows + BM - 1) / BM;
+    int splits = 1;
+    if (!a.stat_partial && !per_img) {
+        // with the K range split, wide filter tiles are affordable again (the caller shrank them to get more CTAs)
+        const int wide = a.n_cols >= 128 ? 128 : bn;
+        splits = fd_splits(l->ctx, m_tiles_f * ((a.n_cols + wide - 1) / wide), a.k_total / 32);
+        if (splits > 1) bn = wide;
+    }
     const CUtensorMap *ma, *mb;
     {
         cuuint64_t dims[4] = {(cuuint64_t)g.cp, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
@@ -406,8 +429,18 @@ int tma_fprop(aet_layer *l, const ConvArgs &a, double flops) {
     t.a_bytes = BM * BK * 4;
     t.tx_bytes = (uint32_t)(bw * bh * bi) * BK * 4 + bn * BK * 4;
     t.tiles_per_img = per_img; t.rows_t = rows_t; t.img_h = g.OH;
-    dim3 grid(per_img ? g.N * per_img : (a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
+    dim3 grid(m_tiles_f, (a.n_cols + bn - 1) / bn, splits);
     if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;   // only the forward launcher is given one
+    if (splits > 1) {
+        const size_t out_floats = (size_t)a.n_rows * a.out_ld;
+        float *partial = nullptr;
+        AET_TRY(ctx_scratch(l->ctx, out_floats * splits * sizeof(float), &partial));
+        t.out = partial; t.bias = nullptr; t.act = AET_LINEAR;
+        t.split_stride = (long long)out_floats;
+        t.slabs_per_split = (t.total_slabs + splits - 1) / splits;
+        AET_TRY(launch_tma<KIND_FPROP>(l->ctx, ma, mb, t, grid, "conv_fprop_tma.ks", flops));
+        return launch_fprop_reduce(l->ctx, partial, a.out, a.bias, out_floats, a.out_ld, splits, a.act);
+    }
     return launch_tma<KIND_FPROP>(l->ctx, ma, mb, t, grid, per_img ? "conv_fprop_tma.ragged" : "conv_fprop_tma", flops);
 }
 
@@ -456,6 +489,18 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
     t.tiles_per_img = per_img; t.rows_t = rows_t; t.img_h = g.H;
     dim3 grid(per_img ? g.N * per_img : (a.n_rows + BM - 1) / BM, (a.n_cols + bn - 1) / bn, 1);
     if (a.stat_rows_out) *a.stat_rows_out = (int)grid.x;   // only the forward launcher is given one
+    const int splits = per_img ? 1 : fd_splits(l->ctx, (int)(grid.x * grid.y), t.total_slabs);
+    if (splits > 1) {
+        const size_t out_floats = (size_t)a.n_rows * a.out_ld;
+        float *partial = nullptr;
+        AET_TRY(ctx_scratch(l->ctx, out_floats * splits * sizeof(float), &partial));
+        t.out = partial;
+        t.split_stride = (long long)out_floats;
+        t.slabs_per_split = (t.total_slabs + splits - 1) / splits;
+        grid.z = splits;
+        AET_TRY(launch_tma<KIND_DGRAD>(l->ctx, ma, mb, t, grid, "conv_dgrad_tma.ks", flops));
+        return launch_wgrad_reduce(l->ctx, partial, a.out, out_floats, splits, 0);
+    }
     return launch_tma<KIND_DGRAD>(l->ctx, ma, mb, t, grid, per_img ? "conv_dgrad_tma.ragged" : "conv_dgrad_tma", flops);
 }
 

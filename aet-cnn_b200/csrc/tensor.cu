@@ -121,6 +121,7 @@ const OptionDesc kOptions[OPT_COUNT] = {
     {"ragged", "AET_NO_RAGGED", 1, 0},
     {"pair", "AET_PAIR", 0, 1},
     {"s2d", "AET_NO_S2D", 1, 0},
+    {"fd_split", "AET_NO_FD_SPLIT", 1, 0},
 };
 }  // namespace
 

@@ -153,6 +153,41 @@ def test_conv_tma_forward_takes_any_filter_count(aet, ctx, oracle, shape):
     check(got, ref, TOL_TF32)
 
 
+@pytest.mark.parametrize("shape,split", [
+    # a fully connected layer as a whole-map filter: one 128-row tile, K = 9216 (its data gradient has 16 K slabs: not split)
+    ((128, 256, 6, 6, 512, 6, 1, 0, 1), {"conv_fprop_tma.ks"}),
+    # FC after FC, 500 outputs (the last filter tile and the last K slab are partial)
+    ((96, 1024, 1, 1, 500, 1, 1, 0, 0), {"conv_fprop_tma.ks"}),
+    # 4096 outputs: the data gradient's K range (128 slabs) is split, the forward pass (16 slabs, 32 tiles) is not
+    ((128, 512, 1, 1, 4096, 1, 1, 0, 1), {"conv_dgrad_tma.ks"}),
+    # a small batch of a wide 3x3 layer: three pixel tiles, 72 K slabs (its data gradient runs on the row-sharing kernel)
+    ((6, 256, 8, 8, 256, 3, 1, 1, 2), {"conv_fprop_tma.ks"}),
+    # ... and a 1x1 layer of the same kind, whose data gradient is the plain kernel's: 64 K slabs
+    ((6, 256, 8, 8, 2048, 1, 1, 0, 1), {"conv_dgrad_tma.ks"}),
+])
+def test_conv_few_tiles_split_the_k_range(aet, ctx, oracle, shape, split):
+    """Forward pass and data gradient of a layer with few output tiles and a long K loop split their K range over
+    blockIdx.z and sum the partial tiles in a second kernel (with bias and activation for the forward pass)."""
+    ctx.set_math(aet.MATH_TF32)
+    ctx.profile(1)
+    try:
+        got, ref = conv_case(aet, ctx, oracle, *shape, seed=760 + shape[4], threads=True)
+        used = variants_used(ctx)
+    finally:
+        ctx.profile(0)
+    names = {u.split("#")[0] for u in used}
+    assert split <= names, sorted(names)
+    assert ("fprop_reduce" in names) == ("conv_fprop_tma.ks" in split), sorted(names)
+    check(got, ref, TOL_TF32)
+    ctx.set_option("fd_split", 0)
+    try:
+        plain, _ = conv_case(aet, ctx, oracle, *shape, seed=760 + shape[4], threads=True)
+    finally:
+        ctx.set_option("fd_split", 1)
+    for key in ("y", "dx"):
+        assert rel_l2(got[key].ravel(), plain[key].ravel()) < 2e-3, key
+
+
 # few input channels: the whole K extent fits one stage of the persistent first-layer kernels
 THIN_SHAPES = [
     (2, 3, 8, 8, 5, 3, 1, 1, 2),          # one ragged tile

@@ -240,25 +240,31 @@ def test_bn_statistics_from_conv_epilogue_match_the_separate_pass(aet, ctx, shap
     import aet_cnn_b200.synth as synth
     N, C, H, W, K = shape
     res = {}
-    for tag in ("epilogue", "separate"):
-        ctx.set_option("epilogue_stats", tag == "epilogue")
-        try:
-            layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, 3, 1, 1, 1, aet.LEAKY, 1, 1)
-            layer.write(aet.P_WEIGHTS, synth.normal((K, C, 3, 3), 31, 1, 0.0, 0.2))
-            x = aet.Tensor(ctx, N, C, H, W)
-            x.write(synth.uniform((N, C, H, W), 31, 2))
-            st = aet.make_state(input=x, train=1)
-            ctx.profile(1)
-            layer.forward(st)
-            layer.forward(st)      # second pass: the shift is the first pass's batch mean
-            used = {r["name"].split(".")[0] for r in ctx.profile_read()}
-            ctx.profile(0)
-            assert ("bn_stats" in used) == (tag == "separate"), used
-            res[tag] = (layer.read(aet.P_MEAN), layer.read(aet.P_VARIANCE), layer.read(aet.P_ROLLING_MEAN),
-                        layer.read(aet.P_OUTPUT))
-            layer.close(); x.close()
-        finally:
-            ctx.set_option("epilogue_stats", 1)
+    # (without statistics to gather, a forward pass with few tiles would split its K range and sum in another order:
+    # both runs keep one CTA per tile, so that only the statistics path differs)
+    ctx.set_option("fd_split", 0)
+    try:
+        for tag in ("epilogue", "separate"):
+            ctx.set_option("epilogue_stats", tag == "epilogue")
+            try:
+                layer = aet.ConvolutionalLayer(ctx, N, H, W, C, K, 3, 1, 1, 1, aet.LEAKY, 1, 1)
+                layer.write(aet.P_WEIGHTS, synth.normal((K, C, 3, 3), 31, 1, 0.0, 0.2))
+                x = aet.Tensor(ctx, N, C, H, W)
+                x.write(synth.uniform((N, C, H, W), 31, 2))
+                st = aet.make_state(input=x, train=1)
+                ctx.profile(1)
+                layer.forward(st)
+                layer.forward(st)      # second pass: the shift is the first pass's batch mean
+                used = {r["name"].split(".")[0] for r in ctx.profile_read()}
+                ctx.profile(0)
+                assert ("bn_stats" in used) == (tag == "separate"), used
+                res[tag] = (layer.read(aet.P_MEAN), layer.read(aet.P_VARIANCE), layer.read(aet.P_ROLLING_MEAN),
+                            layer.read(aet.P_OUTPUT))
+                layer.close(); x.close()
+            finally:
+                ctx.set_option("epilogue_stats", 1)
+    finally:
+        ctx.set_option("fd_split", 1)
     for a, b in zip(res["epilogue"], res["separate"]):
         assert np.isfinite(a).all()
         assert rel_l2(a.ravel(), b.ravel()) < 2e-6
