@@ -113,6 +113,7 @@ struct aet_context {
     cudaStream_t side_stream = nullptr, main_stream_saved = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     bool overlap_wgrad = false;   // set by the network around its backward pass
+    bool wgrad_fresh = false;     // set by a training step without subdivisions: the gradient arena is zero when backward starts, the weight gradients may overwrite
     bool on_side = false, side_pending = false;
     int resident_bn_reduce = 0, resident_bn_apply = 0;   // resident blocks per SM of the window-major BN backward kernels (queried once)
     float *scratch_side = nullptr;
@@ -259,6 +260,8 @@ struct aet_network {
     std::vector<int> steps;
     std::vector<float> scales;
     int64_t seen = 0, cur_iteration = 0;
+    bool grad_clean = true;          // the gradient arena is all zero (creation, or an update ran last)
+    bool graph_clean[4] = {true, true, true, true};   // ... as it was when each step graph was captured
     bool bn_fused = false;   // fuseConvBatchnorm ran: inference only from here on
     float loss_scale = 1.0f;
     int try_fix_nan = 0;

@@ -865,15 +865,19 @@ static int conv_wgrad_one(aet_layer *l, const float *x, const float *dy, float *
     const int splits = (total_slabs + slabs_per_split - 1) / slabs_per_split;
     a.k_per_split = slabs_per_split * BK;
     a.split_stride = (long long)out_floats;
-    float *partial = nullptr;
-    AET_TRY(ctx_scratch(ctx, out_floats * splits * sizeof(float), &partial));
+    // One split that overwrites (a training step's first and only gradient of this layer): the tiles go straight to
+    // their place, without the trip through scratch and the second kernel (a fully connected layer's gradient is as
+    // large as its weights and has four K slabs).
+    const bool direct = splits == 1 && !accumulate;
+    float *partial = dw;
+    if (!direct) AET_TRY(ctx_scratch(ctx, out_floats * splits * sizeof(float), &partial));
     a.out = partial;
     int r = tma_wgrad(l, a, splits, flops);
     if (r == 1) {
         dim3 grid(m_tiles, n_tiles, splits);
         r = launch_gather<KIND_WGRAD>(ctx, a, grid, "conv_wgrad_gather", flops);
     }
-    if (r != AET_OK) return r;
+    if (r != AET_OK || direct) return r;
     return launch_wgrad_reduce(ctx, partial, dw, out_floats, splits, accumulate);
 }
 

@@ -443,6 +443,7 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
     ctx_enter(l ? l->ctx : nullptr);
     if (!l) return fail_invalid("null layer");
     l->ctx->prof_tag = l->net ? l->index : -1;
+    if (l->net && !l->ctx->in_network_pass) l->net->grad_clean = false;   // a caller's own backward call accumulates into the arena
     if (!l->delta) return fail_invalid("layer was created with train=0");
     aet_tensor *pd = state.delta;
     if (pd && (pd->n != l->batch || pd->c != l->c || pd->h != l->h || pd->w != l->w))
@@ -492,7 +493,7 @@ extern "C" int aet_layer_backward(aet_layer *l, aet_state state) {
         // In a network's backward pass the weight gradient runs on the side stream, beside the
         // data-gradient chain of this and the earlier layers (both only read this layer's delta).
         if (l->ctx->overlap_wgrad) AET_TRY(side_begin(l->ctx));
-        const int wr = conv_wgrad(l, state.input->d, l->delta->d, layer_G(l), 1);
+        const int wr = conv_wgrad(l, state.input->d, l->delta->d, layer_G(l), l->ctx->wgrad_fresh ? 0 : 1);
         side_end(l->ctx);
         AET_TRY(wr);
         if (pd) {

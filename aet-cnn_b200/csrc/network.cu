@@ -378,11 +378,17 @@ int run_step(aet_network *net, bool final) {
     st.truth = net->truth; st.input = net->input; st.delta = nullptr; st.train = 1;
     AET_TRY(net_forward(net, st));
     st.input = net->input;
-    AET_TRY(net_backward(net, st, final));
+    // every update leaves the gradient arena zero, so without subdivisions this backward pass is the only writer of G
+    net->ctx->wgrad_fresh = net->subdivisions == 1 && net->grad_clean;
+    const int br = net_backward(net, st, final);
+    net->ctx->wgrad_fresh = false;
+    AET_TRY(br);
+    net->grad_clean = false;
     if (!final) return AET_OK;   // gradients keep accumulating in the arena until the group's last call
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(net->adam ? k_adam_arena(net) : k_sgd_arena(net));
     net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
+    net->grad_clean = true;
     return AET_OK;
 }
 
@@ -769,6 +775,7 @@ extern "C" int aet_network_forward(aet_network *net, aet_state state) {
 extern "C" int aet_network_backward(aet_network *net, aet_state state) {
     ctx_enter(net ? net->ctx : nullptr);
     if (!net) { aet_set_error("null network"); return AET_E_INVALID; }
+    net->grad_clean = false;
     return net_backward(net, state);
 }
 extern "C" int aet_network_update(aet_network *net) {
@@ -778,6 +785,7 @@ extern "C" int aet_network_update(aet_network *net) {
     net->ctx->prof_tag = -1;   // the update belongs to no single layer
     if (net->n_blocks) AET_TRY(net->adam ? k_adam_arena(net) : k_sgd_arena(net));
     net->tail_n = 0;           // the published slices are consumed: a second update must not add them again
+    net->grad_clean = true;
     return AET_OK;
 }
 extern "C" float aet_network_cost(aet_network *net) {
@@ -814,11 +822,14 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
     }
     const long before = ctx->launches;
     const int gi = kind + 2 * net->cur_slot;   // a graph holds its tensors' addresses: one per input slot
-    if (net->use_graph && net->graph_exec[gi] && !ctx->profiling) {
+    const bool clean_now = net->subdivisions == 1 && net->grad_clean;
+    if (net->use_graph && net->graph_exec[gi] && !ctx->profiling && net->graph_clean[gi] == clean_now) {
         AET_CUDA(cudaGraphLaunch(net->graph_exec[gi], ctx->stream));
         ctx->launches += net->graph_launches[gi];
+        net->grad_clean = final;
     } else if (net->use_graph && net->eager_runs[kind] > 0 && !ctx->profiling) {
         // an eager step of this kind has sized every scratch buffer; capture this one
+        if (net->graph_exec[gi]) { cudaGraphExecDestroy(net->graph_exec[gi]); net->graph_exec[gi] = nullptr; }   // captured in the other arena state
         cudaGraph_t graph = nullptr;
         AET_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
         ctx->capturing = true;
@@ -828,6 +839,7 @@ extern "C" int aet_network_train_step_device(aet_network *net, float *loss) {
         if (r != AET_OK) { if (graph) cudaGraphDestroy(graph); return r; }
         if (e != cudaSuccess) { aet_set_error("graph capture failed: %s", cudaGetErrorString(e)); return AET_E_CUDA; }
         net->graph_launches[gi] = ctx->launches - before;
+        net->graph_clean[gi] = clean_now;
         e = cudaGraphInstantiate(&net->graph_exec[gi], graph, 0);
         cudaGraphDestroy(graph);
         if (e != cudaSuccess) { aet_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); net->graph_exec[gi] = nullptr; return AET_E_CUDA; }
