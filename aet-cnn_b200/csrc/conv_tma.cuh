@@ -463,6 +463,14 @@ int tma_dgrad(aet_layer *l, const ConvArgs &a, double flops) {
         for (int c = 256; c >= 32; c -= 32)
             if (g.cp % c == 0) { bn = c; break; }
     if (!bn) return 1;
+    if (!per_img && bn < 256) {
+        // where the K range will be split anyway (few tiles, long K), wide channel tiles move fewer bytes per flop
+        int wide = bn;
+        for (int c = 256; c > bn; c -= 32)
+            if (g.cp % c == 0) { wide = c; break; }
+        const int m_tiles_d = (a.n_rows + BM - 1) / BM;
+        if (wide > bn && fd_splits(l->ctx, m_tiles_d * (a.n_cols / wide), g.R * g.S * ((g.kp + 31) / 32)) > 1) bn = wide;
+    }
     const CUtensorMap *ma, *mb;
     {
         cuuint64_t dims[4] = {(cuuint64_t)g.kp, (cuuint64_t)g.OW, (cuuint64_t)g.OH, (cuuint64_t)g.N};
