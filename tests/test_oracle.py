@@ -412,3 +412,35 @@ def test_stopbackward_freezes_the_front_and_dont_update_holds_a_layer(oracle):
         net.train_step(x, t, 0.1, 0.9, 0.01)
         assert not np.array_equal(net.param(2, ob.P_WEIGHTS), start[2])
         assert np.array_equal(net.param(0, ob.P_WEIGHTS), start[0]) and not np.any(net.param(0, ob.P_WEIGHT_UPDATES))
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 23, 23, 5, 11, 4, 0), (2, 3, 17, 21, 4, 7, 2, 3), (1, 1, 20, 20, 3, 6, 3, 1)])
+def test_strided_convolution_equals_its_regrouped_stride_one_form(oracle, shape):
+    """The algebra behind the device library's treatment of large strided first-layer filters, on the oracle alone:
+    with the (zero-padded) input regrouped into s x s pixel blocks and the filter likewise, a stride-s convolution is
+    a ceil(R/s) x ceil(R/s) stride-1 convolution without padding over s*s*C channels - the same products plus zeros -
+    and the real weight gradient is a gather from the regrouped layer's, every tap exactly once."""
+    n, c, h, w, k, size, s, pad = shape
+    rng = np.random.default_rng(size)
+    x = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+    wt = rng.normal(0, 0.3, (k, c, size, size)).astype(np.float32)
+    y = oracle.conv_forward(x, wt, s, s, pad)
+    oh, ow = y.shape[2:]
+    rb = (size + s - 1) // s
+    hb, wb = oh + rb - 1, ow + rb - 1
+    xp = np.zeros((n, c, hb * s, wb * s), np.float32)        # padded on every side, cut to whole blocks
+    hh, ww = min(h, hb * s - pad), min(w, wb * s - pad)
+    xp[:, :, pad:pad + hh, pad:pad + ww] = x[:, :, :hh, :ww]
+    # xb[n][(dy*s + dx)*C + ch][by][bx] = xp[n][ch][by*s + dy][bx*s + dx]
+    xb = xp.reshape(n, c, hb, s, wb, s).transpose(0, 3, 5, 1, 2, 4).reshape(n, s * s * c, hb, wb)
+    wp = np.zeros((k, c, rb * s, rb * s), np.float32)
+    wp[:, :, :size, :size] = wt
+    wbk = wp.reshape(k, c, rb, s, rb, s).transpose(0, 3, 5, 1, 2, 4).reshape(k, s * s * c, rb, rb)
+    yb = oracle.conv_forward(np.ascontiguousarray(xb), np.ascontiguousarray(wbk), 1, 1, 0)
+    assert yb.shape == y.shape
+    np.testing.assert_allclose(yb, y, rtol=1e-5, atol=1e-5)
+    d = rng.normal(0, 1, y.shape).astype(np.float32)
+    dw, _ = oracle.conv_backward(x, wt, d, s, s, pad, need_dx=False)
+    dwb, _ = oracle.conv_backward(np.ascontiguousarray(xb), np.ascontiguousarray(wbk), d, 1, 1, 0, need_dx=False)
+    fold = dwb.reshape(k, s, s, c, rb, rb).transpose(0, 3, 4, 1, 5, 2).reshape(k, c, rb * s, rb * s)[:, :, :size, :size]
+    np.testing.assert_allclose(fold, dw, rtol=1e-4, atol=1e-4)
