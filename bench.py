@@ -444,6 +444,10 @@ def main():
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             if int(flag.item()) == 1:
                 exchange = "peer"
+                # a rank still loading its kernels in the first eager step must not look like a dead peer to the others:
+                # the benchmark waits up to 10 s for a peer's slice (the library's default of 1 s suits a training loop
+                # that wants to notice a lost rank quickly)
+                ctx.set_wait_limit(10_000_000_000)
             else:
                 net.comm_exchange_detach()
 
